@@ -1,0 +1,344 @@
+#!/usr/bin/env python
+"""Headline benchmark: per-MAC rounded float_mm, 8192 x 8192 x 8192, e5m2 multiply and add, round to
+nearest (BASELINE.json metric "float_mm GMAC/s"), plus the elementwise quantizer's HBM throughput.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One step = one float_mm over the whole problem.  With N > 1 (launched by torch.distributed.run, one rank
+per GPU) the M rows of A and C are split across ranks, B is replicated, and every step ends with an
+all-gather of the C row blocks, so the total work is fixed ("strong" scaling).  Prints ONE JSON line on
+rank 0.  Inputs (512 MiB) are larger than L2, so no flush is needed between iterations.
+
+`--impl reference` times the reference's own CPU implementation (oracle/_ref/quant_cpu, the unmodified
+reference extension, when it has been built; otherwise the C restatement in oracle/) on the host cores on a
+bounded row sample of the same problem.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+SIZE = 8192
+FMT = dict(man_add=2, exp_add=5, man_mul=2, exp_mul=5, subnormals=True, saturate=False)
+# Issued thread-instructions per MAC of the GEMM kernel's fast path, measured with ncu
+# (smsp__thread_inst_executed.sum / MACs; see profiles/).  The issue-rate roofline is
+# SMs x 128 lanes x SM clock / I_MAC.
+I_MAC = 10.6
+METRIC = "float_mm GMAC/s (8192^3, e5m2 RN)"
+
+
+# ----------------------------------------------------------------------------------- clocks
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, power, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        try:
+            for line in open(self.path):
+                p = [x.strip() for x in line.split(",")]
+                if len(p) < 7:
+                    continue
+                try:
+                    sm.append(float(p[0])); mx.append(float(p[1])); power.append(float(p[2]))
+                except ValueError:
+                    continue
+                for nm, v in zip(names, p[3:7]):
+                    if v.lower().startswith("active"):
+                        reasons.add(nm)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            # samples under load: the upper half by power draw
+            order = sorted(range(len(sm)), key=lambda i: power[i])
+            load = [sm[i] for i in order[len(order) // 2:]]
+            out = {"sm_mhz": statistics.median(load), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                   "samples": len(sm), "power_w_max": max(power)}
+        return out
+
+
+# ----------------------------------------------------------------------------------- CPU arm
+def _cpu_worker(args):
+    """Times the reference CPU float_mm on `rows` rows of the 8192-wide problem (one process, one core)."""
+    rows, k, n, seed, use_ref = args
+    import numpy as np
+    import torch
+
+    torch.set_num_threads(1)
+    g = torch.Generator().manual_seed(seed)
+    a = torch.randn(rows, k, generator=g)
+    b = torch.randn(k, n, generator=g)
+    if use_ref:
+        from oracle.build_ref import load_ref
+
+        ref = load_ref("quant_cpu")
+        c = torch.zeros(rows, n)
+        t0 = time.perf_counter()
+        ref.float_quantize_nearest_mm(a, b, c, rows, n, k, FMT["man_add"], FMT["exp_add"], FMT["man_mul"],
+                                      FMT["exp_mul"], True, False, False)
+        return time.perf_counter() - t0
+    os.environ["OMP_NUM_THREADS"] = "1"
+    from oracle import loader
+
+    an, bn = a.numpy(), b.numpy()
+    t0 = time.perf_counter()
+    loader.mm(an, bn, FMT["man_add"], FMT["exp_add"], FMT["man_mul"], FMT["exp_mul"], True, False, False, "seq")
+    return time.perf_counter() - t0
+
+
+def cpu_baseline(rows_per_core: int = 1, cores: int | None = None) -> dict:
+    """All host cores, one process each (the reference CPU path is single threaded), each on its own rows."""
+    import multiprocessing as mp
+
+    from oracle.build_ref import load_ref
+
+    cores = cores or os.cpu_count() or 1
+    use_ref = load_ref("quant_cpu") is not None
+    ctx = mp.get_context("spawn")
+    t0 = time.perf_counter()
+    with ctx.Pool(cores) as pool:
+        times = pool.map(_cpu_worker, [(rows_per_core, SIZE, SIZE, 100 + i, use_ref) for i in range(cores)])
+    wall = max(times)
+    macs = cores * rows_per_core * SIZE * SIZE
+    return {"value": macs / wall / 1e9, "unit": "GMAC/s", "cores": cores, "kind": "reference" if use_ref else "port",
+            "sample": "%d rows of the 8192x8192x8192 problem per core (%d MACs total), sequential K order; "
+                      "slowest core %.1f s" % (rows_per_core, macs, wall),
+            "pool_wall_s": time.perf_counter() - t0}
+
+
+def run_reference(args) -> int:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    res = []
+    for _ in range(args.warmup if args.warmup < 1 else 1):
+        cpu_baseline(1)
+    for _ in range(max(1, min(args.steps, 3))):
+        res.append(cpu_baseline(1))
+    best = max(res, key=lambda r: r["value"])
+    steps = len(res)
+    ms = statistics.mean(r["pool_wall_s"] for r in res) * 1e3
+    line = {"impl": "reference", "metric": METRIC, "value": best["value"], "unit": "GMAC/s", "n_gpus": args.gpus,
+            "steps": steps, "warmup": 1, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32 (each multiply and add rounded to e5m2)", "data": "synthetic",
+            "config": {"workload": "float_mm 8192x8192x8192 e5m2/e5m2 nearest, reference CPU path on a row sample",
+                       "accum_order": "seq"},
+            "cpu_baseline": {k: best[k] for k in ("value", "unit", "cores", "kind", "sample")},
+            "e2e": {"value": best["value"], "unit": "GMAC/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line))
+    return 0
+
+
+# ----------------------------------------------------------------------------------- GPU arm
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--size", type=int, default=SIZE, help="M=N=K (the headline is 8192)")
+    ap.add_argument("--order", default="cuda", choices=["cuda", "seq"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch
+    import torch.distributed as dist
+
+    from mptorch_b200 import backend as be
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    S = args.size
+    assert S % world == 0
+    rows = S // world
+    warmup = max(args.warmup, 3)
+
+    g = torch.Generator(device=dev).manual_seed(1234)
+    a_full = torch.randn(S, S, device=dev, generator=g)      # same on every rank
+    b = torch.randn(S, S, device=dev, generator=g)
+    a = a_full[rank * rows:(rank + 1) * rows].contiguous()
+    del a_full
+    c_full = torch.empty(S, S, device=dev)
+    c = c_full[rank * rows:(rank + 1) * rows]
+
+    def step():
+        be.float_quantize_nearest_mm(a, b, c, rows, S, S, FMT["man_add"], FMT["exp_add"], FMT["man_mul"],
+                                     FMT["exp_mul"], True, False, False, order=args.order)
+        if world > 1:
+            dist.all_gather_into_tensor(c_full, c)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    for _ in range(warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    kev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    e0.record()
+    for i in range(args.steps):
+        kev[i][0].record()
+        be.float_quantize_nearest_mm(a, b, c, rows, S, S, FMT["man_add"], FMT["exp_add"], FMT["man_mul"],
+                                     FMT["exp_mul"], True, False, False, order=args.order)
+        kev[i][1].record()
+        if world > 1:
+            dist.all_gather_into_tensor(c_full, c)
+    e1.record()
+    barrier()
+    total_ms = e0.elapsed_time(e1)
+    kern_ms = statistics.mean(x.elapsed_time(y) for x, y in kev)
+    clocks = sampler.stop() if rank == 0 else None
+    t = torch.tensor([total_ms, kern_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms, kern_ms = t.tolist()
+    ms_per_step = total_ms / args.steps
+    macs = float(S) ** 3
+
+    # ---- end to end through the public API with host buffers (H2D of A shard and B, D2H of the C shard)
+    from mptorch_b200.quant import float_mm
+
+    ah = torch.empty(rows, S).pin_memory(); ah.copy_(a)
+    bh = torch.empty(S, S).pin_memory(); bh.copy_(b)
+    ch = torch.empty(rows, S).pin_memory()
+    e2e_steps = max(1, min(args.steps, 3))
+
+    def e2e_step():
+        ad = ah.to(dev, non_blocking=True)
+        bd = bh.to(dev, non_blocking=True)
+        cd = float_mm(ad, bd, man_add=2, exp_add=5, man_mul=2, exp_mul=5, rounding="nearest", fma=False,
+                      subnormals=True, saturate=False)
+        if world > 1:
+            dist.all_gather_into_tensor(c_full, cd)
+        ch.copy_(cd, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    s1.record()
+    barrier()
+    t = torch.tensor([s0.elapsed_time(s1)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = t.item() / e2e_steps
+
+    # ---- elementwise quantizer, HBM bound: 2^28 elements, e4m3 nearest (BASELINE config 2)
+    quant = None
+    if rank == 0:
+        del ah, bh
+        n = 1 << 28
+        x = torch.randn(n, device=dev, generator=g)
+        for _ in range(3):
+            q = be.float_quantize_nearest(x, 3, 4, True, True)
+        torch.cuda.synchronize(dev)
+        q0, q1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 10
+        q0.record()
+        for _ in range(reps):
+            q = be.float_quantize_nearest(x, 3, 4, True, True)
+        q1.record()
+        torch.cuda.synchronize(dev)
+        qms = q0.elapsed_time(q1) / reps
+        quant = {"gbs": 8.0 * n / qms / 1e6, "ms": qms}
+        del x, q
+
+    if rank == 0:
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except Exception:
+            pass
+        hbm_peak, peak_src = (peaks["hbm_gbs"], "measured") if "hbm_gbs" in peaks else (6650.0, "fallback")
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        clk = (clocks or {}).get("sm_mhz") or peaks.get("sm_max_mhz") or 1965.0
+        issue_peak = sms * 128 * clk * 1e6 / I_MAC / 1e9          # GMAC/s per GPU at the sampled clock
+        achieved = macs / world / kern_ms / 1e6                   # GMAC/s of one GPU's kernel
+        line = {
+            "metric": METRIC, "value": macs / ms_per_step / 1e6, "unit": "GMAC/s", "n_gpus": world,
+            "steps": args.steps, "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None,
+            "dtype": "f32 (each multiply and add rounded to e5m2)", "data": "synthetic",
+            "config": {"workload": "float_mm %dx%dx%d, mul e5m2 / add e5m2, nearest, subnormals, no saturate, "
+                                   "M rows sharded over %d GPU(s)%s" % (S, S, S, world, ", all-gather of C" if world > 1 else ""),
+                       "accum_order": args.order, "l2": "inputs (512 MiB) exceed L2, no flush"},
+            "clocks": clocks,
+            "e2e": {"value": macs / e2e_ms / 1e6, "unit": "GMAC/s", "h2d_bytes_per_step": 4 * (rows * S + S * S),
+                    "d2h_bytes_per_step": 4 * rows * S, "ms_per_step": e2e_ms},
+            "gpu_launches": 4 * args.steps,
+            "roofline": {"bound": "issue", "achieved": achieved, "peak": issue_peak, "unit": "GMAC/s",
+                         "frac": achieved / issue_peak, "traffic": None,
+                         "note": "CUDA-core issue roofline: %d SMs x 128 lanes x %.0f MHz / %.1f instructions per MAC"
+                                 % (sms, clk, I_MAC)},
+            "roofline_quantize": {"bound": "hbm", "achieved": quant["gbs"], "peak": hbm_peak, "unit": "GB/s",
+                                  "frac": quant["gbs"] / hbm_peak, "traffic": None, "peak_source": peak_src,
+                                  "kernel": "float_quantize_nearest e4m3, 2^28 elements, 8 B/element"},
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            try:
+                cb = cpu_baseline(1)
+                line["cpu_baseline"] = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
+            except Exception as ex:  # the baseline is a reported figure, never a reason to lose the bench line
+                line["cpu_baseline"] = {"value": None, "unit": "GMAC/s", "cores": 0, "kind": "port", "sample": "failed: %r" % (ex,)}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

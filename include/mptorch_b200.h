@@ -1,0 +1,136 @@
+/*
+ * mptorch_b200.h -- C ABI of the B200 (sm_100a) simulated-arithmetic kernels.
+ *
+ * Drop-in boundary: each entry point below replaces one function of the reference's
+ * `quant_cuda` pybind11 module (mptorch/quant/quant_cuda/pybind_cuda.cpp); the citation
+ * beside each declaration names the registration it stands in for.  Signatures carry only
+ * plain pointers, sizes and format parameters: no torch types.
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer to fp32 data in row-major contiguous layout unless
+ *     stated otherwise; inputs are never modified; outputs are fully overwritten (no
+ *     pre-zeroing needed, unlike the reference);
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream); all
+ *     work is enqueued on it and the call returns without synchronising;
+ *   - the current CUDA device must be the one that owns the pointers;
+ *   - a format is (man, exp, subnormals, saturate): mantissa bits 0..23 (hidden bit not
+ *     counted), exponent bits 1..8, and two flags (0/1);
+ *   - no entry point allocates or frees device memory; where scratch space is needed the
+ *     caller passes it as `workspace`;
+ *   - return value: MPT_OK, or an error code; mpt_last_error() gives a message for the
+ *     calling thread.
+ */
+#ifndef MPTORCH_B200_H
+#define MPTORCH_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define MPT_API __attribute__((visibility("default")))
+#else
+#define MPT_API
+#endif
+
+enum {
+    MPT_OK = 0,
+    MPT_ERR_INVALID_ARGUMENT = 1,
+    MPT_ERR_CUDA = 2,
+    MPT_ERR_WORKSPACE = 3
+};
+
+/* rounding modes of the elementwise quantizers */
+enum { MPT_RND_NEAREST = 0, MPT_RND_STOCHASTIC = 1, MPT_RND_TRUNCATE = 2 };
+
+/* binary8 overflow policies; values match the reference's OverflowPolicy enum
+ * (quant_cuda/binary8_kernel.h:20-25, registered at pybind_cuda.cpp:784-787) */
+enum { MPT_SATURATE_INFTY = 0, MPT_SATURATE_MAXFLOAT = 1, MPT_SATURATE_MAXFLOAT2 = 2 };
+
+/* K-accumulation order of the GEMMs and association of the row reductions.
+ *   MPT_ORDER_SEQ  : strictly sequential, what the reference CPU path computes
+ *                    (quant_cpu/mm_kernel.h:9-20, softmax.h, layernorm.h)
+ *   MPT_ORDER_CUDA : what the reference CUDA kernels compute: 8-wide K tiles with an inner
+ *                    and an outer accumulator for the GEMM (quant_cuda/mm_kernel.h:34-70),
+ *                    64-way strided partials folded by a shuffle tree for softmax and
+ *                    layernorm (quant_cuda/softmax_kernel.h:5-21, layernorm_kernel.h:29-50) */
+enum { MPT_ORDER_SEQ = 0, MPT_ORDER_CUDA = 1 };
+
+MPT_API const char *mpt_last_error(void);
+MPT_API int mpt_version(void);
+
+/* ---- elementwise quantizers ------------------------------------------------------------- */
+
+/* replaces float_quantize_nearest (pybind_cuda.cpp:44 -> quant.cu:143 -> fp_kernel.cu:164) */
+MPT_API int mpt_float_quantize_nearest(const float *in, float *out, int64_t n, int man, int exp,
+                                       int subnormals, int saturate, void *stream);
+
+/* NEW (no reference counterpart): truncation toward zero with the nearest path's clipping */
+MPT_API int mpt_float_quantize_truncate(const float *in, float *out, int64_t n, int man, int exp,
+                                        int subnormals, int saturate, void *stream);
+
+/* replaces float_quantize_stochastic (pybind_cuda.cpp:98 -> quant.cu:126 -> fp_kernel.cu:150).
+ * `rand` holds one int32 random word per element, as the reference draws with
+ * randint_like(a, INT_MAX); feeding the same words gives the same bits as the reference. */
+MPT_API int mpt_float_quantize_stochastic(const float *in, const int32_t *rand, float *out, int64_t n,
+                                          int man, int exp, int prng_bits, int subnormals, int saturate,
+                                          void *stream);
+
+/* NEW: same rounding with the random words generated in the kernel (Philox4x32-10, key = seed,
+ * counter = element index / 4), which removes the 4 B/element random-word stream. */
+MPT_API int mpt_float_quantize_stochastic_philox(const float *in, float *out, int64_t n, int man, int exp,
+                                                 int prng_bits, int subnormals, int saturate,
+                                                 uint64_t seed, void *stream);
+
+/* replaces binary8_quantize_nearest / _stochastic / _truncate (pybind_cuda.cpp:61,107,115 ->
+ * quant.cu:173-242 -> binary8_kernel.cu:278-342).  `rounding` is an MPT_RND_* value; `rand`
+ * is read only for MPT_RND_STOCHASTIC. */
+MPT_API int mpt_binary8_quantize(const float *in, const int32_t *rand, float *out, int64_t n, int P,
+                                 int is_signed, int overflow_policy, int subnormals, int rounding,
+                                 int prng_bits, void *stream);
+
+/* replaces superfp_quantize_nearest (pybind_cuda.cpp:53 -> quant.cu:158 -> superfp_kernel.cu:70) */
+MPT_API int mpt_superfp_quantize_nearest(const float *in, float *out, int64_t n, int man, int exp,
+                                         int binades_l, int binades_u, int saturate, void *stream);
+
+/* ---- per-MAC rounded GEMM ------------------------------------------------------------------ */
+
+/* Bytes of scratch the GEMM entry points want in `workspace` (device memory, 16-byte aligned).
+ * With workspace == NULL (or too small) they still run, on the slower exact-cast path only. */
+MPT_API size_t mpt_mm_workspace_bytes(void);
+
+/* replaces float_quantize_nearest_mm and _bmm (pybind_cuda.cpp:123,140 -> quant.cu:335,362 ->
+ * fp_kernel.cu:174-245 -> mm_kernel.h:19-132) and their CPU twins (quant_cpu/mm_kernel.h:9-34).
+ *   C[b] = A[b] x B[b],  A: [batch, M, K], B: [batch, K, N], C: [batch, M, N]
+ * every product is rounded to (man_mul, exp_mul) and every sum to (man_add, exp_add); both use the
+ * `subnormals` and `saturate` flags.  order: MPT_ORDER_SEQ or MPT_ORDER_CUDA.
+ * compensated != 0 selects Kahan summation (mm_kernel.h:457-676). */
+MPT_API int mpt_float_mm_nearest(const float *a, const float *b, float *c, int64_t batch, int M, int N, int K,
+                                 int man_add, int exp_add, int man_mul, int exp_mul,
+                                 int subnormals, int saturate, int compensated, int order,
+                                 void *workspace, size_t workspace_bytes, void *stream);
+
+/* replaces float_quantize_nearest_mm_fma and _bmm_fma (pybind_cuda.cpp:157,173 -> quant.cu ->
+ * fp_kernel.cu:247-307 -> mm_kernel.h:134-246): acc = Q(fmaf(a, b, acc)). */
+MPT_API int mpt_float_mm_nearest_fma(const float *a, const float *b, float *c, int64_t batch, int M, int N, int K,
+                                     int man_fma, int exp_fma, int subnormals, int saturate, int compensated,
+                                     int order, void *workspace, size_t workspace_bytes, void *stream);
+
+/* replaces float_quantize_stochastic_mm / _bmm / _mm_fma / _bmm_fma (pybind_cuda.cpp:254-300 ->
+ * fp_kernel.cu:309-415 -> mm_kernel.h:248-455).  Single accumulator over the zero-padded K range.
+ * The reference draws from a per-block cuRAND state seeded by the clock and is not reproducible;
+ * here the random words come from Philox4x32-10 keyed by `seed` with counter (k, output index), so
+ * results are a pure function of the inputs and the seed.  fma != 0 uses (man_add, exp_add,
+ * rbits_add) as the FMA format. */
+MPT_API int mpt_float_mm_stochastic(const float *a, const float *b, float *c, int64_t batch, int M, int N, int K,
+                                    int man_add, int exp_add, int rbits_add,
+                                    int man_mul, int exp_mul, int rbits_mul,
+                                    int subnormals, int saturate, int fma, uint64_t seed, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MPTORCH_B200_H */

@@ -1,0 +1,94 @@
+"""ctypes binding of the C ABI declared in ``include/mptorch_b200.h``.
+
+This is the only place the Python package touches the native library.  There is no fallback:
+if the library has not been built (``python -m mptorch_b200.build``) or a call fails, an
+exception is raised.  Tensors are torch CUDA tensors; torch is used for device memory and the
+current stream only.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import torch
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "lib", "libmptorch_b200.so")
+
+_lib = None
+
+
+class MptError(RuntimeError):
+    pass
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise MptError(
+                "the CUDA library %s is missing; build it with `python -m mptorch_b200.build` "
+                "(there is no CPU fallback)" % LIB_PATH)
+        L = C.CDLL(LIB_PATH)
+        p, i32, i64, u64, sz = C.c_void_p, C.c_int, C.c_int64, C.c_uint64, C.c_size_t
+        L.mpt_last_error.restype = C.c_char_p
+        L.mpt_version.restype = i32
+        L.mpt_mm_workspace_bytes.restype = sz
+        sig = {
+            "mpt_float_quantize_nearest": [p, p, i64, i32, i32, i32, i32, p],
+            "mpt_float_quantize_truncate": [p, p, i64, i32, i32, i32, i32, p],
+            "mpt_float_quantize_stochastic": [p, p, p, i64, i32, i32, i32, i32, i32, p],
+            "mpt_float_quantize_stochastic_philox": [p, p, i64, i32, i32, i32, i32, i32, u64, p],
+            "mpt_binary8_quantize": [p, p, p, i64, i32, i32, i32, i32, i32, i32, p],
+            "mpt_superfp_quantize_nearest": [p, p, i64, i32, i32, i32, i32, i32, p],
+            "mpt_float_mm_nearest": [p, p, p, i64, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, p, sz, p],
+            "mpt_float_mm_nearest_fma": [p, p, p, i64, i32, i32, i32, i32, i32, i32, i32, i32, i32, p, sz, p],
+            "mpt_float_mm_stochastic": [p, p, p, i64, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, u64, p],
+        }
+        for name, args in sig.items():
+            fn = getattr(L, name, None)
+            if fn is None:
+                continue
+            fn.restype = i32
+            fn.argtypes = args
+        _lib = L
+    return _lib
+
+
+def call(name: str, *args) -> None:
+    fn = getattr(lib(), name)
+    rc = fn(*args)
+    if rc != 0:
+        raise MptError("%s failed (code %d): %s" % (name, rc, lib().mpt_last_error().decode()))
+
+
+def check_cuda_f32(t: torch.Tensor, what: str) -> None:
+    """Mirrors the reference's CHECK_INPUT (quant_cuda/pybind_cuda.cpp:8-13) plus a dtype check."""
+    if not t.is_cuda:
+        raise RuntimeError("%s must be a CUDA tensor" % what)
+    if not t.is_contiguous():
+        raise RuntimeError("%s must be contiguous" % what)
+    if t.dtype != torch.float32:
+        raise RuntimeError("%s must be float32" % what)
+
+
+def ptr(t: torch.Tensor | None):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def stream_ptr(device: torch.device):
+    return C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+_workspaces: dict[tuple[int, int], torch.Tensor] = {}
+
+
+def mm_workspace(device: torch.device) -> torch.Tensor:
+    """A small per-(device, stream) scratch buffer for the GEMM's operand statistics."""
+    key = (device.index if device.index is not None else torch.cuda.current_device(),
+           torch.cuda.current_stream(device).cuda_stream)
+    ws = _workspaces.get(key)
+    if ws is None:
+        ws = torch.empty(int(lib().mpt_mm_workspace_bytes()), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws

@@ -1,0 +1,244 @@
+"""Host-side mirror of the reference's ``quant_cuda`` extension module.
+
+Function names, argument order and argument meaning follow the pybind registrations in the
+reference's ``mptorch/quant/quant_cuda/pybind_cuda.cpp`` (line numbers cited per function), so
+``mptorch_b200.quant.quant_function`` can call this module exactly where the reference calls
+``quant_cuda``.  Each function checks its tensors the way the reference's ``CHECK_INPUT`` does,
+allocates outputs, and forwards to the C ABI on the current CUDA stream.
+
+Two knobs exist that the reference does not have, because its CPU and CUDA back ends disagree:
+
+``accum_order``  "cuda" (default) reproduces the CUDA kernels' 8-wide tiled K accumulation,
+                 "seq" the CPU path's strictly sequential accumulation;
+``reduce_order`` same choice for the softmax / layernorm row reductions.
+"""
+from __future__ import annotations
+
+import contextlib
+import enum
+
+import torch
+
+from . import _cabi
+from ._cabi import call, check_cuda_f32, ptr, stream_ptr
+
+INT_MAX = 2147483647
+
+
+class OverflowPolicy(enum.IntEnum):
+    """reference: quant_cuda/binary8_kernel.h:20-25, pybind_cuda.cpp:784-787."""
+    SATURATE_INFTY = 0
+    SATURATE_MAXFLOAT = 1
+    SATURATE_MAXFLOAT2 = 2
+
+
+_ORDER = {"seq": 0, "cuda": 1, "tile8": 1, "tree64": 1}
+_state = {"accum_order": "cuda", "reduce_order": "cuda"}
+
+
+def set_accum_order(order: str) -> None:
+    if order not in _ORDER:
+        raise ValueError("accum_order must be 'cuda' or 'seq'")
+    _state["accum_order"] = order
+
+
+def set_reduce_order(order: str) -> None:
+    if order not in _ORDER:
+        raise ValueError("reduce_order must be 'cuda' or 'seq'")
+    _state["reduce_order"] = order
+
+
+def get_accum_order() -> str:
+    return _state["accum_order"]
+
+
+def get_reduce_order() -> str:
+    return _state["reduce_order"]
+
+
+@contextlib.contextmanager
+def orders(accum: str | None = None, reduce: str | None = None):
+    """Temporarily select accumulation / reduction orders."""
+    old = dict(_state)
+    try:
+        if accum is not None:
+            set_accum_order(accum)
+        if reduce is not None:
+            set_reduce_order(reduce)
+        yield
+    finally:
+        _state.update(old)
+
+
+def _order_code(order: str | None, kind: str) -> int:
+    return _ORDER[_state[kind] if order is None else order]
+
+
+# ---------------------------------------------------------------------------------- quantizers
+def float_quantize_nearest(a, man_bits, exp_bits, subnormals, saturate):
+    """pybind_cuda.cpp:44."""
+    check_cuda_f32(a, "a")
+    o = torch.empty_like(a)
+    with torch.cuda.device(a.device):
+        call("mpt_float_quantize_nearest", ptr(a), ptr(o), a.numel(), man_bits, exp_bits, int(subnormals),
+             int(saturate), stream_ptr(a.device))
+    return o
+
+
+def float_quantize_truncate(a, man_bits, exp_bits, subnormals, saturate):
+    """New: no counterpart in the reference."""
+    check_cuda_f32(a, "a")
+    o = torch.empty_like(a)
+    with torch.cuda.device(a.device):
+        call("mpt_float_quantize_truncate", ptr(a), ptr(o), a.numel(), man_bits, exp_bits, int(subnormals),
+             int(saturate), stream_ptr(a.device))
+    return o
+
+
+def float_quantize_stochastic(a, man_bits, exp_bits, prng_bits, subnormals, saturate, rand=None, seed=None):
+    """pybind_cuda.cpp:98.  By default the random words are drawn exactly as the reference draws them
+    (``randint_like(a, INT_MAX)`` from the torch CUDA generator, quant_cuda/quant.cu:132), so results
+    match the reference under the same ``torch.manual_seed``.  ``rand`` supplies the words explicitly;
+    ``seed`` switches to the in-kernel Philox generator (no random-word tensor at all)."""
+    check_cuda_f32(a, "a")
+    o = torch.empty_like(a)
+    with torch.cuda.device(a.device):
+        if seed is not None:
+            call("mpt_float_quantize_stochastic_philox", ptr(a), ptr(o), a.numel(), man_bits, exp_bits, prng_bits,
+                 int(subnormals), int(saturate), int(seed) & (2**64 - 1), stream_ptr(a.device))
+        else:
+            if rand is None:
+                rand = torch.randint_like(a, INT_MAX, dtype=torch.int32)
+            if not (rand.is_cuda and rand.is_contiguous() and rand.dtype == torch.int32 and rand.numel() == a.numel()):
+                raise RuntimeError("rand must be a contiguous CUDA int32 tensor with one word per element")
+            call("mpt_float_quantize_stochastic", ptr(a), ptr(rand), ptr(o), a.numel(), man_bits, exp_bits, prng_bits,
+                 int(subnormals), int(saturate), stream_ptr(a.device))
+    return o
+
+
+def _binary8(a, P, is_signed, overflow_policy, subnormals, rounding, prng_bits=0, rand=None):
+    check_cuda_f32(a, "a")
+    o = torch.empty_like(a)
+    with torch.cuda.device(a.device):
+        if rounding == 1:
+            if rand is None:
+                rand = torch.randint_like(a, INT_MAX, dtype=torch.int32)
+            if not (rand.is_cuda and rand.is_contiguous() and rand.dtype == torch.int32 and rand.numel() == a.numel()):
+                raise RuntimeError("rand must be a contiguous CUDA int32 tensor with one word per element")
+        call("mpt_binary8_quantize", ptr(a), ptr(rand), ptr(o), a.numel(), P, int(is_signed), int(overflow_policy),
+             int(subnormals), rounding, prng_bits, stream_ptr(a.device))
+    return o
+
+
+def binary8_quantize_nearest(a, P, is_signed, overflow_policy, subnormals):
+    """pybind_cuda.cpp:61."""
+    return _binary8(a, P, is_signed, overflow_policy, subnormals, 0)
+
+
+def binary8_quantize_stochastic(a, P, prng_bits, is_signed, overflow_policy, subnormals, rand=None):
+    """pybind_cuda.cpp:107 (random words drawn as quant_cuda/quant.cu:202 does unless given)."""
+    return _binary8(a, P, is_signed, overflow_policy, subnormals, 1, prng_bits, rand)
+
+
+def binary8_quantize_truncate(a, P, is_signed, overflow_policy, subnormals):
+    """pybind_cuda.cpp:115."""
+    return _binary8(a, P, is_signed, overflow_policy, subnormals, 2)
+
+
+def superfp_quantize_nearest(a, man_bits, exp_bits, binades_l, binades_u, saturate):
+    """pybind_cuda.cpp:53."""
+    check_cuda_f32(a, "a")
+    o = torch.empty_like(a)
+    with torch.cuda.device(a.device):
+        call("mpt_superfp_quantize_nearest", ptr(a), ptr(o), a.numel(), man_bits, exp_bits, binades_l, binades_u,
+             int(saturate), stream_ptr(a.device))
+    return o
+
+
+# ---------------------------------------------------------------------------------- GEMM
+def _mm_checks(a, b, c):
+    check_cuda_f32(a, "a")
+    check_cuda_f32(b, "b")
+    check_cuda_f32(c, "c")
+
+
+def _batch_of(a) -> int:
+    # the reference reads the batch count from a.sizes()[0] for the bmm entry points (quant.cu:370-379)
+    return a.shape[0] if a.dim() > 2 else 1
+
+
+def _mm_nearest(a, b, c, batch, M, N, K, man_add, exp_add, man_mul, exp_mul, subnormals, saturate, compensated, order):
+    _mm_checks(a, b, c)
+    with torch.cuda.device(a.device):
+        ws = _cabi.mm_workspace(a.device)
+        call("mpt_float_mm_nearest", ptr(a), ptr(b), ptr(c), batch, M, N, K, man_add, exp_add, man_mul, exp_mul,
+             int(subnormals), int(saturate), int(compensated), _order_code(order, "accum_order"), ptr(ws), ws.numel(),
+             stream_ptr(a.device))
+
+
+def _mm_nearest_fma(a, b, c, batch, M, N, K, man_fma, exp_fma, subnormals, saturate, compensated, order):
+    _mm_checks(a, b, c)
+    with torch.cuda.device(a.device):
+        ws = _cabi.mm_workspace(a.device)
+        call("mpt_float_mm_nearest_fma", ptr(a), ptr(b), ptr(c), batch, M, N, K, man_fma, exp_fma, int(subnormals),
+             int(saturate), int(compensated), _order_code(order, "accum_order"), ptr(ws), ws.numel(),
+             stream_ptr(a.device))
+
+
+def float_quantize_nearest_mm(a, b, c, M, N, K, man_add, exp_add, man_mul, exp_mul, subnormals, saturate,
+                              compensated, order=None):
+    """pybind_cuda.cpp:123.  Note the (M, N, K) argument order of the reference."""
+    _mm_nearest(a, b, c, 1, M, N, K, man_add, exp_add, man_mul, exp_mul, subnormals, saturate, compensated, order)
+
+
+def float_quantize_nearest_bmm(a, b, c, M, N, K, man_add, exp_add, man_mul, exp_mul, subnormals, saturate,
+                               compensated, order=None):
+    """pybind_cuda.cpp:140."""
+    _mm_nearest(a, b, c, _batch_of(a), M, N, K, man_add, exp_add, man_mul, exp_mul, subnormals, saturate,
+                compensated, order)
+
+
+def float_quantize_nearest_mm_fma(a, b, c, M, N, K, man_fma, exp_fma, subnormals, saturate, compensated, order=None):
+    """pybind_cuda.cpp:157."""
+    _mm_nearest_fma(a, b, c, 1, M, N, K, man_fma, exp_fma, subnormals, saturate, compensated, order)
+
+
+def float_quantize_nearest_bmm_fma(a, b, c, M, N, K, man_fma, exp_fma, subnormals, saturate, compensated, order=None):
+    """pybind_cuda.cpp:173."""
+    _mm_nearest_fma(a, b, c, _batch_of(a), M, N, K, man_fma, exp_fma, subnormals, saturate, compensated, order)
+
+
+def _mm_sr(a, b, c, batch, M, N, K, man_add, exp_add, rbits_add, man_mul, exp_mul, rbits_mul, subnormals, saturate,
+           fma, seed):
+    _mm_checks(a, b, c)
+    if seed is None:
+        # one draw from the torch generator keeps runs reproducible under torch.manual_seed
+        seed = int(torch.randint(0, 2**62, (1,), dtype=torch.int64).item())
+    with torch.cuda.device(a.device):
+        call("mpt_float_mm_stochastic", ptr(a), ptr(b), ptr(c), batch, M, N, K, man_add, exp_add, rbits_add, man_mul,
+             exp_mul, rbits_mul, int(subnormals), int(saturate), int(fma), int(seed) & (2**64 - 1),
+             stream_ptr(a.device))
+
+
+def float_quantize_stochastic_mm(a, b, c, M, N, K, man_add, exp_add, rbits_add, man_mul, exp_mul, rbits_mul,
+                                 subnormals, saturate, seed=None):
+    """pybind_cuda.cpp:254."""
+    _mm_sr(a, b, c, 1, M, N, K, man_add, exp_add, rbits_add, man_mul, exp_mul, rbits_mul, subnormals, saturate, False, seed)
+
+
+def float_quantize_stochastic_bmm(a, b, c, M, N, K, man_add, exp_add, rbits_add, man_mul, exp_mul, rbits_mul,
+                                  subnormals, saturate, seed=None):
+    """pybind_cuda.cpp:270."""
+    _mm_sr(a, b, c, _batch_of(a), M, N, K, man_add, exp_add, rbits_add, man_mul, exp_mul, rbits_mul, subnormals,
+           saturate, False, seed)
+
+
+def float_quantize_stochastic_mm_fma(a, b, c, M, N, K, man_fma, exp_fma, rbits_fma, subnormals, saturate, seed=None):
+    """pybind_cuda.cpp:286."""
+    _mm_sr(a, b, c, 1, M, N, K, man_fma, exp_fma, rbits_fma, man_fma, exp_fma, rbits_fma, subnormals, saturate, True, seed)
+
+
+def float_quantize_stochastic_bmm_fma(a, b, c, M, N, K, man_fma, exp_fma, rbits_fma, subnormals, saturate, seed=None):
+    """pybind_cuda.cpp:300."""
+    _mm_sr(a, b, c, _batch_of(a), M, N, K, man_fma, exp_fma, rbits_fma, man_fma, exp_fma, rbits_fma, subnormals,
+           saturate, True, seed)

@@ -1,0 +1,325 @@
+// Device-side rounding primitives for simulated low-precision arithmetic.
+//
+// Two families live here:
+//   * exact casters (`cast_fp_nearest`, `cast_fp_truncate`, `cast_fp_stochastic`,
+//     `cast_binary8`, `cast_superfp`): complete restatements of the reference
+//     semantics (mptorch quant_cuda/fp_kernel.cu:12-129, binary8_kernel.cu:11-276,
+//     superfp_kernel.cu:12-68, bit_helper.cu), valid for every input pattern and
+//     every format, including the reference's corner-case behaviour.
+//   * the "magic add" fast path (`FastRn`): round-to-nearest-even on the FP32 pipe,
+//     bit-identical to the exact caster on the value range its caller guarantees.
+#pragma once
+#include <cmath>
+#include <cstdint>
+#include <cstring>
+#include <cuda_runtime.h>
+
+namespace mpt {
+
+// Every caster is __host__ __device__ so that the identical source can be swept on the CPU
+// against the oracle (tests/host_cast_check.cu); the library only ever runs the device side.
+#define MPT_HD __host__ __device__ __forceinline__
+
+MPT_HD uint32_t f2u(float x) {
+#ifdef __CUDA_ARCH__
+    return f2u(x);
+#else
+    uint32_t u; memcpy(&u, &x, 4); return u;
+#endif
+}
+MPT_HD float u2f(uint32_t u) {
+#ifdef __CUDA_ARCH__
+    return u2f(u);
+#else
+    float x; memcpy(&x, &u, 4); return x;
+#endif
+}
+// fp32 operations that must never be contracted or reassociated
+MPT_HD float fma_rn(float a, float b, float c) {
+#ifdef __CUDA_ARCH__
+    return __fmaf_rn(a, b, c);
+#else
+    return fmaf(a, b, c);
+#endif
+}
+MPT_HD float add_rn(float a, float b) {
+#ifdef __CUDA_ARCH__
+    return __fadd_rn(a, b);
+#else
+    volatile float r = a + b; return r;
+#endif
+}
+MPT_HD float mul_rn(float a, float b) {
+#ifdef __CUDA_ARCH__
+    return __fmul_rn(a, b);
+#else
+    volatile float r = a * b; return r;
+#endif
+}
+
+// Format descriptor for IEEE-like (exp, man) targets; derived fields are filled on the host.
+struct FpFmt {
+    int man;         // mantissa bits kept (0..23)
+    int exp;         // exponent bits (1..8)
+    int min_exp;     // smallest normal exponent: 2 - 2^(exp-1)
+    int max_store;   // biased fp32 exponent of the largest binade: 2^(exp-1) - 1 + 127
+    int sub;         // subnormals supported
+    int sat;         // saturate to max finite instead of overflowing to inf
+};
+
+__host__ __device__ inline FpFmt make_fmt(int man, int exp, int sub, int sat) {
+    FpFmt f;
+    f.man = man; f.exp = exp; f.sub = sub; f.sat = sat;
+    f.min_exp = 2 - (1 << (exp - 1));
+    f.max_store = (1 << (exp - 1)) - 1 + 127;
+    return f;
+}
+
+MPT_HD uint32_t low_mask(int nbits) {       // nbits in 0..32
+    return nbits >= 32 ? 0xFFFFFFFFu : ((1u << nbits) - 1u);
+}
+
+// Round the fp32 pattern t to m mantissa bits, nearest-even; m in -1..23.
+// With m <= 0 at most 23 bits are cleared (cap23), so a tie moves away from zero; the
+// binary8 P=1 format lifts that cap and resolves the tie on the exponent's low bit.
+MPT_HD uint32_t rne_bits(uint32_t t, int m, bool cap23 = true) {
+    if (m >= 23) return t;
+    const int drop = 23 - m;                       // 1..24 bits to discard
+    const uint32_t half = 1u << (drop - 1);
+    if (m >= 1 || !cap23) {
+        // classic integer RNE: add (half - 1) plus the parity of the kept part
+        const uint32_t odd = (t >> drop) & 1u;
+        return (t + (half - 1u) + odd) & ~low_mask(drop);
+    }
+    return (t + half) & ~0x7FFFFFu;
+}
+
+MPT_HD uint32_t max_finite_bits(const FpFmt& f, uint32_t sign) {
+    const uint32_t man_field = (0x7FFFFFu >> (23 - f.man)) << (23 - f.man);
+    return sign | ((uint32_t)f.max_store << 23) | man_field;
+}
+
+// After rounding in the subnormal range: anything that landed below the smallest
+// subnormal's binade is bumped up one binade (if adjacent) or flushed.
+MPT_HD uint32_t settle_subnormal(const FpFmt& f, uint32_t t, uint32_t q) {
+    if (q == 0u) return 0u;
+    const int qe = (int)((q << 1) >> 24);
+    const int floor_store = f.min_exp - f.man + 127;
+    if (qe < floor_store) {
+        if (qe != floor_store - 1) return 0u;
+        q = (q + 0x00800000u) | (t & 0x80000000u);
+    }
+    return q;
+}
+
+// After rounding in the normal range: overflow to inf / max finite; values below the
+// smallest normal (only reachable without subnormals) snap to it or to signed zero.
+MPT_HD uint32_t settle_normal(const FpFmt& f, uint32_t t, uint32_t q) {
+    if (q == 0u) return 0u;
+    const int qe = (int)((q << 1) >> 24);
+    const uint32_t sign = t & 0x80000000u;
+    const int min_store = f.min_exp + 127;
+    if (qe > f.max_store) return f.sat ? max_finite_bits(f, sign) : (sign | 0x7F800000u);
+    if (qe < min_store) {
+        const bool up = (qe == min_store - 1) && ((t & 0x7FFFFFu) > 0x400000u);
+        return (up ? ((uint32_t)min_store << 23) : 0u) | sign;
+    }
+    return q;
+}
+
+template <bool TRUNC>
+MPT_HD float cast_fp_exact(float x, const FpFmt& f) {
+    if (f.man >= 23 && f.exp >= 8) return x;
+    const uint32_t t = f2u(x);
+    const int E = (int)((t << 1) >> 24) - 127;
+    if (f.sub && E < f.min_exp) {
+        const int d = f.man - (f.min_exp - E);       // mantissa bits left in this binade
+        uint32_t q;
+        if (TRUNC) q = (d >= 0) ? (t & ~low_mask(23 - d)) : 0u;
+        else {
+            const bool keep = (d >= 0) || (d == -1 && (t << 9) != 0u);
+            q = keep ? rne_bits(t, d) : 0u;
+        }
+        return u2f(settle_subnormal(f, t, q));
+    }
+    if (E == 128) return x;
+    const uint32_t q = TRUNC ? (t & ~low_mask(23 - f.man)) : rne_bits(t, f.man);
+    return u2f(settle_normal(f, t, q));
+}
+
+MPT_HD float cast_fp_nearest(float x, const FpFmt& f) { return cast_fp_exact<false>(x, f); }
+MPT_HD float cast_fp_truncate(float x, const FpFmt& f) { return cast_fp_exact<true>(x, f); }
+
+// Stochastic rounding with an explicit 32-bit random word.  No NaN/inf early-out exists on
+// this path in the reference: the exponent clip decides.
+MPT_HD float cast_fp_stochastic(float x, uint32_t r, int rbits, const FpFmt& f) {
+    const uint32_t t = f2u(x);
+    const int E = (int)((t << 1) >> 24) - 127;
+    r &= 0x7FFFFFu;
+    const int sh = 23 - f.man - rbits - 1;           // the reference clears this single bit
+    if (sh >= 0 && sh <= 31) r &= ~(1u << sh);
+    const uint32_t mask = low_mask(23 - f.man);
+    if (f.sub && E < f.min_exp) {
+        // lift into the smallest normal binade, round there, and come back down
+        const float lift = u2f(((uint32_t)(127 + f.min_exp) << 23) | (t & 0x80000000u));
+        const uint32_t v = f2u(add_rn(x, lift));
+        const uint32_t q = (v + (r & mask)) & ~mask;
+        return add_rn(u2f(q), -lift);
+    }
+    uint32_t q = (t + (r & mask)) & ~mask;
+    if (q == 0u) return 0.0f;
+    const int qe = (int)((q << 1) >> 24);
+    const uint32_t sign = t & 0x80000000u;
+    const int min_store = f.min_exp + 127;
+    if (qe > f.max_store) q = f.sat ? max_finite_bits(f, sign) : (sign | 0x7F800000u);
+    else if (qe < min_store) {
+        const uint32_t middle = (uint32_t)(min_store - 1) << 23;
+        q = ((q & 0x7FFFFFFFu) > middle) ? (sign | ((uint32_t)min_store << 23)) : 0u;
+    }
+    return u2f(q);
+}
+
+// ---- P3109 binary8 ------------------------------------------------------------------
+enum : int { B8_INFTY = 0, B8_MAXFLOAT = 1, B8_MAXFLOAT2 = 2 };
+enum : int { RND_NEAREST = 0, RND_STOCHASTIC = 1, RND_TRUNCATE = 2 };
+
+MPT_HD uint32_t binary8_settle(int exp_bits, int man_bits, uint32_t t, uint32_t q,
+                                                   int policy, bool sub) {
+    if (q == 0u) return 0u;
+    const uint32_t qman = q & 0x7FFFFFu;
+    const uint32_t sign = t & 0x80000000u;
+    const uint32_t ones = (1u << man_bits) - 1u;
+    const int up = 23 - man_bits;
+    uint32_t top_man = (ones & ~1u) << up;           // all-ones pattern is reserved
+    int reserve_exp = 0;
+    if (policy == B8_MAXFLOAT2) {
+        if (exp_bits + man_bits == 7) top_man = ones << up;
+    } else if (exp_bits == 8) {
+        reserve_exp = 1;
+    } else if (exp_bits == 7 && man_bits == 1) {
+        reserve_exp = 1; top_man = ones << up;
+    } else if (exp_bits + man_bits == 8) {
+        top_man = (ones - 2u) << up;                 // wraps for man_bits < 2, as the reference does
+    }
+    const int qe = (int)((q << 1) >> 24);
+    const int hi = (1 << (exp_bits - 1)) - 1 + 127 - reserve_exp;
+    const int lo = 127 - ((1 << (exp_bits - 1)) - 1) + (man_bits == 0 ? 1 : 0) - (sub ? 0 : 1);
+    if (qe > hi || (qe == hi && qman > top_man)) {
+        if (policy == B8_INFTY) return sign | 0x7F800000u;
+        q = sign | ((uint32_t)hi << 23) | top_man;
+    }
+    const uint32_t unit = 1u << up;
+    if (qe < lo || (qe == lo && qman < unit)) {      // decided on the pre-overflow fields
+        const uint32_t mag = t & 0x7FFFFFFFu;
+        if (sub) {
+            if (lo - qe > man_bits) {
+                const int tiny = lo - man_bits;
+                q = (mag > ((uint32_t)(tiny - 1) << 23)) ? (sign | ((uint32_t)tiny << 23)) : 0u;
+            }
+        } else {
+            const uint32_t floor_num = ((uint32_t)lo << 23) | unit;
+            const uint32_t mid = ((uint32_t)(lo - 1) << 23) | unit;
+            if (mag > mid) return sign | floor_num;
+            q = 0u;
+        }
+    }
+    return q;
+}
+
+MPT_HD float cast_binary8(float x, int P, bool is_signed, int policy, bool sub,
+                                              int mode, uint32_t r, int prng_bits) {
+    if (!is_signed && x < 0.0f) return u2f(0x7FC00000u);   // NaN
+    const uint32_t t = f2u(x);
+    const int E = (int)((t << 1) >> 24) - 127;
+    const uint32_t tman = t & 0x7FFFFFu;
+    if (E == 128 && (tman != 0u || policy == B8_INFTY)) return x;
+    const int man = P - 1;
+    // the unsigned truncating cast keeps the signed exponent width, as the reference does
+    const int exp = (is_signed || mode == RND_TRUNCATE) ? 8 - P : 9 - P;
+    int shift = 0;
+    if (sub) {
+        const int max_exp = (1 << (exp - 1)) - 1;
+        const int min_exp = (P == 1 ? 1 : 0) - max_exp;
+        if (E < min_exp && min_exp - E <= man) shift = min_exp - E;
+    }
+    const int mb = man - shift;
+    uint32_t q;
+    if (mode == RND_NEAREST) q = rne_bits(t, mb, P != 1);
+    else if (mode == RND_TRUNCATE) q = t & ~low_mask(23 - mb);
+    else {
+        r &= 0x7FFFFFu;
+        const int sh = 23 - man - prng_bits - 1;
+        if (sh >= 0 && sh <= 31) r &= ~(1u << sh);
+        const uint32_t mask = low_mask(23 - mb);
+        q = (t + (r & mask)) & ~mask;
+    }
+    return u2f(binary8_settle(exp, man, t, q, policy, sub));
+}
+
+// ---- supernormal floats -------------------------------------------------------------------
+MPT_HD float cast_superfp(float x, int man, int exp, int bl, int bu, bool sat) {
+    const uint32_t t = f2u(x);
+    const int E = (int)((t << 1) >> 24) - 127;
+    const int lo = 1 - (1 << (exp - 1)) + (bl - 1);
+    const int hi = ((1 << (exp - 1)) - 2) - (bu - 1);
+    const uint32_t sign = t & 0x80000000u;
+    const uint32_t pow2 = (t + 0x400000u) & ~0x7FFFFFu;   // nearest power of two in the log sense
+    if (E < lo) return (E < lo - bl * (1 << man) + 1) ? 0.0f : u2f(pow2);
+    if (E > hi) {
+        const int top = hi + bu * (1 << man);
+        const uint32_t topnum = sign | ((uint32_t)(top + 127) << 23);
+        if (E == 128) return (sat && (t & 0x7FFFFFFFu) == 0x7F800000u) ? u2f(topnum) : x;
+        if (E >= top - 1 + (sat ? 1 : 0)) {
+            if (sat) return u2f(topnum);
+            if ((t << 9) == 0u && E == top - 1) return x;
+            return u2f(sign | 0x7F800000u);
+        }
+        return u2f(pow2);
+    }
+    return u2f(rne_bits(t, man));
+}
+
+// ---- fast round-to-nearest-even on the FP32 pipe ---------------------------------------------
+// For a finite x whose rounded value stays below the format's overflow threshold, and a
+// format with subnormals and man <= 21:
+//     q = 2^(max(E_x, min_exp) - man)            (the rounding quantum)
+//     C = 1.5 * 2^23 * q
+//     round(x) = (x + C) - C                      (both adds in fp32 round-to-nearest-even)
+// x + C lies in [2^23 q, 2^24 q) where one ulp equals q, and C is an even multiple of q, so
+// the hardware's tie-to-even coincides with tie-to-even on x/q; the subtraction is exact.
+// Zero results come out as +0, as in the reference's subnormal branch.  The two adds are
+// issued as FFMA(m, K, x) and FFMA(m, -K, y) with m = 2^max(E_x, min_exp) taken from the
+// exponent field, so the cast costs 2 ALU + 2 FMA instructions.
+struct FastRn {
+    int   min_e_bits;   // (min_exp + 127) << 23
+    float k;            // 1.5 * 2^(23 - man)
+    __host__ __device__ static FastRn make(const FpFmt& f) {
+        FastRn r;
+        r.min_e_bits = (f.min_exp + 127) << 23;
+        union { uint32_t u; float v; } c;
+        c.u = ((uint32_t)(127 + 23 - f.man) << 23) | 0x400000u;
+        r.k = c.v;
+        return r;
+    }
+    MPT_HD float operator()(float x) const {
+        const int e = (int)(f2u(x) & 0x7F800000u);
+        const float m = u2f((uint32_t)(e > min_e_bits ? e : min_e_bits));
+        const float y = fma_rn(m, k, x);
+        return fma_rn(m, -k, y);
+    }
+};
+
+// Largest unbiased exponent E such that every |x| < 2^(E+1) is safe on the fast path of format
+// f: the top binade is excluded because its upper part rounds up into overflow, and
+// C = 1.5 * 2^(E - man + 23) must stay finite.
+__host__ __device__ inline int fast_rn_exp_limit(const FpFmt& f) {
+    const int top = f.max_store - 127 - 1;
+    const int magic = 103 + f.man;
+    return top < magic ? top : magic;
+}
+
+__host__ __device__ inline bool fast_rn_supported(const FpFmt& f) {
+    return f.sub && f.man <= 21 && !(f.man >= 23 && f.exp >= 8);
+}
+
+}  // namespace mpt

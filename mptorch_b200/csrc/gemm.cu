@@ -1,0 +1,508 @@
+// Per-MAC rounded GEMM for sm_100a: C = A x B where every product and every partial sum is
+// rounded to a user format before it is used again.
+//
+// This is CUDA-core work by construction: each output's K accumulation is a serial chain of
+// (multiply, round, add, round), so tensor cores cannot be used.  The kernel is bound by the
+// instruction issue rate; the design goal is the smallest number of issued instructions per
+// MAC that still reproduces the reference bit for bit:
+//
+//   * fast path, 10 instructions per MAC (FMUL, 4 for the product rounding, FADD, 4 for the sum
+//     rounding), see FastRn in cast.cuh.  It is exact whenever no intermediate value can leave
+//     the finite range of its format.  That is established from the magnitude statistics of A
+//     and B (a tiny pre-pass over both matrices writes them to the workspace) plus a per-thread
+//     check of the running accumulators at every fold;
+//   * exact path: the complete reference caster (every corner case), taken per thread and per
+//     8-step group whenever the fast path's precondition cannot be shown.
+//
+// Tiling: 128x64 outputs per CTA, 256 threads, 8x4 outputs per thread, K in slabs of 32 staged
+// through a 3-deep cp.async pipeline in shared memory.  Memory traffic is negligible next to
+// the arithmetic (about 140 GB/s at 8192^3), so tiles are plain cp.async copies.
+//
+// Accumulation orders (both kept bit-exact):
+//   MPT_ORDER_SEQ   acc = Qadd(acc + Qmul(a*b)), k = 0..K-1   (reference quant_cpu/mm_kernel.h:9-20)
+//   MPT_ORDER_CUDA  K walked in groups of 8, zero padded, one extra all-zero group when 8 | K;
+//                   inner accumulates a group, then outer = Qadd(outer + inner)
+//                   (reference quant_cuda/mm_kernel.h:34-70; fma variant :134-186)
+// Kahan-compensated and stochastic variants follow quant_cuda/mm_kernel.h:457-520 and :248-295.
+#include <cuda_pipeline.h>
+
+#include "cast.cuh"
+#include "common.cuh"
+
+namespace mpt {
+namespace {
+
+constexpr int BM = 128, BN = 64, BK = 32;
+constexpr int TM = 8, TN = 4;
+constexpr int THREADS = 256;
+constexpr int STAGES = 3;
+constexpr int AS_LD = BK + 4;   // row stride of the A tile: keeps 16-byte chunks aligned, spreads banks
+constexpr int SMEM_A = BM * AS_LD, SMEM_B = BK * BN;
+constexpr size_t SMEM_BYTES = (size_t)STAGES * (SMEM_A + SMEM_B) * sizeof(float);
+
+enum Algo : int { ALGO_SEQ = 0, ALGO_TILE8 = 1, ALGO_KAHAN = 2, ALGO_SR = 3 };
+
+// Magnitude statistics of the operands, produced by stats_kernel into the workspace.
+struct MmStats {
+    uint32_t max_a, max_b;       // largest |x| bit pattern (NaN and inf compare above every finite)
+    uint32_t minnz_a, minnz_b;   // smallest nonzero |x| bit pattern, 0xFFFFFFFF if all zero
+};
+
+struct MmParams {
+    const float* a;
+    const float* b;
+    float* c;
+    int M, N, K;
+    int64_t stride_a, stride_b, stride_c;
+    FpFmt fadd, fmul;
+    FastRn radd, rmul;
+    int rbits_add, rbits_mul;
+    uint32_t seed_lo, seed_hi;
+    const MmStats* stats;        // NULL: exact path only
+    float growth8;               // upper bound of (1 + 2^-(man_add+1))^8
+};
+
+__global__ void stats_init_kernel(MmStats* s) {
+    if (threadIdx.x == 0) { s->max_a = 0u; s->max_b = 0u; s->minnz_a = 0xFFFFFFFFu; s->minnz_b = 0xFFFFFFFFu; }
+}
+
+__global__ void __launch_bounds__(256) stats_kernel(const float* __restrict__ x, int64_t n, uint32_t* mx, uint32_t* mn) {
+    uint32_t lmax = 0u, lmin = 0xFFFFFFFFu;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const uint32_t a = __float_as_uint(x[i]) & 0x7FFFFFFFu;
+        lmax = max(lmax, a);
+        if (a != 0u) lmin = min(lmin, a);
+    }
+    lmax = __reduce_max_sync(0xFFFFFFFFu, lmax);
+    lmin = __reduce_min_sync(0xFFFFFFFFu, lmin);
+    if ((threadIdx.x & 31) == 0) {
+        atomicMax(mx, lmax);
+        atomicMin(mn, lmin);
+    }
+}
+
+__device__ __forceinline__ void cp_async16(float* dst, const float* src, int src_bytes) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src), "r"(src_bytes));
+}
+__device__ __forceinline__ void cp_async4(float* dst, const float* src, int src_bytes) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"(d), "l"(src), "r"(src_bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+// Stage one K slab: As[m][k] (row stride AS_LD) and Bs[k][n].  Elements outside the matrices are
+// zero filled (cp.async with a source size of 0), which is also how K is zero padded.
+template <bool VEC>
+__device__ __forceinline__ void load_tiles(const MmParams& p, const float* A, const float* B, float* As, float* Bs,
+                                           int m0, int n0, int k0, int tid) {
+    if (VEC) {
+#pragma unroll
+        for (int u = 0; u < (BM * BK / 4) / THREADS; ++u) {
+            const int c = tid + u * THREADS;
+            const int row = c >> 3, kc = (c & 7) << 2;
+            const int gm = m0 + row, gk = k0 + kc;
+            int bytes = (gm < p.M) ? (p.K - gk) * 4 : 0;
+            bytes = bytes < 0 ? 0 : (bytes > 16 ? 16 : bytes);
+            const float* src = bytes ? A + (int64_t)gm * p.K + gk : A;
+            cp_async16(As + row * AS_LD + kc, src, bytes);
+        }
+#pragma unroll
+        for (int u = 0; u < (BK * BN / 4) / THREADS; ++u) {
+            const int c = tid + u * THREADS;
+            const int kr = c >> 4, nc = (c & 15) << 2;
+            const int gk = k0 + kr, gn = n0 + nc;
+            int bytes = (gk < p.K) ? (p.N - gn) * 4 : 0;
+            bytes = bytes < 0 ? 0 : (bytes > 16 ? 16 : bytes);
+            const float* src = bytes ? B + (int64_t)gk * p.N + gn : B;
+            cp_async16(Bs + kr * BN + nc, src, bytes);
+        }
+    } else {
+#pragma unroll 4
+        for (int u = 0; u < (BM * BK) / THREADS; ++u) {
+            const int c = tid + u * THREADS;
+            const int row = c >> 5, kk = c & 31;
+            const int gm = m0 + row, gk = k0 + kk;
+            const bool ok = gm < p.M && gk < p.K;
+            cp_async4(As + row * AS_LD + kk, ok ? A + (int64_t)gm * p.K + gk : A, ok ? 4 : 0);
+        }
+#pragma unroll 4
+        for (int u = 0; u < (BK * BN) / THREADS; ++u) {
+            const int c = tid + u * THREADS;
+            const int kr = c >> 6, nn = c & 63;
+            const int gk = k0 + kr, gn = n0 + nn;
+            const bool ok = gk < p.K && gn < p.N;
+            cp_async4(Bs + kr * BN + nn, ok ? B + (int64_t)gk * p.N + gn : B, ok ? 4 : 0);
+        }
+    }
+}
+
+// One accumulation step on the exact path.
+template <bool FMA>
+__device__ __forceinline__ float mac_exact(float acc, float a, float b, const FpFmt& fadd, const FpFmt& fmul) {
+    if (FMA) return cast_fp_nearest(fma_rn(a, b, acc), fadd);
+    return cast_fp_nearest(add_rn(acc, cast_fp_nearest(mul_rn(a, b), fmul)), fadd);
+}
+template <bool FMA>
+__device__ __forceinline__ float mac_fast(float acc, float a, float b, const FastRn& radd, const FastRn& rmul) {
+    if (FMA) return radd(fma_rn(a, b, acc));
+    return radd(add_rn(acc, rmul(mul_rn(a, b))));
+}
+
+// `nk` (1..8) accumulation steps starting at slab row kbase, for the thread's 8x4 outputs.
+template <bool FMA, bool FAST>
+__device__ __forceinline__ void group_steps(float (&acc)[TM][TN], const float* As, const float* Bs, int kbase, int nk,
+                                            int ty, int tx, const MmParams& p) {
+    if (FAST && nk == 8) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            float4 av[TM];
+#pragma unroll
+            for (int i = 0; i < TM; ++i)
+                av[i] = *reinterpret_cast<const float4*>(As + (ty + 16 * i) * AS_LD + kbase + 4 * h);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float4 bv = *reinterpret_cast<const float4*>(Bs + (kbase + 4 * h + j) * BN + tx * 4);
+#pragma unroll
+                for (int i = 0; i < TM; ++i) {
+                    const float a = j == 0 ? av[i].x : j == 1 ? av[i].y : j == 2 ? av[i].z : av[i].w;
+                    acc[i][0] = mac_fast<FMA>(acc[i][0], a, bv.x, p.radd, p.rmul);
+                    acc[i][1] = mac_fast<FMA>(acc[i][1], a, bv.y, p.radd, p.rmul);
+                    acc[i][2] = mac_fast<FMA>(acc[i][2], a, bv.z, p.radd, p.rmul);
+                    acc[i][3] = mac_fast<FMA>(acc[i][3], a, bv.w, p.radd, p.rmul);
+                }
+            }
+        }
+        return;
+    }
+#pragma unroll 1
+    for (int k = 0; k < nk; ++k) {
+        const float4 bv = *reinterpret_cast<const float4*>(Bs + (kbase + k) * BN + tx * 4);
+#pragma unroll
+        for (int i = 0; i < TM; ++i) {
+            const float a = As[(ty + 16 * i) * AS_LD + kbase + k];
+            if (FAST) {
+                acc[i][0] = mac_fast<FMA>(acc[i][0], a, bv.x, p.radd, p.rmul);
+                acc[i][1] = mac_fast<FMA>(acc[i][1], a, bv.y, p.radd, p.rmul);
+                acc[i][2] = mac_fast<FMA>(acc[i][2], a, bv.z, p.radd, p.rmul);
+                acc[i][3] = mac_fast<FMA>(acc[i][3], a, bv.w, p.radd, p.rmul);
+            } else {
+                acc[i][0] = mac_exact<FMA>(acc[i][0], a, bv.x, p.fadd, p.fmul);
+                acc[i][1] = mac_exact<FMA>(acc[i][1], a, bv.y, p.fadd, p.fmul);
+                acc[i][2] = mac_exact<FMA>(acc[i][2], a, bv.z, p.fadd, p.fmul);
+                acc[i][3] = mac_exact<FMA>(acc[i][3], a, bv.w, p.fadd, p.fmul);
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ float absmax_of(const float (&v)[TM][TN]) {
+    float m = 0.0f;
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) m = fmaxf(m, fabsf(v[i][j]));   // NaN entries are skipped by fmaxf
+    return m;
+}
+
+// What the fast path may assume for this launch, from the operand statistics.
+//   ok        : products can take the fast rounding (finite, no overflow in the multiply format,
+//               no fp32-denormal intermediates where the reference treats those specially)
+//   acc_limit : an accumulator with |acc| below this stays on the fast path for 8 more steps
+//               (ALGO_SEQ), or an outer sum below this takes the fast fold (ALGO_TILE8)
+struct FastPlan { bool ok; float acc_limit; };
+
+template <int ALGO, bool FMA>
+__device__ __forceinline__ FastPlan make_plan(const MmParams& p) {
+    FastPlan plan{false, 0.0f};
+    if (p.stats == nullptr) return plan;
+    if (!fast_rn_supported(p.fadd) || (!FMA && !fast_rn_supported(p.fmul))) return plan;
+    const MmStats s = *p.stats;
+    if (s.max_a >= 0x7F800000u || s.max_b >= 0x7F800000u) return plan;
+    // |a| < 2^(ea+1), |b| < 2^(eb+1)  =>  |a*b| < 2^pe
+    const int pe = (int)(s.max_a >> 23) + (int)(s.max_b >> 23) - 254 + 2;
+    const int lim_add = fast_rn_exp_limit(p.fadd);
+    if (!FMA && pe - 1 > fast_rn_exp_limit(p.fmul)) return plan;
+    if (p.fadd.exp == 8 || (!FMA && p.fmul.exp == 8)) {
+        // the reference rounds fp32-denormal inputs of 8-bit-exponent formats one bit coarser;
+        // stay exact unless every nonzero intermediate is provably far above 2^-126
+        if (s.minnz_a < 0x00800000u || s.minnz_b < 0x00800000u) return plan;
+        if (s.minnz_a != 0xFFFFFFFFu && s.minnz_b != 0xFFFFFFFFu) {
+            const int lo = (int)(s.minnz_a >> 23) + (int)(s.minnz_b >> 23) - 254;
+            if (lo - 23 < -120) return plan;
+        }
+    }
+    // eight steps from |acc| = x reach at most (x + 8 * 2^pe) * growth8
+    const float step8 = ldexpf(8.0f, pe) * p.growth8;
+    const float top = ldexpf(1.0f, lim_add + 1);
+    if (ALGO == ALGO_TILE8) {
+        // inner sums start from zero: |inner| <= step8; the fold needs |outer| + |inner| < top
+        if (!(step8 <= ldexpf(1.0f, lim_add))) return plan;
+        plan.ok = true;
+        plan.acc_limit = ldexpf(1.0f, lim_add);
+    } else {
+        const float lim = top / p.growth8 - ldexpf(8.0f, pe);
+        if (!(lim > 0.0f)) return plan;
+        plan.ok = true;
+        plan.acc_limit = lim;
+    }
+    return plan;
+}
+
+template <int ALGO, bool FMA, bool VEC>
+__global__ void __launch_bounds__(THREADS, 2) mm_kernel(const MmParams p) {
+    extern __shared__ __align__(16) float smem[];
+    float* As = smem;
+    float* Bs = smem + STAGES * SMEM_A;
+
+    const int tid = threadIdx.x;
+    const int ty = tid >> 4, tx = tid & 15;
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int64_t batch = blockIdx.z;
+    const float* A = p.a + batch * p.stride_a;
+    const float* B = p.b + batch * p.stride_b;
+    float* C = p.c + batch * p.stride_c;
+
+    // number of accumulation steps walked: exactly K for the sequential order, the zero-padded
+    // range K + 8 - K % 8 for every order that follows the reference CUDA kernels
+    const int ksteps = (ALGO == ALGO_SEQ) ? p.K : p.K + 8 - p.K % 8;
+    const int ntiles = (ksteps + BK - 1) / BK;
+
+    const FastPlan plan = (ALGO == ALGO_SEQ || ALGO == ALGO_TILE8) ? make_plan<ALGO, FMA>(p) : FastPlan{false, 0.0f};
+
+    float acc[TM][TN];    // running sum (inner sum for ALGO_TILE8)
+    float aux[TM][TN];    // outer sum (ALGO_TILE8) or compensation term (ALGO_KAHAN)
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) { acc[i][j] = 0.0f; aux[i][j] = 0.0f; }
+
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) {
+        if (s < ntiles) load_tiles<VEC>(p, A, B, As + s * SMEM_A, Bs + s * SMEM_B, m0, n0, s * BK, tid);
+        cp_async_commit();
+    }
+
+    for (int t = 0; t < ntiles; ++t) {
+        cp_async_wait<STAGES - 2>();
+        __syncthreads();
+        {
+            const int nt = t + STAGES - 1;
+            if (nt < ntiles) load_tiles<VEC>(p, A, B, As + (nt % STAGES) * SMEM_A, Bs + (nt % STAGES) * SMEM_B, m0, n0, nt * BK, tid);
+            cp_async_commit();
+        }
+        const float* as = As + (t % STAGES) * SMEM_A;
+        const float* bs = Bs + (t % STAGES) * SMEM_B;
+        const int kleft = ksteps - t * BK;
+        const int nk_tile = kleft < BK ? kleft : BK;
+
+        if (ALGO == ALGO_SEQ || ALGO == ALGO_TILE8) {
+            for (int g = 0; g * 8 < nk_tile; ++g) {
+                const int nk = (nk_tile - g * 8) < 8 ? (nk_tile - g * 8) : 8;
+                if (ALGO == ALGO_TILE8) {
+                    if (plan.ok) group_steps<FMA, true>(acc, as, bs, g * 8, nk, ty, tx, p);
+                    else group_steps<FMA, false>(acc, as, bs, g * 8, nk, ty, tx, p);
+                    // fold the group into the outer sum
+                    if (plan.ok && absmax_of(aux) < plan.acc_limit) {
+#pragma unroll
+                        for (int i = 0; i < TM; ++i)
+#pragma unroll
+                            for (int j = 0; j < TN; ++j) { aux[i][j] = p.radd(add_rn(aux[i][j], acc[i][j])); acc[i][j] = 0.0f; }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < TM; ++i)
+#pragma unroll
+                            for (int j = 0; j < TN; ++j) { aux[i][j] = cast_fp_nearest(add_rn(aux[i][j], acc[i][j]), p.fadd); acc[i][j] = 0.0f; }
+                    }
+                } else {
+                    if (plan.ok && absmax_of(acc) < plan.acc_limit) group_steps<FMA, true>(acc, as, bs, g * 8, nk, ty, tx, p);
+                    else group_steps<FMA, false>(acc, as, bs, g * 8, nk, ty, tx, p);
+                }
+            }
+        } else if (ALGO == ALGO_KAHAN) {
+#pragma unroll 1
+            for (int k = 0; k < nk_tile; ++k) {
+                const float4 bv4 = *reinterpret_cast<const float4*>(bs + k * BN + tx * 4);
+                const float bvv[4] = {bv4.x, bv4.y, bv4.z, bv4.w};
+#pragma unroll
+                for (int i = 0; i < TM; ++i) {
+                    const float a = as[(ty + 16 * i) * AS_LD + k];
+#pragma unroll
+                    for (int j = 0; j < TN; ++j) {
+                        const float sum = acc[i][j], comp = aux[i][j];
+                        const float y = FMA ? cast_fp_nearest(fma_rn(a, bvv[j], -comp), p.fadd)
+                                            : cast_fp_nearest(add_rn(cast_fp_nearest(mul_rn(a, bvv[j]), p.fmul), -comp), p.fadd);
+                        const float tt = cast_fp_nearest(add_rn(sum, y), p.fadd);
+                        aux[i][j] = cast_fp_nearest(add_rn(cast_fp_nearest(add_rn(tt, -sum), p.fadd), -y), p.fadd);
+                        acc[i][j] = tt;
+                    }
+                }
+            }
+        } else {   // ALGO_SR
+#pragma unroll 1
+            for (int k = 0; k < nk_tile; ++k) {
+                const float4 bv4 = *reinterpret_cast<const float4*>(bs + k * BN + tx * 4);
+                const float bvv[4] = {bv4.x, bv4.y, bv4.z, bv4.w};
+                const uint32_t kglob = (uint32_t)(t * BK + k);
+#pragma unroll
+                for (int i = 0; i < TM; ++i) {
+                    const float a = as[(ty + 16 * i) * AS_LD + k];
+                    const int gm = m0 + ty + 16 * i;
+#pragma unroll
+                    for (int j = 0; j < TN; ++j) {
+                        const int gn = n0 + tx * 4 + j;
+                        const uint64_t lin = (uint64_t)batch * p.M * p.N + (uint64_t)gm * p.N + gn;
+                        Philox ph(kglob, (uint32_t)lin, (uint32_t)(lin >> 32), 0u);
+                        ph.run(p.seed_lo, p.seed_hi);
+                        if (FMA) acc[i][j] = cast_fp_stochastic(fma_rn(a, bvv[j], acc[i][j]), ph.c[0], p.rbits_add, p.fadd);
+                        else {
+                            const float pr = cast_fp_stochastic(mul_rn(a, bvv[j]), ph.c[1], p.rbits_mul, p.fmul);
+                            acc[i][j] = cast_fp_stochastic(add_rn(acc[i][j], pr), ph.c[0], p.rbits_add, p.fadd);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    cp_async_wait<0>();
+
+    // epilogue
+    const bool vec_store = VEC && ((reinterpret_cast<uintptr_t>(C) & 15u) == 0);
+#pragma unroll
+    for (int i = 0; i < TM; ++i) {
+        const int gm = m0 + ty + 16 * i;
+        if (gm >= p.M) continue;
+        const float* r = (ALGO == ALGO_TILE8) ? aux[i] : acc[i];
+        const int gn = n0 + tx * 4;
+        float* dst = C + (int64_t)gm * p.N + gn;
+        if (vec_store && gn + 3 < p.N) *reinterpret_cast<float4*>(dst) = make_float4(r[0], r[1], r[2], r[3]);
+        else {
+#pragma unroll
+            for (int j = 0; j < TN; ++j)
+                if (gn + j < p.N) dst[j] = r[j];
+        }
+    }
+}
+
+template <int ALGO, bool FMA>
+int launch_mm(const MmParams& p, int64_t batch, bool vec, cudaStream_t st) {
+    dim3 grid((p.N + BN - 1) / BN, (p.M + BM - 1) / BM, (unsigned)batch);
+    auto kern = vec ? mm_kernel<ALGO, FMA, true> : mm_kernel<ALGO, FMA, false>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+    if (e != cudaSuccess) { set_error("float_mm: cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return MPT_ERR_CUDA; }
+    kern<<<grid, THREADS, SMEM_BYTES, st>>>(p);
+    return check_launch("float_mm");
+}
+
+double growth8_bound(int man) {
+    double g = 1.0, f = 1.0 + ldexp(1.0, -(man + 1));
+    for (int i = 0; i < 8; ++i) g *= f;
+    return g * 1.0001;
+}
+
+int run_mm(const float* a, const float* b, float* c, int64_t batch, int M, int N, int K, FpFmt fadd, FpFmt fmul,
+           int rbits_add, int rbits_mul, bool fma, int algo, uint64_t seed, void* workspace, size_t workspace_bytes,
+           cudaStream_t st) {
+    if (batch == 0 || M == 0 || N == 0) return MPT_OK;
+    if (K == 0) {   // an empty sum: every order yields +0
+        cudaError_t e = cudaMemsetAsync(c, 0, sizeof(float) * (size_t)batch * M * N, st);
+        if (e != cudaSuccess) { set_error("float_mm: cudaMemsetAsync: %s", cudaGetErrorString(e)); return MPT_ERR_CUDA; }
+        return MPT_OK;
+    }
+    MmParams p;
+    p.a = a; p.b = b; p.c = c;
+    p.M = M; p.N = N; p.K = K;
+    p.stride_a = (int64_t)M * K; p.stride_b = (int64_t)K * N; p.stride_c = (int64_t)M * N;
+    p.fadd = fadd; p.fmul = fmul;
+    p.radd = FastRn::make(fadd); p.rmul = FastRn::make(fmul);
+    p.rbits_add = rbits_add; p.rbits_mul = rbits_mul;
+    p.seed_lo = (uint32_t)seed; p.seed_hi = (uint32_t)(seed >> 32);
+    p.growth8 = (float)growth8_bound(fadd.man);
+    p.stats = nullptr;
+
+    const bool fast_candidate = (algo == ALGO_SEQ || algo == ALGO_TILE8) && fast_rn_supported(fadd) &&
+                                (fma || fast_rn_supported(fmul)) && workspace != nullptr &&
+                                workspace_bytes >= sizeof(MmStats) && (reinterpret_cast<uintptr_t>(workspace) & 15u) == 0 && K > 0;
+    if (fast_candidate) {
+        MmStats* s = static_cast<MmStats*>(workspace);
+        stats_init_kernel<<<1, 32, 0, st>>>(s);
+        const int64_t na = batch * (int64_t)M * K, nb = batch * (int64_t)K * N;
+        const int sms = sm_count();
+        auto blocks = [&](int64_t n) { int64_t g = (n + 255) / 256; const int64_t cap = (int64_t)sms * 8; return (unsigned)(g > cap ? cap : (g < 1 ? 1 : g)); };
+        stats_kernel<<<blocks(na), 256, 0, st>>>(a, na, &s->max_a, &s->minnz_a);
+        stats_kernel<<<blocks(nb), 256, 0, st>>>(b, nb, &s->max_b, &s->minnz_b);
+        int rc = check_launch("float_mm statistics");
+        if (rc) return rc;
+        p.stats = s;
+    }
+    const bool vec = (K % 4 == 0) && (N % 4 == 0) && (((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) & 15u) == 0);
+    switch (algo * 2 + (fma ? 1 : 0)) {
+        case ALGO_SEQ * 2 + 0: return launch_mm<ALGO_SEQ, false>(p, batch, vec, st);
+        case ALGO_SEQ * 2 + 1: return launch_mm<ALGO_SEQ, true>(p, batch, vec, st);
+        case ALGO_TILE8 * 2 + 0: return launch_mm<ALGO_TILE8, false>(p, batch, vec, st);
+        case ALGO_TILE8 * 2 + 1: return launch_mm<ALGO_TILE8, true>(p, batch, vec, st);
+        case ALGO_KAHAN * 2 + 0: return launch_mm<ALGO_KAHAN, false>(p, batch, vec, st);
+        case ALGO_KAHAN * 2 + 1: return launch_mm<ALGO_KAHAN, true>(p, batch, vec, st);
+        case ALGO_SR * 2 + 0: return launch_mm<ALGO_SR, false>(p, batch, vec, st);
+        default: return launch_mm<ALGO_SR, true>(p, batch, vec, st);
+    }
+}
+
+int check_mm_args(const char* who, const float* a, const float* b, float* c, int64_t batch, int M, int N, int K) {
+    MPT_REQUIRE(batch >= 0 && M >= 0 && N >= 0 && K >= 0, "%s: negative dimension", who);
+    MPT_REQUIRE(batch <= 65535, "%s: batch %lld exceeds 65535", who, (long long)batch);
+    MPT_REQUIRE((int64_t)(M + BM - 1) / BM <= 65535, "%s: M=%d too large", who, M);
+    const bool empty = batch == 0 || M == 0 || N == 0;
+    MPT_REQUIRE(empty || (c && (K == 0 || (a && b))), "%s: null pointer", who);
+    return MPT_OK;
+}
+
+}  // namespace
+}  // namespace mpt
+
+using namespace mpt;
+
+extern "C" {
+
+size_t mpt_mm_workspace_bytes(void) { return 256; }
+
+int mpt_float_mm_nearest(const float* a, const float* b, float* c, int64_t batch, int M, int N, int K, int man_add,
+                         int exp_add, int man_mul, int exp_mul, int subnormals, int saturate, int compensated,
+                         int order, void* workspace, size_t workspace_bytes, void* stream) {
+    int rc = check_mm_args("float_mm_nearest", a, b, c, batch, M, N, K);
+    if (rc) return rc;
+    MPT_REQUIRE(valid_format(man_add, exp_add) && valid_format(man_mul, exp_mul), "float_mm_nearest: unsupported format");
+    MPT_REQUIRE(order == MPT_ORDER_SEQ || order == MPT_ORDER_CUDA, "float_mm_nearest: unknown order %d", order);
+    const int algo = compensated ? ALGO_KAHAN : (order == MPT_ORDER_SEQ ? ALGO_SEQ : ALGO_TILE8);
+    return run_mm(a, b, c, batch, M, N, K, make_fmt(man_add, exp_add, subnormals, saturate),
+                  make_fmt(man_mul, exp_mul, subnormals, saturate), 0, 0, false, algo, 0, workspace, workspace_bytes,
+                  as_stream(stream));
+}
+
+int mpt_float_mm_nearest_fma(const float* a, const float* b, float* c, int64_t batch, int M, int N, int K, int man_fma,
+                             int exp_fma, int subnormals, int saturate, int compensated, int order, void* workspace,
+                             size_t workspace_bytes, void* stream) {
+    int rc = check_mm_args("float_mm_nearest_fma", a, b, c, batch, M, N, K);
+    if (rc) return rc;
+    MPT_REQUIRE(valid_format(man_fma, exp_fma), "float_mm_nearest_fma: unsupported format");
+    MPT_REQUIRE(order == MPT_ORDER_SEQ || order == MPT_ORDER_CUDA, "float_mm_nearest_fma: unknown order %d", order);
+    const int algo = compensated ? ALGO_KAHAN : (order == MPT_ORDER_SEQ ? ALGO_SEQ : ALGO_TILE8);
+    const FpFmt f = make_fmt(man_fma, exp_fma, subnormals, saturate);
+    return run_mm(a, b, c, batch, M, N, K, f, f, 0, 0, true, algo, 0, workspace, workspace_bytes, as_stream(stream));
+}
+
+int mpt_float_mm_stochastic(const float* a, const float* b, float* c, int64_t batch, int M, int N, int K, int man_add,
+                            int exp_add, int rbits_add, int man_mul, int exp_mul, int rbits_mul, int subnormals,
+                            int saturate, int fma, uint64_t seed, void* stream) {
+    int rc = check_mm_args("float_mm_stochastic", a, b, c, batch, M, N, K);
+    if (rc) return rc;
+    MPT_REQUIRE(valid_format(man_add, exp_add) && (fma || valid_format(man_mul, exp_mul)), "float_mm_stochastic: unsupported format");
+    const FpFmt fa = make_fmt(man_add, exp_add, subnormals, saturate);
+    const FpFmt fm = fma ? fa : make_fmt(man_mul, exp_mul, subnormals, saturate);
+    return run_mm(a, b, c, batch, M, N, K, fa, fm, rbits_add, rbits_mul, fma != 0, ALGO_SR, seed, nullptr, 0, as_stream(stream));
+}
+
+}

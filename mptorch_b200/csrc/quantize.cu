@@ -1,0 +1,192 @@
+// Elementwise quantizers: one streaming kernel family, 128-bit accesses, HBM-bound.
+//
+// Algorithmic traffic is 8 B per element (4 read + 4 written); the stochastic cast with caller
+// supplied random words reads 4 B more.  The reference launches one thread per element over a
+// pre-zeroed output (12 or 20 B per element); here the output is written once.
+#include "cast.cuh"
+#include "common.cuh"
+
+namespace mpt {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kVecPerThread = 4;   // float4 loads in flight per thread
+
+// F: float4 -> float4 functor given the linear index of the first element.
+template <class F>
+__global__ void __launch_bounds__(kThreads) map_f4_kernel(const float* __restrict__ in, float* __restrict__ out,
+                                                          int64_t n, F f) {
+    const int64_t nvec = n >> 2;
+    const float4* in4 = reinterpret_cast<const float4*>(in);
+    float4* out4 = reinterpret_cast<float4*>(out);
+    const int64_t stride = (int64_t)gridDim.x * kThreads;
+    int64_t v = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    for (; v + (kVecPerThread - 1) * stride < nvec; v += kVecPerThread * stride) {
+        float4 x[kVecPerThread];
+#pragma unroll
+        for (int u = 0; u < kVecPerThread; ++u) x[u] = __ldcs(in4 + v + u * stride);
+#pragma unroll
+        for (int u = 0; u < kVecPerThread; ++u) __stcs(out4 + v + u * stride, f.vec(x[u], (v + u * stride) << 2));
+    }
+    for (; v < nvec; v += stride) __stcs(out4 + v, f.vec(__ldcs(in4 + v), v << 2));
+    // ragged tail (n % 4 elements)
+    const int64_t tail = (nvec << 2) + (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    if (tail < n) out[tail] = f.one(in[tail], tail);
+}
+
+// Fallback for pointers that are not 16-byte aligned.
+template <class F>
+__global__ void __launch_bounds__(kThreads) map_scalar_kernel(const float* __restrict__ in, float* __restrict__ out,
+                                                              int64_t n, F f) {
+    const int64_t stride = (int64_t)gridDim.x * kThreads;
+    for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += stride) out[i] = f.one(in[i], i);
+}
+
+template <class F>
+int launch_map(const float* in, float* out, int64_t n, F f, cudaStream_t st, const char* what) {
+    if (n == 0) return MPT_OK;
+    const bool aligned = ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15u) == 0;
+    const int sms = sm_count();
+    if (aligned) {
+        const int64_t nvec = n >> 2;
+        int64_t blocks = (nvec + (int64_t)kThreads * kVecPerThread - 1) / ((int64_t)kThreads * kVecPerThread);
+        const int64_t cap = (int64_t)sms * 8 * 4;      // 8 resident CTAs per SM, 4 waves
+        if (blocks > cap) blocks = cap - cap % sms;
+        if (blocks < 1) blocks = 1;
+        map_f4_kernel<F><<<(unsigned)blocks, kThreads, 0, st>>>(in, out, n, f);
+    } else {
+        int64_t blocks = (n + kThreads - 1) / kThreads;
+        const int64_t cap = (int64_t)sms * 32;
+        if (blocks > cap) blocks = cap;
+        map_scalar_kernel<F><<<(unsigned)blocks, kThreads, 0, st>>>(in, out, n, f);
+    }
+    return check_launch(what);
+}
+
+#define MPT_VEC_FROM_ONE                                                                     \
+    __device__ __forceinline__ float4 vec(float4 x, int64_t i) const {                       \
+        return make_float4(one(x.x, i), one(x.y, i + 1), one(x.z, i + 2), one(x.w, i + 3));  \
+    }
+
+struct FpNearest {
+    FpFmt f;
+    __device__ __forceinline__ float one(float x, int64_t) const { return cast_fp_nearest(x, f); }
+    MPT_VEC_FROM_ONE
+};
+struct FpTruncate {
+    FpFmt f;
+    __device__ __forceinline__ float one(float x, int64_t) const { return cast_fp_truncate(x, f); }
+    MPT_VEC_FROM_ONE
+};
+struct FpStochastic {
+    FpFmt f;
+    const int32_t* __restrict__ rnd;
+    int rbits;
+    __device__ __forceinline__ float one(float x, int64_t i) const {
+        return cast_fp_stochastic(x, (uint32_t)__ldcs(rnd + i), rbits, f);
+    }
+    __device__ __forceinline__ float4 vec(float4 x, int64_t i) const {
+        // the random words are as aligned as the data when the caller allocates both the same way
+        int4 r;
+        if ((reinterpret_cast<uintptr_t>(rnd) & 15u) == 0) r = __ldcs(reinterpret_cast<const int4*>(rnd + i));
+        else r = make_int4(rnd[i], rnd[i + 1], rnd[i + 2], rnd[i + 3]);
+        return make_float4(cast_fp_stochastic(x.x, (uint32_t)r.x, rbits, f), cast_fp_stochastic(x.y, (uint32_t)r.y, rbits, f),
+                           cast_fp_stochastic(x.z, (uint32_t)r.z, rbits, f), cast_fp_stochastic(x.w, (uint32_t)r.w, rbits, f));
+    }
+};
+// Random words from Philox4x32-10: counter = (i / 4, i / 4 >> 32, 0, 0), key = seed; element i
+// takes word i % 4.  31 bits are used, like the reference's randint_like(a, INT_MAX).
+struct FpStochasticPhilox {
+    FpFmt f;
+    int rbits;
+    uint32_t k0, k1;
+    __device__ __forceinline__ float one(float x, int64_t i) const {
+        const uint64_t blk = (uint64_t)i >> 2;
+        Philox p((uint32_t)blk, (uint32_t)(blk >> 32), 0u, 0u);
+        p.run(k0, k1);
+        return cast_fp_stochastic(x, p.c[i & 3] & 0x7FFFFFFFu, rbits, f);
+    }
+    __device__ __forceinline__ float4 vec(float4 x, int64_t i) const {
+        const uint64_t blk = (uint64_t)i >> 2;
+        Philox p((uint32_t)blk, (uint32_t)(blk >> 32), 0u, 0u);
+        p.run(k0, k1);
+        return make_float4(cast_fp_stochastic(x.x, p.c[0] & 0x7FFFFFFFu, rbits, f), cast_fp_stochastic(x.y, p.c[1] & 0x7FFFFFFFu, rbits, f),
+                           cast_fp_stochastic(x.z, p.c[2] & 0x7FFFFFFFu, rbits, f), cast_fp_stochastic(x.w, p.c[3] & 0x7FFFFFFFu, rbits, f));
+    }
+};
+struct Binary8 {
+    int P, is_signed, policy, sub, mode, prng_bits;
+    const int32_t* __restrict__ rnd;
+    __device__ __forceinline__ float one(float x, int64_t i) const {
+        const uint32_t r = (mode == RND_STOCHASTIC) ? (uint32_t)rnd[i] : 0u;
+        return cast_binary8(x, P, is_signed != 0, policy, sub != 0, mode, r, prng_bits);
+    }
+    MPT_VEC_FROM_ONE
+};
+struct SuperFp {
+    int man, exp, bl, bu, sat;
+    __device__ __forceinline__ float one(float x, int64_t) const { return cast_superfp(x, man, exp, bl, bu, sat != 0); }
+    MPT_VEC_FROM_ONE
+};
+
+}  // namespace
+}  // namespace mpt
+
+using namespace mpt;
+
+extern "C" {
+
+int mpt_float_quantize_nearest(const float* in, float* out, int64_t n, int man, int exp, int subnormals,
+                               int saturate, void* stream) {
+    MPT_REQUIRE(n >= 0 && (n == 0 || (in && out)), "float_quantize_nearest: null pointer or negative size");
+    MPT_REQUIRE(valid_format(man, exp), "float_quantize_nearest: unsupported format man=%d exp=%d", man, exp);
+    return launch_map(in, out, n, FpNearest{make_fmt(man, exp, subnormals, saturate)}, as_stream(stream),
+                      "float_quantize_nearest");
+}
+
+int mpt_float_quantize_truncate(const float* in, float* out, int64_t n, int man, int exp, int subnormals,
+                                int saturate, void* stream) {
+    MPT_REQUIRE(n >= 0 && (n == 0 || (in && out)), "float_quantize_truncate: null pointer or negative size");
+    MPT_REQUIRE(valid_format(man, exp), "float_quantize_truncate: unsupported format man=%d exp=%d", man, exp);
+    return launch_map(in, out, n, FpTruncate{make_fmt(man, exp, subnormals, saturate)}, as_stream(stream),
+                      "float_quantize_truncate");
+}
+
+int mpt_float_quantize_stochastic(const float* in, const int32_t* rand, float* out, int64_t n, int man, int exp,
+                                  int prng_bits, int subnormals, int saturate, void* stream) {
+    MPT_REQUIRE(n >= 0 && (n == 0 || (in && out && rand)), "float_quantize_stochastic: null pointer or negative size");
+    MPT_REQUIRE(valid_format(man, exp), "float_quantize_stochastic: unsupported format man=%d exp=%d", man, exp);
+    return launch_map(in, out, n, FpStochastic{make_fmt(man, exp, subnormals, saturate), rand, prng_bits},
+                      as_stream(stream), "float_quantize_stochastic");
+}
+
+int mpt_float_quantize_stochastic_philox(const float* in, float* out, int64_t n, int man, int exp, int prng_bits,
+                                         int subnormals, int saturate, uint64_t seed, void* stream) {
+    MPT_REQUIRE(n >= 0 && (n == 0 || (in && out)), "float_quantize_stochastic_philox: null pointer or negative size");
+    MPT_REQUIRE(valid_format(man, exp), "float_quantize_stochastic_philox: unsupported format man=%d exp=%d", man, exp);
+    return launch_map(in, out, n,
+                      FpStochasticPhilox{make_fmt(man, exp, subnormals, saturate), prng_bits, (uint32_t)seed,
+                                         (uint32_t)(seed >> 32)},
+                      as_stream(stream), "float_quantize_stochastic_philox");
+}
+
+int mpt_binary8_quantize(const float* in, const int32_t* rand, float* out, int64_t n, int P, int is_signed,
+                         int overflow_policy, int subnormals, int rounding, int prng_bits, void* stream) {
+    MPT_REQUIRE(n >= 0 && (n == 0 || (in && out)), "binary8_quantize: null pointer or negative size");
+    MPT_REQUIRE(P >= 1 && P <= 7, "binary8_quantize: P=%d outside 1..7", P);
+    MPT_REQUIRE(overflow_policy >= 0 && overflow_policy <= 2, "binary8_quantize: unknown overflow policy %d", overflow_policy);
+    MPT_REQUIRE(rounding >= 0 && rounding <= 2, "binary8_quantize: unknown rounding mode %d", rounding);
+    MPT_REQUIRE(rounding != MPT_RND_STOCHASTIC || n == 0 || rand, "binary8_quantize: stochastic rounding needs random words");
+    return launch_map(in, out, n, Binary8{P, is_signed, overflow_policy, subnormals, rounding, prng_bits, rand},
+                      as_stream(stream), "binary8_quantize");
+}
+
+int mpt_superfp_quantize_nearest(const float* in, float* out, int64_t n, int man, int exp, int binades_l,
+                                 int binades_u, int saturate, void* stream) {
+    MPT_REQUIRE(n >= 0 && (n == 0 || (in && out)), "superfp_quantize_nearest: null pointer or negative size");
+    MPT_REQUIRE(valid_format(man, exp), "superfp_quantize_nearest: unsupported format man=%d exp=%d", man, exp);
+    return launch_map(in, out, n, SuperFp{man, exp, binades_l, binades_u, saturate}, as_stream(stream),
+                      "superfp_quantize_nearest");
+}
+
+}

@@ -1,0 +1,308 @@
+"""Public quantization API: the Python layer of the reference's ``mptorch.quant.quant_function`` on
+top of the B200 kernels.
+
+Names, argument order, defaults and assertion behaviour follow the reference (file:line cited per
+function, paths within the reference project).  Tensors must live on a CUDA device: this library has no
+CPU arithmetic path.  Functions of the reference that are outside the accelerated hot path
+(fixed point, block floating point, cuBLAS passthrough) are present but raise ``NotImplementedError``.
+"""
+from __future__ import annotations
+
+from typing import Literal
+
+import torch
+
+from .. import backend as _be
+from ..number import Binary8, BlockFloatingPoint, FixedPoint, FloatingPoint, Number, SuperNormalFloat
+
+__all__ = [
+    "fixed_point_quantize", "block_quantize", "float_quantize", "binary8_quantize", "superfp_quantize", "quantizer",
+    "mp_mm", "mp_bmm", "float_mm", "float_bmm", "fxp_mm", "fxp_bmm", "superfp_mm", "superfp_bmm",
+    "cublas_mm", "cublas_bmm", "cublas_acceleration",
+    "set_accum_order", "set_reduce_order", "orders",
+]
+
+set_accum_order = _be.set_accum_order
+set_reduce_order = _be.set_reduce_order
+orders = _be.orders
+
+
+def _require_cuda(x: torch.Tensor, who: str) -> None:
+    if not isinstance(x, torch.Tensor):
+        raise AssertionError("x is not a single precision Floating Point Tensor")
+    if not x.is_cuda:
+        raise RuntimeError(
+            "%s: CPU tensors are not supported; this library runs on CUDA devices only (no CPU fallback)" % who)
+
+
+def _f32c(x: torch.Tensor) -> torch.Tensor:
+    return x.contiguous() if x.dtype == torch.float32 else x.float().contiguous()
+
+
+def translate_overflow_policy(policy: str) -> _be.OverflowPolicy:
+    """reference: quant_function.py:108-124."""
+    table = {"saturate_infty": _be.OverflowPolicy.SATURATE_INFTY, "saturate_maxfloat": _be.OverflowPolicy.SATURATE_MAXFLOAT,
+             "saturate_maxfloat2": _be.OverflowPolicy.SATURATE_MAXFLOAT2}
+    if policy not in table:
+        raise ValueError("invalid overflow policy, {}".format(policy))
+    return table[policy]
+
+
+def normalize_binades(binades) -> tuple[int, int]:
+    if isinstance(binades, int):
+        return binades, binades
+    if len(binades) == 1:
+        return binades[0], binades[0]
+    return binades[0], binades[1]
+
+
+# ------------------------------------------------------------------------------------------ quantizers
+def float_quantize(x: torch.Tensor, exp: int, man: int,
+                   rounding: Literal["nearest", "stochastic", "truncate"] = "stochastic",
+                   subnormals: bool = True, saturate: bool = True, prng: int = 0) -> torch.Tensor:
+    """Quantize an fp32 tensor to an IEEE-like (exp, man) format; the result stays fp32.
+
+    reference: quant_function.py:2982-3023.  ``rounding="truncate"`` is new (the reference has it only
+    for binary8).  Stochastic rounding draws its random words from the torch CUDA generator exactly as
+    the reference does, so the two agree bit for bit under the same ``torch.manual_seed``.
+    """
+    assert isinstance(x, torch.Tensor), "x is not a single precision Floating Point Tensor"
+    assert rounding in ["stochastic", "nearest", "truncate"], "invalid rounding mode, {}".format(rounding)
+    _require_cuda(x, "float_quantize")
+    xc = _f32c(x)
+    if rounding == "nearest":
+        return _be.float_quantize_nearest(xc, man, exp, subnormals, saturate)
+    if rounding == "truncate":
+        return _be.float_quantize_truncate(xc, man, exp, subnormals, saturate)
+    if prng == 0:
+        prng = 23 - man
+    return _be.float_quantize_stochastic(xc, man, exp, prng, subnormals, saturate)
+
+
+def binary8_quantize(x: torch.Tensor, P: int, rounding: Literal["nearest", "stochastic", "truncate"] = "nearest",
+                     overflow_policy: str = "saturate_maxfloat", is_signed: bool = True, subnormals: bool = True,
+                     prng_bits: int = 0) -> torch.Tensor:
+    """Quantize to an IEEE P3109 binary8 format.  reference: quant_function.py:3026-3083."""
+    assert isinstance(x, torch.Tensor), "x is not a single precision Floating Point Tensor"
+    assert rounding in ["stochastic", "nearest", "truncate"], "invalid rounding mode, {}".format(rounding)
+    assert 0 <= prng_bits <= 23 - (P - 1), "prng_bits should be between 0 and 23 minus the number of mantissa bits"
+    _require_cuda(x, "binary8_quantize")
+    pol = translate_overflow_policy(overflow_policy)
+    xc = _f32c(x)
+    if rounding == "nearest":
+        return _be.binary8_quantize_nearest(xc, P, is_signed, pol, subnormals)
+    if rounding == "stochastic":
+        return _be.binary8_quantize_stochastic(xc, P, prng_bits, is_signed, pol, subnormals)
+    return _be.binary8_quantize_truncate(xc, P, is_signed, pol, subnormals)
+
+
+def superfp_quantize(x: torch.Tensor, exp: int, man: int, binades, rounding: Literal["stochastic", "nearest"] = "nearest",
+                     saturate: bool = False) -> torch.Tensor:
+    """Quantize to a supernormal float format.  reference: quant_function.py:3086-3125."""
+    assert isinstance(x, torch.Tensor), "x is not a single precision Floating Point Tensor"
+    assert rounding in ["stochastic", "nearest"], "invalid rounding mode, {}".format(rounding)
+    _require_cuda(x, "superfp_quantize")
+    if rounding == "stochastic":
+        raise NotImplementedError("SR SuperNormalFloat not yet implemented")
+    bl, bu = normalize_binades(binades)
+    return _be.superfp_quantize_nearest(_f32c(x), man, exp, bl, bu, saturate)
+
+
+def fixed_point_quantize(*args, **kwargs):
+    """reference: quant_function.py:2913.  Fixed point is outside this library's hot path."""
+    raise NotImplementedError("fixed_point_quantize is not part of the B200 hot path")
+
+
+def block_quantize(*args, **kwargs):
+    """reference: quant_function.py:2950 (legacy block floating point).  See mx_quantize / nvfp4_quantize."""
+    raise NotImplementedError("block_quantize (legacy block floating point) is not part of the B200 hot path")
+
+
+def quantizer(forward_number: Number | None = None, backward_number: Number | None = None,
+              forward_rounding: str = "stochastic", backward_rounding: str = "stochastic",
+              clamping_grad_zero: bool = False, backward_hooks=[]):
+    """A differentiable quantization function: quantizes activations on the way forward and gradients on
+    the way back.  reference: quant_function.py:2661-2910 (float-like formats only here)."""
+    for rnd in (forward_rounding, backward_rounding):
+        assert rnd in ["stochastic", "nearest"], "invalid rounding type {:s}".format(rnd)
+    for num in (forward_number, backward_number):
+        if num is not None:
+            assert isinstance(num, Number)
+    if clamping_grad_zero:
+        raise NotImplementedError("clamping_grad_zero applies to fixed point, which is outside the hot path")
+
+    def make(num, rounding):
+        if num is None:
+            return lambda x: x
+        if isinstance(num, FloatingPoint):
+            return lambda x: float_quantize(x, num.exp, num.man, rounding, num.subnormals, num.saturate)
+        if isinstance(num, Binary8):
+            return lambda x: binary8_quantize(x, num.P, rounding, num.overflow_policy, num.signed, num.subnormals)
+        if isinstance(num, SuperNormalFloat):
+            return lambda x: superfp_quantize(x, num.exp, num.man, num.binades, rounding, num.saturate)
+        raise NotImplementedError("quantizer: %r is outside the B200 hot path" % (num,))
+
+    fwd, bwd = make(forward_number, forward_rounding), make(backward_number, backward_rounding)
+
+    class Rounding(torch.autograd.Function):
+        @staticmethod
+        def forward(ctx, x):
+            return x if forward_number is None else fwd(x.contiguous())
+
+        @staticmethod
+        def backward(ctx, grad_output):
+            if not ctx.needs_input_grad[0]:
+                return None
+            g = grad_output if backward_number is None else bwd(grad_output.contiguous())
+            for hook in backward_hooks:
+                g = hook(g)
+            return g
+
+    return Rounding.apply
+
+
+# ------------------------------------------------------------------------------------------ GEMM
+def _mm_dispatch(a2, b2, batched, man_add, exp_add, man_mul, exp_mul, rounding, fma, subnormals, saturate,
+                 compensated, rbits_add, rbits_mul):
+    """One (possibly batched) GEMM on contiguous fp32 operands; allocates and returns C."""
+    if batched:
+        Bn, M, K = a2.shape
+        N = b2.shape[2]
+        c = torch.empty(Bn, M, N, device=a2.device)
+    else:
+        M, K = a2.shape
+        N = b2.shape[1]
+        c = torch.empty(M, N, device=a2.device)
+    if rounding == "nearest":
+        if not fma:
+            fn = _be.float_quantize_nearest_bmm if batched else _be.float_quantize_nearest_mm
+            fn(a2, b2, c, M, N, K, man_add, exp_add, man_mul, exp_mul, subnormals, saturate, compensated)
+        else:
+            fn = _be.float_quantize_nearest_bmm_fma if batched else _be.float_quantize_nearest_mm_fma
+            fn(a2, b2, c, M, N, K, man_add, exp_add, subnormals, saturate, compensated)
+    else:
+        # reference quant_function.py:1616-1619: rbits_add defaults to 23 - man_add; the matching line for
+        # rbits_mul is a comparison, so rbits_mul keeps the caller's value (0 unless set)
+        if rbits_add <= 0:
+            rbits_add = 23 - man_add
+        if not fma:
+            fn = _be.float_quantize_stochastic_bmm if batched else _be.float_quantize_stochastic_mm
+            fn(a2, b2, c, M, N, K, man_add, exp_add, rbits_add, man_mul, exp_mul, rbits_mul, subnormals, saturate)
+        else:
+            fn = _be.float_quantize_stochastic_bmm_fma if batched else _be.float_quantize_stochastic_mm_fma
+            fn(a2, b2, c, M, N, K, man_add, exp_add, rbits_add, subnormals, saturate)
+    return c
+
+
+def float_mm(a: torch.Tensor, b: torch.Tensor, man_add: int = 23, exp_add: int = 8, man_mul: int = 23, exp_mul: int = 8,
+             rounding: Literal["nearest", "stochastic"] = "nearest", fma: bool = True, subnormals: bool = True,
+             saturate: bool = True, compensated: bool = False, rbits_add: int = 0, rbits_mul: int = 0) -> torch.Tensor:
+    """GEMM (M,K) x (K,N) in which every multiply and every add is rounded to its format.
+
+    reference: quant_function.py:1527-1651.  With ``fma=True`` each step is one fused multiply-add rounded
+    to (man_add, exp_add).  The K-accumulation order is the one selected by ``set_accum_order`` /
+    ``orders`` ("cuda": the reference CUDA kernels' 8-wide tiles; "seq": the reference CPU loop).
+    """
+    assert len(a.shape) == 2
+    assert len(b.shape) == 2
+    assert a.shape[1] == b.shape[0]
+    assert a.device == b.device
+    _require_cuda(a, "float_mm")
+    return _mm_dispatch(_f32c(a), _f32c(b), False, man_add, exp_add, man_mul, exp_mul, rounding, fma, subnormals,
+                        saturate, compensated, rbits_add, rbits_mul)
+
+
+def float_bmm(a: torch.Tensor, b: torch.Tensor, man_add: int = 23, exp_add: int = 8, man_mul: int = 23, exp_mul: int = 8,
+              rounding: Literal["nearest", "stochastic"] = "nearest", fma: bool = True, subnormals: bool = True,
+              saturate: bool = True, compensated: bool = False, rbits_add: int = 0, rbits_mul: int = 0) -> torch.Tensor:
+    """Batched variant; accepts the reference's four shape cases (quant_function.py:1853-1933):
+    3-D x 3-D (equal batch), 3-D x 2-D (one GEMM over the flattened rows), 4-D x 4-D (leading dims
+    flattened) and 2-D x 2-D."""
+    assert a.shape[-1] == b.shape[-2]
+    assert a.device == b.device
+    _require_cuda(a, "float_bmm")
+    kw = (man_add, exp_add, man_mul, exp_mul, rounding, fma, subnormals, saturate, compensated, rbits_add, rbits_mul)
+    a, b = _f32c(a), _f32c(b)
+    if a.dim() == 3 and b.dim() == 3:
+        return _mm_dispatch(a, b, True, *kw)
+    if a.dim() == 3 and b.dim() == 2:
+        c = _mm_dispatch(a.reshape(a.shape[0] * a.shape[1], a.shape[2]), b, False, *kw)
+        return c.reshape(a.shape[0], a.shape[1], b.shape[1])
+    if a.dim() == 4 and b.dim() == 4:
+        a_r = a.reshape(a.shape[0] * a.shape[1], a.shape[2], a.shape[3])
+        b_r = b.reshape(b.shape[0] * b.shape[1], b.shape[2], b.shape[3])
+        c = _mm_dispatch(a_r, b_r, True, *kw)
+        return c.reshape(a.shape[0], a.shape[1], a.shape[2], b.shape[3])
+    if a.dim() == 2 and b.dim() == 2:
+        return _mm_dispatch(a, b, False, *kw)
+    raise Exception("Wrong tensor sizes")
+
+
+_FP32 = FloatingPoint(exp=8, man=23, subnormals=True, saturate=False)
+
+
+def _mac_config(formats, use_forward: bool):
+    """reference: quant_function.py:1358-1387."""
+    if use_forward:
+        if formats.fwd_use_default_prec:
+            return _FP32, _FP32, True, "nearest"
+        return formats.fwd_add, formats.fwd_mul, formats.fwd_fma, formats.fwd_rnd
+    if formats.bwd_use_default_prec:
+        return _FP32, _FP32, True, "nearest"
+    return formats.bwd_add, formats.bwd_mul, formats.bwd_fma, formats.bwd_rnd
+
+
+def _mp_matmul(fn, a, b, formats, use_forward):
+    add_cfg, mul_cfg, fma, rnd = _mac_config(formats, use_forward)
+    assert type(add_cfg) == type(mul_cfg), "Only the same types are currently support for add and mul operations"
+    if type(add_cfg) == FloatingPoint:
+        # subnormals / saturate of the whole MAC come from the add format (quant_function.py:1402-1403)
+        return fn(a, b, man_add=add_cfg.man, exp_add=add_cfg.exp, man_mul=mul_cfg.man, exp_mul=mul_cfg.exp, rounding=rnd,
+                  fma=fma, subnormals=add_cfg.subnormals, saturate=add_cfg.saturate, compensated=formats.compensated,
+                  rbits_add=formats.rbits_add, rbits_mul=formats.rbits_mul)
+    raise NotImplementedError("matrix products in %s are outside the B200 hot path" % type(add_cfg).__name__)
+
+
+def mp_mm(a: torch.Tensor, b: torch.Tensor, formats, use_forward: bool = True) -> torch.Tensor:
+    """reference: quant_function.py:1354-1433."""
+    return _mp_matmul(float_mm, a, b, formats, use_forward)
+
+
+def mp_bmm(a: torch.Tensor, b: torch.Tensor, formats, use_forward: bool = True) -> torch.Tensor:
+    """reference: quant_function.py:1735-1814."""
+    return _mp_matmul(float_bmm, a, b, formats, use_forward)
+
+
+def _outside(name):
+    def fn(*args, **kwargs):
+        raise NotImplementedError("%s is outside the B200 hot path" % name)
+
+    fn.__name__ = name
+    fn.__doc__ = "Present for API compatibility with the reference; not implemented on this back end."
+    return fn
+
+
+fxp_mm, fxp_bmm = _outside("fxp_mm"), _outside("fxp_bmm")
+superfp_mm, superfp_bmm = _outside("superfp_mm"), _outside("superfp_bmm")
+cublas_mm, cublas_bmm = _outside("cublas_mm"), _outside("cublas_bmm")
+
+
+class cublas_acceleration:
+    """reference: mptorch/quant/cublas.py:45-61.  Kept as an inert switch: tensor-core GEMMs do not round
+    per MAC, so this back end never dispatches to them."""
+    enabled = False
+    fast_mode = None
+
+    def __init__(self, enabled: bool, fast_mode=None):
+        self.enabled_new, self.fast_new = enabled, fast_mode
+
+    def __enter__(self):
+        self.prev = (cublas_acceleration.enabled, cublas_acceleration.fast_mode)
+        cublas_acceleration.enabled, cublas_acceleration.fast_mode = False, self.fast_new
+
+    def __exit__(self, *exc):
+        cublas_acceleration.enabled, cublas_acceleration.fast_mode = self.prev
+
+    @staticmethod
+    def enable(enabled: bool, fast_mode=None):
+        cublas_acceleration.enabled, cublas_acceleration.fast_mode = False, fast_mode

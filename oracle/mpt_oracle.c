@@ -367,55 +367,56 @@ ORC_API void orc_mm(const float *a, const float *b, float *c, int64_t B, int M, 
 {
     fmt_t fa = {man_add, exp_add, sub, sat}, fm = {man_mul, exp_mul, sub, sat};
     int Kpad = K + 8 - K % 8;
+    /* Rows of C are independent; each output still sees its k steps in the stated order.  The loops
+       run k outside j (as the reference CPU kernel does) so B is read along its rows. */
+#pragma omp parallel for collapse(2) schedule(dynamic, 1)
     for (int64_t bi = 0; bi < B; ++bi) {
-        const float *A = a + bi * (int64_t)M * K, *Bm = b + bi * (int64_t)K * N;
-        float *C = c + bi * (int64_t)M * N;
-        for (int i = 0; i < M; ++i)
-            for (int j = 0; j < N; ++j) {
-                if (compensated) {
-                    /* order 1 restates the CUDA kernel (per-output state, padded K);
-                       order 0 uses the same recurrence over k < K.               */
-                    float sum = 0.f, comp = 0.f;
-                    int kend = order ? Kpad : K;
-                    for (int k = 0; k < kend; ++k) {
-                        float av = k < K ? A[(int64_t)i * K + k] : 0.f;
+        for (int i = 0; i < M; ++i) {
+            const float *A = a + bi * (int64_t)M * K + (int64_t)i * K, *Bm = b + bi * (int64_t)K * N;
+            float *C = c + bi * (int64_t)M * N + (int64_t)i * N;
+            float *s1 = (float *)calloc((size_t)N, sizeof(float));   /* acc / inner / sum  */
+            float *s2 = (float *)calloc((size_t)N, sizeof(float));   /* outer / comp       */
+            if (compensated) {
+                /* order 1 restates the CUDA kernel (per-output state, padded K);
+                   order 0 uses the same recurrence over k < K.               */
+                int kend = order ? Kpad : K;
+                for (int k = 0; k < kend; ++k) {
+                    float av = k < K ? A[k] : 0.f;
+                    for (int j = 0; j < N; ++j) {
                         float bv = k < K ? Bm[(int64_t)k * N + j] : 0.f;
-                        float y, t;
-                        if (fma) {
-                            y = Q(fmaf(av, bv, -comp), fa);
-                            t = Q(sum + y, fa);
-                            comp = Q(Q(t - sum, fa) - y, fa);
-                        } else {
-                            float upd = Q(av * bv, fm);
-                            y = Q(upd - comp, fa);
-                            t = Q(sum + y, fa);
-                            comp = Q(Q(t - sum, fa) - y, fa);
-                        }
-                        sum = t;
+                        float sum = s1[j], comp = s2[j], y, t;
+                        if (fma) y = Q(fmaf(av, bv, -comp), fa);
+                        else y = Q(Q(av * bv, fm) - comp, fa);
+                        t = Q(sum + y, fa);
+                        s2[j] = Q(Q(t - sum, fa) - y, fa);
+                        s1[j] = t;
                     }
-                    C[(int64_t)i * N + j] = sum;
-                } else if (order == 0) {
-                    float acc = 0.f;
-                    for (int k = 0; k < K; ++k) {
-                        float av = A[(int64_t)i * K + k], bv = Bm[(int64_t)k * N + j];
-                        acc = fma ? Q(fmaf(av, bv, acc), fa) : Q(acc + Q(av * bv, fm), fa);
-                    }
-                    C[(int64_t)i * N + j] = acc;
-                } else {
-                    float inner = 0.f, outer = 0.f;
-                    for (int k0 = 0; k0 < Kpad; k0 += 8) {
-                        for (int kk = 0; kk < 8; ++kk) {
-                            int k = k0 + kk;
-                            float av = k < K ? A[(int64_t)i * K + k] : 0.f;
-                            float bv = k < K ? Bm[(int64_t)k * N + j] : 0.f;
-                            inner = fma ? Q(fmaf(av, bv, inner), fa) : Q(inner + Q(av * bv, fm), fa);
-                        }
-                        outer = Q(outer + inner, fa);
-                        inner = 0.f;
-                    }
-                    C[(int64_t)i * N + j] = outer;
                 }
+                memcpy(C, s1, (size_t)N * sizeof(float));
+            } else if (order == 0) {
+                for (int k = 0; k < K; ++k) {
+                    float av = A[k];
+                    const float *brow = Bm + (int64_t)k * N;
+                    for (int j = 0; j < N; ++j)
+                        s1[j] = fma ? Q(fmaf(av, brow[j], s1[j]), fa) : Q(s1[j] + Q(av * brow[j], fm), fa);
+                }
+                memcpy(C, s1, (size_t)N * sizeof(float));
+            } else {
+                for (int k0 = 0; k0 < Kpad; k0 += 8) {
+                    for (int kk = 0; kk < 8; ++kk) {
+                        int k = k0 + kk;
+                        float av = k < K ? A[k] : 0.f;
+                        for (int j = 0; j < N; ++j) {
+                            float bv = k < K ? Bm[(int64_t)k * N + j] : 0.f;
+                            s1[j] = fma ? Q(fmaf(av, bv, s1[j]), fa) : Q(s1[j] + Q(av * bv, fm), fa);
+                        }
+                    }
+                    for (int j = 0; j < N; ++j) { s2[j] = Q(s2[j] + s1[j], fa); s1[j] = 0.f; }
+                }
+                memcpy(C, s2, (size_t)N * sizeof(float));
             }
+            free(s1); free(s2);
+        }
     }
 }
 

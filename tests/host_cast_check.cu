@@ -1,0 +1,61 @@
+// Host-side harness around mptorch_b200/csrc/cast.cuh (test infrastructure).
+// The casters are __host__ __device__; compiling them for the CPU lets the CPU test suite
+// sweep the very source the kernels use against the oracle, without a GPU.
+#include <cstdint>
+#include <cstring>
+
+#include "../mptorch_b200/csrc/cast.cuh"
+
+using namespace mpt;
+
+#define HC_API extern "C" __attribute__((visibility("default")))
+
+HC_API void hc_float_quantize(const float* in, float* out, int64_t n, int man, int exp, int sub, int sat,
+                              int mode, const int32_t* rnd, int rbits) {
+    const FpFmt f = make_fmt(man, exp, sub, sat);
+    for (int64_t i = 0; i < n; ++i) {
+        if (mode == 0) out[i] = cast_fp_nearest(in[i], f);
+        else if (mode == 2) out[i] = cast_fp_truncate(in[i], f);
+        else out[i] = cast_fp_stochastic(in[i], (uint32_t)rnd[i], rbits, f);
+    }
+}
+
+HC_API void hc_binary8(const float* in, float* out, int64_t n, int P, int is_signed, int policy, int sub,
+                       int mode, const int32_t* rnd, int prng_bits) {
+    for (int64_t i = 0; i < n; ++i)
+        out[i] = cast_binary8(in[i], P, is_signed != 0, policy, sub != 0, mode, rnd ? (uint32_t)rnd[i] : 0u, prng_bits);
+}
+
+HC_API void hc_superfp(const float* in, float* out, int64_t n, int man, int exp, int bl, int bu, int sat) {
+    for (int64_t i = 0; i < n; ++i) out[i] = cast_superfp(in[i], man, exp, bl, bu, sat != 0);
+}
+
+// Sweep fp32 patterns first, first+stride, ... (count of them) and compare the fast FP-pipe rounding
+// with the exact caster wherever the fast path's precondition holds (finite, exponent within
+// fast_rn_exp_limit, and -- for exp == 8 formats -- not an fp32 denormal).  Returns the number of
+// mismatches; the first mismatching pattern is written to *first_bad.
+HC_API int64_t hc_sweep_fast_rn(int man, int exp, uint64_t first, uint64_t count, uint64_t stride,
+                                uint32_t* first_bad) {
+    const FpFmt f = make_fmt(man, exp, 1, 0);
+    const FastRn fast = FastRn::make(f);
+    const int lim = fast_rn_exp_limit(f);
+    int64_t bad = 0;
+    uint32_t firstbad = 0;
+#pragma omp parallel for reduction(+ : bad) schedule(static)
+    for (int64_t i = 0; i < (int64_t)count; ++i) {
+        const uint32_t t = (uint32_t)(first + (uint64_t)i * stride);
+        const int E = (int)((t << 1) >> 24) - 127;
+        if (E > lim) continue;
+        if (exp == 8 && E == -127 && (t & 0x7FFFFFu) != 0u) continue;
+        const float x = u2f(t);
+        const uint32_t want = f2u(cast_fp_nearest(x, f));
+        const uint32_t got = f2u(fast(x));
+        if (want != got) {
+            ++bad;
+#pragma omp critical
+            if (firstbad == 0) firstbad = t;
+        }
+    }
+    if (first_bad) *first_bad = firstbad;
+    return bad;
+}

@@ -1,0 +1,99 @@
+"""Sweeps the kernels' caster source (mptorch_b200/csrc/cast.cuh, compiled for the host by
+tests/host_cast_check.cu) against the oracle on the CPU.  This checks the arithmetic the CUDA
+kernels are built from before any GPU time is spent; the GPU tests then check the kernels."""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+import pytest
+
+from conftest import ROOT, golden, mismatch_report, same_bits
+
+SO = os.path.join(ROOT, "tests", "_build", "libhostcast.so")
+SRC = os.path.join(ROOT, "tests", "host_cast_check.cu")
+HDR = os.path.join(ROOT, "mptorch_b200", "csrc", "cast.cuh")
+POL = ["saturate_infty", "saturate_maxfloat", "saturate_maxfloat2"]
+MODE = {"nearest": 0, "stochastic": 1, "truncate": 2}
+
+
+@pytest.fixture(scope="module")
+def hc():
+    newest = max(os.path.getmtime(SRC), os.path.getmtime(HDR))
+    if not os.path.exists(SO) or os.path.getmtime(SO) < newest:
+        os.makedirs(os.path.dirname(SO), exist_ok=True)
+        subprocess.check_call(["nvcc", "-O2", "-std=c++17", "-Wno-deprecated-gpu-targets", "-Xcompiler",
+                               "-fPIC,-fopenmp,-ffp-contract=off", "-shared", "-o", SO, SRC, "-lgomp"])
+    L = C.CDLL(SO)
+    p, i32, i64, u64 = C.c_void_p, C.c_int, C.c_int64, C.c_uint64
+    L.hc_float_quantize.argtypes = [p, p, i64, i32, i32, i32, i32, i32, p, i32]
+    L.hc_binary8.argtypes = [p, p, i64, i32, i32, i32, i32, i32, p, i32]
+    L.hc_superfp.argtypes = [p, p, i64, i32, i32, i32, i32, i32]
+    L.hc_sweep_fast_rn.restype = i64
+    L.hc_sweep_fast_rn.argtypes = [i32, i32, u64, u64, u64, p]
+    return L
+
+
+def _ptr(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+def _inputs(seed, n):
+    rng = np.random.default_rng(seed)
+    rnd = rng.integers(0, 2**32, size=n, dtype=np.uint64).astype(np.uint32)
+    return np.concatenate([golden("casters.npz")["in_bits"], rnd]).view(np.float32)
+
+
+@pytest.mark.parametrize("fmt", [(5, 2), (4, 3), (5, 10), (8, 7), (8, 1), (2, 23), (3, 0), (6, 9), (8, 23),
+                                 (2, 1), (7, 16), (8, 0), (8, 22), (1, 3), (4, 22)])
+def test_fp_casters_match_oracle(hc, oracle, fmt):
+    e, m = fmt
+    x = _inputs(e * 31 + m, 1 << 18)
+    rng = np.random.default_rng(5)
+    r = rng.integers(0, 2**31 - 1, size=x.size, dtype=np.int64).astype(np.int32)
+    for sub in (0, 1):
+        for sat in (0, 1):
+            for mode in ("nearest", "truncate", "stochastic"):
+                rbits_list = (0, 23 - m, max(0, 10 - m)) if mode == "stochastic" else (0,)
+                for rbits in set(rbits_list):
+                    got = np.empty_like(x)
+                    hc.hc_float_quantize(_ptr(x), _ptr(got), x.size, m, e, sub, sat, MODE[mode], _ptr(r), rbits)
+                    want = oracle.float_quantize(x, m, e, mode, bool(sub), bool(sat), rand=r, rbits=rbits)
+                    assert same_bits(got, want), f"{mode} sub={sub} sat={sat} rbits={rbits}: " + mismatch_report(got, want)
+
+
+@pytest.mark.parametrize("P", range(1, 8))
+def test_binary8_caster_matches_oracle(hc, oracle, P):
+    x = _inputs(P, 1 << 16)
+    rng = np.random.default_rng(6)
+    r = rng.integers(0, 2**31 - 1, size=x.size, dtype=np.int64).astype(np.int32)
+    for sg in (0, 1):
+        for po in range(3):
+            for sub in (0, 1):
+                for mode in ("nearest", "truncate", "stochastic"):
+                    prng = 23 - (P - 1) if mode == "stochastic" else 0
+                    got = np.empty_like(x)
+                    hc.hc_binary8(_ptr(x), _ptr(got), x.size, P, sg, po, sub, MODE[mode], _ptr(r), prng)
+                    want = oracle.binary8_quantize(x, P, mode, POL[po], bool(sg), bool(sub), rand=r, prng_bits=prng)
+                    assert same_bits(got, want), f"{mode} sg={sg} po={po} sub={sub}: " + mismatch_report(got, want)
+
+
+def test_superfp_caster_matches_oracle(hc, oracle):
+    x = _inputs(77, 1 << 17)
+    for (e, m, bl, bu) in [(4, 3, 1, 1), (4, 3, 2, 1), (5, 2, 1, 2), (3, 4, 1, 1), (6, 1, 2, 2), (4, 2, 3, 1), (7, 5, 1, 1)]:
+        for sat in (0, 1):
+            got = np.empty_like(x)
+            hc.hc_superfp(_ptr(x), _ptr(got), x.size, m, e, bl, bu, sat)
+            want = oracle.superfp_quantize(x, m, e, bl, bu, bool(sat))
+            assert same_bits(got, want), f"e{e}m{m} l{bl} u{bu} sat={sat}: " + mismatch_report(got, want)
+
+
+@pytest.mark.parametrize("fmt", [(5, 2), (4, 3), (5, 10), (8, 7), (8, 0), (2, 1), (6, 21), (3, 0), (8, 21), (7, 4)])
+def test_fast_rounding_equals_exact_cast(hc, fmt):
+    """The FP-pipe rounding used in the GEMM inner loop equals the exact caster on its whole domain.
+    Headline formats are swept over all 2^32 patterns; the others over every 257th pattern."""
+    e, m = fmt
+    stride = 1 if fmt in ((5, 2), (4, 3)) else 257
+    first_bad = np.zeros(1, dtype=np.uint32)
+    bad = hc.hc_sweep_fast_rn(m, e, 0, (2**32 + stride - 1) // stride, stride, _ptr(first_bad))
+    assert bad == 0, f"e{e}m{m}: {bad} mismatches, first at pattern {int(first_bad[0]):#010x}"

@@ -1,0 +1,247 @@
+"""GPU parity of the per-MAC rounded GEMM: CUDA kernels (through the C ABI) vs the CPU oracle, bit for bit."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import golden, mismatch_report, same_bits
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def be():
+    from mptorch_b200 import backend
+
+    return backend
+
+
+def dev(x):
+    return torch.from_numpy(np.ascontiguousarray(x, dtype=np.float32)).cuda()
+
+
+def gpu_mm(be, a, b, fadd, fmul, sub=True, sat=False, fma=False, order="cuda", comp=False):
+    ad, bd = dev(a), dev(b)
+    batched = ad.dim() == 3
+    M, K = ad.shape[-2:]
+    N = bd.shape[-1]
+    c = torch.full((ad.shape[0], M, N) if batched else (M, N), float("nan"), device="cuda")
+    if fma:
+        fn = be.float_quantize_nearest_bmm_fma if batched else be.float_quantize_nearest_mm_fma
+        fn(ad, bd, c, M, N, K, fadd[1], fadd[0], sub, sat, comp, order=order)
+    else:
+        fn = be.float_quantize_nearest_bmm if batched else be.float_quantize_nearest_mm
+        fn(ad, bd, c, M, N, K, fadd[1], fadd[0], fmul[1], fmul[0], sub, sat, comp, order=order)
+    return c.cpu().numpy()
+
+
+def cpu_mm(oracle, a, b, fadd, fmul, sub=True, sat=False, fma=False, order="cuda", comp=False):
+    return oracle.mm(a, b, fadd[1], fadd[0], fmul[1], fmul[0], sub, sat, fma, "tile8" if order == "cuda" else "seq", comp)
+
+
+FORMATS = [((5, 2), (5, 2)), ((5, 10), (4, 3)), ((8, 7), (5, 2)), ((4, 3), (4, 3)), ((8, 23), (5, 2)), ((6, 21), (3, 0))]
+SHAPES = [(78, 101, 145), (64, 256, 48), (9, 32, 12), (1, 1, 1), (130, 8, 70), (17, 40, 4), (128, 64, 64), (5, 7, 3)]
+
+
+def test_config1_sequential_256(be, oracle):
+    """BASELINE config 1: 256x256x256, N(0,1), e5m2 multiply and add, nearest, sequential K."""
+    rng = np.random.default_rng(2025)
+    a = rng.standard_normal((256, 256)).astype(np.float32)
+    b = rng.standard_normal((256, 256)).astype(np.float32)
+    got = gpu_mm(be, a, b, (5, 2), (5, 2), order="seq")
+    want = cpu_mm(oracle, a, b, (5, 2), (5, 2), order="seq")
+    assert same_bits(got, want), mismatch_report(got, want)
+    got = gpu_mm(be, a, b, (5, 2), (5, 2), order="cuda")
+    want = cpu_mm(oracle, a, b, (5, 2), (5, 2), order="cuda")
+    assert same_bits(got, want), mismatch_report(got, want)
+
+
+def test_seq_matches_reference_fixture(be):
+    """Against outputs of the reference's own CPU extension (tests/golden/mm_seq.npz)."""
+    g = golden("mm_seq.npz")
+    n = 0
+    for key in g.files:
+        p = key.split("_")
+        if len(p) < 3 or p[1] not in ("mm", "fma") or p[0] == "big":
+            continue
+        a, b = g[p[0] + "_a"], g[p[0] + "_b"]
+        want = g[key].view(np.float32)
+        if p[1] == "mm":
+            ea, ma = p[3][1:].split("m")
+            em, mm_ = p[5][1:].split("m")
+            got = gpu_mm(be, a, b, (int(ea), int(ma)), (int(em), int(mm_)), sat=bool(int(p[6][3:])), order="seq")
+        else:
+            ea, ma = p[2][1:].split("m")
+            got = gpu_mm(be, a, b, (int(ea), int(ma)), None, fma=True, order="seq")
+        assert same_bits(got, want), key + ": " + mismatch_report(got, want)
+        n += 1
+    assert n >= 30
+    got = gpu_mm(be, g["bmm_a"], g["bmm_b"], (5, 2), (5, 2), order="seq")
+    assert same_bits(got, g["bmm_e5m2"].view(np.float32))
+    for sat in (0, 1):
+        got = gpu_mm(be, g["big_a"], g["big_b"], (5, 2), (5, 2), sat=bool(sat), order="seq")
+        want = g[f"big_mm_e5m2_sat{sat}"].view(np.float32)
+        assert same_bits(got, want), mismatch_report(got, want)
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+@pytest.mark.parametrize("order", ["cuda", "seq"])
+def test_shapes_formats(be, oracle, shape, order):
+    M, K, N = shape
+    rng = np.random.default_rng(M * 1000 + K * 10 + N)
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    b = rng.standard_normal((K, N)).astype(np.float32)
+    for fadd, fmul in FORMATS:
+        for fma in (False, True):
+            got = gpu_mm(be, a, b, fadd, fmul, fma=fma, order=order)
+            want = cpu_mm(oracle, a, b, fadd, fmul, fma=fma, order=order)
+            assert same_bits(got, want), f"{fadd}/{fmul} fma={fma}: " + mismatch_report(got, want)
+
+
+@pytest.mark.parametrize("order", ["cuda", "seq"])
+def test_value_ranges_that_leave_the_fast_path(be, oracle, order):
+    """Overflow to inf, saturation, tiny values, specials: the exact path must take over seamlessly."""
+    rng = np.random.default_rng(17)
+    M, K, N = 40, 72, 36
+    base_a = rng.standard_normal((M, K)).astype(np.float32)
+    base_b = rng.standard_normal((K, N)).astype(np.float32)
+    cases = {
+        "huge": (base_a * 300, base_b * 300),
+        "mid": (base_a * 20, base_b * 20),
+        "tiny": (base_a * 1e-4, base_b * 1e-3),
+        "denormal_products": (base_a * 1e-20, base_b * 1e-20),
+    }
+    sp_a, sp_b = base_a.copy(), base_b.copy()
+    sp_a[3, 5] = np.inf; sp_a[7, 1] = np.nan; sp_b[2, 9] = -np.inf; sp_a[11, :] = 0.0; sp_b[:, 4] = -0.0
+    cases["specials"] = (sp_a, sp_b)
+    one_big = base_a.copy(); one_big[0, 0] = 3e4
+    cases["one_big"] = (one_big, base_b)
+    for name, (a, b) in cases.items():
+        for fadd, fmul in [((5, 2), (5, 2)), ((5, 10), (4, 3)), ((8, 7), (5, 2)), ((8, 7), (8, 7))]:
+            for sat in (False, True):
+                for fma in (False, True):
+                    got = gpu_mm(be, a, b, fadd, fmul, sat=sat, fma=fma, order=order)
+                    want = cpu_mm(oracle, a, b, fadd, fmul, sat=sat, fma=fma, order=order)
+                    assert same_bits(got, want), f"{name} {fadd}/{fmul} sat={sat} fma={fma}: " + mismatch_report(got, want)
+
+
+def test_without_subnormals(be, oracle):
+    rng = np.random.default_rng(5)
+    a = (rng.standard_normal((33, 50)) * 0.05).astype(np.float32)
+    b = (rng.standard_normal((50, 20)) * 0.05).astype(np.float32)
+    for order in ("cuda", "seq"):
+        got = gpu_mm(be, a, b, (5, 2), (4, 3), sub=False, order=order)
+        want = cpu_mm(oracle, a, b, (5, 2), (4, 3), sub=False, order=order)
+        assert same_bits(got, want), mismatch_report(got, want)
+
+
+def test_batched(be, oracle):
+    rng = np.random.default_rng(6)
+    a = rng.standard_normal((5, 70, 33)).astype(np.float32)
+    b = rng.standard_normal((5, 33, 20)).astype(np.float32)
+    for order in ("cuda", "seq"):
+        for fma in (False, True):
+            got = gpu_mm(be, a, b, (5, 10), (4, 3), fma=fma, order=order)
+            want = cpu_mm(oracle, a, b, (5, 10), (4, 3), fma=fma, order=order)
+            assert same_bits(got, want), mismatch_report(got, want)
+
+
+def test_attention_shapes(be, oracle):
+    """BASELINE config 5 attention GEMM shapes at reduced batch: [B,1024,64]x[B,64,1024] rows sampled."""
+    rng = np.random.default_rng(8)
+    a = rng.standard_normal((2, 96, 64)).astype(np.float32)
+    b = rng.standard_normal((2, 64, 1024)).astype(np.float32)
+    got = gpu_mm(be, a, b, (5, 10), (4, 3))
+    want = cpu_mm(oracle, a, b, (5, 10), (4, 3))
+    assert same_bits(got, want), mismatch_report(got, want)
+
+
+def test_compensated(be, oracle):
+    rng = np.random.default_rng(9)
+    a = rng.standard_normal((30, 45)).astype(np.float32)
+    b = rng.standard_normal((45, 22)).astype(np.float32)
+    for fma in (False, True):
+        got = gpu_mm(be, a, b, (5, 10), (4, 3), fma=fma, comp=True)
+        want = cpu_mm(oracle, a, b, (5, 10), (4, 3), fma=fma, comp=True)
+        assert same_bits(got, want), f"fma={fma}: " + mismatch_report(got, want)
+
+
+def test_stochastic_matches_oracle_philox(be, oracle):
+    rng = np.random.default_rng(10)
+    a = rng.standard_normal((3, 20, 37)).astype(np.float32)
+    b = rng.standard_normal((3, 37, 24)).astype(np.float32)
+    seed = 0xDEADBEEF12345
+    c = torch.zeros(3, 20, 24, device="cuda")
+    be.float_quantize_stochastic_bmm(dev(a), dev(b), c, 20, 24, 37, 10, 5, 13, 3, 4, 20, True, False, seed=seed)
+    want = oracle.mm_sr(a, b, 10, 5, 13, 3, 4, 20, True, False, False, seed)
+    assert same_bits(c.cpu().numpy(), want), mismatch_report(c.cpu().numpy(), want)
+    c2 = torch.zeros(20, 24, device="cuda")
+    be.float_quantize_stochastic_mm_fma(dev(a[0]), dev(b[0]), c2, 20, 24, 37, 10, 5, 13, True, False, seed=seed)
+    want = oracle.mm_sr(a[0], b[0], 10, 5, 13, 10, 5, 13, True, False, True, seed)
+    assert same_bits(c2.cpu().numpy(), want), mismatch_report(c2.cpu().numpy(), want)
+
+
+def test_stochastic_statistics(be):
+    """SR accumulation is unbiased: the mean over many seeds approaches the fp32 product."""
+    rng = np.random.default_rng(11)
+    a = rng.standard_normal((16, 64)).astype(np.float32)
+    b = rng.standard_normal((64, 16)).astype(np.float32)
+    ad, bd = dev(a), dev(b)
+    acc = torch.zeros(16, 16, device="cuda", dtype=torch.float64)
+    reps = 200
+    for s in range(reps):
+        c = torch.zeros(16, 16, device="cuda")
+        be.float_quantize_stochastic_mm(ad, bd, c, 16, 16, 64, 7, 8, 16, 7, 8, 16, True, False, seed=s)
+        acc += c.double()
+    exact = torch.from_numpy(a.astype(np.float64) @ b.astype(np.float64)).cuda()
+    err = (acc / reps - exact).abs().max().item()
+    assert err < 0.05, err
+
+
+def test_empty_and_degenerate(be):
+    c = torch.full((4, 6), 7.0, device="cuda")
+    be.float_quantize_nearest_mm(torch.zeros(4, 0, device="cuda"), torch.zeros(0, 6, device="cuda"), c, 4, 6, 0, 2, 5, 2, 5, True, False, False)
+    assert torch.equal(c, torch.zeros_like(c))
+    c0 = torch.zeros(0, 6, device="cuda")
+    be.float_quantize_nearest_mm(torch.zeros(0, 3, device="cuda"), torch.zeros(3, 6, device="cuda"), c0, 0, 6, 3, 2, 5, 2, 5, True, False, False)
+
+
+def test_exact_path_without_workspace(oracle):
+    """Calling the C ABI with no workspace still gives the same bits (exact casts only)."""
+    from mptorch_b200 import _cabi
+
+    rng = np.random.default_rng(12)
+    a = rng.standard_normal((50, 64)).astype(np.float32)
+    b = rng.standard_normal((64, 44)).astype(np.float32)
+    ad, bd = dev(a), dev(b)
+    c = torch.zeros(50, 44, device="cuda")
+    _cabi.call("mpt_float_mm_nearest", _cabi.ptr(ad), _cabi.ptr(bd), _cabi.ptr(c), 1, 50, 44, 64, 2, 5, 2, 5, 1, 0, 0, 1,
+               None, 0, _cabi.stream_ptr(c.device))
+    want = oracle.mm(a, b, 2, 5, 2, 5, True, False, False, "tile8")
+    assert same_bits(c.cpu().numpy(), want)
+
+
+@pytest.mark.parametrize("fmts", [((5, 2), (5, 2)), ((5, 10), (4, 3)), ((8, 7), (5, 2))])
+def test_full_size_row_samples_and_sharding(be, oracle, fmts):
+    """BASELINE config 4 at its largest size (8192^3 for the headline format, 4096^3 otherwise): sampled
+    rows equal the oracle bit for bit (rows of C are independent), and a row-sharded run equals the
+    single launch (the multi-GPU decomposition)."""
+    fadd, fmul = fmts
+    S = 8192 if fmts == ((5, 2), (5, 2)) else 4096
+    g = torch.Generator(device="cuda").manual_seed(77)
+    a = torch.randn(S, S, device="cuda", generator=g)
+    b = torch.randn(S, S, device="cuda", generator=g)
+    c = torch.empty(S, S, device="cuda")
+    be.float_quantize_nearest_mm(a, b, c, S, S, S, fadd[1], fadd[0], fmul[1], fmul[0], True, False, False, order="cuda")
+    rows = [0, 1, S // 2 + 3, S - 1]
+    want = oracle.mm(a[rows].cpu().numpy(), b.cpu().numpy(), fadd[1], fadd[0], fmul[1], fmul[0], True, False, False, "tile8")
+    got = c[rows].cpu().numpy()
+    assert same_bits(got, want), mismatch_report(got, want)
+    # row shard [S/4, S/2) computed alone
+    lo, hi = S // 4, S // 2
+    cs = torch.empty(hi - lo, S, device="cuda")
+    be.float_quantize_nearest_mm(a[lo:hi].contiguous(), b, cs, hi - lo, S, S, fadd[1], fadd[0], fmul[1], fmul[0], True, False, False, order="cuda")
+    assert torch.equal(cs.view(torch.int32), c[lo:hi].view(torch.int32))
+    if S == 8192:
+        be.float_quantize_nearest_mm(a, b, c, S, S, S, fadd[1], fadd[0], fmul[1], fmul[0], True, False, False, order="seq")
+        want = oracle.mm(a[rows[:2]].cpu().numpy(), b.cpu().numpy(), fadd[1], fadd[0], fmul[1], fmul[0], True, False, False, "seq")
+        assert same_bits(c[rows[:2]].cpu().numpy(), want)

@@ -1,0 +1,108 @@
+"""Same-GPU comparison with the reference's own CUDA extension (oracle/_ref/quant_cuda, the unmodified
+reference sources compiled for sm_100a).  It pins the "cuda" accumulation order and the elementwise casts
+against the code this library replaces.  Only kernels whose memory accesses are bounds-checked in the
+reference source are run (elementwise quantizers, mm_impl / bmm_impl, mm_fma_impl); its stochastic GEMM
+(racy, out-of-range state indexing) is never launched."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ref_cuda():
+    from oracle.build_ref import load_ref
+
+    try:
+        mod = load_ref("quant_cuda")
+    except Exception as ex:  # pragma: no cover
+        pytest.skip("reference quant_cuda could not be loaded: %r" % (ex,))
+    if mod is None:
+        pytest.skip("oracle/_ref/quant_cuda not built")
+    return mod
+
+
+@pytest.fixture(scope="module")
+def be():
+    from mptorch_b200 import backend
+
+    return backend
+
+
+def bits_equal(a, b):
+    a, b = a.contiguous(), b.contiguous()
+    same = a.view(torch.int32) == b.view(torch.int32)
+    return bool((same | (a.isnan() & b.isnan())).all())
+
+
+def test_float_quantize_nearest(ref_cuda, be):
+    g = torch.Generator(device="cuda").manual_seed(1)
+    bits = torch.randint(-2**31, 2**31 - 1, (1 << 22,), device="cuda", generator=g, dtype=torch.int64).to(torch.int32)
+    x = bits.view(torch.float32)
+    for (e, m) in [(5, 2), (4, 3), (5, 10), (8, 7), (3, 0)]:
+        for sub in (False, True):
+            for sat in (False, True):
+                assert bits_equal(be.float_quantize_nearest(x, m, e, sub, sat), ref_cuda.float_quantize_nearest(x, m, e, sub, sat)), (e, m, sub, sat)
+
+
+def test_float_quantize_stochastic_same_seed(ref_cuda, be):
+    x = torch.randn(1 << 20, device="cuda") * 3
+    for (e, m, prng) in [(4, 3, 20), (5, 2, 21), (5, 2, 4), (8, 7, 16)]:
+        torch.manual_seed(123)
+        want = ref_cuda.float_quantize_stochastic(x, m, e, prng, True, True)
+        torch.manual_seed(123)
+        got = be.float_quantize_stochastic(x, m, e, prng, True, True)
+        assert bits_equal(got, want), (e, m, prng)
+
+
+def test_binary8(ref_cuda, be):
+    g = torch.Generator(device="cuda").manual_seed(2)
+    bits = torch.randint(-2**31, 2**31 - 1, (1 << 20,), device="cuda", generator=g, dtype=torch.int64).to(torch.int32)
+    x = bits.view(torch.float32)
+    pol = [ref_cuda.OverflowPolicy.SATURATE_INFTY, ref_cuda.OverflowPolicy.SATURATE_MAXFLOAT, ref_cuda.OverflowPolicy.SATURATE_MAXFLOAT2]
+    for P in (1, 3, 4, 7):
+        for sg in (False, True):
+            for po in range(3):
+                assert bits_equal(be.binary8_quantize_nearest(x, P, sg, po, True), ref_cuda.binary8_quantize_nearest(x, P, sg, pol[po], True)), (P, sg, po)
+                assert bits_equal(be.binary8_quantize_truncate(x, P, sg, po, True), ref_cuda.binary8_quantize_truncate(x, P, sg, pol[po], True)), (P, sg, po)
+
+
+@pytest.mark.parametrize("shape", [(256, 256, 256), (78, 101, 145), (512, 1000, 320)])
+def test_mm_cuda_order(ref_cuda, be, shape):
+    M, K, N = shape
+    a = torch.randn(M, K, device="cuda")
+    b = torch.randn(K, N, device="cuda")
+    for (ea, ma, em, mm_) in [(5, 2, 5, 2), (5, 10, 4, 3), (8, 7, 5, 2)]:
+        want = torch.zeros(M, N, device="cuda")
+        ref_cuda.float_quantize_nearest_mm(a, b, want, M, N, K, ma, ea, mm_, em, True, False, False)
+        got = torch.empty(M, N, device="cuda")
+        be.float_quantize_nearest_mm(a, b, got, M, N, K, ma, ea, mm_, em, True, False, False, order="cuda")
+        assert bits_equal(got, want), (shape, ea, ma, em, mm_)
+        want = torch.zeros(M, N, device="cuda")
+        ref_cuda.float_quantize_nearest_mm_fma(a, b, want, M, N, K, ma, ea, True, False, False)
+        got = torch.empty(M, N, device="cuda")
+        be.float_quantize_nearest_mm_fma(a, b, got, M, N, K, ma, ea, True, False, False, order="cuda")
+        assert bits_equal(got, want), ("fma", shape, ea, ma)
+
+
+def test_bmm_cuda_order(ref_cuda, be):
+    a = torch.randn(6, 128, 64, device="cuda")
+    b = torch.randn(6, 64, 96, device="cuda")
+    want = torch.zeros(6, 128, 96, device="cuda")
+    ref_cuda.float_quantize_nearest_bmm(a, b, want, 128, 96, 64, 10, 5, 3, 4, True, False, False)
+    got = torch.empty(6, 128, 96, device="cuda")
+    be.float_quantize_nearest_bmm(a, b, got, 128, 96, 64, 10, 5, 3, 4, True, False, False, order="cuda")
+    assert bits_equal(got, want)
+
+
+def test_full_size_headline_vs_reference(ref_cuda, be):
+    """4096^3, e5m2: the whole matrix equals the reference CUDA kernel's output."""
+    S = 4096
+    a = torch.randn(S, S, device="cuda")
+    b = torch.randn(S, S, device="cuda")
+    want = torch.zeros(S, S, device="cuda")
+    ref_cuda.float_quantize_nearest_mm(a, b, want, S, S, S, 2, 5, 2, 5, True, False, False)
+    got = torch.empty(S, S, device="cuda")
+    be.float_quantize_nearest_mm(a, b, got, S, S, S, 2, 5, 2, 5, True, False, False, order="cuda")
+    assert bits_equal(got, want)
