@@ -130,6 +130,55 @@ MPT_API int mpt_float_mm_stochastic(const float *a, const float *b, float *c, in
                                     int man_mul, int exp_mul, int rbits_mul,
                                     int subnormals, int saturate, int fma, uint64_t seed, void *stream);
 
+/* ---- quantized row reductions ------------------------------------------------------------------
+ * The tensor is viewed as [outer, channel, inner] (the reference's partition_tensor,
+ * quant_cuda/quant.cu:678-726); a row is the `channel` elements at a fixed (outer, inner) position.
+ * order: MPT_ORDER_CUDA = the reference CUDA kernels' 64-partials + shuffle-tree association,
+ *        MPT_ORDER_SEQ  = the reference CPU loops' left-to-right association. */
+
+/* replaces float_quantize_nearest_softmax_forward (pybind_cuda.cpp:599 -> quant.cu:854 ->
+ * fp_kernel.cu:417 -> softmax_kernel.h:23-100; CPU twin quant_cpu/softmax.h:11-46) */
+MPT_API int mpt_float_softmax_forward(const float *in, float *out, int64_t outer, int channel, int64_t inner,
+                                      int man_exp, int exp_exp, int man_off, int exp_off, int man_acc, int exp_acc,
+                                      int subnormals, int saturate, int order, void *stream);
+
+/* replaces float_quantize_nearest_softmax_lse_forward (pybind_cuda.cpp:615 -> quant.cu:868 ->
+ * softmax_kernel.h:102-171; CPU twin quant_cpu/softmax.h:50-87) */
+MPT_API int mpt_float_softmax_lse_forward(const float *in, float *out, int64_t outer, int channel, int64_t inner,
+                                          int man_off, int exp_off, int man_lse, int exp_lse,
+                                          int subnormals, int saturate, int order, void *stream);
+
+/* replaces float_quantize_nearest_softmax_backward (pybind_cuda.cpp:629 -> quant.cu:880 ->
+ * softmax_kernel.h:173-222; CPU twin quant_cpu/softmax.h:89-114).  y: softmax output, grad: dL/dy. */
+MPT_API int mpt_float_softmax_backward(const float *y, const float *grad, float *out, int64_t outer, int channel,
+                                       int64_t inner, int man_add, int exp_add, int man_mul, int exp_mul,
+                                       int subnormals, int saturate, int order, void *stream);
+
+/* replaces float_quantize_layernorm_forward (pybind_cuda.cpp:434 -> quant.cu:728 -> fp_kernel.cu:452 ->
+ * layernorm_kernel.h:7-100; CPU twin quant_cpu/layernorm.h:10-57).  weight, bias: [channel];
+ * mean, rstd: [outer * inner] outputs. */
+MPT_API int mpt_float_layernorm_forward(const float *in, const float *weight, const float *bias, float *out,
+                                        float *mean, float *rstd, float eps, int64_t outer, int channel, int64_t inner,
+                                        int man_acc, int exp_acc, int man_mul, int exp_mul, int man_div, int exp_div,
+                                        int man_sqrt, int exp_sqrt, int subnormals, int saturate, int order,
+                                        void *stream);
+
+/* replaces float_quantize_layernorm_backward (pybind_cuda.cpp:459 -> quant.cu:748 -> fp_kernel.cu:468-488 ->
+ * layernorm_kernel.h:105-237; CPU twin quant_cpu/layernorm.h:60-116).  Needs no scratch tensor: the
+ * reference's [rows, channel] x-hat*dy staging buffer (a cudaMalloc per call) is recomputed instead.
+ * grad_gamma, grad_beta: [channel], fully overwritten. */
+MPT_API int mpt_float_layernorm_backward(const float *in, const float *grad_out, const float *weight,
+                                         const float *mean, const float *rstd, float *grad_in, float *grad_gamma,
+                                         float *grad_beta, int64_t outer, int channel, int64_t inner,
+                                         int man_acc, int exp_acc, int man_mul, int exp_mul, int man_div, int exp_div,
+                                         int subnormals, int saturate, int order, void *stream);
+
+/* Sequential rounded column sums of a [rows, cols] matrix: out[c] = Q(...Q(Q(0 + x[0,c]) + x[1,c])...).
+ * One launch for what the reference does as a Python loop of one quantize call per row
+ * (mptorch/quant/functional.py:736-748, used for the bias gradient at :160-168). */
+MPT_API int mpt_qsum_rows(const float *in, float *out, int64_t rows, int64_t cols, int man, int exp,
+                          int subnormals, int saturate, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

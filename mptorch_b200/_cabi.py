@@ -44,6 +44,12 @@ def lib() -> C.CDLL:
             "mpt_float_mm_nearest": [p, p, p, i64, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, p, sz, p],
             "mpt_float_mm_nearest_fma": [p, p, p, i64, i32, i32, i32, i32, i32, i32, i32, i32, i32, p, sz, p],
             "mpt_float_mm_stochastic": [p, p, p, i64, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, u64, p],
+            "mpt_float_softmax_forward": [p, p, i64, i32, i64] + [i32] * 9 + [p],
+            "mpt_float_softmax_lse_forward": [p, p, i64, i32, i64] + [i32] * 7 + [p],
+            "mpt_float_softmax_backward": [p, p, p, i64, i32, i64] + [i32] * 7 + [p],
+            "mpt_float_layernorm_forward": [p] * 6 + [C.c_float, i64, i32, i64] + [i32] * 11 + [p],
+            "mpt_float_layernorm_backward": [p] * 8 + [i64, i32, i64] + [i32] * 9 + [p],
+            "mpt_qsum_rows": [p, p, i64, i64, i32, i32, i32, i32, p],
         }
         for name, args in sig.items():
             fn = getattr(L, name, None)

@@ -242,3 +242,95 @@ def float_quantize_stochastic_bmm_fma(a, b, c, M, N, K, man_fma, exp_fma, rbits_
     """pybind_cuda.cpp:300."""
     _mm_sr(a, b, c, _batch_of(a), M, N, K, man_fma, exp_fma, rbits_fma, man_fma, exp_fma, rbits_fma, subnormals,
            saturate, True, seed)
+
+
+# ---------------------------------------------------------------------------------- row reductions
+def partition_tensor(shape, dim):
+    """(outer, channel, inner) of a reduction over ``dim`` (int) or over the trailing ``dims`` (list, given
+    last dimension first as the layers do).  reference: quant_cuda/quant.cu:678-726."""
+    nd = len(shape)
+    if isinstance(dim, int):
+        real = [(nd + (dim % nd)) % nd]
+        lo = hi = real[0]
+    else:
+        real = [(nd + (d % nd)) % nd for d in dim]
+        lo, hi = real[-1], real[0]
+    channel = 1
+    for d in real:
+        channel *= shape[d]
+    outer = 1
+    for i in range(lo):
+        outer *= shape[i]
+    inner = 1
+    for i in range(hi + 1, nd):
+        inner *= shape[i]
+    return outer, channel, inner
+
+
+def float_quantize_nearest_softmax_forward(a, o, dim, man_exp, exp_exp, man_off, exp_off, man_acc, exp_acc, subnormals,
+                                           saturate, order=None):
+    """pybind_cuda.cpp:599."""
+    check_cuda_f32(a, "a"); check_cuda_f32(o, "o")
+    outer, ch, inner = partition_tensor(a.shape, dim)
+    with torch.cuda.device(a.device):
+        call("mpt_float_softmax_forward", ptr(a), ptr(o), outer, ch, inner, man_exp, exp_exp, man_off, exp_off, man_acc,
+             exp_acc, int(subnormals), int(saturate), _order_code(order, "reduce_order"), stream_ptr(a.device))
+
+
+def float_quantize_nearest_softmax_lse_forward(a, o, dim, man_off, exp_off, man_lse, exp_lse, subnormals, saturate,
+                                               order=None):
+    """pybind_cuda.cpp:615."""
+    check_cuda_f32(a, "a"); check_cuda_f32(o, "o")
+    outer, ch, inner = partition_tensor(a.shape, dim)
+    with torch.cuda.device(a.device):
+        call("mpt_float_softmax_lse_forward", ptr(a), ptr(o), outer, ch, inner, man_off, exp_off, man_lse, exp_lse,
+             int(subnormals), int(saturate), _order_code(order, "reduce_order"), stream_ptr(a.device))
+
+
+def float_quantize_nearest_softmax_backward(a, g, o, dim, man_add, exp_add, man_mul, exp_mul, subnormals, saturate,
+                                            order=None):
+    """pybind_cuda.cpp:629.  ``a`` is the softmax output, ``g`` the incoming gradient."""
+    check_cuda_f32(a, "a"); check_cuda_f32(g, "g"); check_cuda_f32(o, "o")
+    outer, ch, inner = partition_tensor(a.shape, dim)
+    with torch.cuda.device(a.device):
+        call("mpt_float_softmax_backward", ptr(a), ptr(g), ptr(o), outer, ch, inner, man_add, exp_add, man_mul, exp_mul,
+             int(subnormals), int(saturate), _order_code(order, "reduce_order"), stream_ptr(a.device))
+
+
+def float_quantize_layernorm_forward(input, weight, bias, output, mean, rstd, eps, dims, man_acc, exp_acc, man_mul,
+                                     exp_mul, man_div, exp_div, man_sqrt, exp_sqrt, subnormals, saturate, order=None):
+    """pybind_cuda.cpp:434."""
+    for t, n in ((input, "input"), (weight, "weight"), (bias, "bias"), (output, "output"), (mean, "mean"), (rstd, "rstd")):
+        check_cuda_f32(t, n)
+    outer, ch, inner = partition_tensor(input.shape, list(dims))
+    with torch.cuda.device(input.device):
+        call("mpt_float_layernorm_forward", ptr(input), ptr(weight), ptr(bias), ptr(output), ptr(mean), ptr(rstd),
+             float(eps), outer, ch, inner, man_acc, exp_acc, man_mul, exp_mul, man_div, exp_div, man_sqrt, exp_sqrt,
+             int(subnormals), int(saturate), _order_code(order, "reduce_order"), stream_ptr(input.device))
+
+
+def float_quantize_layernorm_backward(input, grad_output, weight, bias, mean, rstd, grad_input, grad_gamma, grad_beta,
+                                      dims, man_acc, exp_acc, man_mul, exp_mul, man_div, exp_div, subnormals, saturate,
+                                      order=None):
+    """pybind_cuda.cpp:459 (``bias`` is accepted and unused, as in the reference)."""
+    for t, n in ((input, "input"), (grad_output, "grad_output"), (weight, "weight"), (mean, "mean"), (rstd, "rstd"),
+                 (grad_input, "grad_input"), (grad_gamma, "grad_gamma"), (grad_beta, "grad_beta")):
+        check_cuda_f32(t, n)
+    outer, ch, inner = partition_tensor(input.shape, list(dims))
+    with torch.cuda.device(input.device):
+        call("mpt_float_layernorm_backward", ptr(input), ptr(grad_output), ptr(weight), ptr(mean), ptr(rstd),
+             ptr(grad_input), ptr(grad_gamma), ptr(grad_beta), outer, ch, inner, man_acc, exp_acc, man_mul, exp_mul,
+             man_div, exp_div, int(subnormals), int(saturate), _order_code(order, "reduce_order"),
+             stream_ptr(input.device))
+
+
+def qsum_rows(a, man_bits, exp_bits, subnormals, saturate):
+    """New: sequential rounded sum over dim 0 of a 2-D tensor in one launch."""
+    check_cuda_f32(a, "a")
+    if a.dim() != 2:
+        raise RuntimeError("qsum_rows expects a 2-D tensor")
+    o = torch.empty(a.shape[1], device=a.device)
+    with torch.cuda.device(a.device):
+        call("mpt_qsum_rows", ptr(a), ptr(o), a.shape[0], a.shape[1], man_bits, exp_bits, int(subnormals), int(saturate),
+             stream_ptr(a.device))
+    return o

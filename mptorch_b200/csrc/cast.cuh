@@ -22,14 +22,14 @@ namespace mpt {
 
 MPT_HD uint32_t f2u(float x) {
 #ifdef __CUDA_ARCH__
-    return f2u(x);
+    return __float_as_uint(x);
 #else
     uint32_t u; memcpy(&u, &x, 4); return u;
 #endif
 }
 MPT_HD float u2f(uint32_t u) {
 #ifdef __CUDA_ARCH__
-    return u2f(u);
+    return __uint_as_float(u);
 #else
     float x; memcpy(&x, &u, 4); return x;
 #endif

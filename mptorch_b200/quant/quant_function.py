@@ -18,6 +18,9 @@ from ..number import Binary8, BlockFloatingPoint, FixedPoint, FloatingPoint, Num
 __all__ = [
     "fixed_point_quantize", "block_quantize", "float_quantize", "binary8_quantize", "superfp_quantize", "quantizer",
     "mp_mm", "mp_bmm", "float_mm", "float_bmm", "fxp_mm", "fxp_bmm", "superfp_mm", "superfp_bmm",
+    "mp_softmax_forward", "mp_softmax_backward", "float_softmax_forward", "float_softmax_lse_forward",
+    "float_softmax_backward", "mp_layernorm_forward", "mp_layernorm_backward", "float_layernorm_forward",
+    "float_layernorm_backward", "qsum_rows",
     "cublas_mm", "cublas_bmm", "cublas_acceleration",
     "set_accum_order", "set_reduce_order", "orders",
 ]
@@ -271,6 +274,140 @@ def mp_mm(a: torch.Tensor, b: torch.Tensor, formats, use_forward: bool = True) -
 def mp_bmm(a: torch.Tensor, b: torch.Tensor, formats, use_forward: bool = True) -> torch.Tensor:
     """reference: quant_function.py:1735-1814."""
     return _mp_matmul(float_bmm, a, b, formats, use_forward)
+
+
+# ------------------------------------------------------------------------------------------ softmax
+def float_softmax_forward(input: torch.Tensor, dim: int, man_exp: int = 23, exp_exp: int = 8, man_off: int = 23,
+                          exp_off: int = 8, man_acc: int = 23, exp_acc: int = 8,
+                          rounding: Literal["nearest", "stochastic"] = "nearest", subnormals: bool = True,
+                          saturate: bool = False) -> torch.Tensor:
+    """Softmax along ``dim``: y = Qexp(exp(Qoff(x - max))) / sum, the sum accumulated in (man_acc, exp_acc).
+    The final division is left unrounded.  reference: quant_function.py:546-575."""
+    assert rounding == "nearest", "Only nearest rounding softmax is implemented."
+    _require_cuda(input, "float_softmax_forward")
+    x = _f32c(input)
+    out = torch.empty_like(x)
+    _be.float_quantize_nearest_softmax_forward(x, out, dim, man_exp, exp_exp, man_off, exp_off, man_acc, exp_acc,
+                                               subnormals, saturate)
+    return out
+
+
+def float_softmax_lse_forward(input: torch.Tensor, dim: int, man_off: int = 23, exp_off: int = 8, man_lse: int = 23,
+                              exp_lse: int = 8, rounding: Literal["nearest", "stochastic"] = "nearest",
+                              subnormals: bool = True, saturate: bool = False) -> torch.Tensor:
+    """Division-free softmax through a rounded log-sum-exp recurrence.  reference: quant_function.py:578-603."""
+    assert rounding == "nearest", "Only nearest rounding softmax is implemented."
+    _require_cuda(input, "float_softmax_lse_forward")
+    x = _f32c(input)
+    out = torch.empty_like(x)
+    _be.float_quantize_nearest_softmax_lse_forward(x, out, dim, man_off, exp_off, man_lse, exp_lse, subnormals, saturate)
+    return out
+
+
+def float_softmax_backward(input: torch.Tensor, grad_output: torch.Tensor, dim: int, man_add: int = 23, exp_add: int = 8,
+                           man_mul: int = 23, exp_mul: int = 8, rounding: Literal["nearest", "stochastic"] = "nearest",
+                           subnormals: bool = True, saturate: bool = False) -> torch.Tensor:
+    """``input`` is the softmax output.  reference: quant_function.py:606-634."""
+    assert input.device == grad_output.device
+    assert rounding == "nearest", "Only nearest rounding softmax is implemented."
+    _require_cuda(input, "float_softmax_backward")
+    y = _f32c(input)
+    out = torch.empty_like(y)
+    _be.float_quantize_nearest_softmax_backward(y, _f32c(grad_output), out, dim, man_add, exp_add, man_mul, exp_mul,
+                                                subnormals, saturate)
+    return out
+
+
+def mp_softmax_forward(a: torch.Tensor, dim: int, formats) -> torch.Tensor:
+    """reference: quant_function.py:382-491."""
+    off_cfg = formats.fwd_off
+    if type(off_cfg) != FloatingPoint:
+        raise NotImplementedError("Unsupported number format.")
+    if not formats.use_lse:
+        assert formats.fwd_exp.subnormals == off_cfg.subnormals and formats.fwd_acc.subnormals == off_cfg.subnormals
+        assert formats.fwd_exp.saturate == off_cfg.saturate and formats.fwd_acc.saturate == off_cfg.saturate
+        return float_softmax_forward(a, dim, formats.fwd_exp.man, formats.fwd_exp.exp, off_cfg.man, off_cfg.exp,
+                                     formats.fwd_acc.man, formats.fwd_acc.exp, formats.fwd_rnd, off_cfg.subnormals,
+                                     off_cfg.saturate)
+    assert formats.fwd_lse.subnormals == off_cfg.subnormals
+    assert formats.fwd_lse.saturate == off_cfg.saturate
+    return float_softmax_lse_forward(a, dim, off_cfg.man, off_cfg.exp, formats.fwd_lse.man, formats.fwd_lse.exp,
+                                     formats.fwd_rnd, off_cfg.subnormals, off_cfg.saturate)
+
+
+def mp_softmax_backward(input: torch.Tensor, grad_output: torch.Tensor, dim: int, formats) -> torch.Tensor:
+    """reference: quant_function.py:494-543."""
+    add_cfg = formats.bwd_add
+    if type(add_cfg) != FloatingPoint:
+        raise NotImplementedError("Unsupported number format.")
+    assert formats.bwd_mul.subnormals == add_cfg.subnormals
+    assert formats.bwd_mul.saturate == add_cfg.saturate
+    return float_softmax_backward(input, grad_output, dim, add_cfg.man, add_cfg.exp, formats.bwd_mul.man,
+                                  formats.bwd_mul.exp, formats.bwd_rnd, add_cfg.subnormals, add_cfg.saturate)
+
+
+# ------------------------------------------------------------------------------------------ layernorm
+def float_layernorm_forward(inp: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float, dims: list[int],
+                            man_acc: int = 23, exp_acc: int = 8, man_mul: int = 23, exp_mul: int = 8, man_div: int = 23,
+                            exp_div: int = 8, man_sqrt: int = 23, exp_sqrt: int = 8,
+                            rounding: Literal["nearest"] = "nearest", subnormals: bool = True, saturate: bool = False):
+    """Layer normalisation over the trailing ``dims``; returns (output, mean, rstd) with mean and rstd shaped
+    like the leading dimensions.  reference: quant_function.py:1009-1058."""
+    assert rounding == "nearest", "Only nearest roudning layernorm is implemented."
+    _require_cuda(inp, "float_layernorm_forward")
+    x = _f32c(inp)
+    lead = list(x.shape[: x.dim() - len(dims)])
+    mean = torch.empty(lead, device=x.device)
+    rstd = torch.empty(lead, device=x.device)
+    out = torch.empty_like(x)
+    _be.float_quantize_layernorm_forward(x, _f32c(weight), _f32c(bias), out, mean, rstd, eps, dims, man_acc, exp_acc,
+                                         man_mul, exp_mul, man_div, exp_div, man_sqrt, exp_sqrt, subnormals, saturate)
+    return out, mean, rstd
+
+
+def float_layernorm_backward(inp: torch.Tensor, grad_output: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor,
+                             mean: torch.Tensor, rstd: torch.Tensor, dims: list[int], man_acc: int = 23, exp_acc: int = 8,
+                             man_mul: int = 23, exp_mul: int = 8, man_div: int = 23, exp_div: int = 8,
+                             rounding: Literal["nearest"] = "nearest", subnormals: bool = True, saturate: bool = False):
+    """Returns (grad_input, grad_weight, grad_bias).  reference: quant_function.py:1186-1234."""
+    assert rounding == "nearest", "Only nearest rounding layernorm is implemented."
+    assert inp.device == grad_output.device
+    _require_cuda(inp, "float_layernorm_backward")
+    x = _f32c(inp)
+    grad_input = torch.empty_like(x)
+    grad_weight = torch.empty_like(weight, dtype=torch.float32).contiguous()
+    grad_bias = torch.empty_like(bias, dtype=torch.float32).contiguous()
+    _be.float_quantize_layernorm_backward(x, _f32c(grad_output), _f32c(weight), _f32c(bias), _f32c(mean), _f32c(rstd),
+                                          grad_input, grad_weight, grad_bias, dims, man_acc, exp_acc, man_mul, exp_mul,
+                                          man_div, exp_div, subnormals, saturate)
+    return grad_input, grad_weight, grad_bias
+
+
+def mp_layernorm_forward(inp, weight, bias, eps, dims, formats):
+    """reference: quant_function.py:855-930."""
+    acc = formats.fwd_acc
+    if type(acc) != FloatingPoint:
+        raise NotImplementedError("Unsupported float type.")
+    return float_layernorm_forward(inp, weight, bias, eps, dims, acc.man, acc.exp, formats.fwd_mul.man, formats.fwd_mul.exp,
+                                   formats.fwd_div.man, formats.fwd_div.exp, formats.fwd_sqrt.man, formats.fwd_sqrt.exp,
+                                   formats.fwd_rnd, acc.subnormals, acc.saturate)
+
+
+def mp_layernorm_backward(inp, grad_output, weight, bias, mean, rstd, dims, formats):
+    """reference: quant_function.py:933-1006."""
+    acc = formats.bwd_acc
+    if type(acc) != FloatingPoint:
+        raise NotImplementedError("Unsupported float type.")
+    return float_layernorm_backward(inp, grad_output, weight, bias, mean, rstd, dims, acc.man, acc.exp,
+                                    formats.bwd_mul.man, formats.bwd_mul.exp, formats.bwd_div.man, formats.bwd_div.exp,
+                                    formats.bwd_rnd, acc.subnormals, acc.saturate)
+
+
+def qsum_rows(x: torch.Tensor, exp: int, man: int, subnormals: bool = True, saturate: bool = False) -> torch.Tensor:
+    """Sequential rounded sum over dim 0 of a 2-D tensor (one rounding per added row), in one kernel launch.
+    Equals the reference's ``qsum(x, 0, quant)`` with a nearest ``float_quantize`` (functional.py:736-748)."""
+    _require_cuda(x, "qsum_rows")
+    return _be.qsum_rows(_f32c(x), man, exp, subnormals, saturate)
 
 
 def _outside(name):
