@@ -319,7 +319,42 @@ __host__ __device__ inline int fast_rn_exp_limit(const FpFmt& f) {
 }
 
 __host__ __device__ inline bool fast_rn_supported(const FpFmt& f) {
-    return f.sub && f.man <= 21 && !(f.man >= 23 && f.exp >= 8);
+    // exp == 1 is degenerate (its largest binade lies below its smallest normal one): exact caster only
+    return f.sub && f.man <= 21 && f.exp >= 2;
 }
+
+
+// Round-to-nearest-even over the WHOLE fp32 input domain, built on FastRn: the elementwise
+// quantizer's inner step.  Finite inputs below the overflow threshold take the 4-instruction
+// FP-pipe rounding; overflow, infinities and NaN are patched in with two compares and two selects
+// (the FastRn result computed for them is simply discarded).  Only formats with an 8-bit exponent
+// keep a data-dependent branch to the exact caster, for magnitudes where 1.5 * 2^23 * quantum would
+// overflow fp32 and for zero and fp32-denormal inputs (which the reference rounds one bit coarser,
+// keeping the sign of a negative zero).
+struct FullRn {
+    FastRn fast;
+    FpFmt fmt;
+    uint32_t ovf_from;    // smallest |x| pattern whose rounding overflows the format
+    uint32_t ovf_value;   // what overflow yields (without sign): max finite, or infinity
+    uint32_t exact_from;  // 8-bit-exponent formats: smallest |x| pattern that must take the exact caster
+    __host__ __device__ static FullRn make(const FpFmt& f) {
+        FullRn r;
+        r.fast = FastRn::make(f);
+        r.fmt = f;
+        const uint32_t maxf = ((uint32_t)f.max_store << 23) | ((0x7FFFFFu >> (23 - f.man)) << (23 - f.man));
+        r.ovf_from = maxf + (1u << (22 - f.man));       // max finite plus half a quantum: a tie rounds up
+        r.ovf_value = f.sat ? maxf : 0x7F800000u;
+        r.exact_from = (f.exp == 8) ? ((uint32_t)(103 + f.man + 1 + 127) << 23) : 0xFFFFFFFFu;
+        return r;
+    }
+    MPT_HD float operator()(float x) const {
+        const uint32_t t = f2u(x);
+        const uint32_t a = t & 0x7FFFFFFFu;
+        if (fmt.exp == 8 && (a >= exact_from || a < 0x00800000u)) return cast_fp_nearest(x, fmt);
+        float y = fast(x);
+        const float over = (a >= 0x7F800000u) ? x : u2f((t & 0x80000000u) | ovf_value);
+        return (a >= ovf_from) ? over : y;
+    }
+};
 
 }  // namespace mpt

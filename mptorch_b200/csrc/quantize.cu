@@ -73,6 +73,13 @@ struct FpNearest {
     __device__ __forceinline__ float one(float x, int64_t) const { return cast_fp_nearest(x, f); }
     MPT_VEC_FROM_ONE
 };
+// Same result as FpNearest on every input (swept on the host against the exact caster), about a
+// quarter of the instructions: what keeps the kernel at the HBM roofline instead of the issue one.
+struct FpNearestFast {
+    FullRn r;
+    __device__ __forceinline__ float one(float x, int64_t) const { return r(x); }
+    MPT_VEC_FROM_ONE
+};
 struct FpTruncate {
     FpFmt f;
     __device__ __forceinline__ float one(float x, int64_t) const { return cast_fp_truncate(x, f); }
@@ -140,8 +147,9 @@ int mpt_float_quantize_nearest(const float* in, float* out, int64_t n, int man, 
                                int saturate, void* stream) {
     MPT_REQUIRE(n >= 0 && (n == 0 || (in && out)), "float_quantize_nearest: null pointer or negative size");
     MPT_REQUIRE(valid_format(man, exp), "float_quantize_nearest: unsupported format man=%d exp=%d", man, exp);
-    return launch_map(in, out, n, FpNearest{make_fmt(man, exp, subnormals, saturate)}, as_stream(stream),
-                      "float_quantize_nearest");
+    const FpFmt f = make_fmt(man, exp, subnormals, saturate);
+    if (fast_rn_supported(f)) return launch_map(in, out, n, FpNearestFast{FullRn::make(f)}, as_stream(stream), "float_quantize_nearest");
+    return launch_map(in, out, n, FpNearest{f}, as_stream(stream), "float_quantize_nearest");
 }
 
 int mpt_float_quantize_truncate(const float* in, float* out, int64_t n, int man, int exp, int subnormals,

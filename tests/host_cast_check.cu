@@ -59,3 +59,28 @@ HC_API int64_t hc_sweep_fast_rn(int man, int exp, uint64_t first, uint64_t count
     if (first_bad) *first_bad = firstbad;
     return bad;
 }
+
+// Same sweep for the whole-domain variant used by the elementwise quantizer: every pattern is
+// compared, no precondition.
+HC_API int64_t hc_sweep_full_rn(int man, int exp, int sat, uint64_t first, uint64_t count, uint64_t stride,
+                                uint32_t* first_bad) {
+    const FpFmt f = make_fmt(man, exp, 1, sat);
+    const FullRn full = FullRn::make(f);
+    int64_t bad = 0;
+    uint32_t firstbad = 0;
+#pragma omp parallel for reduction(+ : bad) schedule(static)
+    for (int64_t i = 0; i < (int64_t)count; ++i) {
+        const uint32_t t = (uint32_t)(first + (uint64_t)i * stride);
+        const float x = u2f(t);
+        const uint32_t want = f2u(cast_fp_nearest(x, f));
+        const uint32_t got = f2u(full(x));
+        const bool both_nan = (want & 0x7FFFFFFFu) > 0x7F800000u && (got & 0x7FFFFFFFu) > 0x7F800000u;
+        if (want != got && !both_nan) {
+            ++bad;
+#pragma omp critical
+            if (firstbad == 0) firstbad = t;
+        }
+    }
+    if (first_bad) *first_bad = firstbad;
+    return bad;
+}

@@ -106,3 +106,42 @@ def test_full_size_headline_vs_reference(ref_cuda, be):
     got = torch.empty(S, S, device="cuda")
     be.float_quantize_nearest_mm(a, b, got, S, S, S, 2, 5, 2, 5, True, False, False, order="cuda")
     assert bits_equal(got, want)
+
+
+def test_softmax_and_layernorm_cuda_order(ref_cuda):
+    """Row reductions in the CUDA association, expf/logf from the same CUDA math library: bit for bit."""
+    import mptorch_b200.quant as q
+
+    x = torch.randn(6, 40, 1024, device="cuda") * 3
+    g = torch.randn_like(x)
+    for (e, m) in [(5, 10), (8, 7), (8, 23), (4, 3)]:
+        for dim in (-1, 1):
+            want = torch.zeros_like(x)
+            ref_cuda.float_quantize_nearest_softmax_forward(x, want, dim, m, e, m, e, m, e, True, False)
+            got = q.float_softmax_forward(x, dim, m, e, m, e, m, e)
+            assert bits_equal(got, want), ("softmax", e, m, dim)
+            want2 = torch.zeros_like(x)
+            ref_cuda.float_quantize_nearest_softmax_lse_forward(x, want2, dim, m, e, m, e, True, False)
+            got2 = q.float_softmax_lse_forward(x, dim, m, e, m, e)
+            assert bits_equal(got2, want2), ("softmax lse", e, m, dim)
+            want3 = torch.zeros_like(x)
+            ref_cuda.float_quantize_nearest_softmax_backward(want, g, want3, dim, m, e, m, e, True, False)
+            got3 = q.float_softmax_backward(want, g, dim, m, e, m, e)
+            assert bits_equal(got3, want3), ("softmax bwd", e, m, dim)
+    xl = torch.randn(4, 256, 768, device="cuda") * 2 + 0.3
+    gl = torch.randn_like(xl)
+    w = torch.randn(768, device="cuda")
+    b = torch.randn(768, device="cuda")
+    for (e, m) in [(5, 10), (8, 7), (8, 23)]:
+        y = torch.zeros_like(xl)
+        mean = torch.zeros(4, 256, device="cuda")
+        rstd = torch.zeros(4, 256, device="cuda")
+        ref_cuda.float_quantize_layernorm_forward(xl, w, b, y, mean, rstd, 1e-5, [-1], m, e, m, e, m, e, m, e, True, False)
+        gy, gm, gr = q.float_layernorm_forward(xl, w, b, 1e-5, [-1], m, e, m, e, m, e, m, e)
+        assert bits_equal(gy, y) and bits_equal(gm, mean) and bits_equal(gr, rstd), ("layernorm fwd", e, m)
+        gi = torch.zeros_like(xl)
+        gg = torch.zeros(768, device="cuda")
+        gb = torch.zeros(768, device="cuda")
+        ref_cuda.float_quantize_layernorm_backward(xl, gl, w, b, mean, rstd, gi, gg, gb, [-1], m, e, m, e, m, e, True, False)
+        ogi, ogg, ogb = q.float_layernorm_backward(xl, gl, w, b, mean, rstd, [-1], m, e, m, e, m, e)
+        assert bits_equal(ogi, gi) and bits_equal(ogg, gg) and bits_equal(ogb, gb), ("layernorm bwd", e, m)
