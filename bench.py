@@ -175,6 +175,7 @@ def main() -> int:
     ap.add_argument("--size", type=int, default=SIZE, help="M=N=K (the headline is 8192)")
     ap.add_argument("--order", default="cuda", choices=["cuda", "seq"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--quant-log2n", type=int, default=28, help="log2 of the quantizer leg's element count")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -281,7 +282,7 @@ def main() -> int:
     quant = None
     if rank == 0:
         del ah, bh
-        n = 1 << 28
+        n = 1 << args.quant_log2n
         x = torch.randn(n, device=dev, generator=g)
         for _ in range(3):
             q = be.float_quantize_nearest(x, 3, 4, True, True)
@@ -326,7 +327,7 @@ def main() -> int:
                                  % (sms, clk, I_MAC)},
             "roofline_quantize": {"bound": "hbm", "achieved": quant["gbs"], "peak": hbm_peak, "unit": "GB/s",
                                   "frac": quant["gbs"] / hbm_peak, "traffic": None, "peak_source": peak_src,
-                                  "kernel": "float_quantize_nearest e4m3, 2^28 elements, 8 B/element"},
+                                  "kernel": "float_quantize_nearest e4m3, 2^%d elements, 8 B/element" % args.quant_log2n},
         }
         if world == 1 and not args.no_cpu_baseline:
             try:
