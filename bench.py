@@ -32,7 +32,7 @@ FMT = dict(man_add=2, exp_add=5, man_mul=2, exp_mul=5, subnormals=True, saturate
 # Issued thread-instructions per MAC of the GEMM kernel's fast path, measured with ncu
 # (smsp__thread_inst_executed.sum / MACs; see profiles/).  The issue-rate roofline is
 # SMs x 128 lanes x SM clock / I_MAC.
-I_MAC = 10.6
+I_MAC = 11.22
 METRIC = "float_mm GMAC/s (8192^3, e5m2 RN)"
 
 

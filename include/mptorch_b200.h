@@ -98,9 +98,12 @@ MPT_API int mpt_superfp_quantize_nearest(const float *in, float *out, int64_t n,
 
 /* ---- per-MAC rounded GEMM ------------------------------------------------------------------ */
 
-/* Bytes of scratch the GEMM entry points want in `workspace` (device memory, 16-byte aligned).
- * With workspace == NULL (or too small) they still run, on the slower exact-cast path only. */
-MPT_API size_t mpt_mm_workspace_bytes(void);
+/* Bytes of scratch the GEMM entry points want in `workspace` (device memory, 16-byte aligned) for a
+ * given batch count: 16 bytes of operand statistics per batch entry, rounded up to 256.  The GEMM
+ * rewrites it on every call; it need not be initialised and can be reused by the next call on the
+ * same stream.  With workspace == NULL (or too small) the GEMM still runs, on the slower exact-cast
+ * path only. */
+MPT_API size_t mpt_mm_workspace_bytes(int64_t batch);
 
 /* replaces float_quantize_nearest_mm and _bmm (pybind_cuda.cpp:123,140 -> quant.cu:335,362 ->
  * fp_kernel.cu:174-245 -> mm_kernel.h:19-132) and their CPU twins (quant_cpu/mm_kernel.h:9-34).
@@ -178,6 +181,25 @@ MPT_API int mpt_float_layernorm_backward(const float *in, const float *grad_out,
  * (mptorch/quant/functional.py:736-748, used for the bias gradient at :160-168). */
 MPT_API int mpt_qsum_rows(const float *in, float *out, int64_t rows, int64_t cols, int man, int exp,
                           int subnormals, int saturate, void *stream);
+
+/* ---- block-scaled quantizers (NEW: the reference has no MX / NVFP4 kernels) ----------------------
+ * Blocks run along the last, contiguous dimension of a [rows, cols] matrix; `out` receives the
+ * dequantized fp32 values. */
+enum { MPT_ELEM_E4M3 = 0, MPT_ELEM_E2M1 = 1 };   /* OCP element formats: max 448 and 6 */
+
+/* OCP MX: one E8M0 scale 2^(floor(log2 amax) - emax_elem) per `block` elements (32 for MXFP8 / MXFP4),
+ * elements rounded to nearest even in `elem_format` with saturation.  `scales` (optional) receives the
+ * E8M0 codes, [rows, ceil(cols / block)], 0xFF for a block holding NaN or infinity. */
+MPT_API int mpt_mx_quantize(const float *in, float *out, uint8_t *scales, int64_t rows, int64_t cols, int block,
+                            int elem_format, void *stream);
+
+/* NVFP4: E2M1 elements in blocks of 16, one E4M3 scale per block (optional output `block_scales`,
+ * [rows, ceil(cols / 16)], as fp32 values) and one fp32 scale per tensor.  global_scale > 0 is used as
+ * given; otherwise it is computed as amax(tensor) / (448 * 6), which needs 4 bytes of device
+ * `workspace` and one extra read of the input.  `global_scale_out` (optional, device) receives the
+ * scale that was used. */
+MPT_API int mpt_nvfp4_quantize(const float *in, float *out, float *block_scales, int64_t rows, int64_t cols,
+                               float global_scale, void *workspace, float *global_scale_out, void *stream);
 
 #ifdef __cplusplus
 }

@@ -34,6 +34,7 @@ def lib() -> C.CDLL:
         L.mpt_last_error.restype = C.c_char_p
         L.mpt_version.restype = i32
         L.mpt_mm_workspace_bytes.restype = sz
+        L.mpt_mm_workspace_bytes.argtypes = [i64]
         sig = {
             "mpt_float_quantize_nearest": [p, p, i64, i32, i32, i32, i32, p],
             "mpt_float_quantize_truncate": [p, p, i64, i32, i32, i32, i32, p],
@@ -50,6 +51,8 @@ def lib() -> C.CDLL:
             "mpt_float_layernorm_forward": [p] * 6 + [C.c_float, i64, i32, i64] + [i32] * 11 + [p],
             "mpt_float_layernorm_backward": [p] * 8 + [i64, i32, i64] + [i32] * 9 + [p],
             "mpt_qsum_rows": [p, p, i64, i64, i32, i32, i32, i32, p],
+            "mpt_mx_quantize": [p, p, p, i64, i64, i32, i32, p],
+            "mpt_nvfp4_quantize": [p, p, p, i64, i64, C.c_float, p, p, p],
         }
         for name, args in sig.items():
             fn = getattr(L, name, None)
@@ -89,12 +92,13 @@ def stream_ptr(device: torch.device):
 _workspaces: dict[tuple[int, int], torch.Tensor] = {}
 
 
-def mm_workspace(device: torch.device) -> torch.Tensor:
-    """A small per-(device, stream) scratch buffer for the GEMM's operand statistics."""
+def mm_workspace(device: torch.device, batch: int = 1) -> torch.Tensor:
+    """A small per-(device, stream) scratch buffer for the GEMM's operand statistics (grown on demand)."""
     key = (device.index if device.index is not None else torch.cuda.current_device(),
            torch.cuda.current_stream(device).cuda_stream)
+    need = int(lib().mpt_mm_workspace_bytes(max(int(batch), 1)))
     ws = _workspaces.get(key)
-    if ws is None:
-        ws = torch.empty(int(lib().mpt_mm_workspace_bytes()), dtype=torch.uint8, device=device)
+    if ws is None or ws.numel() < need:
+        ws = torch.empty(need, dtype=torch.uint8, device=device)
         _workspaces[key] = ws
     return ws

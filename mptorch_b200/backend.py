@@ -170,7 +170,7 @@ def _batch_of(a) -> int:
 def _mm_nearest(a, b, c, batch, M, N, K, man_add, exp_add, man_mul, exp_mul, subnormals, saturate, compensated, order):
     _mm_checks(a, b, c)
     with torch.cuda.device(a.device):
-        ws = _cabi.mm_workspace(a.device)
+        ws = _cabi.mm_workspace(a.device, batch)
         call("mpt_float_mm_nearest", ptr(a), ptr(b), ptr(c), batch, M, N, K, man_add, exp_add, man_mul, exp_mul,
              int(subnormals), int(saturate), int(compensated), _order_code(order, "accum_order"), ptr(ws), ws.numel(),
              stream_ptr(a.device))
@@ -179,7 +179,7 @@ def _mm_nearest(a, b, c, batch, M, N, K, man_add, exp_add, man_mul, exp_mul, sub
 def _mm_nearest_fma(a, b, c, batch, M, N, K, man_fma, exp_fma, subnormals, saturate, compensated, order):
     _mm_checks(a, b, c)
     with torch.cuda.device(a.device):
-        ws = _cabi.mm_workspace(a.device)
+        ws = _cabi.mm_workspace(a.device, batch)
         call("mpt_float_mm_nearest_fma", ptr(a), ptr(b), ptr(c), batch, M, N, K, man_fma, exp_fma, int(subnormals),
              int(saturate), int(compensated), _order_code(order, "accum_order"), ptr(ws), ws.numel(),
              stream_ptr(a.device))
@@ -334,3 +334,38 @@ def qsum_rows(a, man_bits, exp_bits, subnormals, saturate):
         call("mpt_qsum_rows", ptr(a), ptr(o), a.shape[0], a.shape[1], man_bits, exp_bits, int(subnormals), int(saturate),
              stream_ptr(a.device))
     return o
+
+
+# ---------------------------------------------------------------------------------- block-scaled quantizers (new)
+_ELEM = {"e4m3": 0, "e2m1": 1}
+
+
+def mx_quantize(a, elem_format="e4m3", block=32, return_scales=False):
+    """OCP MX block quantization along the last dimension; returns the dequantized tensor (and the E8M0 codes)."""
+    check_cuda_f32(a, "a")
+    if elem_format not in _ELEM:
+        raise ValueError("elem_format must be 'e4m3' or 'e2m1'")
+    cols = a.shape[-1] if a.dim() else 1
+    rows = a.numel() // cols if cols else 0
+    o = torch.empty_like(a)
+    sc = torch.empty(tuple(a.shape[:-1]) + ((cols + block - 1) // block,), dtype=torch.uint8, device=a.device) if return_scales else None
+    with torch.cuda.device(a.device):
+        call("mpt_mx_quantize", ptr(a), ptr(o), ptr(sc), rows, cols, block, _ELEM[elem_format], stream_ptr(a.device))
+    return (o, sc) if return_scales else o
+
+
+def nvfp4_quantize(a, global_scale=None, return_scales=False):
+    """NVFP4 quantization along the last dimension; returns the dequantized tensor (and block scales, tensor scale)."""
+    check_cuda_f32(a, "a")
+    cols = a.shape[-1] if a.dim() else 1
+    rows = a.numel() // cols if cols else 0
+    o = torch.empty_like(a)
+    sc = torch.empty(tuple(a.shape[:-1]) + ((cols + 15) // 16,), device=a.device) if return_scales else None
+    gs_out = torch.empty(1, device=a.device) if return_scales else None
+    ws = None
+    gs = float(global_scale) if global_scale is not None else 0.0
+    if not gs > 0.0:
+        ws = torch.empty(1, dtype=torch.int32, device=a.device)
+    with torch.cuda.device(a.device):
+        call("mpt_nvfp4_quantize", ptr(a), ptr(o), ptr(sc), rows, cols, gs, ptr(ws), ptr(gs_out), stream_ptr(a.device))
+    return (o, sc, gs_out) if return_scales else o

@@ -9,8 +9,8 @@
 //   * fast path, 10 instructions per MAC (FMUL, 4 for the product rounding, FADD, 4 for the sum
 //     rounding), see FastRn in cast.cuh.  It is exact whenever no intermediate value can leave
 //     the finite range of its format.  That is established from the magnitude statistics of A
-//     and B (a tiny pre-pass over both matrices writes them to the workspace) plus a per-thread
-//     check of the running accumulators at every fold;
+//     and B (a tiny pre-pass writes one record per batch entry to the workspace) plus a
+//     per-thread check of the running accumulators at every fold;
 //   * exact path: the complete reference caster (every corner case), taken per thread and per
 //     8-step group whenever the fast path's precondition cannot be shown.
 //
@@ -58,15 +58,20 @@ struct MmParams {
     FastRn radd, rmul;
     int rbits_add, rbits_mul;
     uint32_t seed_lo, seed_hi;
-    const MmStats* stats;        // NULL: exact path only
+    const MmStats* stats;        // one record per batch entry; NULL: exact path only
     float growth8;               // upper bound of (1 + 2^-(man_add+1))^8
 };
 
-__global__ void stats_init_kernel(MmStats* s) {
-    if (threadIdx.x == 0) { s->max_a = 0u; s->max_b = 0u; s->minnz_a = 0xFFFFFFFFu; s->minnz_b = 0xFFFFFFFFu; }
+__global__ void stats_init_kernel(MmStats* s, int64_t batch) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < batch) { s[i].max_a = 0u; s[i].max_b = 0u; s[i].minnz_a = 0xFFFFFFFFu; s[i].minnz_b = 0xFFFFFFFFu; }
 }
 
-__global__ void __launch_bounds__(256) stats_kernel(const float* __restrict__ x, int64_t n, uint32_t* mx, uint32_t* mn) {
+// blockIdx.y walks the batch; `which` selects the A (0) or B (1) fields of that entry's record.
+__global__ void __launch_bounds__(256) stats_kernel(const float* __restrict__ base, int64_t n, MmStats* stats, int which) {
+    const float* x = base + (int64_t)blockIdx.y * n;
+    uint32_t* mx = which ? &stats[blockIdx.y].max_b : &stats[blockIdx.y].max_a;
+    uint32_t* mn = which ? &stats[blockIdx.y].minnz_b : &stats[blockIdx.y].minnz_a;
     uint32_t lmax = 0u, lmin = 0xFFFFFFFFu;
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
@@ -216,11 +221,11 @@ __device__ __forceinline__ float absmax_of(const float (&v)[TM][TN]) {
 struct FastPlan { bool ok; float acc_limit; };
 
 template <int ALGO, bool FMA>
-__device__ __forceinline__ FastPlan make_plan(const MmParams& p) {
+__device__ __forceinline__ FastPlan make_plan(const MmParams& p, int64_t batch) {
     FastPlan plan{false, 0.0f};
     if (p.stats == nullptr) return plan;
     if (!fast_rn_supported(p.fadd) || (!FMA && !fast_rn_supported(p.fmul))) return plan;
-    const MmStats s = *p.stats;
+    const MmStats s = p.stats[batch];
     if (s.max_a >= 0x7F800000u || s.max_b >= 0x7F800000u) return plan;
     // |a| < 2^(ea+1), |b| < 2^(eb+1)  =>  |a*b| < 2^pe
     const int pe = (int)(s.max_a >> 23) + (int)(s.max_b >> 23) - 254 + 2;
@@ -271,7 +276,7 @@ __global__ void __launch_bounds__(THREADS, 2) mm_kernel(const MmParams p) {
     const int ksteps = (ALGO == ALGO_SEQ) ? p.K : p.K + 8 - p.K % 8;
     const int ntiles = (ksteps + BK - 1) / BK;
 
-    const FastPlan plan = (ALGO == ALGO_SEQ || ALGO == ALGO_TILE8) ? make_plan<ALGO, FMA>(p) : FastPlan{false, 0.0f};
+    const FastPlan plan = (ALGO == ALGO_SEQ || ALGO == ALGO_TILE8) ? make_plan<ALGO, FMA>(p, batch) : FastPlan{false, 0.0f};
 
     float acc[TM][TN];    // running sum (inner sum for ALGO_TILE8)
     float aux[TM][TN];    // outer sum (ALGO_TILE8) or compensation term (ALGO_KAHAN)
@@ -425,15 +430,20 @@ int run_mm(const float* a, const float* b, float* c, int64_t batch, int M, int N
 
     const bool fast_candidate = (algo == ALGO_SEQ || algo == ALGO_TILE8) && fast_rn_supported(fadd) &&
                                 (fma || fast_rn_supported(fmul)) && workspace != nullptr &&
-                                workspace_bytes >= sizeof(MmStats) && (reinterpret_cast<uintptr_t>(workspace) & 15u) == 0 && K > 0;
+                                workspace_bytes >= sizeof(MmStats) * (size_t)batch &&
+                                (reinterpret_cast<uintptr_t>(workspace) & 15u) == 0 && K > 0;
     if (fast_candidate) {
         MmStats* s = static_cast<MmStats*>(workspace);
-        stats_init_kernel<<<1, 32, 0, st>>>(s);
-        const int64_t na = batch * (int64_t)M * K, nb = batch * (int64_t)K * N;
+        stats_init_kernel<<<(unsigned)((batch + 255) / 256), 256, 0, st>>>(s, batch);
+        const int64_t na = (int64_t)M * K, nb = (int64_t)K * N;
         const int sms = sm_count();
-        auto blocks = [&](int64_t n) { int64_t g = (n + 255) / 256; const int64_t cap = (int64_t)sms * 8; return (unsigned)(g > cap ? cap : (g < 1 ? 1 : g)); };
-        stats_kernel<<<blocks(na), 256, 0, st>>>(a, na, &s->max_a, &s->minnz_a);
-        stats_kernel<<<blocks(nb), 256, 0, st>>>(b, nb, &s->max_b, &s->minnz_b);
+        auto grid = [&](int64_t n) {
+            int64_t g = (n + 255) / 256;
+            const int64_t cap = ((int64_t)sms * 8 + batch - 1) / batch;
+            return dim3((unsigned)(g > cap ? cap : (g < 1 ? 1 : g)), (unsigned)batch);
+        };
+        stats_kernel<<<grid(na), 256, 0, st>>>(a, na, s, 0);
+        stats_kernel<<<grid(nb), 256, 0, st>>>(b, nb, s, 1);
         int rc = check_launch("float_mm statistics");
         if (rc) return rc;
         p.stats = s;
@@ -467,7 +477,10 @@ using namespace mpt;
 
 extern "C" {
 
-size_t mpt_mm_workspace_bytes(void) { return 256; }
+size_t mpt_mm_workspace_bytes(int64_t batch) {
+    const size_t need = sizeof(MmStats) * (size_t)(batch < 1 ? 1 : batch);
+    return (need + 255) & ~(size_t)255;
+}
 
 int mpt_float_mm_nearest(const float* a, const float* b, float* c, int64_t batch, int M, int N, int K, int man_add,
                          int exp_add, int man_mul, int exp_mul, int subnormals, int saturate, int compensated,

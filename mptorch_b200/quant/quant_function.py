@@ -17,6 +17,7 @@ from ..number import Binary8, BlockFloatingPoint, FixedPoint, FloatingPoint, Num
 
 __all__ = [
     "fixed_point_quantize", "block_quantize", "float_quantize", "binary8_quantize", "superfp_quantize", "quantizer",
+    "mx_quantize", "nvfp4_quantize",
     "mp_mm", "mp_bmm", "float_mm", "float_bmm", "fxp_mm", "fxp_bmm", "superfp_mm", "superfp_bmm",
     "mp_softmax_forward", "mp_softmax_backward", "float_softmax_forward", "float_softmax_lse_forward",
     "float_softmax_backward", "mp_layernorm_forward", "mp_layernorm_backward", "float_layernorm_forward",
@@ -109,6 +110,27 @@ def superfp_quantize(x: torch.Tensor, exp: int, man: int, binades, rounding: Lit
         raise NotImplementedError("SR SuperNormalFloat not yet implemented")
     bl, bu = normalize_binades(binades)
     return _be.superfp_quantize_nearest(_f32c(x), man, exp, bl, bu, saturate)
+
+
+def mx_quantize(x: torch.Tensor, elem_format: Literal["e4m3", "e2m1"] = "e4m3", block: int = 32,
+                return_scales: bool = False):
+    """OCP Microscaling block quantization along the last dimension (new; the reference has none).
+
+    Every ``block`` consecutive elements share one power-of-two scale 2^(floor(log2 amax) - emax) stored as
+    E8M0; elements are rounded to nearest even into OCP E4M3 (MXFP8, max 448) or E2M1 (MXFP4, max 6) with
+    saturation.  Returns the dequantized fp32 tensor, plus the uint8 scale codes with ``return_scales``.
+    Note these OCP element formats differ from ``float_quantize(exp=4, man=3)``, which reserves the top
+    exponent and tops out at 240."""
+    _require_cuda(x, "mx_quantize")
+    return _be.mx_quantize(_f32c(x), elem_format, block, return_scales)
+
+
+def nvfp4_quantize(x: torch.Tensor, global_scale: float | None = None, return_scales: bool = False):
+    """NVFP4 quantization along the last dimension (new): E2M1 elements in blocks of 16, an E4M3 scale per
+    block and one fp32 scale per tensor (``amax / (448 * 6)`` unless given).  Returns the dequantized tensor,
+    plus (block scales, tensor scale) with ``return_scales``."""
+    _require_cuda(x, "nvfp4_quantize")
+    return _be.nvfp4_quantize(_f32c(x), global_scale, return_scales)
 
 
 def fixed_point_quantize(*args, **kwargs):

@@ -145,6 +145,22 @@ def test_batched(be, oracle):
             assert same_bits(got, want), mismatch_report(got, want)
 
 
+def test_batched_mixed_ranges(be, oracle):
+    """The fast-path decision is made per batch entry: one entry with huge / special values next to ordinary ones."""
+    rng = np.random.default_rng(61)
+    a = rng.standard_normal((4, 40, 48)).astype(np.float32)
+    b = rng.standard_normal((4, 48, 36)).astype(np.float32)
+    a[1] *= 500.0
+    b[1] *= 500.0
+    a[2, 3, 4] = np.inf
+    b[3, 0, 0] = np.nan
+    for order in ("cuda", "seq"):
+        for fma in (False, True):
+            got = gpu_mm(be, a, b, (5, 2), (5, 2), fma=fma, order=order)
+            want = cpu_mm(oracle, a, b, (5, 2), (5, 2), fma=fma, order=order)
+            assert same_bits(got, want), f"{order} fma={fma}: " + mismatch_report(got, want)
+
+
 def test_attention_shapes(be, oracle):
     """BASELINE config 5 attention GEMM shapes at reduced batch: [B,1024,64]x[B,64,1024] rows sampled."""
     rng = np.random.default_rng(8)
