@@ -116,6 +116,22 @@ MPT_API int mpt_float_mm_nearest(const float *a, const float *b, float *c, int64
                                  int subnormals, int saturate, int compensated, int order,
                                  void *workspace, size_t workspace_bytes, void *stream);
 
+/* No counterpart in the reference.  Same computation and same results as mpt_float_mm_nearest, for
+ * callers that cannot allocate device memory and therefore have no workspace to pass (an application
+ * whose own pool owns the whole GPU, a plugin interface that hands over only inputs and outputs, a loop
+ * where cudaMalloc's implicit synchronisation is not allowed).  The operand statistics are kept in a
+ * 64 KiB array built into the library (held by every GPU that loads it, until the process exits), which
+ * bounds the batch count: batch > 4096 is rejected with MPT_ERR_INVALID_ARGUMENT.  The call allocates
+ * and frees nothing.
+ *   - The first call on each device looks up the array's device address (with that device current);
+ *     make that first call outside any stream capture.
+ *   - All calls share the array and each one rewrites the part it uses, so calls that may overlap on
+ *     the GPU (different streams, or different host threads without ordering) race; serialise them or
+ *     use mpt_float_mm_nearest with one workspace per stream. */
+MPT_API int mpt_float_mm_nearest_static(const float *a, const float *b, float *c, int64_t batch, int M, int N, int K,
+                                        int man_add, int exp_add, int man_mul, int exp_mul,
+                                        int subnormals, int saturate, int compensated, int order, void *stream);
+
 /* replaces float_quantize_nearest_mm_fma and _bmm_fma (pybind_cuda.cpp:157,173 -> quant.cu ->
  * fp_kernel.cu:247-307 -> mm_kernel.h:134-246): acc = Q(fmaf(a, b, acc)). */
 MPT_API int mpt_float_mm_nearest_fma(const float *a, const float *b, float *c, int64_t batch, int M, int N, int K,

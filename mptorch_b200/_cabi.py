@@ -43,6 +43,7 @@ def lib() -> C.CDLL:
             "mpt_binary8_quantize": [p, p, p, i64, i32, i32, i32, i32, i32, i32, p],
             "mpt_superfp_quantize_nearest": [p, p, i64, i32, i32, i32, i32, i32, p],
             "mpt_float_mm_nearest": [p, p, p, i64, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, p, sz, p],
+            "mpt_float_mm_nearest_static": [p, p, p, i64, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, p],
             "mpt_float_mm_nearest_fma": [p, p, p, i64, i32, i32, i32, i32, i32, i32, i32, i32, i32, p, sz, p],
             "mpt_float_mm_stochastic": [p, p, p, i64, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, u64, p],
             "mpt_float_softmax_forward": [p, p, i64, i32, i64] + [i32] * 9 + [p],

@@ -26,6 +26,8 @@
 // Kahan-compensated and stochastic variants follow quant_cuda/mm_kernel.h:457-520 and :248-295.
 #include <cuda_pipeline.h>
 
+#include <mutex>
+
 #include "cast.cuh"
 #include "common.cuh"
 
@@ -470,6 +472,39 @@ int check_mm_args(const char* who, const float* a, const float* b, float* c, int
     return MPT_OK;
 }
 
+// ---- scratch for the entry point that allocates nothing -------------------------------------------
+// Some callers cannot hand the GEMM a workspace because they cannot allocate device memory at all: a host
+// application that has already given every byte of the GPU to its own pool, a plugin interface that
+// passes nothing but input and output buffers, or a latency-critical loop in which cudaMalloc (and the
+// device-wide synchronisation it implies) is forbidden.  For them the operand statistics live in this
+// fixed array instead.  It is part of the library image: every GPU that loads the library holds these
+// 64 KiB until the process exits.
+constexpr int kStaticScratchMaxBatch = 4096;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchMaxBatch * sizeof(MmStats)];
+
+// In host code `g_static_scratch` is only a handle for the symbol, not a device address; the address on
+// the current device comes from cudaGetSymbolAddress, asked once per device and cached.
+int static_scratch_address(void** out) {
+    static std::mutex mu;
+    static void* cached[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) { set_error("float_mm_nearest_static: cudaGetDevice: %s", cudaGetErrorString(e)); return MPT_ERR_CUDA; }
+    if (dev < 0 || dev >= 64) { set_error("float_mm_nearest_static: device ordinal %d not supported", dev); return MPT_ERR_INVALID_ARGUMENT; }
+    std::lock_guard<std::mutex> lock(mu);
+    if (cached[dev] == nullptr) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess || p == nullptr) {
+            set_error("float_mm_nearest_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+            return MPT_ERR_CUDA;
+        }
+        cached[dev] = p;
+    }
+    *out = cached[dev];
+    return MPT_OK;
+}
+
 }  // namespace
 }  // namespace mpt
 
@@ -493,6 +528,27 @@ int mpt_float_mm_nearest(const float* a, const float* b, float* c, int64_t batch
     return run_mm(a, b, c, batch, M, N, K, make_fmt(man_add, exp_add, subnormals, saturate),
                   make_fmt(man_mul, exp_mul, subnormals, saturate), 0, 0, false, algo, 0, workspace, workspace_bytes,
                   as_stream(stream));
+}
+
+int mpt_float_mm_nearest_static(const float* a, const float* b, float* c, int64_t batch, int M, int N, int K, int man_add,
+                                int exp_add, int man_mul, int exp_mul, int subnormals, int saturate, int compensated,
+                                int order, void* stream) {
+    int rc = check_mm_args("float_mm_nearest_static", a, b, c, batch, M, N, K);
+    if (rc) return rc;
+    MPT_REQUIRE(valid_format(man_add, exp_add) && valid_format(man_mul, exp_mul), "float_mm_nearest_static: unsupported format");
+    MPT_REQUIRE(order == MPT_ORDER_SEQ || order == MPT_ORDER_CUDA, "float_mm_nearest_static: unknown order %d", order);
+    MPT_REQUIRE(batch <= kStaticScratchMaxBatch,
+                "float_mm_nearest_static: batch %lld exceeds the %d entries of the built-in scratch; use "
+                "mpt_float_mm_nearest with a caller-provided workspace", (long long)batch, kStaticScratchMaxBatch);
+    void* scratch = nullptr;
+    rc = static_scratch_address(&scratch);
+    if (rc) return rc;
+    const int algo = compensated ? ALGO_KAHAN : (order == MPT_ORDER_SEQ ? ALGO_SEQ : ALGO_TILE8);
+    // run_mm re-initialises the statistics records it uses before reading them, so whatever the previous
+    // call left in the array is never seen
+    return run_mm(a, b, c, batch, M, N, K, make_fmt(man_add, exp_add, subnormals, saturate),
+                  make_fmt(man_mul, exp_mul, subnormals, saturate), 0, 0, false, algo, 0, scratch,
+                  sizeof(MmStats) * (size_t)kStaticScratchMaxBatch, as_stream(stream));
 }
 
 int mpt_float_mm_nearest_fma(const float* a, const float* b, float* c, int64_t batch, int M, int N, int K, int man_fma,
