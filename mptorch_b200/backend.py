@@ -172,7 +172,7 @@ def _mm_nearest(a, b, c, batch, M, N, K, man_add, exp_add, man_mul, exp_mul, sub
     with torch.cuda.device(a.device):
         ws = _cabi.mm_workspace(a.device, batch)
         call("mpt_float_mm_nearest", ptr(a), ptr(b), ptr(c), batch, M, N, K, man_add, exp_add, man_mul, exp_mul,
-             int(subnormals), int(saturate), int(compensated), _order_code(order, "accum_order"), ptr(ws), ws.numel(),
+             int(subnormals), int(saturate), int(bool(compensated)), _order_code(order, "accum_order"), ptr(ws), ws.numel(),
              stream_ptr(a.device))
 
 
@@ -181,7 +181,7 @@ def _mm_nearest_fma(a, b, c, batch, M, N, K, man_fma, exp_fma, subnormals, satur
     with torch.cuda.device(a.device):
         ws = _cabi.mm_workspace(a.device, batch)
         call("mpt_float_mm_nearest_fma", ptr(a), ptr(b), ptr(c), batch, M, N, K, man_fma, exp_fma, int(subnormals),
-             int(saturate), int(compensated), _order_code(order, "accum_order"), ptr(ws), ws.numel(),
+             int(saturate), int(bool(compensated)), _order_code(order, "accum_order"), ptr(ws), ws.numel(),
              stream_ptr(a.device))
 
 

@@ -1,0 +1,325 @@
+"""Autograd functions that route linear algebra, softmax and layer normalisation through the simulated
+arithmetic kernels.  Semantics follow the reference's ``mptorch/quant/functional.py`` (lines cited per class),
+including the order in which signals are scaled, quantized and un-scaled.
+"""
+from __future__ import annotations
+
+from typing import Callable
+
+import torch
+
+from ..number import FloatingPoint, FloatType
+from .quant_format import QAffineFormats, QLayerNormFormats, QSoftmaxFormats, make_quant_function
+from .quant_function import (mp_bmm, mp_layernorm_backward, mp_layernorm_forward, mp_mm, mp_softmax_backward,
+                             mp_softmax_forward, qsum_rows)
+
+__all__ = ["qlinear", "qmm", "qmatmul", "qsoftmax", "qlayernorm", "qsum", "compute_bias", "scale", "unscale"]
+
+
+# ------------------------------------------------------------------------------------------ tensor scaling
+def compute_bias(x: torch.Tensor, cast_to: FloatType, margin: int) -> torch.Tensor:
+    """Power-of-two exponent that maps the largest magnitude of each matrix onto ``cast_to``'s largest normal value
+    (reference functional.py:39-46; log2 in float64)."""
+    with torch.no_grad():
+        amax = x.abs().amax(dim=-1, keepdim=True).amax(dim=-2, keepdim=True)
+    return torch.floor(torch.log2(cast_to.normal_max / amax.double())).float() - margin
+
+
+def scale(x: torch.Tensor, x_scale) -> torch.Tensor:
+    """x * 2^x_scale (reference functional.py:49-53)."""
+    if isinstance(x_scale, torch.Tensor):
+        return x * torch.pow(2.0 * torch.ones_like(x), x_scale)
+    return x * 2 ** x_scale
+
+
+def unscale(x: torch.Tensor, x_scale) -> torch.Tensor:
+    """x * 2^-x_scale (reference functional.py:56-60)."""
+    if isinstance(x_scale, torch.Tensor):
+        return x * torch.pow(2.0 * torch.ones_like(x), -x_scale)
+    return x * 2 ** (-x_scale)
+
+
+def _scales(ctx, formats, a, b):
+    if formats.weight_scaled_format and formats.input_scaled_format and formats.use_scaling:
+        ctx.weight_scale = compute_bias(b, formats.weight_scaled_format, formats.scale_margin)
+        ctx.input_scale = compute_bias(a, formats.input_scaled_format, formats.scale_margin)
+    else:
+        ctx.input_scale, ctx.weight_scale = 0, 0
+
+
+def _grad_scale(formats, grad_output):
+    if formats.grad_scaled_format and formats.use_scaling:
+        return compute_bias(grad_output, formats.grad_scaled_format, formats.scale_margin)
+    return 0
+
+
+# ------------------------------------------------------------------------------------------ quantized sums
+def qsum_1d(x: torch.Tensor, dim: int, quant: Callable[[torch.Tensor], torch.Tensor]) -> torch.Tensor:
+    """Sequential sum along ``dim`` with ``quant`` applied after every addition, starting from zero
+    (reference functional.py:736-748: one quantize call per slice)."""
+    acc = torch.zeros_like(x.select(dim, 0)).unsqueeze(dim)
+    for k in range(x.shape[dim]):
+        acc = quant(acc + x.narrow(dim, k, 1))
+    return acc
+
+
+def _qsum_dims_fast(x: torch.Tensor, dims, fmt: FloatingPoint) -> torch.Tensor:
+    """The same left-to-right rounded sums over leading dimensions, one kernel launch per reduced dimension
+    instead of one quantize launch per slice."""
+    out = x
+    for d in dims:   # leading dims, reduced in the given order; each reduction keeps the dim (size 1)
+        moved = out.movedim(d, 0).contiguous()
+        rows = moved.shape[0]
+        flat = qsum_rows(moved.reshape(rows, -1), fmt.exp, fmt.man, fmt.subnormals, fmt.saturate)
+        out = flat.reshape((1,) + tuple(moved.shape[1:])).movedim(0, d)
+    return out
+
+
+class qsum_kernel(torch.autograd.Function):
+    """reference functional.py:751-783."""
+
+    @staticmethod
+    def forward(ctx, x, quant, dim=0, keepdim=False):
+        ctx.save_for_backward(x)
+        if dim is None:
+            dim = tuple(range(x.dim()))
+        elif not isinstance(dim, tuple):
+            dim = (dim,)
+        ctx.dim = dim
+        sums = x
+        for d in dim:
+            sums = qsum_1d(sums, d, quant)
+        if keepdim is False:
+            for _ in dim:
+                idx = 0
+                while sums.shape[idx] != 1:
+                    idx += 1
+                sums = torch.squeeze(sums, dim=idx)
+        return sums
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        (x,) = ctx.saved_tensors
+        for d in ctx.dim:
+            grad_output = torch.unsqueeze(grad_output, d)
+        return grad_output * torch.ones_like(x), None, None, None
+
+
+def qsum(x: torch.Tensor, dim=None, quant: Callable[[torch.Tensor], torch.Tensor] = lambda x: x, keepdim: bool = False):
+    """Sum with a quantization after every addition (reference functional.py:786-804)."""
+    return qsum_kernel.apply(x, quant, dim, keepdim)
+
+
+# ------------------------------------------------------------------------------------------ linear
+class qlinear_kernel(torch.autograd.Function):
+    """y = x W^T + b with per-MAC rounded GEMMs forward and backward (reference functional.py:66-173)."""
+
+    @staticmethod
+    def forward(ctx, input, weight, bias, formats):
+        ctx.formats = formats
+        _scales(ctx, formats, input, weight)
+        qinput = formats.input_quant(scale(input, ctx.input_scale))
+        qweight = formats.weight_quant(scale(weight, ctx.weight_scale))
+        qbias = formats.bias_quant(bias) if bias is not None else None
+        if formats.fwd_use_default_prec:
+            with torch.no_grad():
+                output = torch.nn.functional.linear(qinput, qweight)
+        else:
+            output = mp_bmm(qinput, qweight.t(), formats, use_forward=True)
+        output = unscale(output, ctx.input_scale + ctx.weight_scale)
+        if qbias is not None:
+            output += qbias.view(-1, qbias.shape[-1])     # plain fp32 add; rounding is left to output_quant
+        ctx.save_for_backward(qinput, qweight, qbias)
+        return formats.output_quant(output)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        qinput, qweight, qbias = ctx.saved_tensors
+        f = ctx.formats
+        qgrad_input = qgrad_weight = qgrad_bias = None
+        grad_scale = _grad_scale(f, grad_output)
+        qgrad_output = f.grad_quant(scale(grad_output, grad_scale))
+        if ctx.needs_input_grad[0]:
+            if f.bwd_use_default_prec:
+                qgrad_input = torch.matmul(qgrad_output, qweight)
+            else:
+                qgrad_input = mp_bmm(qgrad_output, qweight, formats=f, use_forward=False)
+            qgrad_input = f.grad_quant(unscale(qgrad_input, grad_scale + ctx.weight_scale))
+        if ctx.needs_input_grad[1]:
+            if f.bwd_use_default_prec:
+                qgrad_weight = torch.matmul(qgrad_output.transpose(-2, -1), qinput)
+            else:
+                # for >2-D inputs this is a batched GEMM; autograd sums the [batch, out, in] result over the batch
+                # in plain fp32 when it reduces the gradient to the weight's shape, exactly as in the reference
+                qgrad_weight = mp_bmm(qgrad_output.transpose(-2, -1), qinput, formats=f, use_forward=False)
+            qgrad_weight = f.grad_quant(unscale(qgrad_weight, grad_scale + ctx.input_scale))
+        if qbias is not None and ctx.needs_input_grad[2]:
+            lead = tuple(range(qgrad_output.dim() - 1))
+            if f.bwd_use_default_prec:
+                qgrad_bias = qgrad_output.sum(dim=lead).reshape(qbias.shape)
+            else:
+                with torch.no_grad():
+                    if isinstance(f.bwd_add, FloatingPoint) and f.bwd_rnd == "nearest" and qgrad_output.is_cuda:
+                        qgrad_bias = _qsum_dims_fast(qgrad_output, lead, f.bwd_add).reshape(qbias.shape)
+                    else:
+                        qgrad_bias = qsum(qgrad_output, dim=lead,
+                                          quant=make_quant_function(f.bwd_add, f.bwd_rnd, f.rbits_add)).reshape(qbias.shape)
+            qgrad_bias = f.grad_quant(unscale(qgrad_bias, grad_scale))
+        return qgrad_input, qgrad_weight, qgrad_bias, None, None
+
+
+def qlinear(input: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
+            formats: QAffineFormats = QAffineFormats()) -> torch.Tensor:
+    """Functional form of ``QLinear`` (reference functional.py:176-208)."""
+    return qlinear_kernel.apply(input, weight, bias, formats)
+
+
+# ------------------------------------------------------------------------------------------ mm / matmul
+def _matmul_function(fwd_default, mp_fn, name, requantize_unscaled):
+    class kernel(torch.autograd.Function):
+        @staticmethod
+        def forward(ctx, input, other, formats):
+            ctx.formats = formats
+            _scales(ctx, formats, input, other)
+            qinput = formats.input_quant(scale(input, ctx.input_scale))
+            qother = formats.weight_quant(scale(other, ctx.weight_scale))
+            if formats.fwd_use_default_prec:
+                with torch.no_grad():
+                    output = fwd_default(qinput, qother)
+            else:
+                output = mp_fn(qinput, qother, formats=formats, use_forward=True)
+            output = unscale(output, ctx.input_scale + ctx.weight_scale)
+            ctx.save_for_backward(qinput, qother)
+            return formats.output_quant(output)
+
+        @staticmethod
+        def backward(ctx, grad_output):
+            qinput, qother = ctx.saved_tensors
+            f = ctx.formats
+            qgrad_input = qgrad_other = None
+            grad_scale = _grad_scale(f, grad_output)
+            qgrad_output = f.grad_quant(scale(grad_output, grad_scale))
+            if ctx.needs_input_grad[0]:
+                if f.bwd_use_default_prec:
+                    g = fwd_default(qgrad_output, qother.transpose(-2, -1))
+                else:
+                    g = mp_fn(qgrad_output, qother.transpose(-2, -1), formats=f, use_forward=False)
+                # the reference's qmm quantizes the un-unscaled gradient (functional.py:270-272); qmatmul the unscaled one
+                qgrad_input = f.grad_quant(unscale(g, grad_scale + ctx.weight_scale) if requantize_unscaled else g)
+            if ctx.needs_input_grad[1]:
+                if f.bwd_use_default_prec:
+                    g = fwd_default(qinput.transpose(-2, -1), qgrad_output)
+                else:
+                    g = mp_fn(qinput.transpose(-2, -1), qgrad_output, formats=f, use_forward=False)
+                qgrad_other = f.grad_quant(unscale(g, grad_scale + ctx.input_scale) if requantize_unscaled else g)
+            return qgrad_input, qgrad_other, None
+
+    kernel.__name__ = name
+    return kernel
+
+
+qmm_kernel = _matmul_function(torch.mm, mp_mm, "qmm_kernel", False)            # reference functional.py:211-290
+qmatmul_kernel = _matmul_function(torch.matmul, mp_bmm, "qmatmul_kernel", True)  # reference functional.py:320-401
+
+
+def qmm(input: torch.Tensor, mat2: torch.Tensor, formats: QAffineFormats = QAffineFormats()) -> torch.Tensor:
+    """(n, m) x (m, p) product through the simulated GEMM (reference functional.py:293-317)."""
+    return qmm_kernel.apply(input, mat2, formats)
+
+
+def qmatmul(input: torch.Tensor, other: torch.Tensor, formats: QAffineFormats = QAffineFormats()) -> torch.Tensor:
+    """Batched product for the shape cases of ``float_bmm`` (reference functional.py:404-446)."""
+    return qmatmul_kernel.apply(input, other, formats)
+
+
+# ------------------------------------------------------------------------------------------ softmax
+class qsoftmax_kernel(torch.autograd.Function):
+    """reference functional.py:1024-1058."""
+
+    @staticmethod
+    def forward(ctx, a, dim, formats):
+        ctx.formats, ctx.dim = formats, dim
+        qinput = formats.input_quant(a)
+        if formats.fwd_use_default_prec:
+            with torch.no_grad():
+                output = torch.nn.functional.softmax(qinput, dim)
+        else:
+            output = mp_softmax_forward(qinput, dim, formats)
+        qoutput = formats.output_quant(output)
+        ctx.save_for_backward(qoutput)
+        return qoutput
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        (qoutput,) = ctx.saved_tensors
+        f = ctx.formats
+        qgrad_output = f.grad_quant(grad_output)
+        if f.bwd_use_default_prec:
+            weighted = torch.sum(qoutput * qgrad_output, dim=ctx.dim, keepdim=True)
+            grad_input = qoutput * (qgrad_output - weighted)
+        else:
+            grad_input = mp_softmax_backward(qoutput, qgrad_output, ctx.dim, f)
+        return f.grad_quant(grad_input), None, None
+
+
+def qsoftmax(input: torch.Tensor, dim: int, formats: QSoftmaxFormats) -> torch.Tensor:
+    """Functional form of ``QSoftmax`` (reference functional.py:1061-1091)."""
+    return qsoftmax_kernel.apply(input, dim, formats)
+
+
+# ------------------------------------------------------------------------------------------ layernorm
+class qlayernorm_kernel(torch.autograd.Function):
+    """reference functional.py:876-969."""
+
+    @staticmethod
+    def forward(ctx, x, normalized_shape, weight, bias, eps, formats):
+        ctx.formats, ctx.eps = formats, eps
+        qinput = formats.input_quant(x)
+        qweight = formats.weight_quant(weight) if weight is not None else torch.ones(normalized_shape, device=x.device)
+        qbias = formats.bias_quant(bias) if bias is not None else torch.zeros(normalized_shape, device=x.device)
+        if isinstance(normalized_shape, int):
+            normalized_shape = torch.Size([normalized_shape])
+        elif isinstance(normalized_shape, list):
+            normalized_shape = torch.Size(normalized_shape)
+        assert isinstance(normalized_shape, torch.Size)
+        assert normalized_shape == x.shape[-len(normalized_shape):]
+        dims = [-(i + 1) for i in range(len(normalized_shape))]
+        ctx.dims = dims
+        if formats.fwd_use_default_prec:
+            C = qweight.numel()
+            mean = x.sum(dims, keepdim=True) / C
+            xshift = x - mean
+            rstd = ((xshift ** 2).sum(dims, keepdim=True) / C + eps) ** -0.5
+            output = xshift * rstd * qweight + qbias
+        else:
+            output, mean, rstd = mp_layernorm_forward(qinput, qweight, qbias, eps, dims, formats)
+        ctx.save_for_backward(qinput, qweight, qbias, mean, rstd)
+        return formats.output_quant(output)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        qinput, qweight, qbias, mean, rstd = ctx.saved_tensors
+        f, dims = ctx.formats, ctx.dims
+        qgrad_output = f.grad_quant(grad_output)
+        if f.bwd_use_default_prec:
+            lead = tuple(range(qinput.dim() - len(dims)))
+            m = mean.reshape(mean.shape[:len(lead)] + (1,) * len(dims)) if mean.dim() == len(lead) else mean
+            r = rstd.reshape(m.shape) if rstd.dim() == len(lead) else rstd
+            norm = (qinput - m) * r
+            grad_bias = grad_output.sum(lead)
+            grad_weight = (grad_output * norm).sum(lead)
+            grad_norm = grad_output * qweight
+            grad_input = (grad_norm - grad_norm.mean(dims, keepdim=True)
+                          - norm * (grad_norm * norm).mean(dims, keepdim=True)) * r
+        else:
+            grad_input, grad_weight, grad_bias = mp_layernorm_backward(qinput, qgrad_output, qweight, qbias, mean, rstd, dims, f)
+        qgi = f.grad_quant(grad_input) if ctx.needs_input_grad[0] else None
+        qgw = f.grad_quant(grad_weight) if ctx.needs_input_grad[2] else None
+        qgb = f.grad_quant(grad_bias) if ctx.needs_input_grad[3] else None
+        return qgi, None, qgw, qgb, None, None
+
+
+def qlayernorm(x: torch.Tensor, normalized_shape, weight: torch.Tensor | None, bias: torch.Tensor | None, eps: float,
+               formats: QLayerNormFormats) -> torch.Tensor:
+    """Functional form of ``QLayerNorm`` (reference functional.py:972-1021)."""
+    return qlayernorm_kernel.apply(x, normalized_shape, weight, bias, eps, formats)
