@@ -9,6 +9,7 @@
 //   * the "magic add" fast path (`FastRn`): round-to-nearest-even on the FP32 pipe,
 //     bit-identical to the exact caster on the value range its caller guarantees.
 #pragma once
+#include <cfenv>
 #include <cmath>
 #include <cstdint>
 #include <cstring>
@@ -40,6 +41,18 @@ MPT_HD float fma_rn(float a, float b, float c) {
     return __fmaf_rn(a, b, c);
 #else
     return fmaf(a, b, c);
+#endif
+}
+// fused multiply-add rounded toward zero (host side: through the floating-point environment)
+MPT_HD float fma_rz(float a, float b, float c) {
+#ifdef __CUDA_ARCH__
+    return __fmaf_rz(a, b, c);
+#else
+    const int old = fegetround();
+    fesetround(FE_TOWARDZERO);
+    volatile float r = fmaf(a, b, c);
+    fesetround(old);
+    return r;
 #endif
 }
 MPT_HD float add_rn(float a, float b) {
@@ -354,6 +367,83 @@ struct FullRn {
         float y = fast(x);
         const float over = (a >= 0x7F800000u) ? x : u2f((t & 0x80000000u) | ovf_value);
         return (a >= ovf_from) ? over : y;
+    }
+};
+
+
+// Truncation toward zero over the whole fp32 input domain, the counterpart of FullRn: the magic
+// constant carries the sign of x and the first FFMA rounds toward zero, so |x| + C is cut down to a
+// multiple of the quantum; the second FFMA (exact) removes C again.
+struct FullRz {
+    FastRn fast;
+    FpFmt fmt;
+    uint32_t ovf_from, ovf_value, exact_from;
+    __host__ __device__ static FullRz make(const FpFmt& f) {
+        FullRz r;
+        r.fast = FastRn::make(f);
+        r.fmt = f;
+        const uint32_t maxf = ((uint32_t)f.max_store << 23) | ((0x7FFFFFu >> (23 - f.man)) << (23 - f.man));
+        r.ovf_from = (uint32_t)(f.max_store + 1) << 23;   // truncation never rounds up into overflow
+        r.ovf_value = f.sat ? maxf : 0x7F800000u;
+        r.exact_from = (f.exp == 8) ? ((uint32_t)(103 + f.man + 1 + 127) << 23) : 0xFFFFFFFFu;
+        return r;
+    }
+    MPT_HD float operator()(float x) const {
+        const uint32_t t = f2u(x);
+        const uint32_t a = t & 0x7FFFFFFFu;
+        if (fmt.exp == 8 && (a >= exact_from || a < 0x00800000u)) return cast_fp_truncate(x, fmt);
+        const int e = (int)(t & 0x7F800000u);
+        const float m = u2f((uint32_t)(e > fast.min_e_bits ? e : fast.min_e_bits) | (t & 0x80000000u));
+        const float y = fma_rz(m, fast.k, x);
+        const float r = fma_rn(m, -fast.k, y);
+        // a negative input that truncates to zero leaves -0 here; the reference's subnormal branch returns +0
+        const float rz = (f2u(r) == 0x80000000u) ? 0.0f : r;
+        const float over = (a >= 0x7F800000u) ? x : u2f((t & 0x80000000u) | ovf_value);
+        return (a >= ovf_from) ? over : rz;
+    }
+};
+
+// Round-to-nearest-even for P3109 binary8 (P >= 2, subnormals on) over the whole input domain, on the
+// same FP-pipe rounding.  The format's largest finite value depends on signedness and overflow policy,
+// so the overflow threshold is worked out on the host: the smallest |x| pattern that rounds above it.
+struct FullRnB8 {
+    FastRn fast;
+    uint32_t ovf_from;    // smallest |x| pattern that rounds above the largest finite value
+    uint32_t ovf_value;   // largest finite value, or infinity for the SATURATE_INFTY policy
+    int is_signed, keep_inf;
+    __host__ __device__ static bool supported(int P, bool sub) { return sub && P >= 2 && P <= 7; }
+    __host__ __device__ static FullRnB8 make(int P, bool is_signed, int policy) {
+        FullRnB8 r;
+        const int man = P - 1, exp = is_signed ? 8 - P : 9 - P;
+        const int max_exp = (1 << (exp - 1)) - 1;
+        FpFmt f = make_fmt(man, 8, 1, 0);
+        f.min_exp = -max_exp;                           // P >= 2
+        r.fast = FastRn::make(f);
+        const uint32_t ones = (1u << man) - 1u;
+        const int up = 23 - man;
+        uint32_t top_man = (ones & ~1u) << up;
+        int reserve = 0;
+        if (policy == B8_MAXFLOAT2) { if (exp + man == 7) top_man = ones << up; }
+        else if (exp == 8) reserve = 1;
+        else if (exp == 7 && man == 1) { reserve = 1; top_man = ones << up; }
+        else if (exp + man == 8) top_man = (ones - 2u) << up;
+        const uint32_t maxf = ((uint32_t)(max_exp + 127 - reserve) << 23) | top_man;
+        const bool max_is_odd = ((top_man >> up) & 1u) != 0u;
+        r.ovf_from = maxf + (1u << (up - 1)) + (max_is_odd ? 0u : 1u);   // a tie goes to the even neighbour
+        r.ovf_value = policy == B8_INFTY ? 0x7F800000u : maxf;
+        r.is_signed = is_signed;
+        r.keep_inf = policy == B8_INFTY;
+        return r;
+    }
+    MPT_HD float operator()(float x) const {
+        const uint32_t t = f2u(x);
+        const uint32_t a = t & 0x7FFFFFFFu;
+        float y = fast(x);
+        const bool passthrough = a > 0x7F800000u || (a == 0x7F800000u && keep_inf);
+        const float over = passthrough ? x : u2f((t & 0x80000000u) | ovf_value);
+        y = (a >= ovf_from) ? over : y;
+        if (!is_signed && x < 0.0f) y = u2f(0x7FC00000u);
+        return y;
     }
 };
 

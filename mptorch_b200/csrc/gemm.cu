@@ -26,6 +26,7 @@
 // Kahan-compensated and stochastic variants follow quant_cuda/mm_kernel.h:457-520 and :248-295.
 #include <cuda_pipeline.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "cast.cuh"
@@ -159,8 +160,25 @@ __device__ __forceinline__ float mac_fast(float acc, float a, float b, const Fas
     return radd(add_rn(acc, rmul(mul_rn(a, b))));
 }
 
+// Two accumulation steps at once on sm_100's packed fp32x2 instructions (FMUL2 / FADD2 / FFMA2): the six
+// FP-pipe instructions of a MAC are shared by two neighbouring outputs, so a MAC costs 3 packed FP
+// instructions + 4 ALU instructions (the exponent extraction stays per element) = 7 issue slots
+// instead of 10.  Each half of a packed instruction rounds exactly like its scalar form.
+__device__ __forceinline__ float2 fast_rn2(const FastRn& r, float2 x) {
+    const int e0 = max(__float_as_int(x.x) & 0x7F800000, r.min_e_bits);
+    const int e1 = max(__float_as_int(x.y) & 0x7F800000, r.min_e_bits);
+    const float2 m = make_float2(__int_as_float(e0), __int_as_float(e1));
+    const float2 y = __ffma2_rn(m, make_float2(r.k, r.k), x);
+    return __ffma2_rn(m, make_float2(-r.k, -r.k), y);
+}
+template <bool FMA>
+__device__ __forceinline__ float2 mac_fast2(float2 acc, float2 a2, float2 b2, const FastRn& radd, const FastRn& rmul) {
+    if (FMA) return fast_rn2(radd, __ffma2_rn(a2, b2, acc));
+    return fast_rn2(radd, __fadd2_rn(acc, fast_rn2(rmul, __fmul2_rn(a2, b2))));
+}
+
 // `nk` (1..8) accumulation steps starting at slab row kbase, for the thread's 8x4 outputs.
-template <bool FMA, bool FAST>
+template <bool FMA, bool FAST, bool PACKED>
 __device__ __forceinline__ void group_steps(float (&acc)[TM][TN], const float* As, const float* Bs, int kbase, int nk,
                                             int ty, int tx, const MmParams& p) {
     if (FAST && nk == 8) {
@@ -176,10 +194,17 @@ __device__ __forceinline__ void group_steps(float (&acc)[TM][TN], const float* A
 #pragma unroll
                 for (int i = 0; i < TM; ++i) {
                     const float a = j == 0 ? av[i].x : j == 1 ? av[i].y : j == 2 ? av[i].z : av[i].w;
-                    acc[i][0] = mac_fast<FMA>(acc[i][0], a, bv.x, p.radd, p.rmul);
-                    acc[i][1] = mac_fast<FMA>(acc[i][1], a, bv.y, p.radd, p.rmul);
-                    acc[i][2] = mac_fast<FMA>(acc[i][2], a, bv.z, p.radd, p.rmul);
-                    acc[i][3] = mac_fast<FMA>(acc[i][3], a, bv.w, p.radd, p.rmul);
+                    if (PACKED) {
+                        const float2 a2 = make_float2(a, a);
+                        const float2 lo = mac_fast2<FMA>(make_float2(acc[i][0], acc[i][1]), a2, make_float2(bv.x, bv.y), p.radd, p.rmul);
+                        const float2 hi = mac_fast2<FMA>(make_float2(acc[i][2], acc[i][3]), a2, make_float2(bv.z, bv.w), p.radd, p.rmul);
+                        acc[i][0] = lo.x; acc[i][1] = lo.y; acc[i][2] = hi.x; acc[i][3] = hi.y;
+                    } else {
+                        acc[i][0] = mac_fast<FMA>(acc[i][0], a, bv.x, p.radd, p.rmul);
+                        acc[i][1] = mac_fast<FMA>(acc[i][1], a, bv.y, p.radd, p.rmul);
+                        acc[i][2] = mac_fast<FMA>(acc[i][2], a, bv.z, p.radd, p.rmul);
+                        acc[i][3] = mac_fast<FMA>(acc[i][3], a, bv.w, p.radd, p.rmul);
+                    }
                 }
             }
         }
@@ -259,7 +284,7 @@ __device__ __forceinline__ FastPlan make_plan(const MmParams& p, int64_t batch) 
     return plan;
 }
 
-template <int ALGO, bool FMA, bool VEC>
+template <int ALGO, bool FMA, bool VEC, bool PACKED>
 __global__ void __launch_bounds__(THREADS, 2) mm_kernel(const MmParams p) {
     extern __shared__ __align__(16) float smem[];
     float* As = smem;
@@ -310,14 +335,23 @@ __global__ void __launch_bounds__(THREADS, 2) mm_kernel(const MmParams p) {
             for (int g = 0; g * 8 < nk_tile; ++g) {
                 const int nk = (nk_tile - g * 8) < 8 ? (nk_tile - g * 8) : 8;
                 if (ALGO == ALGO_TILE8) {
-                    if (plan.ok) group_steps<FMA, true>(acc, as, bs, g * 8, nk, ty, tx, p);
-                    else group_steps<FMA, false>(acc, as, bs, g * 8, nk, ty, tx, p);
+                    if (plan.ok) group_steps<FMA, true, PACKED>(acc, as, bs, g * 8, nk, ty, tx, p);
+                    else group_steps<FMA, false, false>(acc, as, bs, g * 8, nk, ty, tx, p);
                     // fold the group into the outer sum
                     if (plan.ok && absmax_of(aux) < plan.acc_limit) {
 #pragma unroll
-                        for (int i = 0; i < TM; ++i)
+                        for (int i = 0; i < TM; ++i) {
+                            if (PACKED) {
+                                const float2 lo = fast_rn2(p.radd, __fadd2_rn(make_float2(aux[i][0], aux[i][1]), make_float2(acc[i][0], acc[i][1])));
+                                const float2 hi = fast_rn2(p.radd, __fadd2_rn(make_float2(aux[i][2], aux[i][3]), make_float2(acc[i][2], acc[i][3])));
+                                aux[i][0] = lo.x; aux[i][1] = lo.y; aux[i][2] = hi.x; aux[i][3] = hi.y;
+                            } else {
 #pragma unroll
-                            for (int j = 0; j < TN; ++j) { aux[i][j] = p.radd(add_rn(aux[i][j], acc[i][j])); acc[i][j] = 0.0f; }
+                                for (int j = 0; j < TN; ++j) aux[i][j] = p.radd(add_rn(aux[i][j], acc[i][j]));
+                            }
+#pragma unroll
+                            for (int j = 0; j < TN; ++j) acc[i][j] = 0.0f;
+                        }
                     } else {
 #pragma unroll
                         for (int i = 0; i < TM; ++i)
@@ -325,8 +359,8 @@ __global__ void __launch_bounds__(THREADS, 2) mm_kernel(const MmParams p) {
                             for (int j = 0; j < TN; ++j) { aux[i][j] = cast_fp_nearest(add_rn(aux[i][j], acc[i][j]), p.fadd); acc[i][j] = 0.0f; }
                     }
                 } else {
-                    if (plan.ok && absmax_of(acc) < plan.acc_limit) group_steps<FMA, true>(acc, as, bs, g * 8, nk, ty, tx, p);
-                    else group_steps<FMA, false>(acc, as, bs, g * 8, nk, ty, tx, p);
+                    if (plan.ok && absmax_of(acc) < plan.acc_limit) group_steps<FMA, true, PACKED>(acc, as, bs, g * 8, nk, ty, tx, p);
+                    else group_steps<FMA, false, false>(acc, as, bs, g * 8, nk, ty, tx, p);
                 }
             }
         } else if (ALGO == ALGO_KAHAN) {
@@ -394,10 +428,20 @@ __global__ void __launch_bounds__(THREADS, 2) mm_kernel(const MmParams p) {
     }
 }
 
+// The packed fp32x2 fast path is the default; MPT_MM_SCALAR=1 in the environment selects the scalar
+// fast path (same bits; kept for A/B measurements).
+bool use_packed() {
+    static const bool packed = [] { const char* e = getenv("MPT_MM_SCALAR"); return !(e && e[0] == '1'); }();
+    return packed;
+}
+
 template <int ALGO, bool FMA>
 int launch_mm(const MmParams& p, int64_t batch, bool vec, cudaStream_t st) {
     dim3 grid((p.N + BN - 1) / BN, (p.M + BM - 1) / BM, (unsigned)batch);
-    auto kern = vec ? mm_kernel<ALGO, FMA, true> : mm_kernel<ALGO, FMA, false>;
+    constexpr bool kHasFast = (ALGO == ALGO_SEQ || ALGO == ALGO_TILE8);
+    const bool packed = kHasFast && use_packed();
+    auto kern = vec ? (packed ? mm_kernel<ALGO, FMA, true, kHasFast> : mm_kernel<ALGO, FMA, true, false>)
+                    : (packed ? mm_kernel<ALGO, FMA, false, kHasFast> : mm_kernel<ALGO, FMA, false, false>);
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
     if (e != cudaSuccess) { set_error("float_mm: cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return MPT_ERR_CUDA; }
     kern<<<grid, THREADS, SMEM_BYTES, st>>>(p);

@@ -80,6 +80,16 @@ struct FpNearestFast {
     __device__ __forceinline__ float one(float x, int64_t) const { return r(x); }
     MPT_VEC_FROM_ONE
 };
+struct FpTruncateFast {
+    FullRz r;
+    __device__ __forceinline__ float one(float x, int64_t) const { return r(x); }
+    MPT_VEC_FROM_ONE
+};
+struct Binary8NearestFast {
+    FullRnB8 r;
+    __device__ __forceinline__ float one(float x, int64_t) const { return r(x); }
+    MPT_VEC_FROM_ONE
+};
 struct FpTruncate {
     FpFmt f;
     __device__ __forceinline__ float one(float x, int64_t) const { return cast_fp_truncate(x, f); }
@@ -156,8 +166,9 @@ int mpt_float_quantize_truncate(const float* in, float* out, int64_t n, int man,
                                 int saturate, void* stream) {
     MPT_REQUIRE(n >= 0 && (n == 0 || (in && out)), "float_quantize_truncate: null pointer or negative size");
     MPT_REQUIRE(valid_format(man, exp), "float_quantize_truncate: unsupported format man=%d exp=%d", man, exp);
-    return launch_map(in, out, n, FpTruncate{make_fmt(man, exp, subnormals, saturate)}, as_stream(stream),
-                      "float_quantize_truncate");
+    const FpFmt f = make_fmt(man, exp, subnormals, saturate);
+    if (fast_rn_supported(f)) return launch_map(in, out, n, FpTruncateFast{FullRz::make(f)}, as_stream(stream), "float_quantize_truncate");
+    return launch_map(in, out, n, FpTruncate{f}, as_stream(stream), "float_quantize_truncate");
 }
 
 int mpt_float_quantize_stochastic(const float* in, const int32_t* rand, float* out, int64_t n, int man, int exp,
@@ -185,6 +196,9 @@ int mpt_binary8_quantize(const float* in, const int32_t* rand, float* out, int64
     MPT_REQUIRE(overflow_policy >= 0 && overflow_policy <= 2, "binary8_quantize: unknown overflow policy %d", overflow_policy);
     MPT_REQUIRE(rounding >= 0 && rounding <= 2, "binary8_quantize: unknown rounding mode %d", rounding);
     MPT_REQUIRE(rounding != MPT_RND_STOCHASTIC || n == 0 || rand, "binary8_quantize: stochastic rounding needs random words");
+    if (rounding == MPT_RND_NEAREST && FullRnB8::supported(P, subnormals != 0))
+        return launch_map(in, out, n, Binary8NearestFast{FullRnB8::make(P, is_signed != 0, overflow_policy)}, as_stream(stream),
+                          "binary8_quantize");
     return launch_map(in, out, n, Binary8{P, is_signed, overflow_policy, subnormals, rounding, prng_bits, rand},
                       as_stream(stream), "binary8_quantize");
 }

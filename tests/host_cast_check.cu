@@ -84,3 +84,39 @@ HC_API int64_t hc_sweep_full_rn(int man, int exp, int sat, uint64_t first, uint6
     if (first_bad) *first_bad = firstbad;
     return bad;
 }
+
+template <class Got, class Want>
+static int64_t sweep_all(uint64_t first, uint64_t count, uint64_t stride, uint32_t* first_bad, Got got_fn, Want want_fn) {
+    int64_t bad = 0;
+    uint32_t firstbad = 0;
+    bool have = false;
+#pragma omp parallel for reduction(+ : bad) schedule(static)
+    for (int64_t i = 0; i < (int64_t)count; ++i) {
+        const uint32_t t = (uint32_t)(first + (uint64_t)i * stride);
+        const float x = u2f(t);
+        const uint32_t want = f2u(want_fn(x));
+        const uint32_t got = f2u(got_fn(x));
+        const bool both_nan = (want & 0x7FFFFFFFu) > 0x7F800000u && (got & 0x7FFFFFFFu) > 0x7F800000u;
+        if (want != got && !both_nan) {
+            ++bad;
+#pragma omp critical
+            if (!have) { firstbad = t; have = true; }
+        }
+    }
+    if (first_bad) *first_bad = firstbad;
+    return bad;
+}
+
+// whole-domain truncation (FullRz) vs the exact truncating caster
+HC_API int64_t hc_sweep_full_rz(int man, int exp, int sat, uint64_t first, uint64_t count, uint64_t stride, uint32_t* first_bad) {
+    const FpFmt f = make_fmt(man, exp, 1, sat);
+    const FullRz full = FullRz::make(f);
+    return sweep_all(first, count, stride, first_bad, [&](float x) { return full(x); }, [&](float x) { return cast_fp_truncate(x, f); });
+}
+
+// whole-domain binary8 nearest (FullRnB8) vs the exact binary8 caster
+HC_API int64_t hc_sweep_full_b8(int P, int is_signed, int policy, uint64_t first, uint64_t count, uint64_t stride, uint32_t* first_bad) {
+    const FullRnB8 full = FullRnB8::make(P, is_signed != 0, policy);
+    return sweep_all(first, count, stride, first_bad, [&](float x) { return full(x); },
+                     [&](float x) { return cast_binary8(x, P, is_signed != 0, policy, true, RND_NEAREST, 0u, 0); });
+}

@@ -31,6 +31,10 @@ def hc():
     L.hc_superfp.argtypes = [p, p, i64, i32, i32, i32, i32, i32]
     L.hc_sweep_fast_rn.restype = i64
     L.hc_sweep_fast_rn.argtypes = [i32, i32, u64, u64, u64, p]
+    L.hc_sweep_full_rz.restype = i64
+    L.hc_sweep_full_rz.argtypes = [i32, i32, i32, u64, u64, u64, p]
+    L.hc_sweep_full_b8.restype = i64
+    L.hc_sweep_full_b8.argtypes = [i32, i32, i32, u64, u64, u64, p]
     L.hc_sweep_full_rn.restype = i64
     L.hc_sweep_full_rn.argtypes = [i32, i32, i32, u64, u64, u64, p]
     return L
@@ -126,3 +130,31 @@ def test_whole_domain_fast_rounding_equals_exact_cast(hc, fmt, sat):
         first = max(centre - 64, 0)
         bad = hc.hc_sweep_full_rn(m, e, sat, first, min(128, 2**32 - first), 1, _ptr(first_bad))
         assert bad == 0, f"e{e}m{m} sat={sat}: mismatch near {centre:#010x}, first at {int(first_bad[0]):#010x}"
+
+
+WINDOWS = (0x00000000, 0x00800000, 0x7F800000, 0x80000000, 0x80800000, 0xFF800000, 0xFFFFFFF0)
+
+
+def _sweep(fn, args, stride, what):
+    first_bad = np.zeros(1, dtype=np.uint32)
+    bad = fn(*args, 0, (2**32 + stride - 1) // stride, stride, _ptr(first_bad))
+    assert bad == 0, f"{what}: {bad} mismatches, first at pattern {int(first_bad[0]):#010x}"
+    for centre in WINDOWS:
+        first = max(centre - 64, 0)
+        bad = fn(*args, first, min(128, 2**32 - first), 1, _ptr(first_bad))
+        assert bad == 0, f"{what}: mismatch near {centre:#010x}, first at {int(first_bad[0]):#010x}"
+
+
+@pytest.mark.parametrize("fmt", [(4, 3), (5, 2), (5, 10), (8, 7), (8, 0), (2, 1), (6, 21), (3, 0)])
+@pytest.mark.parametrize("sat", [0, 1])
+def test_whole_domain_fast_truncation_equals_exact_cast(hc, fmt, sat):
+    e, m = fmt
+    _sweep(hc.hc_sweep_full_rz, (m, e, sat), 1 if fmt == (4, 3) else 129, f"truncate e{e}m{m} sat={sat}")
+
+
+@pytest.mark.parametrize("P", range(2, 8))
+@pytest.mark.parametrize("signed", [0, 1])
+@pytest.mark.parametrize("policy", [0, 1, 2])
+def test_whole_domain_fast_binary8_equals_exact_cast(hc, P, signed, policy):
+    stride = 1 if (P, signed, policy) == (3, 1, 1) else 257      # BASELINE config 2's binary8 arm is swept exhaustively
+    _sweep(hc.hc_sweep_full_b8, (P, signed, policy), stride, f"binary8 P={P} signed={signed} policy={policy}")
