@@ -403,6 +403,50 @@ struct FullRz {
     }
 };
 
+// Stochastic rounding with an explicit random word over the whole input domain, for formats with
+// subnormals: the two branches of the exact caster (lift sub-minimum inputs into the smallest normal
+// binade, round there, come back) collapse into one straight line with a conditional lift of zero.
+struct FullSr {
+    FpFmt fmt;
+    uint32_t rmask;       // random bits that take part: low (23 - man) bits, minus the one bit the reference clears
+    uint32_t keep;        // ~((1 << (23 - man)) - 1)
+    uint32_t min_norm;    // bit pattern of the smallest normal value 2^min_exp
+    uint32_t ovf_from;    // (max_store + 1) << 23
+    uint32_t ovf_value;
+    int rbits;
+    __host__ __device__ static bool supported(const FpFmt& f) { return f.sub && f.exp >= 2; }
+    __host__ __device__ static FullSr make(const FpFmt& f, int rbits) {
+        FullSr r;
+        r.fmt = f;
+        r.rbits = rbits;
+        const uint32_t low = (f.man >= 23) ? 0u : ((1u << (23 - f.man)) - 1u);
+        r.keep = ~low;
+        uint32_t rm = 0x7FFFFFu & low;
+        const int sh = 23 - f.man - rbits - 1;
+        if (sh >= 0 && sh <= 31) rm &= ~(1u << sh);
+        r.rmask = rm;
+        r.min_norm = (uint32_t)(f.min_exp + 127) << 23;
+        r.ovf_from = (uint32_t)(f.max_store + 1) << 23;
+        r.ovf_value = f.sat ? (((uint32_t)f.max_store << 23) | ((0x7FFFFFu >> (23 - f.man)) << (23 - f.man))) : 0x7F800000u;
+        return r;
+    }
+    MPT_HD float operator()(float x, uint32_t rnd) const {
+        const uint32_t t = f2u(x);
+        const uint32_t a = t & 0x7FFFFFFFu;
+        const uint32_t sign = t & 0x80000000u;
+        // NaN payloads can carry into the sign bit when the random word is added; the reference has no NaN
+        // early-out on this path, so whatever its clip makes of the wrapped pattern is reproduced by the exact caster
+        if (a > 0x7F800000u) return cast_fp_stochastic(x, rnd, rbits, fmt);
+        const bool small = a < min_norm;
+        const float lift = u2f(small ? (min_norm | sign) : 0u);
+        const uint32_t v = small ? f2u(add_rn(x, lift)) : t;
+        const uint32_t q = (v + (rnd & rmask)) & keep;
+        const float r = small ? add_rn(u2f(q), -lift) : u2f(q);
+        // the exponent clip of the normal branch: anything at or above 2^(max_exp+1), infinities and NaN included
+        return (!small && (q & 0x7FFFFFFFu) >= ovf_from) ? u2f(sign | ovf_value) : r;
+    }
+};
+
 // Round-to-nearest-even for P3109 binary8 (P >= 2, subnormals on) over the whole input domain, on the
 // same FP-pipe rounding.  The format's largest finite value depends on signedness and overflow policy,
 // so the overflow threshold is worked out on the host: the smallest |x| pattern that rounds above it.

@@ -95,40 +95,44 @@ struct FpTruncate {
     __device__ __forceinline__ float one(float x, int64_t) const { return cast_fp_truncate(x, f); }
     MPT_VEC_FROM_ONE
 };
-struct FpStochastic {
+// SR casters with a common call shape: exact (every format) and the straight-line FullSr (formats with subnormals)
+struct SrExact {
     FpFmt f;
-    const int32_t* __restrict__ rnd;
     int rbits;
-    __device__ __forceinline__ float one(float x, int64_t i) const {
-        return cast_fp_stochastic(x, (uint32_t)__ldcs(rnd + i), rbits, f);
-    }
+    __device__ __forceinline__ float operator()(float x, uint32_t r) const { return cast_fp_stochastic(x, r, rbits, f); }
+};
+
+template <class SR>
+struct FpStochastic {
+    SR sr;
+    const int32_t* __restrict__ rnd;
+    __device__ __forceinline__ float one(float x, int64_t i) const { return sr(x, (uint32_t)__ldcs(rnd + i)); }
     __device__ __forceinline__ float4 vec(float4 x, int64_t i) const {
         // the random words are as aligned as the data when the caller allocates both the same way
         int4 r;
         if ((reinterpret_cast<uintptr_t>(rnd) & 15u) == 0) r = __ldcs(reinterpret_cast<const int4*>(rnd + i));
         else r = make_int4(rnd[i], rnd[i + 1], rnd[i + 2], rnd[i + 3]);
-        return make_float4(cast_fp_stochastic(x.x, (uint32_t)r.x, rbits, f), cast_fp_stochastic(x.y, (uint32_t)r.y, rbits, f),
-                           cast_fp_stochastic(x.z, (uint32_t)r.z, rbits, f), cast_fp_stochastic(x.w, (uint32_t)r.w, rbits, f));
+        return make_float4(sr(x.x, (uint32_t)r.x), sr(x.y, (uint32_t)r.y), sr(x.z, (uint32_t)r.z), sr(x.w, (uint32_t)r.w));
     }
 };
 // Random words from Philox4x32-10: counter = (i / 4, i / 4 >> 32, 0, 0), key = seed; element i
 // takes word i % 4.  31 bits are used, like the reference's randint_like(a, INT_MAX).
+template <class SR>
 struct FpStochasticPhilox {
-    FpFmt f;
-    int rbits;
+    SR sr;
     uint32_t k0, k1;
     __device__ __forceinline__ float one(float x, int64_t i) const {
         const uint64_t blk = (uint64_t)i >> 2;
         Philox p((uint32_t)blk, (uint32_t)(blk >> 32), 0u, 0u);
         p.run(k0, k1);
-        return cast_fp_stochastic(x, p.c[i & 3] & 0x7FFFFFFFu, rbits, f);
+        return sr(x, p.c[i & 3] & 0x7FFFFFFFu);
     }
     __device__ __forceinline__ float4 vec(float4 x, int64_t i) const {
         const uint64_t blk = (uint64_t)i >> 2;
         Philox p((uint32_t)blk, (uint32_t)(blk >> 32), 0u, 0u);
         p.run(k0, k1);
-        return make_float4(cast_fp_stochastic(x.x, p.c[0] & 0x7FFFFFFFu, rbits, f), cast_fp_stochastic(x.y, p.c[1] & 0x7FFFFFFFu, rbits, f),
-                           cast_fp_stochastic(x.z, p.c[2] & 0x7FFFFFFFu, rbits, f), cast_fp_stochastic(x.w, p.c[3] & 0x7FFFFFFFu, rbits, f));
+        return make_float4(sr(x.x, p.c[0] & 0x7FFFFFFFu), sr(x.y, p.c[1] & 0x7FFFFFFFu), sr(x.z, p.c[2] & 0x7FFFFFFFu),
+                           sr(x.w, p.c[3] & 0x7FFFFFFFu));
     }
 };
 struct Binary8 {
@@ -175,18 +179,23 @@ int mpt_float_quantize_stochastic(const float* in, const int32_t* rand, float* o
                                   int prng_bits, int subnormals, int saturate, void* stream) {
     MPT_REQUIRE(n >= 0 && (n == 0 || (in && out && rand)), "float_quantize_stochastic: null pointer or negative size");
     MPT_REQUIRE(valid_format(man, exp), "float_quantize_stochastic: unsupported format man=%d exp=%d", man, exp);
-    return launch_map(in, out, n, FpStochastic{make_fmt(man, exp, subnormals, saturate), rand, prng_bits},
-                      as_stream(stream), "float_quantize_stochastic");
+    const FpFmt f = make_fmt(man, exp, subnormals, saturate);
+    if (FullSr::supported(f))
+        return launch_map(in, out, n, FpStochastic<FullSr>{FullSr::make(f, prng_bits), rand}, as_stream(stream), "float_quantize_stochastic");
+    return launch_map(in, out, n, FpStochastic<SrExact>{SrExact{f, prng_bits}, rand}, as_stream(stream), "float_quantize_stochastic");
 }
 
 int mpt_float_quantize_stochastic_philox(const float* in, float* out, int64_t n, int man, int exp, int prng_bits,
                                          int subnormals, int saturate, uint64_t seed, void* stream) {
     MPT_REQUIRE(n >= 0 && (n == 0 || (in && out)), "float_quantize_stochastic_philox: null pointer or negative size");
     MPT_REQUIRE(valid_format(man, exp), "float_quantize_stochastic_philox: unsupported format man=%d exp=%d", man, exp);
-    return launch_map(in, out, n,
-                      FpStochasticPhilox{make_fmt(man, exp, subnormals, saturate), prng_bits, (uint32_t)seed,
-                                         (uint32_t)(seed >> 32)},
-                      as_stream(stream), "float_quantize_stochastic_philox");
+    const FpFmt f = make_fmt(man, exp, subnormals, saturate);
+    const uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
+    if (FullSr::supported(f))
+        return launch_map(in, out, n, FpStochasticPhilox<FullSr>{FullSr::make(f, prng_bits), k0, k1}, as_stream(stream),
+                          "float_quantize_stochastic_philox");
+    return launch_map(in, out, n, FpStochasticPhilox<SrExact>{SrExact{f, prng_bits}, k0, k1}, as_stream(stream),
+                      "float_quantize_stochastic_philox");
 }
 
 int mpt_binary8_quantize(const float* in, const int32_t* rand, float* out, int64_t n, int P, int is_signed,

@@ -120,3 +120,12 @@ HC_API int64_t hc_sweep_full_b8(int P, int is_signed, int policy, uint64_t first
     return sweep_all(first, count, stride, first_bad, [&](float x) { return full(x); },
                      [&](float x) { return cast_binary8(x, P, is_signed != 0, policy, true, RND_NEAREST, 0u, 0); });
 }
+
+// whole-domain stochastic rounding (FullSr) vs the exact caster, random word derived from the pattern
+HC_API int64_t hc_sweep_full_sr(int man, int exp, int sat, int rbits, uint64_t first, uint64_t count, uint64_t stride, uint32_t* first_bad) {
+    const FpFmt f = make_fmt(man, exp, 1, sat);
+    const FullSr full = FullSr::make(f, rbits);
+    auto word = [](float x) { uint32_t h = f2u(x) * 2654435761u; h ^= h >> 15; h *= 2246822519u; h ^= h >> 13; return h & 0x7FFFFFFFu; };
+    return sweep_all(first, count, stride, first_bad, [&](float x) { return full(x, word(x)); },
+                     [&](float x) { return cast_fp_stochastic(x, word(x), rbits, f); });
+}

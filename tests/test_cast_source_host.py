@@ -35,6 +35,8 @@ def hc():
     L.hc_sweep_full_rz.argtypes = [i32, i32, i32, u64, u64, u64, p]
     L.hc_sweep_full_b8.restype = i64
     L.hc_sweep_full_b8.argtypes = [i32, i32, i32, u64, u64, u64, p]
+    L.hc_sweep_full_sr.restype = i64
+    L.hc_sweep_full_sr.argtypes = [i32, i32, i32, i32, u64, u64, u64, p]
     L.hc_sweep_full_rn.restype = i64
     L.hc_sweep_full_rn.argtypes = [i32, i32, i32, u64, u64, u64, p]
     return L
@@ -158,3 +160,12 @@ def test_whole_domain_fast_truncation_equals_exact_cast(hc, fmt, sat):
 def test_whole_domain_fast_binary8_equals_exact_cast(hc, P, signed, policy):
     stride = 1 if (P, signed, policy) == (3, 1, 1) else 257      # BASELINE config 2's binary8 arm is swept exhaustively
     _sweep(hc.hc_sweep_full_b8, (P, signed, policy), stride, f"binary8 P={P} signed={signed} policy={policy}")
+
+
+@pytest.mark.parametrize("fmt", [(4, 3), (5, 2), (5, 10), (8, 7), (8, 0), (2, 1), (6, 21), (3, 0), (8, 23), (4, 23)])
+@pytest.mark.parametrize("sat", [0, 1])
+def test_whole_domain_fast_stochastic_equals_exact_cast(hc, fmt, sat):
+    e, m = fmt
+    for rbits in sorted({0, 23 - m, max(0, 10 - m)}):
+        _sweep(hc.hc_sweep_full_sr, (m, e, sat, rbits), 1 if (fmt == (4, 3) and rbits == 20) else 257,
+               f"stochastic e{e}m{m} sat={sat} rbits={rbits}")
