@@ -278,25 +278,39 @@ def main() -> int:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_ms = t.item() / e2e_steps
 
-    # ---- elementwise quantizer, HBM bound: 2^28 elements, e4m3 nearest (BASELINE config 2)
-    quant = None
+    # ---- elementwise quantizers, HBM bound: 2^28 elements of the BASELINE config 2 mixture
+    # (90% N(0,1), 5% N(0,1e-6), 5% U(-1e5,1e5)); e4m3 with subnormals and saturation; binary8 P=3
+    quant, quant_all = None, {}
     if rank == 0:
         del ah, bh
         n = 1 << args.quant_log2n
+        u = torch.rand(n, device=dev, generator=g)
         x = torch.randn(n, device=dev, generator=g)
-        for _ in range(3):
-            q = be.float_quantize_nearest(x, 3, 4, True, True)
-        torch.cuda.synchronize(dev)
-        q0, q1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        reps = 10
-        q0.record()
-        for _ in range(reps):
-            q = be.float_quantize_nearest(x, 3, 4, True, True)
-        q1.record()
-        torch.cuda.synchronize(dev)
-        qms = q0.elapsed_time(q1) / reps
-        quant = {"gbs": 8.0 * n / qms / 1e6, "ms": qms}
-        del x, q
+        x = torch.where(u < 0.90, x, torch.where(u < 0.95, x * 1e-3, (torch.rand(n, device=dev, generator=g) * 2 - 1) * 1e5))
+        del u
+        rnd = torch.randint_like(x, 2147483647, dtype=torch.int32)
+        legs = {
+            "nearest": (lambda: be.float_quantize_nearest(x, 3, 4, True, True), 8),
+            "truncate": (lambda: be.float_quantize_truncate(x, 3, 4, True, True), 8),
+            "stochastic_given_words": (lambda: be.float_quantize_stochastic(x, 3, 4, 20, True, True, rand=rnd), 12),
+            "stochastic_philox": (lambda: be.float_quantize_stochastic(x, 3, 4, 20, True, True, seed=1), 8),
+            "binary8_p3_nearest": (lambda: be.binary8_quantize_nearest(x, 3, True, 1, True), 8),
+        }
+        for name, (fn, bytes_per) in legs.items():
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize(dev)
+            q0, q1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps = 10
+            q0.record()
+            for _ in range(reps):
+                fn()
+            q1.record()
+            torch.cuda.synchronize(dev)
+            qms = q0.elapsed_time(q1) / reps
+            quant_all[name] = {"gbs": bytes_per * n / qms / 1e6, "ms": qms, "bytes_per_element": bytes_per}
+        quant = quant_all["nearest"]
+        del x, rnd
 
     if rank == 0:
         peaks = {}
@@ -327,7 +341,8 @@ def main() -> int:
                                  % (sms, clk, I_MAC)},
             "roofline_quantize": {"bound": "hbm", "achieved": quant["gbs"], "peak": hbm_peak, "unit": "GB/s",
                                   "frac": quant["gbs"] / hbm_peak, "traffic": None, "peak_source": peak_src,
-                                  "kernel": "float_quantize_nearest e4m3, 2^%d elements, 8 B/element" % args.quant_log2n},
+                                  "kernel": "float_quantize_nearest e4m3, 2^%d elements, 8 B/element" % args.quant_log2n,
+                                  "all_kernels_gbs": {k: round(v["gbs"], 1) for k, v in quant_all.items()}},
         }
         if world == 1 and not args.no_cpu_baseline:
             try:

@@ -71,7 +71,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if force or procs or _stale(LIB, objs):
         # the CUDA runtime is linked statically (nvcc's default), so the library does not depend on
         # which libcudart the host process happens to have loaded
-        cmd = [_nvcc(), "-shared", "-Wno-deprecated-gpu-targets", "-o", LIB] + objs
+        cmd = [_nvcc(), "-shared", "-Wno-deprecated-gpu-targets", "-Xlinker", "-soname=libmptorch_b200.so", "-o", LIB] + objs
         subprocess.check_call(cmd)
     return LIB
 
