@@ -165,6 +165,71 @@ def run_reference(args) -> int:
     return 0
 
 
+# ----------------------------------------------------------------------------------- config 5: training step
+def run_block(args) -> int:
+    """One quantized GPT-2-small block (d=768, 12 heads, MLP 3072, seq 1024, batch 8 per GPU), forward + backward,
+    gradients averaged over the ranks with bucketed NCCL all-reduces.  Weak scaling: the per-GPU batch is fixed."""
+    import torch
+    import torch.distributed as dist
+
+    from mptorch_b200.gpt2_block import BlockConfig, QTinyGPT
+    from mptorch_b200.parallel import allreduce_gradients
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    B, T = 8, 1024
+    torch.manual_seed(0)                                   # identical random-init weights on every rank
+    model = QTinyGPT(BlockConfig(seq_len=T)).to(dev)
+    g = torch.Generator().manual_seed(1000 + rank)
+    idx_host = torch.randint(0, 50257, (B, T), generator=g).pin_memory()     # synthetic uniform token ids
+
+    def step():
+        idx = idx_host.to(dev, non_blocking=True)
+        model.zero_grad(set_to_none=True)
+        loss = model(idx).float().pow(2).mean()
+        loss.backward()
+        allreduce_gradients(model.parameters())
+        return loss
+
+    warmup = max(args.warmup, 3)
+    for _ in range(warmup):
+        step()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        loss = step()
+        loss_host = loss.item()                            # device -> host read of the step's result
+    e1.record()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize(dev)
+    t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = t.item() / args.steps
+    if rank == 0:
+        macs = model.macs_per_step(B, T) * world
+        v = macs / ms / 1e6
+        print(json.dumps({
+            "metric": "GPT-2-small block training step, simulated GMAC/s", "value": v, "unit": "GMAC/s", "n_gpus": world,
+            "steps": args.steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32 (MACs rounded: add e5m10, mul e4m3)", "data": "synthetic",
+            "config": {"workload": "QLinear/QLayerNorm/QSoftmax block d=768 h=12 mlp=3072 seq=1024 batch=8 per GPU, fwd+bwd, "
+                                   "DP gradient all-reduce", "loss": loss_host},
+            "e2e": {"value": v, "unit": "GMAC/s", "h2d_bytes_per_step": B * T * 8, "d2h_bytes_per_step": 4, "ms_per_step": ms}}))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
 # ----------------------------------------------------------------------------------- GPU arm
 def main() -> int:
     ap = argparse.ArgumentParser()
@@ -176,9 +241,14 @@ def main() -> int:
     ap.add_argument("--order", default="cuda", choices=["cuda", "seq"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--quant-log2n", type=int, default=28, help="log2 of the quantizer leg's element count")
+    ap.add_argument("--workload", default="mm", choices=["mm", "block"],
+                    help="mm: the headline float_mm (default); block: BASELINE config 5, one GPT-2-small-shaped block, "
+                         "fwd+bwd with (add e5m10, mul e4m3) MACs, data parallel with a gradient all-reduce")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    if args.workload == "block":
+        return run_block(args)
 
     import torch
     import torch.distributed as dist

@@ -49,24 +49,82 @@ __device__ __forceinline__ float tree64(float p0, float p1, Op op) {
     return __shfl_sync(0xFFFFFFFFu, r, 0);
 }
 
+// Nearest rounding to one format.  Formats the FP-pipe rounding supports (subnormals on, man <= 21) take
+// FullRn, which equals the exact caster on every input at about a third of the instructions; the rest
+// take the exact caster.  The choice is uniform across the launch.
+struct Caster {
+    FullRn fast;
+    int use_fast;
+    __host__ static Caster make(const FpFmt& f) {
+        Caster c;
+        c.fast = FullRn::make(f);
+        c.use_fast = fast_rn_supported(f) ? 1 : 0;
+        return c;
+    }
+    __device__ __forceinline__ float operator()(float x) const { return use_fast ? fast(x) : cast_fp_nearest(x, fast.fmt); }
+};
+__device__ __forceinline__ float cast_fp_nearest(float x, const Caster& c) { return c(x); }
+
 struct QAdd {
-    FpFmt f;
-    __device__ __forceinline__ float operator()(float a, float b) const { return cast_fp_nearest(__fadd_rn(a, b), f); }
+    Caster f;
+    __device__ __forceinline__ float operator()(float a, float b) const { return f(__fadd_rn(a, b)); }
+};
+
+// Eight sequential rounded additions acc = Q(acc + v[u]).  When the running sum provably stays inside the
+// range where the 4-instruction FP-pipe rounding is exact, the chain uses it (a dependent step is then
+// about 20 cycles instead of about 150), otherwise the exact caster.
+struct SeqAdder {
+    Caster q;
+    FastRn r;
+    float top;        // 2^(limit exponent + 1): every intermediate |sum| must stay below
+    float growth8;    // bound of (1 + 2^-(man+1))^8
+    int chain_ok;     // format supports the fast chain
+    int exp8;         // 8-bit exponent: tiny values need the exact caster (see FullRn)
+    __host__ static SeqAdder make(const FpFmt& f) {
+        SeqAdder s;
+        s.q = Caster::make(f);
+        s.r = FastRn::make(f);
+        s.top = ldexpf(1.0f, fast_rn_exp_limit(f) + 1);
+        double g = 1.0;
+        for (int i = 0; i < 8; ++i) g *= 1.0 + ldexp(1.0, -(f.man + 1));
+        s.growth8 = (float)(g * 1.0001);
+        s.chain_ok = fast_rn_supported(f) ? 1 : 0;
+        s.exp8 = f.exp == 8;
+        return s;
+    }
+    template <int U>
+    __device__ __forceinline__ float add(float acc, const float (&v)[U]) const {
+        float vmax = 0.f;
+        bool tiny = false;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            vmax = fmaxf(vmax, fabsf(v[u]));
+            tiny |= (__float_as_uint(v[u]) & 0x7FFFFFFFu) - 1u < 0x0CFFFFFFu;     // 0 < |v| < 2^-101
+        }
+        tiny |= (__float_as_uint(acc) & 0x7FFFFFFFu) - 1u < 0x0CFFFFFFu;
+        const bool fast = chain_ok && (fabsf(acc) + (float)U * vmax) * growth8 < top && !(exp8 && tiny);
+        if (fast) {
+#pragma unroll
+            for (int u = 0; u < U; ++u) acc = r(__fadd_rn(acc, v[u]));
+        } else {
+#pragma unroll
+            for (int u = 0; u < U; ++u) acc = q(__fadd_rn(acc, v[u]));
+        }
+        return acc;
+    }
 };
 struct FMax {
     __device__ __forceinline__ float operator()(float a, float b) const { return fmaxf(a, b); }
 };
 struct QLse {
-    FpFmt f;
-    __device__ __forceinline__ float operator()(float a, float b) const {
-        return cast_fp_nearest(logf(__fadd_rn(expf(a), expf(b))), f);
-    }
+    Caster f;
+    __device__ __forceinline__ float operator()(float a, float b) const { return f(logf(__fadd_rn(expf(a), expf(b)))); }
 };
 
 // ----------------------------------------------------------------------------------------- softmax
 template <bool TREE>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32) softmax_fwd_kernel(const float* __restrict__ in, float* __restrict__ out,
-                                                                         RowGeom g, FpFmt fexp, FpFmt foff, FpFmt facc) {
+                                                                         RowGeom g, Caster fexp, Caster foff, Caster facc) {
     const QAdd qadd{facc};
     if (TREE) {
         const int lane = threadIdx.x & 31;
@@ -116,7 +174,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) softmax_fwd_kernel(const 
 
 template <bool TREE>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32) softmax_lse_fwd_kernel(const float* __restrict__ in, float* __restrict__ out,
-                                                                             RowGeom g, FpFmt foff, FpFmt flse) {
+                                                                             RowGeom g, Caster foff, Caster flse) {
     const QLse qlse{flse};
     if (TREE) {
         const int lane = threadIdx.x & 31;
@@ -167,7 +225,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) softmax_lse_fwd_kernel(co
 
 template <bool TREE>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32) softmax_bwd_kernel(const float* __restrict__ yv, const float* __restrict__ gv,
-                                                                         float* __restrict__ out, RowGeom g, FpFmt fadd, FpFmt fmul) {
+                                                                         float* __restrict__ out, RowGeom g, Caster fadd, Caster fmul) {
     const QAdd qadd{fadd};
     const int C = g.channel;
     const int64_t st = g.inner;
@@ -198,7 +256,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) softmax_bwd_kernel(const 
 }
 
 // ----------------------------------------------------------------------------------------- layernorm
-struct LnFmt { FpFmt acc, mul, div, sqrt; };
+struct LnFmt { Caster acc, mul, div, sqrt; SeqAdder seq; };
 
 template <bool TREE>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32) layernorm_fwd_kernel(const float* __restrict__ in, const float* __restrict__ w,
@@ -321,62 +379,94 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) layernorm_bwd_dx_kernel(c
     }
 }
 
-// Weight and bias gradients: per channel, a sequential rounded sum over rows 0..R-1 (the order of
-// both references).  One thread per channel; consecutive threads read consecutive channels, so each
-// row is read coalesced.  x-hat * dy is recomputed from the inputs rather than staged through a
-// scratch tensor as the reference does (layernorm_kernel.h:189, fp_kernel.cu:481-487): same values,
-// one tensor less written and read.
-__global__ void __launch_bounds__(128) layernorm_bwd_params_kernel(const float* __restrict__ in, const float* __restrict__ gout,
-                                                                   const float* __restrict__ mean, const float* __restrict__ rstd,
-                                                                   float* __restrict__ ggamma, float* __restrict__ gbeta, RowGeom g, LnFmt f) {
-    const int k = blockIdx.x * blockDim.x + threadIdx.x;
-    if (k >= g.channel) return;
-    const QAdd qacc{f.acc};
-    const int64_t st = g.inner;
-    float gg = 0.f, gb = 0.f;
-    constexpr int U = 8;
-    int64_t row = 0;
-    for (; row + U <= g.rows; row += U) {
-        float xv[U], gv[U], mv[U], rv[U];
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int64_t idx = row_base(g, row + u) + k * st;
-            xv[u] = in[idx]; gv[u] = gout[idx]; mv[u] = mean[row + u]; rv[u] = rstd[row + u];
-        }
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const float xhat = cast_fp_nearest(__fmul_rn(cast_fp_nearest(__fsub_rn(xv[u], mv[u]), f.acc), rv[u]), f.mul);
-            gg = qacc(gg, cast_fp_nearest(__fmul_rn(xhat, gv[u]), f.mul));
-            gb = qacc(gb, gv[u]);
-        }
-    }
-    for (; row < g.rows; ++row) {
-        const int64_t idx = row_base(g, row) + k * st;
-        const float xhat = cast_fp_nearest(__fmul_rn(cast_fp_nearest(__fsub_rn(in[idx], mean[row]), f.acc), rstd[row]), f.mul);
-        gg = qacc(gg, cast_fp_nearest(__fmul_rn(xhat, gout[idx]), f.mul));
-        gb = qacc(gb, gout[idx]);
-    }
-    ggamma[k] = gg;
-    gbeta[k] = gb;
-}
+// Column sums in row order: out[c] = fold over rows r = 0..R-1 of Q(acc + v[r, c]), the association of both
+// references for the layernorm weight/bias gradients (layernorm_kernel.h:206-237, layernorm.h:100-103) and of
+// the qsum loop (functional.py:736-748).  The chain per column is serial by definition, so the kernel splits
+// the work by role: a CTA owns 32 columns; eight producer warps stream row tiles (64 rows x 32 columns,
+// coalesced 128-byte row segments), do the per-element arithmetic that does not depend on the running sum
+// (for layernorm: x-hat * dy, recomputed from the inputs instead of staged through the reference's scratch
+// tensor, fp_kernel.cu:481-487) and park the addends in shared memory; one consumer warp (lane = column)
+// walks the parked tile in row order through the rounded adds.  Tiles are double buffered: the consumer
+// works on tile t while the producers fetch tile t + 1, with one barrier per tile.
+constexpr int kColTile = 32;        // columns per CTA
+constexpr int kRowTile = 64;        // rows per tile (two buffers of two tensors stay within 48 KB of static shared memory)
+constexpr int kProducerWarps = 8;
+constexpr int kColsumThreads = (kProducerWarps + 1) * 32;
 
-// Sequential rounded column sums of a [rows, cols] matrix: out[c] = fold_r Q(acc + x[r, c]), acc0 = 0.
-__global__ void __launch_bounds__(128) qsum_rows_kernel(const float* __restrict__ in, float* __restrict__ out, int64_t rows, int64_t cols, FpFmt f) {
-    const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= cols) return;
-    const QAdd q{f};
-    float acc = 0.f;
-    constexpr int U = 8;
-    int64_t r = 0;
-    for (; r + U <= rows; r += U) {
-        float v[U];
+// MODE 0: layernorm parameter gradients (two chains: x-hat*dy -> out0, dy -> out1).  MODE 1: plain column sum of `in`.
+template <int MODE>
+__global__ void __launch_bounds__(kColsumThreads) colsum_kernel(const float* __restrict__ in, const float* __restrict__ gout,
+                                                                const float* __restrict__ mean, const float* __restrict__ rstd,
+                                                                float* __restrict__ out0, float* __restrict__ out1, RowGeom g,
+                                                                Caster facc, Caster fmul, SeqAdder seq) {
+    __shared__ float sA[2][kRowTile][kColTile];
+    __shared__ float sB[MODE == 0 ? 2 : 1][MODE == 0 ? kRowTile : 1][kColTile];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int col = blockIdx.x * kColTile + lane;
+    const bool col_ok = col < g.channel;
+    const int64_t st = g.inner;
+    const int64_t ntiles = (g.rows + kRowTile - 1) / kRowTile;
+
+    auto produce = [&](int64_t t) {      // producer warps: rows warp, warp + 8, ... of the tile
+        const int buf = (int)(t & 1);
+        const int64_t r0 = t * kRowTile;
+        constexpr int PER = kRowTile / kProducerWarps;     // rows per producer warp, in batches of 8
 #pragma unroll
-        for (int u = 0; u < U; ++u) v[u] = in[(r + u) * cols + c];
+        for (int h = 0; h < PER / 8; ++h) {
+            float xv[8], gv[8], mv[8], rv[8];
 #pragma unroll
-        for (int u = 0; u < U; ++u) acc = q(acc, v[u]);
+            for (int u = 0; u < 8; ++u) {
+                const int lr = warp * PER + h * 8 + u;
+                const int64_t row = r0 + lr;
+                const bool ok = col_ok && row < g.rows;
+                const int64_t idx = ok ? row_base(g, row) + col * st : 0;
+                xv[u] = ok ? in[idx] : 0.f;
+                if (MODE == 0) { gv[u] = ok ? gout[idx] : 0.f; mv[u] = ok ? mean[row] : 0.f; rv[u] = ok ? rstd[row] : 0.f; }
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int lr = warp * PER + h * 8 + u;
+                if (MODE == 0) {
+                    const float xhat = fmul(__fmul_rn(facc(__fsub_rn(xv[u], mv[u])), rv[u]));
+                    sA[buf][lr][lane] = fmul(__fmul_rn(xhat, gv[u]));
+                    sB[buf][lr][lane] = gv[u];
+                } else {
+                    sA[buf][lr][lane] = xv[u];
+                }
+            }
+        }
+    };
+
+    float acc0 = 0.f, acc1 = 0.f;
+    if (warp < kProducerWarps && ntiles > 0) produce(0);
+    __syncthreads();
+    for (int64_t t = 0; t < ntiles; ++t) {
+        if (warp < kProducerWarps) {
+            if (t + 1 < ntiles) produce(t + 1);
+        } else {
+            const int buf = (int)(t & 1);
+            const int64_t left = g.rows - t * kRowTile;
+            const int nrows = left < kRowTile ? (int)left : kRowTile;
+            int r = 0;
+            for (; r + 8 <= nrows; r += 8) {
+                float a[8], b[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) { a[u] = sA[buf][r + u][lane]; if (MODE == 0) b[u] = sB[buf][r + u][lane]; }
+                acc0 = seq.add(acc0, a);
+                if (MODE == 0) acc1 = seq.add(acc1, b);
+            }
+            for (; r < nrows; ++r) {
+                const float a[1] = {sA[buf][r][lane]};
+                acc0 = seq.add(acc0, a);
+                if (MODE == 0) { const float b[1] = {sB[buf][r][lane]}; acc1 = seq.add(acc1, b); }
+            }
+        }
+        __syncthreads();
     }
-    for (; r < rows; ++r) acc = q(acc, in[r * cols + c]);
-    out[c] = acc;
+    if (warp == kProducerWarps && col_ok) {
+        out0[col] = acc0;
+        if (MODE == 0) out1[col] = acc1;
+    }
 }
 
 int check_geom(const char* who, int64_t outer, int channel, int64_t inner) {
@@ -406,8 +496,8 @@ int mpt_float_softmax_forward(const float* in, float* out, int64_t outer, int ch
     const RowGeom g{outer * inner, channel, inner};
     if (g.rows == 0 || channel == 0) return MPT_OK;
     MPT_REQUIRE(in && out, "softmax_forward: null pointer");
-    const FpFmt fe = make_fmt(man_exp, exp_exp, subnormals, saturate), fo = make_fmt(man_off, exp_off, subnormals, saturate),
-                fa = make_fmt(man_acc, exp_acc, subnormals, saturate);
+    const Caster fe = Caster::make(make_fmt(man_exp, exp_exp, subnormals, saturate)), fo = Caster::make(make_fmt(man_off, exp_off, subnormals, saturate)),
+                 fa = Caster::make(make_fmt(man_acc, exp_acc, subnormals, saturate));
     const bool tree = order != MPT_ORDER_SEQ;
     if (tree) softmax_fwd_kernel<true><<<row_blocks(g.rows, true), kWarpsPerBlock * 32, 0, as_stream(stream)>>>(in, out, g, fe, fo, fa);
     else softmax_fwd_kernel<false><<<row_blocks(g.rows, false), kWarpsPerBlock * 32, 0, as_stream(stream)>>>(in, out, g, fe, fo, fa);
@@ -423,7 +513,7 @@ int mpt_float_softmax_lse_forward(const float* in, float* out, int64_t outer, in
     const RowGeom g{outer * inner, channel, inner};
     if (g.rows == 0 || channel == 0) return MPT_OK;
     MPT_REQUIRE(in && out, "softmax_lse_forward: null pointer");
-    const FpFmt fo = make_fmt(man_off, exp_off, subnormals, saturate), fl = make_fmt(man_lse, exp_lse, subnormals, saturate);
+    const Caster fo = Caster::make(make_fmt(man_off, exp_off, subnormals, saturate)), fl = Caster::make(make_fmt(man_lse, exp_lse, subnormals, saturate));
     const bool tree = order != MPT_ORDER_SEQ;
     if (tree) softmax_lse_fwd_kernel<true><<<row_blocks(g.rows, true), kWarpsPerBlock * 32, 0, as_stream(stream)>>>(in, out, g, fo, fl);
     else softmax_lse_fwd_kernel<false><<<row_blocks(g.rows, false), kWarpsPerBlock * 32, 0, as_stream(stream)>>>(in, out, g, fo, fl);
@@ -439,7 +529,7 @@ int mpt_float_softmax_backward(const float* y, const float* grad, float* out, in
     const RowGeom g{outer * inner, channel, inner};
     if (g.rows == 0 || channel == 0) return MPT_OK;
     MPT_REQUIRE(y && grad && out, "softmax_backward: null pointer");
-    const FpFmt fa = make_fmt(man_add, exp_add, subnormals, saturate), fm = make_fmt(man_mul, exp_mul, subnormals, saturate);
+    const Caster fa = Caster::make(make_fmt(man_add, exp_add, subnormals, saturate)), fm = Caster::make(make_fmt(man_mul, exp_mul, subnormals, saturate));
     const bool tree = order != MPT_ORDER_SEQ;
     if (tree) softmax_bwd_kernel<true><<<row_blocks(g.rows, true), kWarpsPerBlock * 32, 0, as_stream(stream)>>>(y, grad, out, g, fa, fm);
     else softmax_bwd_kernel<false><<<row_blocks(g.rows, false), kWarpsPerBlock * 32, 0, as_stream(stream)>>>(y, grad, out, g, fa, fm);
@@ -458,8 +548,10 @@ int mpt_float_layernorm_forward(const float* in, const float* weight, const floa
     if (g.rows == 0) return MPT_OK;
     MPT_REQUIRE(channel > 0, "layernorm_forward: empty normalised shape");
     MPT_REQUIRE(in && weight && bias && out && mean && rstd, "layernorm_forward: null pointer");
-    const LnFmt f{make_fmt(man_acc, exp_acc, subnormals, saturate), make_fmt(man_mul, exp_mul, subnormals, saturate),
-                  make_fmt(man_div, exp_div, subnormals, saturate), make_fmt(man_sqrt, exp_sqrt, subnormals, saturate)};
+    const FpFmt facc = make_fmt(man_acc, exp_acc, subnormals, saturate);
+    const LnFmt f{Caster::make(facc), Caster::make(make_fmt(man_mul, exp_mul, subnormals, saturate)),
+                  Caster::make(make_fmt(man_div, exp_div, subnormals, saturate)), Caster::make(make_fmt(man_sqrt, exp_sqrt, subnormals, saturate)),
+                  SeqAdder::make(facc)};
     const bool tree = order != MPT_ORDER_SEQ;
     if (tree) layernorm_fwd_kernel<true><<<row_blocks(g.rows, true), kWarpsPerBlock * 32, 0, as_stream(stream)>>>(in, weight, bias, out, mean, rstd, eps, g, f);
     else layernorm_fwd_kernel<false><<<row_blocks(g.rows, false), kWarpsPerBlock * 32, 0, as_stream(stream)>>>(in, weight, bias, out, mean, rstd, eps, g, f);
@@ -477,8 +569,9 @@ int mpt_float_layernorm_backward(const float* in, const float* grad_out, const f
     const RowGeom g{outer * inner, channel, inner};
     if (channel == 0) return MPT_OK;
     MPT_REQUIRE(grad_gamma && grad_beta, "layernorm_backward: null pointer");
-    const FpFmt fm = make_fmt(man_mul, exp_mul, subnormals, saturate);
-    const LnFmt f{make_fmt(man_acc, exp_acc, subnormals, saturate), fm, make_fmt(man_div, exp_div, subnormals, saturate), fm};
+    const FpFmt facc = make_fmt(man_acc, exp_acc, subnormals, saturate);
+    const Caster fm = Caster::make(make_fmt(man_mul, exp_mul, subnormals, saturate));
+    const LnFmt f{Caster::make(facc), fm, Caster::make(make_fmt(man_div, exp_div, subnormals, saturate)), fm, SeqAdder::make(facc)};
     if (g.rows > 0) {
         MPT_REQUIRE(in && grad_out && weight && mean && rstd && grad_in, "layernorm_backward: null pointer");
         const bool tree = order != MPT_ORDER_SEQ;
@@ -487,7 +580,8 @@ int mpt_float_layernorm_backward(const float* in, const float* grad_out, const f
         rc = check_launch("layernorm_backward (input gradient)");
         if (rc) return rc;
     }
-    layernorm_bwd_params_kernel<<<(channel + 127) / 128, 128, 0, as_stream(stream)>>>(in, grad_out, mean, rstd, grad_gamma, grad_beta, g, f);
+    colsum_kernel<0><<<(channel + kColTile - 1) / kColTile, kColsumThreads, 0, as_stream(stream)>>>(in, grad_out, mean, rstd, grad_gamma, grad_beta, g,
+                                                                                               f.acc, f.mul, f.seq);
     return check_launch("layernorm_backward (parameter gradients)");
 }
 
@@ -497,7 +591,11 @@ int mpt_qsum_rows(const float* in, float* out, int64_t rows, int64_t cols, int m
     MPT_REQUIRE(valid_format(man, exp), "qsum_rows: unsupported format");
     if (cols == 0) return MPT_OK;
     MPT_REQUIRE(out && (rows == 0 || in), "qsum_rows: null pointer");
-    qsum_rows_kernel<<<(unsigned)((cols + 127) / 128), 128, 0, as_stream(stream)>>>(in, out, rows, cols, make_fmt(man, exp, subnormals, saturate));
+    const FpFmt f = make_fmt(man, exp, subnormals, saturate);
+    MPT_REQUIRE(cols <= 0x7FFFFFFF, "qsum_rows: too many columns");
+    const RowGeom g{rows, (int)cols, 1};      // a [rows, cols] matrix: outer = rows, channel = cols, inner = 1
+    colsum_kernel<1><<<(unsigned)((cols + kColTile - 1) / kColTile), kColsumThreads, 0, as_stream(stream)>>>(in, nullptr, nullptr, nullptr, out, nullptr, g,
+                                                                                                        Caster::make(f), Caster::make(f), SeqAdder::make(f));
     return check_launch("qsum_rows");
 }
 
