@@ -30,9 +30,11 @@ sys.path.insert(0, ROOT)
 SIZE = 8192
 FMT = dict(man_add=2, exp_add=5, man_mul=2, exp_mul=5, subnormals=True, saturate=False)
 # Issued thread-instructions per MAC of the GEMM kernel's fast path, measured with ncu
-# (smsp__thread_inst_executed.sum / MACs; see profiles/).  The issue-rate roofline is
-# SMs x 128 lanes x SM clock / I_MAC.
-I_MAC = 11.22
+# (smsp__inst_executed.sum x 32 / MACs; see profiles/).  The issue-rate roofline is
+# SMs x 128 lanes x SM clock / I_MAC.  Of those instructions ALU_MAC run on the half-rate ALU pipe
+# (64 lanes per SM per clock), which is the tighter bound of the two and is reported alongside.
+I_MAC = 8.11
+ALU_MAC = 4.4
 METRIC = "float_mm GMAC/s (8192^3, e5m2 RN)"
 
 
@@ -407,8 +409,10 @@ def main() -> int:
             "gpu_launches": 4 * args.steps,
             "roofline": {"bound": "issue", "achieved": achieved, "peak": issue_peak, "unit": "GMAC/s",
                          "frac": achieved / issue_peak, "traffic": None,
-                         "note": "CUDA-core issue roofline: %d SMs x 128 lanes x %.0f MHz / %.1f instructions per MAC"
-                                 % (sms, clk, I_MAC)},
+                         "alu_pipe_peak": sms * 64 * clk * 1e6 / ALU_MAC / 1e9,
+                         "note": "CUDA-core issue roofline: %d SMs x 128 lanes x %.0f MHz / %.2f instructions per MAC; "
+                                 "alu_pipe_peak = %d SMs x 64 ALU lanes x clock / %.1f ALU instructions per MAC"
+                                 % (sms, clk, I_MAC, sms, ALU_MAC)},
             "roofline_quantize": {"bound": "hbm", "achieved": quant["gbs"], "peak": hbm_peak, "unit": "GB/s",
                                   "frac": quant["gbs"] / hbm_peak, "traffic": None, "peak_source": peak_src,
                                   "kernel": "float_quantize_nearest e4m3, 2^%d elements, 8 B/element" % args.quant_log2n,
