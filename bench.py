@@ -167,6 +167,71 @@ def run_reference(args) -> int:
     return 0
 
 
+# ----------------------------------------------------------------------------------- HBM-bound kernels
+def run_kernels(args) -> int:
+    """Throughput of the HBM-bound kernels at BASELINE sizes: MX / NVFP4 on 16384 x 16384 (config 3), softmax rows of
+    1024 and layernorm rows of 768 at the config 5 tensor sizes.  `--size` scales the row counts (default 8192 = full)."""
+    import torch
+
+    import mptorch_b200.quant as q
+
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    scale = args.size / 8192.0
+    g = torch.Generator(device=dev).manual_seed(7)
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    hbm_peak = peaks.get("hbm_gbs", 6650.0)
+    out = {}
+
+    def timed(name, fn, nbytes):
+        for _ in range(max(args.warmup, 3)):
+            fn()
+        torch.cuda.synchronize(dev)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(args.steps):
+            fn()
+        b.record()
+        torch.cuda.synchronize(dev)
+        ms = a.elapsed_time(b) / args.steps
+        out[name] = {"ms": round(ms, 4), "gbs": round(nbytes / ms / 1e6, 1), "frac_of_hbm_peak": round(nbytes / ms / 1e6 / hbm_peak, 3),
+                     "algorithmic_bytes": nbytes}
+
+    n = int(16384 * scale)
+    x = torch.randn(n, 16384, device=dev, generator=g) * (10.0 ** (torch.rand(n, 1, device=dev, generator=g) * 6 - 3))
+    e = x.numel()
+    timed("mxfp8_e4m3_block32", lambda: q.mx_quantize(x, "e4m3", 32), 8 * e)
+    timed("mxfp4_e2m1_block32", lambda: q.mx_quantize(x, "e2m1", 32), 8 * e)
+    gs = float(x.abs().max().item() / (448.0 * 6.0))
+    timed("nvfp4_given_tensor_scale", lambda: q.nvfp4_quantize(x, gs), 8 * e)
+    timed("nvfp4_computed_tensor_scale", lambda: q.nvfp4_quantize(x), 12 * e)
+    del x
+    rows = int(8 * 12 * 1024 * scale)
+    att = torch.randn(rows, 1024, device=dev, generator=g) * 3
+    gy = torch.randn(rows, 1024, device=dev, generator=g)
+    e = att.numel()
+    timed("softmax_fwd_e5m10_rows1024", lambda: q.float_softmax_forward(att, -1, 10, 5, 10, 5, 10, 5), 8 * e)
+    timed("softmax_lse_fwd_e5m10_rows1024", lambda: q.float_softmax_lse_forward(att, -1, 10, 5, 10, 5), 8 * e)
+    y = q.float_softmax_forward(att, -1, 10, 5, 10, 5, 10, 5)
+    timed("softmax_bwd_e5m10_rows1024", lambda: q.float_softmax_backward(y, gy, -1, 10, 5, 10, 5), 12 * e)
+    del att, gy, y
+    rows = int(8192 * 8 * scale)      # 8 layernorm-sized tensors' worth of rows so the tensor exceeds L2
+    xl = torch.randn(rows, 768, device=dev, generator=g)
+    gl = torch.randn(rows, 768, device=dev, generator=g)
+    w, b = torch.randn(768, device=dev, generator=g), torch.randn(768, device=dev, generator=g)
+    e = xl.numel()
+    timed("layernorm_fwd_e5m10_rows768", lambda: q.float_layernorm_forward(xl, w, b, 1e-5, [-1], 10, 5, 10, 5, 10, 5, 10, 5), 8 * e)
+    _, mean, rstd = q.float_layernorm_forward(xl, w, b, 1e-5, [-1], 10, 5, 10, 5, 10, 5, 10, 5)
+    timed("layernorm_bwd_e5m10_rows768", lambda: q.float_layernorm_backward(xl, gl, w, b, mean, rstd, [-1], 10, 5, 10, 5, 10, 5), 20 * e)
+    print(json.dumps({"metric": "HBM-bound kernels, GB/s at algorithmic bytes", "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+                      "hbm_peak_gbs": hbm_peak, "kernels": out}))
+    return 0
+
+
 # ----------------------------------------------------------------------------------- config 5: training step
 def run_block(args) -> int:
     """One quantized GPT-2-small block (d=768, 12 heads, MLP 3072, seq 1024, batch 8 per GPU), forward + backward,
@@ -243,7 +308,7 @@ def main() -> int:
     ap.add_argument("--order", default="cuda", choices=["cuda", "seq"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--quant-log2n", type=int, default=28, help="log2 of the quantizer leg's element count")
-    ap.add_argument("--workload", default="mm", choices=["mm", "block"],
+    ap.add_argument("--workload", default="mm", choices=["mm", "block", "kernels"],
                     help="mm: the headline float_mm (default); block: BASELINE config 5, one GPT-2-small-shaped block, "
                          "fwd+bwd with (add e5m10, mul e4m3) MACs, data parallel with a gradient all-reduce")
     args = ap.parse_args()
@@ -251,6 +316,8 @@ def main() -> int:
         return run_reference(args)
     if args.workload == "block":
         return run_block(args)
+    if args.workload == "kernels":
+        return run_kernels(args)
 
     import torch
     import torch.distributed as dist
