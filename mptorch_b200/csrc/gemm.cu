@@ -164,21 +164,29 @@ __device__ __forceinline__ float mac_fast(float acc, float a, float b, const Fas
 // FP-pipe instructions of a MAC are shared by two neighbouring outputs, so a MAC costs 3 packed FP
 // instructions + 4 ALU instructions (the exponent extraction stays per element) = 7 issue slots
 // instead of 10.  Each half of a packed instruction rounds exactly like its scalar form.
+//
+// GUARD = false drops the clamp of the exponent at the format's smallest normal binade (one IMNMX per
+// element).  That is exact for the SUM rounding whenever the multiply format's smallest subnormal is
+// not finer than the add format's: every product and every partial sum is then a multiple of the add
+// format's smallest subnormal, so a sum that lands in the add format's subnormal range has no bits
+// below that quantum and rounding it at its own exponent leaves it unchanged, exactly like the
+// clamped rounding (a zero sum gives m = 0 and comes out as +0).
+template <bool GUARD>
 __device__ __forceinline__ float2 fast_rn2(const FastRn& r, float2 x) {
-    const int e0 = max(__float_as_int(x.x) & 0x7F800000, r.min_e_bits);
-    const int e1 = max(__float_as_int(x.y) & 0x7F800000, r.min_e_bits);
+    int e0 = __float_as_int(x.x) & 0x7F800000, e1 = __float_as_int(x.y) & 0x7F800000;
+    if (GUARD) { e0 = max(e0, r.min_e_bits); e1 = max(e1, r.min_e_bits); }
     const float2 m = make_float2(__int_as_float(e0), __int_as_float(e1));
     const float2 y = __ffma2_rn(m, make_float2(r.k, r.k), x);
     return __ffma2_rn(m, make_float2(-r.k, -r.k), y);
 }
-template <bool FMA>
+template <bool FMA, bool ADDG>
 __device__ __forceinline__ float2 mac_fast2(float2 acc, float2 a2, float2 b2, const FastRn& radd, const FastRn& rmul) {
-    if (FMA) return fast_rn2(radd, __ffma2_rn(a2, b2, acc));
-    return fast_rn2(radd, __fadd2_rn(acc, fast_rn2(rmul, __fmul2_rn(a2, b2))));
+    if (FMA) return fast_rn2<true>(radd, __ffma2_rn(a2, b2, acc));
+    return fast_rn2<ADDG>(radd, __fadd2_rn(acc, fast_rn2<true>(rmul, __fmul2_rn(a2, b2))));
 }
 
 // `nk` (1..8) accumulation steps starting at slab row kbase, for the thread's 8x4 outputs.
-template <bool FMA, bool FAST, bool PACKED>
+template <bool FMA, bool FAST, bool PACKED, bool ADDG>
 __device__ __forceinline__ void group_steps(float (&acc)[TM][TN], const float* As, const float* Bs, int kbase, int nk,
                                             int ty, int tx, const MmParams& p) {
     if (FAST && nk == 8) {
@@ -196,8 +204,8 @@ __device__ __forceinline__ void group_steps(float (&acc)[TM][TN], const float* A
                     const float a = j == 0 ? av[i].x : j == 1 ? av[i].y : j == 2 ? av[i].z : av[i].w;
                     if (PACKED) {
                         const float2 a2 = make_float2(a, a);
-                        const float2 lo = mac_fast2<FMA>(make_float2(acc[i][0], acc[i][1]), a2, make_float2(bv.x, bv.y), p.radd, p.rmul);
-                        const float2 hi = mac_fast2<FMA>(make_float2(acc[i][2], acc[i][3]), a2, make_float2(bv.z, bv.w), p.radd, p.rmul);
+                        const float2 lo = mac_fast2<FMA, ADDG>(make_float2(acc[i][0], acc[i][1]), a2, make_float2(bv.x, bv.y), p.radd, p.rmul);
+                        const float2 hi = mac_fast2<FMA, ADDG>(make_float2(acc[i][2], acc[i][3]), a2, make_float2(bv.z, bv.w), p.radd, p.rmul);
                         acc[i][0] = lo.x; acc[i][1] = lo.y; acc[i][2] = hi.x; acc[i][3] = hi.y;
                     } else {
                         acc[i][0] = mac_fast<FMA>(acc[i][0], a, bv.x, p.radd, p.rmul);
@@ -284,7 +292,7 @@ __device__ __forceinline__ FastPlan make_plan(const MmParams& p, int64_t batch) 
     return plan;
 }
 
-template <int ALGO, bool FMA, bool VEC, bool PACKED>
+template <int ALGO, bool FMA, bool VEC, bool PACKED, bool ADDG>
 __global__ void __launch_bounds__(THREADS, 2) mm_kernel(const MmParams p) {
     extern __shared__ __align__(16) float smem[];
     float* As = smem;
@@ -335,15 +343,15 @@ __global__ void __launch_bounds__(THREADS, 2) mm_kernel(const MmParams p) {
             for (int g = 0; g * 8 < nk_tile; ++g) {
                 const int nk = (nk_tile - g * 8) < 8 ? (nk_tile - g * 8) : 8;
                 if (ALGO == ALGO_TILE8) {
-                    if (plan.ok) group_steps<FMA, true, PACKED>(acc, as, bs, g * 8, nk, ty, tx, p);
-                    else group_steps<FMA, false, false>(acc, as, bs, g * 8, nk, ty, tx, p);
+                    if (plan.ok) group_steps<FMA, true, PACKED, ADDG>(acc, as, bs, g * 8, nk, ty, tx, p);
+                    else group_steps<FMA, false, false, true>(acc, as, bs, g * 8, nk, ty, tx, p);
                     // fold the group into the outer sum
                     if (plan.ok && absmax_of(aux) < plan.acc_limit) {
 #pragma unroll
                         for (int i = 0; i < TM; ++i) {
                             if (PACKED) {
-                                const float2 lo = fast_rn2(p.radd, __fadd2_rn(make_float2(aux[i][0], aux[i][1]), make_float2(acc[i][0], acc[i][1])));
-                                const float2 hi = fast_rn2(p.radd, __fadd2_rn(make_float2(aux[i][2], aux[i][3]), make_float2(acc[i][2], acc[i][3])));
+                                const float2 lo = fast_rn2<ADDG>(p.radd, __fadd2_rn(make_float2(aux[i][0], aux[i][1]), make_float2(acc[i][0], acc[i][1])));
+                                const float2 hi = fast_rn2<ADDG>(p.radd, __fadd2_rn(make_float2(aux[i][2], aux[i][3]), make_float2(acc[i][2], acc[i][3])));
                                 aux[i][0] = lo.x; aux[i][1] = lo.y; aux[i][2] = hi.x; aux[i][3] = hi.y;
                             } else {
 #pragma unroll
@@ -359,8 +367,8 @@ __global__ void __launch_bounds__(THREADS, 2) mm_kernel(const MmParams p) {
                             for (int j = 0; j < TN; ++j) { aux[i][j] = cast_fp_nearest(add_rn(aux[i][j], acc[i][j]), p.fadd); acc[i][j] = 0.0f; }
                     }
                 } else {
-                    if (plan.ok && absmax_of(acc) < plan.acc_limit) group_steps<FMA, true, PACKED>(acc, as, bs, g * 8, nk, ty, tx, p);
-                    else group_steps<FMA, false, false>(acc, as, bs, g * 8, nk, ty, tx, p);
+                    if (plan.ok && absmax_of(acc) < plan.acc_limit) group_steps<FMA, true, PACKED, ADDG>(acc, as, bs, g * 8, nk, ty, tx, p);
+                    else group_steps<FMA, false, false, true>(acc, as, bs, g * 8, nk, ty, tx, p);
                 }
             }
         } else if (ALGO == ALGO_KAHAN) {
@@ -440,8 +448,14 @@ int launch_mm(const MmParams& p, int64_t batch, bool vec, cudaStream_t st) {
     dim3 grid((p.N + BN - 1) / BN, (p.M + BM - 1) / BM, (unsigned)batch);
     constexpr bool kHasFast = (ALGO == ALGO_SEQ || ALGO == ALGO_TILE8);
     const bool packed = kHasFast && use_packed();
-    auto kern = vec ? (packed ? mm_kernel<ALGO, FMA, true, kHasFast> : mm_kernel<ALGO, FMA, true, false>)
-                    : (packed ? mm_kernel<ALGO, FMA, false, kHasFast> : mm_kernel<ALGO, FMA, false, false>);
+    // the sum rounding needs its subnormal clamp only if products can carry bits below the add format's
+    // smallest subnormal (always the case for a fused multiply-add, whose sum is not a sum of rounded values)
+    const bool add_guard = FMA || !packed || (p.fmul.min_exp - p.fmul.man) < (p.fadd.min_exp - p.fadd.man);
+    constexpr bool kCanDrop = kHasFast && !FMA;
+    auto kern = vec ? (packed ? (add_guard ? mm_kernel<ALGO, FMA, true, kHasFast, true> : mm_kernel<ALGO, FMA, true, kHasFast, !kCanDrop>)
+                              : mm_kernel<ALGO, FMA, true, false, true>)
+                    : (packed ? (add_guard ? mm_kernel<ALGO, FMA, false, kHasFast, true> : mm_kernel<ALGO, FMA, false, kHasFast, !kCanDrop>)
+                              : mm_kernel<ALGO, FMA, false, false, true>);
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
     if (e != cudaSuccess) { set_error("float_mm: cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return MPT_ERR_CUDA; }
     kern<<<grid, THREADS, SMEM_BYTES, st>>>(p);

@@ -38,7 +38,9 @@ def cpu_mm(oracle, a, b, fadd, fmul, sub=True, sat=False, fma=False, order="cuda
     return oracle.mm(a, b, fadd[1], fadd[0], fmul[1], fmul[0], sub, sat, fma, "tile8" if order == "cuda" else "seq", comp)
 
 
-FORMATS = [((5, 2), (5, 2)), ((5, 10), (4, 3)), ((8, 7), (5, 2)), ((4, 3), (4, 3)), ((8, 23), (5, 2)), ((6, 21), (3, 0))]
+# (add, mul) pairs; (4,3)/(5,10) and (5,2)/(8,7) have a multiply format finer than the add format
+FORMATS = [((5, 2), (5, 2)), ((5, 10), (4, 3)), ((8, 7), (5, 2)), ((4, 3), (4, 3)), ((8, 23), (5, 2)), ((6, 21), (3, 0)),
+           ((4, 3), (5, 10)), ((5, 2), (8, 7))]
 SHAPES = [(78, 101, 145), (64, 256, 48), (9, 32, 12), (1, 1, 1), (130, 8, 70), (17, 40, 4), (128, 64, 64), (5, 7, 3)]
 
 
@@ -108,6 +110,7 @@ def test_value_ranges_that_leave_the_fast_path(be, oracle, order):
         "huge": (base_a * 300, base_b * 300),
         "mid": (base_a * 20, base_b * 20),
         "tiny": (base_a * 1e-4, base_b * 1e-3),
+        "subnormal_sums": (base_a * 3e-3, base_b * 3e-3),
         "denormal_products": (base_a * 1e-20, base_b * 1e-20),
     }
     sp_a, sp_b = base_a.copy(), base_b.copy()
@@ -116,7 +119,7 @@ def test_value_ranges_that_leave_the_fast_path(be, oracle, order):
     one_big = base_a.copy(); one_big[0, 0] = 3e4
     cases["one_big"] = (one_big, base_b)
     for name, (a, b) in cases.items():
-        for fadd, fmul in [((5, 2), (5, 2)), ((5, 10), (4, 3)), ((8, 7), (5, 2)), ((8, 7), (8, 7))]:
+        for fadd, fmul in [((5, 2), (5, 2)), ((5, 10), (4, 3)), ((8, 7), (5, 2)), ((8, 7), (8, 7)), ((4, 3), (5, 10))]:
             for sat in (False, True):
                 for fma in (False, True):
                     got = gpu_mm(be, a, b, fadd, fmul, sat=sat, fma=fma, order=order)
