@@ -33,8 +33,8 @@ FMT = dict(man_add=2, exp_add=5, man_mul=2, exp_mul=5, subnormals=True, saturate
 # (smsp__inst_executed.sum x 32 / MACs; see profiles/).  The issue-rate roofline is
 # SMs x 128 lanes x SM clock / I_MAC.  Of those instructions ALU_MAC run on the half-rate ALU pipe
 # (64 lanes per SM per clock), which is the tighter bound of the two and is reported alongside.
-I_MAC = 8.11
-ALU_MAC = 4.4
+I_MAC = 6.99
+ALU_MAC = 3.41
 METRIC = "float_mm GMAC/s (8192^3, e5m2 RN)"
 
 
