@@ -60,6 +60,12 @@ def lib() -> C.CDLL:
         L.orc_softmax_backward.argtypes = [p, p, p, i64, i32, i64] + [i32] * 7
         L.orc_layernorm_forward.argtypes = [p, p, p, p, p, p, f32, i64, i32, i64] + [i32] * 11
         L.orc_layernorm_backward.argtypes = [p] * 8 + [i64, i32, i64] + [i32] * 9
+        L.orc_mm_fmt.argtypes = [p, p, p, i64, i32, i32, i32, p, p, i32, i32]
+        L.orc_softmax_forward_fmt.argtypes = [p, p, i64, i32, i64, p, p, p, i32]
+        L.orc_softmax_lse_forward_fmt.argtypes = [p, p, i64, i32, i64, p, p, i32]
+        L.orc_softmax_backward_fmt.argtypes = [p, p, p, i64, i32, i64, p, p, i32]
+        L.orc_layernorm_forward_fmt.argtypes = [p, p, p, p, p, p, f32, i64, i32, i64, p, p, p, p, i32]
+        L.orc_layernorm_backward_fmt.argtypes = [p] * 8 + [i64, i32, i64, p, p, p, i32]
         L.orc_mx_quantize.argtypes = [p, p, p, i64, i64, i32, i32]
         L.orc_nvfp4_quantize.restype = f32
         L.orc_nvfp4_quantize.argtypes = [p, p, p, i64, i64, f32]
@@ -231,3 +237,75 @@ def qsum_rows(x, man, exp, subnormals=True, saturate=False):
     o = np.zeros(x.shape[1], dtype=np.float32)
     lib().orc_qsum_rows(_ptr(x), _ptr(o), x.shape[0], x.shape[1], man, exp, int(subnormals), int(saturate))
     return o
+
+
+# ---------------------------------------------------------------------------------- generic formats
+# A format descriptor is an int32[8]: {kind, man, exp, subnormals, saturate, a, b, c}.
+def fmt_float(man, exp, subnormals=True, saturate=False):
+    return np.array([0, man, exp, int(subnormals), int(saturate), 0, 0, 0], dtype=np.int32)
+
+
+def fmt_superfp(man, exp, binades_l=1, binades_u=1, saturate=False):
+    return np.array([1, man, exp, 0, int(saturate), binades_l, binades_u, 0], dtype=np.int32)
+
+
+def fmt_binary8(P, is_signed=True, overflow_policy="saturate_maxfloat", subnormals=True):
+    pol = POLICY[overflow_policy] if isinstance(overflow_policy, str) else int(overflow_policy)
+    return np.array([2, 0, 0, int(subnormals), 0, P, int(is_signed), pol], dtype=np.int32)
+
+
+def mm_fmt(a, b, fadd, fmul, fma=False, order="seq"):
+    a, b = _f32(a), _f32(b)
+    batched = a.ndim == 3
+    B = a.shape[0] if batched else 1
+    M, K = a.shape[-2:]
+    N = b.shape[-1]
+    c = np.zeros((B, M, N) if batched else (M, N), dtype=np.float32)
+    lib().orc_mm_fmt(_ptr(a), _ptr(b), _ptr(c), B, M, K, N, _ptr(fadd), _ptr(fmul), int(fma), ORDER[order])
+    return c
+
+
+def softmax_forward_fmt(a, dim, fexp, foff, facc, order="seq"):
+    a = _f32(a)
+    o = np.zeros_like(a)
+    outer, ch, inner = partition(a.shape, dim)
+    lib().orc_softmax_forward_fmt(_ptr(a), _ptr(o), outer, ch, inner, _ptr(fexp), _ptr(foff), _ptr(facc), ORDER[order])
+    return o
+
+
+def softmax_lse_forward_fmt(a, dim, foff, flse, order="seq"):
+    a = _f32(a)
+    o = np.zeros_like(a)
+    outer, ch, inner = partition(a.shape, dim)
+    lib().orc_softmax_lse_forward_fmt(_ptr(a), _ptr(o), outer, ch, inner, _ptr(foff), _ptr(flse), ORDER[order])
+    return o
+
+
+def softmax_backward_fmt(y, g, dim, fadd, fmul, order="seq"):
+    y, g = _f32(y), _f32(g)
+    o = np.zeros_like(y)
+    outer, ch, inner = partition(y.shape, dim)
+    lib().orc_softmax_backward_fmt(_ptr(y), _ptr(g), _ptr(o), outer, ch, inner, _ptr(fadd), _ptr(fmul), ORDER[order])
+    return o
+
+
+def layernorm_forward_fmt(x, w, b, eps, dims, facc, fmul, fdiv, fsqrt, order="seq"):
+    x, w, b = _f32(x), _f32(w), _f32(b)
+    outer, ch, inner = partition(x.shape, dims)
+    y = np.zeros_like(x)
+    mean = np.zeros(outer * inner, dtype=np.float32)
+    rstd = np.zeros(outer * inner, dtype=np.float32)
+    lib().orc_layernorm_forward_fmt(_ptr(x), _ptr(w), _ptr(b), _ptr(y), _ptr(mean), _ptr(rstd), eps, outer, ch, inner,
+                                    _ptr(facc), _ptr(fmul), _ptr(fdiv), _ptr(fsqrt), ORDER[order])
+    return y, mean, rstd
+
+
+def layernorm_backward_fmt(x, g, w, mean, rstd, dims, facc, fmul, fdiv, order="seq"):
+    x, g, w, mean, rstd = _f32(x), _f32(g), _f32(w), _f32(mean), _f32(rstd)
+    outer, ch, inner = partition(x.shape, dims)
+    gin = np.zeros_like(x)
+    gg = np.zeros(ch, dtype=np.float32)
+    gb = np.zeros(ch, dtype=np.float32)
+    lib().orc_layernorm_backward_fmt(_ptr(x), _ptr(g), _ptr(w), _ptr(mean), _ptr(rstd), _ptr(gin), _ptr(gg), _ptr(gb), outer, ch,
+                                     inner, _ptr(facc), _ptr(fmul), _ptr(fdiv), ORDER[order])
+    return gin, gg, gb

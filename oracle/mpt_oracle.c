@@ -324,8 +324,19 @@ ORC_API void orc_superfp_quantize(const float *a, float *o, int64_t n, int man, 
 /* per-MAC rounded GEMM                                                      */
 /* ------------------------------------------------------------------------- */
 
-typedef struct { int man, exp, sub, sat; } fmt_t;
-static inline float Q(float x, fmt_t f) { return cast_fp_rn_or_rz(x, f.man, f.exp, f.sub, f.sat, 0); }
+/* A rounding format: IEEE-like float (kind 0), supernormal float (kind 1: a = binades_l, b = binades_u) or
+ * P3109 binary8 (kind 2: a = P, b = is_signed, c = overflow policy).  The reference instantiates the same
+ * GEMM / softmax / layernorm templates with each of the three casters (quant_cuda/superfp_kernel.cu:79-262,
+ * binary8_kernel.cu:344-491; CPU quant.cpp:893-1150, binary8.cpp:370-542). */
+typedef struct { int man, exp, sub, sat; int kind, a, b, c; } fmt_t;
+static inline float Q(float x, fmt_t f)
+{
+    if (f.kind == 1) return orc_cast_superfp(x, f.man, f.exp, f.a, f.b, f.sat);
+    if (f.kind == 2) return orc_cast_binary8(x, f.a, f.b, f.c, f.sub, 0, 0u, 0);
+    return cast_fp_rn_or_rz(x, f.man, f.exp, f.sub, f.sat, 0);
+}
+/* descriptor layout shared with the loader: {kind, man, exp, sub, sat, a, b, c} */
+static fmt_t fmt_from(const int *d) { fmt_t f = {d[1], d[2], d[3], d[4], d[0], d[5], d[6], d[7]}; return f; }
 
 /* Philox4x32-10 (Salmon et al., SC'11), the counter-based generator the
  * stochastic GEMM keys by (seed; batch,row,col,k).  Published algorithm;
@@ -361,11 +372,26 @@ ORC_API void orc_philox(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3,
  *                 reference: quant_cuda/mm_kernel.h:34-70 (fma: :134-186).
  * compensated (Kahan) and stochastic variants walk the zero padded K range
  * with a single accumulator: reference quant_cuda/mm_kernel.h:457-520, :248-295. */
+static void mm_impl(const float *a, const float *b, float *c, int64_t B, int M, int K, int N,
+                    fmt_t fa, fmt_t fm, int fma, int order, int compensated);
+
 ORC_API void orc_mm(const float *a, const float *b, float *c, int64_t B, int M, int K, int N,
                     int man_add, int exp_add, int man_mul, int exp_mul,
                     int sub, int sat, int fma, int order, int compensated)
 {
     fmt_t fa = {man_add, exp_add, sub, sat}, fm = {man_mul, exp_mul, sub, sat};
+    mm_impl(a, b, c, B, M, K, N, fa, fm, fma, order, compensated);
+}
+
+ORC_API void orc_mm_fmt(const float *a, const float *b, float *c, int64_t B, int M, int K, int N,
+                        const int *fmt_add, const int *fmt_mul, int fma, int order)
+{
+    mm_impl(a, b, c, B, M, K, N, fmt_from(fmt_add), fmt_from(fmt_mul), fma, order, 0);
+}
+
+static void mm_impl(const float *a, const float *b, float *c, int64_t B, int M, int K, int N,
+                    fmt_t fa, fmt_t fm, int fma, int order, int compensated)
+{
     int Kpad = K + 8 - K % 8;
     /* Rows of C are independent; each output still sees its k steps in the stated order.  The loops
        run k outside j (as the reference CPU kernel does) so B is read along its rows. */
@@ -485,11 +511,23 @@ static float op_qlse(float a, float b, const void *ctx) { return Q(logf(expf(a) 
 
 /* order 0 (seq): reference quant_cpu/softmax.h:11-46.
  * order 1 (tree64): reference quant_cuda/softmax_kernel.h:23-100.          */
+static void softmax_forward_impl(const float *in, float *out, int64_t outer, int channel, int64_t inner, fmt_t fe, fmt_t fo, fmt_t fa, int order);
+
 ORC_API void orc_softmax_forward(const float *in, float *out, int64_t outer, int channel, int64_t inner,
                                  int man_exp, int exp_exp, int man_off, int exp_off,
                                  int man_acc, int exp_acc, int sub, int sat, int order)
 {
     fmt_t fe = {man_exp, exp_exp, sub, sat}, fo = {man_off, exp_off, sub, sat}, fa = {man_acc, exp_acc, sub, sat};
+    softmax_forward_impl(in, out, outer, channel, inner, fe, fo, fa, order);
+}
+
+ORC_API void orc_softmax_forward_fmt(const float *in, float *out, int64_t outer, int channel, int64_t inner, const int *d_fe, const int *d_fo, const int *d_fa, int order)
+{
+    softmax_forward_impl(in, out, outer, channel, inner, fmt_from(d_fe), fmt_from(d_fo), fmt_from(d_fa), order);
+}
+
+static void softmax_forward_impl(const float *in, float *out, int64_t outer, int channel, int64_t inner, fmt_t fe, fmt_t fo, fmt_t fa, int order)
+{
     for (int64_t row = 0; row < outer * inner; ++row) {
         const float *x = in + (row / inner) * channel * inner + row % inner;
         float *y = out + (row / inner) * channel * inner + row % inner;
@@ -522,11 +560,23 @@ ORC_API void orc_softmax_forward(const float *in, float *out, int64_t outer, int
 }
 
 /* order 0: reference quant_cpu/softmax.h:50-87; order 1: quant_cuda/softmax_kernel.h:102-171. */
+static void softmax_lse_forward_impl(const float *in, float *out, int64_t outer, int channel, int64_t inner, fmt_t fo, fmt_t fl, int order);
+
 ORC_API void orc_softmax_lse_forward(const float *in, float *out, int64_t outer, int channel, int64_t inner,
                                      int man_off, int exp_off, int man_lse, int exp_lse,
                                      int sub, int sat, int order)
 {
     fmt_t fo = {man_off, exp_off, sub, sat}, fl = {man_lse, exp_lse, sub, sat};
+    softmax_lse_forward_impl(in, out, outer, channel, inner, fo, fl, order);
+}
+
+ORC_API void orc_softmax_lse_forward_fmt(const float *in, float *out, int64_t outer, int channel, int64_t inner, const int *d_fo, const int *d_fl, int order)
+{
+    softmax_lse_forward_impl(in, out, outer, channel, inner, fmt_from(d_fo), fmt_from(d_fl), order);
+}
+
+static void softmax_lse_forward_impl(const float *in, float *out, int64_t outer, int channel, int64_t inner, fmt_t fo, fmt_t fl, int order)
+{
     for (int64_t row = 0; row < outer * inner; ++row) {
         const float *x = in + (row / inner) * channel * inner + row % inner;
         float *y = out + (row / inner) * channel * inner + row % inner;
@@ -564,11 +614,23 @@ ORC_API void orc_softmax_lse_forward(const float *in, float *out, int64_t outer,
 }
 
 /* order 0: reference quant_cpu/softmax.h:89-114; order 1: quant_cuda/softmax_kernel.h:173-222. */
+static void softmax_backward_impl(const float *yv, const float *g, float *out, int64_t outer, int channel, int64_t inner, fmt_t fa, fmt_t fm, int order);
+
 ORC_API void orc_softmax_backward(const float *yv, const float *g, float *out, int64_t outer, int channel,
                                   int64_t inner, int man_add, int exp_add, int man_mul, int exp_mul,
                                   int sub, int sat, int order)
 {
     fmt_t fa = {man_add, exp_add, sub, sat}, fm = {man_mul, exp_mul, sub, sat};
+    softmax_backward_impl(yv, g, out, outer, channel, inner, fa, fm, order);
+}
+
+ORC_API void orc_softmax_backward_fmt(const float *yv, const float *g, float *out, int64_t outer, int channel, int64_t inner, const int *d_fa, const int *d_fm, int order)
+{
+    softmax_backward_impl(yv, g, out, outer, channel, inner, fmt_from(d_fa), fmt_from(d_fm), order);
+}
+
+static void softmax_backward_impl(const float *yv, const float *g, float *out, int64_t outer, int channel, int64_t inner, fmt_t fa, fmt_t fm, int order)
+{
     for (int64_t row = 0; row < outer * inner; ++row) {
         int64_t base = (row / inner) * channel * inner + row % inner;
         const float *y = yv + base, *gr = g + base;
@@ -594,6 +656,8 @@ ORC_API void orc_softmax_backward(const float *yv, const float *g, float *out, i
  * rounded with Qdiv after the division).
  * order 1: reference quant_cuda/layernorm_kernel.h:7-100 (tree64 sums; mean
  * and variance are NOT rounded after the division).                        */
+static void layernorm_forward_impl(const float *in, const float *w, const float *bias, float *out, float *mean, float *rstd, float eps, int64_t outer, int channel, int64_t inner, fmt_t fa, fmt_t fm, fmt_t fd, fmt_t fs, int order);
+
 ORC_API void orc_layernorm_forward(const float *in, const float *w, const float *bias, float *out,
                                    float *mean, float *rstd, float eps,
                                    int64_t outer, int channel, int64_t inner,
@@ -603,6 +667,16 @@ ORC_API void orc_layernorm_forward(const float *in, const float *w, const float 
 {
     fmt_t fa = {man_acc, exp_acc, sub, sat}, fm = {man_mul, exp_mul, sub, sat};
     fmt_t fd = {man_div, exp_div, sub, sat}, fs = {man_sqrt, exp_sqrt, sub, sat};
+    layernorm_forward_impl(in, w, bias, out, mean, rstd, eps, outer, channel, inner, fa, fm, fd, fs, order);
+}
+
+ORC_API void orc_layernorm_forward_fmt(const float *in, const float *w, const float *bias, float *out, float *mean, float *rstd, float eps, int64_t outer, int channel, int64_t inner, const int *d_fa, const int *d_fm, const int *d_fd, const int *d_fs, int order)
+{
+    layernorm_forward_impl(in, w, bias, out, mean, rstd, eps, outer, channel, inner, fmt_from(d_fa), fmt_from(d_fm), fmt_from(d_fd), fmt_from(d_fs), order);
+}
+
+static void layernorm_forward_impl(const float *in, const float *w, const float *bias, float *out, float *mean, float *rstd, float eps, int64_t outer, int channel, int64_t inner, fmt_t fa, fmt_t fm, fmt_t fd, fmt_t fs, int order)
+{
     for (int64_t row = 0; row < outer * inner; ++row) {
         int64_t base = (row / inner) * channel * inner + row % inner;
         const float *x = in + base;
@@ -650,6 +724,8 @@ ORC_API void orc_layernorm_forward(const float *in, const float *w, const float 
  * second pass sums rows 0..R-1 per channel starting from zero).
  * grad_gamma/grad_beta must be zero-filled by the caller for order 0, as the
  * reference's Python wrapper does (quant_function.py:1210-1212).           */
+static void layernorm_backward_impl(const float *in, const float *g, const float *w, const float *mean, const float *rstd, float *gin, float *ggamma, float *gbeta, int64_t outer, int channel, int64_t inner, fmt_t fa, fmt_t fm, fmt_t fd, int order);
+
 ORC_API void orc_layernorm_backward(const float *in, const float *g, const float *w,
                                     const float *mean, const float *rstd,
                                     float *gin, float *ggamma, float *gbeta,
@@ -658,6 +734,16 @@ ORC_API void orc_layernorm_backward(const float *in, const float *g, const float
                                     int man_div, int exp_div, int sub, int sat, int order)
 {
     fmt_t fa = {man_acc, exp_acc, sub, sat}, fm = {man_mul, exp_mul, sub, sat}, fd = {man_div, exp_div, sub, sat};
+    layernorm_backward_impl(in, g, w, mean, rstd, gin, ggamma, gbeta, outer, channel, inner, fa, fm, fd, order);
+}
+
+ORC_API void orc_layernorm_backward_fmt(const float *in, const float *g, const float *w, const float *mean, const float *rstd, float *gin, float *ggamma, float *gbeta, int64_t outer, int channel, int64_t inner, const int *d_fa, const int *d_fm, const int *d_fd, int order)
+{
+    layernorm_backward_impl(in, g, w, mean, rstd, gin, ggamma, gbeta, outer, channel, inner, fmt_from(d_fa), fmt_from(d_fm), fmt_from(d_fd), order);
+}
+
+static void layernorm_backward_impl(const float *in, const float *g, const float *w, const float *mean, const float *rstd, float *gin, float *ggamma, float *gbeta, int64_t outer, int channel, int64_t inner, fmt_t fa, fmt_t fm, fmt_t fd, int order)
+{
     if (order == 1) for (int k = 0; k < channel; ++k) { ggamma[k] = 0.f; gbeta[k] = 0.f; }
     for (int64_t row = 0; row < outer * inner; ++row) {
         int64_t base = (row / inner) * channel * inner + row % inner;

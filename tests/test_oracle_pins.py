@@ -264,3 +264,69 @@ def test_tile8_equals_composition_of_pinned_casts(oracle):
     assert same_bits(got, outer), mismatch_report(got, outer)
     seq = oracle.mm(a, b, 2, 5, 3, 4, True, False, False, "seq")
     assert not same_bits(seq, outer)
+
+
+# ------------------------------------------------------------------ superfp / binary8 arithmetic vs the live reference
+def test_superfp_mm_vs_live_reference(oracle, ref_cpu):
+    torch.manual_seed(21)
+    a, b = torch.randn(19, 45), torch.randn(45, 13)
+    for (ma, ea, la, ua, mm_, em, lm, um) in [(3, 4, 1, 1, 2, 4, 2, 1), (2, 5, 1, 2, 2, 5, 1, 2), (4, 3, 1, 1, 3, 4, 1, 1)]:
+        for sat in (False, True):
+            c = torch.zeros(19, 13)
+            ref_cpu.superfp_quantize_nearest_mm(a, b, c, 19, 13, 45, ma, ea, mm_, em, la, ua, lm, um, sat)
+            got = oracle.mm_fmt(a.numpy(), b.numpy(), oracle.fmt_superfp(ma, ea, la, ua, sat), oracle.fmt_superfp(mm_, em, lm, um, sat), False, "seq")
+            assert same_bits(got, c.numpy()), mismatch_report(got, c.numpy())
+            c = torch.zeros(19, 13)
+            ref_cpu.superfp_quantize_nearest_mm_fma(a, b, c, 19, 13, 45, ma, ea, la, ua, sat)
+            f = oracle.fmt_superfp(ma, ea, la, ua, sat)
+            got = oracle.mm_fmt(a.numpy(), b.numpy(), f, f, True, "seq")
+            assert same_bits(got, c.numpy()), mismatch_report(got, c.numpy())
+    a3, b3 = torch.randn(3, 8, 20), torch.randn(3, 20, 6)
+    c3 = torch.zeros(3, 8, 6)
+    ref_cpu.superfp_quantize_nearest_bmm(a3, b3, c3, 8, 6, 20, 3, 4, 2, 4, 1, 1, 2, 1, False)
+    got = oracle.mm_fmt(a3.numpy(), b3.numpy(), oracle.fmt_superfp(3, 4, 1, 1), oracle.fmt_superfp(2, 4, 2, 1), False, "seq")
+    assert same_bits(got, c3.numpy())
+
+
+def test_superfp_and_binary8_reductions_vs_live_reference(oracle, ref_cpu):
+    torch.manual_seed(22)
+    x = torch.randn(3, 33, 4) * 2
+    g = torch.randn(3, 33, 4)
+    pol = [ref_cpu.OverflowPolicy.SATURATE_INFTY, ref_cpu.OverflowPolicy.SATURATE_MAXFLOAT, ref_cpu.OverflowPolicy.SATURATE_MAXFLOAT2]
+    sf = oracle.fmt_superfp(3, 5, 2, 1, False)
+    for dim in (0, 1, 2):
+        y = torch.zeros_like(x)
+        ref_cpu.superfp_quantize_nearest_softmax_forward(x, y, dim, 3, 5, 2, 1, 3, 5, 2, 1, 3, 5, 2, 1, False)
+        assert same_bits(oracle.softmax_forward_fmt(x.numpy(), dim, sf, sf, sf, "seq"), y.numpy())
+        y2 = torch.zeros_like(x)
+        ref_cpu.superfp_quantize_nearest_softmax_lse_forward(x, y2, dim, 3, 5, 2, 1, 3, 5, 2, 1, False)
+        assert same_bits(oracle.softmax_lse_forward_fmt(x.numpy(), dim, sf, sf, "seq"), y2.numpy())
+        d = torch.zeros_like(x)
+        ref_cpu.superfp_quantize_nearest_softmax_backward(y, g, d, dim, 3, 5, 2, 1, 3, 5, 2, 1, False)
+        assert same_bits(oracle.softmax_backward_fmt(y.numpy(), g.numpy(), dim, sf, sf, "seq"), d.numpy())
+        for (P, sg, po) in [(4, True, 1), (3, True, 0), (5, False, 2)]:
+            bf = oracle.fmt_binary8(P, sg, po, True)
+            yb = torch.zeros_like(x)
+            ref_cpu.binary8_quantize_nearest_softmax_forward(x, yb, dim, P, pol[po], sg, P, pol[po], True, P, pol[po], sg, True)
+            bo = oracle.fmt_binary8(P, True, po, True)    # the offset x - max is negative: signed format
+            assert same_bits(oracle.softmax_forward_fmt(x.numpy(), dim, bf, bo, bf, "seq"), yb.numpy())
+            db = torch.zeros_like(x)
+            ref_cpu.binary8_quantize_nearest_softmax_backward(yb, g, db, dim, P, pol[po], True, P, pol[po], True, True)
+            bs = oracle.fmt_binary8(P, True, po, True)
+            assert same_bits(oracle.softmax_backward_fmt(yb.numpy(), g.numpy(), dim, bs, bs, "seq"), db.numpy())
+    xl = torch.randn(4, 5, 24) + 0.3
+    gl = torch.randn(4, 5, 24)
+    w, b = torch.randn(24), torch.randn(24)
+    for fmt, call_f, call_b, args in (
+            (oracle.fmt_superfp(4, 5, 1, 1, False), ref_cpu.superfp_quantize_layernorm_forward, ref_cpu.superfp_quantize_layernorm_backward,
+             lambda n: sum(([4, 5, 1, 1] for _ in range(n)), []) + [False]),
+            (oracle.fmt_binary8(5, True, 1, True), ref_cpu.binary8_quantize_layernorm_forward, ref_cpu.binary8_quantize_layernorm_backward,
+             lambda n: sum(([5, pol[1], True] for _ in range(n)), []) + [True])):
+        y = torch.zeros_like(xl); mean = torch.zeros(4, 5); rstd = torch.zeros(4, 5)
+        call_f(xl, w, b, y, mean, rstd, 1e-5, [-1], *args(4))
+        oy, om, orr = oracle.layernorm_forward_fmt(xl.numpy(), w.numpy(), b.numpy(), 1e-5, [-1], fmt, fmt, fmt, fmt, "seq")
+        assert same_bits(oy, y.numpy()) and same_bits(om, mean.numpy().ravel()) and same_bits(orr, rstd.numpy().ravel())
+        gi = torch.zeros_like(xl); gg = torch.zeros(24); gb = torch.zeros(24)
+        call_b(xl, gl, w, b, mean, rstd, gi, gg, gb, [-1], *args(3))
+        ogi, ogg, ogb = oracle.layernorm_backward_fmt(xl.numpy(), gl.numpy(), w.numpy(), om, orr, [-1], fmt, fmt, fmt, "seq")
+        assert same_bits(ogi, gi.numpy()) and same_bits(ogg, gg.numpy()) and same_bits(ogb, gb.numpy())
