@@ -198,6 +198,44 @@ MPT_API int mpt_float_layernorm_backward(const float *in, const float *grad_out,
 MPT_API int mpt_qsum_rows(const float *in, float *out, int64_t rows, int64_t cols, int man, int exp,
                           int subnormals, int saturate, void *stream);
 
+/* ---- the same GEMM and reductions for the other nearest-rounding format families --------------------
+ * The reference instantiates its mm / softmax / layernorm templates with the supernormal-float caster
+ * (superfp_quantize_nearest_mm, _bmm, _mm_fma, _bmm_fma, pybind_cuda.cpp:815-824; superfp softmax and
+ * layernorm :887-893, :914-917) and, for the reductions, with the binary8 caster (:897-903, :921-924).
+ * One descriptor covers all three families. */
+enum { MPT_FMT_FLOAT = 0, MPT_FMT_SUPERFP = 1, MPT_FMT_BINARY8 = 2 };
+typedef struct mpt_format {
+    int kind;                 /* MPT_FMT_* */
+    int man, exp;             /* float, superfp */
+    int subnormals;           /* float, binary8 */
+    int saturate;             /* float, superfp */
+    int binades_l, binades_u; /* superfp */
+    int P, is_signed, overflow_policy;   /* binary8 */
+} mpt_format;
+
+/* C = A x B with the add and multiply results rounded to `add` and `mul` (fma != 0: one rounding to `add`).
+ * Float formats take the same fast kernels as mpt_float_mm_nearest. */
+MPT_API int mpt_mm_nearest_fmt(const float *a, const float *b, float *c, int64_t batch, int M, int N, int K,
+                               const mpt_format *add, const mpt_format *mul, int fma, int order,
+                               void *workspace, size_t workspace_bytes, void *stream);
+MPT_API int mpt_softmax_forward_fmt(const float *in, float *out, int64_t outer, int channel, int64_t inner,
+                                    const mpt_format *fexp, const mpt_format *foff, const mpt_format *facc,
+                                    int order, void *stream);
+MPT_API int mpt_softmax_lse_forward_fmt(const float *in, float *out, int64_t outer, int channel, int64_t inner,
+                                        const mpt_format *foff, const mpt_format *flse, int order, void *stream);
+MPT_API int mpt_softmax_backward_fmt(const float *y, const float *grad, float *out, int64_t outer, int channel,
+                                     int64_t inner, const mpt_format *fadd, const mpt_format *fmul, int order,
+                                     void *stream);
+MPT_API int mpt_layernorm_forward_fmt(const float *in, const float *weight, const float *bias, float *out,
+                                      float *mean, float *rstd, float eps, int64_t outer, int channel, int64_t inner,
+                                      const mpt_format *facc, const mpt_format *fmul, const mpt_format *fdiv,
+                                      const mpt_format *fsqrt, int order, void *stream);
+MPT_API int mpt_layernorm_backward_fmt(const float *in, const float *grad_out, const float *weight,
+                                       const float *mean, const float *rstd, float *grad_in, float *grad_gamma,
+                                       float *grad_beta, int64_t outer, int channel, int64_t inner,
+                                       const mpt_format *facc, const mpt_format *fmul, const mpt_format *fdiv,
+                                       int order, void *stream);
+
 /* ---- block-scaled quantizers (NEW: the reference has no MX / NVFP4 kernels) ----------------------
  * Blocks run along the last, contiguous dimension of a [rows, cols] matrix; `out` receives the
  * dequantized fp32 values. */

@@ -22,6 +22,25 @@ class MptError(RuntimeError):
     pass
 
 
+class Format(C.Structure):
+    """``mpt_format`` of include/mptorch_b200.h: one descriptor for float, supernormal-float and binary8 rounding."""
+    _fields_ = [("kind", C.c_int), ("man", C.c_int), ("exp", C.c_int), ("subnormals", C.c_int), ("saturate", C.c_int),
+                ("binades_l", C.c_int), ("binades_u", C.c_int), ("P", C.c_int), ("is_signed", C.c_int),
+                ("overflow_policy", C.c_int)]
+
+    @staticmethod
+    def float(man, exp, subnormals=True, saturate=False):
+        return Format(0, man, exp, int(subnormals), int(saturate), 1, 1, 1, 1, 0)
+
+    @staticmethod
+    def superfp(man, exp, binades_l=1, binades_u=1, saturate=False):
+        return Format(1, man, exp, 1, int(saturate), binades_l, binades_u, 1, 1, 0)
+
+    @staticmethod
+    def binary8(P, is_signed=True, overflow_policy=1, subnormals=True):
+        return Format(2, 0, 0, int(subnormals), 0, 1, 1, P, int(is_signed), int(overflow_policy))
+
+
 def lib() -> C.CDLL:
     global _lib
     if _lib is None:
@@ -52,6 +71,12 @@ def lib() -> C.CDLL:
             "mpt_float_layernorm_forward": [p] * 6 + [C.c_float, i64, i32, i64] + [i32] * 11 + [p],
             "mpt_float_layernorm_backward": [p] * 8 + [i64, i32, i64] + [i32] * 9 + [p],
             "mpt_qsum_rows": [p, p, i64, i64, i32, i32, i32, i32, p],
+            "mpt_mm_nearest_fmt": [p, p, p, i64, i32, i32, i32, p, p, i32, i32, p, sz, p],
+            "mpt_softmax_forward_fmt": [p, p, i64, i32, i64, p, p, p, i32, p],
+            "mpt_softmax_lse_forward_fmt": [p, p, i64, i32, i64, p, p, i32, p],
+            "mpt_softmax_backward_fmt": [p, p, p, i64, i32, i64, p, p, i32, p],
+            "mpt_layernorm_forward_fmt": [p] * 6 + [C.c_float, i64, i32, i64, p, p, p, p, i32, p],
+            "mpt_layernorm_backward_fmt": [p] * 8 + [i64, i32, i64, p, p, p, i32, p],
             "mpt_mx_quantize": [p, p, p, i64, i64, i32, i32, p],
             "mpt_nvfp4_quantize": [p, p, p, i64, i64, C.c_float, p, p, p],
         }

@@ -264,6 +264,13 @@ def partition_tensor(shape, dim):
     inner = 1
     for i in range(hi + 1, nd):
         inner *= shape[i]
+    total = 1
+    for n in shape:
+        total *= n
+    if outer * channel * inner != total:
+        # the reference computes sizes that overrun the tensor here; refuse instead
+        raise ValueError("dims %r must be adjacent dimensions listed last-first (e.g. [-1, -2]) of a tensor of shape %r"
+                         % (dim, tuple(shape)))
     return outer, channel, inner
 
 
@@ -334,6 +341,162 @@ def qsum_rows(a, man_bits, exp_bits, subnormals, saturate):
         call("mpt_qsum_rows", ptr(a), ptr(o), a.shape[0], a.shape[1], man_bits, exp_bits, int(subnormals), int(saturate),
              stream_ptr(a.device))
     return o
+
+
+# ---------------------------------------------------------------------------------- other format families
+# The reference registers the same GEMM / softmax / layernorm entry points once more for supernormal floats and, for
+# the reductions, for binary8 (pybind_cuda.cpp:815-824, :887-924).  They all forward to the generic-format C ABI.
+Format = _cabi.Format
+def _fp(f):
+    import ctypes
+
+    return ctypes.byref(f)
+
+
+def mm_fmt(a, b, c, batch, M, N, K, fadd: Format, fmul: Format, fma: bool, order=None):
+    _mm_checks(a, b, c)
+    with torch.cuda.device(a.device):
+        ws = _cabi.mm_workspace(a.device, batch)
+        call("mpt_mm_nearest_fmt", ptr(a), ptr(b), ptr(c), batch, M, N, K, _fp(fadd), _fp(fmul), int(fma),
+             _order_code(order, "accum_order"), ptr(ws), ws.numel(), stream_ptr(a.device))
+
+
+def superfp_quantize_nearest_mm(a, b, c, M, N, K, man_add, exp_add, man_mul, exp_mul, binades_add_l, binades_add_u,
+                                binades_mul_l, binades_mul_u, saturate, order=None):
+    """pybind_cuda.cpp:815."""
+    mm_fmt(a, b, c, 1, M, N, K, Format.superfp(man_add, exp_add, binades_add_l, binades_add_u, saturate),
+           Format.superfp(man_mul, exp_mul, binades_mul_l, binades_mul_u, saturate), False, order)
+
+
+def superfp_quantize_nearest_bmm(a, b, c, M, N, K, man_add, exp_add, man_mul, exp_mul, binades_add_l, binades_add_u,
+                                 binades_mul_l, binades_mul_u, saturate, order=None):
+    """pybind_cuda.cpp:818."""
+    mm_fmt(a, b, c, _batch_of(a), M, N, K, Format.superfp(man_add, exp_add, binades_add_l, binades_add_u, saturate),
+           Format.superfp(man_mul, exp_mul, binades_mul_l, binades_mul_u, saturate), False, order)
+
+
+def superfp_quantize_nearest_mm_fma(a, b, c, M, N, K, man_fma, exp_fma, binades_fma_l, binades_fma_u, saturate, order=None):
+    """pybind_cuda.cpp:821."""
+    f = Format.superfp(man_fma, exp_fma, binades_fma_l, binades_fma_u, saturate)
+    mm_fmt(a, b, c, 1, M, N, K, f, f, True, order)
+
+
+def superfp_quantize_nearest_bmm_fma(a, b, c, M, N, K, man_fma, exp_fma, binades_fma_l, binades_fma_u, saturate, order=None):
+    """pybind_cuda.cpp:824."""
+    f = Format.superfp(man_fma, exp_fma, binades_fma_l, binades_fma_u, saturate)
+    mm_fmt(a, b, c, _batch_of(a), M, N, K, f, f, True, order)
+
+
+def softmax_forward_fmt(a, o, dim, fexp: Format, foff: Format, facc: Format, order=None):
+    check_cuda_f32(a, "a"); check_cuda_f32(o, "o")
+    outer, ch, inner = partition_tensor(a.shape, dim)
+    with torch.cuda.device(a.device):
+        call("mpt_softmax_forward_fmt", ptr(a), ptr(o), outer, ch, inner, _fp(fexp), _fp(foff), _fp(facc),
+             _order_code(order, "reduce_order"), stream_ptr(a.device))
+
+
+def softmax_lse_forward_fmt(a, o, dim, foff: Format, flse: Format, order=None):
+    check_cuda_f32(a, "a"); check_cuda_f32(o, "o")
+    outer, ch, inner = partition_tensor(a.shape, dim)
+    with torch.cuda.device(a.device):
+        call("mpt_softmax_lse_forward_fmt", ptr(a), ptr(o), outer, ch, inner, _fp(foff), _fp(flse),
+             _order_code(order, "reduce_order"), stream_ptr(a.device))
+
+
+def softmax_backward_fmt(a, g, o, dim, fadd: Format, fmul: Format, order=None):
+    check_cuda_f32(a, "a"); check_cuda_f32(g, "g"); check_cuda_f32(o, "o")
+    outer, ch, inner = partition_tensor(a.shape, dim)
+    with torch.cuda.device(a.device):
+        call("mpt_softmax_backward_fmt", ptr(a), ptr(g), ptr(o), outer, ch, inner, _fp(fadd), _fp(fmul),
+             _order_code(order, "reduce_order"), stream_ptr(a.device))
+
+
+def layernorm_forward_fmt(input, weight, bias, output, mean, rstd, eps, dims, facc, fmul, fdiv, fsqrt, order=None):
+    for t, n in ((input, "input"), (weight, "weight"), (bias, "bias"), (output, "output"), (mean, "mean"), (rstd, "rstd")):
+        check_cuda_f32(t, n)
+    outer, ch, inner = partition_tensor(input.shape, list(dims))
+    with torch.cuda.device(input.device):
+        call("mpt_layernorm_forward_fmt", ptr(input), ptr(weight), ptr(bias), ptr(output), ptr(mean), ptr(rstd), float(eps),
+             outer, ch, inner, _fp(facc), _fp(fmul), _fp(fdiv), _fp(fsqrt), _order_code(order, "reduce_order"),
+             stream_ptr(input.device))
+
+
+def layernorm_backward_fmt(input, grad_output, weight, mean, rstd, grad_input, grad_gamma, grad_beta, dims, facc, fmul, fdiv,
+                           order=None):
+    for t, n in ((input, "input"), (grad_output, "grad_output"), (weight, "weight"), (mean, "mean"), (rstd, "rstd"),
+                 (grad_input, "grad_input"), (grad_gamma, "grad_gamma"), (grad_beta, "grad_beta")):
+        check_cuda_f32(t, n)
+    outer, ch, inner = partition_tensor(input.shape, list(dims))
+    with torch.cuda.device(input.device):
+        call("mpt_layernorm_backward_fmt", ptr(input), ptr(grad_output), ptr(weight), ptr(mean), ptr(rstd), ptr(grad_input),
+             ptr(grad_gamma), ptr(grad_beta), outer, ch, inner, _fp(facc), _fp(fmul), _fp(fdiv),
+             _order_code(order, "reduce_order"), stream_ptr(input.device))
+
+
+def superfp_quantize_nearest_softmax_forward(a, o, dim, man_exp, exp_exp, bel, beu, man_off, exp_off, bol, bou, man_acc, exp_acc,
+                                             bal, bau, saturate, order=None):
+    """pybind_cuda.cpp:887."""
+    softmax_forward_fmt(a, o, dim, Format.superfp(man_exp, exp_exp, bel, beu, saturate), Format.superfp(man_off, exp_off, bol, bou, saturate),
+                        Format.superfp(man_acc, exp_acc, bal, bau, saturate), order)
+
+
+def superfp_quantize_nearest_softmax_lse_forward(a, o, dim, man_off, exp_off, bol, bou, man_lse, exp_lse, bll, blu, saturate, order=None):
+    """pybind_cuda.cpp:890."""
+    softmax_lse_forward_fmt(a, o, dim, Format.superfp(man_off, exp_off, bol, bou, saturate), Format.superfp(man_lse, exp_lse, bll, blu, saturate), order)
+
+
+def superfp_quantize_nearest_softmax_backward(a, g, o, dim, man_add, exp_add, bal, bau, man_mul, exp_mul, bml, bmu, saturate, order=None):
+    """pybind_cuda.cpp:893."""
+    softmax_backward_fmt(a, g, o, dim, Format.superfp(man_add, exp_add, bal, bau, saturate), Format.superfp(man_mul, exp_mul, bml, bmu, saturate), order)
+
+
+def binary8_quantize_nearest_softmax_forward(a, o, dim, P_exp, op_exp, signed_exp, P_off, op_off, signed_off, P_acc, op_acc,
+                                             signed_acc, subnormals, order=None):
+    """pybind_cuda.cpp:897."""
+    softmax_forward_fmt(a, o, dim, Format.binary8(P_exp, signed_exp, op_exp, subnormals), Format.binary8(P_off, signed_off, op_off, subnormals),
+                        Format.binary8(P_acc, signed_acc, op_acc, subnormals), order)
+
+
+def binary8_quantize_nearest_softmax_lse_forward(a, o, dim, P_off, op_off, signed_off, P_lse, op_lse, signed_lse, subnormals, order=None):
+    """pybind_cuda.cpp:900."""
+    softmax_lse_forward_fmt(a, o, dim, Format.binary8(P_off, signed_off, op_off, subnormals), Format.binary8(P_lse, signed_lse, op_lse, subnormals), order)
+
+
+def binary8_quantize_nearest_softmax_backward(a, g, o, dim, P_add, op_add, signed_add, P_mul, op_mul, signed_mul, subnormals, order=None):
+    """pybind_cuda.cpp:903."""
+    softmax_backward_fmt(a, g, o, dim, Format.binary8(P_add, signed_add, op_add, subnormals), Format.binary8(P_mul, signed_mul, op_mul, subnormals), order)
+
+
+def superfp_quantize_layernorm_forward(input, weight, bias, output, mean, rstd, eps, dims, man_acc, exp_acc, bal, bau, man_mul, exp_mul,
+                                       bml, bmu, man_div, exp_div, bdl, bdu, man_sqrt, exp_sqrt, bsl, bsu, saturate, order=None):
+    """pybind_cuda.cpp:914."""
+    layernorm_forward_fmt(input, weight, bias, output, mean, rstd, eps, dims, Format.superfp(man_acc, exp_acc, bal, bau, saturate),
+                          Format.superfp(man_mul, exp_mul, bml, bmu, saturate), Format.superfp(man_div, exp_div, bdl, bdu, saturate),
+                          Format.superfp(man_sqrt, exp_sqrt, bsl, bsu, saturate), order)
+
+
+def superfp_quantize_layernorm_backward(input, grad_output, weight, bias, mean, rstd, grad_input, grad_gamma, grad_beta, dims, man_acc,
+                                        exp_acc, bal, bau, man_mul, exp_mul, bml, bmu, man_div, exp_div, bdl, bdu, saturate, order=None):
+    """pybind_cuda.cpp:917."""
+    layernorm_backward_fmt(input, grad_output, weight, mean, rstd, grad_input, grad_gamma, grad_beta, dims,
+                           Format.superfp(man_acc, exp_acc, bal, bau, saturate), Format.superfp(man_mul, exp_mul, bml, bmu, saturate),
+                           Format.superfp(man_div, exp_div, bdl, bdu, saturate), order)
+
+
+def binary8_quantize_layernorm_forward(input, weight, bias, output, mean, rstd, eps, dims, P_acc, op_acc, signed_acc, P_mul, op_mul,
+                                       signed_mul, P_div, op_div, signed_div, P_sqrt, op_sqrt, signed_sqrt, subnormals, order=None):
+    """pybind_cuda.cpp:921."""
+    layernorm_forward_fmt(input, weight, bias, output, mean, rstd, eps, dims, Format.binary8(P_acc, signed_acc, op_acc, subnormals),
+                          Format.binary8(P_mul, signed_mul, op_mul, subnormals), Format.binary8(P_div, signed_div, op_div, subnormals),
+                          Format.binary8(P_sqrt, signed_sqrt, op_sqrt, subnormals), order)
+
+
+def binary8_quantize_layernorm_backward(input, grad_output, weight, bias, mean, rstd, grad_input, grad_gamma, grad_beta, dims, P_acc,
+                                        op_acc, signed_acc, P_mul, op_mul, signed_mul, P_div, op_div, signed_div, subnormals, order=None):
+    """pybind_cuda.cpp:924."""
+    layernorm_backward_fmt(input, grad_output, weight, mean, rstd, grad_input, grad_gamma, grad_beta, dims,
+                           Format.binary8(P_acc, signed_acc, op_acc, subnormals), Format.binary8(P_mul, signed_mul, op_mul, subnormals),
+                           Format.binary8(P_div, signed_div, op_div, subnormals), order)
 
 
 # ---------------------------------------------------------------------------------- block-scaled quantizers (new)

@@ -2,6 +2,7 @@
 #include <cstring>
 #include <mutex>
 
+#include "cast.cuh"
 #include "common.cuh"
 
 namespace mpt {
@@ -22,6 +23,40 @@ int check_launch(const char* what) {
         return MPT_ERR_CUDA;
     }
     return MPT_OK;
+}
+
+bool convert_format(const char* who, const mpt_format* in, AnyFmt* out) {
+    if (in == nullptr) { set_error("%s: null format descriptor", who); return false; }
+    AnyFmt a;
+    a.kind = in->kind;
+    a.bl = a.bu = 1; a.P = 1; a.is_signed = 1; a.policy = 0;
+    switch (in->kind) {
+        case MPT_FMT_FLOAT:
+            if (!valid_format(in->man, in->exp)) { set_error("%s: unsupported float format man=%d exp=%d", who, in->man, in->exp); return false; }
+            a.fp = make_fmt(in->man, in->exp, in->subnormals, in->saturate);
+            break;
+        case MPT_FMT_SUPERFP:
+            if (!valid_format(in->man, in->exp) || in->binades_l < 1 || in->binades_u < 1) {
+                set_error("%s: unsupported supernormal format man=%d exp=%d binades=(%d,%d)", who, in->man, in->exp, in->binades_l, in->binades_u);
+                return false;
+            }
+            a.fp = make_fmt(in->man, in->exp, 1, in->saturate);
+            a.bl = in->binades_l; a.bu = in->binades_u;
+            break;
+        case MPT_FMT_BINARY8:
+            if (in->P < 1 || in->P > 7 || in->overflow_policy < 0 || in->overflow_policy > 2) {
+                set_error("%s: unsupported binary8 format P=%d policy=%d", who, in->P, in->overflow_policy);
+                return false;
+            }
+            a.fp = make_fmt(in->P - 1, 8, in->subnormals, 0);
+            a.P = in->P; a.is_signed = in->is_signed != 0; a.policy = in->overflow_policy;
+            break;
+        default:
+            set_error("%s: unknown format kind %d", who, in->kind);
+            return false;
+    }
+    *out = a;
+    return true;
 }
 
 int sm_count() {

@@ -292,6 +292,27 @@ MPT_HD float cast_superfp(float x, int man, int exp, int bl, int bu, bool sat) {
     return u2f(rne_bits(t, man));
 }
 
+// ---- one descriptor for the three nearest-rounding format families ---------------------------------
+// The reference instantiates its GEMM, softmax and layernorm templates once per family (float, supernormal
+// float, binary8); here the exact arithmetic paths take this descriptor instead.
+enum : int { FMT_FLOAT = 0, FMT_SUPERFP = 1, FMT_BINARY8 = 2 };
+struct AnyFmt {
+    int kind;
+    FpFmt fp;                   // float: all fields; superfp: man, exp, sat; binary8: sub
+    int bl, bu;                 // superfp binades
+    int P, is_signed, policy;   // binary8
+};
+MPT_HD float cast_any(float x, const AnyFmt& f) {
+    if (f.kind == FMT_SUPERFP) return cast_superfp(x, f.fp.man, f.fp.exp, f.bl, f.bu, f.fp.sat != 0);
+    if (f.kind == FMT_BINARY8) return cast_binary8(x, f.P, f.is_signed != 0, f.policy, f.fp.sub != 0, RND_NEAREST, 0u, 0);
+    return cast_fp_nearest(x, f.fp);
+}
+__host__ __device__ inline AnyFmt any_float(const FpFmt& f) {
+    AnyFmt a;
+    a.kind = FMT_FLOAT; a.fp = f; a.bl = a.bu = 1; a.P = 1; a.is_signed = 1; a.policy = 0;
+    return a;
+}
+
 // ---- fast round-to-nearest-even on the FP32 pipe ---------------------------------------------
 // For a finite x whose rounded value stays below the format's overflow threshold, and a
 // format with subnormals and man <= 21:

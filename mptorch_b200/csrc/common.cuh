@@ -24,6 +24,10 @@ inline bool valid_format(int man, int exp) { return man >= 0 && man <= 23 && exp
         }                                          \
     } while (0)
 
+struct AnyFmt;
+// Validate a public format descriptor and convert it; false (with the error set) if it is malformed.
+bool convert_format(const char* who, const mpt_format* in, AnyFmt* out);
+
 // Number of SMs of the current device (cached per device).
 int sm_count();
 

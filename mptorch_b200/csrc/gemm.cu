@@ -57,7 +57,8 @@ struct MmParams {
     float* c;
     int M, N, K;
     int64_t stride_a, stride_b, stride_c;
-    FpFmt fadd, fmul;
+    FpFmt fadd, fmul;            // float view of the formats (fast path, plan)
+    AnyFmt gadd, gmul;           // the formats as the exact path rounds them (float, superfp or binary8)
     FastRn radd, rmul;
     int rbits_add, rbits_mul;
     uint32_t seed_lo, seed_hi;
@@ -150,9 +151,9 @@ __device__ __forceinline__ void load_tiles(const MmParams& p, const float* A, co
 
 // One accumulation step on the exact path.
 template <bool FMA>
-__device__ __forceinline__ float mac_exact(float acc, float a, float b, const FpFmt& fadd, const FpFmt& fmul) {
-    if (FMA) return cast_fp_nearest(fma_rn(a, b, acc), fadd);
-    return cast_fp_nearest(add_rn(acc, cast_fp_nearest(mul_rn(a, b), fmul)), fadd);
+__device__ __forceinline__ float mac_exact(float acc, float a, float b, const AnyFmt& fadd, const AnyFmt& fmul) {
+    if (FMA) return cast_any(fma_rn(a, b, acc), fadd);
+    return cast_any(add_rn(acc, cast_any(mul_rn(a, b), fmul)), fadd);
 }
 template <bool FMA>
 __device__ __forceinline__ float mac_fast(float acc, float a, float b, const FastRn& radd, const FastRn& rmul) {
@@ -230,10 +231,10 @@ __device__ __forceinline__ void group_steps(float (&acc)[TM][TN], const float* A
                 acc[i][2] = mac_fast<FMA>(acc[i][2], a, bv.z, p.radd, p.rmul);
                 acc[i][3] = mac_fast<FMA>(acc[i][3], a, bv.w, p.radd, p.rmul);
             } else {
-                acc[i][0] = mac_exact<FMA>(acc[i][0], a, bv.x, p.fadd, p.fmul);
-                acc[i][1] = mac_exact<FMA>(acc[i][1], a, bv.y, p.fadd, p.fmul);
-                acc[i][2] = mac_exact<FMA>(acc[i][2], a, bv.z, p.fadd, p.fmul);
-                acc[i][3] = mac_exact<FMA>(acc[i][3], a, bv.w, p.fadd, p.fmul);
+                acc[i][0] = mac_exact<FMA>(acc[i][0], a, bv.x, p.gadd, p.gmul);
+                acc[i][1] = mac_exact<FMA>(acc[i][1], a, bv.y, p.gadd, p.gmul);
+                acc[i][2] = mac_exact<FMA>(acc[i][2], a, bv.z, p.gadd, p.gmul);
+                acc[i][3] = mac_exact<FMA>(acc[i][3], a, bv.w, p.gadd, p.gmul);
             }
         }
     }
@@ -364,7 +365,7 @@ __global__ void __launch_bounds__(THREADS, 2) mm_kernel(const MmParams p) {
 #pragma unroll
                         for (int i = 0; i < TM; ++i)
 #pragma unroll
-                            for (int j = 0; j < TN; ++j) { aux[i][j] = cast_fp_nearest(add_rn(aux[i][j], acc[i][j]), p.fadd); acc[i][j] = 0.0f; }
+                            for (int j = 0; j < TN; ++j) { aux[i][j] = cast_any(add_rn(aux[i][j], acc[i][j]), p.gadd); acc[i][j] = 0.0f; }
                     }
                 } else {
                     if (plan.ok && absmax_of(acc) < plan.acc_limit) group_steps<FMA, true, PACKED, ADDG>(acc, as, bs, g * 8, nk, ty, tx, p);
@@ -382,10 +383,10 @@ __global__ void __launch_bounds__(THREADS, 2) mm_kernel(const MmParams p) {
 #pragma unroll
                     for (int j = 0; j < TN; ++j) {
                         const float sum = acc[i][j], comp = aux[i][j];
-                        const float y = FMA ? cast_fp_nearest(fma_rn(a, bvv[j], -comp), p.fadd)
-                                            : cast_fp_nearest(add_rn(cast_fp_nearest(mul_rn(a, bvv[j]), p.fmul), -comp), p.fadd);
-                        const float tt = cast_fp_nearest(add_rn(sum, y), p.fadd);
-                        aux[i][j] = cast_fp_nearest(add_rn(cast_fp_nearest(add_rn(tt, -sum), p.fadd), -y), p.fadd);
+                        const float y = FMA ? cast_any(fma_rn(a, bvv[j], -comp), p.gadd)
+                                            : cast_any(add_rn(cast_any(mul_rn(a, bvv[j]), p.gmul), -comp), p.gadd);
+                        const float tt = cast_any(add_rn(sum, y), p.gadd);
+                        aux[i][j] = cast_any(add_rn(cast_any(add_rn(tt, -sum), p.gadd), -y), p.gadd);
                         acc[i][j] = tt;
                     }
                 }
@@ -468,9 +469,11 @@ double growth8_bound(int man) {
     return g * 1.0001;
 }
 
-int run_mm(const float* a, const float* b, float* c, int64_t batch, int M, int N, int K, FpFmt fadd, FpFmt fmul,
+int run_mm(const float* a, const float* b, float* c, int64_t batch, int M, int N, int K, const AnyFmt& gadd, const AnyFmt& gmul,
            int rbits_add, int rbits_mul, bool fma, int algo, uint64_t seed, void* workspace, size_t workspace_bytes,
            cudaStream_t st) {
+    const FpFmt fadd = gadd.fp, fmul = gmul.fp;
+    const bool all_float = gadd.kind == FMT_FLOAT && (fma || gmul.kind == FMT_FLOAT);
     if (batch == 0 || M == 0 || N == 0) return MPT_OK;
     if (K == 0) {   // an empty sum: every order yields +0
         cudaError_t e = cudaMemsetAsync(c, 0, sizeof(float) * (size_t)batch * M * N, st);
@@ -482,13 +485,14 @@ int run_mm(const float* a, const float* b, float* c, int64_t batch, int M, int N
     p.M = M; p.N = N; p.K = K;
     p.stride_a = (int64_t)M * K; p.stride_b = (int64_t)K * N; p.stride_c = (int64_t)M * N;
     p.fadd = fadd; p.fmul = fmul;
+    p.gadd = gadd; p.gmul = fma ? gadd : gmul;
     p.radd = FastRn::make(fadd); p.rmul = FastRn::make(fmul);
     p.rbits_add = rbits_add; p.rbits_mul = rbits_mul;
     p.seed_lo = (uint32_t)seed; p.seed_hi = (uint32_t)(seed >> 32);
     p.growth8 = (float)growth8_bound(fadd.man);
     p.stats = nullptr;
 
-    const bool fast_candidate = (algo == ALGO_SEQ || algo == ALGO_TILE8) && fast_rn_supported(fadd) &&
+    const bool fast_candidate = all_float && (algo == ALGO_SEQ || algo == ALGO_TILE8) && fast_rn_supported(fadd) &&
                                 (fma || fast_rn_supported(fmul)) && workspace != nullptr &&
                                 workspace_bytes >= sizeof(MmStats) * (size_t)batch &&
                                 (reinterpret_cast<uintptr_t>(workspace) & 15u) == 0 && K > 0;
@@ -583,8 +587,8 @@ int mpt_float_mm_nearest(const float* a, const float* b, float* c, int64_t batch
     MPT_REQUIRE(valid_format(man_add, exp_add) && valid_format(man_mul, exp_mul), "float_mm_nearest: unsupported format");
     MPT_REQUIRE(order == MPT_ORDER_SEQ || order == MPT_ORDER_CUDA, "float_mm_nearest: unknown order %d", order);
     const int algo = compensated ? ALGO_KAHAN : (order == MPT_ORDER_SEQ ? ALGO_SEQ : ALGO_TILE8);
-    return run_mm(a, b, c, batch, M, N, K, make_fmt(man_add, exp_add, subnormals, saturate),
-                  make_fmt(man_mul, exp_mul, subnormals, saturate), 0, 0, false, algo, 0, workspace, workspace_bytes,
+    return run_mm(a, b, c, batch, M, N, K, any_float(make_fmt(man_add, exp_add, subnormals, saturate)),
+                  any_float(make_fmt(man_mul, exp_mul, subnormals, saturate)), 0, 0, false, algo, 0, workspace, workspace_bytes,
                   as_stream(stream));
 }
 
@@ -604,9 +608,22 @@ int mpt_float_mm_nearest_static(const float* a, const float* b, float* c, int64_
     const int algo = compensated ? ALGO_KAHAN : (order == MPT_ORDER_SEQ ? ALGO_SEQ : ALGO_TILE8);
     // run_mm re-initialises the statistics records it uses before reading them, so whatever the previous
     // call left in the array is never seen
-    return run_mm(a, b, c, batch, M, N, K, make_fmt(man_add, exp_add, subnormals, saturate),
-                  make_fmt(man_mul, exp_mul, subnormals, saturate), 0, 0, false, algo, 0, scratch,
+    return run_mm(a, b, c, batch, M, N, K, any_float(make_fmt(man_add, exp_add, subnormals, saturate)),
+                  any_float(make_fmt(man_mul, exp_mul, subnormals, saturate)), 0, 0, false, algo, 0, scratch,
                   sizeof(MmStats) * (size_t)kStaticScratchMaxBatch, as_stream(stream));
+}
+
+int mpt_mm_nearest_fmt(const float* a, const float* b, float* c, int64_t batch, int M, int N, int K, const mpt_format* add,
+                       const mpt_format* mul, int fma, int order, void* workspace, size_t workspace_bytes, void* stream) {
+    int rc = check_mm_args("mm_nearest_fmt", a, b, c, batch, M, N, K);
+    if (rc) return rc;
+    MPT_REQUIRE(order == MPT_ORDER_SEQ || order == MPT_ORDER_CUDA, "mm_nearest_fmt: unknown order %d", order);
+    AnyFmt ga, gm;
+    if (!convert_format("mm_nearest_fmt", add, &ga)) return MPT_ERR_INVALID_ARGUMENT;
+    if (fma) gm = ga;
+    else if (!convert_format("mm_nearest_fmt", mul, &gm)) return MPT_ERR_INVALID_ARGUMENT;
+    return run_mm(a, b, c, batch, M, N, K, ga, gm, 0, 0, fma != 0, order == MPT_ORDER_SEQ ? ALGO_SEQ : ALGO_TILE8, 0, workspace,
+                  workspace_bytes, as_stream(stream));
 }
 
 int mpt_float_mm_nearest_fma(const float* a, const float* b, float* c, int64_t batch, int M, int N, int K, int man_fma,
@@ -617,7 +634,7 @@ int mpt_float_mm_nearest_fma(const float* a, const float* b, float* c, int64_t b
     MPT_REQUIRE(valid_format(man_fma, exp_fma), "float_mm_nearest_fma: unsupported format");
     MPT_REQUIRE(order == MPT_ORDER_SEQ || order == MPT_ORDER_CUDA, "float_mm_nearest_fma: unknown order %d", order);
     const int algo = compensated ? ALGO_KAHAN : (order == MPT_ORDER_SEQ ? ALGO_SEQ : ALGO_TILE8);
-    const FpFmt f = make_fmt(man_fma, exp_fma, subnormals, saturate);
+    const AnyFmt f = any_float(make_fmt(man_fma, exp_fma, subnormals, saturate));
     return run_mm(a, b, c, batch, M, N, K, f, f, 0, 0, true, algo, 0, workspace, workspace_bytes, as_stream(stream));
 }
 
@@ -627,8 +644,8 @@ int mpt_float_mm_stochastic(const float* a, const float* b, float* c, int64_t ba
     int rc = check_mm_args("float_mm_stochastic", a, b, c, batch, M, N, K);
     if (rc) return rc;
     MPT_REQUIRE(valid_format(man_add, exp_add) && (fma || valid_format(man_mul, exp_mul)), "float_mm_stochastic: unsupported format");
-    const FpFmt fa = make_fmt(man_add, exp_add, subnormals, saturate);
-    const FpFmt fm = fma ? fa : make_fmt(man_mul, exp_mul, subnormals, saturate);
+    const AnyFmt fa = any_float(make_fmt(man_add, exp_add, subnormals, saturate));
+    const AnyFmt fm = fma ? fa : any_float(make_fmt(man_mul, exp_mul, subnormals, saturate));
     return run_mm(a, b, c, batch, M, N, K, fa, fm, rbits_add, rbits_mul, fma != 0, ALGO_SR, seed, nullptr, 0, as_stream(stream));
 }
 

@@ -54,14 +54,17 @@ __device__ __forceinline__ float tree64(float p0, float p1, Op op) {
 // take the exact caster.  The choice is uniform across the launch.
 struct Caster {
     FullRn fast;
+    AnyFmt any;
     int use_fast;
-    __host__ static Caster make(const FpFmt& f) {
+    __host__ static Caster make(const AnyFmt& a) {
         Caster c;
-        c.fast = FullRn::make(f);
-        c.use_fast = fast_rn_supported(f) ? 1 : 0;
+        c.any = a;
+        c.fast = FullRn::make(a.fp);
+        c.use_fast = (a.kind == FMT_FLOAT && fast_rn_supported(a.fp)) ? 1 : 0;
         return c;
     }
-    __device__ __forceinline__ float operator()(float x) const { return use_fast ? fast(x) : cast_fp_nearest(x, fast.fmt); }
+    __host__ static Caster make(const FpFmt& f) { return make(any_float(f)); }
+    __device__ __forceinline__ float operator()(float x) const { return use_fast ? fast(x) : cast_any(x, any); }
 };
 __device__ __forceinline__ float cast_fp_nearest(float x, const Caster& c) { return c(x); }
 
@@ -80,6 +83,12 @@ struct SeqAdder {
     float growth8;    // bound of (1 + 2^-(man+1))^8
     int chain_ok;     // format supports the fast chain
     int exp8;         // 8-bit exponent: tiny values need the exact caster (see FullRn)
+    __host__ static SeqAdder make(const AnyFmt& a) {
+        SeqAdder s = make(a.fp);
+        s.q = Caster::make(a);
+        if (a.kind != FMT_FLOAT) s.chain_ok = 0;
+        return s;
+    }
     __host__ static SeqAdder make(const FpFmt& f) {
         SeqAdder s;
         s.q = Caster::make(f);
@@ -484,94 +493,99 @@ unsigned row_blocks(int64_t rows, bool tree) {
 
 using namespace mpt;
 
+namespace {
+
+mpt_format float_desc(int man, int exp, int sub, int sat) {
+    mpt_format f{};
+    f.kind = MPT_FMT_FLOAT; f.man = man; f.exp = exp; f.subnormals = sub; f.saturate = sat;
+    return f;
+}
+
+}  // namespace
+
 extern "C" {
 
-int mpt_float_softmax_forward(const float* in, float* out, int64_t outer, int channel, int64_t inner, int man_exp,
-                              int exp_exp, int man_off, int exp_off, int man_acc, int exp_acc, int subnormals,
-                              int saturate, int order, void* stream) {
+int mpt_softmax_forward_fmt(const float* in, float* out, int64_t outer, int channel, int64_t inner, const mpt_format* fexp,
+                            const mpt_format* foff, const mpt_format* facc, int order, void* stream) {
     int rc = check_geom("softmax_forward", outer, channel, inner);
     if (rc) return rc;
-    MPT_REQUIRE(valid_format(man_exp, exp_exp) && valid_format(man_off, exp_off) && valid_format(man_acc, exp_acc),
-                "softmax_forward: unsupported format");
+    AnyFmt e, o, a;
+    if (!convert_format("softmax_forward", fexp, &e) || !convert_format("softmax_forward", foff, &o) ||
+        !convert_format("softmax_forward", facc, &a)) return MPT_ERR_INVALID_ARGUMENT;
     const RowGeom g{outer * inner, channel, inner};
     if (g.rows == 0 || channel == 0) return MPT_OK;
     MPT_REQUIRE(in && out, "softmax_forward: null pointer");
-    const Caster fe = Caster::make(make_fmt(man_exp, exp_exp, subnormals, saturate)), fo = Caster::make(make_fmt(man_off, exp_off, subnormals, saturate)),
-                 fa = Caster::make(make_fmt(man_acc, exp_acc, subnormals, saturate));
+    const Caster fe = Caster::make(e), fo = Caster::make(o), fa = Caster::make(a);
     const bool tree = order != MPT_ORDER_SEQ;
     if (tree) softmax_fwd_kernel<true><<<row_blocks(g.rows, true), kWarpsPerBlock * 32, 0, as_stream(stream)>>>(in, out, g, fe, fo, fa);
     else softmax_fwd_kernel<false><<<row_blocks(g.rows, false), kWarpsPerBlock * 32, 0, as_stream(stream)>>>(in, out, g, fe, fo, fa);
     return check_launch("softmax_forward");
 }
 
-int mpt_float_softmax_lse_forward(const float* in, float* out, int64_t outer, int channel, int64_t inner, int man_off,
-                                  int exp_off, int man_lse, int exp_lse, int subnormals, int saturate, int order,
-                                  void* stream) {
+int mpt_softmax_lse_forward_fmt(const float* in, float* out, int64_t outer, int channel, int64_t inner, const mpt_format* foff,
+                                const mpt_format* flse, int order, void* stream) {
     int rc = check_geom("softmax_lse_forward", outer, channel, inner);
     if (rc) return rc;
-    MPT_REQUIRE(valid_format(man_off, exp_off) && valid_format(man_lse, exp_lse), "softmax_lse_forward: unsupported format");
+    AnyFmt o, l;
+    if (!convert_format("softmax_lse_forward", foff, &o) || !convert_format("softmax_lse_forward", flse, &l)) return MPT_ERR_INVALID_ARGUMENT;
     const RowGeom g{outer * inner, channel, inner};
     if (g.rows == 0 || channel == 0) return MPT_OK;
     MPT_REQUIRE(in && out, "softmax_lse_forward: null pointer");
-    const Caster fo = Caster::make(make_fmt(man_off, exp_off, subnormals, saturate)), fl = Caster::make(make_fmt(man_lse, exp_lse, subnormals, saturate));
+    const Caster fo = Caster::make(o), fl = Caster::make(l);
     const bool tree = order != MPT_ORDER_SEQ;
     if (tree) softmax_lse_fwd_kernel<true><<<row_blocks(g.rows, true), kWarpsPerBlock * 32, 0, as_stream(stream)>>>(in, out, g, fo, fl);
     else softmax_lse_fwd_kernel<false><<<row_blocks(g.rows, false), kWarpsPerBlock * 32, 0, as_stream(stream)>>>(in, out, g, fo, fl);
     return check_launch("softmax_lse_forward");
 }
 
-int mpt_float_softmax_backward(const float* y, const float* grad, float* out, int64_t outer, int channel, int64_t inner,
-                               int man_add, int exp_add, int man_mul, int exp_mul, int subnormals, int saturate,
-                               int order, void* stream) {
+int mpt_softmax_backward_fmt(const float* y, const float* grad, float* out, int64_t outer, int channel, int64_t inner,
+                             const mpt_format* fadd, const mpt_format* fmul, int order, void* stream) {
     int rc = check_geom("softmax_backward", outer, channel, inner);
     if (rc) return rc;
-    MPT_REQUIRE(valid_format(man_add, exp_add) && valid_format(man_mul, exp_mul), "softmax_backward: unsupported format");
+    AnyFmt a, m;
+    if (!convert_format("softmax_backward", fadd, &a) || !convert_format("softmax_backward", fmul, &m)) return MPT_ERR_INVALID_ARGUMENT;
     const RowGeom g{outer * inner, channel, inner};
     if (g.rows == 0 || channel == 0) return MPT_OK;
     MPT_REQUIRE(y && grad && out, "softmax_backward: null pointer");
-    const Caster fa = Caster::make(make_fmt(man_add, exp_add, subnormals, saturate)), fm = Caster::make(make_fmt(man_mul, exp_mul, subnormals, saturate));
+    const Caster fa = Caster::make(a), fm = Caster::make(m);
     const bool tree = order != MPT_ORDER_SEQ;
     if (tree) softmax_bwd_kernel<true><<<row_blocks(g.rows, true), kWarpsPerBlock * 32, 0, as_stream(stream)>>>(y, grad, out, g, fa, fm);
     else softmax_bwd_kernel<false><<<row_blocks(g.rows, false), kWarpsPerBlock * 32, 0, as_stream(stream)>>>(y, grad, out, g, fa, fm);
     return check_launch("softmax_backward");
 }
 
-int mpt_float_layernorm_forward(const float* in, const float* weight, const float* bias, float* out, float* mean,
-                                float* rstd, float eps, int64_t outer, int channel, int64_t inner, int man_acc,
-                                int exp_acc, int man_mul, int exp_mul, int man_div, int exp_div, int man_sqrt,
-                                int exp_sqrt, int subnormals, int saturate, int order, void* stream) {
+int mpt_layernorm_forward_fmt(const float* in, const float* weight, const float* bias, float* out, float* mean, float* rstd,
+                              float eps, int64_t outer, int channel, int64_t inner, const mpt_format* facc,
+                              const mpt_format* fmul, const mpt_format* fdiv, const mpt_format* fsqrt, int order, void* stream) {
     int rc = check_geom("layernorm_forward", outer, channel, inner);
     if (rc) return rc;
-    MPT_REQUIRE(valid_format(man_acc, exp_acc) && valid_format(man_mul, exp_mul) && valid_format(man_div, exp_div) &&
-                    valid_format(man_sqrt, exp_sqrt), "layernorm_forward: unsupported format");
+    AnyFmt a, m, d, q;
+    if (!convert_format("layernorm_forward", facc, &a) || !convert_format("layernorm_forward", fmul, &m) ||
+        !convert_format("layernorm_forward", fdiv, &d) || !convert_format("layernorm_forward", fsqrt, &q)) return MPT_ERR_INVALID_ARGUMENT;
     const RowGeom g{outer * inner, channel, inner};
     if (g.rows == 0) return MPT_OK;
     MPT_REQUIRE(channel > 0, "layernorm_forward: empty normalised shape");
     MPT_REQUIRE(in && weight && bias && out && mean && rstd, "layernorm_forward: null pointer");
-    const FpFmt facc = make_fmt(man_acc, exp_acc, subnormals, saturate);
-    const LnFmt f{Caster::make(facc), Caster::make(make_fmt(man_mul, exp_mul, subnormals, saturate)),
-                  Caster::make(make_fmt(man_div, exp_div, subnormals, saturate)), Caster::make(make_fmt(man_sqrt, exp_sqrt, subnormals, saturate)),
-                  SeqAdder::make(facc)};
+    const LnFmt f{Caster::make(a), Caster::make(m), Caster::make(d), Caster::make(q), SeqAdder::make(a)};
     const bool tree = order != MPT_ORDER_SEQ;
     if (tree) layernorm_fwd_kernel<true><<<row_blocks(g.rows, true), kWarpsPerBlock * 32, 0, as_stream(stream)>>>(in, weight, bias, out, mean, rstd, eps, g, f);
     else layernorm_fwd_kernel<false><<<row_blocks(g.rows, false), kWarpsPerBlock * 32, 0, as_stream(stream)>>>(in, weight, bias, out, mean, rstd, eps, g, f);
     return check_launch("layernorm_forward");
 }
 
-int mpt_float_layernorm_backward(const float* in, const float* grad_out, const float* weight, const float* mean,
-                                 const float* rstd, float* grad_in, float* grad_gamma, float* grad_beta, int64_t outer,
-                                 int channel, int64_t inner, int man_acc, int exp_acc, int man_mul, int exp_mul,
-                                 int man_div, int exp_div, int subnormals, int saturate, int order, void* stream) {
+int mpt_layernorm_backward_fmt(const float* in, const float* grad_out, const float* weight, const float* mean, const float* rstd,
+                               float* grad_in, float* grad_gamma, float* grad_beta, int64_t outer, int channel, int64_t inner,
+                               const mpt_format* facc, const mpt_format* fmul, const mpt_format* fdiv, int order, void* stream) {
     int rc = check_geom("layernorm_backward", outer, channel, inner);
     if (rc) return rc;
-    MPT_REQUIRE(valid_format(man_acc, exp_acc) && valid_format(man_mul, exp_mul) && valid_format(man_div, exp_div),
-                "layernorm_backward: unsupported format");
+    AnyFmt a, m, d;
+    if (!convert_format("layernorm_backward", facc, &a) || !convert_format("layernorm_backward", fmul, &m) ||
+        !convert_format("layernorm_backward", fdiv, &d)) return MPT_ERR_INVALID_ARGUMENT;
     const RowGeom g{outer * inner, channel, inner};
     if (channel == 0) return MPT_OK;
     MPT_REQUIRE(grad_gamma && grad_beta, "layernorm_backward: null pointer");
-    const FpFmt facc = make_fmt(man_acc, exp_acc, subnormals, saturate);
-    const Caster fm = Caster::make(make_fmt(man_mul, exp_mul, subnormals, saturate));
-    const LnFmt f{Caster::make(facc), fm, Caster::make(make_fmt(man_div, exp_div, subnormals, saturate)), fm, SeqAdder::make(facc)};
+    const Caster cm = Caster::make(m);
+    const LnFmt f{Caster::make(a), cm, Caster::make(d), cm, SeqAdder::make(a)};
     if (g.rows > 0) {
         MPT_REQUIRE(in && grad_out && weight && mean && rstd && grad_in, "layernorm_backward: null pointer");
         const bool tree = order != MPT_ORDER_SEQ;
@@ -583,6 +597,47 @@ int mpt_float_layernorm_backward(const float* in, const float* grad_out, const f
     colsum_kernel<0><<<(channel + kColTile - 1) / kColTile, kColsumThreads, 0, as_stream(stream)>>>(in, grad_out, mean, rstd, grad_gamma, grad_beta, g,
                                                                                                f.acc, f.mul, f.seq);
     return check_launch("layernorm_backward (parameter gradients)");
+}
+
+int mpt_float_softmax_forward(const float* in, float* out, int64_t outer, int channel, int64_t inner, int man_exp,
+                              int exp_exp, int man_off, int exp_off, int man_acc, int exp_acc, int subnormals,
+                              int saturate, int order, void* stream) {
+    const mpt_format e = float_desc(man_exp, exp_exp, subnormals, saturate), o = float_desc(man_off, exp_off, subnormals, saturate),
+                     a = float_desc(man_acc, exp_acc, subnormals, saturate);
+    return mpt_softmax_forward_fmt(in, out, outer, channel, inner, &e, &o, &a, order, stream);
+}
+
+int mpt_float_softmax_lse_forward(const float* in, float* out, int64_t outer, int channel, int64_t inner, int man_off,
+                                  int exp_off, int man_lse, int exp_lse, int subnormals, int saturate, int order,
+                                  void* stream) {
+    const mpt_format o = float_desc(man_off, exp_off, subnormals, saturate), l = float_desc(man_lse, exp_lse, subnormals, saturate);
+    return mpt_softmax_lse_forward_fmt(in, out, outer, channel, inner, &o, &l, order, stream);
+}
+
+int mpt_float_softmax_backward(const float* y, const float* grad, float* out, int64_t outer, int channel, int64_t inner,
+                               int man_add, int exp_add, int man_mul, int exp_mul, int subnormals, int saturate,
+                               int order, void* stream) {
+    const mpt_format a = float_desc(man_add, exp_add, subnormals, saturate), m = float_desc(man_mul, exp_mul, subnormals, saturate);
+    return mpt_softmax_backward_fmt(y, grad, out, outer, channel, inner, &a, &m, order, stream);
+}
+
+int mpt_float_layernorm_forward(const float* in, const float* weight, const float* bias, float* out, float* mean,
+                                float* rstd, float eps, int64_t outer, int channel, int64_t inner, int man_acc,
+                                int exp_acc, int man_mul, int exp_mul, int man_div, int exp_div, int man_sqrt,
+                                int exp_sqrt, int subnormals, int saturate, int order, void* stream) {
+    const mpt_format a = float_desc(man_acc, exp_acc, subnormals, saturate), m = float_desc(man_mul, exp_mul, subnormals, saturate),
+                     d = float_desc(man_div, exp_div, subnormals, saturate), q = float_desc(man_sqrt, exp_sqrt, subnormals, saturate);
+    return mpt_layernorm_forward_fmt(in, weight, bias, out, mean, rstd, eps, outer, channel, inner, &a, &m, &d, &q, order, stream);
+}
+
+int mpt_float_layernorm_backward(const float* in, const float* grad_out, const float* weight, const float* mean,
+                                 const float* rstd, float* grad_in, float* grad_gamma, float* grad_beta, int64_t outer,
+                                 int channel, int64_t inner, int man_acc, int exp_acc, int man_mul, int exp_mul,
+                                 int man_div, int exp_div, int subnormals, int saturate, int order, void* stream) {
+    const mpt_format a = float_desc(man_acc, exp_acc, subnormals, saturate), m = float_desc(man_mul, exp_mul, subnormals, saturate),
+                     d = float_desc(man_div, exp_div, subnormals, saturate);
+    return mpt_layernorm_backward_fmt(in, grad_out, weight, mean, rstd, grad_in, grad_gamma, grad_beta, outer, channel, inner, &a, &m, &d,
+                                      order, stream);
 }
 
 int mpt_qsum_rows(const float* in, float* out, int64_t rows, int64_t cols, int man, int exp, int subnormals, int saturate,

@@ -19,6 +19,9 @@ __all__ = [
     "fixed_point_quantize", "block_quantize", "float_quantize", "binary8_quantize", "superfp_quantize", "quantizer",
     "mx_quantize", "nvfp4_quantize",
     "mp_mm", "mp_bmm", "float_mm", "float_bmm", "fxp_mm", "fxp_bmm", "superfp_mm", "superfp_bmm",
+    "superfp_softmax_forward", "superfp_softmax_lse_forward", "superfp_softmax_backward", "binary8_softmax_forward",
+    "binary8_softmax_lse_forward", "binary8_softmax_backward", "superfp_layernorm_forward", "superfp_layernorm_backward",
+    "binary8_layernorm_forward", "binary8_layernorm_backward",
     "mp_softmax_forward", "mp_softmax_backward", "float_softmax_forward", "float_softmax_lse_forward",
     "float_softmax_backward", "mp_layernorm_forward", "mp_layernorm_backward", "float_layernorm_forward",
     "float_layernorm_backward", "qsum_rows",
@@ -263,6 +266,64 @@ def float_bmm(a: torch.Tensor, b: torch.Tensor, man_add: int = 23, exp_add: int 
     raise Exception("Wrong tensor sizes")
 
 
+def _sfp(man, exp, binades, saturate):
+    bl, bu = normalize_binades(binades)
+    return _be.Format.superfp(man, exp, bl, bu, saturate)
+
+
+def _b8(P, policy, signed, subnormals):
+    return _be.Format.binary8(P, signed, translate_overflow_policy(policy), subnormals)
+
+
+def _mm_fmt(a, b, fadd, fmul, fma):
+    """GEMM for the shape cases of float_bmm with generic rounding formats."""
+    assert a.shape[-1] == b.shape[-2]
+    assert a.device == b.device
+    _require_cuda(a, "matrix product")
+    a, b = _f32c(a), _f32c(b)
+
+    def run(a2, b2, batched):
+        if batched:
+            Bn, M, K = a2.shape
+            N = b2.shape[2]
+            c = torch.empty(Bn, M, N, device=a2.device)
+        else:
+            (M, K), N = a2.shape, b2.shape[1]
+            Bn, c = 1, torch.empty(M, N, device=a2.device)
+        _be.mm_fmt(a2, b2, c, Bn, M, N, K, fadd, fmul, fma)
+        return c
+
+    if a.dim() == 3 and b.dim() == 3:
+        return run(a, b, True)
+    if a.dim() == 3 and b.dim() == 2:
+        return run(a.reshape(-1, a.shape[2]), b, False).reshape(a.shape[0], a.shape[1], b.shape[1])
+    if a.dim() == 4 and b.dim() == 4:
+        c = run(a.reshape(-1, a.shape[2], a.shape[3]), b.reshape(-1, b.shape[2], b.shape[3]), True)
+        return c.reshape(a.shape[0], a.shape[1], a.shape[2], b.shape[3])
+    if a.dim() == 2 and b.dim() == 2:
+        return run(a, b, False)
+    raise Exception("Wrong tensor sizes")
+
+
+def superfp_mm(a: torch.Tensor, b: torch.Tensor, man_add: int = 7, exp_add: int = 8, binades_add=1, man_mul: int = 7,
+               exp_mul: int = 8, binades_mul=1, rounding: Literal["nearest", "stochastic"] = "nearest", fma: bool = True,
+               saturate: bool = False) -> torch.Tensor:
+    """GEMM with multiplies and adds rounded to supernormal-float formats.  reference: quant_function.py:1654-1732."""
+    assert len(a.shape) == 2 and len(b.shape) == 2
+    if rounding != "nearest":
+        raise NotImplementedError("SR SuperNormalFloat MM is not yet implemented")
+    return _mm_fmt(a, b, _sfp(man_add, exp_add, binades_add, saturate), _sfp(man_mul, exp_mul, binades_mul, saturate), fma)
+
+
+def superfp_bmm(a: torch.Tensor, b: torch.Tensor, man_add: int = 7, exp_add: int = 8, binades_add=1, man_mul: int = 7,
+                exp_mul: int = 8, binades_mul=1, rounding: Literal["nearest", "stochastic"] = "nearest", fma: bool = True,
+                saturate: bool = False) -> torch.Tensor:
+    """Batched variant for the shape cases of ``float_bmm``.  reference: quant_function.py:2176-2365."""
+    if rounding != "nearest":
+        raise NotImplementedError("SR SuperNormalFloat BMM is not yet implemented")
+    return _mm_fmt(a, b, _sfp(man_add, exp_add, binades_add, saturate), _sfp(man_mul, exp_mul, binades_mul, saturate), fma)
+
+
 _FP32 = FloatingPoint(exp=8, man=23, subnormals=True, saturate=False)
 
 
@@ -285,6 +346,10 @@ def _mp_matmul(fn, a, b, formats, use_forward):
         return fn(a, b, man_add=add_cfg.man, exp_add=add_cfg.exp, man_mul=mul_cfg.man, exp_mul=mul_cfg.exp, rounding=rnd,
                   fma=fma, subnormals=add_cfg.subnormals, saturate=add_cfg.saturate, compensated=formats.compensated,
                   rbits_add=formats.rbits_add, rbits_mul=formats.rbits_mul)
+    if type(add_cfg) == SuperNormalFloat:
+        sfn = superfp_mm if fn is float_mm else superfp_bmm
+        return sfn(a, b, man_add=add_cfg.man, exp_add=add_cfg.exp, binades_add=add_cfg.binades, man_mul=mul_cfg.man,
+                   exp_mul=mul_cfg.exp, binades_mul=mul_cfg.binades, rounding=rnd, fma=fma, saturate=add_cfg.saturate)
     raise NotImplementedError("matrix products in %s are outside the B200 hot path" % type(add_cfg).__name__)
 
 
@@ -340,9 +405,152 @@ def float_softmax_backward(input: torch.Tensor, grad_output: torch.Tensor, dim: 
     return out
 
 
+def _softmax_fwd(input, dim, fexp, foff, facc):
+    _require_cuda(input, "softmax_forward")
+    x = _f32c(input)
+    out = torch.empty_like(x)
+    _be.softmax_forward_fmt(x, out, dim, fexp, foff, facc)
+    return out
+
+
+def _softmax_lse(input, dim, foff, flse):
+    _require_cuda(input, "softmax_lse_forward")
+    x = _f32c(input)
+    out = torch.empty_like(x)
+    _be.softmax_lse_forward_fmt(x, out, dim, foff, flse)
+    return out
+
+
+def _softmax_bwd(input, grad_output, dim, fadd, fmul):
+    assert input.device == grad_output.device
+    _require_cuda(input, "softmax_backward")
+    y = _f32c(input)
+    out = torch.empty_like(y)
+    _be.softmax_backward_fmt(y, _f32c(grad_output), out, dim, fadd, fmul)
+    return out
+
+
+def superfp_softmax_forward(input, dim, man_exp=23, exp_exp=8, binades_exp=1, man_off=23, exp_off=8, binades_off=1, man_acc=23,
+                            exp_acc=8, binades_acc=1, rounding="nearest", saturate=False):
+    """reference: quant_function.py:637-678."""
+    assert rounding == "nearest", "Only nearest rounding softmax is implemented."
+    return _softmax_fwd(input, dim, _sfp(man_exp, exp_exp, binades_exp, saturate), _sfp(man_off, exp_off, binades_off, saturate),
+                        _sfp(man_acc, exp_acc, binades_acc, saturate))
+
+
+def superfp_softmax_lse_forward(input, dim, man_off=23, exp_off=8, binades_off=1, man_lse=23, exp_lse=8, binades_lse=1,
+                                rounding="nearest", saturate=False):
+    """reference: quant_function.py:681-714."""
+    assert rounding == "nearest", "Only nearest rounding softmax is implemented."
+    return _softmax_lse(input, dim, _sfp(man_off, exp_off, binades_off, saturate), _sfp(man_lse, exp_lse, binades_lse, saturate))
+
+
+def superfp_softmax_backward(input, grad_output, dim, man_add=23, exp_add=8, binades_add=1, man_mul=23, exp_mul=8, binades_mul=1,
+                             rounding="nearest", saturate=False):
+    """reference: quant_function.py:717-753."""
+    assert rounding == "nearest", "Only nearest rounding softmax is implemented."
+    return _softmax_bwd(input, grad_output, dim, _sfp(man_add, exp_add, binades_add, saturate), _sfp(man_mul, exp_mul, binades_mul, saturate))
+
+
+def binary8_softmax_forward(input, dim, P_exp, op_exp, signed_exp, P_off, op_off, signed_off, P_acc, op_acc, signed_acc, rounding,
+                            subnormals):
+    """reference: quant_function.py:756-789."""
+    assert rounding == "nearest", "Only nearest rounding softmax is implemented."
+    return _softmax_fwd(input, dim, _b8(P_exp, op_exp, signed_exp, subnormals), _b8(P_off, op_off, signed_off, subnormals),
+                        _b8(P_acc, op_acc, signed_acc, subnormals))
+
+
+def binary8_softmax_lse_forward(input, dim, P_off, op_off, signed_off, P_lse, op_lse, signed_lse, rounding, subnormals):
+    """reference: quant_function.py:792-819."""
+    assert rounding == "nearest", "Only nearest rounding softmax is implemented."
+    return _softmax_lse(input, dim, _b8(P_off, op_off, signed_off, subnormals), _b8(P_lse, op_lse, signed_lse, subnormals))
+
+
+def binary8_softmax_backward(input, grad_output, dim, P_add, op_add, signed_add, P_mul, op_mul, signed_mul, rounding, subnormals):
+    """reference: quant_function.py:822-852."""
+    assert rounding == "nearest", "Only nearest rounding softmax is implemented."
+    return _softmax_bwd(input, grad_output, dim, _b8(P_add, op_add, signed_add, subnormals), _b8(P_mul, op_mul, signed_mul, subnormals))
+
+
+def _layernorm_fwd(inp, weight, bias, eps, dims, facc, fmul, fdiv, fsqrt):
+    _require_cuda(inp, "layernorm_forward")
+    x = _f32c(inp)
+    lead = list(x.shape[: x.dim() - len(dims)])
+    mean = torch.empty(lead, device=x.device)
+    rstd = torch.empty(lead, device=x.device)
+    out = torch.empty_like(x)
+    _be.layernorm_forward_fmt(x, _f32c(weight), _f32c(bias), out, mean, rstd, eps, dims, facc, fmul, fdiv, fsqrt)
+    return out, mean, rstd
+
+
+def _layernorm_bwd(inp, grad_output, weight, bias, mean, rstd, dims, facc, fmul, fdiv):
+    assert inp.device == grad_output.device
+    _require_cuda(inp, "layernorm_backward")
+    x = _f32c(inp)
+    gi = torch.empty_like(x)
+    gw = torch.empty_like(weight, dtype=torch.float32).contiguous()
+    gb = torch.empty_like(bias, dtype=torch.float32).contiguous()
+    _be.layernorm_backward_fmt(x, _f32c(grad_output), _f32c(weight), _f32c(mean), _f32c(rstd), gi, gw, gb, dims, facc, fmul, fdiv)
+    return gi, gw, gb
+
+
+def superfp_layernorm_forward(inp, weight, bias, eps, dims, man_acc=23, exp_acc=8, binades_acc=1, man_mul=23, exp_mul=8,
+                              binades_mul=1, man_div=23, exp_div=8, binades_div=1, man_sqrt=23, exp_sqrt=8, binades_sqrt=1,
+                              rounding="nearest", saturate=False):
+    """reference: quant_function.py:1061-1125."""
+    assert rounding == "nearest", "Only nearest roudning layernorm is implemented."
+    return _layernorm_fwd(inp, weight, bias, eps, dims, _sfp(man_acc, exp_acc, binades_acc, saturate), _sfp(man_mul, exp_mul, binades_mul, saturate),
+                          _sfp(man_div, exp_div, binades_div, saturate), _sfp(man_sqrt, exp_sqrt, binades_sqrt, saturate))
+
+
+def superfp_layernorm_backward(inp, grad_output, weight, bias, mean, rstd, dims, man_acc=23, exp_acc=8, binades_acc=1, man_mul=23,
+                               exp_mul=8, binades_mul=1, man_div=23, exp_div=8, binades_div=1, rounding="nearest", saturate=False):
+    """reference: quant_function.py:1237-1296."""
+    assert rounding == "nearest", "Only nearest rounding layernorm is implemented."
+    return _layernorm_bwd(inp, grad_output, weight, bias, mean, rstd, dims, _sfp(man_acc, exp_acc, binades_acc, saturate),
+                          _sfp(man_mul, exp_mul, binades_mul, saturate), _sfp(man_div, exp_div, binades_div, saturate))
+
+
+def binary8_layernorm_forward(inp, weight, bias, eps, dims, P_acc, op_acc, signed_acc, P_mul, op_mul, signed_mul, P_div, op_div,
+                              signed_div, P_sqrt, op_sqrt, signed_sqrt, rounding, subnormals):
+    """reference: quant_function.py:1128-1183 (policy names are translated here; the reference passes them through
+    untranslated, which its extension rejects)."""
+    assert rounding == "nearest", "Only nearest roudning layernorm is implemented."
+    return _layernorm_fwd(inp, weight, bias, eps, dims, _b8(P_acc, op_acc, signed_acc, subnormals), _b8(P_mul, op_mul, signed_mul, subnormals),
+                          _b8(P_div, op_div, signed_div, subnormals), _b8(P_sqrt, op_sqrt, signed_sqrt, subnormals))
+
+
+def binary8_layernorm_backward(inp, grad_output, weight, bias, mean, rstd, dims, P_acc, op_acc, signed_acc, P_mul, op_mul, signed_mul,
+                               P_div, op_div, signed_div, rounding, subnormals):
+    """reference: quant_function.py:1299-1351."""
+    assert rounding == "nearest", "Only nearest rounding layernorm is implemented."
+    return _layernorm_bwd(inp, grad_output, weight, bias, mean, rstd, dims, _b8(P_acc, op_acc, signed_acc, subnormals),
+                          _b8(P_mul, op_mul, signed_mul, subnormals), _b8(P_div, op_div, signed_div, subnormals))
+
+
 def mp_softmax_forward(a: torch.Tensor, dim: int, formats) -> torch.Tensor:
     """reference: quant_function.py:382-491."""
     off_cfg = formats.fwd_off
+    if type(off_cfg) == SuperNormalFloat:
+        if not formats.use_lse:
+            e, acc = formats.fwd_exp, formats.fwd_acc
+            assert e.saturate == off_cfg.saturate and acc.saturate == off_cfg.saturate
+            return superfp_softmax_forward(a, dim, e.man, e.exp, e.binades, off_cfg.man, off_cfg.exp, off_cfg.binades, acc.man,
+                                           acc.exp, acc.binades, formats.fwd_rnd, off_cfg.saturate)
+        l = formats.fwd_lse
+        assert l.saturate == off_cfg.saturate
+        return superfp_softmax_lse_forward(a, dim, off_cfg.man, off_cfg.exp, off_cfg.binades, l.man, l.exp, l.binades,
+                                           formats.fwd_rnd, off_cfg.saturate)
+    if type(off_cfg) == Binary8:
+        if not formats.use_lse:
+            e, acc = formats.fwd_exp, formats.fwd_acc
+            assert e.subnormals == off_cfg.subnormals and acc.subnormals == off_cfg.subnormals
+            return binary8_softmax_forward(a, dim, e.P, e.overflow_policy, e.signed, off_cfg.P, off_cfg.overflow_policy, off_cfg.signed,
+                                           acc.P, acc.overflow_policy, acc.signed, formats.fwd_rnd, off_cfg.subnormals)
+        l = formats.fwd_lse
+        assert l.subnormals == off_cfg.subnormals
+        return binary8_softmax_lse_forward(a, dim, off_cfg.P, off_cfg.overflow_policy, off_cfg.signed, l.P, l.overflow_policy, l.signed,
+                                           formats.fwd_rnd, off_cfg.subnormals)
     if type(off_cfg) != FloatingPoint:
         raise NotImplementedError("Unsupported number format.")
     if not formats.use_lse:
@@ -360,6 +568,15 @@ def mp_softmax_forward(a: torch.Tensor, dim: int, formats) -> torch.Tensor:
 def mp_softmax_backward(input: torch.Tensor, grad_output: torch.Tensor, dim: int, formats) -> torch.Tensor:
     """reference: quant_function.py:494-543."""
     add_cfg = formats.bwd_add
+    mul_cfg = formats.bwd_mul
+    if type(add_cfg) == SuperNormalFloat:
+        assert mul_cfg.saturate == add_cfg.saturate
+        return superfp_softmax_backward(input, grad_output, dim, add_cfg.man, add_cfg.exp, add_cfg.binades, mul_cfg.man, mul_cfg.exp,
+                                        mul_cfg.binades, formats.bwd_rnd, add_cfg.saturate)
+    if type(add_cfg) == Binary8:
+        assert mul_cfg.subnormals == add_cfg.subnormals
+        return binary8_softmax_backward(input, grad_output, dim, add_cfg.P, add_cfg.overflow_policy, add_cfg.signed, mul_cfg.P,
+                                        mul_cfg.overflow_policy, mul_cfg.signed, formats.bwd_rnd, add_cfg.subnormals)
     if type(add_cfg) != FloatingPoint:
         raise NotImplementedError("Unsupported number format.")
     assert formats.bwd_mul.subnormals == add_cfg.subnormals
@@ -408,6 +625,14 @@ def float_layernorm_backward(inp: torch.Tensor, grad_output: torch.Tensor, weigh
 def mp_layernorm_forward(inp, weight, bias, eps, dims, formats):
     """reference: quant_function.py:855-930."""
     acc = formats.fwd_acc
+    m, d, q = formats.fwd_mul, formats.fwd_div, formats.fwd_sqrt
+    if type(acc) == SuperNormalFloat:
+        return superfp_layernorm_forward(inp, weight, bias, eps, dims, acc.man, acc.exp, acc.binades, m.man, m.exp, m.binades, d.man, d.exp,
+                                         d.binades, q.man, q.exp, q.binades, formats.fwd_rnd, acc.saturate)
+    if type(acc) == Binary8:
+        return binary8_layernorm_forward(inp, weight, bias, eps, dims, acc.P, acc.overflow_policy, acc.signed, m.P, m.overflow_policy,
+                                         m.signed, d.P, d.overflow_policy, d.signed, q.P, q.overflow_policy, q.signed, formats.fwd_rnd,
+                                         acc.subnormals)
     if type(acc) != FloatingPoint:
         raise NotImplementedError("Unsupported float type.")
     return float_layernorm_forward(inp, weight, bias, eps, dims, acc.man, acc.exp, formats.fwd_mul.man, formats.fwd_mul.exp,
@@ -418,6 +643,13 @@ def mp_layernorm_forward(inp, weight, bias, eps, dims, formats):
 def mp_layernorm_backward(inp, grad_output, weight, bias, mean, rstd, dims, formats):
     """reference: quant_function.py:933-1006."""
     acc = formats.bwd_acc
+    m, d = formats.bwd_mul, formats.bwd_div
+    if type(acc) == SuperNormalFloat:
+        return superfp_layernorm_backward(inp, grad_output, weight, bias, mean, rstd, dims, acc.man, acc.exp, acc.binades, m.man, m.exp,
+                                          m.binades, d.man, d.exp, d.binades, formats.bwd_rnd, acc.saturate)
+    if type(acc) == Binary8:
+        return binary8_layernorm_backward(inp, grad_output, weight, bias, mean, rstd, dims, acc.P, acc.overflow_policy, acc.signed, m.P,
+                                          m.overflow_policy, m.signed, d.P, d.overflow_policy, d.signed, formats.bwd_rnd, acc.subnormals)
     if type(acc) != FloatingPoint:
         raise NotImplementedError("Unsupported float type.")
     return float_layernorm_backward(inp, grad_output, weight, bias, mean, rstd, dims, acc.man, acc.exp,
@@ -442,7 +674,6 @@ def _outside(name):
 
 
 fxp_mm, fxp_bmm = _outside("fxp_mm"), _outside("fxp_bmm")
-superfp_mm, superfp_bmm = _outside("superfp_mm"), _outside("superfp_bmm")
 cublas_mm, cublas_bmm = _outside("cublas_mm"), _outside("cublas_bmm")
 
 

@@ -153,6 +153,8 @@ def partition(shape, dim):
     lo, hi = (real[0], real[0]) if isinstance(dim, int) else (real[-1], real[0])
     outer = int(np.prod(shape[:lo], dtype=np.int64))
     inner = int(np.prod(shape[hi + 1:], dtype=np.int64))
+    if outer * channel * inner != int(np.prod(shape, dtype=np.int64)):
+        raise ValueError("dims %r must be adjacent dimensions listed last-first of shape %r" % (dim, tuple(shape)))
     return outer, channel, inner
 
 

@@ -87,6 +87,8 @@ def test_partition_tensor_matches_reference_rule():
     assert backend.partition_tensor((4, 37, 5), 0) == (1, 4, 185)
     assert backend.partition_tensor((6, 5, 48), [-1]) == (30, 48, 1)
     assert backend.partition_tensor((4, 6, 8), [-1, -2]) == (4, 48, 1)
+    with pytest.raises(ValueError):          # first-to-last order makes the reference overrun the tensor: refused here
+        backend.partition_tensor((4, 6, 8), [-2, -1])
 
 
 def test_order_knobs():
