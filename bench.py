@@ -35,6 +35,11 @@ FMT = dict(man_add=2, exp_add=5, man_mul=2, exp_mul=5, subnormals=True, saturate
 # (64 lanes per SM per clock), which is the tighter bound of the two and is reported alongside.
 I_MAC = 6.99
 ALU_MAC = 3.41
+# An SM executes at most 128 fp32/int32 lane-operations per clock in total (the integer lanes share one of
+# the two fp32 datapaths), and a packed fp32x2 instruction fills two of those slots per lane.  Per MAC the
+# kernel executes 3 packed FP instructions and ALU_MAC integer ones: 2 x 3 + 3.41 datapath slots.  Packing
+# saves issue slots, not datapath slots, so this is the bound the kernel actually runs into.
+SLOTS_MAC = 2 * 3.0 + ALU_MAC
 METRIC = "float_mm GMAC/s (8192^3, e5m2 RN)"
 
 
@@ -510,9 +515,12 @@ def main() -> int:
             "roofline": {"bound": "issue", "achieved": achieved, "peak": issue_peak, "unit": "GMAC/s",
                          "frac": achieved / issue_peak, "traffic": None,
                          "alu_pipe_peak": sms * 64 * clk * 1e6 / ALU_MAC / 1e9,
+                         "datapath_peak": sms * 128 * clk * 1e6 / SLOTS_MAC / 1e9,
+                         "datapath_frac": achieved / (sms * 128 * clk * 1e6 / SLOTS_MAC / 1e9),
                          "note": "CUDA-core issue roofline: %d SMs x 128 lanes x %.0f MHz / %.2f instructions per MAC; "
-                                 "alu_pipe_peak = %d SMs x 64 ALU lanes x clock / %.1f ALU instructions per MAC"
-                                 % (sms, clk, I_MAC, sms, ALU_MAC)},
+                                 "alu_pipe_peak = %d SMs x 64 ALU lanes x clock / %.1f ALU instructions per MAC; "
+                                 "datapath_peak = SMs x 128 fp32/int32 lane slots x clock / %.2f slots per MAC "
+                                 "(a packed fp32x2 instruction takes two)" % (sms, clk, I_MAC, sms, ALU_MAC, SLOTS_MAC)},
             "roofline_quantize": {"bound": "hbm", "achieved": quant["gbs"], "peak": hbm_peak, "unit": "GB/s",
                                   "frac": quant["gbs"] / hbm_peak, "traffic": None, "peak_source": peak_src,
                                   "kernel": "float_quantize_nearest e4m3, 2^%d elements, 8 B/element" % args.quant_log2n,

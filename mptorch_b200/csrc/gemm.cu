@@ -35,8 +35,14 @@
 namespace mpt {
 namespace {
 
-constexpr int BM = 128, BN = 64, BK = 32;
-constexpr int TM = 8, TN = 4;
+#ifndef MPT_MM_TM
+#define MPT_MM_TM 8          // output rows per thread
+#endif
+#ifndef MPT_MM_MIN_CTAS
+#define MPT_MM_MIN_CTAS 2    // resident CTAs per SM the register allocation is held to
+#endif
+constexpr int TM = MPT_MM_TM, TN = 4;
+constexpr int BM = 16 * TM, BN = 64, BK = 32;
 constexpr int THREADS = 256;
 constexpr int STAGES = 3;
 constexpr int AS_LD = BK + 4;   // row stride of the A tile: keeps 16-byte chunks aligned, spreads banks
@@ -294,7 +300,7 @@ __device__ __forceinline__ FastPlan make_plan(const MmParams& p, int64_t batch) 
 }
 
 template <int ALGO, bool FMA, bool VEC, bool PACKED, bool ADDG>
-__global__ void __launch_bounds__(THREADS, 2) mm_kernel(const MmParams p) {
+__global__ void __launch_bounds__(THREADS, MPT_MM_MIN_CTAS) mm_kernel(const MmParams p) {
     extern __shared__ __align__(16) float smem[];
     float* As = smem;
     float* Bs = smem + STAGES * SMEM_A;
