@@ -343,6 +343,16 @@ struct FastRn {
     }
 };
 
+// a / b rounded to nearest even, given r = RN(1 / b) (the correctly rounded reciprocal): the quotient estimate
+// a * r is within one ulp, the remainder a - b * q is exact in one FMA, and the correction FMA lands on the correctly
+// rounded quotient (Markstein's correction step).  Exact while 1 / b, the quotient and the remainder are normal
+// numbers: callers keep 2^-20 <= |b| <= 2^20 and |a| either zero or in [2^-83, 2^64).
+MPT_HD float div_with_rcp(float a, float b, float r) {
+    const float q = mul_rn(a, r);
+    const float rem = fma_rn(-b, q, a);
+    return fma_rn(rem, r, q);
+}
+
 // Largest unbiased exponent E such that every |x| < 2^(E+1) is safe on the fast path of format
 // f: the top binade is excluded because its upper part rounds up into overflow, and
 // C = 1.5 * 2^(E - man + 23) must stay finite.

@@ -129,3 +129,34 @@ HC_API int64_t hc_sweep_full_sr(int man, int exp, int sat, int rbits, uint64_t f
     return sweep_all(first, count, stride, first_bad, [&](float x) { return full(x, word(x)); },
                      [&](float x) { return cast_fp_stochastic(x, word(x), rbits, f); });
 }
+
+// Random (a, b) pairs in the range the row kernels use div_with_rcp on: b = +-2^[-20, 20] * [1, 2), a zero or
+// +-2^[lo_exp, hi_exp] * [1, 2) with a mantissa cut to `man_a` bits (the dividends are rounded values) or full.
+// Compares with the host's IEEE division.  Returns the number of mismatches.
+HC_API int64_t hc_sweep_div_with_rcp(uint64_t seed, uint64_t count, int lo_exp, int hi_exp, int man_a, uint32_t* first_bad) {
+    int64_t bad = 0;
+    uint32_t firstbad = 0;
+#pragma omp parallel for reduction(+ : bad) schedule(static)
+    for (int64_t i = 0; i < (int64_t)count; ++i) {
+        uint64_t z = seed + 0x9E3779B97F4A7C15ull * (uint64_t)(i + 1);      // splitmix64
+        z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull; z = (z ^ (z >> 27)) * 0x94D049BB133111EBull; z ^= z >> 31;
+        uint64_t w = z * 0xD6E8FEB86659FD93ull; w ^= w >> 32;
+        const int eb = (int)(z % 41) - 20;
+        const uint32_t tb = ((uint32_t)(eb + 127) << 23) | (uint32_t)((z >> 8) & 0x7FFFFFu) | ((uint32_t)((z >> 40) & 1u) << 31);
+        const int ea = lo_exp + (int)(w % (uint64_t)(hi_exp - lo_exp + 1));
+        uint32_t ma = (uint32_t)((w >> 8) & 0x7FFFFFu);
+        if (man_a < 23) ma &= ~((1u << (23 - man_a)) - 1u);
+        const uint32_t ta = ((uint32_t)(ea + 127) << 23) | ma | ((uint32_t)((w >> 41) & 1u) << 31);
+        const float a = ((w >> 50) % 64 == 0) ? 0.0f : u2f(ta), b = u2f(tb);
+        volatile float r = 1.0f / b;
+        volatile float want = a / b;
+        const float got = div_with_rcp(a, b, r);
+        if (f2u(want) != f2u(got)) {
+            ++bad;
+#pragma omp critical
+            if (firstbad == 0) firstbad = ta;
+        }
+    }
+    if (first_bad) *first_bad = firstbad;
+    return bad;
+}

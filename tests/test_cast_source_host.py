@@ -39,6 +39,8 @@ def hc():
     L.hc_sweep_full_sr.argtypes = [i32, i32, i32, i32, u64, u64, u64, p]
     L.hc_sweep_full_rn.restype = i64
     L.hc_sweep_full_rn.argtypes = [i32, i32, i32, u64, u64, u64, p]
+    L.hc_sweep_div_with_rcp.restype = i64
+    L.hc_sweep_div_with_rcp.argtypes = [u64, u64, i32, i32, i32, p]
     return L
 
 
@@ -169,3 +171,12 @@ def test_whole_domain_fast_stochastic_equals_exact_cast(hc, fmt, sat):
     for rbits in sorted({0, 23 - m, max(0, 10 - m)}):
         _sweep(hc.hc_sweep_full_sr, (m, e, sat, rbits), 1 if (fmt == (4, 3) and rbits == 20) else 257,
                f"stochastic e{e}m{m} sat={sat} rbits={rbits}")
+
+
+@pytest.mark.parametrize("lo,hi,man", [(-83, 63, 23), (-83, 63, 2), (-83, 63, 10), (-30, 12, 23), (-4, 4, 3), (-24, 0, 10)])
+def test_division_by_row_reciprocal_is_correctly_rounded(hc, lo, hi, man):
+    """The row kernels divide a whole row by one value with a multiply and two FMAs around the correctly rounded
+    reciprocal; that must equal IEEE division over the range they use it on."""
+    first_bad = np.zeros(1, dtype=np.uint32)
+    bad = hc.hc_sweep_div_with_rcp(12345 + man, 60_000_000, lo, hi, man, _ptr(first_bad))
+    assert bad == 0, f"{bad} quotients differ from IEEE division, first dividend 0x{int(first_bad[0]):08x}"
