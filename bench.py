@@ -222,6 +222,7 @@ def run_kernels(args) -> int:
     gy = torch.randn(rows, 1024, device=dev, generator=g)
     e = att.numel()
     timed("softmax_fwd_e5m10_rows1024", lambda: q.float_softmax_forward(att, -1, 10, 5, 10, 5, 10, 5), 8 * e)
+    timed("softmax_fwd_e8m7_rows1024", lambda: q.float_softmax_forward(att, -1, 7, 8, 7, 8, 7, 8), 8 * e)
     timed("softmax_lse_fwd_e5m10_rows1024", lambda: q.float_softmax_lse_forward(att, -1, 10, 5, 10, 5), 8 * e)
     y = q.float_softmax_forward(att, -1, 10, 5, 10, 5, 10, 5)
     timed("softmax_bwd_e5m10_rows1024", lambda: q.float_softmax_backward(y, gy, -1, 10, 5, 10, 5), 12 * e)
@@ -232,6 +233,7 @@ def run_kernels(args) -> int:
     w, b = torch.randn(768, device=dev, generator=g), torch.randn(768, device=dev, generator=g)
     e = xl.numel()
     timed("layernorm_fwd_e5m10_rows768", lambda: q.float_layernorm_forward(xl, w, b, 1e-5, [-1], 10, 5, 10, 5, 10, 5, 10, 5), 8 * e)
+    timed("layernorm_fwd_e8m7_rows768", lambda: q.float_layernorm_forward(xl, w, b, 1e-5, [-1], 7, 8, 7, 8, 7, 8, 7, 8), 8 * e)
     _, mean, rstd = q.float_layernorm_forward(xl, w, b, 1e-5, [-1], 10, 5, 10, 5, 10, 5, 10, 5)
     timed("layernorm_bwd_e5m10_rows768", lambda: q.float_layernorm_backward(xl, gl, w, b, mean, rstd, [-1], 10, 5, 10, 5, 10, 5), 20 * e)
     print(json.dumps({"metric": "HBM-bound kernels, GB/s at algorithmic bytes", "unit": "GB/s", "n_gpus": 1, "steps": args.steps,

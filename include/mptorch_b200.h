@@ -85,6 +85,17 @@ MPT_API int mpt_float_quantize_stochastic_philox(const float *in, float *out, in
                                                  int prng_bits, int subnormals, int saturate,
                                                  uint64_t seed, void *stream);
 
+/* NEW, no reference counterpart: the same casts over a list of tensors in one launch per 48 tensors, for the
+ * optimizer wrappers that quantize every parameter, gradient and moment tensor of a model each step (the
+ * reference's optim_low.py:65-113 calls its quantizer once per tensor).  `in`, `out` and `n` are HOST arrays of
+ * `count` device pointers / element counts; out[i] may equal in[i].  `rounding` is an MPT_RND_* value;
+ * MPT_RND_NEAREST and MPT_RND_TRUNCATE give the bits of the single-tensor entry points, MPT_RND_STOCHASTIC uses
+ * the in-kernel Philox words (key = seed with the tensor's position in the list mixed in, counter = element
+ * index / 4).  Nothing is allocated. */
+MPT_API int mpt_float_quantize_multi(const float *const *in, float *const *out, const int64_t *n, int count,
+                                     int man, int exp, int subnormals, int saturate, int rounding,
+                                     int prng_bits, uint64_t seed, void *stream);
+
 /* replaces binary8_quantize_nearest / _stochastic / _truncate (pybind_cuda.cpp:61,107,115 ->
  * quant.cu:173-242 -> binary8_kernel.cu:278-342).  `rounding` is an MPT_RND_* value; `rand`
  * is read only for MPT_RND_STOCHASTIC. */

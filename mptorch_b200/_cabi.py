@@ -59,6 +59,7 @@ def lib() -> C.CDLL:
             "mpt_float_quantize_truncate": [p, p, i64, i32, i32, i32, i32, p],
             "mpt_float_quantize_stochastic": [p, p, p, i64, i32, i32, i32, i32, i32, p],
             "mpt_float_quantize_stochastic_philox": [p, p, i64, i32, i32, i32, i32, i32, u64, p],
+            "mpt_float_quantize_multi": [p, p, p, i32, i32, i32, i32, i32, i32, i32, u64, p],
             "mpt_binary8_quantize": [p, p, p, i64, i32, i32, i32, i32, i32, i32, p],
             "mpt_superfp_quantize_nearest": [p, p, i64, i32, i32, i32, i32, i32, p],
             "mpt_float_mm_nearest": [p, p, p, i64, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, p, sz, p],

@@ -145,6 +145,28 @@ def binary8_quantize_truncate(a, P, is_signed, overflow_policy, subnormals):
     return _binary8(a, P, is_signed, overflow_policy, subnormals, 2)
 
 
+def float_quantize_multi(ins, outs, man_bits, exp_bits, subnormals, saturate, rounding=0, prng_bits=0, seed=0):
+    """Quantize a list of tensors with one launch per 48 tensors (no reference counterpart; `rounding`: 0 nearest,
+    1 stochastic with in-kernel Philox words, 2 truncate).  `outs[i]` may be `ins[i]`."""
+    import ctypes as C
+
+    assert len(ins) == len(outs)
+    if not ins:
+        return
+    dev = ins[0].device
+    for a, o in zip(ins, outs):
+        check_cuda_f32(a, "input"); check_cuda_f32(o, "output")
+        if a.device != dev or o.device != dev or a.numel() != o.numel():
+            raise RuntimeError("float_quantize_multi: tensors must live on one device and outputs must match inputs in size")
+    n = len(ins)
+    pin = (C.c_void_p * n)(*[a.data_ptr() for a in ins])
+    pout = (C.c_void_p * n)(*[o.data_ptr() for o in outs])
+    cnt = (C.c_int64 * n)(*[a.numel() for a in ins])
+    with torch.cuda.device(dev):
+        call("mpt_float_quantize_multi", pin, pout, cnt, n, man_bits, exp_bits, int(subnormals), int(saturate), int(rounding),
+             int(prng_bits), int(seed) & 0xFFFFFFFFFFFFFFFF, stream_ptr(dev))
+
+
 def superfp_quantize_nearest(a, man_bits, exp_bits, binades_l, binades_u, saturate):
     """pybind_cuda.cpp:53."""
     check_cuda_f32(a, "a")

@@ -150,6 +150,93 @@ struct SuperFp {
     MPT_VEC_FROM_ONE
 };
 
+// ---------------------------------------------------------------------------------- many tensors, one launch
+// The optimizer wrappers quantize every parameter, gradient and moment tensor of a model each step: hundreds of
+// small tensors, one launch each in the reference (optim_low.py:65-113).  Here a launch carries a table of up to
+// kMultiMax tensors in its kernel parameters (no device-side table, so nothing is allocated); a CTA looks up the
+// tensor its block index falls into and processes one contiguous chunk of it.
+constexpr int kMultiMax = 48;
+constexpr int kMultiChunk = kThreads * 4 * kVecPerThread;     // elements per CTA
+
+struct MultiTable {
+    const float* in[kMultiMax];
+    float* out[kMultiMax];
+    int64_t n[kMultiMax];
+    int first_block[kMultiMax + 1];
+    int first_tensor;     // index of in[0] in the caller's list (decorrelates the stochastic streams)
+    int count;
+};
+
+template <class F>
+__global__ void __launch_bounds__(kThreads) multi_map_kernel(const __grid_constant__ MultiTable t, F f0) {
+    int lo = 0, hi = t.count;
+    const int b = blockIdx.x;
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (t.first_block[mid] <= b) lo = mid; else hi = mid;
+    }
+    const F f = f0.for_tensor(t.first_tensor + lo);
+    const float* __restrict__ in = t.in[lo];
+    float* __restrict__ out = t.out[lo];
+    const int64_t n = t.n[lo];
+    const int64_t begin = (int64_t)(b - t.first_block[lo]) * kMultiChunk;
+    const int64_t end = begin + kMultiChunk < n ? begin + kMultiChunk : n;
+    const bool aligned = ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15u) == 0;
+    if (aligned) {
+        const int64_t vend = begin + ((end - begin) & ~(int64_t)3);       // begin is a multiple of 4
+        for (int64_t i = begin + 4 * threadIdx.x; i < vend; i += 4 * kThreads)
+            *reinterpret_cast<float4*>(out + i) = f.vec(*reinterpret_cast<const float4*>(in + i), i);
+        const int64_t tail = vend + threadIdx.x;
+        if (tail < end) out[tail] = f.one(in[tail], tail);
+    } else {
+        for (int64_t i = begin + threadIdx.x; i < end; i += kThreads) out[i] = f.one(in[i], i);
+    }
+}
+
+template <class F>
+int launch_multi(const float* const* in, float* const* out, const int64_t* n, int count, F f, cudaStream_t st, const char* what) {
+    int i = 0;
+    while (i < count) {
+        MultiTable t{};
+        t.first_tensor = i;
+        int blocks = 0, k = 0;
+        for (; i < count && k < kMultiMax; ++i) {
+            if (n[i] == 0) continue;
+            const int64_t nb = (n[i] + kMultiChunk - 1) / kMultiChunk;
+            if (nb > 0x3FFFFFFF - blocks) break;                 // keep the block prefix inside an int: start a new launch
+            t.in[k] = in[i]; t.out[k] = out[i]; t.n[k] = n[i];
+            t.first_block[k] = blocks;
+            blocks += (int)nb;
+            ++k;
+        }
+        if (k == 0) {
+            if (i < count) { set_error("%s: tensor %d is too large for the multi-tensor path", what, i); return MPT_ERR_INVALID_ARGUMENT; }
+            break;
+        }
+        // stochastic streams are keyed by the position of the tensor in the caller's list: entries skipped as empty
+        // shift later keys, which is harmless (any key gives an independent stream)
+        t.first_block[k] = blocks;
+        t.count = k;
+        multi_map_kernel<F><<<(unsigned)blocks, kThreads, 0, st>>>(t, f);
+        const int rc = check_launch(what);
+        if (rc) return rc;
+    }
+    return MPT_OK;
+}
+
+template <class F>
+struct SameForAll : F {
+    __device__ __forceinline__ SameForAll for_tensor(int) const { return *this; }
+};
+template <class SR>
+struct PhiloxPerTensor : FpStochasticPhilox<SR> {
+    __device__ __forceinline__ PhiloxPerTensor for_tensor(int idx) const {
+        PhiloxPerTensor p = *this;
+        p.k1 ^= 0x9E3779B9u * (uint32_t)(idx + 1);
+        return p;
+    }
+};
+
 }  // namespace
 }  // namespace mpt
 
@@ -196,6 +283,31 @@ int mpt_float_quantize_stochastic_philox(const float* in, float* out, int64_t n,
                           "float_quantize_stochastic_philox");
     return launch_map(in, out, n, FpStochasticPhilox<SrExact>{SrExact{f, prng_bits}, k0, k1}, as_stream(stream),
                       "float_quantize_stochastic_philox");
+}
+
+int mpt_float_quantize_multi(const float* const* in, float* const* out, const int64_t* n, int count, int man, int exp,
+                             int subnormals, int saturate, int rounding, int prng_bits, uint64_t seed, void* stream) {
+    MPT_REQUIRE(count >= 0, "float_quantize_multi: negative tensor count");
+    if (count == 0) return MPT_OK;
+    MPT_REQUIRE(in && out && n, "float_quantize_multi: null table");
+    MPT_REQUIRE(valid_format(man, exp), "float_quantize_multi: unsupported format man=%d exp=%d", man, exp);
+    MPT_REQUIRE(rounding >= 0 && rounding <= 2, "float_quantize_multi: unknown rounding mode %d", rounding);
+    for (int i = 0; i < count; ++i)
+        MPT_REQUIRE(n[i] >= 0 && (n[i] == 0 || (in[i] && out[i])), "float_quantize_multi: tensor %d has a null pointer or a negative size", i);
+    const FpFmt f = make_fmt(man, exp, subnormals, saturate);
+    cudaStream_t st = as_stream(stream);
+    const char* who = "float_quantize_multi";
+    if (rounding == MPT_RND_NEAREST) {
+        if (fast_rn_supported(f)) return launch_multi(in, out, n, count, SameForAll<FpNearestFast>{{FullRn::make(f)}}, st, who);
+        return launch_multi(in, out, n, count, SameForAll<FpNearest>{{f}}, st, who);
+    }
+    if (rounding == MPT_RND_TRUNCATE) {
+        if (fast_rn_supported(f)) return launch_multi(in, out, n, count, SameForAll<FpTruncateFast>{{FullRz::make(f)}}, st, who);
+        return launch_multi(in, out, n, count, SameForAll<FpTruncate>{{f}}, st, who);
+    }
+    const uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
+    if (FullSr::supported(f)) return launch_multi(in, out, n, count, PhiloxPerTensor<FullSr>{{FullSr::make(f, prng_bits), k0, k1}}, st, who);
+    return launch_multi(in, out, n, count, PhiloxPerTensor<SrExact>{{SrExact{f, prng_bits}, k0, k1}}, st, who);
 }
 
 int mpt_binary8_quantize(const float* in, const int32_t* rand, float* out, int64_t n, int P, int is_signed,

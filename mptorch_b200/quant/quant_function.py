@@ -16,7 +16,7 @@ from .. import backend as _be
 from ..number import Binary8, BlockFloatingPoint, FixedPoint, FloatingPoint, Number, SuperNormalFloat
 
 __all__ = [
-    "fixed_point_quantize", "block_quantize", "float_quantize", "binary8_quantize", "superfp_quantize", "quantizer",
+    "fixed_point_quantize", "block_quantize", "float_quantize", "float_quantize_multi", "binary8_quantize", "superfp_quantize", "quantizer",
     "mx_quantize", "nvfp4_quantize",
     "mp_mm", "mp_bmm", "float_mm", "float_bmm", "fxp_mm", "fxp_bmm", "superfp_mm", "superfp_bmm",
     "superfp_softmax_forward", "superfp_softmax_lse_forward", "superfp_softmax_backward", "binary8_softmax_forward",
@@ -84,6 +84,37 @@ def float_quantize(x: torch.Tensor, exp: int, man: int,
     if prng == 0:
         prng = 23 - man
     return _be.float_quantize_stochastic(xc, man, exp, prng, subnormals, saturate)
+
+
+def float_quantize_multi(tensors, exp: int, man: int, rounding: Literal["nearest", "stochastic", "truncate"] = "nearest",
+                         subnormals: bool = True, saturate: bool = True, prng: int = 0, inplace: bool = False,
+                         seed: int | None = None):
+    """``float_quantize`` over a list of tensors with one kernel launch per 48 tensors (new; the optimizer wrapper's
+    per-tensor loops, reference optim_low.py:65-113, are its use).  Nearest and truncate give the bits of
+    ``float_quantize`` per tensor; stochastic draws Philox words inside the kernel from ``seed`` (default: one draw
+    from the torch CPU generator), so it is reproducible under ``torch.manual_seed`` but does not repeat the
+    per-tensor ``randint_like`` streams of ``float_quantize``.  Returns the list of results (the inputs themselves
+    when ``inplace``)."""
+    assert rounding in ["stochastic", "nearest", "truncate"], "invalid rounding mode, {}".format(rounding)
+    tensors = list(tensors)
+    for t in tensors:
+        _require_cuda(t, "float_quantize_multi")
+    if inplace:
+        for t in tensors:
+            if t.dtype != torch.float32 or not t.is_contiguous():
+                raise RuntimeError("float_quantize_multi(inplace=True) needs contiguous float32 tensors")
+        ins = outs = tensors
+    else:
+        ins = [_f32c(t) for t in tensors]
+        outs = [torch.empty_like(t) for t in ins]
+    mode = {"nearest": 0, "stochastic": 1, "truncate": 2}[rounding]
+    if mode == 1:
+        if prng == 0:
+            prng = 23 - man
+        if seed is None:
+            seed = int(torch.randint(0, 2**62, (1,)).item())
+    _be.float_quantize_multi(ins, outs, man, exp, subnormals, saturate, mode, prng, seed or 0)
+    return outs
 
 
 def binary8_quantize(x: torch.Tensor, P: int, rounding: Literal["nearest", "stochastic", "truncate"] = "nearest",
@@ -186,7 +217,13 @@ def quantizer(forward_number: Number | None = None, backward_number: Number | No
                 g = hook(g)
             return g
 
-    return Rounding.apply
+    def apply(x):
+        return Rounding.apply(x)
+
+    # what the function does, for callers that can fuse it (the optimizer wrapper quantizes whole parameter lists)
+    apply.forward_number, apply.forward_rounding = forward_number, forward_rounding
+    apply.backward_number, apply.backward_rounding = backward_number, backward_rounding
+    return apply
 
 
 # ------------------------------------------------------------------------------------------ GEMM

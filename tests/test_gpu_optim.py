@@ -1,0 +1,184 @@
+"""Multi-tensor quantization and the low-precision optimizer wrapper.
+
+`float_quantize_multi` must give, per tensor, the bits of `float_quantize`; `QOptim` must leave a model in exactly
+the state the reference's per-tensor wrapper (optim/optim_low.py:65-113, restated inline below) leaves it in."""
+import copy
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def q():
+    import mptorch_b200.quant as quant
+
+    return quant
+
+
+def bits_equal(a, b):
+    a, b = a.contiguous(), b.contiguous()
+    same = a.view(torch.int32) == b.view(torch.int32)
+    return bool((same | (a.isnan() & b.isnan())).all())
+
+
+SIZES = [0, 1, 3, 4, 5, 17, 255, 256, 1023, 4096, 4097, 16384, 100003, 768 * 768, 3 * 1024 * 1024 + 1]
+
+
+@pytest.mark.parametrize("fmt", [(5, 2), (4, 3), (8, 7), (5, 10), (8, 23), (3, 0)])
+@pytest.mark.parametrize("rounding", ["nearest", "truncate"])
+def test_multi_equals_single(q, fmt, rounding):
+    e, m = fmt
+    g = torch.Generator(device="cuda").manual_seed(3)
+    tensors = []
+    for i, n in enumerate(SIZES * 4):                       # 60 tensors: more than one launch
+        bits = torch.randint(-2**31, 2**31 - 1, (n,), device="cuda", generator=g, dtype=torch.int64).to(torch.int32)
+        t = bits.view(torch.float32) if i % 3 == 0 else torch.randn(n, device="cuda", generator=g) * 10.0 ** (i % 7 - 3)
+        tensors.append(t)
+    for sub in (True, False):
+        for sat in (True, False):
+            outs = q.float_quantize_multi(tensors, e, m, rounding, sub, sat)
+            assert len(outs) == len(tensors)
+            for t, o in zip(tensors, outs):
+                assert o.shape == t.shape
+                assert bits_equal(o, q.float_quantize(t, e, m, rounding, sub, sat)), (fmt, rounding, sub, sat, t.numel())
+
+
+def test_multi_unaligned_views_and_inplace(q):
+    base = torch.randn(10000, device="cuda")
+    views = [base[1:1000], base[1001:1004], base[2000:6001]]          # 4-byte aligned only; views of one buffer
+    want = [q.float_quantize(v, 4, 3, "nearest") for v in views]
+    outs = q.float_quantize_multi(views, 4, 3, "nearest")
+    assert all(bits_equal(a, b) for a, b in zip(outs, want))
+    owned = [v.clone() for v in views]
+    same = q.float_quantize_multi(owned, 4, 3, "nearest", inplace=True)
+    assert all(s is o for s, o in zip(same, owned))
+    assert all(bits_equal(a, b) for a, b in zip(owned, want))
+
+
+def test_multi_stochastic_is_seeded_unbiased_and_on_grid(q):
+    x = [torch.full((1 << 16,), 0.3, device="cuda"), torch.full((1 << 16,), 0.3, device="cuda"), torch.randn(1000, device="cuda")]
+    a = q.float_quantize_multi(x, 4, 3, "stochastic", seed=11)
+    b = q.float_quantize_multi(x, 4, 3, "stochastic", seed=11)
+    c = q.float_quantize_multi(x, 4, 3, "stochastic", seed=12)
+    assert all(bits_equal(u, v) for u, v in zip(a, b))
+    assert not bits_equal(a[0], c[0])
+    assert not bits_equal(a[0], a[1])                    # equal tensors at different list positions draw different words
+    lo, hi = 0.28125, 0.3125                             # neighbours of 0.3 in e4m3
+    assert set(a[0].unique().tolist()) <= {lo, hi}
+    assert abs(a[0].mean().item() - 0.3) < 2e-4
+    torch.manual_seed(5)
+    d = q.float_quantize_multi(x, 4, 3, "stochastic")
+    torch.manual_seed(5)
+    e = q.float_quantize_multi(x, 4, 3, "stochastic")
+    assert all(bits_equal(u, v) for u, v in zip(d, e))
+
+
+class _RefQOptim:
+    """The reference wrapper's step, one quantizer call per tensor (optim/optim_low.py:65-113)."""
+
+    def __init__(self, optim, weight_quant=None, grad_quant=None, momentum_quant=None, acc_quant=None):
+        self.optim, self.param_groups = optim, optim.param_groups
+        self.weight_quant, self.grad_quant, self.momentum_quant, self.acc_quant = weight_quant, grad_quant, momentum_quant, acc_quant
+        self.keys = ["momentum_buffer"] if isinstance(optim, torch.optim.SGD) else ["exp_avg", "exp_avg_sq"]
+        if acc_quant is not None:
+            self.weight_acc = {p: p.detach().clone() for g in self.param_groups for p in g["params"]}
+
+    def step(self):
+        if self.grad_quant is not None:
+            for g in self.param_groups:
+                for p in g["params"]:
+                    if p.grad is not None:
+                        p.grad.data = self.grad_quant(p.grad.data)
+        if self.acc_quant is not None:
+            for g in self.param_groups:
+                for p in g["params"]:
+                    p.data = self.weight_acc[p].data
+        self.optim.step()
+        if self.acc_quant is not None:
+            for g in self.param_groups:
+                for p in g["params"]:
+                    p.data = self.weight_acc[p].data = self.acc_quant(p.data).data
+        if self.weight_quant is not None:
+            for g in self.param_groups:
+                for p in g["params"]:
+                    p.data = self.weight_quant(p.data).data
+        if self.momentum_quant is not None:
+            for g in self.param_groups:
+                if isinstance(self.optim, torch.optim.SGD) and g["momentum"] == 0:
+                    continue
+                for p in g["params"]:
+                    if p.grad is None:
+                        continue
+                    st = self.optim.state[p]
+                    for k in self.keys:
+                        st[k] = self.momentum_quant(st[k])
+
+
+def _model():
+    torch.manual_seed(0)
+    return torch.nn.Sequential(torch.nn.Linear(96, 200), torch.nn.GELU(), torch.nn.LayerNorm(200), torch.nn.Linear(200, 33),
+                               torch.nn.Linear(33, 1, bias=False)).cuda()
+
+
+@pytest.mark.parametrize("kind", ["sgd", "sgd_nomomentum", "adam", "adamw"])
+def test_qoptim_equals_per_tensor_wrapper(q, kind):
+    from mptorch_b200 import FloatingPoint
+    from mptorch_b200.optim import QOptim
+
+    wq = q.quantizer(forward_number=FloatingPoint(5, 10, True, True), forward_rounding="nearest")
+    gq = q.quantizer(forward_number=FloatingPoint(5, 2, True, False), forward_rounding="nearest")
+    mq = q.quantizer(forward_number=FloatingPoint(8, 7, True, True), forward_rounding="nearest")
+    aq = q.quantizer(forward_number=FloatingPoint(6, 13, True, True), forward_rounding="nearest")
+    plain = {"w": lambda t: q.float_quantize(t, 5, 10, "nearest", True, True), "g": lambda t: q.float_quantize(t, 5, 2, "nearest", True, False),
+             "m": lambda t: q.float_quantize(t, 8, 7, "nearest", True, True), "a": lambda t: q.float_quantize(t, 6, 13, "nearest", True, True)}
+
+    def make(model):
+        ps = model.parameters()
+        if kind == "sgd":
+            return torch.optim.SGD(ps, lr=0.05, momentum=0.9)
+        if kind == "sgd_nomomentum":
+            return torch.optim.SGD(ps, lr=0.05)
+        if kind == "adam":
+            return torch.optim.Adam(ps, lr=1e-2)
+        return torch.optim.AdamW(ps, lr=1e-2, weight_decay=0.1)
+
+    m1, m2 = _model(), _model()
+    o1 = QOptim(make(m1), weight_quant=wq, grad_quant=gq, momentum_quant=mq, acc_quant=aq)
+    o2 = _RefQOptim(make(m2), weight_quant=plain["w"], grad_quant=plain["g"], momentum_quant=plain["m"], acc_quant=plain["a"])
+    g = torch.Generator(device="cuda").manual_seed(1)
+    for step in range(4):
+        x = torch.randn(64, 96, device="cuda", generator=g)
+        for m, o in ((m1, o1), (m2, o2)):
+            for p in m.parameters():
+                p.grad = None
+            m(x).square().mean().backward()
+            if step == 2:
+                list(m.parameters())[-1].grad = None          # a parameter without a gradient is skipped
+            o.step()
+        for p1, p2 in zip(m1.parameters(), m2.parameters()):
+            assert bits_equal(p1.data, p2.data), (kind, step)
+        for p1, p2 in zip(m1.parameters(), m2.parameters()):
+            s1, s2 = o1.optim.state.get(p1, {}), o2.optim.state.get(p2, {})
+            for k in o1.momentum_keys:
+                if k in s2 and s2[k] is not None:
+                    assert bits_equal(s1[k], s2[k]), (kind, step, k)
+
+
+def test_qoptim_passes_other_callables_through(q):
+    from mptorch_b200.optim import QOptim
+
+    calls = []
+
+    def wq(t):
+        calls.append(t.numel())
+        return q.float_quantize(t, 4, 3, "nearest")
+
+    m = _model()
+    o = QOptim(torch.optim.SGD(m.parameters(), lr=0.1), weight_quant=wq)
+    m(torch.randn(8, 96, device="cuda")).sum().backward()
+    o.step()
+    assert len(calls) == len(list(m.parameters()))
+    for p in m.parameters():
+        assert bits_equal(p.data, q.float_quantize(p.data, 4, 3, "nearest"))

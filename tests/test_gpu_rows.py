@@ -48,6 +48,11 @@ def nasty_rows(rows, C, seed, scale=1.0):
     x[11, 0] = 3.0e38
     x[12] *= 1e-41
     x[13, 1::3] = -0.0
+    x[14, C // 3:] = float("-inf")          # a causal-mask row
+    x[15, C // 2:] = -1.0e9                 # a finite mask value
+    x[16, ::5] = -1.0e4
+    x[17, 1:] = float("-inf")
+    x[18] = x[18] * 40.0 - 60.0             # differences around the -128 cut
     return x
 
 
