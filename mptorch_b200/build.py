@@ -50,16 +50,28 @@ def _stale(target: str, deps: list[str]) -> bool:
     return any(os.path.getmtime(d) > t for d in deps)
 
 
+def _includes(path: str, seen: set[str]) -> set[str]:
+    """Local headers a source file pulls in, transitively (`#include "..."` relative to csrc/ or include/)."""
+    import re
+
+    for name in re.findall(r'^\s*#include\s+"([^"]+)"', open(path).read(), flags=re.M):
+        for base in (CSRC, os.path.join(PKG, "..", "include")):
+            cand = os.path.normpath(os.path.join(base, name))
+            if os.path.exists(cand) and cand not in seen:
+                seen.add(cand)
+                _includes(cand, seen)
+    return seen
+
+
 def build(force: bool = False, verbose: bool = False) -> str:
     os.makedirs(LIBDIR, exist_ok=True)
     os.makedirs(OBJDIR, exist_ok=True)
-    headers = glob.glob(os.path.join(CSRC, "*.cuh")) + glob.glob(os.path.join(PKG, "..", "include", "*.h"))
     objs = []
     procs = []
     for src in sources():
         obj = os.path.join(OBJDIR, os.path.basename(src)[:-3] + ".o")
         objs.append(obj)
-        if force or _stale(obj, [src] + headers):
+        if force or _stale(obj, [src] + sorted(_includes(src, set()))):
             extra = EXTRA_FLAGS.get(os.path.basename(src), DEFAULT_EXTRA)
             cmd = [_nvcc()] + NVCC_FLAGS + extra + (["-Xptxas", "-v"] if verbose else []) + ["-c", src, "-o", obj]
             procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))

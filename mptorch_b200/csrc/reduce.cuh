@@ -3,6 +3,7 @@
 // layer normalisation, and the host-side selection of the register-resident kernels.
 #pragma once
 #include <cmath>
+#include <initializer_list>
 
 #include "cast.cuh"
 #include "common.cuh"
@@ -43,9 +44,11 @@ struct Caster {
     FullRn fast;
     AnyFmt any;
     int use_fast;
+    uint32_t neg_zero;     // what -0 rounds to: -0 in 8-bit-exponent formats, +0 in the others (as the reference does)
     __host__ static Caster make(const AnyFmt& a) {
         Caster c;
         c.any = a;
+        c.neg_zero = (a.kind == FMT_FLOAT && a.fp.exp == 8) ? 0x80000000u : 0u;
         c.fast = FullRn::make(a.fp);
         c.use_fast = (a.kind == FMT_FLOAT && fast_rn_supported(a.fp)) ? 1 : 0;
         return c;
@@ -254,22 +257,46 @@ __device__ __forceinline__ void layernorm_bwd_row(const float* x, const float* g
 // l + 32 (j odd) exactly as in the kernels above, every element is read from memory once, and the unrolled
 // loops carry no index arithmetic.
 //
-// TRUSTED = true additionally replaces every rounding by the bare 4-instruction FP-pipe form and the
+// The checked modes (MODE 1 and 2, `TRUSTED` in the kernels) replace every rounding by the bare 4-instruction FP-pipe form and the
 // per-element IEEE division by a multiply and two FMAs with the row's correctly rounded reciprocal
 // (Markstein's correction step, which returns the correctly rounded quotient).  Both are exact only while
 // every intermediate is finite and inside the range of its format, so the warp bounds all of them from the
 // maxima of its inputs (tracked with one FMNMX per element) BEFORE anything is stored; a row that fails the
 // bound, or contains NaN or infinity, is handed to the whole-domain code path above (`*_row_tree`).
-// TRUSTED needs formats with fewer than 8 exponent bits (the reference rounds fp32-denormal inputs of
-// 8-bit-exponent formats differently, which only the whole-domain rounding reproduces); the host picks it.
-template <bool TRUSTED>
-__device__ __forceinline__ float rr(const Caster& c, float x) { return TRUSTED ? c.fast.fast(x) : c.fast(x); }
+// The host picks the mode from the formats.
+// MODE 0: whole-domain rounding, no range checks.  MODE 1: bare FP-pipe rounding (every format has fewer than 8
+// exponent bits).  MODE 2: bare FP-pipe rounding for any mix of formats; 8-bit-exponent formats keep -0 (patched in
+// with a select) and round fp32-denormal inputs in their own way, so every rounding also records, branch-free,
+// whether it saw a nonzero denormal, and a row that did is handed to the whole-domain fallback like a row that
+// fails its range check.
+template <int MODE>
+__device__ __forceinline__ float rr(const Caster& c, float x, bool& odd) {
+    if (MODE == 0) return c.fast(x);
+    if (MODE == 2) {
+        const uint32_t t = __float_as_uint(x);
+        odd |= ((t & 0x7FFFFFFFu) - 1u < 0x007FFFFFu);
+        const float r = c.fast.fast(x);
+        return t == 0x80000000u ? __uint_as_float(c.neg_zero) : r;
+    }
+    return c.fast.fast(x);
+}
 
-template <bool TRUSTED>
+template <int MODE>
 struct RAdd {
     const Caster& c;
-    __device__ __forceinline__ float operator()(float a, float b) const { return rr<TRUSTED>(c, __fadd_rn(a, b)); }
+    bool& odd;
+    __device__ __forceinline__ float operator()(float a, float b) const { return rr<MODE>(c, __fadd_rn(a, b), odd); }
 };
+
+// a / b given r = RN(1 / b), for the checked modes.  MODE 2 records dividends too small for the remainder to stay a
+// normal number (0 < |a| < 2^-83); MODE 1 cannot meet one (its dividends are rounded to formats whose smallest
+// subnormal is larger).
+template <int MODE>
+__device__ __forceinline__ float row_div(float a, float b, float r, bool& odd) {
+    if (MODE == 2) odd |= ((__float_as_uint(a) & 0x7FFFFFFFu) - 1u < 0x16000000u - 1u);
+    return div_with_rcp(a, b, r);
+}
+
 // Warp-wide maximum of non-negative values in one instruction (their bit patterns order like unsigned integers; a
 // NaN pattern orders above infinity and so survives, which is what the range checks want).
 __device__ __forceinline__ float warp_max_nonneg(float v) {
@@ -321,6 +348,13 @@ inline bool rows_shape_ok(const RowGeom& g, int max_channel) {
 inline float top_of(const Caster& c) { return ldexpf(1.0f, fast_rn_exp_limit(c.any.fp) + 1); }
 inline double step_growth(const Caster& c) { return 1.0 + ldexp(1.0, -(c.any.fp.man + 1)); }
 inline bool small_exp(const Caster& c) { return c.use_fast && c.any.fp.exp < 8; }
+// Mode of the register-resident kernels for a set of formats the FP-pipe rounding supports.
+inline int rows_mode(std::initializer_list<const Caster*> cs, bool ranges_ok) {
+    if (!ranges_ok) return 0;
+    for (const Caster* c : cs)
+        if (!small_exp(*c)) return 2;
+    return 1;
+}
 
 inline RowLimits ln_limits(const LnFmt& f, int channel) {
     RowLimits lim{};
@@ -335,12 +369,13 @@ inline RowLimits ln_limits(const LnFmt& f, int channel) {
 
 #define MPT_ROWS_CASE(KERNEL, J, ...)                                                                                       \
     case J:                                                                                                                 \
-        if (trusted_) KERNEL<J, true><<<grid_, thr_, 0, st_>>>(__VA_ARGS__);                                                \
-        else KERNEL<J, false><<<grid_, thr_, 0, st_>>>(__VA_ARGS__);                                                        \
+        if (mode_ == 1) KERNEL<J, 1><<<grid_, thr_, 0, st_>>>(__VA_ARGS__);                                                 \
+        else if (mode_ == 2) KERNEL<J, 2><<<grid_, thr_, 0, st_>>>(__VA_ARGS__);                                            \
+        else KERNEL<J, 0><<<grid_, thr_, 0, st_>>>(__VA_ARGS__);                                                            \
         break;
 #define MPT_ROWS_DISPATCH(KERNEL, TRUSTED, ...)                                                                             \
     do {                                                                                                                    \
-        const bool trusted_ = (TRUSTED);                                                                                    \
+        const int mode_ = (TRUSTED);                                                                                         \
         const unsigned grid_ = row_blocks(g.rows, true);                                                                    \
         const unsigned thr_ = kWarpsPerBlock * 32;                                                                          \
         cudaStream_t st_ = as_stream(stream);                                                                               \
@@ -359,7 +394,7 @@ inline RowLimits ln_limits(const LnFmt& f, int channel) {
 #define MPT_ROWS_DISPATCH_WIDE(KERNEL, TRUSTED, ...)                                                                        \
     do {                                                                                                                    \
         if (g.channel / 32 <= 32) { MPT_ROWS_DISPATCH(KERNEL, TRUSTED, __VA_ARGS__); break; }                               \
-        const bool trusted_ = (TRUSTED);                                                                                    \
+        const int mode_ = (TRUSTED);                                                                                         \
         const unsigned grid_ = row_blocks(g.rows, true);                                                                    \
         const unsigned thr_ = kWarpsPerBlock * 32;                                                                          \
         cudaStream_t st_ = as_stream(stream);                                                                               \
@@ -372,12 +407,12 @@ inline RowLimits ln_limits(const LnFmt& f, int channel) {
 
 // Launchers of the register-resident kernels (rows_*.cu); the caller has checked rows_shape_ok and the formats.
 void launch_softmax_fwd_rows(const float* in, float* out, const RowGeom& g, const Caster& fe, const Caster& fo, const Caster& fa,
-                             bool trusted, const RowLimits& lim, void* stream);
+                             int mode, const RowLimits& lim, void* stream);
 void launch_softmax_bwd_rows(const float* y, const float* grad, float* out, const RowGeom& g, const Caster& fa, const Caster& fm,
-                             bool trusted, const RowLimits& lim, void* stream);
+                             int mode, const RowLimits& lim, void* stream);
 void launch_layernorm_fwd_rows(const float* in, const float* weight, const float* bias, float* out, float* mean, float* rstd, float eps,
-                               const RowGeom& g, const LnFmt& f, bool trusted, const RowLimits& lim, void* stream);
+                               const RowGeom& g, const LnFmt& f, int mode, const RowLimits& lim, void* stream);
 void launch_layernorm_bwd_rows(const float* in, const float* grad_out, const float* weight, const float* mean, const float* rstd,
-                               float* grad_in, const RowGeom& g, const LnFmt& f, bool trusted, const RowLimits& lim, void* stream);
+                               float* grad_in, const RowGeom& g, const LnFmt& f, int mode, const RowLimits& lim, void* stream);
 
 }  // namespace mpt

@@ -5,12 +5,13 @@
 namespace mpt {
 namespace {
 
-template <int JMAX, bool TRUSTED>
+template <int JMAX, int MODE>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32) layernorm_bwd_rows_kernel(const float* __restrict__ in, const float* __restrict__ gout,
                                                                                 const float* __restrict__ w, const float* __restrict__ mean,
                                                                                 const float* __restrict__ rstd, float* __restrict__ gin,
                                                                                 int64_t rows, int C, const __grid_constant__ LnFmt f,
                                                                                 RowLimits lim) {
+    constexpr bool TRUSTED = MODE != 0;
     const int lane = threadIdx.x & 31;
     const int64_t row = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
     if (row >= rows) return;
@@ -19,7 +20,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) layernorm_bwd_rows_kernel
     float* o = gin + row * C;
     const float fC = (float)C;
     const float m = mean[row], r = rstd[row];
-    const RAdd<TRUSTED> qacc{f.acc};
+    bool odd = false;
+    const RAdd<MODE> qacc{f.acc, odd};
     float xh[JMAX], ng[JMAX];
 #pragma unroll
     for (int j = 0; j < JMAX; ++j)
@@ -49,10 +51,10 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) layernorm_bwd_rows_kernel
             {
 #pragma unroll
                 for (int u = 0; u < 2; ++u) {
-                    const float h = rr<TRUSTED>(f.mul, __fmul_rn(rr<TRUSTED>(f.acc, __fsub_rn(xh[j + u], m)), r));
-                    const float n = rr<TRUSTED>(f.mul, ng[j + u]);
+                    const float h = rr<MODE>(f.mul, __fmul_rn(rr<MODE>(f.acc, __fsub_rn(xh[j + u], m), odd), r), odd);
+                    const float n = rr<MODE>(f.mul, ng[j + u], odd);
                     xh[j + u] = h; ng[j + u] = n;
-                    const float dot = rr<TRUSTED>(f.mul, __fmul_rn(h, n));
+                    const float dot = rr<MODE>(f.mul, __fmul_rn(h, n), odd);
                     if (u == 0) { a0 = qacc(a0, n); b0 = qacc(b0, dot); }
                     else { a1 = qacc(a1, n); b1 = qacc(b1, dot); }
                 }
@@ -70,14 +72,18 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) layernorm_bwd_rows_kernel
         }
         if (ok) {
 #pragma unroll
-            for (int j = 0; j < JMAX; ++j)
-                {
-                    const float wg = rr<TRUSTED>(f.mul, __fmul_rn(xh[j], gsx));
-                    float gi = rr<TRUSTED>(f.acc, __fsub_rn(ng[j], gs));
-                    gi = rr<TRUSTED>(f.acc, __fsub_rn(gi, wg));
-                    o[lane + 32 * j] = rr<TRUSTED>(f.mul, __fmul_rn(gi, r));
-                }
-            return;
+            for (int j = 0; j < JMAX; ++j) {
+                const float wg = rr<MODE>(f.mul, __fmul_rn(xh[j], gsx), odd);
+                float gi = rr<MODE>(f.acc, __fsub_rn(ng[j], gs), odd);
+                gi = rr<MODE>(f.acc, __fsub_rn(gi, wg), odd);
+                xh[j] = rr<MODE>(f.mul, __fmul_rn(gi, r), odd);
+            }
+            if (MODE == 2) ok = !__any_sync(0xFFFFFFFFu, odd);
+            if (ok) {
+#pragma unroll
+                for (int j = 0; j < JMAX; ++j) o[lane + 32 * j] = xh[j];
+                return;
+            }
         }
     }
     layernorm_bwd_row_cold(x, gr, w, m, r, o, C, lane, &f);
@@ -86,8 +92,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) layernorm_bwd_rows_kernel
 }  // namespace
 
 void launch_layernorm_bwd_rows(const float* in, const float* grad_out, const float* weight, const float* mean, const float* rstd,
-                               float* grad_in, const RowGeom& g, const LnFmt& f, bool trusted, const RowLimits& lim, void* stream) {
-    MPT_ROWS_DISPATCH(layernorm_bwd_rows_kernel, trusted, in, grad_out, weight, mean, rstd, grad_in, g.rows, g.channel, f, lim);
+                               float* grad_in, const RowGeom& g, const LnFmt& f, int mode, const RowLimits& lim, void* stream) {
+    MPT_ROWS_DISPATCH(layernorm_bwd_rows_kernel, mode, in, grad_out, weight, mean, rstd, grad_in, g.rows, g.channel, f, lim);
 }
 
 }  // namespace mpt

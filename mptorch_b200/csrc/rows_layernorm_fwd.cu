@@ -5,19 +5,21 @@
 namespace mpt {
 namespace {
 
-template <int JMAX, bool TRUSTED>
+template <int JMAX, int MODE>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32) layernorm_fwd_rows_kernel(const float* __restrict__ in, const float* __restrict__ w,
                                                                                 const float* __restrict__ bias, float* __restrict__ out,
                                                                                 float* __restrict__ mean, float* __restrict__ rstd, float eps,
                                                                                 int64_t rows, int C, const __grid_constant__ LnFmt f,
                                                                                 RowLimits lim) {
+    constexpr bool TRUSTED = MODE != 0;
     const int lane = threadIdx.x & 31;
     const int64_t row = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
     if (row >= rows) return;
     const float* x = in + row * C;
     float* y = out + row * C;
     const float fC = (float)C;
-    const RAdd<TRUSTED> qacc{f.acc};
+    bool odd = false;
+    const RAdd<MODE> qacc{f.acc, odd};
     float v[JMAX];
 #pragma unroll
     for (int j = 0; j < JMAX; ++j)
@@ -47,10 +49,10 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) layernorm_fwd_rows_kernel
 #pragma unroll
         for (int j = 0; j < JMAX; j += 2)
             {
-                const float d0 = rr<TRUSTED>(f.acc, __fsub_rn(v[j], m)), d1 = rr<TRUSTED>(f.acc, __fsub_rn(v[j + 1], m));
+                const float d0 = rr<MODE>(f.acc, __fsub_rn(v[j], m), odd), d1 = rr<MODE>(f.acc, __fsub_rn(v[j + 1], m), odd);
                 v[j] = d0; v[j + 1] = d1;
-                s0 = qacc(s0, rr<TRUSTED>(f.mul, __fmul_rn(d0, d0)));
-                s1 = qacc(s1, rr<TRUSTED>(f.mul, __fmul_rn(d1, d1)));
+                s0 = qacc(s0, rr<MODE>(f.mul, __fmul_rn(d0, d0), odd));
+                s1 = qacc(s1, rr<MODE>(f.mul, __fmul_rn(d1, d1), odd));
             }
         const float vsum = tree64(s0, s1, qacc);
         const float var = __fdiv_rn(vsum, fC);
@@ -68,15 +70,16 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) layernorm_fwd_rows_kernel
 #pragma unroll
             for (int j = 0; j < JMAX; ++j)
                 {
-                    const float q = TRUSTED ? div_with_rcp(v[j], sd, rs) : __fdiv_rn(v[j], sd);
-                    const float p = __fmul_rn(w[lane + 32 * j], rr<TRUSTED>(f.div, q));
+                    const float q = TRUSTED ? row_div<MODE>(v[j], sd, rs, odd) : __fdiv_rn(v[j], sd);
+                    const float p = __fmul_rn(w[lane + 32 * j], rr<MODE>(f.div, q, odd));
                     if (TRUSTED) pm = fmaxf(pm, fabsf(p));
-                    v[j] = __fadd_rn(rr<TRUSTED>(f.mul, p), bias[lane + 32 * j]);
+                    v[j] = __fadd_rn(rr<MODE>(f.mul, p, odd), bias[lane + 32 * j]);
                 }
             if (TRUSTED) {
                 pm = warp_max_nonneg(pm);
                 // fmaxf skips a NaN product (a NaN weight); the trusted rounding turns it into NaN as the exact one does
                 ok = pm < lim.top[1];
+                if (MODE == 2) ok = ok && !__any_sync(0xFFFFFFFFu, odd);
             }
             if (ok) {
 #pragma unroll
@@ -96,8 +99,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) layernorm_fwd_rows_kernel
 }  // namespace
 
 void launch_layernorm_fwd_rows(const float* in, const float* weight, const float* bias, float* out, float* mean, float* rstd, float eps,
-                               const RowGeom& g, const LnFmt& f, bool trusted, const RowLimits& lim, void* stream) {
-    MPT_ROWS_DISPATCH_WIDE(layernorm_fwd_rows_kernel, trusted, in, weight, bias, out, mean, rstd, eps, g.rows, g.channel, f, lim);
+                               const RowGeom& g, const LnFmt& f, int mode, const RowLimits& lim, void* stream) {
+    MPT_ROWS_DISPATCH_WIDE(layernorm_fwd_rows_kernel, mode, in, weight, bias, out, mean, rstd, eps, g.rows, g.channel, f, lim);
 }
 
 }  // namespace mpt

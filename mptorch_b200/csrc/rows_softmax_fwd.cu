@@ -5,11 +5,12 @@
 namespace mpt {
 namespace {
 
-template <int JMAX, bool TRUSTED>
+template <int JMAX, int MODE>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32) softmax_fwd_rows_kernel(const float* __restrict__ in, float* __restrict__ out,
                                                                               int64_t rows, int C, const __grid_constant__ Caster fexp,
                                                                               const __grid_constant__ Caster foff,
                                                                               const __grid_constant__ Caster facc, RowLimits lim) {
+    constexpr bool TRUSTED = MODE != 0;
     const int lane = threadIdx.x & 31;
     const int64_t row = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
     if (row >= rows) return;
@@ -24,16 +25,16 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) softmax_fwd_rows_kernel(c
     for (int j = 0; j < JMAX; j += 2)
         { m0 = fmaxf(m0, v[j]); m1 = fmaxf(m1, v[j + 1]); }
     const float mx = tree64(m0, m1, FMax{});
-    bool ok = true;
+    bool ok = true, odd = false;
     {
-        const RAdd<TRUSTED> qadd{facc};
+        const RAdd<MODE> qadd{facc, odd};
         float s0 = 0.f, s1 = 0.f;
 #pragma unroll
         for (int j = 0; j < JMAX; j += 2)
             {
                 const float d0 = __fsub_rn(v[j], mx), d1 = __fsub_rn(v[j + 1], mx);
-                float e0 = rr<TRUSTED>(fexp, expf(rr<TRUSTED>(foff, d0)));
-                float e1 = rr<TRUSTED>(fexp, expf(rr<TRUSTED>(foff, d1)));
+                float e0 = rr<MODE>(fexp, expf(rr<MODE>(foff, d0, odd)), odd);
+                float e1 = rr<MODE>(fexp, expf(rr<MODE>(foff, d1, odd)), odd);
                 if (TRUSTED) {
                     // x - max <= -128 (masked entries, -inf included) rounds to a value <= -128 in any format that reaches
                     // 128, whose exponential is exactly zero; everything else lies in (-128, 0], inside the fast range.
@@ -51,9 +52,13 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) softmax_fwd_rows_kernel(c
             if (ok) {
                 const float r = __frcp_rn(sum);
 #pragma unroll
-                for (int j = 0; j < JMAX; ++j)
-                    y[lane + 32 * j] = div_with_rcp(v[j], sum, r);
-                return;
+                for (int j = 0; j < JMAX; ++j) v[j] = row_div<MODE>(v[j], sum, r, odd);
+                if (MODE == 2) ok = !__any_sync(0xFFFFFFFFu, odd);
+                if (ok) {
+#pragma unroll
+                    for (int j = 0; j < JMAX; ++j) y[lane + 32 * j] = v[j];
+                    return;
+                }
             }
         } else {
 #pragma unroll
@@ -68,8 +73,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) softmax_fwd_rows_kernel(c
 }  // namespace
 
 void launch_softmax_fwd_rows(const float* in, float* out, const RowGeom& g, const Caster& fe, const Caster& fo, const Caster& fa,
-                             bool trusted, const RowLimits& lim, void* stream) {
-    MPT_ROWS_DISPATCH_WIDE(softmax_fwd_rows_kernel, trusted, in, out, g.rows, g.channel, fe, fo, fa, lim);
+                             int mode, const RowLimits& lim, void* stream) {
+    MPT_ROWS_DISPATCH_WIDE(softmax_fwd_rows_kernel, mode, in, out, g.rows, g.channel, fe, fo, fa, lim);
 }
 
 }  // namespace mpt

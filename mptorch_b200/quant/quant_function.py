@@ -18,7 +18,7 @@ from ..number import Binary8, BlockFloatingPoint, FixedPoint, FloatingPoint, Num
 __all__ = [
     "fixed_point_quantize", "block_quantize", "float_quantize", "float_quantize_multi", "binary8_quantize", "superfp_quantize", "quantizer",
     "mx_quantize", "nvfp4_quantize",
-    "mp_mm", "mp_bmm", "float_mm", "float_bmm", "fxp_mm", "fxp_bmm", "superfp_mm", "superfp_bmm",
+    "mp_mm", "mp_bmm", "float_mm", "float_mm_streamed", "float_bmm", "fxp_mm", "fxp_bmm", "superfp_mm", "superfp_bmm",
     "superfp_softmax_forward", "superfp_softmax_lse_forward", "superfp_softmax_backward", "binary8_softmax_forward",
     "binary8_softmax_lse_forward", "binary8_softmax_backward", "superfp_layernorm_forward", "superfp_layernorm_backward",
     "binary8_layernorm_forward", "binary8_layernorm_backward",
@@ -275,6 +275,67 @@ def float_mm(a: torch.Tensor, b: torch.Tensor, man_add: int = 23, exp_add: int =
     _require_cuda(a, "float_mm")
     return _mm_dispatch(_f32c(a), _f32c(b), False, man_add, exp_add, man_mul, exp_mul, rounding, fma, subnormals,
                         saturate, compensated, rbits_add, rbits_mul)
+
+
+def float_mm_streamed(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, *, device=None, block_rows: int = 1024,
+                      man_add: int = 23, exp_add: int = 8, man_mul: int = 23, exp_mul: int = 8,
+                      rounding: Literal["nearest", "stochastic"] = "nearest", fma: bool = True, subnormals: bool = True,
+                      saturate: bool = True, compensated: bool = False, rbits_add: int = 0, rbits_mul: int = 0) -> torch.Tensor:
+    """``float_mm`` for operands that live in HOST memory (new; the reference would run them on the CPU).
+
+    B is copied to the GPU once; A travels in blocks of ``block_rows`` rows on a copy stream while the previous block
+    is in the kernel and the one before that returns to the host on a third stream, so the copies of A and C overlap
+    the arithmetic.  Rows of C are independent, so the bits equal one ``float_mm`` call on the whole matrices
+    (nearest rounding; the stochastic kernel's words are keyed by output position within a call, so its blocks draw
+    as separate calls do).  ``a``, ``b`` and ``out`` must be pinned float32 CPU tensors for the copies to overlap;
+    pageable tensors work but serialise.  Returns ``out`` (allocated pinned when not given); the call returns after
+    the last block has arrived."""
+    assert len(a.shape) == 2 and len(b.shape) == 2 and a.shape[1] == b.shape[0]
+    for t in (a, b):
+        if t.is_cuda or t.dtype != torch.float32 or not t.is_contiguous():
+            raise RuntimeError("float_mm_streamed takes contiguous float32 CPU tensors (use float_mm for CUDA tensors)")
+    if not torch.cuda.is_available():
+        raise RuntimeError("float_mm_streamed: no CUDA device (there is no CPU fallback)")
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    M, K = a.shape
+    N = b.shape[1]
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.float32).pin_memory()
+    assert out.shape == (M, N) and out.dtype == torch.float32 and not out.is_cuda and out.is_contiguous()
+    block_rows = max(1, min(int(block_rows), M)) if M else 1
+    kw = (man_add, exp_add, man_mul, exp_mul, rounding, fma, subnormals, saturate, compensated, rbits_add, rbits_mul)
+    with torch.cuda.device(dev):
+        main = torch.cuda.current_stream(dev)
+        s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+        bd = b.to(dev, non_blocking=True)
+        abuf = [torch.empty(block_rows, K, device=dev) for _ in range(2)]
+        a_free = [None, None]          # event: the kernel that read abuf[i] has finished
+        c_done = []                    # C blocks in flight to the host (kept alive until the final synchronisation)
+        s_in.wait_stream(main)
+        for i, r0 in enumerate(range(0, M, block_rows)):
+            r1 = min(M, r0 + block_rows)
+            slot = i & 1
+            with torch.cuda.stream(s_in):
+                if a_free[slot] is not None:
+                    s_in.wait_event(a_free[slot])
+                ad = abuf[slot][: r1 - r0]
+                ad.copy_(a[r0:r1], non_blocking=True)
+                arrived = torch.cuda.Event()
+                arrived.record(s_in)
+            main.wait_event(arrived)
+            cd = _mm_dispatch(ad, bd, False, *kw)
+            a_free[slot] = torch.cuda.Event()
+            a_free[slot].record(main)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(a_free[slot])
+                out[r0:r1].copy_(cd, non_blocking=True)
+            cd.record_stream(s_out)
+            c_done.append(cd)
+        s_out.synchronize()
+        main.synchronize()
+        for t in abuf:
+            t.record_stream(s_in)
+    return out
 
 
 def float_bmm(a: torch.Tensor, b: torch.Tensor, man_add: int = 23, exp_add: int = 8, man_mul: int = 23, exp_mul: int = 8,

@@ -264,3 +264,26 @@ def test_full_size_row_samples_and_sharding(be, oracle, fmts):
         be.float_quantize_nearest_mm(a, b, c, S, S, S, fadd[1], fadd[0], fmul[1], fmul[0], True, False, False, order="seq")
         want = oracle.mm(a[rows[:2]].cpu().numpy(), b.cpu().numpy(), fadd[1], fadd[0], fmul[1], fmul[0], True, False, False, "seq")
         assert same_bits(c[rows[:2]].cpu().numpy(), want)
+
+
+def test_streamed_host_operands_equal_one_call():
+    """float_mm_streamed (host operands, row blocks overlapped with the copies) gives the bits of one float_mm call."""
+    import mptorch_b200.quant as q
+
+    torch.manual_seed(3)
+    a = torch.randn(1000, 384).pin_memory()
+    b = torch.randn(384, 520).pin_memory()
+    want = q.float_mm(a.cuda(), b.cuda(), man_add=2, exp_add=5, man_mul=2, exp_mul=5, rounding="nearest", fma=False,
+                      subnormals=True, saturate=False).cpu()
+    for block in (128, 333, 1000, 4096):
+        got = q.float_mm_streamed(a, b, block_rows=block, man_add=2, exp_add=5, man_mul=2, exp_mul=5, rounding="nearest", fma=False,
+                                  subnormals=True, saturate=False)
+        assert got.is_pinned() and torch.equal(got.view(torch.int32), want.view(torch.int32)), block
+    out = torch.empty(1000, 520)                       # pageable output and inputs still work
+    got = q.float_mm_streamed(a.clone(), b.clone(), out=out, block_rows=256, man_add=10, exp_add=5, man_mul=3, exp_mul=4,
+                              rounding="nearest", fma=True, subnormals=True, saturate=False)
+    want = q.float_mm(a.cuda(), b.cuda(), man_add=10, exp_add=5, man_mul=3, exp_mul=4, rounding="nearest", fma=True,
+                      subnormals=True, saturate=False).cpu()
+    assert got is out and torch.equal(got.view(torch.int32), want.view(torch.int32))
+    with pytest.raises(RuntimeError):
+        q.float_mm_streamed(a.cuda(), b)
