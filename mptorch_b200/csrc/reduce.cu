@@ -169,88 +169,105 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) layernorm_bwd_dx_kernel(c
 // the work by role: a CTA owns 32 columns; eight producer warps stream row tiles (64 rows x 32 columns,
 // coalesced 128-byte row segments), do the per-element arithmetic that does not depend on the running sum
 // (for layernorm: x-hat * dy, recomputed from the inputs instead of staged through the reference's scratch
-// tensor, fp_kernel.cu:481-487) and park the addends in shared memory; one consumer warp (lane = column)
-// walks the parked tile in row order through the rounded adds.  Tiles are double buffered: the consumer
-// works on tile t while the producers fetch tile t + 1, with one barrier per tile.
-constexpr int kColTile = 32;        // columns per CTA
-constexpr int kRowTile = 64;        // rows per tile (two buffers of two tensors stay within 48 KB of static shared memory)
-constexpr int kProducerWarps = 8;
-constexpr int kColsumThreads = (kProducerWarps + 1) * 32;
+// tensor, fp_kernel.cu:481-487) and park the addends in shared memory; one consumer warp per chain (lane =
+// column) walks the parked tile in row order through the rounded adds, 32 rows per range check so that the
+// dependent adds run back to back.  Tiles are double buffered: the consumers work on tile t while the producers
+// fetch tile t + 1, with one barrier per tile.
+// A chain's speed is set by the latency of its dependent adds, not by how many columns share a CTA, so the tile
+// is narrow: 8 columns per CTA puts four times as many SMs to work on the per-element arithmetic of the producers
+// (a 32-byte sector per row and tensor).  A producer warp covers 4 rows x 8 columns per load.
+constexpr int kColTile = 8;         // columns per CTA
+constexpr int kRowTile = 64;        // rows per tile
+constexpr int kProducerWarps = 2;   // 32 rows of a tile each
+constexpr int kColsumThreads(int mode) { return (kProducerWarps + (mode == 0 ? 2 : 1)) * 32; }
 
 // MODE 0: layernorm parameter gradients (two chains: x-hat*dy -> out0, dy -> out1).  MODE 1: plain column sum of `in`.
 template <int MODE>
-__global__ void __launch_bounds__(kColsumThreads) colsum_kernel(const float* __restrict__ in, const float* __restrict__ gout,
+__global__ void __launch_bounds__(kColsumThreads(MODE)) colsum_kernel(const float* __restrict__ in, const float* __restrict__ gout,
                                                                 const float* __restrict__ mean, const float* __restrict__ rstd,
                                                                 float* __restrict__ out0, float* __restrict__ out1, RowGeom g,
                                                                 Caster facc, Caster fmul, SeqAdder seq) {
     __shared__ float sA[2][kRowTile][kColTile];
     __shared__ float sB[MODE == 0 ? 2 : 1][MODE == 0 ? kRowTile : 1][kColTile];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int col = blockIdx.x * kColTile + lane;
+    const int cl = lane & (kColTile - 1), rs = lane / kColTile;      // column within the tile, row within a 4-row group
+    const int col = blockIdx.x * kColTile + cl;
     const bool col_ok = col < g.channel;
     const int64_t st = g.inner;
     const int64_t ntiles = (g.rows + kRowTile - 1) / kRowTile;
 
-    auto produce = [&](int64_t t) {      // producer warps: rows warp, warp + 8, ... of the tile
+    // Producer warp w: rows 32 w .. 32 w + 31 of a tile, eight loads of 4 rows x 8 columns.  The loads of tile t + 2
+    // are issued before the arithmetic of tile t + 1, so a tile's memory latency hides behind the previous tile's work.
+    static_assert(kRowTile == 32 * kProducerWarps && kColTile == 8, "eight loads of 4 rows x 8 columns per producer warp");
+    struct Tile { float xv[8], gv[8], mv[8], rv[8]; };
+    auto load = [&](int64_t t, Tile& T) {
+        const int64_t r0 = t * kRowTile + warp * 32 + rs;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int64_t row = r0 + 4 * u;
+            const bool ok = col_ok && row < g.rows;
+            const int64_t idx = ok ? row_base(g, row) + col * st : 0;
+            T.xv[u] = ok ? in[idx] : 0.f;
+            if (MODE == 0) { T.gv[u] = ok ? gout[idx] : 0.f; T.mv[u] = ok ? mean[row] : 0.f; T.rv[u] = ok ? rstd[row] : 0.f; }
+        }
+    };
+    auto finish = [&](int64_t t, const Tile& T) {
         const int buf = (int)(t & 1);
-        const int64_t r0 = t * kRowTile;
-        constexpr int PER = kRowTile / kProducerWarps;     // rows per producer warp, in batches of 8
 #pragma unroll
-        for (int h = 0; h < PER / 8; ++h) {
-            float xv[8], gv[8], mv[8], rv[8];
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                const int lr = warp * PER + h * 8 + u;
-                const int64_t row = r0 + lr;
-                const bool ok = col_ok && row < g.rows;
-                const int64_t idx = ok ? row_base(g, row) + col * st : 0;
-                xv[u] = ok ? in[idx] : 0.f;
-                if (MODE == 0) { gv[u] = ok ? gout[idx] : 0.f; mv[u] = ok ? mean[row] : 0.f; rv[u] = ok ? rstd[row] : 0.f; }
-            }
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                const int lr = warp * PER + h * 8 + u;
-                if (MODE == 0) {
-                    const float xhat = fmul(__fmul_rn(facc(__fsub_rn(xv[u], mv[u])), rv[u]));
-                    sA[buf][lr][lane] = fmul(__fmul_rn(xhat, gv[u]));
-                    sB[buf][lr][lane] = gv[u];
-                } else {
-                    sA[buf][lr][lane] = xv[u];
-                }
+        for (int u = 0; u < 8; ++u) {
+            const int lr = warp * 32 + 4 * u + rs;
+            if (MODE == 0) {
+                const float xhat = fmul(__fmul_rn(facc(__fsub_rn(T.xv[u], T.mv[u])), T.rv[u]));
+                sA[buf][lr][cl] = fmul(__fmul_rn(xhat, T.gv[u]));
+                sB[buf][lr][cl] = T.gv[u];
+            } else {
+                sA[buf][lr][cl] = T.xv[u];
             }
         }
     };
 
-    float acc0 = 0.f, acc1 = 0.f;
-    if (warp < kProducerWarps && ntiles > 0) produce(0);
+    float acc = 0.f;
+    const int chain = warp - kProducerWarps;          // consumer warps: 0 sums sA into out0, 1 sums sB into out1
+    Tile cur, nxt;
+    if (warp < kProducerWarps && ntiles > 0) {
+        load(0, cur);
+        if (ntiles > 1) load(1, nxt);
+        finish(0, cur);
+    }
     __syncthreads();
     for (int64_t t = 0; t < ntiles; ++t) {
         if (warp < kProducerWarps) {
-            if (t + 1 < ntiles) produce(t + 1);
+            if (t + 1 < ntiles) {
+                cur = nxt;
+                if (t + 2 < ntiles) load(t + 2, nxt);
+                finish(t + 1, cur);
+            }
         } else {
             const int buf = (int)(t & 1);
+            const float (*src)[kColTile] = (MODE == 0 && chain == 1) ? sB[buf] : sA[buf];
             const int64_t left = g.rows - t * kRowTile;
             const int nrows = left < kRowTile ? (int)left : kRowTile;
             int r = 0;
-            for (; r + 8 <= nrows; r += 8) {
-                float a[8], b[8];
+            for (; r + 32 <= nrows; r += 32) {
+                float v[32];
 #pragma unroll
-                for (int u = 0; u < 8; ++u) { a[u] = sA[buf][r + u][lane]; if (MODE == 0) b[u] = sB[buf][r + u][lane]; }
-                acc0 = seq.add(acc0, a);
-                if (MODE == 0) acc1 = seq.add(acc1, b);
+                for (int u = 0; u < 32; ++u) v[u] = src[r + u][cl];
+                acc = seq.add(acc, v);
+            }
+            for (; r + 8 <= nrows; r += 8) {
+                float v[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) v[u] = src[r + u][cl];
+                acc = seq.add(acc, v);
             }
             for (; r < nrows; ++r) {
-                const float a[1] = {sA[buf][r][lane]};
-                acc0 = seq.add(acc0, a);
-                if (MODE == 0) { const float b[1] = {sB[buf][r][lane]}; acc1 = seq.add(acc1, b); }
+                const float v[1] = {src[r][cl]};
+                acc = seq.add(acc, v);
             }
         }
         __syncthreads();
     }
-    if (warp == kProducerWarps && col_ok) {
-        out0[col] = acc0;
-        if (MODE == 0) out1[col] = acc1;
-    }
+    if (warp >= kProducerWarps && lane < kColTile && col_ok) (chain == 0 ? out0 : out1)[col] = acc;
 }
 
 int check_geom(const char* who, int64_t outer, int channel, int64_t inner) {
@@ -394,7 +411,7 @@ int mpt_layernorm_backward_fmt(const float* in, const float* grad_out, const flo
         rc = check_launch("layernorm_backward (input gradient)");
         if (rc) return rc;
     }
-    colsum_kernel<0><<<(channel + kColTile - 1) / kColTile, kColsumThreads, 0, as_stream(stream)>>>(in, grad_out, mean, rstd, grad_gamma, grad_beta, g,
+    colsum_kernel<0><<<(channel + kColTile - 1) / kColTile, kColsumThreads(0), 0, as_stream(stream)>>>(in, grad_out, mean, rstd, grad_gamma, grad_beta, g,
                                                                                                f.acc, f.mul, f.seq);
     return check_launch("layernorm_backward (parameter gradients)");
 }
@@ -449,7 +466,7 @@ int mpt_qsum_rows(const float* in, float* out, int64_t rows, int64_t cols, int m
     const FpFmt f = make_fmt(man, exp, subnormals, saturate);
     MPT_REQUIRE(cols <= 0x7FFFFFFF, "qsum_rows: too many columns");
     const RowGeom g{rows, (int)cols, 1};      // a [rows, cols] matrix: outer = rows, channel = cols, inner = 1
-    colsum_kernel<1><<<(unsigned)((cols + kColTile - 1) / kColTile), kColsumThreads, 0, as_stream(stream)>>>(in, nullptr, nullptr, nullptr, out, nullptr, g,
+    colsum_kernel<1><<<(unsigned)((cols + kColTile - 1) / kColTile), kColsumThreads(1), 0, as_stream(stream)>>>(in, nullptr, nullptr, nullptr, out, nullptr, g,
                                                                                                         Caster::make(f), Caster::make(f), SeqAdder::make(f));
     return check_launch("qsum_rows");
 }

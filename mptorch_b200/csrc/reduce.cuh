@@ -20,6 +20,7 @@ struct RowGeom {
 };
 
 __device__ __forceinline__ int64_t row_base(const RowGeom& g, int64_t row) {
+    if (g.inner == 1) return row * (int64_t)g.channel;       // contiguous rows: no 64-bit division
     return (row / g.inner) * (int64_t)g.channel * g.inner + row % g.inner;
 }
 
@@ -63,14 +64,15 @@ struct QAdd {
     __device__ __forceinline__ float operator()(float a, float b) const { return f(__fadd_rn(a, b)); }
 };
 
-// Eight sequential rounded additions acc = Q(acc + v[u]).  When the running sum provably stays inside the
+// U sequential rounded additions acc = Q(acc + v[u]).  When the running sum provably stays inside the
 // range where the 4-instruction FP-pipe rounding is exact, the chain uses it (a dependent step is then
-// about 20 cycles instead of about 150), otherwise the exact caster.
+// about 20 cycles instead of about 150), otherwise the exact caster.  The bound: acc is a value of the format,
+// so rounding acc + v moves the sum by at most |v| (acc itself is a candidate), and every intermediate stays
+// below |acc| + 2 * sum |v|.
 struct SeqAdder {
     Caster q;
     FastRn r;
     float top;        // 2^(limit exponent + 1): every intermediate |sum| must stay below
-    float growth8;    // bound of (1 + 2^-(man+1))^8
     int chain_ok;     // format supports the fast chain
     int exp8;         // 8-bit exponent: tiny values need the exact caster (see FullRn)
     __host__ static SeqAdder make(const AnyFmt& a) {
@@ -84,9 +86,6 @@ struct SeqAdder {
         s.q = Caster::make(f);
         s.r = FastRn::make(f);
         s.top = ldexpf(1.0f, fast_rn_exp_limit(f) + 1);
-        double g = 1.0;
-        for (int i = 0; i < 8; ++i) g *= 1.0 + ldexp(1.0, -(f.man + 1));
-        s.growth8 = (float)(g * 1.0001);
         s.chain_ok = fast_rn_supported(f) ? 1 : 0;
         s.exp8 = f.exp == 8;
         return s;
@@ -101,7 +100,7 @@ struct SeqAdder {
             tiny |= (__float_as_uint(v[u]) & 0x7FFFFFFFu) - 1u < 0x0CFFFFFFu;     // 0 < |v| < 2^-101
         }
         tiny |= (__float_as_uint(acc) & 0x7FFFFFFFu) - 1u < 0x0CFFFFFFu;
-        const bool fast = chain_ok && (fabsf(acc) + (float)U * vmax) * growth8 < top && !(exp8 && tiny);
+        const bool fast = chain_ok && (fabsf(acc) + (float)(2 * U) * vmax) * 1.0001f < top && !(exp8 && tiny);
         if (fast) {
 #pragma unroll
             for (int u = 0; u < U; ++u) acc = r(__fadd_rn(acc, v[u]));
