@@ -236,6 +236,26 @@ def run_kernels(args) -> int:
     timed("layernorm_fwd_e8m7_rows768", lambda: q.float_layernorm_forward(xl, w, b, 1e-5, [-1], 7, 8, 7, 8, 7, 8, 7, 8), 8 * e)
     _, mean, rstd = q.float_layernorm_forward(xl, w, b, 1e-5, [-1], 10, 5, 10, 5, 10, 5, 10, 5)
     timed("layernorm_bwd_e5m10_rows768", lambda: q.float_layernorm_backward(xl, gl, w, b, mean, rstd, [-1], 10, 5, 10, 5, 10, 5), 20 * e)
+    # QConv2d forward (ResNet-style 3x3 layer, 64 -> 64 channels, 56 x 56, batch 64): implicit GEMM vs unfold + GEMM
+    import mptorch_b200.quant.modules as qmod
+    from mptorch_b200 import FloatingPoint
+
+    nb = max(1, int(64 * scale))
+    fmt = q.QAffineFormats(fwd_mac=(FloatingPoint(5, 10, True, False), FloatingPoint(4, 3, True, False)),
+                           bwd_mac=(FloatingPoint(5, 10, True, False), FloatingPoint(4, 3, True, False)))
+    conv = q.QConv2d(64, 64, 3, fmt, padding=1).to(dev)
+    xc = torch.randn(nb, 64, 56, 56, device=dev, generator=g)
+    conv_macs = nb * 56 * 56 * 64 * 64 * 9
+    with torch.no_grad():
+        timed("qconv2d_fwd_implicit_gemm", lambda: conv(xc), 0)
+        eligible = qmod.implicit_conv_eligible
+        qmod.implicit_conv_eligible = lambda f, t: False
+        try:
+            timed("qconv2d_fwd_unfold_gemm", lambda: conv(xc), 0)
+        finally:
+            qmod.implicit_conv_eligible = eligible
+    for k in ("qconv2d_fwd_implicit_gemm", "qconv2d_fwd_unfold_gemm"):
+        out[k] = {"ms": out[k]["ms"], "gmacs": round(conv_macs / out[k]["ms"] / 1e6, 1)}
     print(json.dumps({"metric": "HBM-bound kernels, GB/s at algorithmic bytes", "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
                       "hbm_peak_gbs": hbm_peak, "kernels": out}))
     return 0

@@ -143,6 +143,20 @@ MPT_API int mpt_float_mm_nearest_static(const float *a, const float *b, float *c
                                         int man_add, int exp_add, int man_mul, int exp_mul,
                                         int subnormals, int saturate, int compensated, int order, void *stream);
 
+/* NEW (the reference's QConv2d materialises the unfolded input, conv.py:591-617, and multiplies it with
+ * float_quantize_nearest_mm / _mm_fma): 2-D convolution as an implicit GEMM with the same product order
+ * (channel, kernel row, kernel column) and the same accumulation orders, reading the NCHW input in place.
+ *   x  [n_img, c_in, H, W]; y [n_img, c_out, OH, OW] with OH = (H + 2 pad_h - dil_h (KH - 1) - 1) / stride_h + 1;
+ *   wt [groups][c_in / groups * KH * KW][c_out / groups]: per group the weight matrix TRANSPOSED (K rows, outputs
+ *      contiguous), i.e. weight[g].reshape(c_out / groups, K).t().contiguous().
+ * Zero padding only (other modes: pad the input first).  Bias is not added.  `workspace` as for mpt_float_mm_nearest
+ * with batch = 1.  With fma != 0 every step is one fused multiply-add rounded to (man_add, exp_add). */
+MPT_API int mpt_float_conv2d_nearest(const float *x, const float *wt, float *y, int n_img, int c_in, int H, int W,
+                                     int c_out, int groups, int KH, int KW, int stride_h, int stride_w, int pad_h,
+                                     int pad_w, int dil_h, int dil_w, int man_add, int exp_add, int man_mul,
+                                     int exp_mul, int subnormals, int saturate, int fma, int order, void *workspace,
+                                     size_t workspace_bytes, void *stream);
+
 /* replaces float_quantize_nearest_mm_fma and _bmm_fma (pybind_cuda.cpp:157,173 -> quant.cu ->
  * fp_kernel.cu:247-307 -> mm_kernel.h:134-246): acc = Q(fmaf(a, b, acc)). */
 MPT_API int mpt_float_mm_nearest_fma(const float *a, const float *b, float *c, int64_t batch, int M, int N, int K,

@@ -230,6 +230,22 @@ def float_quantize_nearest_bmm_fma(a, b, c, M, N, K, man_fma, exp_fma, subnormal
     _mm_nearest_fma(a, b, c, _batch_of(a), M, N, K, man_fma, exp_fma, subnormals, saturate, compensated, order)
 
 
+def float_conv2d_nearest(x, wt, y, groups, kernel_size, stride, padding, dilation, man_add, exp_add, man_mul, exp_mul,
+                         subnormals, saturate, fma=False, order=None):
+    """2-D convolution as an implicit GEMM (new; no pybind counterpart: the reference unfolds the input and calls
+    float_quantize_nearest_mm).  ``x`` [N, C, H, W], ``y`` [N, C_out, OH, OW], ``wt`` the per-group transposed
+    weight matrices [groups, C / groups * KH * KW, C_out / groups], all contiguous float32 on one device."""
+    check_cuda_f32(x, "x"); check_cuda_f32(wt, "wt"); check_cuda_f32(y, "y")
+    n, c, h, w = x.shape
+    c_out = y.shape[1]
+    with torch.cuda.device(x.device):
+        ws = _cabi.mm_workspace(x.device, 1)
+        call("mpt_float_conv2d_nearest", ptr(x), ptr(wt), ptr(y), n, c, h, w, c_out, groups, kernel_size[0], kernel_size[1],
+             stride[0], stride[1], padding[0], padding[1], dilation[0], dilation[1], man_add, exp_add, man_mul, exp_mul,
+             int(subnormals), int(saturate), int(bool(fma)), _order_code(order, "accum_order"), ptr(ws), ws.numel(),
+             stream_ptr(x.device))
+
+
 def _mm_sr(a, b, c, batch, M, N, K, man_add, exp_add, rbits_add, man_mul, exp_mul, rbits_mul, subnormals, saturate,
            fma, seed):
     _mm_checks(a, b, c)

@@ -57,7 +57,17 @@ struct MmStats {
     uint32_t minnz_a, minnz_b;   // smallest nonzero |x| bit pattern, 0xFFFFFFFF if all zero
 };
 
+// Convolution as an implicit GEMM: row m of A is output position (image, oh, ow), column k is (channel, kh, kw) in
+// that order (the order of F.unfold and of the reference's unfoldNd, conv.py:591-617), and the element is read
+// straight from the NCHW input (zero outside the image), so the unfolded matrix never exists.  C is written to the
+// NCHW output.
+struct ConvGeom {
+    int H, W, KH, KW, OH, OW, sh, sw, ph, pw, dh, dw;
+    int64_t x_image_stride, y_image_stride;      // elements between consecutive images of input and output
+};
+
 struct MmParams {
+    ConvGeom cv;                 // used by the CONV instantiations only
     const float* a;
     const float* b;
     float* c;
@@ -111,9 +121,38 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 
 // Stage one K slab: As[m][k] (row stride AS_LD) and Bs[k][n].  Elements outside the matrices are
 // zero filled (cp.async with a source size of 0), which is also how K is zero padded.
-template <bool VEC>
+struct ConvRow { int64_t base; int ih0, iw0; };     // per output position: image offset, top-left input coordinate
+
+template <bool VEC, bool CONV = false>
 __device__ __forceinline__ void load_tiles(const MmParams& p, const float* A, const float* B, float* As, float* Bs,
-                                           int m0, int n0, int k0, int tid) {
+                                           int m0, int n0, int k0, int tid, const ConvRow* rows = nullptr) {
+    if (CONV) {
+        // A: the thread's column of the slab is fixed (tid & 31), its rows are (tid >> 5) + 8 u
+        const int kk = tid & 31, gk = k0 + kk;
+        const int khkw = p.cv.KH * p.cv.KW;
+        const int ch = gk / khkw, rem = gk - ch * khkw;
+        const int kh = rem / p.cv.KW, kw = rem - kh * p.cv.KW;
+        const bool kok = gk < p.K;
+        const int dih = kh * p.cv.dh, diw = kw * p.cv.dw;
+        const int64_t coff = (int64_t)ch * p.cv.H * p.cv.W;
+#pragma unroll 4
+        for (int u = 0; u < BM / 8; ++u) {
+            const int row = (tid >> 5) + 8 * u;
+            const ConvRow r = rows[row];
+            const int ih = r.ih0 + dih, iw = r.iw0 + diw;
+            const bool ok = kok && (unsigned)ih < (unsigned)p.cv.H && (unsigned)iw < (unsigned)p.cv.W;
+            cp_async4(As + row * AS_LD + kk, ok ? A + r.base + coff + (int64_t)ih * p.cv.W + iw : A, ok ? 4 : 0);
+        }
+#pragma unroll 4
+        for (int u = 0; u < (BK * BN) / THREADS; ++u) {
+            const int c = tid + u * THREADS;
+            const int kr = c >> 6, nn = c & 63;
+            const int gk2 = k0 + kr, gn = n0 + nn;
+            const bool ok = gk2 < p.K && gn < p.N;
+            cp_async4(Bs + kr * BN + nn, ok ? B + (int64_t)gk2 * p.N + gn : B, ok ? 4 : 0);
+        }
+        return;
+    }
     if (VEC) {
 #pragma unroll
         for (int u = 0; u < (BM * BK / 4) / THREADS; ++u) {
@@ -299,11 +338,12 @@ __device__ __forceinline__ FastPlan make_plan(const MmParams& p, int64_t batch) 
     return plan;
 }
 
-template <int ALGO, bool FMA, bool VEC, bool PACKED, bool ADDG>
+template <int ALGO, bool FMA, bool VEC, bool PACKED, bool ADDG, bool CONV = false>
 __global__ void __launch_bounds__(THREADS, MPT_MM_MIN_CTAS) mm_kernel(const MmParams p) {
     extern __shared__ __align__(16) float smem[];
     float* As = smem;
     float* Bs = smem + STAGES * SMEM_A;
+    ConvRow* crow = reinterpret_cast<ConvRow*>(smem + STAGES * (SMEM_A + SMEM_B));      // CONV: BM entries
 
     const int tid = threadIdx.x;
     const int ty = tid >> 4, tx = tid & 15;
@@ -320,6 +360,25 @@ __global__ void __launch_bounds__(THREADS, MPT_MM_MIN_CTAS) mm_kernel(const MmPa
 
     const FastPlan plan = (ALGO == ALGO_SEQ || ALGO == ALGO_TILE8) ? make_plan<ALGO, FMA>(p, batch) : FastPlan{false, 0.0f};
 
+    if (CONV) {
+        if (tid < BM) {
+            const int gm = m0 + tid;
+            ConvRow r;
+            if (gm < p.M) {
+                const int L = p.cv.OH * p.cv.OW;
+                const int img = gm / L, l = gm - img * L;
+                const int oh = l / p.cv.OW, ow = l - oh * p.cv.OW;
+                r.base = (int64_t)img * p.cv.x_image_stride;
+                r.ih0 = oh * p.cv.sh - p.cv.ph;
+                r.iw0 = ow * p.cv.sw - p.cv.pw;
+            } else {
+                r.base = 0; r.ih0 = -(1 << 30); r.iw0 = -(1 << 30);      // fails every bounds check: zero rows
+            }
+            crow[tid] = r;
+        }
+        __syncthreads();
+    }
+
     float acc[TM][TN];    // running sum (inner sum for ALGO_TILE8)
     float aux[TM][TN];    // outer sum (ALGO_TILE8) or compensation term (ALGO_KAHAN)
 #pragma unroll
@@ -329,7 +388,7 @@ __global__ void __launch_bounds__(THREADS, MPT_MM_MIN_CTAS) mm_kernel(const MmPa
 
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s) {
-        if (s < ntiles) load_tiles<VEC>(p, A, B, As + s * SMEM_A, Bs + s * SMEM_B, m0, n0, s * BK, tid);
+        if (s < ntiles) load_tiles<VEC, CONV>(p, A, B, As + s * SMEM_A, Bs + s * SMEM_B, m0, n0, s * BK, tid, crow);
         cp_async_commit();
     }
 
@@ -338,7 +397,7 @@ __global__ void __launch_bounds__(THREADS, MPT_MM_MIN_CTAS) mm_kernel(const MmPa
         __syncthreads();
         {
             const int nt = t + STAGES - 1;
-            if (nt < ntiles) load_tiles<VEC>(p, A, B, As + (nt % STAGES) * SMEM_A, Bs + (nt % STAGES) * SMEM_B, m0, n0, nt * BK, tid);
+            if (nt < ntiles) load_tiles<VEC, CONV>(p, A, B, As + (nt % STAGES) * SMEM_A, Bs + (nt % STAGES) * SMEM_B, m0, n0, nt * BK, tid, crow);
             cp_async_commit();
         }
         const float* as = As + (t % STAGES) * SMEM_A;
@@ -426,6 +485,23 @@ __global__ void __launch_bounds__(THREADS, MPT_MM_MIN_CTAS) mm_kernel(const MmPa
     cp_async_wait<0>();
 
     // epilogue
+    if (CONV) {     // C[m][n] goes to y[image][n][oh][ow]: consecutive m are consecutive addresses
+        const int L = p.cv.OH * p.cv.OW;
+#pragma unroll
+        for (int i = 0; i < TM; ++i) {
+            const int gm = m0 + ty + 16 * i;
+            if (gm >= p.M) continue;
+            const int img = gm / L, l = gm - img * L;
+            const float* r = (ALGO == ALGO_TILE8) ? aux[i] : acc[i];
+            float* dst = C + (int64_t)img * p.cv.y_image_stride + l;
+#pragma unroll
+            for (int j = 0; j < TN; ++j) {
+                const int gn = n0 + tx * 4 + j;
+                if (gn < p.N) dst[(int64_t)gn * L] = r[j];
+            }
+        }
+        return;
+    }
     const bool vec_store = VEC && ((reinterpret_cast<uintptr_t>(C) & 15u) == 0);
 #pragma unroll
     for (int i = 0; i < TM; ++i) {
@@ -467,6 +543,19 @@ int launch_mm(const MmParams& p, int64_t batch, bool vec, cudaStream_t st) {
     if (e != cudaSuccess) { set_error("float_mm: cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return MPT_ERR_CUDA; }
     kern<<<grid, THREADS, SMEM_BYTES, st>>>(p);
     return check_launch("float_mm");
+}
+
+// Convolution launch: scalar operand copies (the gather has no 16-byte runs), packed fast path.
+template <int ALGO, bool FMA>
+int launch_conv(const MmParams& p, cudaStream_t st) {
+    dim3 grid((p.N + BN - 1) / BN, (p.M + BM - 1) / BM, 1);
+    const bool add_guard = FMA || (p.fmul.min_exp - p.fmul.man) < (p.fadd.min_exp - p.fadd.man);
+    auto kern = add_guard ? mm_kernel<ALGO, FMA, false, true, true, true> : mm_kernel<ALGO, FMA, false, true, FMA, true>;
+    const size_t smem = SMEM_BYTES + BM * sizeof(ConvRow);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) { set_error("float_conv2d: cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return MPT_ERR_CUDA; }
+    kern<<<grid, THREADS, smem, st>>>(p);
+    return check_launch("float_conv2d");
 }
 
 double growth8_bound(int man) {
@@ -529,6 +618,61 @@ int run_mm(const float* a, const float* b, float* c, int64_t batch, int M, int N
         case ALGO_SR * 2 + 0: return launch_mm<ALGO_SR, false>(p, batch, vec, st);
         default: return launch_mm<ALGO_SR, true>(p, batch, vec, st);
     }
+}
+
+int run_conv(const float* x, const float* wt, float* y, int n_img, int c_in, int H, int W, int c_out, int groups, int KH, int KW,
+             int sh, int sw, int ph, int pw, int dh, int dw, const FpFmt& fadd, const FpFmt& fmul, bool fma, int algo,
+             void* workspace, size_t workspace_bytes, cudaStream_t st) {
+    const int OH = (H + 2 * ph - dh * (KH - 1) - 1) / sh + 1, OW = (W + 2 * pw - dw * (KW - 1) - 1) / sw + 1;
+    if (n_img == 0 || c_out == 0 || OH <= 0 || OW <= 0) return MPT_OK;
+    const int cg = c_in / groups, og = c_out / groups;
+    const int64_t M64 = (int64_t)n_img * OH * OW, K64 = (int64_t)cg * KH * KW;
+    MPT_REQUIRE(M64 <= 0x7FFFFFFF && K64 <= 0x7FFFFFFF, "float_conv2d: problem too large");
+    MPT_REQUIRE((M64 + BM - 1) / BM <= 65535, "float_conv2d: more than 65535 row tiles (images x output positions too large)");
+    MmParams p;
+    p.cv = ConvGeom{H, W, KH, KW, OH, OW, sh, sw, ph, pw, dh, dw, (int64_t)c_in * H * W, (int64_t)c_out * OH * OW};
+    p.M = (int)M64; p.N = og; p.K = (int)K64;
+    p.stride_a = p.stride_b = p.stride_c = 0;
+    p.fadd = fadd; p.fmul = fma ? fadd : fmul;
+    p.gadd = any_float(fadd); p.gmul = any_float(fma ? fadd : fmul);
+    p.radd = FastRn::make(fadd); p.rmul = FastRn::make(p.fmul);
+    p.rbits_add = p.rbits_mul = 0; p.seed_lo = p.seed_hi = 0;
+    p.growth8 = (float)growth8_bound(fadd.man);
+    p.stats = nullptr;
+    const bool fast_candidate = fast_rn_supported(fadd) && (fma || fast_rn_supported(fmul)) && workspace != nullptr &&
+                                workspace_bytes >= sizeof(MmStats) && (reinterpret_cast<uintptr_t>(workspace) & 15u) == 0 && K64 > 0;
+    if (K64 == 0) {
+        cudaError_t e = cudaMemsetAsync(y, 0, sizeof(float) * (size_t)n_img * c_out * OH * OW, st);
+        if (e != cudaSuccess) { set_error("float_conv2d: cudaMemsetAsync: %s", cudaGetErrorString(e)); return MPT_ERR_CUDA; }
+        return MPT_OK;
+    }
+    if (fast_candidate) {
+        // one record for all groups: the maxima over the whole input and the whole weight bound every group's products
+        MmStats* s = static_cast<MmStats*>(workspace);
+        stats_init_kernel<<<1, 256, 0, st>>>(s, 1);
+        const int64_t nx = (int64_t)n_img * c_in * H * W, nw = (int64_t)c_out * K64;
+        const int sms = sm_count();
+        auto grid = [&](int64_t n) { int64_t g = (n + 255) / 256; const int64_t cap = (int64_t)sms * 8; return dim3((unsigned)(g > cap ? cap : (g < 1 ? 1 : g)), 1); };
+        stats_kernel<<<grid(nx), 256, 0, st>>>(x, nx, s, 0);
+        stats_kernel<<<grid(nw), 256, 0, st>>>(wt, nw, s, 1);
+        int rc = check_launch("float_conv2d statistics");
+        if (rc) return rc;
+        p.stats = s;
+    }
+    for (int g = 0; g < groups; ++g) {
+        p.a = x + (int64_t)g * cg * H * W;
+        p.b = wt + (int64_t)g * K64 * og;
+        p.c = y + (int64_t)g * og * OH * OW;
+        int rc;
+        switch (algo * 2 + (fma ? 1 : 0)) {
+            case ALGO_SEQ * 2 + 0: rc = launch_conv<ALGO_SEQ, false>(p, st); break;
+            case ALGO_SEQ * 2 + 1: rc = launch_conv<ALGO_SEQ, true>(p, st); break;
+            case ALGO_TILE8 * 2 + 0: rc = launch_conv<ALGO_TILE8, false>(p, st); break;
+            default: rc = launch_conv<ALGO_TILE8, true>(p, st); break;
+        }
+        if (rc) return rc;
+    }
+    return MPT_OK;
 }
 
 int check_mm_args(const char* who, const float* a, const float* b, float* c, int64_t batch, int M, int N, int K) {
@@ -630,6 +774,24 @@ int mpt_mm_nearest_fmt(const float* a, const float* b, float* c, int64_t batch, 
     else if (!convert_format("mm_nearest_fmt", mul, &gm)) return MPT_ERR_INVALID_ARGUMENT;
     return run_mm(a, b, c, batch, M, N, K, ga, gm, 0, 0, fma != 0, order == MPT_ORDER_SEQ ? ALGO_SEQ : ALGO_TILE8, 0, workspace,
                   workspace_bytes, as_stream(stream));
+}
+
+int mpt_float_conv2d_nearest(const float* x, const float* wt, float* y, int n_img, int c_in, int H, int W, int c_out, int groups,
+                             int KH, int KW, int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w, int man_add,
+                             int exp_add, int man_mul, int exp_mul, int subnormals, int saturate, int fma, int order,
+                             void* workspace, size_t workspace_bytes, void* stream) {
+    MPT_REQUIRE(n_img >= 0 && c_in >= 0 && H >= 0 && W >= 0 && c_out >= 0, "float_conv2d_nearest: negative extent");
+    MPT_REQUIRE(groups >= 1 && c_in % groups == 0 && c_out % groups == 0, "float_conv2d_nearest: channels not divisible by groups=%d", groups);
+    MPT_REQUIRE(KH >= 1 && KW >= 1 && stride_h >= 1 && stride_w >= 1 && dil_h >= 1 && dil_w >= 1 && pad_h >= 0 && pad_w >= 0,
+                "float_conv2d_nearest: invalid kernel / stride / padding / dilation");
+    MPT_REQUIRE(valid_format(man_add, exp_add) && (fma || valid_format(man_mul, exp_mul)), "float_conv2d_nearest: unsupported format");
+    MPT_REQUIRE(order == MPT_ORDER_SEQ || order == MPT_ORDER_CUDA, "float_conv2d_nearest: unknown order %d", order);
+    MPT_REQUIRE((int64_t)c_in * H * W <= 0x7FFFFFFF, "float_conv2d_nearest: one input image exceeds 2^31 elements");
+    const bool empty = n_img == 0 || c_out == 0;
+    MPT_REQUIRE(empty || (x && wt && y), "float_conv2d_nearest: null pointer");
+    return run_conv(x, wt, y, n_img, c_in, H, W, c_out, groups, KH, KW, stride_h, stride_w, pad_h, pad_w, dil_h, dil_w,
+                    make_fmt(man_add, exp_add, subnormals, saturate), make_fmt(fma ? man_add : man_mul, fma ? exp_add : exp_mul, subnormals, saturate),
+                    fma != 0, order == MPT_ORDER_SEQ ? ALGO_SEQ : ALGO_TILE8, workspace, workspace_bytes, as_stream(stream));
 }
 
 int mpt_float_mm_nearest_fma(const float* a, const float* b, float* c, int64_t batch, int M, int N, int K, int man_fma,

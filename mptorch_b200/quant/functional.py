@@ -9,11 +9,11 @@ from typing import Callable
 import torch
 
 from ..number import FloatingPoint, FloatType
-from .quant_format import QAffineFormats, QLayerNormFormats, QSoftmaxFormats, make_quant_function
+from .quant_format import QAffineFormats, QLayerNormFormats, QSoftmaxFormats, id_quant, make_quant_function
 from .quant_function import (mp_bmm, mp_layernorm_backward, mp_layernorm_forward, mp_mm, mp_softmax_backward,
                              mp_softmax_forward, qsum_rows)
 
-__all__ = ["qlinear", "qmm", "qmatmul", "qsoftmax", "qlayernorm", "qsum", "compute_bias", "scale", "unscale"]
+__all__ = ["qlinear", "qconv2d", "qmm", "qmatmul", "qsoftmax", "qlayernorm", "qsum", "compute_bias", "scale", "unscale"]
 
 
 # ------------------------------------------------------------------------------------------ tensor scaling
@@ -172,6 +172,101 @@ def qlinear(input: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None
             formats: QAffineFormats = QAffineFormats()) -> torch.Tensor:
     """Functional form of ``QLinear`` (reference functional.py:176-208)."""
     return qlinear_kernel.apply(input, weight, bias, formats)
+
+
+# ------------------------------------------------------------------------------------------ convolution
+def _conv_cols(x, kernel_size, dilation, padding, stride):
+    """[N, C, H, W] -> [N * L, C * kh * kw], K ordered channel, kernel row, kernel column (reference conv.py:591-617)."""
+    cols = torch.nn.functional.unfold(x, kernel_size, dilation=dilation, padding=padding, stride=stride)
+    return cols.transpose(1, 2).reshape(-1, cols.shape[1])
+
+
+def implicit_conv_eligible(formats, input) -> bool:
+    """The implicit-GEMM path gives the bits of the unfold + GEMM composition when the forward MACs are float formats
+    with nearest rounding (plain or compensated sums excluded), no tensor scaling is in play, and the input quantizer
+    rounds deterministically (a stochastic one would draw once per input element instead of once per unfolded copy)."""
+    if not input.is_cuda or formats.fwd_use_default_prec or formats.use_scaling or formats.compensated:
+        return False
+    if formats.fwd_rnd != "nearest" or not isinstance(formats.fwd_add, FloatingPoint) or not isinstance(formats.fwd_mul, FloatingPoint):
+        return False
+    iq = formats.input_quant
+    return iq is id_quant or getattr(iq, "forward_number", 0) is None or getattr(iq, "forward_rounding", None) == "nearest"
+
+
+class qconv2d_kernel(torch.autograd.Function):
+    """Zero-padded 2-D convolution whose forward pass is one implicit GEMM per group on the NCHW input
+    (``mpt_float_conv2d_nearest``): the unfolded input, nine times the input for a 3x3 kernel, is neither built nor
+    kept for the backward pass.  The backward pass unfolds the saved (already quantized) input and runs the two
+    GEMMs of ``qlinear_kernel.backward`` per group, so gradients equal those of the unfold + ``qlinear`` composition
+    bit for bit (reference: modules/conv.py:537-640 with functional.py:66-173)."""
+
+    @staticmethod
+    def forward(ctx, input, weight, bias, formats, stride, padding, dilation, groups):
+        from .. import backend as _be
+
+        ctx.formats, ctx.geom = formats, (stride, padding, dilation, groups)
+        qinput = formats.input_quant(input).contiguous()
+        qweight = formats.weight_quant(weight)
+        qbias = formats.bias_quant(bias) if bias is not None else None
+        n, c, h, w = qinput.shape
+        c_out, cg, kh, kw = qweight.shape
+        oh = (h + 2 * padding[0] - dilation[0] * (kh - 1) - 1) // stride[0] + 1
+        ow = (w + 2 * padding[1] - dilation[1] * (kw - 1) - 1) // stride[1] + 1
+        wt = qweight.reshape(groups, c_out // groups, cg * kh * kw).transpose(1, 2).contiguous()
+        out = torch.empty(n, c_out, oh, ow, device=input.device)
+        add, mul = formats.fwd_add, formats.fwd_mul
+        _be.float_conv2d_nearest(qinput.float(), wt.float(), out, groups, (kh, kw), stride, padding, dilation, add.man, add.exp,
+                                 mul.man, mul.exp, add.subnormals, add.saturate, fma=formats.fwd_fma)
+        if qbias is not None:
+            out += qbias.view(1, -1, 1, 1)               # plain fp32 add; rounding is left to output_quant, as in qlinear
+        ctx.save_for_backward(qinput, qweight, qbias)
+        return formats.output_quant(out)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        qinput, qweight, qbias = ctx.saved_tensors
+        f = ctx.formats
+        stride, padding, dilation, groups = ctx.geom
+        n, c, h, w = qinput.shape
+        c_out, cg, kh, kw = qweight.shape
+        og = c_out // groups
+        grad_scale = _grad_scale(f, grad_output)
+        gin, gws, gbs = [], [], []
+        for g in range(groups):
+            go = grad_output[:, g * og:(g + 1) * og]
+            go2 = go.reshape(n, og, -1).transpose(1, 2).reshape(-1, og)              # [N * L, og], as qlinear sees it
+            qgo = f.grad_quant(scale(go2, grad_scale))
+            w2 = qweight[g * og:(g + 1) * og].reshape(og, -1)
+            if ctx.needs_input_grad[0]:
+                gc = torch.matmul(qgo, w2) if f.bwd_use_default_prec else mp_bmm(qgo, w2, formats=f, use_forward=False)
+                gc = f.grad_quant(unscale(gc, grad_scale + 0))
+                gc = gc.view(n, -1, gc.shape[-1]).transpose(1, 2)                    # [N, K, L]
+                gin.append(torch.nn.functional.fold(gc, (h, w), (kh, kw), dilation=dilation, padding=padding, stride=stride))
+            if ctx.needs_input_grad[1]:
+                cols = _conv_cols(qinput[:, g * cg:(g + 1) * cg], (kh, kw), dilation, padding, stride)
+                gw = (torch.matmul(qgo.transpose(-2, -1), cols) if f.bwd_use_default_prec
+                      else mp_bmm(qgo.transpose(-2, -1), cols, formats=f, use_forward=False))
+                gws.append(f.grad_quant(unscale(gw, grad_scale + 0)).view(og, cg, kh, kw))
+            if qbias is not None and ctx.needs_input_grad[2]:
+                if f.bwd_use_default_prec:
+                    gb = qgo.sum(dim=0)
+                else:
+                    with torch.no_grad():
+                        if isinstance(f.bwd_add, FloatingPoint) and f.bwd_rnd == "nearest":
+                            gb = _qsum_dims_fast(qgo, (0,), f.bwd_add)
+                        else:
+                            gb = qsum(qgo, dim=(0,), quant=make_quant_function(f.bwd_add, f.bwd_rnd, f.rbits_add))
+                gbs.append(f.grad_quant(unscale(gb.reshape(-1), grad_scale)))
+        grad_input = torch.cat(gin, dim=1) if gin else None
+        grad_weight = torch.cat(gws, dim=0) if gws else None
+        grad_bias = torch.cat(gbs, dim=0) if gbs else None
+        return grad_input, grad_weight, grad_bias, None, None, None, None, None
+
+
+def qconv2d(input, weight, bias, formats, stride=(1, 1), padding=(0, 0), dilation=(1, 1), groups=1):
+    """Functional zero-padded 2-D convolution through the implicit GEMM; see ``implicit_conv_eligible`` for when the
+    module uses it."""
+    return qconv2d_kernel.apply(input, weight, bias, formats, tuple(stride), tuple(padding), tuple(dilation), groups)
 
 
 # ------------------------------------------------------------------------------------------ mm / matmul

@@ -15,7 +15,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..number import Number
-from .functional import qlayernorm, qlinear, qsoftmax
+from .functional import implicit_conv_eligible, qconv2d, qlayernorm, qlinear, qsoftmax
 from .quant_format import QAffineFormats, QLayerNormFormats, QSoftmaxFormats
 from .quant_function import quantizer
 
@@ -138,6 +138,12 @@ class QConv2d(nn.Conv2d, _QuantSignals):
                 return self.Qo(F.conv2d(x, self.Qw(self.weight), self.Qb(self.bias), self.stride, (0, 0), self.dilation, self.groups))
             return self.Qo(F.conv2d(self.Qi(input), self.Qw(self.weight), self.Qb(self.bias), self.stride, self.padding,
                                     self.dilation, self.groups))
+        if implicit_conv_eligible(f, input) and not isinstance(self.padding, str):
+            # one implicit GEMM per group on the NCHW input: same products in the same order, no unfolded tensor
+            if self.padding_mode != "zeros":
+                x = F.pad(input, self._reversed_padding_repeated_twice, mode=self.padding_mode)
+                return qconv2d(x, self.weight, self.bias, f, self.stride, (0, 0), self.dilation, self.groups)
+            return qconv2d(input, self.weight, self.bias, f, self.stride, self.padding, self.dilation, self.groups)
         batch, in_channel, in_h, in_w = input.shape
         num_filter, _, kh, kw = self.weight.shape
         pad = self.padding if not isinstance(self.padding, str) else (0, 0)
