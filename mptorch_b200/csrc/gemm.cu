@@ -1,562 +1,9 @@
-// Per-MAC rounded GEMM for sm_100a: C = A x B where every product and every partial sum is
-// rounded to a user format before it is used again.
-//
-// This is CUDA-core work by construction: each output's K accumulation is a serial chain of
-// (multiply, round, add, round), so tensor cores cannot be used.  The kernel is bound by the
-// instruction issue rate; the design goal is the smallest number of issued instructions per
-// MAC that still reproduces the reference bit for bit:
-//
-//   * fast path, 10 instructions per MAC (FMUL, 4 for the product rounding, FADD, 4 for the sum
-//     rounding), see FastRn in cast.cuh.  It is exact whenever no intermediate value can leave
-//     the finite range of its format.  That is established from the magnitude statistics of A
-//     and B (a tiny pre-pass writes one record per batch entry to the workspace) plus a
-//     per-thread check of the running accumulators at every fold;
-//   * exact path: the complete reference caster (every corner case), taken per thread and per
-//     8-step group whenever the fast path's precondition cannot be shown.
-//
-// Tiling: 128x64 outputs per CTA, 256 threads, 8x4 outputs per thread, K in slabs of 32 staged
-// through a 3-deep cp.async pipeline in shared memory.  Memory traffic is negligible next to
-// the arithmetic (about 140 GB/s at 8192^3), so tiles are plain cp.async copies.
-//
-// Accumulation orders (both kept bit-exact):
-//   MPT_ORDER_SEQ   acc = Qadd(acc + Qmul(a*b)), k = 0..K-1   (reference quant_cpu/mm_kernel.h:9-20)
-//   MPT_ORDER_CUDA  K walked in groups of 8, zero padded, one extra all-zero group when 8 | K;
-//                   inner accumulates a group, then outer = Qadd(outer + inner)
-//                   (reference quant_cuda/mm_kernel.h:34-70; fma variant :134-186)
-// Kahan-compensated and stochastic variants follow quant_cuda/mm_kernel.h:457-520 and :248-295.
-#include <cuda_pipeline.h>
-
-#include <cstdlib>
-#include <mutex>
-
-#include "cast.cuh"
-#include "common.cuh"
+// C entry points of the per-MAC rounded GEMM and of the implicit-GEMM convolution: argument checks, operand
+// statistics, problem set-up.  The kernel lives in gemm_kernel.cuh, its instantiations in gemm_*.cu.
+#include "gemm_kernel.cuh"
 
 namespace mpt {
 namespace {
-
-#ifndef MPT_MM_TM
-#define MPT_MM_TM 8          // output rows per thread
-#endif
-#ifndef MPT_MM_MIN_CTAS
-#define MPT_MM_MIN_CTAS 2    // resident CTAs per SM the register allocation is held to
-#endif
-constexpr int TM = MPT_MM_TM, TN = 4;
-constexpr int BM = 16 * TM, BN = 64, BK = 32;
-constexpr int THREADS = 256;
-constexpr int STAGES = 3;
-constexpr int AS_LD = BK + 4;   // row stride of the A tile: keeps 16-byte chunks aligned, spreads banks
-constexpr int SMEM_A = BM * AS_LD, SMEM_B = BK * BN;
-constexpr size_t SMEM_BYTES = (size_t)STAGES * (SMEM_A + SMEM_B) * sizeof(float);
-
-enum Algo : int { ALGO_SEQ = 0, ALGO_TILE8 = 1, ALGO_KAHAN = 2, ALGO_SR = 3 };
-
-// Magnitude statistics of the operands, produced by stats_kernel into the workspace.
-struct MmStats {
-    uint32_t max_a, max_b;       // largest |x| bit pattern (NaN and inf compare above every finite)
-    uint32_t minnz_a, minnz_b;   // smallest nonzero |x| bit pattern, 0xFFFFFFFF if all zero
-};
-
-// Convolution as an implicit GEMM: row m of A is output position (image, oh, ow), column k is (channel, kh, kw) in
-// that order (the order of F.unfold and of the reference's unfoldNd, conv.py:591-617), and the element is read
-// straight from the NCHW input (zero outside the image), so the unfolded matrix never exists.  C is written to the
-// NCHW output.
-struct ConvGeom {
-    int H, W, KH, KW, OH, OW, sh, sw, ph, pw, dh, dw;
-    int64_t x_image_stride, y_image_stride;      // elements between consecutive images of input and output
-};
-
-struct MmParams {
-    ConvGeom cv;                 // used by the CONV instantiations only
-    const float* a;
-    const float* b;
-    float* c;
-    int M, N, K;
-    int64_t stride_a, stride_b, stride_c;
-    FpFmt fadd, fmul;            // float view of the formats (fast path, plan)
-    AnyFmt gadd, gmul;           // the formats as the exact path rounds them (float, superfp or binary8)
-    FastRn radd, rmul;
-    int rbits_add, rbits_mul;
-    uint32_t seed_lo, seed_hi;
-    const MmStats* stats;        // one record per batch entry; NULL: exact path only
-    float growth8;               // upper bound of (1 + 2^-(man_add+1))^8
-};
-
-__global__ void stats_init_kernel(MmStats* s, int64_t batch) {
-    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < batch) { s[i].max_a = 0u; s[i].max_b = 0u; s[i].minnz_a = 0xFFFFFFFFu; s[i].minnz_b = 0xFFFFFFFFu; }
-}
-
-// blockIdx.y walks the batch; `which` selects the A (0) or B (1) fields of that entry's record.
-__global__ void __launch_bounds__(256) stats_kernel(const float* __restrict__ base, int64_t n, MmStats* stats, int which) {
-    const float* x = base + (int64_t)blockIdx.y * n;
-    uint32_t* mx = which ? &stats[blockIdx.y].max_b : &stats[blockIdx.y].max_a;
-    uint32_t* mn = which ? &stats[blockIdx.y].minnz_b : &stats[blockIdx.y].minnz_a;
-    uint32_t lmax = 0u, lmin = 0xFFFFFFFFu;
-    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
-        const uint32_t a = __float_as_uint(x[i]) & 0x7FFFFFFFu;
-        lmax = max(lmax, a);
-        if (a != 0u) lmin = min(lmin, a);
-    }
-    lmax = __reduce_max_sync(0xFFFFFFFFu, lmax);
-    lmin = __reduce_min_sync(0xFFFFFFFFu, lmin);
-    if ((threadIdx.x & 31) == 0) {
-        atomicMax(mx, lmax);
-        atomicMin(mn, lmin);
-    }
-}
-
-__device__ __forceinline__ void cp_async16(float* dst, const float* src, int src_bytes) {
-    const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src), "r"(src_bytes));
-}
-__device__ __forceinline__ void cp_async4(float* dst, const float* src, int src_bytes) {
-    const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"(d), "l"(src), "r"(src_bytes));
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
-
-// Stage one K slab: As[m][k] (row stride AS_LD) and Bs[k][n].  Elements outside the matrices are
-// zero filled (cp.async with a source size of 0), which is also how K is zero padded.
-struct ConvRow { int64_t base; int ih0, iw0; };     // per output position: image offset, top-left input coordinate
-
-template <bool VEC, bool CONV = false>
-__device__ __forceinline__ void load_tiles(const MmParams& p, const float* A, const float* B, float* As, float* Bs,
-                                           int m0, int n0, int k0, int tid, const ConvRow* rows = nullptr) {
-    if (CONV) {
-        // A: the thread's column of the slab is fixed (tid & 31), its rows are (tid >> 5) + 8 u
-        const int kk = tid & 31, gk = k0 + kk;
-        const int khkw = p.cv.KH * p.cv.KW;
-        const int ch = gk / khkw, rem = gk - ch * khkw;
-        const int kh = rem / p.cv.KW, kw = rem - kh * p.cv.KW;
-        const bool kok = gk < p.K;
-        const int dih = kh * p.cv.dh, diw = kw * p.cv.dw;
-        const int64_t coff = (int64_t)ch * p.cv.H * p.cv.W;
-#pragma unroll 4
-        for (int u = 0; u < BM / 8; ++u) {
-            const int row = (tid >> 5) + 8 * u;
-            const ConvRow r = rows[row];
-            const int ih = r.ih0 + dih, iw = r.iw0 + diw;
-            const bool ok = kok && (unsigned)ih < (unsigned)p.cv.H && (unsigned)iw < (unsigned)p.cv.W;
-            cp_async4(As + row * AS_LD + kk, ok ? A + r.base + coff + (int64_t)ih * p.cv.W + iw : A, ok ? 4 : 0);
-        }
-#pragma unroll 4
-        for (int u = 0; u < (BK * BN) / THREADS; ++u) {
-            const int c = tid + u * THREADS;
-            const int kr = c >> 6, nn = c & 63;
-            const int gk2 = k0 + kr, gn = n0 + nn;
-            const bool ok = gk2 < p.K && gn < p.N;
-            cp_async4(Bs + kr * BN + nn, ok ? B + (int64_t)gk2 * p.N + gn : B, ok ? 4 : 0);
-        }
-        return;
-    }
-    if (VEC) {
-#pragma unroll
-        for (int u = 0; u < (BM * BK / 4) / THREADS; ++u) {
-            const int c = tid + u * THREADS;
-            const int row = c >> 3, kc = (c & 7) << 2;
-            const int gm = m0 + row, gk = k0 + kc;
-            int bytes = (gm < p.M) ? (p.K - gk) * 4 : 0;
-            bytes = bytes < 0 ? 0 : (bytes > 16 ? 16 : bytes);
-            const float* src = bytes ? A + (int64_t)gm * p.K + gk : A;
-            cp_async16(As + row * AS_LD + kc, src, bytes);
-        }
-#pragma unroll
-        for (int u = 0; u < (BK * BN / 4) / THREADS; ++u) {
-            const int c = tid + u * THREADS;
-            const int kr = c >> 4, nc = (c & 15) << 2;
-            const int gk = k0 + kr, gn = n0 + nc;
-            int bytes = (gk < p.K) ? (p.N - gn) * 4 : 0;
-            bytes = bytes < 0 ? 0 : (bytes > 16 ? 16 : bytes);
-            const float* src = bytes ? B + (int64_t)gk * p.N + gn : B;
-            cp_async16(Bs + kr * BN + nc, src, bytes);
-        }
-    } else {
-#pragma unroll 4
-        for (int u = 0; u < (BM * BK) / THREADS; ++u) {
-            const int c = tid + u * THREADS;
-            const int row = c >> 5, kk = c & 31;
-            const int gm = m0 + row, gk = k0 + kk;
-            const bool ok = gm < p.M && gk < p.K;
-            cp_async4(As + row * AS_LD + kk, ok ? A + (int64_t)gm * p.K + gk : A, ok ? 4 : 0);
-        }
-#pragma unroll 4
-        for (int u = 0; u < (BK * BN) / THREADS; ++u) {
-            const int c = tid + u * THREADS;
-            const int kr = c >> 6, nn = c & 63;
-            const int gk = k0 + kr, gn = n0 + nn;
-            const bool ok = gk < p.K && gn < p.N;
-            cp_async4(Bs + kr * BN + nn, ok ? B + (int64_t)gk * p.N + gn : B, ok ? 4 : 0);
-        }
-    }
-}
-
-// One accumulation step on the exact path.
-template <bool FMA>
-__device__ __forceinline__ float mac_exact(float acc, float a, float b, const AnyFmt& fadd, const AnyFmt& fmul) {
-    if (FMA) return cast_any(fma_rn(a, b, acc), fadd);
-    return cast_any(add_rn(acc, cast_any(mul_rn(a, b), fmul)), fadd);
-}
-template <bool FMA>
-__device__ __forceinline__ float mac_fast(float acc, float a, float b, const FastRn& radd, const FastRn& rmul) {
-    if (FMA) return radd(fma_rn(a, b, acc));
-    return radd(add_rn(acc, rmul(mul_rn(a, b))));
-}
-
-// Two accumulation steps at once on sm_100's packed fp32x2 instructions (FMUL2 / FADD2 / FFMA2): the six
-// FP-pipe instructions of a MAC are shared by two neighbouring outputs, so a MAC costs 3 packed FP
-// instructions + 4 ALU instructions (the exponent extraction stays per element) = 7 issue slots
-// instead of 10.  Each half of a packed instruction rounds exactly like its scalar form.
-//
-// GUARD = false drops the clamp of the exponent at the format's smallest normal binade (one IMNMX per
-// element).  That is exact for the SUM rounding whenever the multiply format's smallest subnormal is
-// not finer than the add format's: every product and every partial sum is then a multiple of the add
-// format's smallest subnormal, so a sum that lands in the add format's subnormal range has no bits
-// below that quantum and rounding it at its own exponent leaves it unchanged, exactly like the
-// clamped rounding (a zero sum gives m = 0 and comes out as +0).
-template <bool GUARD>
-__device__ __forceinline__ float2 fast_rn2(const FastRn& r, float2 x) {
-    int e0 = __float_as_int(x.x) & 0x7F800000, e1 = __float_as_int(x.y) & 0x7F800000;
-    if (GUARD) { e0 = max(e0, r.min_e_bits); e1 = max(e1, r.min_e_bits); }
-    const float2 m = make_float2(__int_as_float(e0), __int_as_float(e1));
-    const float2 y = __ffma2_rn(m, make_float2(r.k, r.k), x);
-    return __ffma2_rn(m, make_float2(-r.k, -r.k), y);
-}
-template <bool FMA, bool ADDG>
-__device__ __forceinline__ float2 mac_fast2(float2 acc, float2 a2, float2 b2, const FastRn& radd, const FastRn& rmul) {
-    if (FMA) return fast_rn2<true>(radd, __ffma2_rn(a2, b2, acc));
-    return fast_rn2<ADDG>(radd, __fadd2_rn(acc, fast_rn2<true>(rmul, __fmul2_rn(a2, b2))));
-}
-
-// `nk` (1..8) accumulation steps starting at slab row kbase, for the thread's 8x4 outputs.
-template <bool FMA, bool FAST, bool PACKED, bool ADDG>
-__device__ __forceinline__ void group_steps(float (&acc)[TM][TN], const float* As, const float* Bs, int kbase, int nk,
-                                            int ty, int tx, const MmParams& p) {
-    if (FAST && nk == 8) {
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            float4 av[TM];
-#pragma unroll
-            for (int i = 0; i < TM; ++i)
-                av[i] = *reinterpret_cast<const float4*>(As + (ty + 16 * i) * AS_LD + kbase + 4 * h);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const float4 bv = *reinterpret_cast<const float4*>(Bs + (kbase + 4 * h + j) * BN + tx * 4);
-#pragma unroll
-                for (int i = 0; i < TM; ++i) {
-                    const float a = j == 0 ? av[i].x : j == 1 ? av[i].y : j == 2 ? av[i].z : av[i].w;
-                    if (PACKED) {
-                        const float2 a2 = make_float2(a, a);
-                        const float2 lo = mac_fast2<FMA, ADDG>(make_float2(acc[i][0], acc[i][1]), a2, make_float2(bv.x, bv.y), p.radd, p.rmul);
-                        const float2 hi = mac_fast2<FMA, ADDG>(make_float2(acc[i][2], acc[i][3]), a2, make_float2(bv.z, bv.w), p.radd, p.rmul);
-                        acc[i][0] = lo.x; acc[i][1] = lo.y; acc[i][2] = hi.x; acc[i][3] = hi.y;
-                    } else {
-                        acc[i][0] = mac_fast<FMA>(acc[i][0], a, bv.x, p.radd, p.rmul);
-                        acc[i][1] = mac_fast<FMA>(acc[i][1], a, bv.y, p.radd, p.rmul);
-                        acc[i][2] = mac_fast<FMA>(acc[i][2], a, bv.z, p.radd, p.rmul);
-                        acc[i][3] = mac_fast<FMA>(acc[i][3], a, bv.w, p.radd, p.rmul);
-                    }
-                }
-            }
-        }
-        return;
-    }
-#pragma unroll 1
-    for (int k = 0; k < nk; ++k) {
-        const float4 bv = *reinterpret_cast<const float4*>(Bs + (kbase + k) * BN + tx * 4);
-#pragma unroll
-        for (int i = 0; i < TM; ++i) {
-            const float a = As[(ty + 16 * i) * AS_LD + kbase + k];
-            if (FAST) {
-                acc[i][0] = mac_fast<FMA>(acc[i][0], a, bv.x, p.radd, p.rmul);
-                acc[i][1] = mac_fast<FMA>(acc[i][1], a, bv.y, p.radd, p.rmul);
-                acc[i][2] = mac_fast<FMA>(acc[i][2], a, bv.z, p.radd, p.rmul);
-                acc[i][3] = mac_fast<FMA>(acc[i][3], a, bv.w, p.radd, p.rmul);
-            } else {
-                acc[i][0] = mac_exact<FMA>(acc[i][0], a, bv.x, p.gadd, p.gmul);
-                acc[i][1] = mac_exact<FMA>(acc[i][1], a, bv.y, p.gadd, p.gmul);
-                acc[i][2] = mac_exact<FMA>(acc[i][2], a, bv.z, p.gadd, p.gmul);
-                acc[i][3] = mac_exact<FMA>(acc[i][3], a, bv.w, p.gadd, p.gmul);
-            }
-        }
-    }
-}
-
-__device__ __forceinline__ float absmax_of(const float (&v)[TM][TN]) {
-    float m = 0.0f;
-#pragma unroll
-    for (int i = 0; i < TM; ++i)
-#pragma unroll
-        for (int j = 0; j < TN; ++j) m = fmaxf(m, fabsf(v[i][j]));   // NaN entries are skipped by fmaxf
-    return m;
-}
-
-// What the fast path may assume for this launch, from the operand statistics.
-//   ok        : products can take the fast rounding (finite, no overflow in the multiply format,
-//               no fp32-denormal intermediates where the reference treats those specially)
-//   acc_limit : an accumulator with |acc| below this stays on the fast path for 8 more steps
-//               (ALGO_SEQ), or an outer sum below this takes the fast fold (ALGO_TILE8)
-struct FastPlan { bool ok; float acc_limit; };
-
-template <int ALGO, bool FMA>
-__device__ __forceinline__ FastPlan make_plan(const MmParams& p, int64_t batch) {
-    FastPlan plan{false, 0.0f};
-    if (p.stats == nullptr) return plan;
-    if (!fast_rn_supported(p.fadd) || (!FMA && !fast_rn_supported(p.fmul))) return plan;
-    const MmStats s = p.stats[batch];
-    if (s.max_a >= 0x7F800000u || s.max_b >= 0x7F800000u) return plan;
-    // |a| < 2^(ea+1), |b| < 2^(eb+1)  =>  |a*b| < 2^pe
-    const int pe = (int)(s.max_a >> 23) + (int)(s.max_b >> 23) - 254 + 2;
-    const int lim_add = fast_rn_exp_limit(p.fadd);
-    if (!FMA && pe - 1 > fast_rn_exp_limit(p.fmul)) return plan;
-    if (p.fadd.exp == 8 || (!FMA && p.fmul.exp == 8)) {
-        // the reference rounds fp32-denormal inputs of 8-bit-exponent formats one bit coarser;
-        // stay exact unless every nonzero intermediate is provably far above 2^-126
-        if (s.minnz_a < 0x00800000u || s.minnz_b < 0x00800000u) return plan;
-        if (s.minnz_a != 0xFFFFFFFFu && s.minnz_b != 0xFFFFFFFFu) {
-            const int lo = (int)(s.minnz_a >> 23) + (int)(s.minnz_b >> 23) - 254;
-            if (lo - 23 < -120) return plan;
-        }
-    }
-    // eight steps from |acc| = x reach at most (x + 8 * 2^pe) * growth8
-    const float step8 = ldexpf(8.0f, pe) * p.growth8;
-    const float top = ldexpf(1.0f, lim_add + 1);
-    if (ALGO == ALGO_TILE8) {
-        // inner sums start from zero: |inner| <= step8; the fold needs |outer| + |inner| < top
-        if (!(step8 <= ldexpf(1.0f, lim_add))) return plan;
-        plan.ok = true;
-        plan.acc_limit = ldexpf(1.0f, lim_add);
-    } else {
-        const float lim = top / p.growth8 - ldexpf(8.0f, pe);
-        if (!(lim > 0.0f)) return plan;
-        plan.ok = true;
-        plan.acc_limit = lim;
-    }
-    return plan;
-}
-
-template <int ALGO, bool FMA, bool VEC, bool PACKED, bool ADDG, bool CONV = false>
-__global__ void __launch_bounds__(THREADS, MPT_MM_MIN_CTAS) mm_kernel(const MmParams p) {
-    extern __shared__ __align__(16) float smem[];
-    float* As = smem;
-    float* Bs = smem + STAGES * SMEM_A;
-    ConvRow* crow = reinterpret_cast<ConvRow*>(smem + STAGES * (SMEM_A + SMEM_B));      // CONV: BM entries
-
-    const int tid = threadIdx.x;
-    const int ty = tid >> 4, tx = tid & 15;
-    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
-    const int64_t batch = blockIdx.z;
-    const float* A = p.a + batch * p.stride_a;
-    const float* B = p.b + batch * p.stride_b;
-    float* C = p.c + batch * p.stride_c;
-
-    // number of accumulation steps walked: exactly K for the sequential order, the zero-padded
-    // range K + 8 - K % 8 for every order that follows the reference CUDA kernels
-    const int ksteps = (ALGO == ALGO_SEQ) ? p.K : p.K + 8 - p.K % 8;
-    const int ntiles = (ksteps + BK - 1) / BK;
-
-    const FastPlan plan = (ALGO == ALGO_SEQ || ALGO == ALGO_TILE8) ? make_plan<ALGO, FMA>(p, batch) : FastPlan{false, 0.0f};
-
-    if (CONV) {
-        if (tid < BM) {
-            const int gm = m0 + tid;
-            ConvRow r;
-            if (gm < p.M) {
-                const int L = p.cv.OH * p.cv.OW;
-                const int img = gm / L, l = gm - img * L;
-                const int oh = l / p.cv.OW, ow = l - oh * p.cv.OW;
-                r.base = (int64_t)img * p.cv.x_image_stride;
-                r.ih0 = oh * p.cv.sh - p.cv.ph;
-                r.iw0 = ow * p.cv.sw - p.cv.pw;
-            } else {
-                r.base = 0; r.ih0 = -(1 << 30); r.iw0 = -(1 << 30);      // fails every bounds check: zero rows
-            }
-            crow[tid] = r;
-        }
-        __syncthreads();
-    }
-
-    float acc[TM][TN];    // running sum (inner sum for ALGO_TILE8)
-    float aux[TM][TN];    // outer sum (ALGO_TILE8) or compensation term (ALGO_KAHAN)
-#pragma unroll
-    for (int i = 0; i < TM; ++i)
-#pragma unroll
-        for (int j = 0; j < TN; ++j) { acc[i][j] = 0.0f; aux[i][j] = 0.0f; }
-
-#pragma unroll
-    for (int s = 0; s < STAGES - 1; ++s) {
-        if (s < ntiles) load_tiles<VEC, CONV>(p, A, B, As + s * SMEM_A, Bs + s * SMEM_B, m0, n0, s * BK, tid, crow);
-        cp_async_commit();
-    }
-
-    for (int t = 0; t < ntiles; ++t) {
-        cp_async_wait<STAGES - 2>();
-        __syncthreads();
-        {
-            const int nt = t + STAGES - 1;
-            if (nt < ntiles) load_tiles<VEC, CONV>(p, A, B, As + (nt % STAGES) * SMEM_A, Bs + (nt % STAGES) * SMEM_B, m0, n0, nt * BK, tid, crow);
-            cp_async_commit();
-        }
-        const float* as = As + (t % STAGES) * SMEM_A;
-        const float* bs = Bs + (t % STAGES) * SMEM_B;
-        const int kleft = ksteps - t * BK;
-        const int nk_tile = kleft < BK ? kleft : BK;
-
-        if (ALGO == ALGO_SEQ || ALGO == ALGO_TILE8) {
-            for (int g = 0; g * 8 < nk_tile; ++g) {
-                const int nk = (nk_tile - g * 8) < 8 ? (nk_tile - g * 8) : 8;
-                if (ALGO == ALGO_TILE8) {
-                    if (plan.ok) group_steps<FMA, true, PACKED, ADDG>(acc, as, bs, g * 8, nk, ty, tx, p);
-                    else group_steps<FMA, false, false, true>(acc, as, bs, g * 8, nk, ty, tx, p);
-                    // fold the group into the outer sum
-                    if (plan.ok && absmax_of(aux) < plan.acc_limit) {
-#pragma unroll
-                        for (int i = 0; i < TM; ++i) {
-                            if (PACKED) {
-                                const float2 lo = fast_rn2<ADDG>(p.radd, __fadd2_rn(make_float2(aux[i][0], aux[i][1]), make_float2(acc[i][0], acc[i][1])));
-                                const float2 hi = fast_rn2<ADDG>(p.radd, __fadd2_rn(make_float2(aux[i][2], aux[i][3]), make_float2(acc[i][2], acc[i][3])));
-                                aux[i][0] = lo.x; aux[i][1] = lo.y; aux[i][2] = hi.x; aux[i][3] = hi.y;
-                            } else {
-#pragma unroll
-                                for (int j = 0; j < TN; ++j) aux[i][j] = p.radd(add_rn(aux[i][j], acc[i][j]));
-                            }
-#pragma unroll
-                            for (int j = 0; j < TN; ++j) acc[i][j] = 0.0f;
-                        }
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < TM; ++i)
-#pragma unroll
-                            for (int j = 0; j < TN; ++j) { aux[i][j] = cast_any(add_rn(aux[i][j], acc[i][j]), p.gadd); acc[i][j] = 0.0f; }
-                    }
-                } else {
-                    if (plan.ok && absmax_of(acc) < plan.acc_limit) group_steps<FMA, true, PACKED, ADDG>(acc, as, bs, g * 8, nk, ty, tx, p);
-                    else group_steps<FMA, false, false, true>(acc, as, bs, g * 8, nk, ty, tx, p);
-                }
-            }
-        } else if (ALGO == ALGO_KAHAN) {
-#pragma unroll 1
-            for (int k = 0; k < nk_tile; ++k) {
-                const float4 bv4 = *reinterpret_cast<const float4*>(bs + k * BN + tx * 4);
-                const float bvv[4] = {bv4.x, bv4.y, bv4.z, bv4.w};
-#pragma unroll
-                for (int i = 0; i < TM; ++i) {
-                    const float a = as[(ty + 16 * i) * AS_LD + k];
-#pragma unroll
-                    for (int j = 0; j < TN; ++j) {
-                        const float sum = acc[i][j], comp = aux[i][j];
-                        const float y = FMA ? cast_any(fma_rn(a, bvv[j], -comp), p.gadd)
-                                            : cast_any(add_rn(cast_any(mul_rn(a, bvv[j]), p.gmul), -comp), p.gadd);
-                        const float tt = cast_any(add_rn(sum, y), p.gadd);
-                        aux[i][j] = cast_any(add_rn(cast_any(add_rn(tt, -sum), p.gadd), -y), p.gadd);
-                        acc[i][j] = tt;
-                    }
-                }
-            }
-        } else {   // ALGO_SR
-#pragma unroll 1
-            for (int k = 0; k < nk_tile; ++k) {
-                const float4 bv4 = *reinterpret_cast<const float4*>(bs + k * BN + tx * 4);
-                const float bvv[4] = {bv4.x, bv4.y, bv4.z, bv4.w};
-                const uint32_t kglob = (uint32_t)(t * BK + k);
-#pragma unroll
-                for (int i = 0; i < TM; ++i) {
-                    const float a = as[(ty + 16 * i) * AS_LD + k];
-                    const int gm = m0 + ty + 16 * i;
-#pragma unroll
-                    for (int j = 0; j < TN; ++j) {
-                        const int gn = n0 + tx * 4 + j;
-                        const uint64_t lin = (uint64_t)batch * p.M * p.N + (uint64_t)gm * p.N + gn;
-                        Philox ph(kglob, (uint32_t)lin, (uint32_t)(lin >> 32), 0u);
-                        ph.run(p.seed_lo, p.seed_hi);
-                        if (FMA) acc[i][j] = cast_fp_stochastic(fma_rn(a, bvv[j], acc[i][j]), ph.c[0], p.rbits_add, p.fadd);
-                        else {
-                            const float pr = cast_fp_stochastic(mul_rn(a, bvv[j]), ph.c[1], p.rbits_mul, p.fmul);
-                            acc[i][j] = cast_fp_stochastic(add_rn(acc[i][j], pr), ph.c[0], p.rbits_add, p.fadd);
-                        }
-                    }
-                }
-            }
-        }
-    }
-    cp_async_wait<0>();
-
-    // epilogue
-    if (CONV) {     // C[m][n] goes to y[image][n][oh][ow]: consecutive m are consecutive addresses
-        const int L = p.cv.OH * p.cv.OW;
-#pragma unroll
-        for (int i = 0; i < TM; ++i) {
-            const int gm = m0 + ty + 16 * i;
-            if (gm >= p.M) continue;
-            const int img = gm / L, l = gm - img * L;
-            const float* r = (ALGO == ALGO_TILE8) ? aux[i] : acc[i];
-            float* dst = C + (int64_t)img * p.cv.y_image_stride + l;
-#pragma unroll
-            for (int j = 0; j < TN; ++j) {
-                const int gn = n0 + tx * 4 + j;
-                if (gn < p.N) dst[(int64_t)gn * L] = r[j];
-            }
-        }
-        return;
-    }
-    const bool vec_store = VEC && ((reinterpret_cast<uintptr_t>(C) & 15u) == 0);
-#pragma unroll
-    for (int i = 0; i < TM; ++i) {
-        const int gm = m0 + ty + 16 * i;
-        if (gm >= p.M) continue;
-        const float* r = (ALGO == ALGO_TILE8) ? aux[i] : acc[i];
-        const int gn = n0 + tx * 4;
-        float* dst = C + (int64_t)gm * p.N + gn;
-        if (vec_store && gn + 3 < p.N) *reinterpret_cast<float4*>(dst) = make_float4(r[0], r[1], r[2], r[3]);
-        else {
-#pragma unroll
-            for (int j = 0; j < TN; ++j)
-                if (gn + j < p.N) dst[j] = r[j];
-        }
-    }
-}
-
-// The packed fp32x2 fast path is the default; MPT_MM_SCALAR=1 in the environment selects the scalar
-// fast path (same bits; kept for A/B measurements).
-bool use_packed() {
-    static const bool packed = [] { const char* e = getenv("MPT_MM_SCALAR"); return !(e && e[0] == '1'); }();
-    return packed;
-}
-
-template <int ALGO, bool FMA>
-int launch_mm(const MmParams& p, int64_t batch, bool vec, cudaStream_t st) {
-    dim3 grid((p.N + BN - 1) / BN, (p.M + BM - 1) / BM, (unsigned)batch);
-    constexpr bool kHasFast = (ALGO == ALGO_SEQ || ALGO == ALGO_TILE8);
-    const bool packed = kHasFast && use_packed();
-    // the sum rounding needs its subnormal clamp only if products can carry bits below the add format's
-    // smallest subnormal (always the case for a fused multiply-add, whose sum is not a sum of rounded values)
-    const bool add_guard = FMA || !packed || (p.fmul.min_exp - p.fmul.man) < (p.fadd.min_exp - p.fadd.man);
-    constexpr bool kCanDrop = kHasFast && !FMA;
-    auto kern = vec ? (packed ? (add_guard ? mm_kernel<ALGO, FMA, true, kHasFast, true> : mm_kernel<ALGO, FMA, true, kHasFast, !kCanDrop>)
-                              : mm_kernel<ALGO, FMA, true, false, true>)
-                    : (packed ? (add_guard ? mm_kernel<ALGO, FMA, false, kHasFast, true> : mm_kernel<ALGO, FMA, false, kHasFast, !kCanDrop>)
-                              : mm_kernel<ALGO, FMA, false, false, true>);
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
-    if (e != cudaSuccess) { set_error("float_mm: cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return MPT_ERR_CUDA; }
-    kern<<<grid, THREADS, SMEM_BYTES, st>>>(p);
-    return check_launch("float_mm");
-}
-
-// Convolution launch: scalar operand copies (the gather has no 16-byte runs), packed fast path.
-template <int ALGO, bool FMA>
-int launch_conv(const MmParams& p, cudaStream_t st) {
-    dim3 grid((p.N + BN - 1) / BN, (p.M + BM - 1) / BM, 1);
-    const bool add_guard = FMA || (p.fmul.min_exp - p.fmul.man) < (p.fadd.min_exp - p.fadd.man);
-    auto kern = add_guard ? mm_kernel<ALGO, FMA, false, true, true, true> : mm_kernel<ALGO, FMA, false, true, FMA, true>;
-    const size_t smem = SMEM_BYTES + BM * sizeof(ConvRow);
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) { set_error("float_conv2d: cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return MPT_ERR_CUDA; }
-    kern<<<grid, THREADS, smem, st>>>(p);
-    return check_launch("float_conv2d");
-}
 
 double growth8_bound(int man) {
     double g = 1.0, f = 1.0 + ldexp(1.0, -(man + 1));
@@ -608,15 +55,11 @@ int run_mm(const float* a, const float* b, float* c, int64_t batch, int M, int N
         p.stats = s;
     }
     const bool vec = (K % 4 == 0) && (N % 4 == 0) && (((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) & 15u) == 0);
-    switch (algo * 2 + (fma ? 1 : 0)) {
-        case ALGO_SEQ * 2 + 0: return launch_mm<ALGO_SEQ, false>(p, batch, vec, st);
-        case ALGO_SEQ * 2 + 1: return launch_mm<ALGO_SEQ, true>(p, batch, vec, st);
-        case ALGO_TILE8 * 2 + 0: return launch_mm<ALGO_TILE8, false>(p, batch, vec, st);
-        case ALGO_TILE8 * 2 + 1: return launch_mm<ALGO_TILE8, true>(p, batch, vec, st);
-        case ALGO_KAHAN * 2 + 0: return launch_mm<ALGO_KAHAN, false>(p, batch, vec, st);
-        case ALGO_KAHAN * 2 + 1: return launch_mm<ALGO_KAHAN, true>(p, batch, vec, st);
-        case ALGO_SR * 2 + 0: return launch_mm<ALGO_SR, false>(p, batch, vec, st);
-        default: return launch_mm<ALGO_SR, true>(p, batch, vec, st);
+    switch (algo) {
+        case ALGO_SEQ: return launch_mm_seq(fma, p, batch, vec, st);
+        case ALGO_TILE8: return launch_mm_tile8(fma, p, batch, vec, st);
+        case ALGO_KAHAN: return launch_mm_kahan(fma, p, batch, vec, st);
+        default: return launch_mm_sr(fma, p, batch, vec, st);
     }
 }
 
@@ -663,13 +106,7 @@ int run_conv(const float* x, const float* wt, float* y, int n_img, int c_in, int
         p.a = x + (int64_t)g * cg * H * W;
         p.b = wt + (int64_t)g * K64 * og;
         p.c = y + (int64_t)g * og * OH * OW;
-        int rc;
-        switch (algo * 2 + (fma ? 1 : 0)) {
-            case ALGO_SEQ * 2 + 0: rc = launch_conv<ALGO_SEQ, false>(p, st); break;
-            case ALGO_SEQ * 2 + 1: rc = launch_conv<ALGO_SEQ, true>(p, st); break;
-            case ALGO_TILE8 * 2 + 0: rc = launch_conv<ALGO_TILE8, false>(p, st); break;
-            default: rc = launch_conv<ALGO_TILE8, true>(p, st); break;
-        }
+        const int rc = launch_conv_any(algo, fma, p, st);
         if (rc) return rc;
     }
     return MPT_OK;
