@@ -33,6 +33,10 @@ int run_mm(const float* a, const float* b, float* c, int64_t batch, int M, int N
     p.seed_lo = (uint32_t)seed; p.seed_hi = (uint32_t)(seed >> 32);
     p.growth8 = (float)growth8_bound(fadd.man);
     p.stats = nullptr;
+    p.whole_ok = all_float && fast_rn_supported(fadd) && (fma || fast_rn_supported(fmul));
+    p.wadd = FullRn::make(fadd); p.wmul = FullRn::make(fma ? fadd : fmul);
+    p.sr_ok = all_float && FullSr::supported(fadd) && (fma || FullSr::supported(fmul));
+    p.sadd = FullSr::make(fadd, rbits_add); p.smul = FullSr::make(fma ? fadd : fmul, fma ? rbits_add : rbits_mul);
 
     const bool fast_candidate = all_float && (algo == ALGO_SEQ || algo == ALGO_TILE8) && fast_rn_supported(fadd) &&
                                 (fma || fast_rn_supported(fmul)) && workspace != nullptr &&
@@ -82,6 +86,9 @@ int run_conv(const float* x, const float* wt, float* y, int n_img, int c_in, int
     p.rbits_add = p.rbits_mul = 0; p.seed_lo = p.seed_hi = 0;
     p.growth8 = (float)growth8_bound(fadd.man);
     p.stats = nullptr;
+    p.whole_ok = 0; p.sr_ok = 0;
+    p.wadd = p.wmul = FullRn::make(fadd);
+    p.sadd = p.smul = FullSr::make(fadd, 0);
     const bool fast_candidate = fast_rn_supported(fadd) && (fma || fast_rn_supported(fmul)) && workspace != nullptr &&
                                 workspace_bytes >= sizeof(MmStats) && (reinterpret_cast<uintptr_t>(workspace) & 15u) == 0 && K64 > 0;
     if (K64 == 0) {

@@ -85,7 +85,43 @@ struct MmParams {
     uint32_t seed_lo, seed_hi;
     const MmStats* stats;        // one record per batch entry; NULL: exact path only
     float growth8;               // upper bound of (1 + 2^-(man_add+1))^8
+    // whole-domain fast casters for the variants without a range-checked fast path (Kahan, stochastic): same bits as
+    // the exact casters on every input at a fraction of the instructions, for the formats that support them
+    FullRn wadd, wmul;
+    int whole_ok;
+    FullSr sadd, smul;
+    int sr_ok;
 };
+
+// Nearest rounding to the add / multiply format on the whole input domain.  The exact caster is an out-of-line call
+// (taken for formats without the fast rounding, and for the tiny or huge inputs 8-bit-exponent formats treat
+// specially), so that the many rounding sites of the Kahan kernels stay small.
+static __device__ __noinline__ float exact_add_cold(const MmParams* p, float x) { return cast_any(x, p->gadd); }
+static __device__ __noinline__ float exact_mul_cold(const MmParams* p, float x) { return cast_any(x, p->gmul); }
+__device__ __forceinline__ bool whole_fast(const FullRn& w, float x, float& out) {
+    const uint32_t t = __float_as_uint(x), a = t & 0x7FFFFFFFu;
+    if (w.fmt.exp == 8 && (a >= w.exact_from || a < 0x00800000u)) return false;
+    const float y = w.fast(x);
+    const float over = (a >= 0x7F800000u) ? x : __uint_as_float((t & 0x80000000u) | w.ovf_value);
+    out = (a >= w.ovf_from) ? over : y;
+    return true;
+}
+__device__ __forceinline__ float round_add(const MmParams& p, float x) {
+    float r;
+    if (p.whole_ok && whole_fast(p.wadd, x, r)) return r;
+    return exact_add_cold(&p, x);
+}
+__device__ __forceinline__ float round_mul(const MmParams& p, float x) {
+    float r;
+    if (p.whole_ok && whole_fast(p.wmul, x, r)) return r;
+    return exact_mul_cold(&p, x);
+}
+__device__ __forceinline__ float sr_add(const MmParams& p, float x, uint32_t r) {
+    return p.sr_ok ? p.sadd(x, r) : cast_fp_stochastic(x, r, p.rbits_add, p.fadd);
+}
+__device__ __forceinline__ float sr_mul(const MmParams& p, float x, uint32_t r) {
+    return p.sr_ok ? p.smul(x, r) : cast_fp_stochastic(x, r, p.rbits_mul, p.fmul);
+}
 
 static __global__ void stats_init_kernel(MmStats* s, int64_t batch) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -344,7 +380,7 @@ __device__ __forceinline__ FastPlan make_plan(const MmParams& p, int64_t batch) 
 }
 
 template <int ALGO, bool FMA, bool VEC, bool PACKED, bool ADDG, bool CONV = false>
-__global__ void __launch_bounds__(THREADS, MPT_MM_MIN_CTAS) mm_kernel(const MmParams p) {
+__global__ void __launch_bounds__(THREADS, MPT_MM_MIN_CTAS) mm_kernel(const __grid_constant__ MmParams p) {
     extern __shared__ __align__(16) float smem[];
     float* As = smem;
     float* Bs = smem + STAGES * SMEM_A;
@@ -453,10 +489,10 @@ __global__ void __launch_bounds__(THREADS, MPT_MM_MIN_CTAS) mm_kernel(const MmPa
 #pragma unroll
                     for (int j = 0; j < TN; ++j) {
                         const float sum = acc[i][j], comp = aux[i][j];
-                        const float y = FMA ? cast_any(fma_rn(a, bvv[j], -comp), p.gadd)
-                                            : cast_any(add_rn(cast_any(mul_rn(a, bvv[j]), p.gmul), -comp), p.gadd);
-                        const float tt = cast_any(add_rn(sum, y), p.gadd);
-                        aux[i][j] = cast_any(add_rn(cast_any(add_rn(tt, -sum), p.gadd), -y), p.gadd);
+                        const float y = FMA ? round_add(p, fma_rn(a, bvv[j], -comp))
+                                            : round_add(p, add_rn(round_mul(p, mul_rn(a, bvv[j])), -comp));
+                        const float tt = round_add(p, add_rn(sum, y));
+                        aux[i][j] = round_add(p, add_rn(round_add(p, add_rn(tt, -sum)), -y));
                         acc[i][j] = tt;
                     }
                 }
@@ -477,10 +513,10 @@ __global__ void __launch_bounds__(THREADS, MPT_MM_MIN_CTAS) mm_kernel(const MmPa
                         const uint64_t lin = (uint64_t)batch * p.M * p.N + (uint64_t)gm * p.N + gn;
                         Philox ph(kglob, (uint32_t)lin, (uint32_t)(lin >> 32), 0u);
                         ph.run(p.seed_lo, p.seed_hi);
-                        if (FMA) acc[i][j] = cast_fp_stochastic(fma_rn(a, bvv[j], acc[i][j]), ph.c[0], p.rbits_add, p.fadd);
+                        if (FMA) acc[i][j] = sr_add(p, fma_rn(a, bvv[j], acc[i][j]), ph.c[0]);
                         else {
-                            const float pr = cast_fp_stochastic(mul_rn(a, bvv[j]), ph.c[1], p.rbits_mul, p.fmul);
-                            acc[i][j] = cast_fp_stochastic(add_rn(acc[i][j], pr), ph.c[0], p.rbits_add, p.fadd);
+                            const float pr = sr_mul(p, mul_rn(a, bvv[j]), ph.c[1]);
+                            acc[i][j] = sr_add(p, add_rn(acc[i][j], pr), ph.c[0]);
                         }
                     }
                 }
