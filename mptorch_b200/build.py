@@ -27,7 +27,7 @@ NVCC_FLAGS = [
 # compiler never contracts.  -fmad=false additionally keeps it from contracting the few plain
 # expressions that remain.  reduce.cu is the exception: it calls expf/logf, and those must compile
 # exactly as they do in the reference's CUDA build (nvcc defaults) to give the same bits.
-EXTRA_FLAGS = {"reduce.cu": [], "rows_softmax_fwd.cu": [], "rows_softmax_bwd.cu": [], "rows_layernorm_fwd.cu": [],
+EXTRA_FLAGS = {"reduce.cu": [], "rows_softmax_fwd.cu": [], "rows_softmax_bwd.cu": [], "rows_softmax_lse.cu": [], "rows_layernorm_fwd.cu": [],
                "rows_layernorm_bwd.cu": []}
 DEFAULT_EXTRA = ["-fmad=false"]
 

@@ -59,29 +59,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) softmax_lse_fwd_kernel(co
         const int lane = threadIdx.x & 31;
         const int64_t row = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
         if (row >= g.rows) return;
-        const float* x = in + row_base(g, row);
-        float* y = out + row_base(g, row);
-        const int C = g.channel;
-        const int64_t st = g.inner;
-        float m0 = -INFINITY, m1 = -INFINITY;
-        for (int k = lane; k < C; k += 64) {
-            m0 = fmaxf(m0, x[k * st]);
-            if (k + 32 < C) m1 = fmaxf(m1, x[(k + 32) * st]);
-        }
-        const float mx = tree64(m0, m1, FMax{});
-        float l0 = -INFINITY, l1 = -INFINITY;
-        for (int k = lane; k < C; k += 64) {
-            const float v0 = cast_fp_nearest(__fsub_rn(x[k * st], mx), foff);
-            y[k * st] = v0;
-            l0 = qlse(l0, v0);
-            if (k + 32 < C) {
-                const float v1 = cast_fp_nearest(__fsub_rn(x[(k + 32) * st], mx), foff);
-                y[(k + 32) * st] = v1;
-                l1 = qlse(l1, v1);
-            }
-        }
-        const float lgs = tree64(l0, l1, qlse);
-        for (int k = lane; k < C; k += 32) y[k * st] = expf(cast_fp_nearest(__fsub_rn(y[k * st], lgs), foff));
+        softmax_lse_row_tree(in + row_base(g, row), out + row_base(g, row), g.channel, g.inner, lane, foff, flse);
     } else {
         const int64_t row = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
         if (row >= g.rows) return;
@@ -329,6 +307,13 @@ int mpt_softmax_lse_forward_fmt(const float* in, float* out, int64_t outer, int 
     MPT_REQUIRE(in && out, "softmax_lse_forward: null pointer");
     const Caster fo = Caster::make(o), fl = Caster::make(l);
     const bool tree = order != MPT_ORDER_SEQ;
+    if (tree && rows_shape_ok(g, 1024) && fo.use_fast && fl.use_fast) {
+        // checked modes: x - max clamped to [-128, 0] and the running log-sum in [-128, log C] must lie inside the fast
+        // range of their formats (below 256)
+        const int mode = rows_mode({&fo, &fl}, fast_rn_exp_limit(fo.any.fp) >= 7 && fast_rn_exp_limit(fl.any.fp) >= 7);
+        launch_softmax_lse_rows(in, out, g, fo, fl, mode, stream);
+        return check_launch("softmax_lse_forward");
+    }
     if (tree) softmax_lse_fwd_kernel<true><<<row_blocks(g.rows, true), kWarpsPerBlock * 32, 0, as_stream(stream)>>>(in, out, g, fo, fl);
     else softmax_lse_fwd_kernel<false><<<row_blocks(g.rows, false), kWarpsPerBlock * 32, 0, as_stream(stream)>>>(in, out, g, fo, fl);
     return check_launch("softmax_lse_forward");

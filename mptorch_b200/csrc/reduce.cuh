@@ -119,6 +119,31 @@ struct QLse {
     __device__ __forceinline__ float operator()(float a, float b) const { return f(logf(__fadd_rn(expf(a), expf(b)))); }
 };
 
+// Log-sum-exp form of the softmax forward, one row in the CUDA association, whole input domain.
+__device__ __forceinline__ void softmax_lse_row_tree(const float* x, float* y, int C, int64_t st, int lane, const Caster& foff,
+                                                     const Caster& flse) {
+    const QLse qlse{flse};
+    float m0 = -INFINITY, m1 = -INFINITY;
+    for (int k = lane; k < C; k += 64) {
+        m0 = fmaxf(m0, x[k * st]);
+        if (k + 32 < C) m1 = fmaxf(m1, x[(k + 32) * st]);
+    }
+    const float mx = tree64(m0, m1, FMax{});
+    float l0 = -INFINITY, l1 = -INFINITY;
+    for (int k = lane; k < C; k += 64) {
+        const float v0 = cast_fp_nearest(__fsub_rn(x[k * st], mx), foff);
+        y[k * st] = v0;
+        l0 = qlse(l0, v0);
+        if (k + 32 < C) {
+            const float v1 = cast_fp_nearest(__fsub_rn(x[(k + 32) * st], mx), foff);
+            y[(k + 32) * st] = v1;
+            l1 = qlse(l1, v1);
+        }
+    }
+    const float lgs = tree64(l0, l1, qlse);
+    for (int k = lane; k < C; k += 32) y[k * st] = expf(cast_fp_nearest(__fsub_rn(y[k * st], lgs), foff));
+}
+
 // One row in the CUDA association, whole input domain; called by all 32 lanes of the warp that owns the row.
 __device__ __forceinline__ void softmax_fwd_row_tree(const float* x, float* y, int C, int64_t st, int lane, const Caster& fexp,
                                                      const Caster& foff, const Caster& facc) {
@@ -317,6 +342,9 @@ static __device__ __noinline__ void softmax_fwd_row_cold(const float* x, float* 
                                                  const Caster* facc) {
     softmax_fwd_row_tree(x, y, C, 1, lane, *fexp, *foff, *facc);
 }
+static __device__ __noinline__ void softmax_lse_row_cold(const float* x, float* y, int C, int lane, const Caster* foff, const Caster* flse) {
+    softmax_lse_row_tree(x, y, C, 1, lane, *foff, *flse);
+}
 static __device__ __noinline__ void softmax_bwd_row_cold(const float* y, const float* gr, float* o, int C, int lane, const Caster* fadd,
                                                  const Caster* fmul) {
     softmax_bwd_row_tree(y, gr, o, C, 1, lane, *fadd, *fmul);
@@ -407,6 +435,7 @@ inline RowLimits ln_limits(const LnFmt& f, int channel) {
 // Launchers of the register-resident kernels (rows_*.cu); the caller has checked rows_shape_ok and the formats.
 void launch_softmax_fwd_rows(const float* in, float* out, const RowGeom& g, const Caster& fe, const Caster& fo, const Caster& fa,
                              int mode, const RowLimits& lim, void* stream);
+void launch_softmax_lse_rows(const float* in, float* out, const RowGeom& g, const Caster& fo, const Caster& fl, int mode, void* stream);
 void launch_softmax_bwd_rows(const float* y, const float* grad, float* out, const RowGeom& g, const Caster& fa, const Caster& fm,
                              int mode, const RowLimits& lim, void* stream);
 void launch_layernorm_fwd_rows(const float* in, const float* weight, const float* bias, float* out, float* mean, float* rstd, float eps,

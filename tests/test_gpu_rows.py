@@ -70,6 +70,18 @@ def test_softmax_forward_rows_equal_general_kernel(q, C):
 
 
 @pytest.mark.parametrize("C", CHANNELS)
+def test_softmax_lse_forward_rows_equal_general_kernel(q, C):
+    x = nasty_rows(37, C, C + 9)
+    for (e, m) in FMTS + [(5, 21), (8, 21)]:
+        fast = q.float_softmax_lse_forward(x, -1, m, e, m, e)
+        general = q.float_softmax_lse_forward(x.t().contiguous(), 0, m, e, m, e).t()
+        assert bits_equal(fast, general), (C, e, m, (fast != general).nonzero()[:4].tolist())
+    fast = q.float_softmax_lse_forward(x, -1, 10, 5, 7, 8)
+    general = q.float_softmax_lse_forward(x.t().contiguous(), 0, 10, 5, 7, 8).t()
+    assert bits_equal(fast, general)
+
+
+@pytest.mark.parametrize("C", CHANNELS)
 def test_softmax_backward_rows(q, oracle, C):
     y = torch.softmax(nasty_rows(29, C, C + 1), dim=-1)
     y[3, 5] = float("nan")
