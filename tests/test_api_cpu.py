@@ -109,3 +109,40 @@ def test_default_precision_layers_run_anywhere():
     assert q.QSoftmax(-1, q.QSoftmaxFormats())(torch.randn(2, 5)).sum().item() == pytest.approx(2.0, abs=1e-5)
     assert q.QLayerNorm(8, q.QLayerNormFormats())(torch.randn(2, 8)).shape == (2, 8)
     assert q.QConv2d(3, 4, 3, q.QAffineFormats(), padding=1)(torch.randn(1, 3, 8, 8)).shape == (1, 4, 8, 8)
+
+
+def test_optimizer_wrapper_recognises_fusable_quantizers():
+    """QOptim fuses only quantizers whose format and rounding it can read; everything else is called per tensor."""
+    import mptorch_b200.quant as q
+    from mptorch_b200 import Binary8, FloatingPoint
+    from mptorch_b200.optim import _fusable
+
+    near = q.quantizer(forward_number=FloatingPoint(5, 10, True, True), forward_rounding="nearest")
+    sr = q.quantizer(forward_number=FloatingPoint(5, 10, True, True), forward_rounding="stochastic")
+    b8 = q.quantizer(forward_number=Binary8(3), forward_rounding="nearest")
+    assert _fusable(near, False)[1] == "nearest" and _fusable(near, False)[0].man == 10
+    assert _fusable(sr, False) is None and _fusable(sr, True)[1] == "stochastic"
+    assert _fusable(b8, False) is None
+    assert _fusable(lambda t: t, True) is None
+
+
+def test_streamed_gemm_and_multi_quantize_reject_cpu_execution():
+    import mptorch_b200.quant as q
+
+    a, b = torch.zeros(4, 4), torch.zeros(4, 4)
+    if not torch.cuda.is_available():
+        with pytest.raises(RuntimeError):
+            q.float_mm_streamed(a, b)
+    with pytest.raises(RuntimeError):
+        q.float_quantize_multi([a], 4, 3, "nearest")
+    with pytest.raises(RuntimeError):
+        q.float_mm_streamed(a, b.t())            # non-contiguous operand
+
+
+def test_implicit_conv_needs_cuda_and_plain_nearest_formats():
+    import mptorch_b200.quant as q
+    from mptorch_b200 import FloatingPoint
+    from mptorch_b200.quant.functional import implicit_conv_eligible
+
+    f = q.QAffineFormats(fwd_mac=(FloatingPoint(5, 10, True, False), FloatingPoint(4, 3, True, False)), fwd_rnd="nearest")
+    assert not implicit_conv_eligible(f, torch.zeros(1))          # CPU tensor
