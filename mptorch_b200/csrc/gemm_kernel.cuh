@@ -388,7 +388,21 @@ __global__ void __launch_bounds__(THREADS, MPT_MM_MIN_CTAS) mm_kernel(const __gr
 
     const int tid = threadIdx.x;
     const int ty = tid >> 4, tx = tid & 15;
-    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    // CTAs are launched x-fastest; walking the output in bands of kGroupM row tiles (all column tiles of a band before
+    // the next band) keeps the A rows and B columns that concurrently resident CTAs share inside L2, so the operands
+    // are read from HBM a few times instead of once per row of tiles.
+    int tile_m, tile_n;
+    {
+        constexpr int kGroupM = 16;
+        const int pid = blockIdx.y * gridDim.x + blockIdx.x;
+        const int per_band = kGroupM * gridDim.x;
+        const int band = pid / per_band, in_band = pid - band * per_band;
+        const int first_m = band * kGroupM;
+        const int rows_here = min((int)gridDim.y - first_m, kGroupM);
+        tile_n = in_band / rows_here;
+        tile_m = first_m + (in_band - tile_n * rows_here);
+    }
+    const int m0 = tile_m * BM, n0 = tile_n * BN;
     const int64_t batch = blockIdx.z;
     const float* A = p.a + batch * p.stride_a;
     const float* B = p.b + batch * p.stride_b;
