@@ -40,6 +40,10 @@ ALU_MAC = 3.41
 # kernel executes 3 packed FP instructions and ALU_MAC integer ones: 2 x 3 + 3.41 datapath slots.  Packing
 # saves issue slots, not datapath slots, so this is the bound the kernel actually runs into.
 SLOTS_MAC = 2 * 3.0 + ALU_MAC
+# dram__bytes_read.sum + dram__bytes_write.sum of one mm_kernel launch at 8192^3 on one GPU (one-pass ncu capture,
+# see profiles/): 3.88 GB read + 0.27 GB written against 0.805 GB of operands and result.  The kernel is not
+# memory-bound (29 GB/s), so the re-reads of B (once per band of 8 row tiles) cost nothing.
+MM_TRAFFIC_8192 = 3881603584 + 269514496
 METRIC = "float_mm GMAC/s (8192^3, e5m2 RN)"
 
 
@@ -532,7 +536,9 @@ def main() -> int:
                     "d2h_bytes_per_step": 4 * rows * S, "ms_per_step": e2e_ms},
             "gpu_launches": 4 * args.steps,
             "roofline": {"bound": "issue", "achieved": achieved, "peak": issue_peak, "unit": "GMAC/s",
-                         "frac": achieved / issue_peak, "traffic": None,
+                         "frac": achieved / issue_peak,
+                         "traffic": MM_TRAFFIC_8192 if (S == 8192 and world == 1) else None,
+                         "algorithmic_bytes": 3 * 4 * S * S // world + (world - 1) * 4 * S * S // world,
                          "alu_pipe_peak": sms * 64 * clk * 1e6 / ALU_MAC / 1e9,
                          "datapath_peak": sms * 128 * clk * 1e6 / SLOTS_MAC / 1e9,
                          "datapath_frac": achieved / (sms * 128 * clk * 1e6 / SLOTS_MAC / 1e9),

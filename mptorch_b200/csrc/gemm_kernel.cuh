@@ -393,7 +393,7 @@ __global__ void __launch_bounds__(THREADS, MPT_MM_MIN_CTAS) mm_kernel(const __gr
     // are read from HBM a few times instead of once per row of tiles.
     int tile_m, tile_n;
     {
-        constexpr int kGroupM = 16;
+        constexpr int kGroupM = 8;
         const int pid = blockIdx.y * gridDim.x + blockIdx.x;
         const int per_band = kGroupM * gridDim.x;
         const int band = pid / per_band, in_band = pid - band * per_band;
