@@ -1,6 +1,6 @@
 #!/usr/bin/env python
 """Headline benchmark: per-MAC rounded float_mm, 8192 x 8192 x 8192, e5m2 multiply and add, round to
-nearest (BASELINE.json metric "float_mm GMAC/s"), plus the elementwise quantizer's HBM throughput.
+nearest (the headline metric "float_mm GMAC/s"), plus the elementwise quantizer's HBM throughput.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
@@ -180,7 +180,7 @@ def run_reference(args) -> int:
 
 # ----------------------------------------------------------------------------------- HBM-bound kernels
 def run_kernels(args) -> int:
-    """Throughput of the HBM-bound kernels at BASELINE sizes: MX / NVFP4 on 16384 x 16384 (config 3), softmax rows of
+    """Throughput of the HBM-bound kernels at the benchmark sizes: MX / NVFP4 on 16384 x 16384 (config 3), softmax rows of
     1024 and layernorm rows of 768 at the config 5 tensor sizes.  `--size` scales the row counts (default 8192 = full)."""
     import torch
 
@@ -342,7 +342,7 @@ def main() -> int:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--quant-log2n", type=int, default=28, help="log2 of the quantizer leg's element count")
     ap.add_argument("--workload", default="mm", choices=["mm", "block", "kernels"],
-                    help="mm: the headline float_mm (default); block: BASELINE config 5, one GPT-2-small-shaped block, "
+                    help="mm: the headline float_mm (default); block: benchmark config 5, one GPT-2-small-shaped block, "
                          "fwd+bwd with (add e5m10, mul e4m3) MACs, data parallel with a gradient all-reduce")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -447,7 +447,7 @@ def main() -> int:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_ms = t.item() / e2e_steps
 
-    # ---- elementwise quantizers, HBM bound: 2^28 elements of the BASELINE config 2 mixture
+    # ---- elementwise quantizers, HBM bound: 2^28 elements of the benchmark config 2 mixture
     # (90% N(0,1), 5% N(0,1e-6), 5% U(-1e5,1e5)); e4m3 with subnormals and saturation; binary8 P=3
     quant, quant_all = None, {}
     if rank == 0:

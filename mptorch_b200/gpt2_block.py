@@ -1,5 +1,5 @@
 """A GPT-2-small-shaped transformer block built from the quantized layers: the caller-side workload of
-BASELINE config 5 (d=768, 12 heads, MLP 3072), wired like the reference's example
+benchmark config 5 (d=768, 12 heads, MLP 3072), wired like the reference's example
 ``examples/gpt/mptorch_shakespeare_softmax_gpt.py:246-337`` (pre-LN block: QLayerNorm -> attention with QLinear
 projections, qmatmul for QK^T and PV, QSoftmax -> QLayerNorm -> QLinear MLP with GELU).
 """

@@ -123,7 +123,7 @@ def test_fast_rounding_equals_exact_cast(hc, fmt):
 @pytest.mark.parametrize("sat", [0, 1])
 def test_whole_domain_fast_rounding_equals_exact_cast(hc, fmt, sat):
     """The elementwise quantizer's rounding (FP-pipe fast path plus overflow/special patch) equals the exact
-    caster on every fp32 pattern: all 2^32 for the BASELINE config 2 format e4m3, every 129th otherwise."""
+    caster on every fp32 pattern: all 2^32 for the benchmark config 2 format e4m3, every 129th otherwise."""
     e, m = fmt
     stride = 1 if fmt == (4, 3) else 129
     first_bad = np.zeros(1, dtype=np.uint32)
@@ -160,7 +160,7 @@ def test_whole_domain_fast_truncation_equals_exact_cast(hc, fmt, sat):
 @pytest.mark.parametrize("signed", [0, 1])
 @pytest.mark.parametrize("policy", [0, 1, 2])
 def test_whole_domain_fast_binary8_equals_exact_cast(hc, P, signed, policy):
-    stride = 1 if (P, signed, policy) == (3, 1, 1) else 257      # BASELINE config 2's binary8 arm is swept exhaustively
+    stride = 1 if (P, signed, policy) == (3, 1, 1) else 257      # benchmark config 2's binary8 arm is swept exhaustively
     _sweep(hc.hc_sweep_full_b8, (P, signed, policy), stride, f"binary8 P={P} signed={signed} policy={policy}")
 
 

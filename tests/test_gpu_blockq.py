@@ -16,7 +16,7 @@ def q():
 
 
 def data(rows, cols, seed):
-    """BASELINE config 3 distribution: N(0,1) times a per-row scale drawn log-uniform over [1e-3, 1e3]."""
+    """benchmark config 3 distribution: N(0,1) times a per-row scale drawn log-uniform over [1e-3, 1e3]."""
     rng = np.random.default_rng(seed)
     s = 10.0 ** rng.uniform(-3, 3, size=(rows, 1))
     return (rng.standard_normal((rows, cols)) * s).astype(np.float32)
@@ -71,7 +71,7 @@ def test_nvfp4(q, oracle, shape):
 
 
 def test_config3_full_size_properties(q, oracle):
-    """16384 x 16384 (BASELINE config 3): sampled rows equal the oracle; quantization is idempotent."""
+    """16384 x 16384 (benchmark config 3): sampled rows equal the oracle; quantization is idempotent."""
     g = torch.Generator(device="cuda").manual_seed(9)
     n = 16384
     x = torch.randn(n, n, device="cuda", generator=g) * (10.0 ** (torch.rand(n, 1, device="cuda", generator=g) * 6 - 3))

@@ -45,7 +45,7 @@ SHAPES = [(78, 101, 145), (64, 256, 48), (9, 32, 12), (1, 1, 1), (130, 8, 70), (
 
 
 def test_config1_sequential_256(be, oracle):
-    """BASELINE config 1: 256x256x256, N(0,1), e5m2 multiply and add, nearest, sequential K."""
+    """benchmark config 1: 256x256x256, N(0,1), e5m2 multiply and add, nearest, sequential K."""
     rng = np.random.default_rng(2025)
     a = rng.standard_normal((256, 256)).astype(np.float32)
     b = rng.standard_normal((256, 256)).astype(np.float32)
@@ -165,7 +165,7 @@ def test_batched_mixed_ranges(be, oracle):
 
 
 def test_attention_shapes(be, oracle):
-    """BASELINE config 5 attention GEMM shapes at reduced batch: [B,1024,64]x[B,64,1024] rows sampled."""
+    """benchmark config 5 attention GEMM shapes at reduced batch: [B,1024,64]x[B,64,1024] rows sampled."""
     rng = np.random.default_rng(8)
     a = rng.standard_normal((2, 96, 64)).astype(np.float32)
     b = rng.standard_normal((2, 64, 1024)).astype(np.float32)
@@ -241,7 +241,7 @@ def test_exact_path_without_workspace(oracle):
 
 @pytest.mark.parametrize("fmts", [((5, 2), (5, 2)), ((5, 10), (4, 3)), ((8, 7), (5, 2))])
 def test_full_size_row_samples_and_sharding(be, oracle, fmts):
-    """BASELINE config 4 at its largest size (8192^3 for the headline format, 4096^3 otherwise): sampled
+    """benchmark config 4 at its largest size (8192^3 for the headline format, 4096^3 otherwise): sampled
     rows equal the oracle bit for bit (rows of C are independent), and a row-sharded run equals the
     single launch (the multi-GPU decomposition)."""
     fadd, fmul = fmts

@@ -28,7 +28,7 @@ def inputs(seed, n):
 
 
 def mixture(n, seed, sigma_small=1e-3):
-    """BASELINE config 2 value distribution: 90% N(0,1), 5% N(0, sigma_small^2), 5% U(-1e5, 1e5)."""
+    """benchmark config 2 value distribution: 90% N(0,1), 5% N(0, sigma_small^2), 5% U(-1e5, 1e5)."""
     rng = np.random.default_rng(seed)
     u = rng.random(n)
     x = rng.standard_normal(n)
@@ -190,7 +190,7 @@ def test_checks_mirror_reference(be):
 
 
 def test_full_size_properties(be):
-    """2^28 elements (BASELINE config 2 size): idempotence, sign symmetry and agreement with a sharded run."""
+    """2^28 elements (benchmark config 2 size): idempotence, sign symmetry and agreement with a sharded run."""
     n = 1 << 28
     g = torch.Generator(device="cuda").manual_seed(3)
     x = torch.randn(n, device="cuda", generator=g)

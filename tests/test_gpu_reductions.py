@@ -135,7 +135,7 @@ def test_qsum_rows(q, oracle):
 
 
 def test_config5_shapes(q, oracle):
-    """BASELINE config 5 reduction shapes: softmax rows of 1024 and layernorm rows of 768 (rows sampled for the oracle)."""
+    """benchmark config 5 reduction shapes: softmax rows of 1024 and layernorm rows of 768 (rows sampled for the oracle)."""
     g = torch.Generator(device="cuda").manual_seed(5)
     att = torch.randn(8, 12, 128, 1024, device="cuda", generator=g)
     y = q.float_softmax_forward(att, -1, 10, 5, 10, 5, 10, 5)

@@ -234,7 +234,7 @@ def test_superfp_vs_live_reference(oracle, ref_cpu):
 
 
 def test_mm_config1_vs_live_reference(oracle, ref_cpu):
-    """BASELINE config 1 at reduced M,N (full K=256): e5m2 multiply and add, nearest, sequential K."""
+    """benchmark config 1 at reduced M,N (full K=256): e5m2 multiply and add, nearest, sequential K."""
     torch.manual_seed(0)
     a, b = torch.randn(48, 256), torch.randn(256, 40)
     c = torch.zeros(48, 40)
