@@ -29,22 +29,81 @@ sys.path.insert(0, ROOT)
 
 SIZE = 8192
 FMT = dict(man_add=2, exp_add=5, man_mul=2, exp_mul=5, subnormals=True, saturate=False)
-# Issued thread-instructions per MAC of the GEMM kernel's fast path, measured with ncu
-# (smsp__inst_executed.sum x 32 / MACs; see profiles/).  The issue-rate roofline is
-# SMs x 128 lanes x SM clock / I_MAC.  Of those instructions ALU_MAC run on the half-rate ALU pipe
-# (64 lanes per SM per clock), which is the tighter bound of the two and is reported alongside.
-I_MAC = 6.99
-ALU_MAC = 3.41
-# An SM executes at most 128 fp32/int32 lane-operations per clock in total (the integer lanes share one of
-# the two fp32 datapaths), and a packed fp32x2 instruction fills two of those slots per lane.  Per MAC the
-# kernel executes 3 packed FP instructions and ALU_MAC integer ones: 2 x 3 + 3.41 datapath slots.  Packing
-# saves issue slots, not datapath slots, so this is the bound the kernel actually runs into.
-SLOTS_MAC = 2 * 3.0 + ALU_MAC
-# dram__bytes_read.sum + dram__bytes_write.sum of one mm_kernel launch at 8192^3 on one GPU (one-pass ncu capture,
-# see profiles/): 3.88 GB read + 0.27 GB written against 0.805 GB of operands and result.  The kernel is not
-# memory-bound (29 GB/s), so the re-reads of B (once per band of 8 row tiles) cost nothing.
-MM_TRAFFIC_8192 = 3881603584 + 269514496
+# The roofline of the GEMM kernel is built from counters of an ncu capture of that kernel: issued thread-instructions
+# per MAC (smsp__inst_executed.sum x 32 / MACs), the share of them on the half-rate ALU pipe, and the DRAM traffic of one
+# launch at the bench size.  They live in profiles/mm_kernel_counters.json together with the command that produced them
+# and the git blob hashes of the kernel sources they were taken at; when the sources have changed since, the bench line
+# says so ("constants_stale") instead of silently reporting an old roofline.
+COUNTERS_PATH = os.path.join(ROOT, "profiles", "mm_kernel_counters.json")
+KERNEL_SOURCES = ("mptorch_b200/csrc/gemm_kernel.cuh", "mptorch_b200/csrc/cast.cuh")
+
+
+def git_blob_hash(path: str) -> str:
+    import hashlib
+
+    data = open(path, "rb").read()
+    return hashlib.sha1(b"blob %d\0" % len(data) + data).hexdigest()
+
+
+def load_counters() -> dict:
+    c = json.load(open(COUNTERS_PATH))
+    now = {src: git_blob_hash(os.path.join(ROOT, src)) for src in KERNEL_SOURCES}
+    c["constants_stale"] = any(c.get("source_blobs", {}).get(src) != h for src, h in now.items())
+    return c
+
+
+def record_counters(per_mac_csv: str, per_mac_size: int, traffic_csv: str | None, note: str) -> dict:
+    """Rebuild profiles/mm_kernel_counters.json from ncu `--csv` logs of the GEMM kernel: `per_mac_csv` holds
+    smsp__inst_executed.sum, sm__inst_executed_pipe_alu.sum, sm__inst_executed_pipe_fma.sum (and anything else asked for) of
+    one mm_kernel launch at M = N = K = `per_mac_size`; `traffic_csv` dram__bytes_read.sum / dram__bytes_write.sum of one
+    launch at 8192^3.  The hashes of the kernel sources as they are now are stored beside the numbers."""
+    import csv
+
+    def metrics(path):
+        out = {}
+        rows = [r for r in csv.reader(l for l in open(path) if l.startswith('"'))]
+        head = rows[0]
+        ik, im, iv, iu = head.index("Kernel Name"), head.index("Metric Name"), head.index("Metric Value"), head.index("Metric Unit")
+        for r in rows[1:]:
+            if "mm_kernel" in r[ik] and r[im] not in out:
+                v = float(r[iv].replace(",", ""))
+                unit = r[iu].lower()
+                v *= {"kbyte": 1e3, "mbyte": 1e6, "gbyte": 1e9}.get(unit, 1.0)
+                out[r[im]] = v
+                out["kernel"] = r[ik]
+        return out
+
+    m = metrics(per_mac_csv)
+    macs = float(per_mac_size) ** 3
+    old = json.load(open(COUNTERS_PATH)) if os.path.exists(COUNTERS_PATH) else {}
+    c = dict(old)
+    c["kernel"] = m.pop("kernel", old.get("kernel"))
+    c["captured_at"] = note
+    c["metrics"] = {k: v for k, v in m.items()}
+    c["metrics"]["macs"] = macs
+    c["inst_per_mac"] = round(m["smsp__inst_executed.sum"] * 32 / macs, 3)
+    c["alu_inst_per_mac"] = round(m["sm__inst_executed_pipe_alu.sum"] * 32 / macs, 3)
+    if "sm__inst_executed_pipe_fma.sum" in m:
+        # fp32 instructions of this kernel's fast path are all packed fp32x2 (FMUL2 / FADD2 / FFMA2)
+        c["packed_fp_inst_per_mac"] = round(m["sm__inst_executed_pipe_fma.sum"] * 32 / macs, 3)
+    if traffic_csv:
+        t = metrics(traffic_csv)
+        c["metrics"]["dram__bytes_read.sum_8192cubed"] = t["dram__bytes_read.sum"]
+        c["metrics"]["dram__bytes_write.sum_8192cubed"] = t["dram__bytes_write.sum"]
+        c["dram_bytes_per_launch_8192cubed"] = int(t["dram__bytes_read.sum"] + t["dram__bytes_write.sum"])
+    c["source_blobs"] = {src: git_blob_hash(os.path.join(ROOT, src)) for src in KERNEL_SOURCES}
+    json.dump(c, open(COUNTERS_PATH, "w"), indent=1)
+    return c
+
+
 METRIC = "float_mm GMAC/s (8192^3, e5m2 RN)"
+WORKLOAD = "float_mm 8192x8192x8192, mul e5m2 / add e5m2, nearest, subnormals, no saturate"
+
+
+def config_for(size: int) -> dict:
+    """The same dictionary from both arms (the reference CPU arm and the GPU arm) for the same command line."""
+    wl = WORKLOAD if size == SIZE else WORKLOAD.replace("8192x8192x8192", "%dx%dx%d" % (size, size, size))
+    return {"workload": wl, "l2": "operands (512 MiB at 8192^3) exceed L2, no flush between iterations"}
 
 
 # ----------------------------------------------------------------------------------- clocks
@@ -169,8 +228,9 @@ def run_reference(args) -> int:
     line = {"impl": "reference", "metric": METRIC, "value": best["value"], "unit": "GMAC/s", "n_gpus": args.gpus,
             "steps": steps, "warmup": max(0, args.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f32 (each multiply and add rounded to e5m2)", "data": "synthetic",
-            "config": {"workload": "float_mm 8192x8192x8192 e5m2/e5m2 nearest, reference CPU path on a row sample",
-                       "accum_order": "seq"},
+            "config": config_for(SIZE), "accum_order": "seq",
+            "notes": "reference CPU extension (quant_cpu, sequential K order, single threaded) on one row of the problem per "
+                     "host core, all cores at once; the MAC count per row is that of the GPU arm",
             "cpu_baseline": {k: best[k] for k in ("value", "unit", "cores", "kind", "sample")},
             "e2e": {"value": best["value"], "unit": "GMAC/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
@@ -179,16 +239,24 @@ def run_reference(args) -> int:
 
 
 # ----------------------------------------------------------------------------------- HBM-bound kernels
-def run_kernels(args) -> int:
+def _ref_cuda():
+    """The reference's own CUDA extension built for sm_100a (oracle/_ref/quant_cuda), or None when it is not there."""
+    try:
+        from oracle.build_ref import load_ref
+
+        return load_ref("quant_cuda")
+    except Exception:
+        return None
+
+
+def kernels_legs(dev, steps: int, warmup: int, scale: float = 1.0, with_reference: bool = True) -> dict:
     """Throughput of the HBM-bound kernels at the benchmark sizes: MX / NVFP4 on 16384 x 16384 (config 3), softmax rows of
-    1024 and layernorm rows of 768 at the config 5 tensor sizes.  `--size` scales the row counts (default 8192 = full)."""
+    1024 and layernorm rows of 768 at the config 5 tensor sizes (`scale` shrinks the row counts).  Beside each figure that
+    has a counterpart, the reference's own CUDA kernel (unmodified sources built for sm_100a) is timed on the same tensor."""
     import torch
 
     import mptorch_b200.quant as q
 
-    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
-    torch.cuda.set_device(dev)
-    scale = args.size / 8192.0
     g = torch.Generator(device=dev).manual_seed(7)
     peaks = {}
     try:
@@ -197,20 +265,31 @@ def run_kernels(args) -> int:
         pass
     hbm_peak = peaks.get("hbm_gbs", 6650.0)
     out = {}
+    ref = _ref_cuda() if with_reference else None
 
-    def timed(name, fn, nbytes):
-        for _ in range(max(args.warmup, 3)):
+    def clock(fn):
+        for _ in range(max(warmup, 3)):
             fn()
         torch.cuda.synchronize(dev)
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
-        for _ in range(args.steps):
+        for _ in range(steps):
             fn()
         b.record()
         torch.cuda.synchronize(dev)
-        ms = a.elapsed_time(b) / args.steps
+        return a.elapsed_time(b) / steps
+
+    def timed(name, fn, nbytes, ref_fn=None):
+        ms = clock(fn)
         out[name] = {"ms": round(ms, 4), "gbs": round(nbytes / ms / 1e6, 1), "frac_of_hbm_peak": round(nbytes / ms / 1e6 / hbm_peak, 3),
                      "algorithmic_bytes": nbytes}
+        if ref is not None and ref_fn is not None:
+            try:
+                rms = clock(ref_fn)
+                out[name]["reference_cuda_ms"] = round(rms, 4)
+                out[name]["speedup_vs_reference_cuda"] = round(rms / ms, 2)
+            except Exception as ex:
+                out[name]["reference_cuda_error"] = repr(ex)[:120]
 
     n = int(16384 * scale)
     x = torch.randn(n, 16384, device=dev, generator=g) * (10.0 ** (torch.rand(n, 1, device=dev, generator=g) * 6 - 3))
@@ -224,22 +303,39 @@ def run_kernels(args) -> int:
     rows = int(8 * 12 * 1024 * scale)
     att = torch.randn(rows, 1024, device=dev, generator=g) * 3
     gy = torch.randn(rows, 1024, device=dev, generator=g)
+    ro = torch.zeros_like(att) if ref is not None else None
     e = att.numel()
-    timed("softmax_fwd_e5m10_rows1024", lambda: q.float_softmax_forward(att, -1, 10, 5, 10, 5, 10, 5), 8 * e)
-    timed("softmax_fwd_e8m7_rows1024", lambda: q.float_softmax_forward(att, -1, 7, 8, 7, 8, 7, 8), 8 * e)
-    timed("softmax_lse_fwd_e5m10_rows1024", lambda: q.float_softmax_lse_forward(att, -1, 10, 5, 10, 5), 8 * e)
+    timed("softmax_fwd_e5m10_rows1024", lambda: q.float_softmax_forward(att, -1, 10, 5, 10, 5, 10, 5), 8 * e,
+          lambda: ref.float_quantize_nearest_softmax_forward(att, ro, -1, 10, 5, 10, 5, 10, 5, True, False))
+    timed("softmax_fwd_e8m7_rows1024", lambda: q.float_softmax_forward(att, -1, 7, 8, 7, 8, 7, 8), 8 * e,
+          lambda: ref.float_quantize_nearest_softmax_forward(att, ro, -1, 7, 8, 7, 8, 7, 8, True, False))
+    timed("softmax_lse_fwd_e5m10_rows1024", lambda: q.float_softmax_lse_forward(att, -1, 10, 5, 10, 5), 8 * e,
+          lambda: ref.float_quantize_nearest_softmax_lse_forward(att, ro, -1, 10, 5, 10, 5, True, False))
     y = q.float_softmax_forward(att, -1, 10, 5, 10, 5, 10, 5)
-    timed("softmax_bwd_e5m10_rows1024", lambda: q.float_softmax_backward(y, gy, -1, 10, 5, 10, 5), 12 * e)
-    del att, gy, y
+    timed("softmax_bwd_e5m10_rows1024", lambda: q.float_softmax_backward(y, gy, -1, 10, 5, 10, 5), 12 * e,
+          lambda: ref.float_quantize_nearest_softmax_backward(y, gy, ro, -1, 10, 5, 10, 5, True, False))
+    del att, gy, y, ro
     rows = int(8192 * 8 * scale)      # 8 layernorm-sized tensors' worth of rows so the tensor exceeds L2
     xl = torch.randn(rows, 768, device=dev, generator=g)
     gl = torch.randn(rows, 768, device=dev, generator=g)
     w, b = torch.randn(768, device=dev, generator=g), torch.randn(768, device=dev, generator=g)
     e = xl.numel()
-    timed("layernorm_fwd_e5m10_rows768", lambda: q.float_layernorm_forward(xl, w, b, 1e-5, [-1], 10, 5, 10, 5, 10, 5, 10, 5), 8 * e)
-    timed("layernorm_fwd_e8m7_rows768", lambda: q.float_layernorm_forward(xl, w, b, 1e-5, [-1], 7, 8, 7, 8, 7, 8, 7, 8), 8 * e)
+    if ref is not None:
+        ry, rm, rr = torch.zeros_like(xl), torch.zeros(rows, device=dev), torch.zeros(rows, device=dev)
+        rgi, rgg, rgb = torch.zeros_like(xl), torch.zeros(768, device=dev), torch.zeros(768, device=dev)
+    timed("layernorm_fwd_e5m10_rows768", lambda: q.float_layernorm_forward(xl, w, b, 1e-5, [-1], 10, 5, 10, 5, 10, 5, 10, 5), 8 * e,
+          lambda: ref.float_quantize_layernorm_forward(xl, w, b, ry, rm, rr, 1e-5, [-1], 10, 5, 10, 5, 10, 5, 10, 5, True, False))
+    timed("layernorm_fwd_e8m7_rows768", lambda: q.float_layernorm_forward(xl, w, b, 1e-5, [-1], 7, 8, 7, 8, 7, 8, 7, 8), 8 * e,
+          lambda: ref.float_quantize_layernorm_forward(xl, w, b, ry, rm, rr, 1e-5, [-1], 7, 8, 7, 8, 7, 8, 7, 8, True, False))
     _, mean, rstd = q.float_layernorm_forward(xl, w, b, 1e-5, [-1], 10, 5, 10, 5, 10, 5, 10, 5)
-    timed("layernorm_bwd_e5m10_rows768", lambda: q.float_layernorm_backward(xl, gl, w, b, mean, rstd, [-1], 10, 5, 10, 5, 10, 5), 20 * e)
+    timed("layernorm_bwd_e5m10_rows768", lambda: q.float_layernorm_backward(xl, gl, w, b, mean, rstd, [-1], 10, 5, 10, 5, 10, 5), 20 * e,
+          lambda: ref.float_quantize_layernorm_backward(xl, gl, w, b, mean, rstd, rgi, rgg, rgb, [-1], 10, 5, 10, 5, 10, 5, True, False))
+    # the same backward pass at the config 5 tensor size (8192 rows): the parameter gradients are a chain over the rows
+    r5 = max(1, int(8192 * scale))
+    timed("layernorm_bwd_e5m10_rows768_config5_size", lambda: q.float_layernorm_backward(xl[:r5], gl[:r5], w, b, mean[:r5], rstd[:r5], [-1], 10, 5, 10, 5, 10, 5),
+          20 * r5 * 768,
+          lambda: ref.float_quantize_layernorm_backward(xl[:r5], gl[:r5], w, b, mean[:r5], rstd[:r5], rgi[:r5], rgg, rgb, [-1], 10, 5, 10, 5, 10, 5, True, False))
+    del xl, gl
     # QConv2d forward (ResNet-style 3x3 layer, 64 -> 64 channels, 56 x 56, batch 64): implicit GEMM vs unfold + GEMM
     import mptorch_b200.quant.modules as qmod
     from mptorch_b200 import FloatingPoint
@@ -260,43 +356,114 @@ def run_kernels(args) -> int:
             qmod.implicit_conv_eligible = eligible
     for k in ("qconv2d_fwd_implicit_gemm", "qconv2d_fwd_unfold_gemm"):
         out[k] = {"ms": out[k]["ms"], "gmacs": round(conv_macs / out[k]["ms"] / 1e6, 1)}
-    print(json.dumps({"metric": "HBM-bound kernels, GB/s at algorithmic bytes", "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
-                      "hbm_peak_gbs": hbm_peak, "kernels": out}))
+    return {"hbm_peak_gbs": hbm_peak, "unit": "GB/s at algorithmic bytes", "kernels": out}
+
+
+def run_kernels(args) -> int:
+    import torch
+
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    res = kernels_legs(dev, args.steps, args.warmup, args.size / 8192.0)
+    print(json.dumps({"metric": "HBM-bound kernels, GB/s at algorithmic bytes", "unit": "GB/s", "n_gpus": 1, "steps": args.steps, **res}))
+    return 0
+
+
+# ----------------------------------------------------------------------------------- config 4: GEMM sweep
+C4_PAIRS = {"mul e4m3 / add e5m10": (10, 5, 3, 4), "mul e5m2 / add e8m7": (7, 8, 2, 5), "mul e5m2 / add e5m2": (2, 5, 2, 5)}
+
+
+def c4_sweep(dev, sizes=(2048, 4096, 8192), variants=True) -> dict:
+    """float_mm at M = N = K in `sizes` for the three format pairs of benchmark config 4, both accumulation orders, the
+    fused multiply-add form, and (at 4096) the Kahan-compensated and stochastic variants.  CUDA events around a loop of
+    calls through the reference-named backend functions; operands of 2048^3 (48 MiB) fit L2, the larger ones do not."""
+    import torch
+
+    from mptorch_b200 import backend as be
+
+    g = torch.Generator(device=dev).manual_seed(4)
+
+    def timed(fn, reps):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        return e0.elapsed_time(e1) / reps
+
+    rows = []
+    for S in sizes:
+        a = torch.randn(S, S, device=dev, generator=g)
+        b = torch.randn(S, S, device=dev, generator=g)
+        c = torch.empty(S, S, device=dev)
+        reps = 20 if S <= 2048 else (6 if S <= 4096 else 3)
+
+        def rec(name, order, form, ms):
+            rows.append({"size": S, "formats": name, "order": order, "form": form, "ms": round(ms, 3),
+                         "tmacs": round(float(S) ** 3 / ms / 1e9, 3)})
+
+        for name, (ma, ea, mm, em) in C4_PAIRS.items():
+            for order in ("cuda", "seq"):
+                rec(name, order, "mul+add", timed(lambda: be.float_quantize_nearest_mm(a, b, c, S, S, S, ma, ea, mm, em, True, False, False, order=order), reps))
+            rec(name, "cuda", "fma (add format)", timed(lambda: be.float_quantize_nearest_mm_fma(a, b, c, S, S, S, ma, ea, True, False, False, order="cuda"), reps))
+        if variants and S == 4096:
+            for name, (ma, ea, mm, em) in C4_PAIRS.items():
+                rec(name, "cuda", "kahan", timed(lambda: be.float_quantize_nearest_mm(a, b, c, S, S, S, ma, ea, mm, em, True, False, True, order="cuda"), 3))
+                rec(name, "cuda", "stochastic", timed(lambda: be.float_quantize_stochastic_mm(a, b, c, S, S, S, ma, ea, 23 - ma, mm, em, 23 - mm, True, False, seed=5), 3))
+            rec("fma e5m10", "cuda", "kahan fma", timed(lambda: be.float_quantize_nearest_mm_fma(a, b, c, S, S, S, 10, 5, True, False, True, order="cuda"), 3))
+            rec("fma e5m10", "cuda", "stochastic fma", timed(lambda: be.float_quantize_stochastic_mm_fma(a, b, c, S, S, S, 10, 5, 13, True, False, seed=5), 3))
+        del a, b, c
+    return {"rows": rows}
+
+
+def run_c4(args) -> int:
+    import torch
+
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    sizes = (2048, 4096, 8192) if args.size == SIZE else (args.size,)
+    out = c4_sweep(dev, sizes)
+    for r in out["rows"]:
+        sys.stderr.write("%5d  %-22s %-4s %-16s %9.3f ms %7.3f TMAC/s\n" % (r["size"], r["formats"], r["order"], r["form"], r["ms"], r["tmacs"]))
+    print(json.dumps({"metric": "float_mm sweep (benchmark config 4), simulated TMAC/s", "unit": "TMAC/s", "n_gpus": 1, **out}))
     return 0
 
 
 # ----------------------------------------------------------------------------------- config 5: training step
-def run_block(args) -> int:
+def block_step(dev, world: int, rank: int, steps: int, warmup: int, overlap: bool = True) -> dict | None:
     """One quantized GPT-2-small block (d=768, 12 heads, MLP 3072, seq 1024, batch 8 per GPU), forward + backward,
-    gradients averaged over the ranks with bucketed NCCL all-reduces.  Weak scaling: the per-GPU batch is fixed."""
+    gradients averaged over the ranks with bucketed NCCL all-reduces launched from autograd hooks while the backward
+    pass runs (`overlap`; otherwise after it).  Weak scaling: the per-GPU batch is fixed.  The process group must
+    exist already when world > 1.  Returns the record on rank 0, None elsewhere."""
     import torch
     import torch.distributed as dist
 
     from mptorch_b200.gpt2_block import BlockConfig, QTinyGPT
-    from mptorch_b200.parallel import allreduce_gradients
+    from mptorch_b200.parallel import GradientAllReducer, allreduce_gradients
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
     B, T = 8, 1024
     torch.manual_seed(0)                                   # identical random-init weights on every rank
     model = QTinyGPT(BlockConfig(seq_len=T)).to(dev)
     g = torch.Generator().manual_seed(1000 + rank)
     idx_host = torch.randint(0, 50257, (B, T), generator=g).pin_memory()     # synthetic uniform token ids
+    reducer = GradientAllReducer(model.parameters()) if (overlap and world > 1) else None
 
     def step():
         idx = idx_host.to(dev, non_blocking=True)
         model.zero_grad(set_to_none=True)
         loss = model(idx).float().pow(2).mean()
         loss.backward()
-        allreduce_gradients(model.parameters())
+        if reducer is not None:
+            reducer.finish()
+        else:
+            allreduce_gradients(model.parameters())
         return loss
 
-    warmup = max(args.warmup, 3)
+    warmup = max(warmup, 3)
     for _ in range(warmup):
         step()
     if world > 1:
@@ -304,7 +471,7 @@ def run_block(args) -> int:
     torch.cuda.synchronize(dev)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(args.steps):
+    for _ in range(steps):
         loss = step()
         loss_host = loss.item()                            # device -> host read of the step's result
     e1.record()
@@ -314,17 +481,37 @@ def run_block(args) -> int:
     t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = t.item() / args.steps
-    if rank == 0:
-        macs = model.macs_per_step(B, T) * world
-        v = macs / ms / 1e6
-        print(json.dumps({
-            "metric": "GPT-2-small block training step, simulated GMAC/s", "value": v, "unit": "GMAC/s", "n_gpus": world,
-            "steps": args.steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+    ms = t.item() / steps
+    if reducer is not None:
+        reducer.remove()
+    macs = model.macs_per_step(B, T) * world
+    del model
+    if rank != 0:
+        return None
+    v = macs / ms / 1e6
+    return {"metric": "GPT-2-small block training step, simulated GMAC/s", "value": v, "unit": "GMAC/s", "n_gpus": world,
+            "steps": steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32 (MACs rounded: add e5m10, mul e4m3)", "data": "synthetic",
             "config": {"workload": "QLinear/QLayerNorm/QSoftmax block d=768 h=12 mlp=3072 seq=1024 batch=8 per GPU, fwd+bwd, "
-                                   "DP gradient all-reduce", "loss": loss_host},
-            "e2e": {"value": v, "unit": "GMAC/s", "h2d_bytes_per_step": B * T * 8, "d2h_bytes_per_step": 4, "ms_per_step": ms}}))
+                                   "DP gradient all-reduce %s" % ("under the backward pass" if reducer is not None or world == 1 else "after the backward pass"),
+                       "loss": loss_host},
+            "e2e": {"value": v, "unit": "GMAC/s", "h2d_bytes_per_step": B * T * 8, "d2h_bytes_per_step": 4, "ms_per_step": ms}}
+
+
+def run_block(args) -> int:
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    rec = block_step(dev, world, rank, args.steps, args.warmup, overlap=not args.no_overlap)
+    if rec is not None:
+        print(json.dumps(rec))
     if world > 1:
         dist.destroy_process_group()
     return 0
@@ -340,22 +527,37 @@ def main() -> int:
     ap.add_argument("--size", type=int, default=SIZE, help="M=N=K (the headline is 8192)")
     ap.add_argument("--order", default="cuda", choices=["cuda", "seq"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="headline legs only: skip the kernel, sweep and training-step legs")
+    ap.add_argument("--no-overlap", action="store_true", help="collectives after the compute they follow instead of under it")
+    ap.add_argument("--panels", type=int, default=4, help="row panels per rank whose all-gather runs under the next panel's kernel")
     ap.add_argument("--quant-log2n", type=int, default=28, help="log2 of the quantizer leg's element count")
-    ap.add_argument("--workload", default="mm", choices=["mm", "block", "kernels"],
+    ap.add_argument("--workload", default="mm", choices=["mm", "block", "kernels", "c4"],
                     help="mm: the headline float_mm (default); block: benchmark config 5, one GPT-2-small-shaped block, "
                          "fwd+bwd with (add e5m10, mul e4m3) MACs, data parallel with a gradient all-reduce")
+    ap.add_argument("--record-counters", nargs="+", metavar="CSV",
+                    help="no benchmark: rebuild profiles/mm_kernel_counters.json from ncu --csv logs "
+                         "(PER_MAC_CSV SIZE [TRAFFIC_CSV_8192]) and stamp it with the kernel sources' git blob hashes")
     args = ap.parse_args()
+    if args.record_counters:
+        rc = args.record_counters
+        c = record_counters(rc[0], int(rc[1]), rc[2] if len(rc) > 2 else None,
+                            "float_mm %s^3 mul e5m2 / add e5m2 (per-MAC counters), 8192^3 (DRAM traffic)" % rc[1])
+        print(json.dumps(c))
+        return 0
     if args.impl == "reference":
         return run_reference(args)
     if args.workload == "block":
         return run_block(args)
     if args.workload == "kernels":
         return run_kernels(args)
+    if args.workload == "c4":
+        return run_c4(args)
 
     import torch
     import torch.distributed as dist
 
     from mptorch_b200 import backend as be
+    from mptorch_b200.parallel import sharded_float_mm, sharded_float_mm_streamed
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -370,6 +572,7 @@ def main() -> int:
     assert S % world == 0
     rows = S // world
     warmup = max(args.warmup, 3)
+    panels = 1 if (world == 1 or args.no_overlap) else max(1, args.panels)
 
     g = torch.Generator(device=dev).manual_seed(1234)
     a_full = torch.randn(S, S, device=dev, generator=g)      # same on every rank
@@ -377,13 +580,25 @@ def main() -> int:
     a = a_full[rank * rows:(rank + 1) * rows].contiguous()
     del a_full
     c_full = torch.empty(S, S, device=dev)
-    c = c_full[rank * rows:(rank + 1) * rows]
+    launches = [0]
+
+    def mm_rows(x, y):
+        """This rank's kernel on a block of its rows: the reference-named backend entry (C ABI underneath)."""
+        out = torch.empty(x.shape[0], S, device=dev)
+        be.float_quantize_nearest_mm(x, y, out, x.shape[0], S, S, FMT["man_add"], FMT["exp_add"], FMT["man_mul"],
+                                     FMT["exp_mul"], True, False, False, order=args.order)
+        launches[0] += 4                                     # stats_init_kernel, two stats_kernel, mm_kernel
+        return out
 
     def step():
-        be.float_quantize_nearest_mm(a, b, c, rows, S, S, FMT["man_add"], FMT["exp_add"], FMT["man_mul"],
-                                     FMT["exp_mul"], True, False, False, order=args.order)
-        if world > 1:
-            dist.all_gather_into_tensor(c_full, c)
+        # one float_mm over the whole problem: the local row block in `panels` panels, each panel's C rows all-gathered
+        # on a side stream under the next panel's kernel
+        if world == 1:
+            be.float_quantize_nearest_mm(a, b, c_full, S, S, S, FMT["man_add"], FMT["exp_add"], FMT["man_mul"],
+                                         FMT["exp_mul"], True, False, False, order=args.order)
+            launches[0] += 4
+        else:
+            sharded_float_mm(a, b, S, mm_rows, panels=panels, out=c_full)
 
     def barrier():
         if world > 1:
@@ -398,21 +613,27 @@ def main() -> int:
         sampler.start()
         time.sleep(0.3)
     barrier()
+    launches[0] = 0
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    kev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     e0.record()
     for i in range(args.steps):
-        kev[i][0].record()
-        be.float_quantize_nearest_mm(a, b, c, rows, S, S, FMT["man_add"], FMT["exp_add"], FMT["man_mul"],
-                                     FMT["exp_mul"], True, False, False, order=args.order)
-        kev[i][1].record()
-        if world > 1:
-            dist.all_gather_into_tensor(c_full, c)
+        step()
     e1.record()
     barrier()
     total_ms = e0.elapsed_time(e1)
+    launches_timed = launches[0]
+    # the kernel alone (no exchange), for the roofline: this rank's whole row block in one launch, CUDA events around it
+    c_rows = torch.empty(rows, S, device=dev)
+    kev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(max(1, min(args.steps, 5)))]
+    for x, y in kev:
+        x.record()
+        be.float_quantize_nearest_mm(a, b, c_rows, rows, S, S, FMT["man_add"], FMT["exp_add"], FMT["man_mul"],
+                                     FMT["exp_mul"], True, False, False, order=args.order)
+        y.record()
+    barrier()
     kern_ms = statistics.mean(x.elapsed_time(y) for x, y in kev)
     clocks = sampler.stop() if rank == 0 else None
+    del c_rows
     t = torch.tensor([total_ms, kern_ms], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -420,19 +641,21 @@ def main() -> int:
     ms_per_step = total_ms / args.steps
     macs = float(S) ** 3
 
-    # ---- end to end through the public API with host buffers (H2D of A shard and B, D2H of the C shard)
-    from mptorch_b200.quant import float_mm_streamed
-
+    # ---- end to end through the public API with host buffers: each rank's A rows and its 1/world slice of B travel host ->
+    # device (the ranks assemble B with one all-gather over NVLink), the rank's C rows travel back
     ah = torch.empty(rows, S).pin_memory(); ah.copy_(a)
     bh = torch.empty(S, S).pin_memory(); bh.copy_(b)
     ch = torch.empty(rows, S).pin_memory()
     e2e_steps = max(1, min(args.steps, 3))
+    kw = dict(man_add=2, exp_add=5, man_mul=2, exp_mul=5, rounding="nearest", fma=False, subnormals=True, saturate=False)
 
     def e2e_step():
-        # host operands in, host result out: B once, A and C in row blocks whose copies overlap the kernel
-        # (each rank returns its row shard of C to host memory; no all-gather is needed for that)
-        float_mm_streamed(ah, bh, out=ch, device=dev, block_rows=1024, man_add=2, exp_add=5, man_mul=2, exp_mul=5,
-                          rounding="nearest", fma=False, subnormals=True, saturate=False)
+        if args.no_overlap and world > 1:
+            from mptorch_b200.quant import float_mm_streamed
+
+            float_mm_streamed(ah, bh, out=ch, device=dev, block_rows=1024, **kw)      # every rank copies all of B
+        else:
+            sharded_float_mm_streamed(ah, bh, S, out=ch, device=dev, block_rows=1024, **kw)
 
     e2e_step()
     barrier()
@@ -446,12 +669,29 @@ def main() -> int:
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_ms = t.item() / e2e_steps
+    b_h2d_rows = S if (args.no_overlap or world == 1) else S // world
+    del ah, bh, ch, a, b, c_full
+    torch.cuda.empty_cache()
+
+    extras = not args.no_extras
+    ref = _ref_cuda() if (rank == 0 and not args.no_cpu_baseline) else None
+
+    def clock(fn, reps):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize(dev)
+        q0, q1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        q0.record()
+        for _ in range(reps):
+            fn()
+        q1.record()
+        torch.cuda.synchronize(dev)
+        return q0.elapsed_time(q1) / reps
 
     # ---- elementwise quantizers, HBM bound: 2^28 elements of the benchmark config 2 mixture
     # (90% N(0,1), 5% N(0,1e-6), 5% U(-1e5,1e5)); e4m3 with subnormals and saturation; binary8 P=3
     quant, quant_all = None, {}
     if rank == 0:
-        del ah, bh
         n = 1 << args.quant_log2n
         u = torch.rand(n, device=dev, generator=g)
         x = torch.randn(n, device=dev, generator=g)
@@ -459,58 +699,69 @@ def main() -> int:
         del u
         rnd = torch.randint_like(x, 2147483647, dtype=torch.int32)
         legs = {
-            "nearest": (lambda: be.float_quantize_nearest(x, 3, 4, True, True), 8),
-            "truncate": (lambda: be.float_quantize_truncate(x, 3, 4, True, True), 8),
-            "stochastic_given_words": (lambda: be.float_quantize_stochastic(x, 3, 4, 20, True, True, rand=rnd), 12),
-            "stochastic_philox": (lambda: be.float_quantize_stochastic(x, 3, 4, 20, True, True, seed=1), 8),
-            "binary8_p3_nearest": (lambda: be.binary8_quantize_nearest(x, 3, True, 1, True), 8),
+            "nearest": (lambda: be.float_quantize_nearest(x, 3, 4, True, True), 8,
+                        (lambda: ref.float_quantize_nearest(x, 3, 4, True, True)) if ref is not None else None),
+            "truncate": (lambda: be.float_quantize_truncate(x, 3, 4, True, True), 8, None),
+            "stochastic_given_words": (lambda: be.float_quantize_stochastic(x, 3, 4, 20, True, True, rand=rnd), 12,
+                                       (lambda: ref.float_quantize_stochastic(x, 3, 4, 20, True, True)) if ref is not None else None),
+            "stochastic_philox": (lambda: be.float_quantize_stochastic(x, 3, 4, 20, True, True, seed=1), 8, None),
+            "binary8_p3_nearest": (lambda: be.binary8_quantize_nearest(x, 3, True, 1, True), 8,
+                                   (lambda: ref.binary8_quantize_nearest(x, 3, True, ref.OverflowPolicy.SATURATE_MAXFLOAT, True)) if ref is not None else None),
         }
-        for name, (fn, bytes_per) in legs.items():
-            for _ in range(3):
-                fn()
-            torch.cuda.synchronize(dev)
-            q0, q1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            reps = 10
-            q0.record()
-            for _ in range(reps):
-                fn()
-            q1.record()
-            torch.cuda.synchronize(dev)
-            qms = q0.elapsed_time(q1) / reps
+        for name, (fn, bytes_per, ref_fn) in legs.items():
+            qms = clock(fn, 10)
             quant_all[name] = {"gbs": bytes_per * n / qms / 1e6, "ms": qms, "bytes_per_element": bytes_per}
+            if ref_fn is not None:
+                try:
+                    # the reference call includes what it always does around its kernel (zeros_like, its own random words)
+                    quant_all[name]["reference_cuda_ms"] = clock(ref_fn, 5)
+                except Exception as ex:
+                    quant_all[name]["reference_cuda_error"] = repr(ex)[:120]
         quant = quant_all["nearest"]
         del x, rnd
+        torch.cuda.empty_cache()
 
     # ---- same-GPU baseline: the reference's own CUDA kernel (unmodified sources built for sm_100a into oracle/_ref),
     # same formats and accumulation order, at 2048^3 (its 8x8-thread blocks are slow; the rate is size independent)
     ref_gpu = None
-    if rank == 0 and not args.no_cpu_baseline:
+    if ref is not None:
         try:
-            from oracle.build_ref import load_ref
-
-            rc = load_ref("quant_cuda")
-            if rc is not None:
-                R = 2048
-                ra = torch.randn(R, R, device=dev, generator=g)
-                rb = torch.randn(R, R, device=dev, generator=g)
-                rcout = torch.zeros(R, R, device=dev)
-                rc.float_quantize_nearest_mm(ra, rb, rcout, R, R, R, 2, 5, 2, 5, True, False, False)
-                torch.cuda.synchronize(dev)
-                r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                r0.record()
-                for _ in range(3):
-                    rc.float_quantize_nearest_mm(ra, rb, rcout, R, R, R, 2, 5, 2, 5, True, False, False)
-                r1.record()
-                torch.cuda.synchronize(dev)
-                rms = r0.elapsed_time(r1) / 3
-                ours = torch.empty(R, R, device=dev)
-                be.float_quantize_nearest_mm(ra, rb, ours, R, R, R, 2, 5, 2, 5, True, False, False, order="cuda")
-                ref_gpu = {"value": float(R) ** 3 / rms / 1e6, "unit": "GMAC/s", "size": R, "ms": rms,
-                           "kernel": "reference quant_cuda mm_impl (float_quantize_nearest_mm), same GPU",
-                           "bit_identical_to_ours": bool(torch.equal(ours.view(torch.int32), rcout.view(torch.int32)))}
-                del ra, rb, rcout, ours
+            R = 2048
+            ra = torch.randn(R, R, device=dev, generator=g)
+            rb = torch.randn(R, R, device=dev, generator=g)
+            rcout = torch.zeros(R, R, device=dev)
+            rms = clock(lambda: ref.float_quantize_nearest_mm(ra, rb, rcout, R, R, R, 2, 5, 2, 5, True, False, False), 3)
+            ours = torch.empty(R, R, device=dev)
+            be.float_quantize_nearest_mm(ra, rb, ours, R, R, R, 2, 5, 2, 5, True, False, False, order="cuda")
+            ref_gpu = {"value": float(R) ** 3 / rms / 1e6, "unit": "GMAC/s", "size": R, "ms": rms,
+                       "kernel": "reference quant_cuda mm_impl (float_quantize_nearest_mm), same GPU",
+                       "bit_identical_to_ours": bool(torch.equal(ours.view(torch.int32), rcout.view(torch.int32)))}
+            del ra, rb, rcout, ours
         except Exception as ex:
             ref_gpu = {"value": None, "error": repr(ex)[:200]}
+
+    # ---- the other benchmark configurations, so that one driver-run line carries them: config 3 and the reductions
+    # (HBM-bound kernels), config 4 (the GEMM sweep with its variants), config 5 (the training step, every N)
+    kernels = sweep = None
+    if extras and rank == 0 and world == 1:
+        try:
+            kernels = kernels_legs(dev, 10, 3, 1.0, with_reference=ref is not None)
+        except Exception as ex:
+            kernels = {"error": repr(ex)[:300]}
+        torch.cuda.empty_cache()
+        try:
+            sweep = c4_sweep(dev)
+        except Exception as ex:
+            sweep = {"error": repr(ex)[:300]}
+        torch.cuda.empty_cache()
+    block = None
+    if extras:
+        try:
+            block = block_step(dev, world, rank, 3, 3, overlap=not args.no_overlap)
+        except Exception as ex:
+            block = {"error": repr(ex)[:300]}
+            if world > 1:
+                raise
 
     if rank == 0:
         peaks = {}
@@ -521,38 +772,51 @@ def main() -> int:
         hbm_peak, peak_src = (peaks["hbm_gbs"], "measured") if "hbm_gbs" in peaks else (6650.0, "fallback")
         sms = torch.cuda.get_device_properties(dev).multi_processor_count
         clk = (clocks or {}).get("sm_mhz") or peaks.get("sm_max_mhz") or 1965.0
-        issue_peak = sms * 128 * clk * 1e6 / I_MAC / 1e9          # GMAC/s per GPU at the sampled clock
+        cnt = load_counters()
+        i_mac, alu_mac = cnt["inst_per_mac"], cnt["alu_inst_per_mac"]
+        slots_mac = 2 * cnt["packed_fp_inst_per_mac"] + alu_mac
+        issue_peak = sms * 128 * clk * 1e6 / i_mac / 1e9          # GMAC/s per GPU at the sampled clock
         achieved = macs / world / kern_ms / 1e6                   # GMAC/s of one GPU's kernel
         line = {
             "metric": METRIC, "value": macs / ms_per_step / 1e6, "unit": "GMAC/s", "n_gpus": world,
             "steps": args.steps, "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None,
             "dtype": "f32 (each multiply and add rounded to e5m2)", "data": "synthetic",
-            "config": {"workload": "float_mm %dx%dx%d, mul e5m2 / add e5m2, nearest, subnormals, no saturate, "
-                                   "M rows sharded over %d GPU(s)%s" % (S, S, S, world, ", all-gather of C" if world > 1 else ""),
-                       "accum_order": args.order, "l2": "inputs (512 MiB) exceed L2, no flush"},
+            "config": config_for(S), "accum_order": args.order,
+            "notes": "M rows sharded over %d GPU(s)%s" % (world, (", C all-gathered in %d row panels per rank under the next panel's kernel" % panels) if world > 1 else ""),
             "clocks": clocks,
-            "e2e": {"value": macs / e2e_ms / 1e6, "unit": "GMAC/s", "h2d_bytes_per_step": 4 * (rows * S + S * S),
-                    "d2h_bytes_per_step": 4 * rows * S, "ms_per_step": e2e_ms},
-            "gpu_launches": 4 * args.steps,
+            "e2e": {"value": macs / e2e_ms / 1e6, "unit": "GMAC/s", "h2d_bytes_per_step": 4 * (rows * S + b_h2d_rows * S),
+                    "d2h_bytes_per_step": 4 * rows * S, "ms_per_step": e2e_ms,
+                    "b_operand": "each rank copies 1/%d of B from host memory; one NCCL all-gather assembles it" % world if b_h2d_rows != S else "whole B copied from host memory"},
+            "gpu_launches": launches_timed,
             "roofline": {"bound": "issue", "achieved": achieved, "peak": issue_peak, "unit": "GMAC/s",
                          "frac": achieved / issue_peak,
-                         "traffic": MM_TRAFFIC_8192 if (S == 8192 and world == 1) else None,
+                         "traffic": cnt.get("dram_bytes_per_launch_8192cubed") if (S == 8192 and world == 1) else None,
+                         "traffic_source": "ncu capture recorded in profiles/mm_kernel_counters.json",
                          "algorithmic_bytes": 3 * 4 * S * S // world + (world - 1) * 4 * S * S // world,
-                         "alu_pipe_peak": sms * 64 * clk * 1e6 / ALU_MAC / 1e9,
-                         "datapath_peak": sms * 128 * clk * 1e6 / SLOTS_MAC / 1e9,
-                         "datapath_frac": achieved / (sms * 128 * clk * 1e6 / SLOTS_MAC / 1e9),
+                         "alu_pipe_peak": sms * 64 * clk * 1e6 / alu_mac / 1e9,
+                         "datapath_peak": sms * 128 * clk * 1e6 / slots_mac / 1e9,
+                         "datapath_frac": achieved / (sms * 128 * clk * 1e6 / slots_mac / 1e9),
+                         "constants_stale": cnt["constants_stale"], "constants_from": cnt.get("captured_at"),
                          "note": "CUDA-core issue roofline: %d SMs x 128 lanes x %.0f MHz / %.2f instructions per MAC; "
-                                 "alu_pipe_peak = %d SMs x 64 ALU lanes x clock / %.1f ALU instructions per MAC; "
+                                 "alu_pipe_peak = %d SMs x 64 ALU lanes x clock / %.2f ALU instructions per MAC; "
                                  "datapath_peak = SMs x 128 fp32/int32 lane slots x clock / %.2f slots per MAC "
-                                 "(a packed fp32x2 instruction takes two)" % (sms, clk, I_MAC, sms, ALU_MAC, SLOTS_MAC)},
+                                 "(a packed fp32x2 instruction takes two)" % (sms, clk, i_mac, sms, alu_mac, slots_mac)},
             "roofline_quantize": {"bound": "hbm", "achieved": quant["gbs"], "peak": hbm_peak, "unit": "GB/s",
                                   "frac": quant["gbs"] / hbm_peak, "traffic": None, "peak_source": peak_src,
                                   "kernel": "float_quantize_nearest e4m3, 2^%d elements, 8 B/element" % args.quant_log2n,
-                                  "all_kernels_gbs": {k: round(v["gbs"], 1) for k, v in quant_all.items()}},
+                                  "all_kernels_gbs": {k: round(v["gbs"], 1) for k, v in quant_all.items()},
+                                  "reference_cuda_ms": {k: round(v["reference_cuda_ms"], 4) for k, v in quant_all.items() if "reference_cuda_ms" in v},
+                                  "ms": {k: round(v["ms"], 4) for k, v in quant_all.items()}},
         }
         if ref_gpu is not None:
             line["reference_cuda_same_gpu"] = ref_gpu
+        if kernels is not None:
+            line["roofline_kernels"] = kernels
+        if sweep is not None:
+            line["c4_sweep"] = sweep
+        if block is not None:
+            line["block_step"] = block
         if world == 1 and not args.no_cpu_baseline:
             try:
                 cb = cpu_baseline(1)

@@ -135,7 +135,9 @@ MPT_API int mpt_float_mm_nearest(const float *a, const float *b, float *c, int64
  * bounds the batch count: batch > 4096 is rejected with MPT_ERR_INVALID_ARGUMENT.  The call allocates
  * and frees nothing.
  *   - The first call on each device looks up the array's device address (with that device current);
- *     make that first call outside any stream capture.
+ *     make that first call outside any stream capture.  The address is cached per device ordinal and
+ *     stays valid for the lifetime of the device's primary context: after a cudaDeviceReset (or any
+ *     other teardown of that context) the library must be reloaded before this entry point is used again.
  *   - All calls share the array and each one rewrites the part it uses, so calls that may overlap on
  *     the GPU (different streams, or different host threads without ordering) race; serialise them or
  *     use mpt_float_mm_nearest with one workspace per stream. */
@@ -166,13 +168,17 @@ MPT_API int mpt_float_mm_nearest_fma(const float *a, const float *b, float *c, i
 /* replaces float_quantize_stochastic_mm / _bmm / _mm_fma / _bmm_fma (pybind_cuda.cpp:254-300 ->
  * fp_kernel.cu:309-415 -> mm_kernel.h:248-455).  Single accumulator over the zero-padded K range.
  * The reference draws from a per-block cuRAND state seeded by the clock and is not reproducible;
- * here the random words come from Philox4x32-10 keyed by `seed` with counter (k, output index), so
- * results are a pure function of the inputs and the seed.  fma != 0 uses (man_add, exp_add,
- * rbits_add) as the FMA format. */
+ * here the random words come from Philox4x32-10 keyed by `seed`, so results are a pure function of
+ * the inputs and the seed.  Accumulation step k of the output with linear index `lin` in C uses
+ * counter (k / 2, lin) and words 2 (k % 2) for the sum and 2 (k % 2) + 1 for the product; the fused
+ * form (fma != 0, format (man_add, exp_add, rbits_add)) uses counter (k / 4, lin) and word k % 4.
+ * workspace (mpt_mm_workspace_bytes(batch) bytes, 16-byte aligned) enables the range-checked fast
+ * path as for mpt_float_mm_nearest; NULL runs the whole-domain casters.  Same bits either way. */
 MPT_API int mpt_float_mm_stochastic(const float *a, const float *b, float *c, int64_t batch, int M, int N, int K,
                                     int man_add, int exp_add, int rbits_add,
                                     int man_mul, int exp_mul, int rbits_mul,
-                                    int subnormals, int saturate, int fma, uint64_t seed, void *stream);
+                                    int subnormals, int saturate, int fma, uint64_t seed,
+                                    void *workspace, size_t workspace_bytes, void *stream);
 
 /* ---- quantized row reductions ------------------------------------------------------------------
  * The tensor is viewed as [outer, channel, inner] (the reference's partition_tensor,

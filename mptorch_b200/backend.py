@@ -253,8 +253,9 @@ def _mm_sr(a, b, c, batch, M, N, K, man_add, exp_add, rbits_add, man_mul, exp_mu
         # one draw from the torch generator keeps runs reproducible under torch.manual_seed
         seed = int(torch.randint(0, 2**62, (1,), dtype=torch.int64).item())
     with torch.cuda.device(a.device):
+        ws = _cabi.mm_workspace(a.device, batch)
         call("mpt_float_mm_stochastic", ptr(a), ptr(b), ptr(c), batch, M, N, K, man_add, exp_add, rbits_add, man_mul,
-             exp_mul, rbits_mul, int(subnormals), int(saturate), int(fma), int(seed) & (2**64 - 1),
+             exp_mul, rbits_mul, int(subnormals), int(saturate), int(fma), int(seed) & (2**64 - 1), ptr(ws), ws.numel(),
              stream_ptr(a.device))
 
 

@@ -1,5 +1,7 @@
 // C entry points of the per-MAC rounded GEMM and of the implicit-GEMM convolution: argument checks, operand
 // statistics, problem set-up.  The kernel lives in gemm_kernel.cuh, its instantiations in gemm_*.cu.
+#include <cmath>
+
 #include "gemm_kernel.cuh"
 
 namespace mpt {
@@ -9,6 +11,38 @@ double growth8_bound(int man) {
     double g = 1.0, f = 1.0 + ldexp(1.0, -(man + 1));
     for (int i = 0; i < 8; ++i) g *= f;
     return g * 1.0001;
+}
+
+// Bounds for the Kahan fast path.  One step maps the magnitudes S = |sum|, C = |comp| and the product bound P to
+//     Y  <= g (P + C) + d            y = Q(update - comp)
+//     T  <= g (S + Y) + d            t = Q(sum + y),  |t - (sum + y)| <= E = u (S + Y) + d
+//     C1 <= g (Y + E) + d            c1 = Q(t - sum), t - sum = y + e with |e| <= E (the fp32 subtraction adds 2^-24)
+//     C' <= g (E + u (Y + E) + d) + d
+// with u = 2^-(man+1) the relative rounding error of the add format, g = 1 + u, and d = 2^min_exp covering the absolute
+// error of roundings that land in the subnormal range.  Every bound is linear with non-negative coefficients in
+// (S, C, P, d), so the largest intermediate of eight steps is at most sc * max(S, C) + cp * P + cd * d, where each
+// coefficient is the largest one seen for its variable; the kernel keeps a group on the fast path while that stays
+// below the add format's fast-rounding limit.
+struct KahanBounds { double sc, p, d; };
+KahanBounds kahan_bounds(int man) {
+    const double u = ldexp(1.0, -(man + 1)), g = (1.0 + u) * (1.0 + ldexp(1.0, -23));
+    // vectors of coefficients over (S0, C0, P, d)
+    struct V { double v[4]; };
+    auto add = [](V a, V b) { V r; for (int i = 0; i < 4; ++i) r.v[i] = a.v[i] + b.v[i]; return r; };
+    auto mul = [](V a, double k) { V r; for (int i = 0; i < 4; ++i) r.v[i] = a.v[i] * k; return r; };
+    V S{{1, 0, 0, 0}}, C{{0, 1, 0, 0}}, P{{0, 0, 1, 0}}, D{{0, 0, 0, 1}}, top{{0, 0, 0, 0}};
+    auto see = [&](V x) { for (int i = 0; i < 4; ++i) top.v[i] = x.v[i] > top.v[i] ? x.v[i] : top.v[i]; };
+    see(S); see(C);
+    for (int step = 0; step < 8; ++step) {
+        V Y = add(mul(add(P, C), g), D);
+        V T = add(mul(add(S, Y), g), D);
+        V E = add(mul(add(S, Y), u), D);
+        V C1 = add(mul(add(Y, E), g), D);
+        V Cn = add(mul(add(add(E, mul(add(Y, E), u)), D), g), D);
+        see(Y); see(T); see(C1); see(Cn);
+        S = T; C = Cn;
+    }
+    return KahanBounds{(top.v[0] + top.v[1]) * 1.001, top.v[2] * 1.001, top.v[3] * 1.001};
 }
 
 int run_mm(const float* a, const float* b, float* c, int64_t batch, int M, int N, int K, const AnyFmt& gadd, const AnyFmt& gmul,
@@ -32,14 +66,19 @@ int run_mm(const float* a, const float* b, float* c, int64_t batch, int M, int N
     p.rbits_add = rbits_add; p.rbits_mul = rbits_mul;
     p.seed_lo = (uint32_t)seed; p.seed_hi = (uint32_t)(seed >> 32);
     p.growth8 = (float)growth8_bound(fadd.man);
+    {
+        const KahanBounds kb = kahan_bounds(fadd.man);
+        p.kah_sc = (float)kb.sc; p.kah_p = (float)kb.p; p.kah_const = (float)(kb.d * ldexp(1.0, fadd.min_exp));
+        p.growth8_sr = (float)(pow(1.0 + ldexp(1.0, -fadd.man), 8.0) * 1.0001);
+    }
     p.stats = nullptr;
     p.whole_ok = all_float && fast_rn_supported(fadd) && (fma || fast_rn_supported(fmul));
     p.wadd = FullRn::make(fadd); p.wmul = FullRn::make(fma ? fadd : fmul);
     p.sr_ok = all_float && FullSr::supported(fadd) && (fma || FullSr::supported(fmul));
     p.sadd = FullSr::make(fadd, rbits_add); p.smul = FullSr::make(fma ? fadd : fmul, fma ? rbits_add : rbits_mul);
 
-    const bool fast_candidate = all_float && (algo == ALGO_SEQ || algo == ALGO_TILE8) && fast_rn_supported(fadd) &&
-                                (fma || fast_rn_supported(fmul)) && workspace != nullptr &&
+    const bool fmt_fast = algo == ALGO_SR ? p.sr_ok != 0 : (fast_rn_supported(fadd) && (fma || fast_rn_supported(fmul)));
+    const bool fast_candidate = all_float && fmt_fast && workspace != nullptr &&
                                 workspace_bytes >= sizeof(MmStats) * (size_t)batch &&
                                 (reinterpret_cast<uintptr_t>(workspace) & 15u) == 0 && K > 0;
     if (fast_candidate) {
@@ -87,6 +126,7 @@ int run_conv(const float* x, const float* wt, float* y, int n_img, int c_in, int
     p.growth8 = (float)growth8_bound(fadd.man);
     p.stats = nullptr;
     p.whole_ok = 0; p.sr_ok = 0;
+    p.kah_sc = p.kah_p = p.kah_const = 0.0f; p.growth8_sr = 1.0f;
     p.wadd = p.wmul = FullRn::make(fadd);
     p.sadd = p.smul = FullSr::make(fadd, 0);
     const bool fast_candidate = fast_rn_supported(fadd) && (fma || fast_rn_supported(fmul)) && workspace != nullptr &&
@@ -122,7 +162,7 @@ int run_conv(const float* x, const float* wt, float* y, int n_img, int c_in, int
 int check_mm_args(const char* who, const float* a, const float* b, float* c, int64_t batch, int M, int N, int K) {
     MPT_REQUIRE(batch >= 0 && M >= 0 && N >= 0 && K >= 0, "%s: negative dimension", who);
     MPT_REQUIRE(batch <= 65535, "%s: batch %lld exceeds 65535", who, (long long)batch);
-    MPT_REQUIRE((int64_t)(M + BM - 1) / BM <= 65535, "%s: M=%d too large", who, M);
+    MPT_REQUIRE(((int64_t)M + BM - 1) / BM <= 65535, "%s: M=%d too large", who, M);
     const bool empty = batch == 0 || M == 0 || N == 0;
     MPT_REQUIRE(empty || (c && (K == 0 || (a && b))), "%s: null pointer", who);
     return MPT_OK;
@@ -252,13 +292,14 @@ int mpt_float_mm_nearest_fma(const float* a, const float* b, float* c, int64_t b
 
 int mpt_float_mm_stochastic(const float* a, const float* b, float* c, int64_t batch, int M, int N, int K, int man_add,
                             int exp_add, int rbits_add, int man_mul, int exp_mul, int rbits_mul, int subnormals,
-                            int saturate, int fma, uint64_t seed, void* stream) {
+                            int saturate, int fma, uint64_t seed, void* workspace, size_t workspace_bytes, void* stream) {
     int rc = check_mm_args("float_mm_stochastic", a, b, c, batch, M, N, K);
     if (rc) return rc;
     MPT_REQUIRE(valid_format(man_add, exp_add) && (fma || valid_format(man_mul, exp_mul)), "float_mm_stochastic: unsupported format");
     const AnyFmt fa = any_float(make_fmt(man_add, exp_add, subnormals, saturate));
     const AnyFmt fm = fma ? fa : any_float(make_fmt(man_mul, exp_mul, subnormals, saturate));
-    return run_mm(a, b, c, batch, M, N, K, fa, fm, rbits_add, rbits_mul, fma != 0, ALGO_SR, seed, nullptr, 0, as_stream(stream));
+    return run_mm(a, b, c, batch, M, N, K, fa, fm, rbits_add, rbits_mul, fma != 0, ALGO_SR, seed, workspace, workspace_bytes,
+                  as_stream(stream));
 }
 
 }

@@ -91,6 +91,11 @@ struct MmParams {
     int whole_ok;
     FullSr sadd, smul;
     int sr_ok;
+    // Kahan fast path: with |sum|, |comp| <= L and |a*b| <= P at the start of an 8-step group, every intermediate of
+    // the group stays below kah_sc * L + kah_p * P + kah_const (coefficients worked out on the host from the add
+    // format's rounding error, see kahan_bounds in gemm.cu)
+    float kah_sc, kah_p, kah_const;
+    float growth8_sr;            // upper bound of (1 + 2^-man_add)^8: eight stochastic roundings of a sum
 };
 
 // Nearest rounding to the add / multiply format on the whole input domain.  The exact caster is an out-of-line call
@@ -326,6 +331,157 @@ __device__ __forceinline__ void group_steps(float (&acc)[TM][TN], const float* A
     }
 }
 
+// ---- Kahan-compensated accumulation (reference quant_cuda/mm_kernel.h:487-497, fma variant :600-608) --------------
+//     update = Qmul(a*b);  y = Qadd(update - comp);  t = Qadd(sum + y);  comp = Qadd(Qadd(t - sum) - y);  sum = t
+// One step on the exact casters.
+template <bool FMA>
+__device__ __forceinline__ void kahan_exact(float& sum, float& comp, float a, float b, const MmParams& p) {
+    const float y = FMA ? round_add(p, fma_rn(a, b, -comp)) : round_add(p, add_rn(round_mul(p, mul_rn(a, b)), -comp));
+    const float t = round_add(p, add_rn(sum, y));
+    comp = round_add(p, add_rn(round_add(p, add_rn(t, -sum)), -y));
+    sum = t;
+}
+// Two neighbouring outputs at once on the packed fp32x2 instructions, five 4-instruction roundings per step.  The state
+// carried through a group is the NEGATED compensation term nc = -comp, so that every subtraction is an FADD2 or an FFMA2
+// with the constant -1 (t - sum = fma(sum, -1, t), one rounding, like the subtraction itself) and no separate negations
+// are issued; rounding to nearest is symmetric, so Q(y - c1) = -Q(c1 - y).
+template <bool FMA, bool ADDG>
+__device__ __forceinline__ void kahan_fast2(float2& sum, float2& nc, float2 a2, float2 b2, const FastRn& radd, const FastRn& rmul) {
+    const float2 m1 = make_float2(-1.0f, -1.0f);
+    const float2 y = FMA ? fast_rn2<true>(radd, __ffma2_rn(a2, b2, nc))
+                         : fast_rn2<ADDG>(radd, __fadd2_rn(fast_rn2<true>(rmul, __fmul2_rn(a2, b2)), nc));
+    const float2 t = fast_rn2<ADDG || FMA>(radd, __fadd2_rn(sum, y));
+    const float2 c1 = fast_rn2<ADDG || FMA>(radd, __ffma2_rn(sum, m1, t));
+    nc = fast_rn2<ADDG || FMA>(radd, __ffma2_rn(c1, m1, y));
+    sum = t;
+}
+// Eight accumulation steps starting at slab row kbase; acc = running sums, aux = compensation terms.
+template <bool FMA, bool ADDG>
+__device__ __forceinline__ void kahan_group_fast(float (&acc)[TM][TN], float (&aux)[TM][TN], const float* As, const float* Bs,
+                                                 int kbase, int ty, int tx, const MmParams& p) {
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) aux[i][j] = add_rn(0.0f, -aux[i][j]);      // nc = -comp (+0 for a zero term)
+#pragma unroll 1
+    for (int h = 0; h < 2; ++h) {
+        float4 av[TM];
+#pragma unroll
+        for (int i = 0; i < TM; ++i) av[i] = *reinterpret_cast<const float4*>(As + (ty + 16 * i) * AS_LD + kbase + 4 * h);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float4 bv = *reinterpret_cast<const float4*>(Bs + (kbase + 4 * h + j) * BN + tx * 4);
+#pragma unroll
+            for (int i = 0; i < TM; ++i) {
+                const float a = j == 0 ? av[i].x : j == 1 ? av[i].y : j == 2 ? av[i].z : av[i].w;
+                const float2 a2 = make_float2(a, a);
+                float2 s0 = make_float2(acc[i][0], acc[i][1]), c0 = make_float2(aux[i][0], aux[i][1]);
+                float2 s1 = make_float2(acc[i][2], acc[i][3]), c1 = make_float2(aux[i][2], aux[i][3]);
+                kahan_fast2<FMA, ADDG>(s0, c0, a2, make_float2(bv.x, bv.y), p.radd, p.rmul);
+                kahan_fast2<FMA, ADDG>(s1, c1, a2, make_float2(bv.z, bv.w), p.radd, p.rmul);
+                acc[i][0] = s0.x; acc[i][1] = s0.y; acc[i][2] = s1.x; acc[i][3] = s1.y;
+                aux[i][0] = c0.x; aux[i][1] = c0.y; aux[i][2] = c1.x; aux[i][3] = c1.y;
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) aux[i][j] = add_rn(0.0f, -aux[i][j]);
+}
+
+// ---- stochastic rounding -------------------------------------------------------------------------------------------
+// Random words of accumulation step k of output `lin` (its linear index in C): Philox4x32-10 with the seed as key and
+// the counter (k / 2, lin) for the two-rounding MAC (words 0,1 serve the even step's sum and product, words 2,3 the odd
+// step's), (k / 4, lin) for the fused MAC (word k % 4), so that every generated word is used.
+// Stochastic rounding of a finite value that cannot reach the format's overflow threshold (the caller has shown so):
+// FullSr without its NaN branch and overflow select.
+__device__ __forceinline__ float sr_inrange(const FullSr& f, float x, uint32_t rnd) {
+    // values below the smallest normal are lifted into its binade, rounded there and brought back; for all others the
+    // lift is zero and both additions leave the value as it is (a zero input counts as small, so -0 never meets + 0)
+    const float lift = fabsf(x) < __uint_as_float(f.min_norm) ? copysignf(__uint_as_float(f.min_norm), x) : 0.0f;
+    const uint32_t v = __float_as_uint(add_rn(x, lift));
+    const uint32_t q = (v + (rnd & f.rmask)) & f.keep;
+    return add_rn(__uint_as_float(q), -lift);
+}
+// One accumulation step; FAST: the caller has shown that nothing can leave the formats' ranges.
+template <bool FMA, bool FAST>
+__device__ __forceinline__ float sr_mac(float acc, float a, float b, uint32_t radd_word, uint32_t rmul_word, const MmParams& p) {
+    if (FAST) {
+        if (FMA) return sr_inrange(p.sadd, fma_rn(a, b, acc), radd_word);
+        return sr_inrange(p.sadd, add_rn(acc, sr_inrange(p.smul, mul_rn(a, b), rmul_word)), radd_word);
+    }
+    if (FMA) return sr_add(p, fma_rn(a, b, acc), radd_word);
+    return sr_add(p, add_rn(acc, sr_mul(p, mul_rn(a, b), rmul_word)), radd_word);
+}
+// Eight steps (kglob .. kglob + 7, kglob a multiple of 8) for the thread's outputs on the fast path, one Philox call per
+// output and PER steps.  The loop over the Philox calls stays rolled (the body, unrolled over the 32 outputs, is large).
+template <bool FMA>
+__device__ __forceinline__ void sr_group_fast(float (&acc)[TM][TN], const float* As, const float* Bs, int kbase, uint32_t kglob,
+                                              int ty, int tx, int m0, int n0, int64_t batch, const MmParams& p) {
+    constexpr int PER = FMA ? 4 : 2;          // accumulation steps served by one Philox call
+    const uint64_t lin0 = (uint64_t)batch * p.M * p.N + (uint64_t)(m0 + ty) * p.N + (n0 + tx * 4);
+#pragma unroll 1
+    for (int c = 0; c < 8 / PER; ++c) {
+        const int k0 = kbase + c * PER;
+        float bv[PER][4];
+#pragma unroll
+        for (int u = 0; u < PER; ++u) {
+            const float4 b4 = *reinterpret_cast<const float4*>(Bs + (k0 + u) * BN + tx * 4);
+            bv[u][0] = b4.x; bv[u][1] = b4.y; bv[u][2] = b4.z; bv[u][3] = b4.w;
+        }
+#pragma unroll
+        for (int i = 0; i < TM; ++i) {
+            float av[PER];
+            if (FMA) {
+                const float4 a4 = *reinterpret_cast<const float4*>(As + (ty + 16 * i) * AS_LD + k0);
+                av[0] = a4.x; av[1] = a4.y; av[PER - 2] = a4.z; av[PER - 1] = a4.w;
+            } else {
+                const float2 a2 = *reinterpret_cast<const float2*>(As + (ty + 16 * i) * AS_LD + k0);
+                av[0] = a2.x; av[1] = a2.y;
+            }
+#pragma unroll
+            for (int j = 0; j < TN; ++j) {
+                const uint64_t lin = lin0 + (uint64_t)(16 * i) * p.N + j;
+                Philox ph(kglob / PER + c, (uint32_t)lin, (uint32_t)(lin >> 32), 0u);
+                ph.run(p.seed_lo, p.seed_hi);
+                float v = acc[i][j];
+#pragma unroll
+                for (int u = 0; u < PER; ++u)
+                    v = FMA ? sr_mac<true, true>(v, av[u], bv[u][j], ph.c[u], 0u, p)
+                            : sr_mac<false, true>(v, av[u], bv[u][j], ph.c[2 * u], ph.c[2 * u + 1], p);
+                acc[i][j] = v;
+            }
+        }
+    }
+}
+// The same eight steps on the whole-domain casters: an out-of-line function over a copy of the accumulators in local
+// memory, with every loop rolled, so that this rarely taken path costs the fast one neither registers nor code size.
+template <bool FMA>
+static __device__ __noinline__ void sr_group_exact(float* accv, const float* As, const float* Bs, int kbase, uint32_t kglob,
+                                                   int ty, int tx, int m0, int n0, int64_t batch, const MmParams* pp) {
+    const MmParams& p = *pp;
+    constexpr int PER = FMA ? 4 : 2;
+#pragma unroll 1
+    for (int o = 0; o < TM * TN; ++o) {
+        const int i = o / TN, j = o % TN;
+        const uint64_t lin = (uint64_t)batch * p.M * p.N + (uint64_t)(m0 + ty + 16 * i) * p.N + (n0 + tx * 4 + j);
+        float v = accv[o];
+#pragma unroll 1
+        for (int c = 0; c < 8 / PER; ++c) {
+            Philox ph(kglob / PER + c, (uint32_t)lin, (uint32_t)(lin >> 32), 0u);
+            ph.run(p.seed_lo, p.seed_hi);
+#pragma unroll
+            for (int u = 0; u < PER; ++u) {
+                const int k = kbase + c * PER + u;
+                const float a = As[(ty + 16 * i) * AS_LD + k], b = Bs[k * BN + tx * 4 + j];
+                v = FMA ? sr_mac<true, false>(v, a, b, ph.c[u], 0u, p) : sr_mac<false, false>(v, a, b, ph.c[2 * u], ph.c[2 * u + 1], p);
+            }
+        }
+        accv[o] = v;
+    }
+}
+
 __device__ __forceinline__ float absmax_of(const float (&v)[TM][TN]) {
     float m = 0.0f;
 #pragma unroll
@@ -346,11 +502,23 @@ template <int ALGO, bool FMA>
 __device__ __forceinline__ FastPlan make_plan(const MmParams& p, int64_t batch) {
     FastPlan plan{false, 0.0f};
     if (p.stats == nullptr) return plan;
-    if (!fast_rn_supported(p.fadd) || (!FMA && !fast_rn_supported(p.fmul))) return plan;
     const MmStats s = p.stats[batch];
     if (s.max_a >= 0x7F800000u || s.max_b >= 0x7F800000u) return plan;
     // |a| < 2^(ea+1), |b| < 2^(eb+1)  =>  |a*b| < 2^pe
     const int pe = (int)(s.max_a >> 23) + (int)(s.max_b >> 23) - 254 + 2;
+    if (ALGO == ALGO_SR) {
+        // stochastic rounding moves a value by less than one quantum: a product below 2^pe stays at or below 2^pe, a sum
+        // grows by at most (1 + 2^-man) per step; nothing may reach the upper edge of the top binade (the exponent clip)
+        if (!p.sr_ok) return plan;
+        const int top_add = p.fadd.max_store - 127, top_mul = p.fmul.max_store - 127;
+        if (!FMA && pe > top_mul) return plan;
+        const float lim = ldexpf(1.0f, top_add) / p.growth8_sr - ldexpf(8.0f, pe);
+        if (!(lim > 0.0f)) return plan;
+        plan.ok = true;
+        plan.acc_limit = lim;
+        return plan;
+    }
+    if (!fast_rn_supported(p.fadd) || (!FMA && !fast_rn_supported(p.fmul))) return plan;
     const int lim_add = fast_rn_exp_limit(p.fadd);
     if (!FMA && pe - 1 > fast_rn_exp_limit(p.fmul)) return plan;
     if (p.fadd.exp == 8 || (!FMA && p.fmul.exp == 8)) {
@@ -358,14 +526,21 @@ __device__ __forceinline__ FastPlan make_plan(const MmParams& p, int64_t batch) 
         // stay exact unless every nonzero intermediate is provably far above 2^-126
         if (s.minnz_a < 0x00800000u || s.minnz_b < 0x00800000u) return plan;
         if (s.minnz_a != 0xFFFFFFFFu && s.minnz_b != 0xFFFFFFFFu) {
+            // a rounded product is a multiple of 2^(lo - 23), an exact (fused) one of 2^(lo - 46); sums, differences
+            // and roundings of such multiples are multiples again, so nothing nonzero can fall below that grid
             const int lo = (int)(s.minnz_a >> 23) + (int)(s.minnz_b >> 23) - 254;
-            if (lo - 23 < -120) return plan;
+            if (lo - (FMA ? 46 : 23) < -120) return plan;
         }
     }
     // eight steps from |acc| = x reach at most (x + 8 * 2^pe) * growth8
     const float step8 = ldexpf(8.0f, pe) * p.growth8;
     const float top = ldexpf(1.0f, lim_add + 1);
-    if (ALGO == ALGO_TILE8) {
+    if (ALGO == ALGO_KAHAN) {
+        const float lim = (top - p.kah_p * ldexpf(1.0f, pe) - p.kah_const) / p.kah_sc;
+        if (!(lim > 0.0f)) return plan;
+        plan.ok = true;
+        plan.acc_limit = lim;
+    } else if (ALGO == ALGO_TILE8) {
         // inner sums start from zero: |inner| <= step8; the fold needs |outer| + |inner| < top
         if (!(step8 <= ldexpf(1.0f, lim_add))) return plan;
         plan.ok = true;
@@ -394,13 +569,15 @@ __global__ void __launch_bounds__(THREADS, MPT_MM_MIN_CTAS) mm_kernel(const __gr
     int tile_m, tile_n;
     {
         constexpr int kGroupM = 8;
-        const int pid = blockIdx.y * gridDim.x + blockIdx.x;
-        const int per_band = kGroupM * gridDim.x;
-        const int band = pid / per_band, in_band = pid - band * per_band;
+        // 64-bit: gridDim.x * gridDim.y can pass 2^31 for a very wide N
+        const uint64_t pid = (uint64_t)blockIdx.y * gridDim.x + blockIdx.x;
+        const uint64_t per_band = (uint64_t)kGroupM * gridDim.x;
+        const int band = (int)(pid / per_band);
+        const uint64_t in_band = pid - (uint64_t)band * per_band;
         const int first_m = band * kGroupM;
         const int rows_here = min((int)gridDim.y - first_m, kGroupM);
-        tile_n = in_band / rows_here;
-        tile_m = first_m + (in_band - tile_n * rows_here);
+        tile_n = (int)(in_band / (unsigned)rows_here);
+        tile_m = first_m + (int)(in_band - (uint64_t)tile_n * rows_here);
     }
     const int m0 = tile_m * BM, n0 = tile_n * BN;
     const int64_t batch = blockIdx.z;
@@ -413,7 +590,7 @@ __global__ void __launch_bounds__(THREADS, MPT_MM_MIN_CTAS) mm_kernel(const __gr
     const int ksteps = (ALGO == ALGO_SEQ) ? p.K : p.K + 8 - p.K % 8;
     const int ntiles = (ksteps + BK - 1) / BK;
 
-    const FastPlan plan = (ALGO == ALGO_SEQ || ALGO == ALGO_TILE8) ? make_plan<ALGO, FMA>(p, batch) : FastPlan{false, 0.0f};
+    const FastPlan plan = make_plan<ALGO, FMA>(p, batch);
 
     if (CONV) {
         if (tid < BM) {
@@ -493,46 +670,39 @@ __global__ void __launch_bounds__(THREADS, MPT_MM_MIN_CTAS) mm_kernel(const __gr
                 }
             }
         } else if (ALGO == ALGO_KAHAN) {
+            // the reference pads K to a multiple of 8 (and walks the padding), so a tile is whole groups of 8 steps
+            for (int g = 0; g * 8 < nk_tile; ++g) {
+                if (PACKED && plan.ok && absmax_of(acc) < plan.acc_limit && absmax_of(aux) < plan.acc_limit) {
+                    kahan_group_fast<FMA, ADDG>(acc, aux, as, bs, g * 8, ty, tx, p);
+                } else {
 #pragma unroll 1
-            for (int k = 0; k < nk_tile; ++k) {
-                const float4 bv4 = *reinterpret_cast<const float4*>(bs + k * BN + tx * 4);
-                const float bvv[4] = {bv4.x, bv4.y, bv4.z, bv4.w};
+                    for (int k = g * 8; k < g * 8 + 8; ++k) {
+                        const float4 bv4 = *reinterpret_cast<const float4*>(bs + k * BN + tx * 4);
+                        const float bvv[4] = {bv4.x, bv4.y, bv4.z, bv4.w};
 #pragma unroll
-                for (int i = 0; i < TM; ++i) {
-                    const float a = as[(ty + 16 * i) * AS_LD + k];
+                        for (int i = 0; i < TM; ++i) {
+                            const float a = as[(ty + 16 * i) * AS_LD + k];
 #pragma unroll
-                    for (int j = 0; j < TN; ++j) {
-                        const float sum = acc[i][j], comp = aux[i][j];
-                        const float y = FMA ? round_add(p, fma_rn(a, bvv[j], -comp))
-                                            : round_add(p, add_rn(round_mul(p, mul_rn(a, bvv[j])), -comp));
-                        const float tt = round_add(p, add_rn(sum, y));
-                        aux[i][j] = round_add(p, add_rn(round_add(p, add_rn(tt, -sum)), -y));
-                        acc[i][j] = tt;
+                            for (int j = 0; j < TN; ++j) kahan_exact<FMA>(acc[i][j], aux[i][j], a, bvv[j], p);
+                        }
                     }
                 }
             }
         } else {   // ALGO_SR
-#pragma unroll 1
-            for (int k = 0; k < nk_tile; ++k) {
-                const float4 bv4 = *reinterpret_cast<const float4*>(bs + k * BN + tx * 4);
-                const float bvv[4] = {bv4.x, bv4.y, bv4.z, bv4.w};
-                const uint32_t kglob = (uint32_t)(t * BK + k);
+            for (int g = 0; g * 8 < nk_tile; ++g) {
+                const uint32_t kglob = (uint32_t)(t * BK + g * 8);
+                if (plan.ok && absmax_of(acc) < plan.acc_limit) sr_group_fast<FMA>(acc, as, bs, g * 8, kglob, ty, tx, m0, n0, batch, p);
+                else {
+                    float tmp[TM * TN];
 #pragma unroll
-                for (int i = 0; i < TM; ++i) {
-                    const float a = as[(ty + 16 * i) * AS_LD + k];
-                    const int gm = m0 + ty + 16 * i;
+                    for (int i = 0; i < TM; ++i)
 #pragma unroll
-                    for (int j = 0; j < TN; ++j) {
-                        const int gn = n0 + tx * 4 + j;
-                        const uint64_t lin = (uint64_t)batch * p.M * p.N + (uint64_t)gm * p.N + gn;
-                        Philox ph(kglob, (uint32_t)lin, (uint32_t)(lin >> 32), 0u);
-                        ph.run(p.seed_lo, p.seed_hi);
-                        if (FMA) acc[i][j] = sr_add(p, fma_rn(a, bvv[j], acc[i][j]), ph.c[0]);
-                        else {
-                            const float pr = sr_mul(p, mul_rn(a, bvv[j]), ph.c[1]);
-                            acc[i][j] = sr_add(p, add_rn(acc[i][j], pr), ph.c[0]);
-                        }
-                    }
+                        for (int j = 0; j < TN; ++j) tmp[i * TN + j] = acc[i][j];
+                    sr_group_exact<FMA>(tmp, as, bs, g * 8, kglob, ty, tx, m0, n0, batch, &p);
+#pragma unroll
+                    for (int i = 0; i < TM; ++i)
+#pragma unroll
+                        for (int j = 0; j < TN; ++j) acc[i][j] = tmp[i * TN + j];
                 }
             }
         }
@@ -583,8 +753,8 @@ inline bool use_packed() {
 
 template <int ALGO, bool FMA>
 int launch_mm(const MmParams& p, int64_t batch, bool vec, cudaStream_t st) {
-    dim3 grid((p.N + BN - 1) / BN, (p.M + BM - 1) / BM, (unsigned)batch);
-    constexpr bool kHasFast = (ALGO == ALGO_SEQ || ALGO == ALGO_TILE8);
+    dim3 grid((unsigned)(((int64_t)p.N + BN - 1) / BN), (unsigned)(((int64_t)p.M + BM - 1) / BM), (unsigned)batch);
+    constexpr bool kHasFast = ALGO != ALGO_SR;       // the stochastic kernel has one form (scalar, both clamps)
     const bool packed = kHasFast && use_packed();
     // the sum rounding needs its subnormal clamp only if products can carry bits below the add format's
     // smallest subnormal (always the case for a fused multiply-add, whose sum is not a sum of rounded values)
@@ -603,7 +773,7 @@ int launch_mm(const MmParams& p, int64_t batch, bool vec, cudaStream_t st) {
 // Convolution launch: scalar operand copies (the gather has no 16-byte runs), packed fast path.
 template <int ALGO, bool FMA>
 int launch_conv(const MmParams& p, cudaStream_t st) {
-    dim3 grid((p.N + BN - 1) / BN, (p.M + BM - 1) / BM, 1);
+    dim3 grid((unsigned)(((int64_t)p.N + BN - 1) / BN), (unsigned)(((int64_t)p.M + BM - 1) / BM), 1);
     const bool add_guard = FMA || (p.fmul.min_exp - p.fmul.man) < (p.fadd.min_exp - p.fadd.man);
     auto kern = add_guard ? mm_kernel<ALGO, FMA, false, true, true, true> : mm_kernel<ALGO, FMA, false, true, FMA, true>;
     const size_t smem = SMEM_BYTES + BM * sizeof(ConvRow);

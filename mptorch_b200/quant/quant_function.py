@@ -280,7 +280,8 @@ def float_mm(a: torch.Tensor, b: torch.Tensor, man_add: int = 23, exp_add: int =
 def float_mm_streamed(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, *, device=None, block_rows: int = 1024,
                       man_add: int = 23, exp_add: int = 8, man_mul: int = 23, exp_mul: int = 8,
                       rounding: Literal["nearest", "stochastic"] = "nearest", fma: bool = True, subnormals: bool = True,
-                      saturate: bool = True, compensated: bool = False, rbits_add: int = 0, rbits_mul: int = 0) -> torch.Tensor:
+                      saturate: bool = True, compensated: bool = False, rbits_add: int = 0, rbits_mul: int = 0,
+                      b_ready: "torch.cuda.Event | None" = None) -> torch.Tensor:
     """``float_mm`` for operands that live in HOST memory (new; the reference would run them on the CPU).
 
     B is copied to the GPU once; A travels in blocks of ``block_rows`` rows on a copy stream while the previous block
@@ -289,10 +290,14 @@ def float_mm_streamed(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None
     (nearest rounding; the stochastic kernel's words are keyed by output position within a call, so its blocks draw
     as separate calls do).  ``a``, ``b`` and ``out`` must be pinned float32 CPU tensors for the copies to overlap;
     pageable tensors work but serialise.  Returns ``out`` (allocated pinned when not given); the call returns after
-    the last block has arrived."""
+    the last block has arrived.
+
+    ``b`` may instead already be resident on the device (a caller that assembles it there, e.g. from slices the ranks
+    of a job exchange); ``b_ready`` is then an event after which its contents are valid: the first kernel waits for
+    it, the copies of A do not."""
     assert len(a.shape) == 2 and len(b.shape) == 2 and a.shape[1] == b.shape[0]
     for t in (a, b):
-        if t.is_cuda or t.dtype != torch.float32 or not t.is_contiguous():
+        if (t.is_cuda and t is not b) or t.dtype != torch.float32 or not t.is_contiguous():
             raise RuntimeError("float_mm_streamed takes contiguous float32 CPU tensors (use float_mm for CUDA tensors)")
     if not torch.cuda.is_available():
         raise RuntimeError("float_mm_streamed: no CUDA device (there is no CPU fallback)")
@@ -307,11 +312,16 @@ def float_mm_streamed(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None
     with torch.cuda.device(dev):
         main = torch.cuda.current_stream(dev)
         s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
-        bd = b.to(dev, non_blocking=True)
         abuf = [torch.empty(block_rows, K, device=dev) for _ in range(2)]
         a_free = [None, None]          # event: the kernel that read abuf[i] has finished
         c_done = []                    # C blocks in flight to the host (kept alive until the final synchronisation)
         s_in.wait_stream(main)
+        if b.is_cuda:
+            bd = b
+            if b_ready is not None:
+                main.wait_event(b_ready)
+        else:
+            bd = b.to(dev, non_blocking=True)
         for i, r0 in enumerate(range(0, M, block_rows)):
             r1 = min(M, r0 + block_rows)
             slot = i & 1

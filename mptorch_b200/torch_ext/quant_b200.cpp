@@ -134,8 +134,9 @@ void mm_sr(at::Tensor a, at::Tensor b, at::Tensor c, int64_t batch, int M, int N
     CHECK_INPUT(a); CHECK_INPUT(b); CHECK_INPUT(c);
     c10::cuda::CUDAGuard guard(a.device());
     const uint64_t seed = (uint64_t)at::randint(0, INT64_MAX >> 1, {1}, at::kLong).item<int64_t>();   // reproducible under torch.manual_seed
+    auto ws = at::empty({(int64_t)mpt_mm_workspace_bytes(batch)}, a.options().dtype(at::kByte));
     check(mpt_float_mm_stochastic(a.data_ptr<float>(), b.data_ptr<float>(), c.data_ptr<float>(), batch, M, N, K, man_add, exp_add, rbits_add, man_mul,
-                                  exp_mul, rbits_mul, subnormals, saturate, fma, seed, stream()));
+                                  exp_mul, rbits_mul, subnormals, saturate, fma, seed, ws.data_ptr(), (size_t)ws.numel(), stream()));
 }
 void float_quantize_stochastic_mm(at::Tensor a, at::Tensor b, at::Tensor c, int M, int N, int K, int man_add, int exp_add, int rbits_add,
                                   int man_mul, int exp_mul, int rbits_mul, bool subnormals, bool saturate) {   // :254

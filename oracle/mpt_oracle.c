@@ -448,9 +448,18 @@ static void mm_impl(const float *a, const float *b, float *c, int64_t B, int M, 
 
 /* Stochastic-rounding GEMM, single accumulator over the zero padded K range
  * (structure: reference quant_cuda/mm_kernel.h:248-295; fma :358-400).
- * Random words: Philox4x32-10 with key (seed_lo, seed_hi) and counter
- * (k, linear output index lo, hi, 0); word 0 feeds the add (or fma) rounding,
- * word 1 the multiply rounding.  PARITY UNPINNED against the reference.   */
+ * Random words: Philox4x32-10 with key (seed_lo, seed_hi); every word of a
+ * call is used.  Two-rounding MAC: counter (k / 2, linear output index lo,
+ * hi, 0), word 2 (k % 2) feeds the add rounding and word 2 (k % 2) + 1 the
+ * multiply rounding.  Fused MAC: counter (k / 4, ...), word k % 4.
+ * The stochastic caster has no NaN early-out: it adds the random word to the
+ * NaN's bit pattern and clips whatever comes out, so the result depends on the
+ * payload.  CUDA arithmetic returns the canonical NaN 0x7FFFFFFF (x86 returns
+ * 0xFFC00000 for inf - inf), and the product is CUDA code, so every NaN that
+ * an arithmetic step yields is replaced by 0x7FFFFFFF before it is cast.
+ * PARITY UNPINNED against the reference (its generator state is racy).    */
+static float cuda_nan(float x) { return x != x ? u2f(0x7FFFFFFFu) : x; }
+
 ORC_API void orc_mm_sr(const float *a, const float *b, float *c, int64_t B, int M, int K, int N,
                        int man_add, int exp_add, int rbits_add,
                        int man_mul, int exp_mul, int rbits_mul,
@@ -467,13 +476,15 @@ ORC_API void orc_mm_sr(const float *a, const float *b, float *c, int64_t B, int 
                 for (int k = 0; k < Kpad; ++k) {
                     float av = k < K ? A[(int64_t)i * K + k] : 0.f;
                     float bv = k < K ? Bm[(int64_t)k * N + j] : 0.f;
-                    uint32_t ctr[4] = {(uint32_t)k, (uint32_t)lin, (uint32_t)(lin >> 32), 0u};
+                    uint32_t ctr[4] = {(uint32_t)(fma ? k / 4 : k / 2), (uint32_t)lin, (uint32_t)(lin >> 32), 0u};
                     philox4x32_10(ctr, (uint32_t)seed, (uint32_t)(seed >> 32));
                     if (fma) {
-                        acc = orc_cast_fp_stochastic(fmaf(av, bv, acc), ctr[0], rbits_add, man_add, exp_add, sub, sat);
+                        acc = orc_cast_fp_stochastic(cuda_nan(fmaf(av, bv, acc)), ctr[k % 4], rbits_add, man_add, exp_add, sub, sat);
                     } else {
-                        float p = orc_cast_fp_stochastic(av * bv, ctr[1], rbits_mul, man_mul, exp_mul, sub, sat);
-                        acc = orc_cast_fp_stochastic(acc + p, ctr[0], rbits_add, man_add, exp_add, sub, sat);
+                        volatile float prod = av * bv;
+                        float p = orc_cast_fp_stochastic(cuda_nan(prod), ctr[2 * (k % 2) + 1], rbits_mul, man_mul, exp_mul, sub, sat);
+                        volatile float sum = acc + p;
+                        acc = orc_cast_fp_stochastic(cuda_nan(sum), ctr[2 * (k % 2)], rbits_add, man_add, exp_add, sub, sat);
                     }
                 }
                 C[(int64_t)i * N + j] = acc;

@@ -184,6 +184,71 @@ def test_compensated(be, oracle):
         assert same_bits(got, want), f"fma={fma}: " + mismatch_report(got, want)
 
 
+@pytest.mark.parametrize("fmts", FORMATS)
+@pytest.mark.parametrize("fma", [False, True])
+def test_compensated_range_checked_path(be, oracle, fmts, fma):
+    """Kahan GEMM on operands that stay in range (packed FP-pipe roundings), that overflow part of the way (the
+    per-group fallback to the whole-domain casters), and that hold zeros, negative zeros and tiny values."""
+    fadd, fmul = fmts
+    rng = np.random.default_rng(90)
+    for (M, K, N), scale in [((70, 203, 52), 1.0), ((33, 64, 40), 40.0), ((16, 96, 24), 1e-3), ((130, 40, 70), 6.0)]:
+        a = (rng.standard_normal((M, K)) * scale).astype(np.float32)
+        b = rng.standard_normal((K, N)).astype(np.float32)
+        a[rng.random((M, K)) < 0.1] = 0.0
+        b[rng.random((K, N)) < 0.1] = -0.0
+        for sat in (False, True):
+            got = gpu_mm(be, a, b, fadd, fmul, sat=sat, fma=fma, comp=True)
+            want = cpu_mm(oracle, a, b, fadd, fmul, sat=sat, fma=fma, comp=True)
+            assert same_bits(got, want), f"{fmts} fma={fma} {(M, K, N)} x{scale} sat={sat}: " + mismatch_report(got, want)
+    a = rng.standard_normal((3, 48, 72)).astype(np.float32)
+    b = rng.standard_normal((3, 72, 36)).astype(np.float32)
+    a[1] *= 300.0
+    b[2, 5, 5] = np.inf
+    got = gpu_mm(be, a, b, fadd, fmul, fma=fma, comp=True)
+    want = cpu_mm(oracle, a, b, fadd, fmul, fma=fma, comp=True)
+    assert same_bits(got, want), f"batched {fmts} fma={fma}: " + mismatch_report(got, want)
+
+
+def test_fma_cancellation_into_fp32_denormals(be, oracle):
+    """A fused multiply-add can cancel to a nonzero fp32 denormal (exact product minus an equal-sized sum), which an
+    8-bit-exponent format rounds in its own way: operands around 2^-48 must not take the FP-pipe rounding."""
+    a = np.zeros((8, 8), np.float32)
+    b = np.zeros((8, 8), np.float32)
+    a[:, 0] = -np.float32(2.0 ** -48)
+    b[0, :] = np.float32(2.0 ** -48)
+    a[:, 1] = np.float32((1 + 2.0 ** -23) * 2.0 ** -48)
+    b[1, :] = np.float32((1 - 2.0 ** -23) * 2.0 ** -48)
+    a[:, 2:] = np.float32(2.0 ** -47)
+    b[2:, :] = np.float32(2.0 ** -49)
+    for order in ("seq", "cuda"):
+        for fadd in ((8, 7), (8, 10)):
+            got = gpu_mm(be, a, b, fadd, fadd, fma=True, order=order)
+            want = cpu_mm(oracle, a, b, fadd, fadd, fma=True, order=order)
+            assert same_bits(got, want), f"{order} {fadd}: " + mismatch_report(got, want)
+
+
+@pytest.mark.parametrize("fma", [False, True])
+def test_stochastic_range_checked_path(be, oracle, fma):
+    """Stochastic GEMM: in-range operands (straight-line rounding), overflowing ones (fallback), saturation, zeros."""
+    rng = np.random.default_rng(91)
+    seed = 0x1234ABCD5678
+    for (fadd, rb_a), (fmul, rb_m) in [(((5, 10), 13), ((4, 3), 20)), (((5, 2), 21), ((5, 2), 8)), (((8, 7), 16), ((8, 7), 16))]:
+        for (M, K, N), scale in [((40, 77, 36), 1.0), ((20, 64, 24), 200.0), ((12, 33, 20), 1e-4)]:
+            a = (rng.standard_normal((M, K)) * scale).astype(np.float32)
+            b = rng.standard_normal((K, N)).astype(np.float32)
+            a[rng.random((M, K)) < 0.1] = 0.0
+            for sat in (False, True):
+                c = torch.full((M, N), float("nan"), device="cuda")
+                if fma:
+                    be.float_quantize_stochastic_mm_fma(dev(a), dev(b), c, M, N, K, fadd[1], fadd[0], rb_a, True, sat, seed=seed)
+                    want = oracle.mm_sr(a, b, fadd[1], fadd[0], rb_a, fadd[1], fadd[0], rb_a, True, sat, True, seed)
+                else:
+                    be.float_quantize_stochastic_mm(dev(a), dev(b), c, M, N, K, fadd[1], fadd[0], rb_a, fmul[1], fmul[0], rb_m, True, sat, seed=seed)
+                    want = oracle.mm_sr(a, b, fadd[1], fadd[0], rb_a, fmul[1], fmul[0], rb_m, True, sat, False, seed)
+                got = c.cpu().numpy()
+                assert same_bits(got, want), f"{fadd} {fmul} fma={fma} {(M, K, N)} x{scale} sat={sat}: " + mismatch_report(got, want)
+
+
 def test_stochastic_matches_oracle_philox(be, oracle):
     rng = np.random.default_rng(10)
     a = rng.standard_normal((3, 20, 37)).astype(np.float32)
@@ -241,11 +306,11 @@ def test_exact_path_without_workspace(oracle):
 
 @pytest.mark.parametrize("fmts", [((5, 2), (5, 2)), ((5, 10), (4, 3)), ((8, 7), (5, 2))])
 def test_full_size_row_samples_and_sharding(be, oracle, fmts):
-    """benchmark config 4 at its largest size (8192^3 for the headline format, 4096^3 otherwise): sampled
+    """benchmark config 4 at its largest size, 8192^3, for the headline format pair and both sweep pairs: sampled
     rows equal the oracle bit for bit (rows of C are independent), and a row-sharded run equals the
     single launch (the multi-GPU decomposition)."""
     fadd, fmul = fmts
-    S = 8192 if fmts == ((5, 2), (5, 2)) else 4096
+    S = 8192
     g = torch.Generator(device="cuda").manual_seed(77)
     a = torch.randn(S, S, device="cuda", generator=g)
     b = torch.randn(S, S, device="cuda", generator=g)
@@ -260,7 +325,7 @@ def test_full_size_row_samples_and_sharding(be, oracle, fmts):
     cs = torch.empty(hi - lo, S, device="cuda")
     be.float_quantize_nearest_mm(a[lo:hi].contiguous(), b, cs, hi - lo, S, S, fadd[1], fadd[0], fmul[1], fmul[0], True, False, False, order="cuda")
     assert torch.equal(cs.view(torch.int32), c[lo:hi].view(torch.int32))
-    if S == 8192:
+    if fmts == ((5, 2), (5, 2)):
         be.float_quantize_nearest_mm(a, b, c, S, S, S, fadd[1], fadd[0], fmul[1], fmul[0], True, False, False, order="seq")
         want = oracle.mm(a[rows[:2]].cpu().numpy(), b.cpu().numpy(), fadd[1], fadd[0], fmul[1], fmul[0], True, False, False, "seq")
         assert same_bits(c[rows[:2]].cpu().numpy(), want)

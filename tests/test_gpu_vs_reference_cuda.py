@@ -1,8 +1,9 @@
 """Same-GPU comparison with the reference's own CUDA extension (oracle/_ref/quant_cuda, the unmodified
 reference sources compiled for sm_100a).  It pins the "cuda" accumulation order and the elementwise casts
 against the code this library replaces.  Only kernels whose memory accesses are bounds-checked in the
-reference source are run (elementwise quantizers, mm_impl / bmm_impl, mm_fma_impl); its stochastic GEMM
-(racy, out-of-range state indexing) is never launched."""
+reference source are run (elementwise quantizers, mm_impl / bmm_impl, mm_fma_impl, the Kahan-compensated
+mm_kahan_impl family, whose loads carry the same guards); its stochastic GEMM (racy, out-of-range state
+indexing) is never launched."""
 import numpy as np
 import pytest
 import torch
@@ -66,6 +67,87 @@ def test_binary8(ref_cuda, be):
             for po in range(3):
                 assert bits_equal(be.binary8_quantize_nearest(x, P, sg, po, True), ref_cuda.binary8_quantize_nearest(x, P, sg, pol[po], True)), (P, sg, po)
                 assert bits_equal(be.binary8_quantize_truncate(x, P, sg, po, True), ref_cuda.binary8_quantize_truncate(x, P, sg, pol[po], True)), (P, sg, po)
+
+
+def _mismatches(got, want):
+    """Number of elements whose bits differ (two NaNs of any payload count as equal)."""
+    diff = got.view(torch.int32) != want.view(torch.int32)
+    diff &= ~(got.isnan() & want.isnan())
+    return int(diff.sum().item())
+
+
+@pytest.mark.parametrize("fmt", [(5, 2), (4, 3), (5, 10), (8, 7)])
+def test_float_quantize_nearest_all_bit_patterns(ref_cuda, be, fmt):
+    """Every one of the 2^32 fp32 bit patterns, in 16 chunks of 2^28, through this library's nearest quantizer and
+    through the reference's float_kernel_nearest (quant_cuda/fp_kernel.cu:12-58, 164-172), for the four formats
+    of the benchmark configurations with subnormals and saturation on and off."""
+    e, m = fmt
+    chunk = 1 << 28
+    for sub in (True, False):
+        for sat in (True, False):
+            bad = 0
+            for c in range(16):
+                lo = -(1 << 31) + c * chunk
+                x = torch.arange(lo, lo + chunk, dtype=torch.int32, device="cuda").view(torch.float32)
+                got = be.float_quantize_nearest(x, m, e, sub, sat)
+                want = ref_cuda.float_quantize_nearest(x, m, e, sub, sat)
+                bad += _mismatches(got, want)
+                del x, got, want
+            assert bad == 0, (e, m, sub, sat, bad)
+
+
+def test_binary8_p3_nearest_all_bit_patterns(ref_cuda, be):
+    """All 2^32 inputs through binary8 P=3 signed nearest (benchmark config 2's arm: saturate_maxfloat, subnormals),
+    plus the other two overflow policies, against the reference's kernel (quant_cuda/binary8_kernel.cu:11-276)."""
+    pol = [ref_cuda.OverflowPolicy.SATURATE_INFTY, ref_cuda.OverflowPolicy.SATURATE_MAXFLOAT, ref_cuda.OverflowPolicy.SATURATE_MAXFLOAT2]
+    chunk = 1 << 28
+    for po in (1, 0, 2):
+        bad = 0
+        for c in range(16):
+            lo = -(1 << 31) + c * chunk
+            x = torch.arange(lo, lo + chunk, dtype=torch.int32, device="cuda").view(torch.float32)
+            got = be.binary8_quantize_nearest(x, 3, True, po, True)
+            want = ref_cuda.binary8_quantize_nearest(x, 3, True, pol[po], True)
+            bad += _mismatches(got, want)
+            del x, got, want
+        assert bad == 0, (po, bad)
+
+
+@pytest.mark.parametrize("shape", [(256, 256, 256), (78, 101, 145), (64, 203, 96), (512, 1000, 320)])
+def test_mm_kahan_cuda_order(ref_cuda, be, shape):
+    """The Kahan-compensated GEMMs against the reference's mm_kahan_impl / mm_kahan_fma_impl
+    (quant_cuda/mm_kernel.h:457-676, selected by `compensated` at fp_kernel.cu:190-198); K = 203 and 145 are not
+    multiples of the reference's 8-wide tile."""
+    M, K, N = shape
+    a = torch.randn(M, K, device="cuda")
+    b = torch.randn(K, N, device="cuda")
+    for (ea, ma, em, mm_) in [(5, 2, 5, 2), (5, 10, 4, 3), (8, 7, 5, 2)]:
+        want = torch.zeros(M, N, device="cuda")
+        ref_cuda.float_quantize_nearest_mm(a, b, want, M, N, K, ma, ea, mm_, em, True, False, True)
+        got = torch.empty(M, N, device="cuda")
+        be.float_quantize_nearest_mm(a, b, got, M, N, K, ma, ea, mm_, em, True, False, True, order="cuda")
+        assert bits_equal(got, want), (shape, ea, ma, em, mm_)
+        want = torch.zeros(M, N, device="cuda")
+        ref_cuda.float_quantize_nearest_mm_fma(a, b, want, M, N, K, ma, ea, True, False, True)
+        got = torch.empty(M, N, device="cuda")
+        be.float_quantize_nearest_mm_fma(a, b, got, M, N, K, ma, ea, True, False, True, order="cuda")
+        assert bits_equal(got, want), ("fma", shape, ea, ma)
+
+
+def test_bmm_kahan_cuda_order(ref_cuda, be):
+    a = torch.randn(5, 96, 77, device="cuda") * 4
+    b = torch.randn(5, 77, 64, device="cuda")
+    for sat in (False, True):
+        want = torch.zeros(5, 96, 64, device="cuda")
+        ref_cuda.float_quantize_nearest_bmm(a, b, want, 96, 64, 77, 10, 5, 3, 4, True, sat, True)
+        got = torch.empty(5, 96, 64, device="cuda")
+        be.float_quantize_nearest_bmm(a, b, got, 96, 64, 77, 10, 5, 3, 4, True, sat, True, order="cuda")
+        assert bits_equal(got, want), sat
+        want = torch.zeros(5, 96, 64, device="cuda")
+        ref_cuda.float_quantize_nearest_bmm_fma(a, b, want, 96, 64, 77, 2, 5, True, sat, True)
+        got = torch.empty(5, 96, 64, device="cuda")
+        be.float_quantize_nearest_bmm_fma(a, b, got, 96, 64, 77, 2, 5, True, sat, True, order="cuda")
+        assert bits_equal(got, want), ("fma", sat)
 
 
 @pytest.mark.parametrize("shape", [(256, 256, 256), (78, 101, 145), (512, 1000, 320)])

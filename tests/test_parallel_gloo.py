@@ -9,7 +9,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from mptorch_b200.parallel import allreduce_gradients, row_shard, sharded_float_mm
+from mptorch_b200.parallel import GradientAllReducer, allreduce_gradients, panel_bounds, row_shard, sharded_float_mm
 
 
 def test_row_shard_partitions_exactly():
@@ -22,6 +22,14 @@ def test_row_shard_partitions_exactly():
             assert max(sizes) - min(sizes) <= 1
     with pytest.raises(ValueError):
         row_shard(4, 2, 2)
+
+
+def test_panel_bounds_cover_the_block():
+    for block in (1, 2, 7, 8, 1024, 1025):
+        for panels in (1, 2, 3, 4, 16, 5000):
+            cuts = panel_bounds(block, panels)
+            assert cuts[0] == 0 and cuts[-1] == block and all(a < b for a, b in zip(cuts, cuts[1:]))
+            assert len(cuts) - 1 <= max(1, min(panels, block))
 
 
 def _free_port():
@@ -53,6 +61,14 @@ def _worker(rank, world, port, M, out_dir):
         assert torch.equal(c.view(torch.int32), want.view(torch.int32)), "gathered result differs from the unsharded one"
         local = sharded_float_mm(a[lo:hi].contiguous(), b, M, mm_fn, gather=False)
         assert torch.equal(local, want[lo:hi])
+        # row panels (the exchange of one panel runs under the next panel's kernel on a GPU): same bits for any panel
+        # count, also when the ranks' row counts differ and the last panel is short on some ranks
+        for panels in (2, 3, 5, 64):
+            cp = sharded_float_mm(a[lo:hi].contiguous(), b, M, mm_fn, panels=panels)
+            assert torch.equal(cp.view(torch.int32), want.view(torch.int32)), "panels=%d" % panels
+        into = torch.full((M, 10), float("nan"))
+        assert sharded_float_mm(a[lo:hi].contiguous(), b, M, mm_fn, panels=3, out=into) is into
+        assert torch.equal(into.view(torch.int32), want.view(torch.int32))
 
         # gradient all-reduce: two buckets, averaged
         torch.manual_seed(100 + rank)
@@ -67,6 +83,32 @@ def _worker(rank, world, port, M, out_dir):
         for i, p in enumerate(params):
             mean = sum(torch.from_numpy(gathered[r][i]) for r in range(world)) / world
             assert torch.allclose(p.grad, mean, atol=1e-6)
+        # the same reduction driven by autograd hooks while the backward pass runs
+        torch.manual_seed(5)
+        net = torch.nn.Sequential(torch.nn.Linear(6, 9), torch.nn.Tanh(), torch.nn.Linear(9, 4), torch.nn.Linear(4, 2))
+        unused = torch.nn.Parameter(torch.zeros(3))          # never receives a gradient
+        red = GradientAllReducer(list(net.parameters()) + [unused], bucket_bytes=200)
+        assert len(red.buckets) >= 3
+        for it in range(2):
+            net.zero_grad(set_to_none=True)
+            xin = torch.randn(5, 6, generator=torch.Generator().manual_seed(40 + 2 * rank + it))
+            net(xin).pow(2).sum().backward()
+            # every bucket that filled up has already been reduced inside backward()
+            assert red.calls >= 1
+            calls = red.finish()
+            assert calls >= 3 and unused.grad is None
+            # the gradients were reduced in place, so recompute every rank's own gradients for the comparison
+            ref = []
+            for r in range(world):
+                net2 = torch.nn.Sequential(torch.nn.Linear(6, 9), torch.nn.Tanh(), torch.nn.Linear(9, 4), torch.nn.Linear(4, 2))
+                net2.load_state_dict(net.state_dict())
+                xr = torch.randn(5, 6, generator=torch.Generator().manual_seed(40 + 2 * r + it))
+                net2(xr).pow(2).sum().backward()
+                ref.append([p.grad for p in net2.parameters()])
+            for i, p in enumerate(net.parameters()):
+                mean = sum(ref[r][i] for r in range(world)) / world
+                assert torch.allclose(p.grad, mean, atol=1e-6), (it, i)
+        red.remove()
         open(os.path.join(out_dir, "ok%d" % rank), "w").write("ok")
     finally:
         dist.destroy_process_group()
