@@ -62,6 +62,11 @@ enum { MPT_ORDER_SEQ = 0, MPT_ORDER_CUDA = 1 };
 MPT_API const char *mpt_last_error(void);
 MPT_API int mpt_version(void);
 
+/* No counterpart in the reference (host helper of the multi-GPU decomposition).  The numerically lowest and highest
+ * priorities a stream of the current device can take (cudaDeviceGetStreamPriorityRange; smaller = more urgent): the
+ * row-sharded GEMM runs its row panels on streams of descending priority so that a panel's tail is filled by the next. */
+MPT_API int mpt_stream_priority_range(int *lowest, int *highest);
+
 /* ---- elementwise quantizers ------------------------------------------------------------- */
 
 /* replaces float_quantize_nearest (pybind_cuda.cpp:44 -> quant.cu:143 -> fp_kernel.cu:164) */
@@ -285,6 +290,53 @@ MPT_API int mpt_mx_quantize(const float *in, float *out, uint8_t *scales, int64_
  * scale that was used. */
 MPT_API int mpt_nvfp4_quantize(const float *in, float *out, float *block_scales, int64_t rows, int64_t cols,
                                float global_scale, void *workspace, float *global_scale_out, void *stream);
+
+/* ---- quantized optimizer steps and tensor scaling -----------------------------------------------------
+ * One launch updates many tensors in place (up to 40 per launch; more are split over launches).  The
+ * table is a HOST array; nothing is allocated.  Quantizers are the reference's callables of the form
+ * Q(x + y * z) with Q = round to nearest in a (man, exp) format; `*_quant` = 0 means "no quantizer given"
+ * (the plain fp32 update of that part).  Scalars arrive already rounded to fp32 the way the reference's
+ * torch expressions round them (e.g. one_minus_dampening = (float)(1.0 - dampening)). */
+enum { MPT_OPT_FIRST_STEP = 1 };   /* per-tensor flag: the momentum buffer does not exist yet (QSGD) */
+typedef struct mpt_optim_tensor {
+    float *param;      /* updated in place */
+    float *grad;       /* QSGD with weight decay adds weight_decay * param into it, as the reference does */
+    float *buf0;       /* QSGD: momentum buffer (momentum != 0)            QAdamW: exp_avg */
+    float *buf1;       /* QSGD: compensation buffer (compensated)          QAdamW: exp_avg_sq */
+    float *buf2;       /*                                                  QAdamW: compensation buffer (compensated) */
+    float *buf3;       /*                                                  QAdamW: max_exp_avg_sq (amsgrad) */
+    int64_t n;         /* elements */
+    int32_t flags;     /* MPT_OPT_* */
+} mpt_optim_tensor;
+
+/* replaces the per-parameter loop of QSGD.step (mptorch/optim/sgd.py:63-150): weight decay into the gradient,
+ * momentum buffer update buf = Qm(buf * momentum + d_p * (1 - dampening)) (first step: Qm(d_p)), Nesterov
+ * look-ahead, and the weight update p = Qa(p - lr * d_p) or its Kahan-compensated form with the buffer in buf1. */
+MPT_API int mpt_qsgd_step(const mpt_optim_tensor *tensors, int count, float lr, float momentum,
+                          float one_minus_dampening, float weight_decay, int nesterov, int compensated,
+                          int momentum_quant, int man_mom, int exp_mom, int acc_quant, int man_acc, int exp_acc,
+                          int subnormals, int saturate, void *stream);
+
+/* replaces the per-parameter loop of QAdamW.step (mptorch/optim/adamw.py:44-150) for tensors that share one
+ * step count: moments m = Qm(m * beta1 + g * (1 - beta1)), v = Qm(v * beta2 + g^2 * (1 - beta2)), optional
+ * amsgrad maximum, denom = sqrt(v) * inv_sqrt_bias_correction2 + eps, and the weight update
+ * p = Qa(p - step_size * m / denom) or its Kahan-compensated form.  step_size = lr / bias_correction1 and
+ * inv_sqrt_bias_correction2 = (float)(1.0 / sqrt(bias_correction2)) are computed by the caller. */
+MPT_API int mpt_qadamw_step(const mpt_optim_tensor *tensors, int count, float beta1, float beta2,
+                            float one_minus_beta1, float one_minus_beta2, float inv_sqrt_bias_correction2,
+                            float eps, float step_size, int amsgrad, int compensated,
+                            int momentum_quant, int man_mom, int exp_mom, int acc_quant, int man_acc, int exp_acc,
+                            int subnormals, int saturate, void *stream);
+
+/* replaces compute_bias + scale + the quantizer call of the layers' tensor scaling
+ * (mptorch/quant/functional.py:39-53 as used at :82-90): for each of `matrices` consecutive blocks of
+ * `per_matrix` elements, s = floor(log2(normal_max / amax)) - margin (log2 in double precision) and
+ * out = Q(in * 2^s); `quantize` = 0 leaves the scaled values unrounded.  `scale_out` (optional, device,
+ * `matrices` floats) receives s.  workspace: mpt_scale_quantize_workspace_bytes(matrices) bytes. */
+MPT_API size_t mpt_scale_quantize_workspace_bytes(int64_t matrices);
+MPT_API int mpt_scale_quantize(const float *in, float *out, int64_t matrices, int64_t per_matrix, double normal_max,
+                               int margin, int quantize, int man, int exp, int subnormals, int saturate,
+                               float *scale_out, void *workspace, size_t workspace_bytes, void *stream);
 
 #ifdef __cplusplus
 }

@@ -54,6 +54,8 @@ def lib() -> C.CDLL:
         L.mpt_version.restype = i32
         L.mpt_mm_workspace_bytes.restype = sz
         L.mpt_mm_workspace_bytes.argtypes = [i64]
+        L.mpt_scale_quantize_workspace_bytes.restype = sz
+        L.mpt_scale_quantize_workspace_bytes.argtypes = [i64]
         sig = {
             "mpt_float_quantize_nearest": [p, p, i64, i32, i32, i32, i32, p],
             "mpt_float_quantize_truncate": [p, p, i64, i32, i32, i32, i32, p],
@@ -79,6 +81,10 @@ def lib() -> C.CDLL:
             "mpt_softmax_backward_fmt": [p, p, p, i64, i32, i64, p, p, i32, p],
             "mpt_layernorm_forward_fmt": [p] * 6 + [C.c_float, i64, i32, i64, p, p, p, p, i32, p],
             "mpt_layernorm_backward_fmt": [p] * 8 + [i64, i32, i64, p, p, p, i32, p],
+            "mpt_stream_priority_range": [p, p],
+            "mpt_qsgd_step": [p, i32, C.c_float, C.c_float, C.c_float, C.c_float] + [i32] * 10 + [p],
+            "mpt_qadamw_step": [p, i32] + [C.c_float] * 7 + [i32] * 10 + [p],
+            "mpt_scale_quantize": [p, p, i64, i64, C.c_double, i32, i32, i32, i32, i32, i32, p, p, sz, p],
             "mpt_mx_quantize": [p, p, p, i64, i64, i32, i32, p],
             "mpt_nvfp4_quantize": [p, p, p, i64, i64, C.c_float, p, p, p],
         }

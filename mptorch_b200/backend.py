@@ -382,6 +382,26 @@ def qsum_rows(a, man_bits, exp_bits, subnormals, saturate):
     return o
 
 
+def scale_quantize(a, normal_max, margin, fmt=None):
+    """New: the layers' tensor scaling in two kernels.  For every matrix (the last two dimensions) of ``a``:
+    s = floor(log2(normal_max / amax)) - margin and out = Q(a * 2^s), with Q the nearest rounding to ``fmt`` =
+    (man, exp, subnormals, saturate), or no rounding when ``fmt`` is None.  Returns (out, s) with s shaped
+    [..., 1, 1] like the reference's compute_bias (functional.py:39-46)."""
+    check_cuda_f32(a, "a")
+    if a.dim() < 2:
+        raise RuntimeError("scale_quantize expects at least two dimensions")
+    per = a.shape[-1] * a.shape[-2]
+    mats = a.numel() // per if per else 0
+    o = torch.empty_like(a)
+    sc = torch.empty(tuple(a.shape[:-2]) + (1, 1), device=a.device)
+    man, exp, sub, sat = fmt if fmt is not None else (23, 8, True, False)
+    with torch.cuda.device(a.device):
+        ws = torch.empty(max(4 * mats, 4), dtype=torch.uint8, device=a.device)
+        call("mpt_scale_quantize", ptr(a), ptr(o), mats, per, float(normal_max), int(margin), int(fmt is not None), man, exp,
+             int(sub), int(sat), ptr(sc), ptr(ws), ws.numel(), stream_ptr(a.device))
+    return o, sc
+
+
 # ---------------------------------------------------------------------------------- other format families
 # The reference registers the same GEMM / softmax / layernorm entry points once more for supernormal floats and, for
 # the reductions, for binary8 (pybind_cuda.cpp:815-824, :887-924).  They all forward to the generic-format C ABI.

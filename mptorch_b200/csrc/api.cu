@@ -78,4 +78,13 @@ extern "C" {
 const char* mpt_last_error(void) { return mpt::g_err; }
 int mpt_version(void) { return 100; }
 
+int mpt_stream_priority_range(int* lowest, int* highest) {
+    int lo = 0, hi = 0;
+    const cudaError_t e = cudaDeviceGetStreamPriorityRange(&lo, &hi);
+    if (e != cudaSuccess) { mpt::set_error("stream_priority_range: %s", cudaGetErrorString(e)); return MPT_ERR_CUDA; }
+    if (lowest) *lowest = lo;
+    if (highest) *highest = hi;
+    return MPT_OK;
+}
+
 }

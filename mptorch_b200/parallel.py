@@ -70,27 +70,34 @@ def sharded_float_mm(a_rows: torch.Tensor, b: torch.Tensor, M: int, mm_fn: Calla
     if out is None:
         out = torch.empty(M, N, dtype=a_rows.dtype, device=a_rows.device)
     cuda = a_rows.is_cuda
-    main = torch.cuda.current_stream(a_rows.device) if cuda else None
-    side = torch.cuda.Stream(a_rows.device) if cuda else None
-    if cuda:
-        side.wait_stream(main)                   # `out` may be recycled memory still in use on the main stream
     cuts = panel_bounds(block, panels)
+    npan = len(cuts) - 1
     keep = []
-    for plo, phi in zip(cuts[:-1], cuts[1:]):
+    if cuda:
+        # Each panel's kernel runs on a stream of its own, earlier panels at higher priority: the GPU fills the SMs that
+        # a finishing panel leaves idle with the next panel's thread blocks, so cutting the launch into panels costs no
+        # partial waves, and a panel's rows are complete (and on their way to the peers) while later panels compute.
+        main = torch.cuda.current_stream(a_rows.device)
+        side = torch.cuda.Stream(a_rows.device)
+        low, high = _priority_range()
+        compute = [torch.cuda.Stream(a_rows.device, priority=max(high, min(low, high + i))) for i in range(npan)] if npan > 1 else [main]
+        side.wait_stream(main)                   # `out` may be recycled memory still in use on the main stream
+        for cs in compute:
+            if cs is not main:
+                cs.wait_stream(main)
+    for i, (plo, phi) in enumerate(zip(cuts[:-1], cuts[1:])):
         mine = a_rows[min(plo, nloc):min(phi, nloc)]
-        c_p = mm_fn(mine, b) if mine.shape[0] else torch.empty(0, N, dtype=a_rows.dtype, device=a_rows.device)
         even = all(c >= phi for c in counts)     # every rank holds the whole panel
-        if not even:
-            padded = torch.zeros(phi - plo, N, dtype=c_p.dtype, device=c_p.device)
-            padded[: c_p.shape[0]] = c_p
-            c_p = padded
-        if cuda:
-            ready = torch.cuda.Event()
-            ready.record(main)
-            ctx = torch.cuda.stream(side)
-        else:
-            ctx = _NullContext()
-        with ctx:
+        with (torch.cuda.stream(compute[i]) if cuda else _NullContext()):
+            c_p = mm_fn(mine, b) if mine.shape[0] else torch.empty(0, N, dtype=a_rows.dtype, device=a_rows.device)
+            if not even:
+                padded = torch.zeros(phi - plo, N, dtype=c_p.dtype, device=c_p.device)
+                padded[: c_p.shape[0]] = c_p
+                c_p = padded
+            if cuda:
+                ready = torch.cuda.Event()
+                ready.record(compute[i])
+        with (torch.cuda.stream(side) if cuda else _NullContext()):
             if cuda:
                 side.wait_event(ready)
             if even:
@@ -109,9 +116,23 @@ def sharded_float_mm(a_rows: torch.Tensor, b: torch.Tensor, M: int, mm_fn: Calla
         keep.append(c_p)
     if cuda:
         main.wait_stream(side)
+        for cs in compute:
+            if cs is not main:
+                main.wait_stream(cs)
         for t in keep:
             t.record_stream(main)
     return out
+
+
+def _priority_range() -> tuple[int, int]:
+    """(lowest, highest) CUDA stream priority of the current device; a numerically smaller value is a higher priority."""
+    import ctypes
+
+    from . import _cabi
+
+    lo, hi = ctypes.c_int(0), ctypes.c_int(0)
+    _cabi.call("mpt_stream_priority_range", ctypes.byref(lo), ctypes.byref(hi))
+    return lo.value, hi.value
 
 
 class _NullContext:

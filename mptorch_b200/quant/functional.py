@@ -39,18 +39,52 @@ def unscale(x: torch.Tensor, x_scale) -> torch.Tensor:
     return x * 2 ** (-x_scale)
 
 
-def _scales(ctx, formats, a, b):
+def _unscale(x, x_scale):
+    """``unscale`` inside the layers: a scale of exactly 0 (no tensor scaling) multiplies by one, which leaves every
+    value as it is, so the elementwise kernel is skipped."""
+    return x if (isinstance(x_scale, int) and x_scale == 0) else unscale(x, x_scale)
+
+
+def _float_nearest_spec(quant):
+    """What ``quant`` does, when a kernel can do it too: "identity", (man, exp, subnormals, saturate) for a float format
+    rounded to nearest, or None for anything else (stochastic rounding, other format families, user callables)."""
+    if quant is id_quant:
+        return "identity"
+    num, rnd = getattr(quant, "forward_number", 0), getattr(quant, "forward_rounding", None)
+    if num is None:
+        return "identity"
+    if isinstance(num, FloatingPoint) and rnd == "nearest":
+        return (num.man, num.exp, num.subnormals, num.saturate)
+    return None
+
+
+def _scaled_quant(x, scaled_format, margin, quant):
+    """(quant(scale(x, s)), s) with s = compute_bias(x, scaled_format, margin): two kernels (row maxima, then scale and
+    round) instead of the reference's two reductions, five elementwise kernels and the quantizer launch, same bits."""
+    spec = _float_nearest_spec(quant)
+    if spec is not None and x.is_cuda and x.dim() >= 2 and x.dtype == torch.float32:
+        from .. import backend as _be
+
+        return _be.scale_quantize(x.contiguous(), scaled_format.normal_max, margin, None if spec == "identity" else spec)
+    s = compute_bias(x, scaled_format, margin)
+    return quant(scale(x, s)), s
+
+
+def _quantize_operands(ctx, formats, a, b):
+    """The scaled and quantized operands of a layer's forward GEMM; records the scales on ``ctx``."""
     if formats.weight_scaled_format and formats.input_scaled_format and formats.use_scaling:
-        ctx.weight_scale = compute_bias(b, formats.weight_scaled_format, formats.scale_margin)
-        ctx.input_scale = compute_bias(a, formats.input_scaled_format, formats.scale_margin)
-    else:
-        ctx.input_scale, ctx.weight_scale = 0, 0
+        qb, ctx.weight_scale = _scaled_quant(b, formats.weight_scaled_format, formats.scale_margin, formats.weight_quant)
+        qa, ctx.input_scale = _scaled_quant(a, formats.input_scaled_format, formats.scale_margin, formats.input_quant)
+        return qa, qb
+    ctx.input_scale, ctx.weight_scale = 0, 0
+    return formats.input_quant(a), formats.weight_quant(b)
 
 
-def _grad_scale(formats, grad_output):
+def _quantize_grad(formats, grad_output):
+    """(quantized, possibly scaled, output gradient; its scale)."""
     if formats.grad_scaled_format and formats.use_scaling:
-        return compute_bias(grad_output, formats.grad_scaled_format, formats.scale_margin)
-    return 0
+        return _scaled_quant(grad_output, formats.grad_scaled_format, formats.scale_margin, formats.grad_quant)
+    return formats.grad_quant(grad_output), 0
 
 
 # ------------------------------------------------------------------------------------------ quantized sums
@@ -117,16 +151,14 @@ class qlinear_kernel(torch.autograd.Function):
     @staticmethod
     def forward(ctx, input, weight, bias, formats):
         ctx.formats = formats
-        _scales(ctx, formats, input, weight)
-        qinput = formats.input_quant(scale(input, ctx.input_scale))
-        qweight = formats.weight_quant(scale(weight, ctx.weight_scale))
+        qinput, qweight = _quantize_operands(ctx, formats, input, weight)
         qbias = formats.bias_quant(bias) if bias is not None else None
         if formats.fwd_use_default_prec:
             with torch.no_grad():
                 output = torch.nn.functional.linear(qinput, qweight)
         else:
             output = mp_bmm(qinput, qweight.t(), formats, use_forward=True)
-        output = unscale(output, ctx.input_scale + ctx.weight_scale)
+        output = _unscale(output, ctx.input_scale + ctx.weight_scale)
         if qbias is not None:
             output += qbias.view(-1, qbias.shape[-1])     # plain fp32 add; rounding is left to output_quant
         ctx.save_for_backward(qinput, qweight, qbias)
@@ -137,14 +169,13 @@ class qlinear_kernel(torch.autograd.Function):
         qinput, qweight, qbias = ctx.saved_tensors
         f = ctx.formats
         qgrad_input = qgrad_weight = qgrad_bias = None
-        grad_scale = _grad_scale(f, grad_output)
-        qgrad_output = f.grad_quant(scale(grad_output, grad_scale))
+        qgrad_output, grad_scale = _quantize_grad(f, grad_output)
         if ctx.needs_input_grad[0]:
             if f.bwd_use_default_prec:
                 qgrad_input = torch.matmul(qgrad_output, qweight)
             else:
                 qgrad_input = mp_bmm(qgrad_output, qweight, formats=f, use_forward=False)
-            qgrad_input = f.grad_quant(unscale(qgrad_input, grad_scale + ctx.weight_scale))
+            qgrad_input = f.grad_quant(_unscale(qgrad_input, grad_scale + ctx.weight_scale))
         if ctx.needs_input_grad[1]:
             if f.bwd_use_default_prec:
                 qgrad_weight = torch.matmul(qgrad_output.transpose(-2, -1), qinput)
@@ -152,7 +183,7 @@ class qlinear_kernel(torch.autograd.Function):
                 # for >2-D inputs this is a batched GEMM; autograd sums the [batch, out, in] result over the batch
                 # in plain fp32 when it reduces the gradient to the weight's shape, exactly as in the reference
                 qgrad_weight = mp_bmm(qgrad_output.transpose(-2, -1), qinput, formats=f, use_forward=False)
-            qgrad_weight = f.grad_quant(unscale(qgrad_weight, grad_scale + ctx.input_scale))
+            qgrad_weight = f.grad_quant(_unscale(qgrad_weight, grad_scale + ctx.input_scale))
         if qbias is not None and ctx.needs_input_grad[2]:
             lead = tuple(range(qgrad_output.dim() - 1))
             if f.bwd_use_default_prec:
@@ -164,7 +195,7 @@ class qlinear_kernel(torch.autograd.Function):
                     else:
                         qgrad_bias = qsum(qgrad_output, dim=lead,
                                           quant=make_quant_function(f.bwd_add, f.bwd_rnd, f.rbits_add)).reshape(qbias.shape)
-            qgrad_bias = f.grad_quant(unscale(qgrad_bias, grad_scale))
+            qgrad_bias = f.grad_quant(_unscale(qgrad_bias, grad_scale))
         return qgrad_input, qgrad_weight, qgrad_bias, None, None
 
 
@@ -230,23 +261,23 @@ class qconv2d_kernel(torch.autograd.Function):
         n, c, h, w = qinput.shape
         c_out, cg, kh, kw = qweight.shape
         og = c_out // groups
-        grad_scale = _grad_scale(f, grad_output)
+        grad_scale = 0                # the implicit path is taken only without tensor scaling (implicit_conv_eligible)
         gin, gws, gbs = [], [], []
         for g in range(groups):
             go = grad_output[:, g * og:(g + 1) * og]
             go2 = go.reshape(n, og, -1).transpose(1, 2).reshape(-1, og)              # [N * L, og], as qlinear sees it
-            qgo = f.grad_quant(scale(go2, grad_scale))
+            qgo = f.grad_quant(go2)
             w2 = qweight[g * og:(g + 1) * og].reshape(og, -1)
             if ctx.needs_input_grad[0]:
                 gc = torch.matmul(qgo, w2) if f.bwd_use_default_prec else mp_bmm(qgo, w2, formats=f, use_forward=False)
-                gc = f.grad_quant(unscale(gc, grad_scale + 0))
+                gc = f.grad_quant(gc)
                 gc = gc.view(n, -1, gc.shape[-1]).transpose(1, 2)                    # [N, K, L]
                 gin.append(torch.nn.functional.fold(gc, (h, w), (kh, kw), dilation=dilation, padding=padding, stride=stride))
             if ctx.needs_input_grad[1]:
                 cols = _conv_cols(qinput[:, g * cg:(g + 1) * cg], (kh, kw), dilation, padding, stride)
                 gw = (torch.matmul(qgo.transpose(-2, -1), cols) if f.bwd_use_default_prec
                       else mp_bmm(qgo.transpose(-2, -1), cols, formats=f, use_forward=False))
-                gws.append(f.grad_quant(unscale(gw, grad_scale + 0)).view(og, cg, kh, kw))
+                gws.append(f.grad_quant(gw).view(og, cg, kh, kw))
             if qbias is not None and ctx.needs_input_grad[2]:
                 if f.bwd_use_default_prec:
                     gb = qgo.sum(dim=0)
@@ -256,7 +287,7 @@ class qconv2d_kernel(torch.autograd.Function):
                             gb = _qsum_dims_fast(qgo, (0,), f.bwd_add)
                         else:
                             gb = qsum(qgo, dim=(0,), quant=make_quant_function(f.bwd_add, f.bwd_rnd, f.rbits_add))
-                gbs.append(f.grad_quant(unscale(gb.reshape(-1), grad_scale)))
+                gbs.append(f.grad_quant(gb.reshape(-1)))
         grad_input = torch.cat(gin, dim=1) if gin else None
         grad_weight = torch.cat(gws, dim=0) if gws else None
         grad_bias = torch.cat(gbs, dim=0) if gbs else None
@@ -275,15 +306,13 @@ def _matmul_function(fwd_default, mp_fn, name, requantize_unscaled):
         @staticmethod
         def forward(ctx, input, other, formats):
             ctx.formats = formats
-            _scales(ctx, formats, input, other)
-            qinput = formats.input_quant(scale(input, ctx.input_scale))
-            qother = formats.weight_quant(scale(other, ctx.weight_scale))
+            qinput, qother = _quantize_operands(ctx, formats, input, other)
             if formats.fwd_use_default_prec:
                 with torch.no_grad():
                     output = fwd_default(qinput, qother)
             else:
                 output = mp_fn(qinput, qother, formats=formats, use_forward=True)
-            output = unscale(output, ctx.input_scale + ctx.weight_scale)
+            output = _unscale(output, ctx.input_scale + ctx.weight_scale)
             ctx.save_for_backward(qinput, qother)
             return formats.output_quant(output)
 
@@ -292,21 +321,20 @@ def _matmul_function(fwd_default, mp_fn, name, requantize_unscaled):
             qinput, qother = ctx.saved_tensors
             f = ctx.formats
             qgrad_input = qgrad_other = None
-            grad_scale = _grad_scale(f, grad_output)
-            qgrad_output = f.grad_quant(scale(grad_output, grad_scale))
+            qgrad_output, grad_scale = _quantize_grad(f, grad_output)
             if ctx.needs_input_grad[0]:
                 if f.bwd_use_default_prec:
                     g = fwd_default(qgrad_output, qother.transpose(-2, -1))
                 else:
                     g = mp_fn(qgrad_output, qother.transpose(-2, -1), formats=f, use_forward=False)
                 # the reference's qmm quantizes the un-unscaled gradient (functional.py:270-272); qmatmul the unscaled one
-                qgrad_input = f.grad_quant(unscale(g, grad_scale + ctx.weight_scale) if requantize_unscaled else g)
+                qgrad_input = f.grad_quant(_unscale(g, grad_scale + ctx.weight_scale) if requantize_unscaled else g)
             if ctx.needs_input_grad[1]:
                 if f.bwd_use_default_prec:
                     g = fwd_default(qinput.transpose(-2, -1), qgrad_output)
                 else:
                     g = mp_fn(qinput.transpose(-2, -1), qgrad_output, formats=f, use_forward=False)
-                qgrad_other = f.grad_quant(unscale(g, grad_scale + ctx.input_scale) if requantize_unscaled else g)
+                qgrad_other = f.grad_quant(_unscale(g, grad_scale + ctx.input_scale) if requantize_unscaled else g)
             return qgrad_input, qgrad_other, None
 
     kernel.__name__ = name

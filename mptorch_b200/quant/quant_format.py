@@ -21,9 +21,15 @@ def id_quant(x):
 
 
 def make_quant_function(num: Number, rounding: str, prng_bits: int = 0) -> Callable:
-    """A tensor -> tensor quantizer for ``num`` with the given rounding."""
+    """A tensor -> tensor quantizer for ``num`` with the given rounding.  Float quantizers carry what they do as
+    attributes (``forward_number``, ``forward_rounding``), so that callers which can fuse them into a larger kernel
+    (tensor scaling, the implicit convolution) recognise them."""
     if isinstance(num, FloatingPoint):
-        return lambda x: float_quantize(x, num.exp, num.man, rounding, num.subnormals, num.saturate, prng_bits)
+        def q(x):
+            return float_quantize(x, num.exp, num.man, rounding, num.subnormals, num.saturate, prng_bits)
+
+        q.forward_number, q.forward_rounding = num, rounding
+        return q
     if isinstance(num, FixedPoint):
         return lambda x: fixed_point_quantize(x, num.wl, num.fl, num.clamp, num.symmetric, rounding)
     if isinstance(num, SuperNormalFloat):

@@ -197,3 +197,46 @@ def test_quantizer_module_and_ste():
     g = torch.randn(64, device="cuda")
     y.backward(g)
     assert torch.equal(x.grad, q.float_quantize(g, 5, 2, "nearest", True, True))
+
+
+def test_fused_tensor_scaling_equals_reference_sequence():
+    """compute_bias -> scale -> quantize as two kernels against the reference's sequence of torch operations and the
+    quantizer call (functional.py:39-53), bit for bit, scales included; then a scaled QLinear forward and backward with
+    the fused path on and off."""
+    g = torch.Generator(device="cuda").manual_seed(21)
+    fmt = mp.FloatingPoint(4, 3, True, True)
+    quant = q.quant_format.make_quant_function(fmt, "nearest")
+    for shape in [(64, 48), (5, 33, 70), (2, 3, 16, 8), (1, 1)]:
+        x = torch.randn(shape, device="cuda", generator=g) * (10.0 ** torch.randint(-6, 6, shape[:-2] + (1, 1), device="cuda", generator=g).float())
+        for margin in (0, 2):
+            for qq in (quant, Fq.id_quant):
+                got, s = Fq._scaled_quant(x, fmt, margin, qq)
+                ws = Fq.compute_bias(x, fmt, margin)
+                want = qq(Fq.scale(x, ws))
+                assert s.shape == ws.shape and torch.equal(s, ws), (shape, margin)
+                assert torch.equal(got.view(torch.int32), want.view(torch.int32)), (shape, margin)
+    z = torch.zeros(4, 4, device="cuda")                     # amax = 0: the reference yields inf * 0 = NaN everywhere
+    got, s = Fq._scaled_quant(z, fmt, 0, quant)
+    assert torch.isinf(s).all() and torch.isnan(got).all()
+
+    f = q.QAffineFormats(fwd_mac=(mp.FloatingPoint(5, 10, True, False), fmt), bwd_mac=(mp.FloatingPoint(5, 10, True, False), fmt),
+                         weight_quant=(fmt, "nearest"), input_quant=(fmt, "nearest"), grad_quant=(mp.FloatingPoint(5, 2, True, True), "nearest"),
+                         use_scaling=True, scale_margin=1)
+    torch.manual_seed(5)
+    lin = q.QLinear(48, 40, f).cuda()
+    xin = (torch.randn(3, 20, 48, device="cuda") * 1e-3)
+    outs = []
+    for fused in (True, False):
+        spec = Fq._float_nearest_spec
+        if not fused:
+            Fq._float_nearest_spec = lambda quant: None
+        try:
+            xi = xin.clone().requires_grad_(True)
+            lin.zero_grad()
+            y = lin(xi)
+            (y * torch.linspace(-1, 1, y.numel(), device="cuda").view_as(y)).sum().backward()
+            outs.append((y.detach().clone(), xi.grad.clone(), lin.weight.grad.clone(), lin.bias.grad.clone()))
+        finally:
+            Fq._float_nearest_spec = spec
+    for a, b in zip(*outs):
+        assert torch.equal(a.view(torch.int32), b.view(torch.int32))

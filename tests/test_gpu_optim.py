@@ -182,3 +182,112 @@ def test_qoptim_passes_other_callables_through(q):
     assert len(calls) == len(list(m.parameters()))
     for p in m.parameters():
         assert bits_equal(p.data, q.float_quantize(p.data, 4, 3, "nearest"))
+
+
+# ------------------------------------------------------------------------------------------ QSGD / QAdamW
+def _models(seed, n=3):
+    g = torch.Generator().manual_seed(seed)
+    shapes = [(301,), (64, 33), (7, 5, 3), (4096 + 5,), (1,)]
+    return [[torch.nn.Parameter(torch.randn(s, generator=g).cuda()) for s in shapes] for _ in range(n)], shapes, g
+
+
+def _same(a, b):
+    return torch.equal(a.detach().contiguous().view(torch.int32), b.detach().contiguous().view(torch.int32))
+
+
+SGD_CONFIGS = [
+    dict(lr=0.05, momentum=0.9),
+    dict(lr=0.05, momentum=0.9, compensated=True),
+    dict(lr=0.1, momentum=0.8, dampening=0.25, weight_decay=0.01, compensated=True),
+    dict(lr=0.1, momentum=0.8, nesterov=True, weight_decay=0.001),
+    dict(lr=0.03, momentum=0.0, compensated=True),
+    dict(lr=0.03, momentum=0.0),
+]
+
+
+@pytest.mark.parametrize("cfg", SGD_CONFIGS)
+@pytest.mark.parametrize("fmts", [((8, 7), (8, 7)), ((5, 10), (5, 2)), (None, (4, 3)), ((5, 2), None), ((3, 0), (1, 3))])
+def test_qsgd_fused_step_equals_per_tensor_steps(cfg, fmts):
+    """One fused launch per step against the reference's per-tensor sequence of torch kernels and quantizer calls,
+    on identical parameters and gradients, bit for bit, buffers included."""
+    from mptorch_b200 import FloatingPoint
+    from mptorch_b200.optim import QSGD, fma_quantizer
+
+    mq, aq = [fma_quantizer(FloatingPoint(f[0], f[1], True, True)) if f else None for f in fmts]
+    (pa, pb, _), shapes, g = _models(11)
+    for x, y in zip(pa, pb):
+        y.data.copy_(x.data)
+    oa = QSGD(pa, momentum_quant=mq, acc_quant=aq, **cfg)                  # fused
+    ob = QSGD(pb, momentum_quant=mq, acc_quant=aq, fused=False, **cfg)     # per tensor
+    for step in range(4):
+        for x, y in zip(pa, pb):
+            gr = (torch.randn(x.shape, generator=g) * (0.3 + step)).cuda()
+            x.grad, y.grad = gr.clone(), gr.clone()
+        oa.step()
+        ob.step()
+        for i, (x, y) in enumerate(zip(pa, pb)):
+            assert _same(x.data, y.data), ("param", step, i, cfg, fmts)
+            assert _same(x.grad, y.grad), ("grad", step, i)
+            for key in ("momentum_buffer", "compensated_buffer"):
+                if key in ob.state[y]:
+                    assert _same(oa.state[x][key], ob.state[y][key]), (key, step, i, cfg, fmts)
+
+
+ADAM_CONFIGS = [
+    dict(lr=0.01, betas=(0.9, 0.99)),
+    dict(lr=0.01, betas=(0.9, 0.99), compensated=True),
+    dict(lr=0.02, betas=(0.8, 0.95), amsgrad=True, eps=1e-6),
+    dict(lr=0.02, betas=(0.8, 0.95), amsgrad=True, compensated=True),
+]
+
+
+@pytest.mark.parametrize("cfg", ADAM_CONFIGS)
+@pytest.mark.parametrize("fmts", [((8, 7), (8, 7)), ((5, 10), (5, 2)), (None, (4, 3)), ((5, 10), None)])
+def test_qadamw_fused_step_equals_per_tensor_steps(cfg, fmts):
+    from mptorch_b200 import FloatingPoint
+    from mptorch_b200.optim import QAdamW, fma_quantizer
+
+    mq, aq = [fma_quantizer(FloatingPoint(f[0], f[1], True, True)) if f else None for f in fmts]
+    (pa, pb, _), shapes, g = _models(12)
+    for x, y in zip(pa, pb):
+        y.data.copy_(x.data)
+    oa = QAdamW(pa, momentum_quant=mq, acc_quant=aq, **cfg)
+    ob = QAdamW(pb, momentum_quant=mq, acc_quant=aq, fused=False, **cfg)
+    for step in range(4):
+        for x, y in zip(pa, pb):
+            gr = (torch.randn(x.shape, generator=g) * (0.3 + step)).cuda()
+            x.grad, y.grad = gr.clone(), gr.clone()
+        oa.step()
+        ob.step()
+        for i, (x, y) in enumerate(zip(pa, pb)):
+            assert _same(x.data, y.data), ("param", step, i, cfg, fmts)
+            assert oa.state[x]["step"] == ob.state[y]["step"]
+            for key in ("exp_avg", "exp_avg_sq", "max_exp_avg_sq", "compensated_buffer"):
+                if key in ob.state[y]:
+                    assert _same(oa.state[x][key], ob.state[y][key]), (key, step, i, cfg, fmts)
+
+
+@pytest.mark.parametrize("name", ["sgd_mom_acc", "sgd_mom_acc_comp", "sgd_mom_damp_comp_e5m2", "sgd_mom_only"])
+def test_qsgd_fused_step_matches_reference_fixture(name):
+    """The fused kernel against the outputs of the reference's own QSGD (CPU run, committed fixture): these cases use
+    only separately rounded multiplies and adds, which a CPU and a GPU evaluate alike, so the bits must agree."""
+    from test_optim_cpu import check_against_fixture
+
+    from mptorch_b200 import FloatingPoint
+    from mptorch_b200.optim import fma_quantizer
+
+    check_against_fixture(name, lambda fmt: fma_quantizer(FloatingPoint(fmt[0], fmt[1], True, True)) if fmt else None, device="cuda")
+
+
+def test_optimizers_fall_back_for_other_callables():
+    """Any other trivariate callable takes the per-tensor path and still works on CUDA tensors."""
+    from mptorch_b200.optim import QSGD
+    from mptorch_b200.quant import float_quantize
+
+    p = torch.nn.Parameter(torch.randn(50).cuda())
+    q = lambda x, y, z: float_quantize(x + y * z, 8, 7, "nearest")   # noqa: E731
+    opt = QSGD([p], lr=0.1, momentum=0.9, momentum_quant=q, acc_quant=q, compensated=True)
+    before = p.data.clone()
+    p.grad = torch.randn(50).cuda()
+    opt.step()
+    assert not torch.equal(before, p.data) and torch.isfinite(p.data).all()
