@@ -410,7 +410,7 @@ def c4_sweep(dev, sizes=(2048, 4096, 8192), variants=True) -> dict:
             for order in ("cuda", "seq"):
                 rec(name, order, "mul+add", timed(lambda: be.float_quantize_nearest_mm(a, b, c, S, S, S, ma, ea, mm, em, True, False, False, order=order), reps))
             rec(name, "cuda", "fma (add format)", timed(lambda: be.float_quantize_nearest_mm_fma(a, b, c, S, S, S, ma, ea, True, False, False, order="cuda"), reps))
-        if variants and S == 4096:
+        if variants and (S == 4096 or len(sizes) == 1):
             for name, (ma, ea, mm, em) in C4_PAIRS.items():
                 rec(name, "cuda", "kahan", timed(lambda: be.float_quantize_nearest_mm(a, b, c, S, S, S, ma, ea, mm, em, True, False, True, order="cuda"), 3))
                 rec(name, "cuda", "stochastic", timed(lambda: be.float_quantize_stochastic_mm(a, b, c, S, S, S, ma, ea, 23 - ma, mm, em, 23 - mm, True, False, seed=5), 3))

@@ -399,6 +399,15 @@ struct FullRn {
         const float over = (a >= 0x7F800000u) ? x : u2f((t & 0x80000000u) | ovf_value);
         return (a >= ovf_from) ? over : y;
     }
+    // The same for formats with fewer than 8 exponent bits, without the test for them: straight-line code (no branch),
+    // so that a compiler can interleave several independent roundings.
+    MPT_HD float line(float x) const {
+        const uint32_t t = f2u(x);
+        const uint32_t a = t & 0x7FFFFFFFu;
+        const float y = fast(x);
+        const float over = (a >= 0x7F800000u) ? x : u2f((t & 0x80000000u) | ovf_value);
+        return (a >= ovf_from) ? over : y;
+    }
 };
 
 

@@ -554,8 +554,8 @@ __device__ __forceinline__ FastPlan make_plan(const MmParams& p, int64_t batch) 
     return plan;
 }
 
-template <int ALGO, bool FMA, bool VEC, bool PACKED, bool ADDG, bool CONV = false>
-__global__ void __launch_bounds__(THREADS, MPT_MM_MIN_CTAS) mm_kernel(const __grid_constant__ MmParams p) {
+template <int ALGO, bool FMA, bool VEC, bool PACKED, bool ADDG, bool CONV = false, int MINB = MPT_MM_MIN_CTAS>
+__global__ void __launch_bounds__(THREADS, MINB) mm_kernel(const __grid_constant__ MmParams p) {
     extern __shared__ __align__(16) float smem[];
     float* As = smem;
     float* Bs = smem + STAGES * SMEM_A;
@@ -754,16 +754,19 @@ inline bool use_packed() {
 template <int ALGO, bool FMA>
 int launch_mm(const MmParams& p, int64_t batch, bool vec, cudaStream_t st) {
     dim3 grid((unsigned)(((int64_t)p.N + BN - 1) / BN), (unsigned)(((int64_t)p.M + BM - 1) / BM), (unsigned)batch);
-    constexpr bool kHasFast = ALGO != ALGO_SR;       // the stochastic kernel has one form (scalar, both clamps)
+    // The stochastic kernel has one form (scalar, both clamps).  It interleaves many Philox chains per thread: one CTA
+    // per SM with twice the registers (no spills) is a few per cent faster than two.
+    constexpr bool kHasFast = ALGO != ALGO_SR;
+    constexpr int kMinB = ALGO == ALGO_SR ? 1 : MPT_MM_MIN_CTAS;
     const bool packed = kHasFast && use_packed();
     // the sum rounding needs its subnormal clamp only if products can carry bits below the add format's
     // smallest subnormal (always the case for a fused multiply-add, whose sum is not a sum of rounded values)
     const bool add_guard = FMA || !packed || (p.fmul.min_exp - p.fmul.man) < (p.fadd.min_exp - p.fadd.man);
     constexpr bool kCanDrop = kHasFast && !FMA;
-    auto kern = vec ? (packed ? (add_guard ? mm_kernel<ALGO, FMA, true, kHasFast, true> : mm_kernel<ALGO, FMA, true, kHasFast, !kCanDrop>)
-                              : mm_kernel<ALGO, FMA, true, false, true>)
-                    : (packed ? (add_guard ? mm_kernel<ALGO, FMA, false, kHasFast, true> : mm_kernel<ALGO, FMA, false, kHasFast, !kCanDrop>)
-                              : mm_kernel<ALGO, FMA, false, false, true>);
+    auto kern = vec ? (packed ? (add_guard ? mm_kernel<ALGO, FMA, true, kHasFast, true, false, kMinB> : mm_kernel<ALGO, FMA, true, kHasFast, !kCanDrop, false, kMinB>)
+                              : mm_kernel<ALGO, FMA, true, false, true, false, kMinB>)
+                    : (packed ? (add_guard ? mm_kernel<ALGO, FMA, false, kHasFast, true, false, kMinB> : mm_kernel<ALGO, FMA, false, kHasFast, !kCanDrop, false, kMinB>)
+                              : mm_kernel<ALGO, FMA, false, false, true, false, kMinB>);
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
     if (e != cudaSuccess) { set_error("float_mm: cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return MPT_ERR_CUDA; }
     kern<<<grid, THREADS, SMEM_BYTES, st>>>(p);

@@ -143,109 +143,135 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) layernorm_bwd_dx_kernel(c
 
 // Column sums in row order: out[c] = fold over rows r = 0..R-1 of Q(acc + v[r, c]), the association of both
 // references for the layernorm weight/bias gradients (layernorm_kernel.h:206-237, layernorm.h:100-103) and of
-// the qsum loop (functional.py:736-748).  The chain per column is serial by definition, so the kernel splits
-// the work by role: a CTA owns 32 columns; eight producer warps stream row tiles (64 rows x 32 columns,
-// coalesced 128-byte row segments), do the per-element arithmetic that does not depend on the running sum
-// (for layernorm: x-hat * dy, recomputed from the inputs instead of staged through the reference's scratch
-// tensor, fp_kernel.cu:481-487) and park the addends in shared memory; one consumer warp per chain (lane =
-// column) walks the parked tile in row order through the rounded adds, 32 rows per range check so that the
-// dependent adds run back to back.  Tiles are double buffered: the consumers work on tile t while the producers
-// fetch tile t + 1, with one barrier per tile.
-// A chain's speed is set by the latency of its dependent adds, not by how many columns share a CTA, so the tile
-// is narrow: 8 columns per CTA puts four times as many SMs to work on the per-element arithmetic of the producers
-// (a 32-byte sector per row and tensor).  A producer warp covers 4 rows x 8 columns per load.
-constexpr int kColTile = 8;         // columns per CTA
-constexpr int kRowTile = 64;        // rows per tile
-constexpr int kProducerWarps = 2;   // 32 rows of a tile each
-constexpr int kColsumThreads(int mode) { return (kProducerWarps + (mode == 0 ? 2 : 1)) * 32; }
+// the qsum loop (functional.py:736-748).  The chain per column is serial by definition: its time is (rows) x
+// (latency of one dependent rounded add, five back-to-back instructions), so everything that does not depend on the
+// running sum is taken off the warps that walk the chains.  A CTA owns 32 columns (lane = column).  Six producer
+// warps stream row groups (8 rows x 32 columns, coalesced 128-byte row segments), do the per-element arithmetic
+// (for layernorm: x-hat * dy, recomputed from the inputs instead of staged through the reference's scratch tensor,
+// fp_kernel.cu:481-487), park the addends in shared memory and record, per group and column, the largest addend and
+// whether a tiny one occurred: what the consumer needs to decide, with one compare per group, whether the group may
+// take the FP-pipe rounding.  One consumer warp per chain (two for layernorm: x-hat * dy and dy) carries its 32 columns
+// and executes, per row, one shared-memory load and the five dependent instructions (measured: about 56 cycles per row,
+// which is the floor of this formulation; two chains interleaved in one warp take 75).
+// Tiles of 128 rows are double buffered with one barrier per tile.
+constexpr int kChainCols = 32;        // columns per CTA
+constexpr int kChainGroup = 8;        // rows per range check
+constexpr int kChainTile = 128;       // rows per tile
+constexpr int kChainProducers = 6;
+constexpr int chain_threads(int mode) { return (kChainProducers + (mode == 0 ? 2 : 1)) * 32; }
+constexpr int kChainGroups = kChainTile / kChainGroup;
+constexpr size_t chain_smem_bytes(int mode) {
+    return (size_t)(mode == 0 ? 2 : 1) * 2 * (kChainTile + kChainGroups) * kChainCols * sizeof(float);
+}
+
+// |v| of a group folded into one float: the maximum, negated when some addend is nonzero and below 2^-101 (formats with
+// an 8-bit exponent round such values in their own way, see FullRn).
+__device__ __forceinline__ void group_note(float v, float& vmax, bool& tiny) {
+    vmax = fmaxf(vmax, fabsf(v));
+    tiny |= (__float_as_uint(v) & 0x7FFFFFFFu) - 1u < 0x0CFFFFFFu;
+}
 
 // MODE 0: layernorm parameter gradients (two chains: x-hat*dy -> out0, dy -> out1).  MODE 1: plain column sum of `in`.
-template <int MODE>
-__global__ void __launch_bounds__(kColsumThreads(MODE)) colsum_kernel(const float* __restrict__ in, const float* __restrict__ gout,
-                                                                const float* __restrict__ mean, const float* __restrict__ rstd,
-                                                                float* __restrict__ out0, float* __restrict__ out1, RowGeom g,
-                                                                Caster facc, Caster fmul, SeqAdder seq) {
-    __shared__ float sA[2][kRowTile][kColTile];
-    __shared__ float sB[MODE == 0 ? 2 : 1][MODE == 0 ? kRowTile : 1][kColTile];
+// LINE: both formats of the per-element arithmetic round on the FP pipe and have fewer than 8 exponent bits, so the
+// producers use the branch-free rounding and the eight elements of a group interleave.
+template <int MODE, bool LINE>
+__global__ void __launch_bounds__(chain_threads(MODE)) colsum_kernel(const float* __restrict__ in, const float* __restrict__ gout,
+                                                               const float* __restrict__ mean, const float* __restrict__ rstd,
+                                                               float* __restrict__ out0, float* __restrict__ out1, RowGeom g,
+                                                               Caster facc, Caster fmul, SeqAdder seq) {
+    extern __shared__ __align__(16) float chain_smem[];
+    // layout: addends A [2][tile][32], group notes A [2][groups][32], then the same for B (MODE 0)
+    float* sA = chain_smem;
+    float* nA = sA + 2 * kChainTile * kChainCols;
+    float* sB = nA + 2 * kChainGroups * kChainCols;
+    float* nB = sB + 2 * kChainTile * kChainCols;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int cl = lane & (kColTile - 1), rs = lane / kColTile;      // column within the tile, row within a 4-row group
-    const int col = blockIdx.x * kColTile + cl;
+    const int col = blockIdx.x * kChainCols + lane;
     const bool col_ok = col < g.channel;
     const int64_t st = g.inner;
-    const int64_t ntiles = (g.rows + kRowTile - 1) / kRowTile;
+    const int64_t ntiles = (g.rows + kChainTile - 1) / kChainTile;
 
-    // Producer warp w: rows 32 w .. 32 w + 31 of a tile, eight loads of 4 rows x 8 columns.  The loads of tile t + 2
-    // are issued before the arithmetic of tile t + 1, so a tile's memory latency hides behind the previous tile's work.
-    static_assert(kRowTile == 32 * kProducerWarps && kColTile == 8, "eight loads of 4 rows x 8 columns per producer warp");
-    struct Tile { float xv[8], gv[8], mv[8], rv[8]; };
-    auto load = [&](int64_t t, Tile& T) {
-        const int64_t r0 = t * kRowTile + warp * 32 + rs;
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-            const int64_t row = r0 + 4 * u;
-            const bool ok = col_ok && row < g.rows;
-            const int64_t idx = ok ? row_base(g, row) + col * st : 0;
-            T.xv[u] = ok ? in[idx] : 0.f;
-            if (MODE == 0) { T.gv[u] = ok ? gout[idx] : 0.f; T.mv[u] = ok ? mean[row] : 0.f; T.rv[u] = ok ? rstd[row] : 0.f; }
-        }
-    };
-    auto finish = [&](int64_t t, const Tile& T) {
+    // Producer warp w fills groups w, w + 7, ... of a tile.  All loads of a group are issued before its arithmetic.
+    auto produce = [&](int64_t t) {
         const int buf = (int)(t & 1);
+        for (int gi = warp; gi < kChainGroups; gi += kChainProducers) {
+            const int64_t r0 = t * kChainTile + gi * kChainGroup;
+            if (r0 >= g.rows) break;
+            float xv[kChainGroup], gv[kChainGroup], mv[kChainGroup], rv[kChainGroup];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
-            const int lr = warp * 32 + 4 * u + rs;
-            if (MODE == 0) {
-                const float xhat = fmul(__fmul_rn(facc(__fsub_rn(T.xv[u], T.mv[u])), T.rv[u]));
-                sA[buf][lr][cl] = fmul(__fmul_rn(xhat, T.gv[u]));
-                sB[buf][lr][cl] = T.gv[u];
-            } else {
-                sA[buf][lr][cl] = T.xv[u];
+            for (int u = 0; u < kChainGroup; ++u) {
+                const int64_t row = r0 + u;
+                const bool rok = row < g.rows, ok = rok && col_ok;
+                const int64_t idx = ok ? row_base(g, row) + col * st : 0;
+                xv[u] = ok ? in[idx] : 0.f;
+                if (MODE == 0) { gv[u] = ok ? gout[idx] : 0.f; mv[u] = rok ? mean[row] : 0.f; rv[u] = rok ? rstd[row] : 0.f; }
             }
+            float ma = 0.f, mb = 0.f;
+            bool ta = false, tb = false;
+#pragma unroll
+            for (int u = 0; u < kChainGroup; ++u) {
+                const int lr = gi * kChainGroup + u;
+                float a = xv[u];
+                if (MODE == 0) {
+                    if (LINE) {
+                        const float xhat = fmul.fast.line(__fmul_rn(facc.fast.line(__fsub_rn(xv[u], mv[u])), rv[u]));
+                        a = fmul.fast.line(__fmul_rn(xhat, gv[u]));
+                    } else {
+                        const float xhat = fmul(__fmul_rn(facc(__fsub_rn(xv[u], mv[u])), rv[u]));
+                        a = fmul(__fmul_rn(xhat, gv[u]));
+                    }
+                    sB[(buf * kChainTile + lr) * kChainCols + lane] = gv[u];
+                    group_note(gv[u], mb, tb);
+                }
+                sA[(buf * kChainTile + lr) * kChainCols + lane] = a;
+                group_note(a, ma, ta);
+            }
+            nA[(buf * kChainGroups + gi) * kChainCols + lane] = ta ? -ma : ma;
+            if (MODE == 0) nB[(buf * kChainGroups + gi) * kChainCols + lane] = tb ? -mb : mb;
         }
     };
 
+    // consumer warp `chain` (0: addends A into out0, 1: addends B into out1)
+    const int chain = warp - kChainProducers;
     float acc = 0.f;
-    const int chain = warp - kProducerWarps;          // consumer warps: 0 sums sA into out0, 1 sums sB into out1
-    Tile cur, nxt;
-    if (warp < kProducerWarps && ntiles > 0) {
-        load(0, cur);
-        if (ntiles > 1) load(1, nxt);
-        finish(0, cur);
-    }
+    if (warp < kChainProducers && ntiles > 0) produce(0);
     __syncthreads();
     for (int64_t t = 0; t < ntiles; ++t) {
-        if (warp < kProducerWarps) {
-            if (t + 1 < ntiles) {
-                cur = nxt;
-                if (t + 2 < ntiles) load(t + 2, nxt);
-                finish(t + 1, cur);
-            }
+        if (warp < kChainProducers) {
+            if (t + 1 < ntiles) produce(t + 1);
         } else {
             const int buf = (int)(t & 1);
-            const float (*src)[kColTile] = (MODE == 0 && chain == 1) ? sB[buf] : sA[buf];
-            const int64_t left = g.rows - t * kRowTile;
-            const int nrows = left < kRowTile ? (int)left : kRowTile;
-            int r = 0;
-            for (; r + 32 <= nrows; r += 32) {
-                float v[32];
+            const int64_t left = g.rows - t * kChainTile;
+            const int nrows = left < kChainTile ? (int)left : kChainTile;
+            const float* a = (chain == 0 ? sA : sB) + (size_t)buf * kChainTile * kChainCols + lane;
+            const float* notes = (chain == 0 ? nA : nB) + (size_t)buf * kChainGroups * kChainCols + lane;
+            int gi = 0;
+            for (; (gi + 1) * kChainGroup <= nrows; ++gi) {
+                float va[kChainGroup];
 #pragma unroll
-                for (int u = 0; u < 32; ++u) v[u] = src[r + u][cl];
-                acc = seq.add(acc, v);
+                for (int u = 0; u < kChainGroup; ++u) va[u] = a[(gi * kChainGroup + u) * kChainCols];
+                acc = seq.add_noted(acc, va, notes[gi * kChainCols]);
             }
-            for (; r + 8 <= nrows; r += 8) {
-                float v[8];
-#pragma unroll
-                for (int u = 0; u < 8; ++u) v[u] = src[r + u][cl];
-                acc = seq.add(acc, v);
-            }
-            for (; r < nrows; ++r) {
-                const float v[1] = {src[r][cl]};
+            for (int r = gi * kChainGroup; r < nrows; ++r) {
+                const float v[1] = {a[r * kChainCols]};
                 acc = seq.add(acc, v);
             }
         }
         __syncthreads();
     }
-    if (warp >= kProducerWarps && lane < kColTile && col_ok) (chain == 0 ? out0 : out1)[col] = acc;
+    if (warp >= kChainProducers && col_ok) (chain == 0 ? out0 : out1)[col] = acc;
+}
+
+template <int MODE>
+int launch_colsum(const float* in, const float* gout, const float* mean, const float* rstd, float* out0, float* out1, const RowGeom& g,
+                  const Caster& facc, const Caster& fmul, const SeqAdder& seq, cudaStream_t st, const char* who) {
+    const size_t smem = chain_smem_bytes(MODE);
+    const bool line = MODE == 0 && facc.use_fast && fmul.use_fast && facc.any.fp.exp < 8 && fmul.any.fp.exp < 8;
+    auto kern = line ? colsum_kernel<MODE, true> : colsum_kernel<MODE, false>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) { set_error("%s: cudaFuncSetAttribute: %s", who, cudaGetErrorString(e)); return MPT_ERR_CUDA; }
+    kern<<<(unsigned)((g.channel + kChainCols - 1) / kChainCols), chain_threads(MODE), smem, st>>>(in, gout, mean, rstd, out0, out1, g, facc, fmul, seq);
+    return check_launch(who);
 }
 
 int check_geom(const char* who, int64_t outer, int channel, int64_t inner) {
@@ -396,9 +422,8 @@ int mpt_layernorm_backward_fmt(const float* in, const float* grad_out, const flo
         rc = check_launch("layernorm_backward (input gradient)");
         if (rc) return rc;
     }
-    colsum_kernel<0><<<(channel + kColTile - 1) / kColTile, kColsumThreads(0), 0, as_stream(stream)>>>(in, grad_out, mean, rstd, grad_gamma, grad_beta, g,
-                                                                                               f.acc, f.mul, f.seq);
-    return check_launch("layernorm_backward (parameter gradients)");
+    return launch_colsum<0>(in, grad_out, mean, rstd, grad_gamma, grad_beta, g, f.acc, f.mul, f.seq, as_stream(stream),
+                            "layernorm_backward (parameter gradients)");
 }
 
 int mpt_float_softmax_forward(const float* in, float* out, int64_t outer, int channel, int64_t inner, int man_exp,
@@ -451,9 +476,8 @@ int mpt_qsum_rows(const float* in, float* out, int64_t rows, int64_t cols, int m
     const FpFmt f = make_fmt(man, exp, subnormals, saturate);
     MPT_REQUIRE(cols <= 0x7FFFFFFF, "qsum_rows: too many columns");
     const RowGeom g{rows, (int)cols, 1};      // a [rows, cols] matrix: outer = rows, channel = cols, inner = 1
-    colsum_kernel<1><<<(unsigned)((cols + kColTile - 1) / kColTile), kColsumThreads(1), 0, as_stream(stream)>>>(in, nullptr, nullptr, nullptr, out, nullptr, g,
-                                                                                                        Caster::make(f), Caster::make(f), SeqAdder::make(f));
-    return check_launch("qsum_rows");
+    return launch_colsum<1>(in, nullptr, nullptr, nullptr, out, nullptr, g, Caster::make(f), Caster::make(f), SeqAdder::make(f),
+                            as_stream(stream), "qsum_rows");
 }
 
 }

@@ -110,6 +110,23 @@ struct SeqAdder {
         }
         return acc;
     }
+    // The same with the group's largest |v| and its "tiny value present" flag precomputed (`note`: the maximum, negated
+    // when the flag is set), so that the warp walking the chain spends one compare per group on the decision.
+    __device__ __forceinline__ bool noted_fast(float acc, float note, int U) const {
+        const bool tiny = note < 0.f || (__float_as_uint(acc) & 0x7FFFFFFFu) - 1u < 0x0CFFFFFFu;
+        return chain_ok && (fabsf(acc) + (float)(2 * U) * fabsf(note)) * 1.0001f < top && !(exp8 && tiny);
+    }
+    template <int U>
+    __device__ __forceinline__ float add_noted(float acc, const float (&v)[U], float note) const {
+        if (noted_fast(acc, note, U)) {
+#pragma unroll
+            for (int u = 0; u < U; ++u) acc = r(__fadd_rn(acc, v[u]));
+        } else {
+#pragma unroll 1
+            for (int u = 0; u < U; ++u) acc = q(__fadd_rn(acc, v[u]));
+        }
+        return acc;
+    }
 };
 struct FMax {
     __device__ __forceinline__ float operator()(float a, float b) const { return fmaxf(a, b); }
