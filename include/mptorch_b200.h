@@ -279,17 +279,23 @@ enum { MPT_ELEM_E4M3 = 0, MPT_ELEM_E2M1 = 1 };   /* OCP element formats: max 448
 
 /* OCP MX: one E8M0 scale 2^(floor(log2 amax) - emax_elem) per `block` elements (32 for MXFP8 / MXFP4),
  * elements rounded to nearest even in `elem_format` with saturation.  `scales` (optional) receives the
- * E8M0 codes, [rows, ceil(cols / block)], 0xFF for a block holding NaN or infinity. */
-MPT_API int mpt_mx_quantize(const float *in, float *out, uint8_t *scales, int64_t rows, int64_t cols, int block,
-                            int elem_format, void *stream);
+ * E8M0 codes, [rows, ceil(cols / block)], 0xFF for a block holding NaN or infinity.  `codes` (optional)
+ * receives the packed elements: [rows, cols] bytes for E4M3, [rows, ceil(cols / 2)] bytes for E2M1 with
+ * element 2i in the low nibble (needs an even block size); a poisoned block writes 0x7F / 0. */
+MPT_API int mpt_mx_quantize(const float *in, float *out, uint8_t *scales, uint8_t *codes, int64_t rows, int64_t cols,
+                            int block, int elem_format, void *stream);
 
 /* NVFP4: E2M1 elements in blocks of 16, one E4M3 scale per block (optional output `block_scales`,
  * [rows, ceil(cols / 16)], as fp32 values) and one fp32 scale per tensor.  global_scale > 0 is used as
  * given; otherwise it is computed as amax(tensor) / (448 * 6), which needs 4 bytes of device
- * `workspace` and one extra read of the input.  `global_scale_out` (optional, device) receives the
- * scale that was used. */
-MPT_API int mpt_nvfp4_quantize(const float *in, float *out, float *block_scales, int64_t rows, int64_t cols,
-                               float global_scale, void *workspace, float *global_scale_out, void *stream);
+ * `workspace` and one extra read of the input; the maximum is taken over the finite entries.
+ * `global_scale_out` (optional, device) receives the scale that was used.  `codes` (optional): packed
+ * E2M1 elements, [rows, ceil(cols / 2)] bytes, element 2i in the low nibble; `scale_codes` (optional):
+ * the block scales as E4M3 bytes.  A NaN element stays NaN in `out` and is coded as 0 (E2M1 has no NaN);
+ * an infinite one saturates its block scale at 448 and itself at +-6. */
+MPT_API int mpt_nvfp4_quantize(const float *in, float *out, float *block_scales, uint8_t *codes, uint8_t *scale_codes,
+                               int64_t rows, int64_t cols, float global_scale, void *workspace,
+                               float *global_scale_out, void *stream);
 
 /* ---- quantized optimizer steps and tensor scaling -----------------------------------------------------
  * One launch updates many tensors in place (up to 40 per launch; more are split over launches).  The

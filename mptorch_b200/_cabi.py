@@ -85,8 +85,8 @@ def lib() -> C.CDLL:
             "mpt_qsgd_step": [p, i32, C.c_float, C.c_float, C.c_float, C.c_float] + [i32] * 10 + [p],
             "mpt_qadamw_step": [p, i32] + [C.c_float] * 7 + [i32] * 10 + [p],
             "mpt_scale_quantize": [p, p, i64, i64, C.c_double, i32, i32, i32, i32, i32, i32, p, p, sz, p],
-            "mpt_mx_quantize": [p, p, p, i64, i64, i32, i32, p],
-            "mpt_nvfp4_quantize": [p, p, p, i64, i64, C.c_float, p, p, p],
+            "mpt_mx_quantize": [p, p, p, p, i64, i64, i32, i32, p],
+            "mpt_nvfp4_quantize": [p, p, p, p, p, i64, i64, C.c_float, p, p, p],
         }
         for name, args in sig.items():
             fn = getattr(L, name, None)

@@ -35,17 +35,52 @@ class OverflowPolicy(enum.IntEnum):
 _ORDER = {"seq": 0, "cuda": 1, "tile8": 1, "tree64": 1}
 _state = {"accum_order": "cuda", "reduce_order": "cuda"}
 
+# Two routes lead from here to the C ABI: the PyTorch C++ extension `quant_b200` (mptorch_b200/torch_ext, the reference's
+# quant_cuda interface over the C ABI, a few microseconds less host time per call) when it has been built, and ctypes
+# otherwise.  Both call the same entry points of the same library.  MPT_BACKEND=ctypes (or =ext) forces one.
+_ext = None
+
+
+def _load_ext():
+    import os
+
+    global _ext
+    want = os.environ.get("MPT_BACKEND", "")
+    if want == "ctypes":
+        return
+    try:
+        from . import torch_ext
+
+        if want == "ext" or torch_ext.available():
+            _ext = torch_ext.load(build_if_missing=(want == "ext"))
+    except Exception:
+        if want == "ext":
+            raise
+        _ext = None
+
+
+_load_ext()
+
+
+def route() -> str:
+    """Which host layer the hot entry points go through: "ext" (the C++ extension) or "ctypes"."""
+    return "ext" if _ext is not None else "ctypes"
+
 
 def set_accum_order(order: str) -> None:
     if order not in _ORDER:
         raise ValueError("accum_order must be 'cuda' or 'seq'")
     _state["accum_order"] = order
+    if _ext is not None:
+        _ext.set_accum_order("seq" if _ORDER[order] == 0 else "cuda")
 
 
 def set_reduce_order(order: str) -> None:
     if order not in _ORDER:
         raise ValueError("reduce_order must be 'cuda' or 'seq'")
     _state["reduce_order"] = order
+    if _ext is not None:
+        _ext.set_reduce_order("seq" if _ORDER[order] == 0 else "cuda")
 
 
 def get_accum_order() -> str:
@@ -67,7 +102,8 @@ def orders(accum: str | None = None, reduce: str | None = None):
             set_reduce_order(reduce)
         yield
     finally:
-        _state.update(old)
+        set_accum_order(old["accum_order"])
+        set_reduce_order(old["reduce_order"])
 
 
 def _order_code(order: str | None, kind: str) -> int:
@@ -77,6 +113,8 @@ def _order_code(order: str | None, kind: str) -> int:
 # ---------------------------------------------------------------------------------- quantizers
 def float_quantize_nearest(a, man_bits, exp_bits, subnormals, saturate):
     """pybind_cuda.cpp:44."""
+    if _ext is not None:
+        return _ext.float_quantize_nearest(a, man_bits, exp_bits, subnormals, saturate)
     check_cuda_f32(a, "a")
     o = torch.empty_like(a)
     with torch.cuda.device(a.device):
@@ -190,6 +228,9 @@ def _batch_of(a) -> int:
 
 
 def _mm_nearest(a, b, c, batch, M, N, K, man_add, exp_add, man_mul, exp_mul, subnormals, saturate, compensated, order):
+    if _ext is not None and order is None and batch == _batch_of(a):
+        _ext.float_quantize_nearest_bmm(a, b, c, M, N, K, man_add, exp_add, man_mul, exp_mul, bool(subnormals), bool(saturate), bool(compensated))
+        return
     _mm_checks(a, b, c)
     with torch.cuda.device(a.device):
         ws = _cabi.mm_workspace(a.device, batch)
@@ -199,6 +240,9 @@ def _mm_nearest(a, b, c, batch, M, N, K, man_add, exp_add, man_mul, exp_mul, sub
 
 
 def _mm_nearest_fma(a, b, c, batch, M, N, K, man_fma, exp_fma, subnormals, saturate, compensated, order):
+    if _ext is not None and order is None and batch == _batch_of(a):
+        _ext.float_quantize_nearest_bmm_fma(a, b, c, M, N, K, man_fma, exp_fma, bool(subnormals), bool(saturate), bool(compensated))
+        return
     _mm_checks(a, b, c)
     with torch.cuda.device(a.device):
         ws = _cabi.mm_workspace(a.device, batch)
@@ -316,6 +360,9 @@ def partition_tensor(shape, dim):
 def float_quantize_nearest_softmax_forward(a, o, dim, man_exp, exp_exp, man_off, exp_off, man_acc, exp_acc, subnormals,
                                            saturate, order=None):
     """pybind_cuda.cpp:599."""
+    if _ext is not None and order is None and isinstance(dim, int):
+        _ext.float_quantize_nearest_softmax_forward(a, o, dim, man_exp, exp_exp, man_off, exp_off, man_acc, exp_acc, bool(subnormals), bool(saturate))
+        return
     check_cuda_f32(a, "a"); check_cuda_f32(o, "o")
     outer, ch, inner = partition_tensor(a.shape, dim)
     with torch.cuda.device(a.device):
@@ -336,6 +383,9 @@ def float_quantize_nearest_softmax_lse_forward(a, o, dim, man_off, exp_off, man_
 def float_quantize_nearest_softmax_backward(a, g, o, dim, man_add, exp_add, man_mul, exp_mul, subnormals, saturate,
                                             order=None):
     """pybind_cuda.cpp:629.  ``a`` is the softmax output, ``g`` the incoming gradient."""
+    if _ext is not None and order is None and isinstance(dim, int):
+        _ext.float_quantize_nearest_softmax_backward(a, g, o, dim, man_add, exp_add, man_mul, exp_mul, bool(subnormals), bool(saturate))
+        return
     check_cuda_f32(a, "a"); check_cuda_f32(g, "g"); check_cuda_f32(o, "o")
     outer, ch, inner = partition_tensor(a.shape, dim)
     with torch.cuda.device(a.device):
@@ -346,9 +396,13 @@ def float_quantize_nearest_softmax_backward(a, g, o, dim, man_add, exp_add, man_
 def float_quantize_layernorm_forward(input, weight, bias, output, mean, rstd, eps, dims, man_acc, exp_acc, man_mul,
                                      exp_mul, man_div, exp_div, man_sqrt, exp_sqrt, subnormals, saturate, order=None):
     """pybind_cuda.cpp:434."""
+    outer, ch, inner = partition_tensor(input.shape, list(dims))      # also refuses dimension lists the reference mishandles
+    if _ext is not None and order is None:
+        _ext.float_quantize_layernorm_forward(input, weight, bias, output, mean, rstd, float(eps), [int(d) for d in dims], man_acc, exp_acc,
+                                              man_mul, exp_mul, man_div, exp_div, man_sqrt, exp_sqrt, bool(subnormals), bool(saturate))
+        return
     for t, n in ((input, "input"), (weight, "weight"), (bias, "bias"), (output, "output"), (mean, "mean"), (rstd, "rstd")):
         check_cuda_f32(t, n)
-    outer, ch, inner = partition_tensor(input.shape, list(dims))
     with torch.cuda.device(input.device):
         call("mpt_float_layernorm_forward", ptr(input), ptr(weight), ptr(bias), ptr(output), ptr(mean), ptr(rstd),
              float(eps), outer, ch, inner, man_acc, exp_acc, man_mul, exp_mul, man_div, exp_div, man_sqrt, exp_sqrt,
@@ -359,10 +413,15 @@ def float_quantize_layernorm_backward(input, grad_output, weight, bias, mean, rs
                                       dims, man_acc, exp_acc, man_mul, exp_mul, man_div, exp_div, subnormals, saturate,
                                       order=None):
     """pybind_cuda.cpp:459 (``bias`` is accepted and unused, as in the reference)."""
+    outer, ch, inner = partition_tensor(input.shape, list(dims))
+    if _ext is not None and order is None:
+        _ext.float_quantize_layernorm_backward(input, grad_output, weight, bias if bias is not None else weight, mean, rstd, grad_input,
+                                               grad_gamma, grad_beta, [int(d) for d in dims], man_acc, exp_acc, man_mul, exp_mul, man_div,
+                                               exp_div, bool(subnormals), bool(saturate))
+        return
     for t, n in ((input, "input"), (grad_output, "grad_output"), (weight, "weight"), (mean, "mean"), (rstd, "rstd"),
                  (grad_input, "grad_input"), (grad_gamma, "grad_gamma"), (grad_beta, "grad_beta")):
         check_cuda_f32(t, n)
-    outer, ch, inner = partition_tensor(input.shape, list(dims))
     with torch.cuda.device(input.device):
         call("mpt_float_layernorm_backward", ptr(input), ptr(grad_output), ptr(weight), ptr(mean), ptr(rstd),
              ptr(grad_input), ptr(grad_gamma), ptr(grad_beta), outer, ch, inner, man_acc, exp_acc, man_mul, exp_mul,
@@ -372,6 +431,8 @@ def float_quantize_layernorm_backward(input, grad_output, weight, bias, mean, rs
 
 def qsum_rows(a, man_bits, exp_bits, subnormals, saturate):
     """New: sequential rounded sum over dim 0 of a 2-D tensor in one launch."""
+    if _ext is not None:
+        return _ext.qsum_rows(a, man_bits, exp_bits, bool(subnormals), bool(saturate))
     check_cuda_f32(a, "a")
     if a.dim() != 2:
         raise RuntimeError("qsum_rows expects a 2-D tensor")
@@ -562,32 +623,44 @@ def binary8_quantize_layernorm_backward(input, grad_output, weight, bias, mean, 
 _ELEM = {"e4m3": 0, "e2m1": 1}
 
 
-def mx_quantize(a, elem_format="e4m3", block=32, return_scales=False):
-    """OCP MX block quantization along the last dimension; returns the dequantized tensor (and the E8M0 codes)."""
+def mx_quantize(a, elem_format="e4m3", block=32, return_scales=False, return_codes=False):
+    """OCP MX block quantization along the last dimension; returns the dequantized tensor, then (on request) the E8M0
+    scale codes and the packed element codes (uint8: one byte per E4M3 element, two E2M1 elements per byte)."""
     check_cuda_f32(a, "a")
     if elem_format not in _ELEM:
         raise ValueError("elem_format must be 'e4m3' or 'e2m1'")
     cols = a.shape[-1] if a.dim() else 1
     rows = a.numel() // cols if cols else 0
     o = torch.empty_like(a)
-    sc = torch.empty(tuple(a.shape[:-1]) + ((cols + block - 1) // block,), dtype=torch.uint8, device=a.device) if return_scales else None
+    lead = tuple(a.shape[:-1])
+    sc = torch.empty(lead + ((cols + block - 1) // block,), dtype=torch.uint8, device=a.device) if return_scales else None
+    width = cols if elem_format == "e4m3" else (cols + 1) // 2
+    codes = torch.zeros(lead + (width,), dtype=torch.uint8, device=a.device) if return_codes else None
     with torch.cuda.device(a.device):
-        call("mpt_mx_quantize", ptr(a), ptr(o), ptr(sc), rows, cols, block, _ELEM[elem_format], stream_ptr(a.device))
-    return (o, sc) if return_scales else o
+        call("mpt_mx_quantize", ptr(a), ptr(o), ptr(sc), ptr(codes), rows, cols, block, _ELEM[elem_format], stream_ptr(a.device))
+    res = (o,) + ((sc,) if return_scales else ()) + ((codes,) if return_codes else ())
+    return res if len(res) > 1 else o
 
 
-def nvfp4_quantize(a, global_scale=None, return_scales=False):
-    """NVFP4 quantization along the last dimension; returns the dequantized tensor (and block scales, tensor scale)."""
+def nvfp4_quantize(a, global_scale=None, return_scales=False, return_codes=False):
+    """NVFP4 quantization along the last dimension; returns the dequantized tensor, then (``return_scales``) the block
+    scales as fp32 and the tensor scale, then (``return_codes``) the packed E2M1 codes and the E4M3 scale bytes."""
     check_cuda_f32(a, "a")
     cols = a.shape[-1] if a.dim() else 1
     rows = a.numel() // cols if cols else 0
     o = torch.empty_like(a)
-    sc = torch.empty(tuple(a.shape[:-1]) + ((cols + 15) // 16,), device=a.device) if return_scales else None
+    lead = tuple(a.shape[:-1])
+    nblk = (cols + 15) // 16
+    sc = torch.empty(lead + (nblk,), device=a.device) if return_scales else None
     gs_out = torch.empty(1, device=a.device) if return_scales else None
+    codes = torch.zeros(lead + ((cols + 1) // 2,), dtype=torch.uint8, device=a.device) if return_codes else None
+    scodes = torch.empty(lead + (nblk,), dtype=torch.uint8, device=a.device) if return_codes else None
     ws = None
     gs = float(global_scale) if global_scale is not None else 0.0
     if not gs > 0.0:
         ws = torch.empty(1, dtype=torch.int32, device=a.device)
     with torch.cuda.device(a.device):
-        call("mpt_nvfp4_quantize", ptr(a), ptr(o), ptr(sc), rows, cols, gs, ptr(ws), ptr(gs_out), stream_ptr(a.device))
-    return (o, sc, gs_out) if return_scales else o
+        call("mpt_nvfp4_quantize", ptr(a), ptr(o), ptr(sc), ptr(codes), ptr(scodes), rows, cols, gs, ptr(ws), ptr(gs_out),
+             stream_ptr(a.device))
+    res = (o,) + ((sc, gs_out) if return_scales else ()) + ((codes, scodes) if return_codes else ())
+    return res if len(res) > 1 else o

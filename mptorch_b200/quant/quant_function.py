@@ -147,24 +147,27 @@ def superfp_quantize(x: torch.Tensor, exp: int, man: int, binades, rounding: Lit
 
 
 def mx_quantize(x: torch.Tensor, elem_format: Literal["e4m3", "e2m1"] = "e4m3", block: int = 32,
-                return_scales: bool = False):
+                return_scales: bool = False, return_codes: bool = False):
     """OCP Microscaling block quantization along the last dimension (new; the reference has none).
 
     Every ``block`` consecutive elements share one power-of-two scale 2^(floor(log2 amax) - emax) stored as
     E8M0; elements are rounded to nearest even into OCP E4M3 (MXFP8, max 448) or E2M1 (MXFP4, max 6) with
-    saturation.  Returns the dequantized fp32 tensor, plus the uint8 scale codes with ``return_scales``.
-    Note these OCP element formats differ from ``float_quantize(exp=4, man=3)``, which reserves the top
-    exponent and tops out at 240."""
+    saturation.  Returns the dequantized fp32 tensor, plus the uint8 scale codes with ``return_scales`` and the
+    packed element codes with ``return_codes`` (uint8: a byte per E4M3 element; two E2M1 elements per byte, the
+    even one in the low nibble).  Note these OCP element formats differ from ``float_quantize(exp=4, man=3)``,
+    which reserves the top exponent and tops out at 240."""
     _require_cuda(x, "mx_quantize")
-    return _be.mx_quantize(_f32c(x), elem_format, block, return_scales)
+    return _be.mx_quantize(_f32c(x), elem_format, block, return_scales, return_codes)
 
 
-def nvfp4_quantize(x: torch.Tensor, global_scale: float | None = None, return_scales: bool = False):
+def nvfp4_quantize(x: torch.Tensor, global_scale: float | None = None, return_scales: bool = False,
+                   return_codes: bool = False):
     """NVFP4 quantization along the last dimension (new): E2M1 elements in blocks of 16, an E4M3 scale per
-    block and one fp32 scale per tensor (``amax / (448 * 6)`` unless given).  Returns the dequantized tensor,
-    plus (block scales, tensor scale) with ``return_scales``."""
+    block and one fp32 scale per tensor (``amax / (448 * 6)`` over the finite entries unless given).  Returns the
+    dequantized tensor, plus (block scales, tensor scale) with ``return_scales`` and (packed E2M1 codes, E4M3 scale
+    bytes) with ``return_codes``."""
     _require_cuda(x, "nvfp4_quantize")
-    return _be.nvfp4_quantize(_f32c(x), global_scale, return_scales)
+    return _be.nvfp4_quantize(_f32c(x), global_scale, return_scales, return_codes)
 
 
 def fixed_point_quantize(*args, **kwargs):

@@ -41,6 +41,12 @@ def build(verbose: bool = False) -> str:
     return _SO
 
 
+def available() -> bool:
+    """True when the extension has been built and is not older than its source."""
+    src = os.path.join(_HERE, "quant_b200.cpp")
+    return os.path.exists(_SO) and os.path.getmtime(_SO) >= os.path.getmtime(src)
+
+
 def load(build_if_missing: bool = True):
     src = os.path.join(_HERE, "quant_b200.cpp")
     if not os.path.exists(_SO) or os.path.getmtime(_SO) < os.path.getmtime(src):

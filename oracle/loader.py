@@ -214,24 +214,42 @@ def layernorm_backward(x, g, w, mean, rstd, dims, man_acc, exp_acc, man_mul, exp
     return gin, gg, gb
 
 
-def mx_quantize(x, elem="e4m3", block=32):
+def mx_quantize(x, elem="e4m3", block=32, return_codes=False):
     x = _f32(x)
     rows = int(np.prod(x.shape[:-1], dtype=np.int64))
     cols = x.shape[-1]
     o = np.empty_like(x)
     sc = np.zeros((rows, (cols + block - 1) // block), dtype=np.uint8)
-    lib().orc_mx_quantize(_ptr(x), _ptr(o), _ptr(sc), rows, cols, block, {"e4m3": 0, "e2m1": 1}[elem])
-    return o, sc.reshape(x.shape[:-1] + (sc.shape[1],))
+    kind = {"e4m3": 0, "e2m1": 1}[elem]
+    if not return_codes:
+        lib().orc_mx_quantize(_ptr(x), _ptr(o), _ptr(sc), rows, cols, block, kind)
+        return o, sc.reshape(x.shape[:-1] + (sc.shape[1],))
+    width = cols if kind == 0 else (cols + 1) // 2
+    codes = np.zeros((rows, width), dtype=np.uint8)
+    L = lib()
+    L.orc_mx_quantize_codes.restype = None
+    L.orc_mx_quantize_codes.argtypes = [C.c_void_p] * 4 + [C.c_int64, C.c_int64, C.c_int, C.c_int]
+    L.orc_mx_quantize_codes(_ptr(x), _ptr(o), _ptr(sc), _ptr(codes), rows, cols, block, kind)
+    return o, sc.reshape(x.shape[:-1] + (sc.shape[1],)), codes.reshape(x.shape[:-1] + (width,))
 
 
-def nvfp4_quantize(x, global_scale=0.0):
+def nvfp4_quantize(x, global_scale=0.0, return_codes=False):
     x = _f32(x)
     rows = int(np.prod(x.shape[:-1], dtype=np.int64))
     cols = x.shape[-1]
     o = np.empty_like(x)
     sc = np.zeros((rows, (cols + 15) // 16), dtype=np.float32)
-    sg = lib().orc_nvfp4_quantize(_ptr(x), _ptr(o), _ptr(sc), rows, cols, float(global_scale))
-    return o, sc.reshape(x.shape[:-1] + (sc.shape[1],)), sg
+    if not return_codes:
+        sg = lib().orc_nvfp4_quantize(_ptr(x), _ptr(o), _ptr(sc), rows, cols, float(global_scale))
+        return o, sc.reshape(x.shape[:-1] + (sc.shape[1],)), sg
+    codes = np.zeros((rows, (cols + 1) // 2), dtype=np.uint8)
+    scodes = np.zeros_like(sc, dtype=np.uint8)
+    L = lib()
+    L.orc_nvfp4_quantize_codes.restype = C.c_float
+    L.orc_nvfp4_quantize_codes.argtypes = [C.c_void_p] * 5 + [C.c_int64, C.c_int64, C.c_float]
+    sg = L.orc_nvfp4_quantize_codes(_ptr(x), _ptr(o), _ptr(sc), _ptr(codes), _ptr(scodes), rows, cols, float(global_scale))
+    lead = x.shape[:-1]
+    return o, sc.reshape(lead + (sc.shape[1],)), sg, codes.reshape(lead + (codes.shape[1],)), scodes.reshape(lead + (sc.shape[1],))
 
 
 def qsum_rows(x, man, exp, subnormals=True, saturate=False):

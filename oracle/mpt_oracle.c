@@ -823,14 +823,48 @@ static float ocp_elem_rne(float v, int exp_e, int man_e, float emax_val)
     return u2f(sign | f2u(r));
 }
 
+/* Bit code of a value that is exactly representable in the OCP element format (sign, exp_e exponent bits with bias
+ * 2^(exp_e-1)-1, man_e mantissa bits; subnormals below the smallest normal).  NaN: 0x7F for E4M3 (S.1111.111), 0 for
+ * E2M1, which has no NaN. */
+static uint8_t ocp_elem_code(float q, int exp_e, int man_e)
+{
+    if (q != q) return exp_e == 4 ? 0x7F : 0;
+    uint32_t t = f2u(q);
+    uint8_t sign = (uint8_t)((t >> 31) << (exp_e + man_e));
+    float a = fabsf(q);
+    int bias = (1 << (exp_e - 1)) - 1;
+    int min_exp = 1 - bias;
+    if (a < ldexpf(1.0f, min_exp)) return sign | (uint8_t)(a * ldexpf(1.0f, man_e - min_exp));   /* subnormal: a / 2^(min_exp-man) */
+    int E = (int)((t << 1) >> 24) - 127;
+    uint32_t man = (t & 0x7FFFFFu) >> (23 - man_e);
+    return sign | (uint8_t)(((E + bias) << man_e) | man);
+}
+
 /* MX block quantize along the last (contiguous) dimension.
  * Shared scale: e = floor(log2(amax)) - emax_elem, clamped to [-127,127],
  * stored as E8M0 code e+127.  amax == 0 -> code 0 (scale 2^-127), block all 0.
  * A block holding NaN or inf gets code 0xFF and every output NaN.
  * Elements: RNE(v * 2^-e) in the element format, saturating; out = elem * 2^e.
- * elem_kind: 0 = E4M3 (emax_elem 8, max 448), 1 = E2M1 (emax_elem 2, max 6). */
+ * elem_kind: 0 = E4M3 (emax_elem 8, max 448), 1 = E2M1 (emax_elem 2, max 6).
+ * codes (optional): the element codes, one byte per element for E4M3, two elements per byte for E2M1 (element 2i
+ * in the low nibble; a row occupies ceil(cols / 2) bytes).  A poisoned block writes 0x7F (E4M3) or 0 (E2M1). */
+ORC_API void orc_mx_quantize_codes(const float *in, float *out, uint8_t *scales, uint8_t *codes, int64_t rows, int64_t cols,
+                                   int block, int elem_kind);
 ORC_API void orc_mx_quantize(const float *in, float *out, uint8_t *scales, int64_t rows, int64_t cols,
                              int block, int elem_kind)
+{
+    orc_mx_quantize_codes(in, out, scales, NULL, rows, cols, block, elem_kind);
+}
+static void put_code(uint8_t *codes, int64_t r, int64_t c, int64_t cols, int fp4, uint8_t code)
+{
+    if (!codes) return;
+    if (!fp4) { codes[r * cols + c] = code; return; }
+    uint8_t *b = codes + r * ((cols + 1) / 2) + c / 2;
+    if (c & 1) *b = (uint8_t)((*b & 0x0F) | (code << 4));
+    else *b = (uint8_t)((*b & 0xF0) | (code & 0x0F));
+}
+ORC_API void orc_mx_quantize_codes(const float *in, float *out, uint8_t *scales, uint8_t *codes, int64_t rows, int64_t cols,
+                                   int block, int elem_kind)
 {
     int exp_e = elem_kind == 0 ? 4 : 2, man_e = elem_kind == 0 ? 3 : 1;
     int emax_elem = elem_kind == 0 ? 8 : 2;
@@ -847,7 +881,10 @@ ORC_API void orc_mx_quantize(const float *in, float *out, uint8_t *scales, int64
             uint8_t code;
             if (amax_bits >= 0x7F800000u) {
                 code = 0xFF;
-                for (int64_t c = c0; c < c1; ++c) out[r * cols + c] = NAN;
+                for (int64_t c = c0; c < c1; ++c) {
+                    out[r * cols + c] = NAN;
+                    put_code(codes, r, c, cols, elem_kind == 1, elem_kind == 0 ? 0x7F : 0);
+                }
             } else {
                 int e;
                 if (amax_bits == 0) e = -127;
@@ -868,6 +905,7 @@ ORC_API void orc_mx_quantize(const float *in, float *out, uint8_t *scales, int64
                     float v = ldexpf(ldexpf(in[r * cols + c], -e / 2), -(e - e / 2));
                     float q = ocp_elem_rne(v, exp_e, man_e, emax_val);
                     out[r * cols + c] = ldexpf(ldexpf(q, e / 2), e - e / 2);
+                    put_code(codes, r, c, cols, elem_kind == 1, ocp_elem_code(q, exp_e, man_e));
                 }
             }
             if (scales) scales[r * nblk + bidx] = code;
@@ -878,16 +916,29 @@ ORC_API void orc_mx_quantize(const float *in, float *out, uint8_t *scales, int64
  * "fn", max 448) scale per block and one fp32 global scale s_g.
  *   s_b  = RNE_E4M3(amax_block / (6 * s_g))        (true fp32 divisions)
  *   elem = RNE_E2M1(v / (s_b * s_g)), saturating at +-6;   out = elem * (s_b * s_g)
- * s_b == 0 -> block outputs 0.  If global_scale <= 0 it is computed as
- * amax_tensor / (448 * 6) (1.0 for an all-zero tensor).                     */
+ * s_b == 0 -> block outputs 0, except that a NaN element stays NaN.  If
+ * global_scale <= 0 it is computed as amax_tensor / (448 * 6) over the FINITE
+ * entries (1.0 when there is none above zero): infinities and NaN do not
+ * take part.  Within a block NaN entries are skipped by the maximum, an
+ * infinite one saturates its block scale at 448 and itself at +-6.
+ * codes (optional): E2M1 element codes, two per byte (element 2i in the low
+ * nibble, ceil(cols / 2) bytes per row; a NaN element is coded as 0, E2M1
+ * has no NaN); scale_codes (optional): the block scales as E4M3 bytes.    */
+ORC_API float orc_nvfp4_quantize_codes(const float *in, float *out, float *block_scales, uint8_t *codes, uint8_t *scale_codes,
+                                       int64_t rows, int64_t cols, float global_scale);
 ORC_API float orc_nvfp4_quantize(const float *in, float *out, float *block_scales, int64_t rows, int64_t cols,
                                  float global_scale)
+{
+    return orc_nvfp4_quantize_codes(in, out, block_scales, NULL, NULL, rows, cols, global_scale);
+}
+ORC_API float orc_nvfp4_quantize_codes(const float *in, float *out, float *block_scales, uint8_t *codes, uint8_t *scale_codes,
+                                       int64_t rows, int64_t cols, float global_scale)
 {
     const int block = 16;
     float sg = global_scale;
     if (!(sg > 0.f)) {
         float amax = 0.f;
-        for (int64_t i = 0; i < rows * cols; ++i) { float a = fabsf(in[i]); if (a > amax) amax = a; }
+        for (int64_t i = 0; i < rows * cols; ++i) { float a = fabsf(in[i]); if (a > amax && a < INFINITY) amax = a; }
         sg = amax > 0.f ? amax / (448.0f * 6.0f) : 1.0f;
     }
     int64_t nblk = (cols + block - 1) / block;
@@ -901,11 +952,14 @@ ORC_API float orc_nvfp4_quantize(const float *in, float *out, float *block_scale
             float sb = ocp_elem_rne(ratio, 4, 3, 448.0f);
             volatile float sc = sb * sg;
             if (block_scales) block_scales[r * nblk + bidx] = sb;
+            if (scale_codes) scale_codes[r * nblk + bidx] = ocp_elem_code(sb, 4, 3);
             for (int64_t c = c0; c < c1; ++c) {
-                if (sc == 0.f) { out[r * cols + c] = 0.f; continue; }
-                volatile float v = in[r * cols + c] / sc;
+                float x = in[r * cols + c];
+                if (sc == 0.f) { out[r * cols + c] = (x != x) ? x : 0.f; put_code(codes, r, c, cols, 1, 0); continue; }
+                volatile float v = x / sc;
                 volatile float q = ocp_elem_rne(v, 2, 1, 6.0f);
                 out[r * cols + c] = q * sc;
+                put_code(codes, r, c, cols, 1, ocp_elem_code(q, 2, 1));
             }
         }
     return sg;

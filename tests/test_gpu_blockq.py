@@ -87,3 +87,36 @@ def test_config3_full_size_properties(q, oracle):
     want, wsb, _ = oracle.nvfp4_quantize(x[rows].cpu().numpy(), float(sg.item()))
     assert same_bits(y[rows].cpu().numpy(), want)
     assert abs(sg.item() - sgv) <= 1e-6 * sgv
+
+
+@pytest.mark.parametrize("elem", ["e4m3", "e2m1"])
+@pytest.mark.parametrize("shape,block", [((64, 1024), 32), ((3, 5, 96), 32), ((16, 256), 16), ((7, 100), 32), ((5, 34), 8)])
+def test_mx_packed_codes(q, oracle, elem, shape, block):
+    """The packed element codes (a byte per E4M3 element, two E2M1 elements per byte) equal the oracle's, whose
+    encoding is checked against ml_dtypes on the CPU."""
+    x = data(int(np.prod(shape[:-1])), shape[-1], 6).reshape(shape)
+    if shape == (64, 1024):
+        x = specials(x)
+    got, sc, codes = q.mx_quantize(dev(x), elem, block, return_scales=True, return_codes=True)
+    want, wsc, wcodes = oracle.mx_quantize(x, elem, block, return_codes=True)
+    assert same_bits(got.cpu().numpy(), want) and np.array_equal(sc.cpu().numpy(), wsc)
+    assert codes.dtype == torch.uint8 and np.array_equal(codes.cpu().numpy(), wcodes)
+
+
+@pytest.mark.parametrize("shape", [(64, 1024), (3, 5, 96), (7, 100), (1, 16), (9, 24)])
+def test_nvfp4_packed_codes_and_nan_rules(q, oracle, shape):
+    x = data(int(np.prod(shape[:-1])), shape[-1], 7).reshape(shape)
+    got, sb, sg, codes, scodes = q.nvfp4_quantize(dev(x), None, return_scales=True, return_codes=True)
+    want, wsb, wsg, wcodes, wscodes = oracle.nvfp4_quantize(x, 0.0, return_codes=True)
+    assert same_bits(got.cpu().numpy(), want) and same_bits(sb.cpu().numpy(), wsb)
+    assert np.array_equal(codes.cpu().numpy(), wcodes) and np.array_equal(scodes.cpu().numpy(), wscodes)
+    # a NaN in an otherwise zero block stays NaN; infinities and NaN do not take part in the tensor scale
+    z = np.zeros((4, 64), dtype=np.float32)
+    z[1, 3] = np.nan
+    z[2, 20] = np.inf
+    z[3, 5] = 3.0
+    got, sb, sg = q.nvfp4_quantize(dev(z), None, return_scales=True)
+    want, wsb, wsg = oracle.nvfp4_quantize(z)
+    g = got.cpu().numpy()
+    assert np.float32(sg.item()) == np.float32(wsg) == np.float32(3.0 / (448.0 * 6.0))
+    assert same_bits(g, want) and np.isnan(g[1, 3]) and g[3, 5] == 3.0 and np.isfinite(g[2, 20])

@@ -64,3 +64,27 @@ def test_nvfp4_matches_ml_dtypes_casts(oracle):
     assert np.array_equal(q.reshape(8, 8, 16), want)
     q2, _, sg2 = oracle.nvfp4_quantize(x, global_scale=0.01)
     assert sg2 == np.float32(0.01) and np.all(np.abs(q2) <= 6 * 448 * 0.01 * 1.001)
+
+
+def test_packed_codes_decode_with_ml_dtypes(oracle):
+    """The packed element and scale codes decode, with ml_dtypes' own types, to the dequantized output."""
+    x = data(8, 128, 3)
+    for elem, dt in (("e4m3", ml_dtypes.float8_e4m3fn), ("e2m1", ml_dtypes.float4_e2m1fn)):
+        q, sc, codes = oracle.mx_quantize(x, elem, 32, return_codes=True)
+        if elem == "e4m3":
+            vals = codes.view(dt).astype(np.float32)
+        else:
+            vals = np.stack([codes & 0xF, codes >> 4], -1).reshape(8, 128).astype(np.uint8).view(dt).astype(np.float32)
+        scale = np.ldexp(1.0, sc.astype(np.int32) - 127).astype(np.float32)
+        assert np.array_equal((vals.reshape(8, 4, 32) * scale[..., None]).reshape(8, 128), q)
+    q, sb, sg, codes, scodes = oracle.nvfp4_quantize(x, 0.0, return_codes=True)
+    vals = np.stack([codes & 0xF, codes >> 4], -1).reshape(8, 128).astype(np.uint8).view(ml_dtypes.float4_e2m1fn).astype(np.float32)
+    assert np.array_equal(scodes.view(ml_dtypes.float8_e4m3fn).astype(np.float32), sb)
+    assert np.array_equal((vals.reshape(8, 8, 16) * (sb * np.float32(sg))[..., None]).reshape(8, 128).astype(np.float32), q)
+    # NaN handling of NVFP4: kept in a zero block, skipped by the tensor scale
+    z = np.zeros((2, 32), dtype=np.float32)
+    z[0, 3] = np.nan
+    z[1, 7] = np.inf
+    z[1, 9] = 2.0
+    q, sb, sg = oracle.nvfp4_quantize(z)
+    assert np.isnan(q[0, 3]) and np.all(q[0, :3] == 0) and sg == np.float32(2.0 / (448.0 * 6.0)) and q[1, 9] == 2.0
