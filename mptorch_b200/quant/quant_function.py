@@ -233,6 +233,14 @@ def quantizer(forward_number: Number | None = None, backward_number: Number | No
 def _mm_dispatch(a2, b2, batched, man_add, exp_add, man_mul, exp_mul, rounding, fma, subnormals, saturate,
                  compensated, rbits_add, rbits_mul):
     """One (possibly batched) GEMM on contiguous fp32 operands; allocates and returns C."""
+    # The kernel's CTA tile is 128 rows by 64 columns: a product with at most 64 rows and many columns would leave half of
+    # every tile idle.  C^T = B^T A^T has the same products (multiplication commutes exactly) accumulated in the same
+    # K order, so the transposed problem gives the same bits with full tiles; the result comes back as a transposed view.
+    # (Not for stochastic rounding: its random words are keyed by the position of the output in C.)
+    if rounding == "nearest" and a2.shape[-2] <= 64 and b2.shape[-1] >= 256 and a2.shape[-1] >= 128:
+        ct = _mm_dispatch(b2.transpose(-2, -1).contiguous(), a2.transpose(-2, -1).contiguous(), batched, man_add, exp_add, man_mul,
+                          exp_mul, rounding, fma, subnormals, saturate, compensated, rbits_add, rbits_mul)
+        return ct.transpose(-2, -1)
     if batched:
         Bn, M, K = a2.shape
         N = b2.shape[2]

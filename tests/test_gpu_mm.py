@@ -331,6 +331,32 @@ def test_full_size_row_samples_and_sharding(be, oracle, fmts):
         assert same_bits(c[rows[:2]].cpu().numpy(), want)
 
 
+def test_short_wide_products_equal_the_backend_call(be):
+    """float_mm / float_bmm compute products with at most 64 rows and many columns as the transposed problem (full CTA
+    tiles); the bits must equal the direct backend call, for both accumulation orders, plain, fused and compensated."""
+    import mptorch_b200.quant as q
+
+    g = torch.Generator(device="cuda").manual_seed(31)
+    a = torch.randn(3, 64, 200, device="cuda", generator=g)
+    b = torch.randn(3, 200, 320, device="cuda", generator=g)
+    for order in ("cuda", "seq"):
+        with q.orders(accum=order):
+            for fma in (False, True):
+                for comp in (False, True):
+                    got = q.float_bmm(a, b, man_add=10, exp_add=5, man_mul=3, exp_mul=4, rounding="nearest", fma=fma, subnormals=True,
+                                      saturate=False, compensated=comp)
+                    want = torch.empty(3, 64, 320, device="cuda")
+                    if fma:
+                        be.float_quantize_nearest_bmm_fma(a, b, want, 64, 320, 200, 10, 5, True, False, comp, order=order)
+                    else:
+                        be.float_quantize_nearest_bmm(a, b, want, 64, 320, 200, 10, 5, 3, 4, True, False, comp, order=order)
+                    assert got.shape == want.shape and torch.equal(got.contiguous().view(torch.int32), want.view(torch.int32)), (order, fma, comp)
+    got = q.float_mm(a[0, :17].contiguous(), b[0], man_add=2, exp_add=5, man_mul=2, exp_mul=5, rounding="nearest", fma=False, subnormals=True, saturate=False)
+    want = torch.empty(17, 320, device="cuda")
+    be.float_quantize_nearest_mm(a[0, :17].contiguous(), b[0], want, 17, 320, 200, 2, 5, 2, 5, True, False, False)
+    assert torch.equal(got.contiguous().view(torch.int32), want.view(torch.int32))
+
+
 def test_streamed_host_operands_equal_one_call():
     """float_mm_streamed (host operands, row blocks overlapped with the copies) gives the bits of one float_mm call."""
     import mptorch_b200.quant as q
