@@ -76,7 +76,8 @@ __device__ __forceinline__ float pow2f(int e) {   // 2^e for e in [-127, 127]
 
 // ---- MX -------------------------------------------------------------------------------------
 // LANES lanes (each with 4 consecutive elements) share one block of 4 * LANES elements.
-template <int LANES>
+// CODES: the packed element codes are wanted too (a launch without them carries none of that arithmetic).
+template <int LANES, bool CODES>
 __global__ void __launch_bounds__(kThreads) mx_kernel(const float4* __restrict__ in, float4* __restrict__ out,
                                                       uint8_t* __restrict__ scales, uint8_t* __restrict__ codes, int fp4,
                                                       int64_t nvec, ElemFmt ef, int emax_elem) {
@@ -92,12 +93,12 @@ __global__ void __launch_bounds__(kThreads) mx_kernel(const float4* __restrict__
         for (int off = LANES / 2; off > 0; off >>= 1) amax = max(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, off));
         float4 y;
         uint8_t code;
-        uint32_t packed;                      // the four element codes: a byte each (E4M3) or a nibble each (E2M1)
+        uint32_t packed = 0u;                 // the four element codes: a byte each (E4M3) or a nibble each (E2M1)
         if (amax >= 0x7F800000u) {            // a NaN or an infinity poisons the block
             code = 0xFF;
             const float nanv = __uint_as_float(0x7FC00000u);
             y = make_float4(nanv, nanv, nanv, nanv);
-            packed = fp4 ? 0u : 0x7F7F7F7Fu;
+            if (CODES) packed = fp4 ? 0u : 0x7F7F7F7Fu;
         } else {
             int e = -127;
             if (amax != 0u) {
@@ -112,7 +113,7 @@ __global__ void __launch_bounds__(kThreads) mx_kernel(const float4* __restrict__
             y.y = __fmul_rn(q1, up);
             y.z = __fmul_rn(q2, up);
             y.w = __fmul_rn(q3, up);
-            if (codes != nullptr) {
+            if (CODES) {
                 const int w = fp4 ? 4 : 8;
                 packed = ef.code(q0) | (ef.code(q1) << w) | (ef.code(q2) << (2 * w)) | (ef.code(q3) << (3 * w));
             }
@@ -120,7 +121,7 @@ __global__ void __launch_bounds__(kThreads) mx_kernel(const float4* __restrict__
         if (live) {
             __stcs(out + v, y);
             if (scales != nullptr && (v % LANES) == 0) scales[v / LANES] = code;
-            if (codes != nullptr) {
+            if (CODES) {
                 if (fp4) reinterpret_cast<uint16_t*>(codes)[v] = (uint16_t)packed;
                 else reinterpret_cast<uint32_t*>(codes)[v] = packed;
             }
@@ -194,14 +195,17 @@ __device__ __forceinline__ float nvfp4_global_scale(float given, const uint32_t*
     return amax > 0.f ? __fdiv_rn(amax, 448.0f * 6.0f) : 1.0f;
 }
 
-// Dequantized value of one element; `code` receives its E2M1 bits.  A zero block scale yields zeros, but a NaN stays NaN.
+// Dequantized value of one element; with CODES, `code` receives its E2M1 bits.  A zero block scale yields zeros, but a
+// NaN stays NaN.
+template <bool CODES>
 __device__ __forceinline__ float nvfp4_elem(float x, float sc, const ElemFmt& e2m1, uint32_t& code) {
     if (sc == 0.f) { code = 0u; return (x != x) ? x : 0.f; }
     const float q = e2m1.round(__fdiv_rn(x, sc));
-    code = e2m1.code(q);
+    if (CODES) code = e2m1.code(q);
     return __fmul_rn(q, sc);
 }
 
+template <bool CODES>
 __global__ void __launch_bounds__(kThreads) nvfp4_kernel(const float4* __restrict__ in, float4* __restrict__ out,
                                                          float* __restrict__ block_scales, uint8_t* __restrict__ codes,
                                                          uint8_t* __restrict__ scale_codes, int64_t nvec, float given_scale,
@@ -220,14 +224,14 @@ __global__ void __launch_bounds__(kThreads) nvfp4_kernel(const float4* __restric
         const float sb = f.e4m3.round(__fdiv_rn(amax, denom));
         const float sc = __fmul_rn(sb, sg);
         if (live) {
-            uint32_t c0, c1, c2, c3;
-            const float4 y = make_float4(nvfp4_elem(x.x, sc, f.e2m1, c0), nvfp4_elem(x.y, sc, f.e2m1, c1),
-                                         nvfp4_elem(x.z, sc, f.e2m1, c2), nvfp4_elem(x.w, sc, f.e2m1, c3));
+            uint32_t c0 = 0u, c1 = 0u, c2 = 0u, c3 = 0u;
+            const float4 y = make_float4(nvfp4_elem<CODES>(x.x, sc, f.e2m1, c0), nvfp4_elem<CODES>(x.y, sc, f.e2m1, c1),
+                                         nvfp4_elem<CODES>(x.z, sc, f.e2m1, c2), nvfp4_elem<CODES>(x.w, sc, f.e2m1, c3));
             __stcs(out + v, y);
-            if (codes != nullptr) reinterpret_cast<uint16_t*>(codes)[v] = (uint16_t)(c0 | (c1 << 4) | (c2 << 8) | (c3 << 12));
+            if (CODES && codes != nullptr) reinterpret_cast<uint16_t*>(codes)[v] = (uint16_t)(c0 | (c1 << 4) | (c2 << 8) | (c3 << 12));
             if ((v & 3) == 0) {
                 if (block_scales != nullptr) block_scales[v >> 2] = sb;
-                if (scale_codes != nullptr) scale_codes[v >> 2] = (uint8_t)f.e4m3.code(sb);
+                if (CODES && scale_codes != nullptr) scale_codes[v >> 2] = (uint8_t)f.e4m3.code(sb);
             }
         }
     }
@@ -254,7 +258,7 @@ __global__ void __launch_bounds__(kThreads) nvfp4_generic_kernel(const float* __
         if (scale_codes != nullptr) scale_codes[b] = (uint8_t)f.e4m3.code(sb);
         for (int64_t c = c0; c < c1; ++c) {
             uint32_t code;
-            y[c] = nvfp4_elem(x[c], sc, f.e2m1, code);
+            y[c] = nvfp4_elem<true>(x[c], sc, f.e2m1, code);
             if (codes != nullptr) put_code(codes, r, c, cols, 1, code);
         }
     }
@@ -290,8 +294,8 @@ int mpt_mx_quantize(const float* in, float* out, uint8_t* scales, uint8_t* codes
     cudaStream_t st = as_stream(stream);
     if (aligned && cols % block == 0 && (block == 32 || block == 16)) {
         const int64_t nvec = rows * cols / 4;
-        if (block == 32) mx_kernel<8><<<stream_blocks(nvec), kThreads, 0, st>>>(reinterpret_cast<const float4*>(in), reinterpret_cast<float4*>(out), scales, codes, fp4, nvec, ef, emax_elem);
-        else mx_kernel<4><<<stream_blocks(nvec), kThreads, 0, st>>>(reinterpret_cast<const float4*>(in), reinterpret_cast<float4*>(out), scales, codes, fp4, nvec, ef, emax_elem);
+        auto kern = block == 32 ? (codes ? mx_kernel<8, true> : mx_kernel<8, false>) : (codes ? mx_kernel<4, true> : mx_kernel<4, false>);
+        kern<<<stream_blocks(nvec), kThreads, 0, st>>>(reinterpret_cast<const float4*>(in), reinterpret_cast<float4*>(out), scales, codes, fp4, nvec, ef, emax_elem);
     } else {
         const int64_t nblk = rows * ((cols + block - 1) / block);
         mx_generic_kernel<<<stream_blocks(nblk), kThreads, 0, st>>>(in, out, scales, codes, fp4, rows, cols, block, ef, emax_elem);
@@ -317,8 +321,9 @@ int mpt_nvfp4_quantize(const float* in, float* out, float* block_scales, uint8_t
                          (reinterpret_cast<uintptr_t>(codes) & 1u) == 0;
     if (aligned && cols % 16 == 0) {
         const int64_t nvec = rows * cols / 4;
-        nvfp4_kernel<<<stream_blocks(nvec), kThreads, 0, st>>>(reinterpret_cast<const float4*>(in), reinterpret_cast<float4*>(out),
-                                                              block_scales, codes, scale_codes, nvec, global_scale, amax_bits, global_scale_out, f);
+        auto kern = (codes != nullptr || scale_codes != nullptr) ? nvfp4_kernel<true> : nvfp4_kernel<false>;
+        kern<<<stream_blocks(nvec), kThreads, 0, st>>>(reinterpret_cast<const float4*>(in), reinterpret_cast<float4*>(out),
+                                                      block_scales, codes, scale_codes, nvec, global_scale, amax_bits, global_scale_out, f);
     } else {
         nvfp4_generic_kernel<<<stream_blocks(rows * ((cols + 15) / 16)), kThreads, 0, st>>>(in, out, block_scales, codes, scale_codes, rows, cols,
                                                                                      global_scale, amax_bits, global_scale_out, f);

@@ -89,7 +89,9 @@ def load_ref(name: str = "quant_cpu"):
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default=os.environ.get("MPT_REFERENCE_ROOT", "/root/reference"))
+    here = os.path.dirname(os.path.abspath(__file__))
+    ap.add_argument("--ref", default=os.environ.get("MPT_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(here)), "reference"),
+                    help="root of the reference checkout (default: $MPT_REFERENCE_ROOT, else a sibling directory `reference`)")
     ap.add_argument("--cuda", action="store_true", help="also build quant_cuda for sm_100a")
     ap.add_argument("-v", "--verbose", action="store_true")
     args = ap.parse_args(argv)

@@ -1,6 +1,7 @@
 """Generate tests/golden/optim_steps.npz from the UNMODIFIED reference optimizers.
 
-Run where the reference tree is mounted (MPT_REFERENCE_ROOT, default /root/reference) after `python oracle/build_ref.py`:
+Run where the reference tree is mounted (MPT_REFERENCE_ROOT, default: a sibling directory `reference`) after
+`python oracle/build_ref.py`:
 
     python tests/golden/make_optim_golden.py
 
@@ -51,7 +52,7 @@ def bits(t):
 
 
 def main() -> int:
-    root = os.environ.get("MPT_REFERENCE_ROOT", "/root/reference")
+    root = os.environ.get("MPT_REFERENCE_ROOT") or os.path.join(os.path.dirname(ROOT), "reference")
     ref = load_ref("quant_cpu")
     if ref is None or not os.path.isdir(root):
         print("needs the reference tree and oracle/_ref/quant_cpu")
