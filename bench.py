@@ -529,7 +529,9 @@ def main() -> int:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="headline legs only: skip the kernel, sweep and training-step legs")
     ap.add_argument("--no-overlap", action="store_true", help="collectives after the compute they follow instead of under it")
-    ap.add_argument("--panels", type=int, default=4, help="row panels per rank whose all-gather runs under the next panel's kernel")
+    ap.add_argument("--panels", type=int, default=1,
+                    help="row panels per rank whose all-gather runs under the next panel's kernel (1: one launch and one "
+                         "all-gather, the fastest form measured at 2, 4 and 8 GPUs)")
     ap.add_argument("--quant-log2n", type=int, default=28, help="log2 of the quantizer leg's element count")
     ap.add_argument("--workload", default="mm", choices=["mm", "block", "kernels", "c4"],
                     help="mm: the headline float_mm (default); block: benchmark config 5, one GPT-2-small-shaped block, "
@@ -783,7 +785,7 @@ def main() -> int:
             "scaling": "strong", "vs_baseline": None,
             "dtype": "f32 (each multiply and add rounded to e5m2)", "data": "synthetic",
             "config": config_for(S), "accum_order": args.order,
-            "notes": "M rows sharded over %d GPU(s)%s" % (world, (", C all-gathered in %d row panels per rank under the next panel's kernel" % panels) if world > 1 else ""),
+            "notes": "M rows sharded over %d GPU(s)%s" % (world, (", C all-gathered in %d row panel(s) per rank" % panels) if world > 1 else ""),
             "clocks": clocks,
             "e2e": {"value": macs / e2e_ms / 1e6, "unit": "GMAC/s", "h2d_bytes_per_step": 4 * (rows * S + b_h2d_rows * S),
                     "d2h_bytes_per_step": 4 * rows * S, "ms_per_step": e2e_ms,

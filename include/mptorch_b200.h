@@ -164,6 +164,17 @@ MPT_API int mpt_float_conv2d_nearest(const float *x, const float *wt, float *y, 
                                      int exp_mul, int subnormals, int saturate, int fma, int order, void *workspace,
                                      size_t workspace_bytes, void *stream);
 
+/* replaces, in the backward pass of QConv2d, the unfold of the saved input and the GEMM on it for the weight gradient
+ * (mptorch/quant/modules/conv.py:537-640 with functional.py:150-155): grad_w[o][(channel, kh, kw)] = sum over (image,
+ * oh, ow), in that order, of grad_out[image][o][oh][ow] * x[image][channel][ih][iw], every product and sum rounded as in
+ * mpt_float_mm_nearest.  grad_out: [n_img, c_out, OH, OW]; x: [n_img, c_in, H, W]; grad_w: [c_out, c_in / groups * KH *
+ * KW].  The unfolded input never exists.  workspace as for mpt_float_mm_nearest with batch = 1. */
+MPT_API int mpt_float_conv2d_wgrad_nearest(const float *grad_out, const float *x, float *grad_w, int n_img, int c_in, int H,
+                                           int W, int c_out, int groups, int KH, int KW, int stride_h, int stride_w,
+                                           int pad_h, int pad_w, int dil_h, int dil_w, int man_add, int exp_add,
+                                           int man_mul, int exp_mul, int subnormals, int saturate, int fma, int order,
+                                           void *workspace, size_t workspace_bytes, void *stream);
+
 /* replaces float_quantize_nearest_mm_fma and _bmm_fma (pybind_cuda.cpp:157,173 -> quant.cu ->
  * fp_kernel.cu:247-307 -> mm_kernel.h:134-246): acc = Q(fmaf(a, b, acc)). */
 MPT_API int mpt_float_mm_nearest_fma(const float *a, const float *b, float *c, int64_t batch, int M, int N, int K,

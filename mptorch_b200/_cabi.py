@@ -66,6 +66,7 @@ def lib() -> C.CDLL:
             "mpt_superfp_quantize_nearest": [p, p, i64, i32, i32, i32, i32, i32, p],
             "mpt_float_mm_nearest": [p, p, p, i64, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, p, sz, p],
             "mpt_float_conv2d_nearest": [p, p, p] + [i32] * 22 + [p, sz, p],
+            "mpt_float_conv2d_wgrad_nearest": [p, p, p] + [i32] * 22 + [p, sz, p],
             "mpt_float_mm_nearest_static": [p, p, p, i64, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, p],
             "mpt_float_mm_nearest_fma": [p, p, p, i64, i32, i32, i32, i32, i32, i32, i32, i32, i32, p, sz, p],
             "mpt_float_mm_stochastic": [p, p, p, i64, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, u64, p, sz, p],

@@ -290,6 +290,22 @@ def float_conv2d_nearest(x, wt, y, groups, kernel_size, stride, padding, dilatio
              stream_ptr(x.device))
 
 
+def float_conv2d_wgrad_nearest(grad_out, x, grad_w, groups, kernel_size, stride, padding, dilation, man_add, exp_add, man_mul,
+                               exp_mul, subnormals, saturate, fma=False, order=None):
+    """Weight gradient of the 2-D convolution as an implicit GEMM (new; the reference unfolds the saved input and calls
+    float_quantize_nearest_mm on it).  ``grad_out`` [N, C_out, OH, OW], ``x`` [N, C, H, W], ``grad_w`` [C_out, C / groups *
+    KH * KW], all contiguous float32 on one device."""
+    check_cuda_f32(grad_out, "grad_out"); check_cuda_f32(x, "x"); check_cuda_f32(grad_w, "grad_w")
+    n, c, h, w = x.shape
+    c_out = grad_out.shape[1]
+    with torch.cuda.device(x.device):
+        ws = _cabi.mm_workspace(x.device, 1)
+        call("mpt_float_conv2d_wgrad_nearest", ptr(grad_out), ptr(x), ptr(grad_w), n, c, h, w, c_out, groups, kernel_size[0],
+             kernel_size[1], stride[0], stride[1], padding[0], padding[1], dilation[0], dilation[1], man_add, exp_add, man_mul,
+             exp_mul, int(subnormals), int(saturate), int(bool(fma)), _order_code(order, "accum_order"), ptr(ws), ws.numel(),
+             stream_ptr(x.device))
+
+
 def _mm_sr(a, b, c, batch, M, N, K, man_add, exp_add, rbits_add, man_mul, exp_mul, rbits_mul, subnormals, saturate,
            fma, seed):
     _mm_checks(a, b, c)

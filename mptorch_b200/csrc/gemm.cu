@@ -159,6 +159,60 @@ int run_conv(const float* x, const float* wt, float* y, int n_img, int c_in, int
     return MPT_OK;
 }
 
+// Weight gradient of the convolution as an implicit GEMM per group: M = output channels of the group, K = images x
+// output positions, N = input channels of the group x KH x KW.
+int run_conv_wgrad(const float* gout, const float* x, float* gw, int n_img, int c_in, int H, int W, int c_out, int groups, int KH,
+                   int KW, int sh, int sw, int ph, int pw, int dh, int dw, const FpFmt& fadd, const FpFmt& fmul, bool fma, int algo,
+                   void* workspace, size_t workspace_bytes, cudaStream_t st) {
+    const int OH = (H + 2 * ph - dh * (KH - 1) - 1) / sh + 1, OW = (W + 2 * pw - dw * (KW - 1) - 1) / sw + 1;
+    const int cg = c_in / groups, og = c_out / groups;
+    const int64_t Kw = (int64_t)cg * KH * KW;
+    if (c_out == 0 || Kw == 0) return MPT_OK;
+    const int64_t L = (OH > 0 && OW > 0) ? (int64_t)OH * OW : 0, K64 = (int64_t)n_img * L;
+    MPT_REQUIRE(K64 <= 0x7FFFFFF0 && Kw <= 0x7FFFFFFF, "float_conv2d_wgrad: problem too large");
+    if (K64 == 0) {   // no output positions: an empty sum
+        cudaError_t e = cudaMemsetAsync(gw, 0, sizeof(float) * (size_t)c_out * Kw, st);
+        if (e != cudaSuccess) { set_error("float_conv2d_wgrad: cudaMemsetAsync: %s", cudaGetErrorString(e)); return MPT_ERR_CUDA; }
+        return MPT_OK;
+    }
+    MmParams p;
+    p.cv = ConvGeom{H, W, KH, KW, OH, OW, sh, sw, ph, pw, dh, dw, (int64_t)c_in * H * W, (int64_t)c_out * L};
+    p.M = og; p.N = (int)Kw; p.K = (int)K64;
+    p.stride_a = p.stride_b = p.stride_c = 0;
+    p.fadd = fadd; p.fmul = fma ? fadd : fmul;
+    p.gadd = any_float(fadd); p.gmul = any_float(fma ? fadd : fmul);
+    p.radd = FastRn::make(fadd); p.rmul = FastRn::make(p.fmul);
+    p.rbits_add = p.rbits_mul = 0; p.seed_lo = p.seed_hi = 0;
+    p.growth8 = (float)growth8_bound(fadd.man);
+    p.stats = nullptr;
+    p.whole_ok = 0; p.sr_ok = 0;
+    p.kah_sc = p.kah_p = p.kah_const = 0.0f; p.growth8_sr = 1.0f;
+    p.wadd = p.wmul = FullRn::make(fadd);
+    p.sadd = p.smul = FullSr::make(fadd, 0);
+    const bool fast_candidate = fast_rn_supported(fadd) && (fma || fast_rn_supported(fmul)) && workspace != nullptr &&
+                                workspace_bytes >= sizeof(MmStats) && (reinterpret_cast<uintptr_t>(workspace) & 15u) == 0;
+    if (fast_candidate) {
+        MmStats* s = static_cast<MmStats*>(workspace);
+        stats_init_kernel<<<1, 256, 0, st>>>(s, 1);
+        const int64_t ng = (int64_t)n_img * c_out * L, nx = (int64_t)n_img * c_in * H * W;
+        const int sms = sm_count();
+        auto grid = [&](int64_t n) { int64_t g = (n + 255) / 256; const int64_t cap = (int64_t)sms * 8; return dim3((unsigned)(g > cap ? cap : (g < 1 ? 1 : g)), 1); };
+        stats_kernel<<<grid(ng), 256, 0, st>>>(gout, ng, s, 0);
+        stats_kernel<<<grid(nx), 256, 0, st>>>(x, nx, s, 1);
+        int rc = check_launch("float_conv2d_wgrad statistics");
+        if (rc) return rc;
+        p.stats = s;
+    }
+    for (int g = 0; g < groups; ++g) {
+        p.a = gout + (int64_t)g * og * L;
+        p.b = x + (int64_t)g * cg * H * W;
+        p.c = gw + (int64_t)g * og * Kw;
+        const int rc = launch_conv_wgrad_any(algo, fma, p, st);
+        if (rc) return rc;
+    }
+    return MPT_OK;
+}
+
 int check_mm_args(const char* who, const float* a, const float* b, float* c, int64_t batch, int M, int N, int K) {
     MPT_REQUIRE(batch >= 0 && M >= 0 && N >= 0 && K >= 0, "%s: negative dimension", who);
     MPT_REQUIRE(batch <= 65535, "%s: batch %lld exceeds 65535", who, (long long)batch);
@@ -276,6 +330,27 @@ int mpt_float_conv2d_nearest(const float* x, const float* wt, float* y, int n_im
     return run_conv(x, wt, y, n_img, c_in, H, W, c_out, groups, KH, KW, stride_h, stride_w, pad_h, pad_w, dil_h, dil_w,
                     make_fmt(man_add, exp_add, subnormals, saturate), make_fmt(fma ? man_add : man_mul, fma ? exp_add : exp_mul, subnormals, saturate),
                     fma != 0, order == MPT_ORDER_SEQ ? ALGO_SEQ : ALGO_TILE8, workspace, workspace_bytes, as_stream(stream));
+}
+
+int mpt_float_conv2d_wgrad_nearest(const float* grad_out, const float* x, float* grad_w, int n_img, int c_in, int H, int W, int c_out,
+                                   int groups, int KH, int KW, int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w,
+                                   int man_add, int exp_add, int man_mul, int exp_mul, int subnormals, int saturate, int fma, int order,
+                                   void* workspace, size_t workspace_bytes, void* stream) {
+    const char* who = "float_conv2d_wgrad_nearest";
+    MPT_REQUIRE(n_img >= 0 && c_in >= 0 && H >= 0 && W >= 0 && c_out >= 0, "%s: negative extent", who);
+    MPT_REQUIRE(groups >= 1 && c_in % groups == 0 && c_out % groups == 0, "%s: channels not divisible by groups=%d", who, groups);
+    MPT_REQUIRE(KH >= 1 && KW >= 1 && stride_h >= 1 && stride_w >= 1 && dil_h >= 1 && dil_w >= 1 && pad_h >= 0 && pad_w >= 0,
+                "%s: invalid kernel / stride / padding / dilation", who);
+    MPT_REQUIRE(valid_format(man_add, exp_add) && (fma || valid_format(man_mul, exp_mul)), "%s: unsupported format", who);
+    MPT_REQUIRE(order == MPT_ORDER_SEQ || order == MPT_ORDER_CUDA, "%s: unknown order %d", who, order);
+    MPT_REQUIRE((int64_t)c_in * H * W <= 0x7FFFFFFF, "%s: one input image exceeds 2^31 elements", who);
+    MPT_REQUIRE(c_out / groups <= 65535 * BM, "%s: too many output channels per group", who);
+    const bool empty = c_out == 0 || c_in == 0;
+    MPT_REQUIRE(empty || grad_w, "%s: null pointer", who);
+    MPT_REQUIRE(empty || n_img == 0 || (grad_out && x), "%s: null pointer", who);
+    return run_conv_wgrad(grad_out, x, grad_w, n_img, c_in, H, W, c_out, groups, KH, KW, stride_h, stride_w, pad_h, pad_w, dil_h, dil_w,
+                          make_fmt(man_add, exp_add, subnormals, saturate), make_fmt(fma ? man_add : man_mul, fma ? exp_add : exp_mul, subnormals, saturate),
+                          fma != 0, order == MPT_ORDER_SEQ ? ALGO_SEQ : ALGO_TILE8, workspace, workspace_bytes, as_stream(stream));
 }
 
 int mpt_float_mm_nearest_fma(const float* a, const float* b, float* c, int64_t batch, int M, int N, int K, int man_fma,

@@ -66,10 +66,15 @@ struct MmStats {
 // that order (the order of F.unfold and of the reference's unfoldNd, conv.py:591-617), and the element is read
 // straight from the NCHW input (zero outside the image), so the unfolded matrix never exists.  C is written to the
 // NCHW output.
+// The weight gradient of the same convolution is a GEMM too (CONV mode 2): dW[o][(channel, kh, kw)] = sum over k =
+// (image, oh, ow) of dY[image][o][oh][ow] * x[image][channel][ih][iw], i.e. A = dY seen as [c_out, images * OH * OW]
+// (row o, column k: a strided read of the NCHW gradient) and B = the unfolded input, gathered on the fly; K runs over
+// the images and output positions in the order of the reference's unfold + transpose (conv.py:591-617).
 struct ConvGeom {
     int H, W, KH, KW, OH, OW, sh, sw, ph, pw, dh, dw;
     int64_t x_image_stride, y_image_stride;      // elements between consecutive images of input and output
 };
+enum ConvMode : int { CONV_NONE = 0, CONV_FWD = 1, CONV_WGRAD = 2 };
 
 struct MmParams {
     ConvGeom cv;                 // used by the CONV instantiations only
@@ -169,10 +174,44 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 // zero filled (cp.async with a source size of 0), which is also how K is zero padded.
 struct ConvRow { int64_t base; int ih0, iw0; };     // per output position: image offset, top-left input coordinate
 
-template <bool VEC, bool CONV = false>
+template <bool VEC, int CONV = CONV_NONE>
 __device__ __forceinline__ void load_tiles(const MmParams& p, const float* A, const float* B, float* As, float* Bs,
                                            int m0, int n0, int k0, int tid, const ConvRow* rows = nullptr) {
-    if (CONV) {
+    if (CONV == CONV_WGRAD) {
+        const int L = p.cv.OH * p.cv.OW;
+        {   // A[m][k] = dY[image(k)][m][position(k)]: the thread's slab column is fixed, its rows are (tid >> 5) + 8 u
+            const int kk = tid & 31, gk = k0 + kk;
+            const bool kok = gk < p.K;
+            const int img = gk / L, l = gk - img * L;
+            const int64_t koff = (int64_t)img * p.cv.y_image_stride + l;
+#pragma unroll 4
+            for (int u = 0; u < BM / 8; ++u) {
+                const int row = (tid >> 5) + 8 * u, gm = m0 + row;
+                const bool ok = kok && gm < p.M;
+                cp_async4(As + row * AS_LD + kk, ok ? A + koff + (int64_t)gm * L : A, ok ? 4 : 0);
+            }
+        }
+        {   // B[k][j] = x[image(k)][channel(j)][ih][iw]: the thread's column j is fixed, its slab rows are (tid >> 6) + 4 u
+            const int nn = tid & 63, gj = n0 + nn;
+            const int khkw = p.cv.KH * p.cv.KW;
+            const int ch = gj / khkw, rem = gj - ch * khkw;
+            const int kh = rem / p.cv.KW, kw = rem - kh * p.cv.KW;
+            const bool jok = gj < p.N;
+            const int dih = kh * p.cv.dh - p.cv.ph, diw = kw * p.cv.dw - p.cv.pw;
+            const int64_t coff = (int64_t)ch * p.cv.H * p.cv.W;
+#pragma unroll 4
+            for (int u = 0; u < (BK * BN) / THREADS; ++u) {
+                const int kr = (tid >> 6) + 4 * u, gk = k0 + kr;
+                const int img = gk / L, l = gk - img * L;
+                const int oh = l / p.cv.OW, ow = l - oh * p.cv.OW;
+                const int ih = oh * p.cv.sh + dih, iw = ow * p.cv.sw + diw;
+                const bool ok = jok && gk < p.K && (unsigned)ih < (unsigned)p.cv.H && (unsigned)iw < (unsigned)p.cv.W;
+                cp_async4(Bs + kr * BN + nn, ok ? B + (int64_t)img * p.cv.x_image_stride + coff + (int64_t)ih * p.cv.W + iw : B, ok ? 4 : 0);
+            }
+        }
+        return;
+    }
+    if (CONV == CONV_FWD) {
         // A: the thread's column of the slab is fixed (tid & 31), its rows are (tid >> 5) + 8 u
         const int kk = tid & 31, gk = k0 + kk;
         const int khkw = p.cv.KH * p.cv.KW;
@@ -554,7 +593,7 @@ __device__ __forceinline__ FastPlan make_plan(const MmParams& p, int64_t batch) 
     return plan;
 }
 
-template <int ALGO, bool FMA, bool VEC, bool PACKED, bool ADDG, bool CONV = false, int MINB = MPT_MM_MIN_CTAS>
+template <int ALGO, bool FMA, bool VEC, bool PACKED, bool ADDG, int CONV = CONV_NONE, int MINB = MPT_MM_MIN_CTAS>
 __global__ void __launch_bounds__(THREADS, MINB) mm_kernel(const __grid_constant__ MmParams p) {
     extern __shared__ __align__(16) float smem[];
     float* As = smem;
@@ -592,7 +631,7 @@ __global__ void __launch_bounds__(THREADS, MINB) mm_kernel(const __grid_constant
 
     const FastPlan plan = make_plan<ALGO, FMA>(p, batch);
 
-    if (CONV) {
+    if (CONV == CONV_FWD) {
         if (tid < BM) {
             const int gm = m0 + tid;
             ConvRow r;
@@ -710,7 +749,7 @@ __global__ void __launch_bounds__(THREADS, MINB) mm_kernel(const __grid_constant
     cp_async_wait<0>();
 
     // epilogue
-    if (CONV) {     // C[m][n] goes to y[image][n][oh][ow]: consecutive m are consecutive addresses
+    if (CONV == CONV_FWD) {     // C[m][n] goes to y[image][n][oh][ow]: consecutive m are consecutive addresses
         const int L = p.cv.OH * p.cv.OW;
 #pragma unroll
         for (int i = 0; i < TM; ++i) {
@@ -763,10 +802,10 @@ int launch_mm(const MmParams& p, int64_t batch, bool vec, cudaStream_t st) {
     // smallest subnormal (always the case for a fused multiply-add, whose sum is not a sum of rounded values)
     const bool add_guard = FMA || !packed || (p.fmul.min_exp - p.fmul.man) < (p.fadd.min_exp - p.fadd.man);
     constexpr bool kCanDrop = kHasFast && !FMA;
-    auto kern = vec ? (packed ? (add_guard ? mm_kernel<ALGO, FMA, true, kHasFast, true, false, kMinB> : mm_kernel<ALGO, FMA, true, kHasFast, !kCanDrop, false, kMinB>)
-                              : mm_kernel<ALGO, FMA, true, false, true, false, kMinB>)
-                    : (packed ? (add_guard ? mm_kernel<ALGO, FMA, false, kHasFast, true, false, kMinB> : mm_kernel<ALGO, FMA, false, kHasFast, !kCanDrop, false, kMinB>)
-                              : mm_kernel<ALGO, FMA, false, false, true, false, kMinB>);
+    auto kern = vec ? (packed ? (add_guard ? mm_kernel<ALGO, FMA, true, kHasFast, true, CONV_NONE, kMinB> : mm_kernel<ALGO, FMA, true, kHasFast, !kCanDrop, CONV_NONE, kMinB>)
+                              : mm_kernel<ALGO, FMA, true, false, true, CONV_NONE, kMinB>)
+                    : (packed ? (add_guard ? mm_kernel<ALGO, FMA, false, kHasFast, true, CONV_NONE, kMinB> : mm_kernel<ALGO, FMA, false, kHasFast, !kCanDrop, CONV_NONE, kMinB>)
+                              : mm_kernel<ALGO, FMA, false, false, true, CONV_NONE, kMinB>);
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
     if (e != cudaSuccess) { set_error("float_mm: cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return MPT_ERR_CUDA; }
     kern<<<grid, THREADS, SMEM_BYTES, st>>>(p);
@@ -778,12 +817,24 @@ template <int ALGO, bool FMA>
 int launch_conv(const MmParams& p, cudaStream_t st) {
     dim3 grid((unsigned)(((int64_t)p.N + BN - 1) / BN), (unsigned)(((int64_t)p.M + BM - 1) / BM), 1);
     const bool add_guard = FMA || (p.fmul.min_exp - p.fmul.man) < (p.fadd.min_exp - p.fadd.man);
-    auto kern = add_guard ? mm_kernel<ALGO, FMA, false, true, true, true> : mm_kernel<ALGO, FMA, false, true, FMA, true>;
+    auto kern = add_guard ? mm_kernel<ALGO, FMA, false, true, true, CONV_FWD> : mm_kernel<ALGO, FMA, false, true, FMA, CONV_FWD>;
     const size_t smem = SMEM_BYTES + BM * sizeof(ConvRow);
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) { set_error("float_conv2d: cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return MPT_ERR_CUDA; }
     kern<<<grid, THREADS, smem, st>>>(p);
     return check_launch("float_conv2d");
+}
+
+// Weight-gradient launch: both operands are gathered with scalar copies; the result is an ordinary row-major matrix.
+template <int ALGO, bool FMA>
+int launch_conv_wgrad(const MmParams& p, cudaStream_t st) {
+    dim3 grid((unsigned)(((int64_t)p.N + BN - 1) / BN), (unsigned)(((int64_t)p.M + BM - 1) / BM), 1);
+    const bool add_guard = FMA || (p.fmul.min_exp - p.fmul.man) < (p.fadd.min_exp - p.fadd.man);
+    auto kern = add_guard ? mm_kernel<ALGO, FMA, false, true, true, CONV_WGRAD> : mm_kernel<ALGO, FMA, false, true, FMA, CONV_WGRAD>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+    if (e != cudaSuccess) { set_error("float_conv2d_wgrad: cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return MPT_ERR_CUDA; }
+    kern<<<grid, THREADS, SMEM_BYTES, st>>>(p);
+    return check_launch("float_conv2d_wgrad");
 }
 
 // Defined in the instantiation files.
@@ -792,5 +843,6 @@ int launch_mm_tile8(bool fma, const MmParams& p, int64_t batch, bool vec, cudaSt
 int launch_mm_kahan(bool fma, const MmParams& p, int64_t batch, bool vec, cudaStream_t st);
 int launch_mm_sr(bool fma, const MmParams& p, int64_t batch, bool vec, cudaStream_t st);
 int launch_conv_any(int algo, bool fma, const MmParams& p, cudaStream_t st);
+int launch_conv_wgrad_any(int algo, bool fma, const MmParams& p, cudaStream_t st);
 
 }  // namespace mpt

@@ -224,11 +224,24 @@ def implicit_conv_eligible(formats, input) -> bool:
     return iq is id_quant or getattr(iq, "forward_number", 0) is None or getattr(iq, "forward_rounding", None) == "nearest"
 
 
+def implicit_wgrad_eligible(formats) -> bool:
+    """The weight gradient can be taken by the implicit GEMM (no unfolded input) when the backward MACs are float
+    formats rounded to nearest without compensation and the gradient quantizer is deterministic (a stochastic one would
+    draw once per gradient element here and once per (group, element) in the per-group composition)."""
+    if formats.bwd_use_default_prec or formats.compensated or formats.bwd_rnd != "nearest":
+        return False
+    if not isinstance(formats.bwd_add, FloatingPoint) or not isinstance(formats.bwd_mul, FloatingPoint):
+        return False
+    return _float_nearest_spec(formats.grad_quant) is not None
+
+
 class qconv2d_kernel(torch.autograd.Function):
     """Zero-padded 2-D convolution whose forward pass is one implicit GEMM per group on the NCHW input
     (``mpt_float_conv2d_nearest``): the unfolded input, nine times the input for a 3x3 kernel, is neither built nor
-    kept for the backward pass.  The backward pass unfolds the saved (already quantized) input and runs the two
-    GEMMs of ``qlinear_kernel.backward`` per group, so gradients equal those of the unfold + ``qlinear`` composition
+    kept for the backward pass.  The weight gradient is an implicit GEMM as well (``mpt_float_conv2d_wgrad_nearest``: the
+    NCHW output gradient against the input gathered on the fly) whenever ``implicit_wgrad_eligible``; otherwise, and for
+    the input gradient, the backward pass unfolds the saved (already quantized) input and runs the GEMMs of
+    ``qlinear_kernel.backward`` per group.  Either way the gradients equal those of the unfold + ``qlinear`` composition
     bit for bit (reference: modules/conv.py:537-640 with functional.py:66-173)."""
 
     @staticmethod
@@ -263,6 +276,16 @@ class qconv2d_kernel(torch.autograd.Function):
         og = c_out // groups
         grad_scale = 0                # the implicit path is taken only without tensor scaling (implicit_conv_eligible)
         gin, gws, gbs = [], [], []
+        implicit_w = ctx.needs_input_grad[1] and implicit_wgrad_eligible(f)
+        if implicit_w:
+            from .. import backend as _be
+
+            qgo_all = f.grad_quant(grad_output).contiguous().float()         # elementwise: the values the per-group path sees
+            gw_all = torch.empty(c_out, cg * kh * kw, device=grad_output.device)
+            _be.float_conv2d_wgrad_nearest(qgo_all, qinput.float(), gw_all, groups, (kh, kw), stride, padding, dilation, f.bwd_add.man,
+                                           f.bwd_add.exp, f.bwd_mul.man, f.bwd_mul.exp, f.bwd_add.subnormals, f.bwd_add.saturate,
+                                           fma=f.bwd_fma)
+            gws.append(f.grad_quant(gw_all).view(c_out, cg, kh, kw))
         for g in range(groups):
             go = grad_output[:, g * og:(g + 1) * og]
             go2 = go.reshape(n, og, -1).transpose(1, 2).reshape(-1, og)              # [N * L, og], as qlinear sees it
@@ -273,7 +296,7 @@ class qconv2d_kernel(torch.autograd.Function):
                 gc = f.grad_quant(gc)
                 gc = gc.view(n, -1, gc.shape[-1]).transpose(1, 2)                    # [N, K, L]
                 gin.append(torch.nn.functional.fold(gc, (h, w), (kh, kw), dilation=dilation, padding=padding, stride=stride))
-            if ctx.needs_input_grad[1]:
+            if ctx.needs_input_grad[1] and not implicit_w:
                 cols = _conv_cols(qinput[:, g * cg:(g + 1) * cg], (kh, kw), dilation, padding, stride)
                 gw = (torch.matmul(qgo.transpose(-2, -1), cols) if f.bwd_use_default_prec
                       else mp_bmm(qgo.transpose(-2, -1), cols, formats=f, use_forward=False))

@@ -101,6 +101,35 @@ def test_implicit_conv_other_formats_and_special_values(q, monkeypatch):
     a = run(q, conv, x, g, True, monkeypatch)
     b = run(q, conv, x, g, False, monkeypatch)
     assert bits_equal(a[0], b[0])
+    assert bits_equal(a[2], b[2]), "weight gradient through the implicit GEMM"
+
+
+def test_implicit_weight_gradient_entry_point(q):
+    """mpt_float_conv2d_wgrad_nearest against the unfold + float_mm composition it replaces, directly: groups, strides,
+    dilation, padding, a K (images x positions) that is not a multiple of the 8-wide tile, and gradients that overflow."""
+    from mptorch_b200 import backend as be
+
+    torch.manual_seed(7)
+    for (n, c, h, w, cout, k, s, p, d, groups) in [(3, 4, 9, 7, 6, (3, 2), (2, 1), (1, 0), (1, 2), 2), (2, 3, 11, 11, 70, (3, 3), (1, 1), (1, 1), (1, 1), 1),
+                                                    (1, 2, 5, 5, 2, (5, 5), (1, 1), (2, 2), (1, 1), 1)]:
+        x = torch.randn(n, c, h, w, device="cuda")
+        oh = (h + 2 * p[0] - d[0] * (k[0] - 1) - 1) // s[0] + 1
+        ow = (w + 2 * p[1] - d[1] * (k[1] - 1) - 1) // s[1] + 1
+        go = torch.randn(n, cout, oh, ow, device="cuda") * 30
+        cg, og = c // groups, cout // groups
+        for order in ("cuda", "seq"):
+            for (ma, ea, mm, em, fma) in [(10, 5, 3, 4, False), (2, 5, 2, 5, False), (7, 8, 7, 8, True)]:
+                got = torch.full((cout, cg * k[0] * k[1]), float("nan"), device="cuda")
+                be.float_conv2d_wgrad_nearest(go, x, got, groups, k, s, p, d, ma, ea, mm, em, True, False, fma=fma, order=order)
+                for g in range(groups):
+                    cols = torch.nn.functional.unfold(x[:, g * cg:(g + 1) * cg], k, dilation=d, padding=p, stride=s).transpose(1, 2).reshape(-1, cg * k[0] * k[1]).contiguous()
+                    a = go[:, g * og:(g + 1) * og].reshape(n, og, -1).transpose(1, 2).reshape(-1, og).t().contiguous()
+                    want = torch.empty(og, cols.shape[1], device="cuda")
+                    if fma:
+                        be.float_quantize_nearest_mm_fma(a, cols, want, og, cols.shape[1], a.shape[1], ma, ea, True, False, False, order=order)
+                    else:
+                        be.float_quantize_nearest_mm(a, cols, want, og, cols.shape[1], a.shape[1], ma, ea, mm, em, True, False, False, order=order)
+                    assert bits_equal(got[g * og:(g + 1) * og], want), ((n, c, h, w, cout, k, s, p, d, groups), order, ma, ea, fma, g)
 
 
 def test_ineligible_configurations_take_the_unfold_path(q):
