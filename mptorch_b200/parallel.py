@@ -100,7 +100,10 @@ def sharded_float_mm(a_rows: torch.Tensor, b: torch.Tensor, M: int, mm_fn: Calla
         with (torch.cuda.stream(side) if cuda else _NullContext()):
             if cuda:
                 side.wait_event(ready)
-            if even:
+            if even and npan == 1 and out.is_contiguous():
+                # one panel and equal row blocks: the result is the ranks' blocks back to back, gathered in place
+                dist.all_gather_into_tensor(out, c_p.contiguous(), group=group)
+            elif even:
                 dist.all_gather([out[starts[r] + plo: starts[r] + phi] for r in range(world)], c_p, group=group)
             else:
                 pr = phi - plo
