@@ -442,7 +442,9 @@ def block_step(dev, world: int, rank: int, steps: int, warmup: int, overlap: boo
     import torch
     import torch.distributed as dist
 
+    from mptorch_b200 import FloatingPoint
     from mptorch_b200.gpt2_block import BlockConfig, QTinyGPT
+    from mptorch_b200.optim import QSGD, fma_quantizer
     from mptorch_b200.parallel import GradientAllReducer, allreduce_gradients
 
     B, T = 8, 1024
@@ -451,8 +453,13 @@ def block_step(dev, world: int, rank: int, steps: int, warmup: int, overlap: boo
     g = torch.Generator().manual_seed(1000 + rank)
     idx_host = torch.randint(0, 50257, (B, T), generator=g).pin_memory()     # synthetic uniform token ids
     reducer = GradientAllReducer(model.parameters()) if (overlap and world > 1) else None
+    # the weight update of the step: SGD with momentum, momentum and weights kept in e8m7 with a Kahan compensation
+    # buffer (the reference's QSGD), as one fused launch per 40 tensors
+    acc_q = fma_quantizer(FloatingPoint(8, 7, True, True))
+    opt = QSGD(model.parameters(), lr=1e-3, momentum=0.9, momentum_quant=acc_q, acc_quant=acc_q, compensated=True)
+    opt_ev = []
 
-    def step():
+    def step(timed=False):
         idx = idx_host.to(dev, non_blocking=True)
         model.zero_grad(set_to_none=True)
         loss = model(idx).float().pow(2).mean()
@@ -461,6 +468,14 @@ def block_step(dev, world: int, rank: int, steps: int, warmup: int, overlap: boo
             reducer.finish()
         else:
             allreduce_gradients(model.parameters())
+        if timed:
+            o0, o1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            o0.record()
+            opt.step()
+            o1.record()
+            opt_ev.append((o0, o1))
+        else:
+            opt.step()
         return loss
 
     warmup = max(warmup, 3)
@@ -472,7 +487,7 @@ def block_step(dev, world: int, rank: int, steps: int, warmup: int, overlap: boo
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(steps):
-        loss = step()
+        loss = step(timed=True)
         loss_host = loss.item()                            # device -> host read of the step's result
     e1.record()
     if world > 1:
@@ -484,8 +499,19 @@ def block_step(dev, world: int, rank: int, steps: int, warmup: int, overlap: boo
     ms = t.item() / steps
     if reducer is not None:
         reducer.remove()
+    opt_ms = statistics.mean(a.elapsed_time(b) for a, b in opt_ev)
+    # the same update through the reference's per-tensor sequence of torch kernels and quantizer launches, once, for scale
+    opt.fused = False
+    torch.cuda.synchronize(dev)
+    p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    p0.record()
+    opt.step()
+    p1.record()
+    torch.cuda.synchronize(dev)
+    opt_per_tensor_ms = p0.elapsed_time(p1)
+    n_params = sum(p.numel() for p in model.parameters())
     macs = model.macs_per_step(B, T) * world
-    del model
+    del model, opt
     if rank != 0:
         return None
     v = macs / ms / 1e6
@@ -493,8 +519,13 @@ def block_step(dev, world: int, rank: int, steps: int, warmup: int, overlap: boo
             "steps": steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32 (MACs rounded: add e5m10, mul e4m3)", "data": "synthetic",
             "config": {"workload": "QLinear/QLayerNorm/QSoftmax block d=768 h=12 mlp=3072 seq=1024 batch=8 per GPU, fwd+bwd, "
-                                   "DP gradient all-reduce %s" % ("under the backward pass" if reducer is not None or world == 1 else "after the backward pass"),
+                                   "DP gradient all-reduce %s, QSGD update (momentum 0.9, e8m7 momentum and weights, Kahan-compensated)"
+                                   % ("under the backward pass" if reducer is not None or world == 1 else "after the backward pass"),
                        "loss": loss_host},
+            "optimizer": {"fused_step_ms": round(opt_ms, 4), "per_tensor_step_ms": round(opt_per_tensor_ms, 4), "parameters": n_params,
+                          "gbs": round(32.0 * n_params / opt_ms / 1e6, 1),
+                          "note": "QSGD.step inside the timed step: one launch for all parameter tensors; 32 B per parameter "
+                                  "(weight, gradient, momentum, compensation read; weight, momentum, compensation written)"},
             "e2e": {"value": v, "unit": "GMAC/s", "h2d_bytes_per_step": B * T * 8, "d2h_bytes_per_step": 4, "ms_per_step": ms}}
 
 

@@ -33,6 +33,10 @@ struct OptTable {
     int count;
 };
 
+// The exact caster as a function call: it is rarely taken, and a copy inlined at every rounding of an unrolled
+// update would push the kernel out of the instruction cache.
+__device__ __noinline__ float exact_nearest(float x, FpFmt fmt) { return cast_fp_nearest(x, fmt); }
+
 // One quantizer Q of the optimizer: identity (no quantizer given), the FP-pipe rounding, or the exact caster.
 struct Rounder {
     FullRn fast;
@@ -40,10 +44,32 @@ struct Rounder {
     int mode;                // 0 identity, 1 fast, 2 exact
     __device__ __forceinline__ float operator()(float x) const {
         if (mode == 0) return x;
-        return mode == 1 ? fast(x) : cast_fp_nearest(x, fmt);
+        if (mode == 2) return exact_nearest(x, fmt);
+        if (fmt.exp == 8) {
+            // formats with an 8-bit exponent: fp32 denormals and the largest magnitudes go to the exact caster; a
+            // positive zero (the usual gradient of an unused embedding row) is its own rounding
+            const uint32_t t = f2u(x), a = t & 0x7FFFFFFFu;
+            if (t == 0u) return x;
+            if (a >= fast.exact_from || a < 0x00800000u) return exact_nearest(x, fmt);
+        }
+        return fast.line(x);
     }
     // the reference's callable: Q(x + y * z), the product rounded to fp32 before the sum
     __device__ __forceinline__ float fma3(float x, float y, float z) const { return (*this)(add_rn(x, mul_rn(y, z))); }
+
+    // The same without a branch, for modes 0 and 1: the FP-pipe rounding is always computed, and an input the exact
+    // caster would have to handle (8-bit exponent: an fp32 denormal or a magnitude near the top of the range) only
+    // sets `rare`; the caller then recomputes that element through operator().  Straight-line code lets the compiler
+    // interleave the roundings of independent elements.
+    uint32_t span;           // rare when (|x| bits - 0x00800000) >= span, zero excepted
+    uint32_t check;          // 1 where that test applies (mode 1, 8-bit exponent)
+    __device__ __forceinline__ float line(float x, uint32_t& rare) const {
+        const uint32_t t = f2u(x), a = t & 0x7FFFFFFFu;
+        rare |= ((a - 0x00800000u >= span) && t != 0u) ? check : 0u;
+        const float y = (t == 0u) ? x : fast.line(x);
+        return mode == 0 ? x : y;
+    }
+    __device__ __forceinline__ float line3(float x, float y, float z, uint32_t& rare) const { return line(add_rn(x, mul_rn(y, z)), rare); }
 };
 
 Rounder make_rounder(int enabled, int man, int exp, int sub, int sat) {
@@ -51,6 +77,8 @@ Rounder make_rounder(int enabled, int man, int exp, int sub, int sat) {
     r.fmt = make_fmt(enabled ? man : 23, enabled ? exp : 8, sub, sat);
     r.fast = FullRn::make(r.fmt);
     r.mode = !enabled ? 0 : (fast_rn_supported(r.fmt) ? 1 : 2);
+    r.check = (r.mode == 1 && r.fmt.exp == 8) ? 1u : 0u;
+    r.span = r.check ? r.fast.exact_from - 0x00800000u : 0xFFFFFFFFu;
     return r;
 }
 
@@ -84,6 +112,137 @@ __device__ __forceinline__ void compensated_update(float& p, float& comp, float 
     p = s;
 }
 
+// Internal per-tensor flag (set by launch_optim, never by the caller): every buffer of the tensor starts on a 16-byte
+// boundary, so full chunks move as float4.
+constexpr int kOptAligned = 1 << 30;
+
+// One element of the QSGD step.  m and c are read only where the configuration uses them.
+__device__ __forceinline__ void sgd_elem(float& p, float& g, float& m, float& c, bool first, const SgdArgs& a) {
+    if (a.weight_decay != 0.0f) g = fma_rn(p, a.weight_decay, g);      // d_p.add_(p.data, alpha=weight_decay), in place on the gradient
+    float d = g;
+    if (a.momentum != 0.0f) {
+        float buf;
+        if (first) {
+            // momentum_quant(clone(d_p), zeros, zeros), or a plain clone
+            buf = a.has_momentum_quant ? a.qm.fma3(g, 0.0f, 0.0f) : g;
+        } else {
+            const float scaled = mul_rn(m, a.momentum);                // buf.mul_(momentum)
+            buf = a.has_momentum_quant ? a.qm.fma3(scaled, g, a.one_minus_dampening)
+                                       : fma_rn(g, a.one_minus_dampening, scaled);   // .add_(d_p, alpha=1 - dampening)
+        }
+        m = buf;
+        d = a.nesterov ? fma_rn(buf, a.momentum, g) : buf;             // d_p.add(buf, alpha=momentum)
+    }
+    if (a.has_acc_quant) {
+        if (!a.compensated) p = a.qa.fma3(p, d, a.neg_lr);
+        else compensated_update(p, c, d, a.lr, a.qa);
+    } else if (!a.compensated) {
+        p = fma_rn(d, a.neg_lr, p);                                    // p.add_(d_p, alpha=-lr)
+    } else {
+        // u = -lr * d_p; y = u - comp; s = p + y; comp = (s - p) - y
+        const float u = mul_rn(a.neg_lr, d), y = add_rn(u, -c), s = add_rn(p, y);
+        c = add_rn(add_rn(s, -p), -y);
+        p = s;
+    }
+}
+
+constexpr int kOptPer = kOptChunk / kThreads;            // elements per thread and chunk
+constexpr int kOptVecs = kOptPer / 4;                    // float4 groups per thread and chunk
+
+__device__ __forceinline__ void ld4(const float* src, float* dst) {
+    const float4 v = *reinterpret_cast<const float4*>(src);
+    dst[0] = v.x; dst[1] = v.y; dst[2] = v.z; dst[3] = v.w;
+}
+__device__ __forceinline__ void st4(float* dst, const float* src) { *reinterpret_cast<float4*>(dst) = make_float4(src[0], src[1], src[2], src[3]); }
+__device__ __forceinline__ void zero4(float* dst) { dst[0] = dst[1] = dst[2] = dst[3] = 0.0f; }
+
+#define MPT_EACH for (int e = 0; e < kOptPer; ++e)
+
+__device__ __forceinline__ void compensated_line(float& p, float& comp, float d, float scale, const Rounder& qa, uint32_t& rare) {
+    const float y = -qa.line3(comp, d, scale, rare);
+    const float s = qa.line3(p, y, 1.0f, rare);
+    comp = qa.line3(qa.line3(s, p, -1.0f, rare), y, -1.0f, rare);
+    p = s;
+}
+
+// The QSGD step over the kOptPer elements a thread holds, one phase at a time: the configuration's branches sit
+// between the phases, each phase is straight-line code over independent elements.  Same operations as sgd_elem.
+__device__ __forceinline__ uint32_t sgd_block(float (&p)[kOptPer], float (&g)[kOptPer], float (&m)[kOptPer], float (&c)[kOptPer], bool first,
+                                              const SgdArgs& a) {
+    uint32_t rare = 0u;
+    float d[kOptPer];
+    if (a.weight_decay != 0.0f) {
+#pragma unroll
+        MPT_EACH g[e] = fma_rn(p[e], a.weight_decay, g[e]);
+    }
+    if (a.momentum != 0.0f) {
+        if (first) {
+            if (a.has_momentum_quant) {
+#pragma unroll
+                MPT_EACH m[e] = a.qm.line3(g[e], 0.0f, 0.0f, rare);
+            } else {
+#pragma unroll
+                MPT_EACH m[e] = g[e];
+            }
+        } else if (a.has_momentum_quant) {
+#pragma unroll
+            MPT_EACH m[e] = a.qm.line3(mul_rn(m[e], a.momentum), g[e], a.one_minus_dampening, rare);
+        } else {
+#pragma unroll
+            MPT_EACH m[e] = fma_rn(g[e], a.one_minus_dampening, mul_rn(m[e], a.momentum));
+        }
+        if (a.nesterov) {
+#pragma unroll
+            MPT_EACH d[e] = fma_rn(m[e], a.momentum, g[e]);
+        } else {
+#pragma unroll
+            MPT_EACH d[e] = m[e];
+        }
+    } else {
+#pragma unroll
+        MPT_EACH d[e] = g[e];
+    }
+    if (a.has_acc_quant) {
+        if (!a.compensated) {
+#pragma unroll
+            MPT_EACH p[e] = a.qa.line3(p[e], d[e], a.neg_lr, rare);
+        } else {
+#pragma unroll
+            MPT_EACH compensated_line(p[e], c[e], d[e], a.lr, a.qa, rare);
+        }
+    } else if (!a.compensated) {
+#pragma unroll
+        MPT_EACH p[e] = fma_rn(d[e], a.neg_lr, p[e]);
+    } else {
+#pragma unroll
+        MPT_EACH {
+            const float u = mul_rn(a.neg_lr, d[e]), y = add_rn(u, -c[e]), s = add_rn(p[e], y);
+            c[e] = add_rn(add_rn(s, -p[e]), -y);
+            p[e] = s;
+        }
+    }
+    return rare;
+}
+
+// A thread's elements of one chunk again, from memory, through the branching rounder: taken when sgd_block met an
+// input its straight-line rounding does not cover (nothing of the chunk has been stored yet at that point).
+__device__ __noinline__ void sgd_redo(float* P, float* G, float* M, float* C, int64_t base, bool first, const SgdArgs& a) {
+    const bool use_m = a.momentum != 0.0f, rd_m = use_m && !first, use_c = a.compensated != 0, wr_g = a.weight_decay != 0.0f;
+#pragma unroll 1
+    for (int e = 0; e < kOptPer; ++e) {
+        const int64_t i = base + (int64_t)(e >> 2) * (kThreads * 4) + (e & 3);
+        float p = P[i], g = G[i], m = rd_m ? M[i] : 0.0f, c = use_c ? C[i] : 0.0f;
+        sgd_elem(p, g, m, c, first, a);
+        P[i] = p;
+        if (wr_g) G[i] = g;
+        if (use_m) M[i] = m;
+        if (use_c) C[i] = c;
+    }
+}
+
+// LINE: neither quantizer needs the exact caster throughout (the host decides), so aligned full chunks take the
+// vector path with straight-line roundings.
+template <bool LINE>
 __global__ void __launch_bounds__(kThreads) qsgd_kernel(const __grid_constant__ OptTable t, const __grid_constant__ SgdArgs a) {
     const int k = find_tensor(t, blockIdx.x);
     float* __restrict__ P = t.param[k];
@@ -91,47 +250,154 @@ __global__ void __launch_bounds__(kThreads) qsgd_kernel(const __grid_constant__ 
     float* __restrict__ M = t.buf0[k];
     float* __restrict__ C = t.buf1[k];
     const bool first = (t.flags[k] & MPT_OPT_FIRST_STEP) != 0;
+    const bool use_m = a.momentum != 0.0f, rd_m = use_m && !first, use_c = a.compensated != 0, wr_g = a.weight_decay != 0.0f;
     const int64_t begin = (int64_t)(blockIdx.x - t.first_block[k]) * kOptChunk;
     const int64_t end = begin + kOptChunk < t.n[k] ? begin + kOptChunk : t.n[k];
+    if (LINE && (t.flags[k] & kOptAligned) && end - begin == kOptChunk) {
+        // all loads of the chunk first, so that every thread has its elements of each buffer in flight at once
+        const int64_t base = begin + (int64_t)threadIdx.x * 4;
+        float p[kOptPer], g[kOptPer], m[kOptPer], c[kOptPer];
+#pragma unroll
+        for (int h = 0; h < kOptVecs; ++h) {
+            const int64_t i = base + (int64_t)h * (kThreads * 4);
+            ld4(P + i, p + 4 * h);
+            ld4(G + i, g + 4 * h);
+            if (rd_m) ld4(M + i, m + 4 * h); else zero4(m + 4 * h);
+            if (use_c) ld4(C + i, c + 4 * h); else zero4(c + 4 * h);
+        }
+        if (sgd_block(p, g, m, c, first, a)) { sgd_redo(P, G, M, C, base, first, a); return; }
+#pragma unroll
+        for (int h = 0; h < kOptVecs; ++h) {
+            const int64_t i = base + (int64_t)h * (kThreads * 4);
+            st4(P + i, p + 4 * h);
+            if (wr_g) st4(G + i, g + 4 * h);
+            if (use_m) st4(M + i, m + 4 * h);
+            if (use_c) st4(C + i, c + 4 * h);
+        }
+        return;
+    }
     for (int64_t i = begin + threadIdx.x; i < end; i += kThreads) {
-        float p = P[i], g = G[i];
-        if (a.weight_decay != 0.0f) {                       // d_p.add_(p.data, alpha=weight_decay), in place on the gradient
-            g = fma_rn(p, a.weight_decay, g);
-            G[i] = g;
-        }
-        float d = g;
-        if (a.momentum != 0.0f) {
-            float buf;
-            if (first) {
-                // momentum_quant(clone(d_p), zeros, zeros), or a plain clone
-                buf = a.has_momentum_quant ? a.qm.fma3(g, 0.0f, 0.0f) : g;
-            } else {
-                const float scaled = mul_rn(M[i], a.momentum);        // buf.mul_(momentum)
-                buf = a.has_momentum_quant ? a.qm.fma3(scaled, g, a.one_minus_dampening)
-                                           : fma_rn(g, a.one_minus_dampening, scaled);   // .add_(d_p, alpha=1 - dampening)
-            }
-            M[i] = buf;
-            d = a.nesterov ? fma_rn(buf, a.momentum, g) : buf;         // d_p.add(buf, alpha=momentum)
-        }
-        if (a.has_acc_quant) {
-            if (!a.compensated) p = a.qa.fma3(p, d, a.neg_lr);
-            else {
-                float comp = C[i];
-                compensated_update(p, comp, d, a.lr, a.qa);
-                C[i] = comp;
-            }
-        } else if (!a.compensated) {
-            p = fma_rn(d, a.neg_lr, p);                                // p.add_(d_p, alpha=-lr)
-        } else {
-            // u = -lr * d_p; y = u - comp; s = p + y; comp = (s - p) - y
-            const float u = mul_rn(a.neg_lr, d), y = add_rn(u, -C[i]), s = add_rn(p, y);
-            C[i] = add_rn(add_rn(s, -p), -y);
-            p = s;
-        }
+        float p = P[i], g = G[i], m = rd_m ? M[i] : 0.0f, c = use_c ? C[i] : 0.0f;
+        sgd_elem(p, g, m, c, first, a);
         P[i] = p;
+        if (wr_g) G[i] = g;
+        if (use_m) M[i] = m;
+        if (use_c) C[i] = c;
     }
 }
 
+// One element of the QAdamW step.  c and vm are read only where the configuration uses them.
+__device__ __forceinline__ void adam_elem(float& p, float g, float& m, float& v, float& c, float& vm, const AdamArgs& a) {
+    m = mul_rn(m, a.beta1);                                 // exp_avg.mul_(beta1)
+    v = mul_rn(v, a.beta2);                                 // exp_avg_sq.mul_(beta2)
+    const float gg = mul_rn(g, g);
+    if (a.has_momentum_quant) {
+        m = a.qm.fma3(m, g, a.one_minus_beta1);
+        v = a.qm.fma3(v, gg, a.one_minus_beta2);
+    } else {
+        m = fma_rn(g, a.one_minus_beta1, m);                // .add_(d_p, alpha=1 - beta1)
+        v = fma_rn(a.one_minus_beta2, gg, v);               // .addcmul_(d_p, d_p, value=1 - beta2)
+    }
+    float vv = v;
+    if (a.amsgrad) {
+        vv = fmaxf(vm, v);
+        if (vm != vm || v != v) vv = __uint_as_float(0x7FC00000u);   // torch.max propagates NaN
+        vm = vv;
+    }
+    // (sqrt(v) / sqrt(bias_correction2)).add_(eps): a tensor over a Python scalar multiplies by the reciprocal
+    const float denom = add_rn(mul_rn(__fsqrt_rn(vv), a.inv_sqrt_bc2), a.eps);
+    if (a.has_acc_quant) {
+        if (!a.compensated) {
+            p = fma_rn(a.neg_step_size, __fdiv_rn(m, denom), p);    // addcdiv_(exp_avg, denom, value=-step_size)
+            p = a.qa.fma3(p, 0.0f, 0.0f);
+        } else {
+            const float u = a.qa.fma3(__fdiv_rn(m, denom), 0.0f, 0.0f);
+            compensated_update(p, c, u, a.step_size, a.qa);
+        }
+    } else if (!a.compensated) {
+        p = fma_rn(a.neg_step_size, __fdiv_rn(m, denom), p);
+    } else {
+        // u = -step_size * exp_avg / denom; y = u - comp; s = p + y; comp = (s - p) - y
+        const float u = __fdiv_rn(mul_rn(a.neg_step_size, m), denom), y = add_rn(u, -c), s = add_rn(p, y);
+        c = add_rn(add_rn(s, -p), -y);
+        p = s;
+    }
+}
+
+// The QAdamW step over a thread's elements, phase by phase (see sgd_block).  Same operations as adam_elem.
+__device__ __forceinline__ uint32_t adam_block(float (&p)[kOptPer], const float (&g)[kOptPer], float (&m)[kOptPer], float (&v)[kOptPer],
+                                               float (&c)[kOptPer], float (&vm)[kOptPer], const AdamArgs& a) {
+    uint32_t rare = 0u;
+    float q[kOptPer];                                      // exp_avg / denom
+    if (a.has_momentum_quant) {
+#pragma unroll
+        MPT_EACH {
+            m[e] = a.qm.line3(mul_rn(m[e], a.beta1), g[e], a.one_minus_beta1, rare);
+            v[e] = a.qm.line3(mul_rn(v[e], a.beta2), mul_rn(g[e], g[e]), a.one_minus_beta2, rare);
+        }
+    } else {
+#pragma unroll
+        MPT_EACH {
+            m[e] = fma_rn(g[e], a.one_minus_beta1, mul_rn(m[e], a.beta1));
+            v[e] = fma_rn(a.one_minus_beta2, mul_rn(g[e], g[e]), mul_rn(v[e], a.beta2));
+        }
+    }
+    if (a.amsgrad) {
+#pragma unroll
+        MPT_EACH {
+            float vv = fmaxf(vm[e], v[e]);
+            if (vm[e] != vm[e] || v[e] != v[e]) vv = __uint_as_float(0x7FC00000u);
+            vm[e] = vv;
+            q[e] = vv;
+        }
+    } else {
+#pragma unroll
+        MPT_EACH q[e] = v[e];
+    }
+    const bool scale_first = !a.has_acc_quant && a.compensated;      // that branch multiplies by -step_size before dividing
+#pragma unroll
+    MPT_EACH {
+        const float denom = add_rn(mul_rn(__fsqrt_rn(q[e]), a.inv_sqrt_bc2), a.eps);
+        q[e] = __fdiv_rn(scale_first ? mul_rn(a.neg_step_size, m[e]) : m[e], denom);
+    }
+    if (a.has_acc_quant) {
+        if (!a.compensated) {
+#pragma unroll
+            MPT_EACH p[e] = a.qa.line3(fma_rn(a.neg_step_size, q[e], p[e]), 0.0f, 0.0f, rare);
+        } else {
+#pragma unroll
+            MPT_EACH compensated_line(p[e], c[e], a.qa.line3(q[e], 0.0f, 0.0f, rare), a.step_size, a.qa, rare);
+        }
+    } else if (!a.compensated) {
+#pragma unroll
+        MPT_EACH p[e] = fma_rn(a.neg_step_size, q[e], p[e]);
+    } else {
+#pragma unroll
+        MPT_EACH {
+            const float y = add_rn(q[e], -c[e]), s = add_rn(p[e], y);
+            c[e] = add_rn(add_rn(s, -p[e]), -y);
+            p[e] = s;
+        }
+    }
+    return rare;
+}
+
+__device__ __noinline__ void adam_redo(float* P, const float* G, float* M, float* V, float* C, float* VM, int64_t base, const AdamArgs& a) {
+    const bool use_c = a.compensated != 0, use_vm = a.amsgrad != 0;
+#pragma unroll 1
+    for (int e = 0; e < kOptPer; ++e) {
+        const int64_t i = base + (int64_t)(e >> 2) * (kThreads * 4) + (e & 3);
+        float p = P[i], m = M[i], v = V[i], c = use_c ? C[i] : 0.0f, vm = use_vm ? VM[i] : 0.0f;
+        adam_elem(p, G[i], m, v, c, vm, a);
+        P[i] = p;
+        M[i] = m;
+        V[i] = v;
+        if (use_c) C[i] = c;
+        if (use_vm) VM[i] = vm;
+    }
+}
+
+template <bool LINE>
 __global__ void __launch_bounds__(kThreads) qadamw_kernel(const __grid_constant__ OptTable t, const __grid_constant__ AdamArgs a) {
     const int k = find_tensor(t, blockIdx.x);
     float* __restrict__ P = t.param[k];
@@ -140,50 +406,46 @@ __global__ void __launch_bounds__(kThreads) qadamw_kernel(const __grid_constant_
     float* __restrict__ V = t.buf1[k];
     float* __restrict__ C = t.buf2[k];
     float* __restrict__ VM = t.buf3[k];
+    const bool use_c = a.compensated != 0, use_vm = a.amsgrad != 0;
     const int64_t begin = (int64_t)(blockIdx.x - t.first_block[k]) * kOptChunk;
     const int64_t end = begin + kOptChunk < t.n[k] ? begin + kOptChunk : t.n[k];
-    for (int64_t i = begin + threadIdx.x; i < end; i += kThreads) {
-        const float g = G[i];
-        float p = P[i], m = mul_rn(M[i], a.beta1), v = mul_rn(V[i], a.beta2);       // exp_avg.mul_(beta1), exp_avg_sq.mul_(beta2)
-        const float gg = mul_rn(g, g);
-        if (a.has_momentum_quant) {
-            m = a.qm.fma3(m, g, a.one_minus_beta1);
-            v = a.qm.fma3(v, gg, a.one_minus_beta2);
-        } else {
-            m = fma_rn(g, a.one_minus_beta1, m);            // .add_(d_p, alpha=1 - beta1)
-            v = fma_rn(a.one_minus_beta2, gg, v);           // .addcmul_(d_p, d_p, value=1 - beta2)
+    if (LINE && (t.flags[k] & kOptAligned) && end - begin == kOptChunk) {
+        const int64_t base = begin + (int64_t)threadIdx.x * 4;
+        float p[kOptPer], g[kOptPer], m[kOptPer], v[kOptPer], c[kOptPer], vm[kOptPer];
+#pragma unroll
+        for (int h = 0; h < kOptVecs; ++h) {
+            const int64_t i = base + (int64_t)h * (kThreads * 4);
+            ld4(P + i, p + 4 * h);
+            ld4(G + i, g + 4 * h);
+            ld4(M + i, m + 4 * h);
+            ld4(V + i, v + 4 * h);
+            if (use_c) ld4(C + i, c + 4 * h); else zero4(c + 4 * h);
+            if (use_vm) ld4(VM + i, vm + 4 * h); else zero4(vm + 4 * h);
         }
+        if (adam_block(p, g, m, v, c, vm, a)) { adam_redo(P, G, M, V, C, VM, base, a); return; }
+#pragma unroll
+        for (int h = 0; h < kOptVecs; ++h) {
+            const int64_t i = base + (int64_t)h * (kThreads * 4);
+            st4(P + i, p + 4 * h);
+            st4(M + i, m + 4 * h);
+            st4(V + i, v + 4 * h);
+            if (use_c) st4(C + i, c + 4 * h);
+            if (use_vm) st4(VM + i, vm + 4 * h);
+        }
+        return;
+    }
+    for (int64_t i = begin + threadIdx.x; i < end; i += kThreads) {
+        float p = P[i], m = M[i], v = V[i], c = use_c ? C[i] : 0.0f, vm = use_vm ? VM[i] : 0.0f;
+        adam_elem(p, G[i], m, v, c, vm, a);
+        P[i] = p;
         M[i] = m;
         V[i] = v;
-        float vv = v;
-        if (a.amsgrad) {
-            vv = fmaxf(VM[i], v);
-            if (VM[i] != VM[i] || v != v) vv = __uint_as_float(0x7FC00000u);   // torch.max propagates NaN
-            VM[i] = vv;
-        }
-        // (sqrt(v) / sqrt(bias_correction2)).add_(eps): a tensor over a Python scalar multiplies by the reciprocal
-        const float denom = add_rn(mul_rn(__fsqrt_rn(vv), a.inv_sqrt_bc2), a.eps);
-        if (a.has_acc_quant) {
-            if (!a.compensated) {
-                p = fma_rn(a.neg_step_size, __fdiv_rn(m, denom), p);    // addcdiv_(exp_avg, denom, value=-step_size)
-                p = a.qa.fma3(p, 0.0f, 0.0f);
-            } else {
-                const float u = a.qa.fma3(__fdiv_rn(m, denom), 0.0f, 0.0f);
-                float comp = C[i];
-                compensated_update(p, comp, u, a.step_size, a.qa);
-                C[i] = comp;
-            }
-        } else if (!a.compensated) {
-            p = fma_rn(a.neg_step_size, __fdiv_rn(m, denom), p);
-        } else {
-            // u = -step_size * exp_avg / denom; y = u - comp; s = p + y; comp = (s - p) - y
-            const float u = __fdiv_rn(mul_rn(a.neg_step_size, m), denom), y = add_rn(u, -C[i]), s = add_rn(p, y);
-            C[i] = add_rn(add_rn(s, -p), -y);
-            p = s;
-        }
-        P[i] = p;
+        if (use_c) C[i] = c;
+        if (use_vm) VM[i] = vm;
     }
 }
+
+#undef MPT_EACH
 
 template <class Args, class Kernel>
 int launch_optim(const mpt_optim_tensor* tensors, int count, const Args& args, Kernel kern, bool need0, bool need1, bool need2, bool need3,
@@ -198,7 +460,8 @@ int launch_optim(const mpt_optim_tensor* tensors, int count, const Args& args, K
             const int64_t nb = (x.n + kOptChunk - 1) / kOptChunk;
             if (nb > 0x3FFFFFFF - blocks) break;
             t.param[k] = x.param; t.grad[k] = x.grad; t.buf0[k] = x.buf0; t.buf1[k] = x.buf1; t.buf2[k] = x.buf2; t.buf3[k] = x.buf3;
-            t.n[k] = x.n; t.flags[k] = x.flags; t.first_block[k] = blocks;
+            const uintptr_t bits = (uintptr_t)x.param | (uintptr_t)x.grad | (uintptr_t)x.buf0 | (uintptr_t)x.buf1 | (uintptr_t)x.buf2 | (uintptr_t)x.buf3;
+            t.n[k] = x.n; t.flags[k] = (x.flags & ~kOptAligned) | ((bits & 15) == 0 ? kOptAligned : 0); t.first_block[k] = blocks;
             blocks += (int)nb;
             ++k;
         }
@@ -290,7 +553,8 @@ int mpt_qsgd_step(const mpt_optim_tensor* tensors, int count, float lr, float mo
     a.has_momentum_quant = momentum_quant != 0; a.has_acc_quant = acc_quant != 0;
     a.qm = make_rounder(momentum_quant, man_mom, exp_mom, subnormals, saturate);
     a.qa = make_rounder(acc_quant, man_acc, exp_acc, subnormals, saturate);
-    return launch_optim(tensors, count, a, qsgd_kernel, need_m, need_c, false, false, as_stream(stream), who);
+    const bool line = a.qm.mode != 2 && a.qa.mode != 2;
+    return launch_optim(tensors, count, a, line ? qsgd_kernel<true> : qsgd_kernel<false>, need_m, need_c, false, false, as_stream(stream), who);
 }
 
 int mpt_qadamw_step(const mpt_optim_tensor* tensors, int count, float beta1, float beta2, float one_minus_beta1,
@@ -309,7 +573,8 @@ int mpt_qadamw_step(const mpt_optim_tensor* tensors, int count, float beta1, flo
     a.has_momentum_quant = momentum_quant != 0; a.has_acc_quant = acc_quant != 0;
     a.qm = make_rounder(momentum_quant, man_mom, exp_mom, subnormals, saturate);
     a.qa = make_rounder(acc_quant, man_acc, exp_acc, subnormals, saturate);
-    return launch_optim(tensors, count, a, qadamw_kernel, true, true, compensated != 0, amsgrad != 0, as_stream(stream), who);
+    const bool line = a.qm.mode != 2 && a.qa.mode != 2;
+    return launch_optim(tensors, count, a, line ? qadamw_kernel<true> : qadamw_kernel<false>, true, true, compensated != 0, amsgrad != 0, as_stream(stream), who);
 }
 
 size_t mpt_scale_quantize_workspace_bytes(int64_t matrices) { return sizeof(uint32_t) * (size_t)(matrices < 1 ? 1 : matrices); }

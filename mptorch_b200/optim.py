@@ -152,7 +152,7 @@ def _fusable_pair(mq, aq):
             return None
     nums = [q.number for q in (mq, aq) if q is not None]
     if not nums:
-        return None
+        return (None, None, True, True)       # plain fp32 arithmetic: the same kernel with both quantizers off
     if any((n.subnormals, n.saturate) != (nums[0].subnormals, nums[0].saturate) for n in nums):
         return None
     return (mq.number if mq is not None else None, aq.number if aq is not None else None, nums[0].subnormals, nums[0].saturate)

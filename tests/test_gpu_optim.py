@@ -206,7 +206,7 @@ SGD_CONFIGS = [
 
 
 @pytest.mark.parametrize("cfg", SGD_CONFIGS)
-@pytest.mark.parametrize("fmts", [((8, 7), (8, 7)), ((5, 10), (5, 2)), (None, (4, 3)), ((5, 2), None), ((3, 0), (1, 3))])
+@pytest.mark.parametrize("fmts", [((8, 7), (8, 7)), ((5, 10), (5, 2)), (None, (4, 3)), ((5, 2), None), ((3, 0), (1, 3)), (None, None)])
 def test_qsgd_fused_step_equals_per_tensor_steps(cfg, fmts):
     """One fused launch per step against the reference's per-tensor sequence of torch kernels and quantizer calls,
     on identical parameters and gradients, bit for bit, buffers included."""
@@ -242,7 +242,7 @@ ADAM_CONFIGS = [
 
 
 @pytest.mark.parametrize("cfg", ADAM_CONFIGS)
-@pytest.mark.parametrize("fmts", [((8, 7), (8, 7)), ((5, 10), (5, 2)), (None, (4, 3)), ((5, 10), None)])
+@pytest.mark.parametrize("fmts", [((8, 7), (8, 7)), ((5, 10), (5, 2)), (None, (4, 3)), ((5, 10), None), (None, None)])
 def test_qadamw_fused_step_equals_per_tensor_steps(cfg, fmts):
     from mptorch_b200 import FloatingPoint
     from mptorch_b200.optim import QAdamW, fma_quantizer
@@ -265,6 +265,59 @@ def test_qadamw_fused_step_equals_per_tensor_steps(cfg, fmts):
             for key in ("exp_avg", "exp_avg_sq", "max_exp_avg_sq", "compensated_buffer"):
                 if key in ob.state[y]:
                     assert _same(oa.state[x][key], ob.state[y][key]), (key, step, i, cfg, fmts)
+
+
+def _awkward(n, g, scale):
+    """Values around every special case of a rounding to an 8-bit-exponent format: zeros of both signs, fp32
+    denormals, the smallest normals, magnitudes next to the top of the range, infinities and NaN, among ordinary ones."""
+    x = torch.randn(n, generator=g) * scale
+    special = torch.tensor([0.0, -0.0, 1e-45, -3e-42, 1.1754942e-38, 1.1754944e-38, -1.2e-38, 3.3e38, -3.4e38, 3.4028235e38,
+                            float("inf"), float("-inf"), float("nan"), 1e-30, -1e30, 2.5e-39])
+    idx = torch.randperm(n, generator=g)[: 8 * special.numel()]
+    x[idx] = special.repeat(8)
+    return x
+
+
+@pytest.mark.parametrize("opt", ["sgd", "sgd_comp", "adamw", "adamw_comp"])
+@pytest.mark.parametrize("fmt", [(8, 7), (8, 3), (5, 10)])
+def test_fused_steps_with_denormals_extremes_and_nonfinite_values(opt, fmt):
+    """Whole 2048-element chunks (the vector path of the fused kernels) holding inputs that the straight-line rounding
+    hands to the exact caster; the per-tensor sequence of torch kernels and quantizer calls is the reference."""
+    from mptorch_b200 import FloatingPoint
+    from mptorch_b200.optim import QAdamW, QSGD, fma_quantizer
+
+    g = torch.Generator().manual_seed(21)
+    q = fma_quantizer(FloatingPoint(fmt[0], fmt[1], True, True))
+    n = 3 * 2048 + 17
+    base = _awkward(n, g, 1.0)
+    pa, pb = [torch.nn.Parameter(base.clone().cuda())], [torch.nn.Parameter(base.clone().cuda())]
+    comp = opt.endswith("comp")
+    if opt.startswith("sgd"):
+        oa = QSGD(pa, lr=0.05, momentum=0.9, momentum_quant=q, acc_quant=q, compensated=comp)
+        ob = QSGD(pb, lr=0.05, momentum=0.9, momentum_quant=q, acc_quant=q, compensated=comp, fused=False)
+        keys = ("momentum_buffer", "compensated_buffer")
+    else:
+        oa = QAdamW(pa, lr=0.01, momentum_quant=q, acc_quant=q, compensated=comp)
+        ob = QAdamW(pb, lr=0.01, momentum_quant=q, acc_quant=q, compensated=comp, fused=False)
+        keys = ("exp_avg", "exp_avg_sq", "compensated_buffer")
+    for step in range(3):
+        gr = _awkward(n, g, 10.0 ** (step - 1)).cuda()
+        pa[0].grad, pb[0].grad = gr.clone(), gr.clone()
+        oa.step()
+        ob.step()
+        assert _same_or_nan(pa[0].data, pb[0].data), (opt, fmt, step)
+        for key in keys:
+            if key in ob.state[pb[0]]:
+                assert _same_or_nan(oa.state[pa[0]][key], ob.state[pb[0]][key]), (key, opt, fmt, step)
+
+
+def _same_or_nan(a, b):
+    """Bit equality where either side is a number; a NaN must be a NaN on the other side (its payload is the
+    arithmetic unit's business)."""
+    a, b = a.detach().contiguous(), b.detach().contiguous()
+    both_nan = a.isnan() & b.isnan()
+    eq = a.view(torch.int32) == b.view(torch.int32)
+    return bool((eq | both_nan).all())
 
 
 @pytest.mark.parametrize("name", ["sgd_mom_acc", "sgd_mom_acc_comp", "sgd_mom_damp_comp_e5m2", "sgd_mom_only"])
