@@ -59,7 +59,7 @@ def test_fma_quantizer_is_recognised_only_for_nearest_float_formats():
     q = fma_quantizer(f)
     assert _fusable_pair(q, q) == (f, f, True, True)
     assert _fusable_pair(None, q) == (None, f, True, True)
-    assert _fusable_pair(None, None) is None
+    assert _fusable_pair(None, None) == (None, None, True, True)      # plain fp32 steps fuse too
     assert _fusable_pair(lambda x, y, z: x, q) is None
     assert _fusable_pair(fma_quantizer(f, "stochastic"), q) is None
     assert _fusable_pair(fma_quantizer(FloatingPoint(8, 7, True, False)), q) is None
