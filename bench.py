@@ -356,6 +356,26 @@ def kernels_legs(dev, steps: int, warmup: int, scale: float = 1.0, with_referenc
             qmod.implicit_conv_eligible = eligible
     for k in ("qconv2d_fwd_implicit_gemm", "qconv2d_fwd_unfold_gemm"):
         out[k] = {"ms": out[k]["ms"], "gmacs": round(conv_macs / out[k]["ms"] / 1e6, 1)}
+    del xc, conv
+    # fused optimizer steps over the parameter tensors of a GPT-2-small (embeddings + one block, 46.5 M parameters):
+    # QSGD with momentum and QAdamW, momentum / moments and weights in e8m7 with the Kahan compensation buffer
+    from mptorch_b200.optim import QAdamW, QSGD, fma_quantizer
+
+    shapes = [(50257, 768), (1024, 768), (768,), (768,), (2304, 768), (2304,), (768, 768), (768,), (768,), (768,), (3072, 768), (3072,),
+              (768, 3072), (768,)]
+    if scale < 1.0:
+        shapes[0] = (max(1024, int(50257 * scale)), 768)
+    params = [torch.nn.Parameter(torch.randn(*s, device=dev, generator=g)) for s in shapes]
+    for p_ in params:
+        p_.grad = torch.randn(p_.shape, device=dev, generator=g) * 0.01
+    npar = sum(p_.numel() for p_ in params)
+    accq = fma_quantizer(FloatingPoint(8, 7, True, True))
+    sgd = QSGD(params, lr=1e-3, momentum=0.9, momentum_quant=accq, acc_quant=accq, compensated=True)
+    sgd.step()                                   # creates the momentum buffers
+    timed("qsgd_fused_step_e8m7_compensated", sgd.step, 32 * npar)          # weight, gradient, momentum, compensation read; all but the gradient written
+    adam = QAdamW(params, lr=1e-3, momentum_quant=accq, acc_quant=accq, compensated=True)
+    adam.step()
+    timed("qadamw_fused_step_e8m7_compensated", adam.step, 36 * npar)
     return {"hbm_peak_gbs": hbm_peak, "unit": "GB/s at algorithmic bytes", "kernels": out}
 
 
