@@ -314,10 +314,13 @@ template <int MODE>
 __device__ __forceinline__ float rr(const Caster& c, float x, bool& odd) {
     if (MODE == 0) return c.fast(x);
     if (MODE == 2) {
+        // t + t drops the sign bit, so one three-input add and one compare find a nonzero fp32 denormal.  A zero result
+        // can only come from a zero input here (8-bit-exponent formats have subnormals below every fp32 normal, and
+        // denormal inputs leave this path), so OR-ing the input's sign in, where the format keeps it, restores -0.
         const uint32_t t = __float_as_uint(x);
-        odd |= ((t & 0x7FFFFFFFu) - 1u < 0x007FFFFFu);
+        odd |= (t + t - 1u < 0x00FFFFFFu);
         const float r = c.fast.fast(x);
-        return t == 0x80000000u ? __uint_as_float(c.neg_zero) : r;
+        return __uint_as_float(__float_as_uint(r) | (t & c.neg_zero));
     }
     return c.fast.fast(x);
 }
@@ -334,7 +337,7 @@ struct RAdd {
 // subnormal is larger).
 template <int MODE>
 __device__ __forceinline__ float row_div(float a, float b, float r, bool& odd) {
-    if (MODE == 2) odd |= ((__float_as_uint(a) & 0x7FFFFFFFu) - 1u < 0x16000000u - 1u);
+    if (MODE == 2) { const uint32_t t = __float_as_uint(a); odd |= (t + t - 1u < 0x2BFFFFFEu); }
     return div_with_rcp(a, b, r);
 }
 
