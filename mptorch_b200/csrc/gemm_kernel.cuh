@@ -46,6 +46,9 @@ namespace mpt {
 #ifndef MPT_MM_MIN_CTAS
 #define MPT_MM_MIN_CTAS 2    // resident CTAs per SM the register allocation is held to
 #endif
+#ifndef MPT_MM_SR_MIN_CTAS
+#define MPT_MM_SR_MIN_CTAS 1 // the same for the stochastic kernel
+#endif
 constexpr int TM = MPT_MM_TM, TN = 4;
 constexpr int BM = 16 * TM, BN = 64, BK = 32;
 constexpr int THREADS = 256;
@@ -793,10 +796,10 @@ inline bool use_packed() {
 template <int ALGO, bool FMA>
 int launch_mm(const MmParams& p, int64_t batch, bool vec, cudaStream_t st) {
     dim3 grid((unsigned)(((int64_t)p.N + BN - 1) / BN), (unsigned)(((int64_t)p.M + BM - 1) / BM), (unsigned)batch);
-    // The stochastic kernel has one form (scalar, both clamps).  It interleaves many Philox chains per thread: one CTA
-    // per SM with twice the registers (no spills) is a few per cent faster than two.
+    if (grid.y > 65535u) { set_error("float_mm: M=%d has more than 65535 row tiles of %d", p.M, BM); return MPT_ERR_INVALID_ARGUMENT; }
+    // The stochastic kernel has one form (scalar, both clamps); its translation unit picks tile height and residency.
     constexpr bool kHasFast = ALGO != ALGO_SR;
-    constexpr int kMinB = ALGO == ALGO_SR ? 1 : MPT_MM_MIN_CTAS;
+    constexpr int kMinB = ALGO == ALGO_SR ? MPT_MM_SR_MIN_CTAS : MPT_MM_MIN_CTAS;
     const bool packed = kHasFast && use_packed();
     // the sum rounding needs its subnormal clamp only if products can carry bits below the add format's
     // smallest subnormal (always the case for a fused multiply-add, whose sum is not a sum of rounded values)
