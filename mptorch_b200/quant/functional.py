@@ -16,6 +16,51 @@ from .quant_function import (mp_bmm, mp_layernorm_backward, mp_layernorm_forward
 __all__ = ["qlinear", "qconv2d", "qmm", "qmatmul", "qsoftmax", "qlayernorm", "qsum", "compute_bias", "scale", "unscale"]
 
 
+# ------------------------------------------------------------------------------------------ two gradients at once
+# The two GEMMs of a layer's backward pass (gradient of the input, gradient of the weight or of the other operand) do
+# not depend on one another, and neither fills the GPU evenly: a [8192, 768] result is 2.59 waves of CTAs, a weight
+# gradient a fraction of one wave with a long K.  Launched on two streams, the CTAs of one fill the SMs the other
+# leaves idle.  The results do not change: each kernel computes what it would compute alone.
+overlap_backward_gemms = True
+_side_streams: dict[int, "torch.cuda.Stream"] = {}
+
+
+class _second_gradient:
+    """Context for the second gradient of a backward pass: on a CUDA device (and with the switch above on) its body
+    runs on a side stream that starts after everything the current stream held when the object was made (so the first
+    gradient, launched in between, does not hold it back); ``join`` makes the current stream wait for it and hands the
+    tensors made there over to the current stream.  The host-side order of the calls, and with it the order in which
+    stochastic quantizers draw their seeds, stays that of the reference."""
+
+    def __init__(self, like: torch.Tensor, enabled: bool = True):
+        self.main = self.side = None
+        if enabled and overlap_backward_gemms and like.is_cuda and not torch.cuda.is_current_stream_capturing():
+            dev = like.device.index if like.device.index is not None else torch.cuda.current_device()
+            if dev not in _side_streams:
+                _side_streams[dev] = torch.cuda.Stream(device=dev)
+            self.main, self.side = torch.cuda.current_stream(like.device), _side_streams[dev]
+            self.fork = self.main.record_event()
+
+    def __enter__(self):
+        if self.side is not None:
+            self.side.wait_event(self.fork)
+            self._ctx = torch.cuda.stream(self.side)
+            self._ctx.__enter__()
+        return self
+
+    def __exit__(self, *exc):
+        if self.side is not None:
+            self._ctx.__exit__(*exc)
+        return False
+
+    def join(self, *tensors):
+        if self.side is not None:
+            self.main.wait_stream(self.side)
+            for t in tensors:
+                if t is not None:
+                    t.record_stream(self.main)
+
+
 # ------------------------------------------------------------------------------------------ tensor scaling
 def compute_bias(x: torch.Tensor, cast_to: FloatType, margin: int) -> torch.Tensor:
     """Power-of-two exponent that maps the largest magnitude of each matrix onto ``cast_to``'s largest normal value
@@ -170,6 +215,7 @@ class qlinear_kernel(torch.autograd.Function):
         f = ctx.formats
         qgrad_input = qgrad_weight = qgrad_bias = None
         qgrad_output, grad_scale = _quantize_grad(f, grad_output)
+        second = _second_gradient(qgrad_output, ctx.needs_input_grad[0] and ctx.needs_input_grad[1])
         if ctx.needs_input_grad[0]:
             if f.bwd_use_default_prec:
                 qgrad_input = torch.matmul(qgrad_output, qweight)
@@ -177,13 +223,15 @@ class qlinear_kernel(torch.autograd.Function):
                 qgrad_input = mp_bmm(qgrad_output, qweight, formats=f, use_forward=False)
             qgrad_input = f.grad_quant(_unscale(qgrad_input, grad_scale + ctx.weight_scale))
         if ctx.needs_input_grad[1]:
-            if f.bwd_use_default_prec:
-                qgrad_weight = torch.matmul(qgrad_output.transpose(-2, -1), qinput)
-            else:
-                # for >2-D inputs this is a batched GEMM; autograd sums the [batch, out, in] result over the batch
-                # in plain fp32 when it reduces the gradient to the weight's shape, exactly as in the reference
-                qgrad_weight = mp_bmm(qgrad_output.transpose(-2, -1), qinput, formats=f, use_forward=False)
-            qgrad_weight = f.grad_quant(_unscale(qgrad_weight, grad_scale + ctx.input_scale))
+            with second:
+                if f.bwd_use_default_prec:
+                    qgrad_weight = torch.matmul(qgrad_output.transpose(-2, -1), qinput)
+                else:
+                    # for >2-D inputs this is a batched GEMM; autograd sums the [batch, out, in] result over the batch
+                    # in plain fp32 when it reduces the gradient to the weight's shape, exactly as in the reference
+                    qgrad_weight = mp_bmm(qgrad_output.transpose(-2, -1), qinput, formats=f, use_forward=False)
+                qgrad_weight = f.grad_quant(_unscale(qgrad_weight, grad_scale + ctx.input_scale))
+        second.join(qgrad_weight)
         if qbias is not None and ctx.needs_input_grad[2]:
             lead = tuple(range(qgrad_output.dim() - 1))
             if f.bwd_use_default_prec:
@@ -277,15 +325,19 @@ class qconv2d_kernel(torch.autograd.Function):
         grad_scale = 0                # the implicit path is taken only without tensor scaling (implicit_conv_eligible)
         gin, gws, gbs = [], [], []
         implicit_w = ctx.needs_input_grad[1] and implicit_wgrad_eligible(f)
+        # the implicit weight gradient runs beside the per-group input gradients (its quantizer is deterministic, so
+        # the order of the calls does not matter to any random stream)
+        second = _second_gradient(grad_output, bool(implicit_w and ctx.needs_input_grad[0]))
         if implicit_w:
             from .. import backend as _be
 
-            qgo_all = f.grad_quant(grad_output).contiguous().float()         # elementwise: the values the per-group path sees
-            gw_all = torch.empty(c_out, cg * kh * kw, device=grad_output.device)
-            _be.float_conv2d_wgrad_nearest(qgo_all, qinput.float(), gw_all, groups, (kh, kw), stride, padding, dilation, f.bwd_add.man,
-                                           f.bwd_add.exp, f.bwd_mul.man, f.bwd_mul.exp, f.bwd_add.subnormals, f.bwd_add.saturate,
-                                           fma=f.bwd_fma)
-            gws.append(f.grad_quant(gw_all).view(c_out, cg, kh, kw))
+            with second:
+                qgo_all = f.grad_quant(grad_output).contiguous().float()     # elementwise: the values the per-group path sees
+                gw_all = torch.empty(c_out, cg * kh * kw, device=grad_output.device)
+                _be.float_conv2d_wgrad_nearest(qgo_all, qinput.float(), gw_all, groups, (kh, kw), stride, padding, dilation,
+                                               f.bwd_add.man, f.bwd_add.exp, f.bwd_mul.man, f.bwd_mul.exp, f.bwd_add.subnormals,
+                                               f.bwd_add.saturate, fma=f.bwd_fma)
+                gws.append(f.grad_quant(gw_all).view(c_out, cg, kh, kw))
         for g in range(groups):
             go = grad_output[:, g * og:(g + 1) * og]
             go2 = go.reshape(n, og, -1).transpose(1, 2).reshape(-1, og)              # [N * L, og], as qlinear sees it
@@ -311,6 +363,7 @@ class qconv2d_kernel(torch.autograd.Function):
                         else:
                             gb = qsum(qgo, dim=(0,), quant=make_quant_function(f.bwd_add, f.bwd_rnd, f.rbits_add))
                 gbs.append(f.grad_quant(gb.reshape(-1)))
+        second.join(*gws)
         grad_input = torch.cat(gin, dim=1) if gin else None
         grad_weight = torch.cat(gws, dim=0) if gws else None
         grad_bias = torch.cat(gbs, dim=0) if gbs else None
@@ -345,6 +398,7 @@ def _matmul_function(fwd_default, mp_fn, name, requantize_unscaled):
             f = ctx.formats
             qgrad_input = qgrad_other = None
             qgrad_output, grad_scale = _quantize_grad(f, grad_output)
+            second = _second_gradient(qgrad_output, ctx.needs_input_grad[0] and ctx.needs_input_grad[1])
             if ctx.needs_input_grad[0]:
                 if f.bwd_use_default_prec:
                     g = fwd_default(qgrad_output, qother.transpose(-2, -1))
@@ -353,11 +407,13 @@ def _matmul_function(fwd_default, mp_fn, name, requantize_unscaled):
                 # the reference's qmm quantizes the un-unscaled gradient (functional.py:270-272); qmatmul the unscaled one
                 qgrad_input = f.grad_quant(_unscale(g, grad_scale + ctx.weight_scale) if requantize_unscaled else g)
             if ctx.needs_input_grad[1]:
-                if f.bwd_use_default_prec:
-                    g = fwd_default(qinput.transpose(-2, -1), qgrad_output)
-                else:
-                    g = mp_fn(qinput.transpose(-2, -1), qgrad_output, formats=f, use_forward=False)
-                qgrad_other = f.grad_quant(_unscale(g, grad_scale + ctx.input_scale) if requantize_unscaled else g)
+                with second:
+                    if f.bwd_use_default_prec:
+                        g = fwd_default(qinput.transpose(-2, -1), qgrad_output)
+                    else:
+                        g = mp_fn(qinput.transpose(-2, -1), qgrad_output, formats=f, use_forward=False)
+                    qgrad_other = f.grad_quant(_unscale(g, grad_scale + ctx.input_scale) if requantize_unscaled else g)
+            second.join(qgrad_other)
             return qgrad_input, qgrad_other, None
 
     kernel.__name__ = name

@@ -240,3 +240,36 @@ def test_fused_tensor_scaling_equals_reference_sequence():
             Fq._float_nearest_spec = spec
     for a, b in zip(*outs):
         assert torch.equal(a.view(torch.int32), b.view(torch.int32))
+
+
+@pytest.mark.parametrize("grad_rounding", ["nearest", "stochastic"])
+def test_two_stream_backward_equals_one_stream_backward(grad_rounding):
+    """The input gradient and the weight gradient of a layer are launched on two streams; gradients, repeated steps and
+    a stochastic gradient quantizer (seeds drawn on the host in the same order) give the bits of the one-stream pass."""
+    add, mul = fp(5, 10, True, False), fp(4, 3, True, False)
+    fmt = q.QAffineFormats(fwd_mac=(add, mul), bwd_mac=(add, mul), fwd_rnd="nearest", bwd_rnd="nearest",
+                           weight_quant=(fp(4, 3, True, True), "nearest"), input_quant=(fp(4, 3, True, True), "nearest"),
+                           grad_quant=(fp(5, 2, True, True), grad_rounding))
+    results = []
+    for overlap in (True, False):
+        Fq.overlap_backward_gemms = overlap
+        try:
+            torch.manual_seed(5)
+            lin1, lin2 = q.QLinear(192, 320, fmt, bias=True).cuda(), q.QLinear(320, 64, fmt, bias=True).cuda()
+            x = torch.randn(4, 256, 192, device="cuda", requires_grad=True)
+            a = torch.randn(2, 3, 128, 64, device="cuda", requires_grad=True)
+            b = torch.randn(2, 3, 64, 96, device="cuda", requires_grad=True)
+            out = []
+            for step in range(3):
+                for t in (x, a, b, *lin1.parameters(), *lin2.parameters()):
+                    t.grad = None
+                y = lin2(torch.nn.functional.gelu(lin1(x)))
+                z = Fq.qmatmul(a, b, fmt)
+                (y.square().mean() + z.square().mean()).backward()
+                out += [t.grad.clone() for t in (x, a, b, *lin1.parameters(), *lin2.parameters())]
+            torch.cuda.synchronize()
+            results.append(out)
+        finally:
+            Fq.overlap_backward_gemms = True
+    for u, v in zip(*results):
+        assert torch.equal(u.view(torch.int32), v.view(torch.int32))
