@@ -67,6 +67,12 @@ MPT_API int mpt_version(void);
  * row-sharded GEMM runs its row panels on streams of descending priority so that a panel's tail is filled by the next. */
 MPT_API int mpt_stream_priority_range(int *lowest, int *highest);
 
+/* No counterpart in the reference (host helper of the K-panel pipeline of float_mm_streamed).  Copies `rows` rows of
+ * `width_bytes` bytes between two pitched buffers, host or device on either side (one cudaMemcpy2DAsync with
+ * cudaMemcpyDefault on `stream`): a column panel of a row-major host matrix into a dense device buffer. */
+MPT_API int mpt_copy_columns_async(void *dst, size_t dst_pitch, const void *src, size_t src_pitch, size_t width_bytes,
+                                   size_t rows, void *stream);
+
 /* ---- elementwise quantizers ------------------------------------------------------------- */
 
 /* replaces float_quantize_nearest (pybind_cuda.cpp:44 -> quant.cu:143 -> fp_kernel.cu:164) */
@@ -131,6 +137,24 @@ MPT_API int mpt_float_mm_nearest(const float *a, const float *b, float *c, int64
                                  int man_add, int exp_add, int man_mul, int exp_mul,
                                  int subnormals, int saturate, int compensated, int order,
                                  void *workspace, size_t workspace_bytes, void *stream);
+
+/* No counterpart in the reference: the product of mpt_float_mm_nearest / _fma (not compensated) computed in
+ * pieces along K, for callers whose operands arrive piece by piece (a host buffer copied in K panels while
+ * the panels before are being multiplied).  One call handles the steps k0 .. k0 + K - 1 of the full product:
+ * A: [batch, M, K] holds those columns of the full A, B: [batch, K, N] those rows of the full B, both dense.
+ *   MPT_MM_PIECE_FROM_C: C holds the running sums after the steps before k0 (written by the call for the
+ *                        piece before); without it the sums start from zero (the first piece).
+ *   MPT_MM_PIECE_MORE:   another piece follows; K must then be a multiple of 8, the group size of the CUDA
+ *                        accumulation order, and the zero padding that order walks after the last step is
+ *                        left to the last piece.
+ * The rounded running sums ARE the result so far, so the pieces in sequence perform exactly the operations
+ * of the single call and leave the same bits in C.  fma != 0 selects the fused form (man_mul / exp_mul
+ * unused). */
+enum { MPT_MM_PIECE_FROM_C = 1, MPT_MM_PIECE_MORE = 2 };
+MPT_API int mpt_float_mm_nearest_piece(const float *a, const float *b, float *c, int64_t batch, int M, int N, int K,
+                                       int man_add, int exp_add, int man_mul, int exp_mul,
+                                       int subnormals, int saturate, int fma, int order, int flags,
+                                       void *workspace, size_t workspace_bytes, void *stream);
 
 /* No counterpart in the reference.  Same computation and same results as mpt_float_mm_nearest, for
  * callers that cannot allocate device memory and therefore have no workspace to pass (an application

@@ -251,6 +251,36 @@ def _mm_nearest_fma(a, b, c, batch, M, N, K, man_fma, exp_fma, subnormals, satur
              stream_ptr(a.device))
 
 
+MM_PIECE_FROM_C, MM_PIECE_MORE = 1, 2
+
+
+def float_mm_nearest_piece(a, b, c, man_add, exp_add, man_mul, exp_mul, subnormals, saturate, fma, flags, order=None):
+    """The steps of a product that one K panel contributes (no reference counterpart; `mpt_float_mm_nearest_piece`):
+    a [M, K] and b [K, N] are the panel's columns of A and rows of B, c [M, N] carries the running sums from piece to
+    piece (MM_PIECE_FROM_C: start from what c holds; MM_PIECE_MORE: another piece follows, K a multiple of 8)."""
+    _mm_checks(a, b, c)
+    (M, K), N = a.shape, b.shape[1]
+    assert b.shape[0] == K and tuple(c.shape) == (M, N)
+    with torch.cuda.device(a.device):
+        ws = _cabi.mm_workspace(a.device, 1)
+        call("mpt_float_mm_nearest_piece", ptr(a), ptr(b), ptr(c), 1, M, N, K, man_add, exp_add, man_mul, exp_mul,
+             int(subnormals), int(saturate), int(bool(fma)), _order_code(order, "accum_order"), int(flags), ptr(ws), ws.numel(),
+             stream_ptr(a.device))
+
+
+def copy_columns_async(dst, src, col0: int, col1: int):
+    """dst[:, :] = src[:, col0:col1] for row-major float32 matrices on either side of the bus, as one pitched copy on
+    the current stream of dst's (or src's) device; dst is dense with col1 - col0 columns."""
+    assert dst.dim() == 2 and src.dim() == 2 and dst.is_contiguous() and src.is_contiguous()
+    assert dst.dtype == torch.float32 and src.dtype == torch.float32
+    rows, width = src.shape[0], col1 - col0
+    assert dst.shape == (rows, width) and 0 <= col0 <= col1 <= src.shape[1]
+    dev = dst.device if dst.is_cuda else src.device
+    with torch.cuda.device(dev):
+        call("mpt_copy_columns_async", dst.data_ptr(), 4 * width, src.data_ptr() + 4 * col0, 4 * src.shape[1], 4 * width, rows,
+             stream_ptr(dev))
+
+
 def float_quantize_nearest_mm(a, b, c, M, N, K, man_add, exp_add, man_mul, exp_mul, subnormals, saturate,
                               compensated, order=None):
     """pybind_cuda.cpp:123.  Note the (M, N, K) argument order of the reference."""

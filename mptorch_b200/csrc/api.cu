@@ -87,4 +87,17 @@ int mpt_stream_priority_range(int* lowest, int* highest) {
     return MPT_OK;
 }
 
+int mpt_copy_columns_async(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width_bytes, size_t rows,
+                           void* stream) {
+    if (rows == 0 || width_bytes == 0) return MPT_OK;
+    if (!dst || !src || width_bytes > dst_pitch || width_bytes > src_pitch) {
+        mpt::set_error("copy_columns_async: null pointer or a row wider than its pitch");
+        return MPT_ERR_INVALID_ARGUMENT;
+    }
+    const cudaError_t e = cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, width_bytes, rows, cudaMemcpyDefault,
+                                            static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) { mpt::set_error("copy_columns_async: %s", cudaGetErrorString(e)); return MPT_ERR_CUDA; }
+    return MPT_OK;
+}
+
 }

@@ -47,10 +47,11 @@ KahanBounds kahan_bounds(int man) {
 
 int run_mm(const float* a, const float* b, float* c, int64_t batch, int M, int N, int K, const AnyFmt& gadd, const AnyFmt& gmul,
            int rbits_add, int rbits_mul, bool fma, int algo, uint64_t seed, void* workspace, size_t workspace_bytes,
-           cudaStream_t st) {
+           cudaStream_t st, int resume = 0) {
     const FpFmt fadd = gadd.fp, fmul = gmul.fp;
     const bool all_float = gadd.kind == FMT_FLOAT && (fma || gmul.kind == FMT_FLOAT);
     if (batch == 0 || M == 0 || N == 0) return MPT_OK;
+    if (K == 0 && (resume & MM_FROM_C)) return MPT_OK;      // nothing to add to the sums C holds
     if (K == 0) {   // an empty sum: every order yields +0
         cudaError_t e = cudaMemsetAsync(c, 0, sizeof(float) * (size_t)batch * M * N, st);
         if (e != cudaSuccess) { set_error("float_mm: cudaMemsetAsync: %s", cudaGetErrorString(e)); return MPT_ERR_CUDA; }
@@ -59,6 +60,7 @@ int run_mm(const float* a, const float* b, float* c, int64_t batch, int M, int N
     MmParams p;
     p.a = a; p.b = b; p.c = c;
     p.M = M; p.N = N; p.K = K;
+    p.resume = resume;
     p.stride_a = (int64_t)M * K; p.stride_b = (int64_t)K * N; p.stride_c = (int64_t)M * N;
     p.fadd = fadd; p.fmul = fmul;
     p.gadd = gadd; p.gmul = fma ? gadd : gmul;
@@ -278,6 +280,23 @@ int mpt_float_mm_nearest(const float* a, const float* b, float* c, int64_t batch
     return run_mm(a, b, c, batch, M, N, K, any_float(make_fmt(man_add, exp_add, subnormals, saturate)),
                   any_float(make_fmt(man_mul, exp_mul, subnormals, saturate)), 0, 0, false, algo, 0, workspace, workspace_bytes,
                   as_stream(stream));
+}
+
+int mpt_float_mm_nearest_piece(const float* a, const float* b, float* c, int64_t batch, int M, int N, int K, int man_add,
+                               int exp_add, int man_mul, int exp_mul, int subnormals, int saturate, int fma, int order,
+                               int flags, void* workspace, size_t workspace_bytes, void* stream) {
+    int rc = check_mm_args("float_mm_nearest_piece", a, b, c, batch, M, N, K);
+    if (rc) return rc;
+    MPT_REQUIRE(valid_format(man_add, exp_add) && (fma || valid_format(man_mul, exp_mul)), "float_mm_nearest_piece: unsupported format");
+    MPT_REQUIRE(order == MPT_ORDER_SEQ || order == MPT_ORDER_CUDA, "float_mm_nearest_piece: unknown order %d", order);
+    MPT_REQUIRE((flags & ~(MPT_MM_PIECE_FROM_C | MPT_MM_PIECE_MORE)) == 0, "float_mm_nearest_piece: unknown flags %d", flags);
+    MPT_REQUIRE(!(flags & MPT_MM_PIECE_MORE) || K % 8 == 0,
+                "float_mm_nearest_piece: a piece that another follows must cover a multiple of 8 steps (K=%d)", K);
+    const AnyFmt fa = any_float(make_fmt(man_add, exp_add, subnormals, saturate));
+    const AnyFmt fm = fma ? fa : any_float(make_fmt(man_mul, exp_mul, subnormals, saturate));
+    const int resume = ((flags & MPT_MM_PIECE_FROM_C) ? MM_FROM_C : 0) | ((flags & MPT_MM_PIECE_MORE) ? MM_MORE : 0);
+    return run_mm(a, b, c, batch, M, N, K, fa, fm, 0, 0, fma != 0, order == MPT_ORDER_SEQ ? ALGO_SEQ : ALGO_TILE8, 0, workspace,
+                  workspace_bytes, as_stream(stream), resume);
 }
 
 int mpt_float_mm_nearest_static(const float* a, const float* b, float* c, int64_t batch, int M, int N, int K, int man_add,

@@ -104,7 +104,12 @@ struct MmParams {
     // format's rounding error, see kahan_bounds in gemm.cu)
     float kah_sc, kah_p, kah_const;
     float growth8_sr;            // upper bound of (1 + 2^-man_add)^8: eight stochastic roundings of a sum
+    // A product computed in pieces along K (ALGO_SEQ / ALGO_TILE8 only; every piece but the last a multiple of 8 steps):
+    // MM_FROM_C starts the running sums from what C holds (the sums after the pieces before) instead of zero,
+    // MM_MORE says another piece follows, so the zero padding the CUDA order walks after the last step is left to it.
+    int resume = 0;
 };
+enum { MM_FROM_C = 1, MM_MORE = 2 };
 
 // Nearest rounding to the add / multiply format on the whole input domain.  The exact caster is an out-of-line call
 // (taken for formats without the fast rounding, and for the tiny or huge inputs 8-bit-exponent formats treat
@@ -629,7 +634,7 @@ __global__ void __launch_bounds__(THREADS, MINB) mm_kernel(const __grid_constant
 
     // number of accumulation steps walked: exactly K for the sequential order, the zero-padded
     // range K + 8 - K % 8 for every order that follows the reference CUDA kernels
-    const int ksteps = (ALGO == ALGO_SEQ) ? p.K : p.K + 8 - p.K % 8;
+    const int ksteps = (ALGO == ALGO_SEQ || (p.resume & MM_MORE)) ? p.K : p.K + 8 - p.K % 8;
     const int ntiles = (ksteps + BK - 1) / BK;
 
     const FastPlan plan = make_plan<ALGO, FMA>(p, batch);
@@ -659,6 +664,18 @@ __global__ void __launch_bounds__(THREADS, MINB) mm_kernel(const __grid_constant
     for (int i = 0; i < TM; ++i)
 #pragma unroll
         for (int j = 0; j < TN; ++j) { acc[i][j] = 0.0f; aux[i][j] = 0.0f; }
+    if (CONV == CONV_NONE && (ALGO == ALGO_SEQ || ALGO == ALGO_TILE8) && (p.resume & MM_FROM_C)) {
+#pragma unroll
+        for (int i = 0; i < TM; ++i) {
+            const int gm = m0 + ty + 16 * i;
+#pragma unroll
+            for (int j = 0; j < TN; ++j) {
+                const int gn = n0 + tx * 4 + j;
+                const float v = (gm < p.M && gn < p.N) ? C[(int64_t)gm * p.N + gn] : 0.0f;
+                if (ALGO == ALGO_TILE8) aux[i][j] = v; else acc[i][j] = v;
+            }
+        }
+    }
 
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s) {

@@ -320,6 +320,10 @@ def float_mm_streamed(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None
     assert out.shape == (M, N) and out.dtype == torch.float32 and not out.is_cuda and out.is_contiguous()
     block_rows = max(1, min(int(block_rows), M)) if M else 1
     kw = (man_add, exp_add, man_mul, exp_mul, rounding, fma, subnormals, saturate, compensated, rbits_add, rbits_mul)
+    panels = _k_panels(K) if (rounding == "nearest" and not compensated and not b.is_cuda and M > 0 and N > 0) else None
+    if panels is not None:
+        fmt = (man_add, exp_add, man_add, exp_add) if fma else (man_add, exp_add, man_mul, exp_mul)
+        return _mm_streamed_by_panels(a, b, out, dev, block_rows, panels, fmt, subnormals, saturate, fma)
     with torch.cuda.device(dev):
         main = torch.cuda.current_stream(dev)
         s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
@@ -356,6 +360,77 @@ def float_mm_streamed(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None
         main.synchronize()
         for t in abuf:
             t.record_stream(s_in)
+    return out
+
+
+_PANEL, _FIRST_PANEL, _LAST_PANEL = 1024, 256, 512
+
+
+def _k_panels(K: int):
+    """Column panels [(k0, k1), ...] of the K-panel pipeline, or None when K is too short to be worth it: a short first
+    panel (the first kernel starts after one small copy), panels of 1024 steps, and a last panel just long enough for
+    its kernels to cover the copy of C back to the host.  Every boundary but the end is a multiple of 8."""
+    if K < _FIRST_PANEL + _PANEL + _LAST_PANEL:
+        return None
+    last0 = (K - _LAST_PANEL) // 8 * 8
+    cuts = [0, _FIRST_PANEL]
+    while last0 - cuts[-1] > _PANEL + _PANEL // 2:
+        cuts.append(cuts[-1] + _PANEL)
+    if last0 > cuts[-1]:
+        cuts.append(last0)
+    cuts.append(K)
+    return list(zip(cuts[:-1], cuts[1:]))
+
+
+def _mm_streamed_by_panels(a, b, out, dev, block_rows, panels, fmt, subnormals, saturate, fma):
+    """``float_mm_streamed`` for host operands, nearest rounding: the product advances along K.  Panel c of A (columns)
+    and of B (rows) travels to the GPU while panel c - 1 is in the kernel; a kernel continues the running sums that C
+    holds (`mpt_float_mm_nearest_piece`), which performs exactly the operations of the single call, so the bits are
+    those of ``float_mm``.  The last panel is multiplied in blocks of ``block_rows`` rows, each finished block of C
+    returning to the host under the next block's kernel.  Against copying B whole before the first kernel this hides
+    all of the inbound traffic but one short panel."""
+    M, K = a.shape
+    N = b.shape[1]
+    widest = max(k1 - k0 for k0, k1 in panels)
+    with torch.cuda.device(dev):
+        main = torch.cuda.current_stream(dev)
+        s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+        abuf = [torch.empty(M * widest, device=dev) for _ in range(2)]
+        bbuf = [torch.empty(widest * N, device=dev) for _ in range(2)]
+        c = torch.empty(M, N, device=dev)
+        free = [None, None]            # event: the kernels that read slot i have finished
+        s_in.wait_stream(main)
+        last = len(panels) - 1
+        for ci, (k0, k1) in enumerate(panels):
+            slot, kc = ci & 1, k1 - k0
+            ad, bd = abuf[slot][: M * kc].view(M, kc), bbuf[slot][: kc * N].view(kc, N)
+            with torch.cuda.stream(s_in):
+                if free[slot] is not None:
+                    s_in.wait_event(free[slot])
+                _be.copy_columns_async(ad, a, k0, k1)
+                bd.copy_(b[k0:k1], non_blocking=True)
+                arrived = torch.cuda.Event()
+                arrived.record(s_in)
+            main.wait_event(arrived)
+            flags = (_be.MM_PIECE_FROM_C if ci else 0) | (_be.MM_PIECE_MORE if ci < last else 0)
+            if ci < last:
+                _be.float_mm_nearest_piece(ad, bd, c, *fmt, subnormals, saturate, fma, flags)
+            else:
+                for r0 in range(0, M, block_rows):
+                    r1 = min(M, r0 + block_rows)
+                    _be.float_mm_nearest_piece(ad[r0:r1], bd, c[r0:r1], *fmt, subnormals, saturate, fma, flags)
+                    done = torch.cuda.Event()
+                    done.record(main)
+                    with torch.cuda.stream(s_out):
+                        s_out.wait_event(done)
+                        out[r0:r1].copy_(c[r0:r1], non_blocking=True)
+            free[slot] = torch.cuda.Event()
+            free[slot].record(main)
+        s_out.synchronize()
+        main.synchronize()
+        for t in (*abuf, *bbuf):
+            t.record_stream(s_in)
+        c.record_stream(s_out)
     return out
 
 

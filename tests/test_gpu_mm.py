@@ -378,3 +378,58 @@ def test_streamed_host_operands_equal_one_call():
     assert got is out and torch.equal(got.view(torch.int32), want.view(torch.int32))
     with pytest.raises(RuntimeError):
         q.float_mm_streamed(a.cuda(), b)
+
+
+@pytest.mark.parametrize("order", ["cuda", "seq"])
+@pytest.mark.parametrize("fma", [False, True])
+def test_product_in_k_pieces_equals_one_call(order, fma):
+    """mpt_float_mm_nearest_piece: pieces along K that continue the running sums held in C leave the bits of the single
+    call, for both orders, fused or not, with a ragged last piece, a piece shorter than a K slab, sums that pass
+    through both signs of zero, overflow and NaN, and a product whose range check fails (exact path)."""
+    import mptorch_b200.backend as be
+    import mptorch_b200.quant as q
+
+    g = torch.Generator(device="cuda").manual_seed(17)
+    M, K, N = 200, 701, 136
+    a = torch.randn(M, K, device="cuda", generator=g)
+    b = torch.randn(K, N, device="cuda", generator=g)
+    a[3] = 0.0
+    a[4] = -a[4].abs() * 1e-12            # products below the smallest subnormal
+    a[5, ::2] = 300.0                     # sums that overflow e5m2's range: the exact path and infinities
+    a[6, 100] = float("nan")
+    a[7, :64] = 0.0
+    b[:, 9] = -0.0
+    fmt = dict(man_add=2, exp_add=5, man_mul=2, exp_mul=5)
+    with be.orders(accum=order):
+        want = q.float_mm(a, b, rounding="nearest", fma=fma, subnormals=True, saturate=False, **fmt)
+        for cuts in ([0, 8, 16, 48, 400, 701], [0, 696, 701], [0, 256, 701], [0, 701]):
+            c = torch.full((M, N), float("nan"), device="cuda")
+            for i, (k0, k1) in enumerate(zip(cuts[:-1], cuts[1:])):
+                flags = (be.MM_PIECE_FROM_C if i else 0) | (be.MM_PIECE_MORE if k1 < K else 0)
+                be.float_mm_nearest_piece(a[:, k0:k1].contiguous(), b[k0:k1].contiguous(), c, 2, 5, 2, 5, True, False, fma, flags)
+            same = (c.view(torch.int32) == want.view(torch.int32)) | (c.isnan() & want.isnan())
+            assert bool(same.all()), (order, fma, cuts, int((~same).sum()))
+    with pytest.raises(RuntimeError):     # a piece that another follows must be whole groups of 8 steps
+        be.float_mm_nearest_piece(a[:, :10].contiguous(), b[:10].contiguous(), c, 2, 5, 2, 5, True, False, fma, be.MM_PIECE_MORE)
+
+
+def test_streamed_k_panel_pipeline_equals_one_call():
+    """Host operands long enough along K for the K-panel pipeline of float_mm_streamed (panels of A's columns and B's
+    rows copied under the kernels of the panels before): bits of one float_mm call, K not a multiple of 8 included."""
+    import mptorch_b200.backend as be
+    import mptorch_b200.quant as q
+    from mptorch_b200.quant.quant_function import _k_panels
+
+    torch.manual_seed(5)
+    for (M, K, N), fma, order in (((300, 2053, 260), False, "cuda"), ((129, 1800, 72), True, "cuda"), ((260, 3000, 200), False, "seq")):
+        assert _k_panels(K) is not None
+        a = torch.randn(M, K).pin_memory()
+        b = torch.randn(K, N).pin_memory()
+        with be.orders(accum=order):
+            want = q.float_mm(a.cuda(), b.cuda(), man_add=10, exp_add=5, man_mul=3, exp_mul=4, rounding="nearest", fma=fma,
+                              subnormals=True, saturate=False).cpu()
+            for block in (64, 1024):
+                got = q.float_mm_streamed(a, b, block_rows=block, man_add=10, exp_add=5, man_mul=3, exp_mul=4, rounding="nearest",
+                                          fma=fma, subnormals=True, saturate=False)
+                assert torch.equal(got.view(torch.int32), want.view(torch.int32)), (M, K, N, fma, order, block)
+    assert _k_panels(1000) is None
