@@ -840,7 +840,7 @@ def main() -> int:
             "clocks": clocks,
             "e2e": {"value": macs / e2e_ms / 1e6, "unit": "GMAC/s", "h2d_bytes_per_step": 4 * (rows * S + b_h2d_rows * S),
                     "d2h_bytes_per_step": 4 * rows * S, "ms_per_step": e2e_ms,
-                    "b_operand": "each rank copies 1/%d of B from host memory; one NCCL all-gather assembles it" % world if b_h2d_rows != S
+                    "b_operand": "each rank copies 1/%d of every K panel of B from host memory; one NCCL all-gather per panel assembles it under the kernels of the panels before" % world if b_h2d_rows != S
                     else "A and B copied from host memory in K panels under the kernels of the panels before; C returns in row blocks under the last panel"},
             "gpu_launches": launches_timed,
             "roofline": {"bound": "issue", "achieved": achieved, "peak": issue_peak, "unit": "GMAC/s",

@@ -163,6 +163,9 @@ def sharded_float_mm_streamed(a_rows: torch.Tensor, b: torch.Tensor, M: int, out
         raise RuntimeError("sharded_float_mm_streamed takes a contiguous float32 CPU matrix B")
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     K, N = b.shape
+    res = _streamed_by_panels(a_rows, b, out, dev, block_rows, group, world, rank, formats)
+    if res is not None:
+        return res
     klo, khi = row_shard(K, world, rank)
     kblock = -(-K // world)
     with torch.cuda.device(dev):
@@ -184,6 +187,47 @@ def sharded_float_mm_streamed(a_rows: torch.Tensor, b: torch.Tensor, M: int, out
         res = float_mm_streamed(a_rows, bd, out, device=dev, block_rows=block_rows, b_ready=b_ready, **formats)
         for t in (gathered, piece, bd):
             t.record_stream(s_b)
+    return res
+
+
+def _streamed_by_panels(a_rows, b, out, dev, block_rows, group, world, rank, formats):
+    """The K-panel pipeline of ``float_mm_streamed`` over the ranks (nearest rounding, K long enough, every panel a
+    multiple of the world size): per panel a rank copies its columns of its rows of A and 1/world of the panel's rows
+    of B from host memory, one all-gather assembles the panel of B on every GPU, and the kernel continues the rank's
+    running sums.  None when the conditions do not hold (the caller then assembles B whole first)."""
+    from .quant import quant_function as qf
+
+    f = dict(man_add=23, exp_add=8, man_mul=23, exp_mul=8, rounding="nearest", fma=True, subnormals=True, saturate=True,
+             compensated=False, rbits_add=0, rbits_mul=0)
+    unknown = set(formats) - set(f)
+    if unknown:
+        raise TypeError("sharded_float_mm_streamed: unexpected arguments %s" % sorted(unknown))
+    f.update(formats)
+    Mr, K = a_rows.shape
+    N = b.shape[1]
+    panels = qf._k_panels(K) if (f["rounding"] == "nearest" and not f["compensated"] and Mr > 0 and N > 0) else None
+    if panels is None or any((k1 - k0) % world for k0, k1 in panels):
+        return None
+    if a_rows.is_cuda or a_rows.dtype != torch.float32 or not a_rows.is_contiguous():
+        raise RuntimeError("sharded_float_mm_streamed takes contiguous float32 CPU tensors")
+    if out is None:
+        out = torch.empty(Mr, N, dtype=torch.float32).pin_memory()
+    assert out.shape == (Mr, N) and out.dtype == torch.float32 and not out.is_cuda and out.is_contiguous()
+    widest = max(k1 - k0 for k0, k1 in panels)
+    with torch.cuda.device(dev):
+        stage = torch.empty(widest // world * N, device=dev)
+
+        def load_b(k0, k1, bd):
+            rows = (k1 - k0) // world
+            mine = stage[: rows * N].view(rows, N)
+            mine.copy_(b[k0 + rank * rows: k0 + (rank + 1) * rows], non_blocking=True)
+            dist.all_gather_into_tensor(bd, mine, group=group)     # the copy stream waits for it
+
+        fmt = ((f["man_add"], f["exp_add"], f["man_add"], f["exp_add"]) if f["fma"]
+               else (f["man_add"], f["exp_add"], f["man_mul"], f["exp_mul"]))
+        res = qf._mm_streamed_by_panels(a_rows, N, out, dev, max(1, int(block_rows)), panels, fmt, f["subnormals"], f["saturate"],
+                                        f["fma"], load_b)
+        stage.record_stream(torch.cuda.current_stream(dev))
     return res
 
 

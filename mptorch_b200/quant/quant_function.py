@@ -323,7 +323,8 @@ def float_mm_streamed(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None
     panels = _k_panels(K) if (rounding == "nearest" and not compensated and not b.is_cuda and M > 0 and N > 0) else None
     if panels is not None:
         fmt = (man_add, exp_add, man_add, exp_add) if fma else (man_add, exp_add, man_mul, exp_mul)
-        return _mm_streamed_by_panels(a, b, out, dev, block_rows, panels, fmt, subnormals, saturate, fma)
+        return _mm_streamed_by_panels(a, N, out, dev, block_rows, panels, fmt, subnormals, saturate, fma,
+                                      lambda k0, k1, bd: bd.copy_(b[k0:k1], non_blocking=True))
     with torch.cuda.device(dev):
         main = torch.cuda.current_stream(dev)
         s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
@@ -382,15 +383,16 @@ def _k_panels(K: int):
     return list(zip(cuts[:-1], cuts[1:]))
 
 
-def _mm_streamed_by_panels(a, b, out, dev, block_rows, panels, fmt, subnormals, saturate, fma):
+def _mm_streamed_by_panels(a, N, out, dev, block_rows, panels, fmt, subnormals, saturate, fma, load_b):
     """``float_mm_streamed`` for host operands, nearest rounding: the product advances along K.  Panel c of A (columns)
     and of B (rows) travels to the GPU while panel c - 1 is in the kernel; a kernel continues the running sums that C
     holds (`mpt_float_mm_nearest_piece`), which performs exactly the operations of the single call, so the bits are
     those of ``float_mm``.  The last panel is multiplied in blocks of ``block_rows`` rows, each finished block of C
     returning to the host under the next block's kernel.  Against copying B whole before the first kernel this hides
-    all of the inbound traffic but one short panel."""
+    all of the inbound traffic but one short panel.  ``load_b(k0, k1, bd)`` fills the device buffer ``bd`` with rows
+    k0 .. k1 - 1 of B on the current (copy) stream: a host copy, or whatever assembles the panel."""
     M, K = a.shape
-    N = b.shape[1]
+    block_rows = min(block_rows, max(128, -(-M // 4)))       # at least four blocks of C on their way home
     widest = max(k1 - k0 for k0, k1 in panels)
     with torch.cuda.device(dev):
         main = torch.cuda.current_stream(dev)
@@ -408,7 +410,7 @@ def _mm_streamed_by_panels(a, b, out, dev, block_rows, panels, fmt, subnormals, 
                 if free[slot] is not None:
                     s_in.wait_event(free[slot])
                 _be.copy_columns_async(ad, a, k0, k1)
-                bd.copy_(b[k0:k1], non_blocking=True)
+                load_b(k0, k1, bd)
                 arrived = torch.cuda.Event()
                 arrived.record(s_in)
             main.wait_event(arrived)

@@ -33,7 +33,9 @@ def _worker(rank, world, port, out_dir):
         import mptorch_b200.quant as q
         from mptorch_b200.parallel import GradientAllReducer, row_shard, sharded_float_mm, sharded_float_mm_streamed
 
-        for M, K, N in ((1024, 512, 640), (1001, 333, 520)):
+        # the third case is long enough along K for the K-panel pipeline (a panel of B assembled per all-gather), the
+        # fourth has a last panel that does not divide by the world size and takes the whole-B path
+        for M, K, N in ((1024, 512, 640), (1001, 333, 520), (520, 2048, 264), (300, 1801, 136)):
             g = torch.Generator().manual_seed(7)
             a = torch.randn(M, K, generator=g)
             b = torch.randn(K, N, generator=g)
