@@ -364,19 +364,22 @@ def float_mm_streamed(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None
     return out
 
 
-_PANEL, _FIRST_PANEL, _LAST_PANEL = 1024, 256, 512
+_PANEL, _FIRST_PANEL, _LAST_PANEL = 2048, 256, 512
 
 
 def _k_panels(K: int):
     """Column panels [(k0, k1), ...] of the K-panel pipeline, or None when K is too short to be worth it: a short first
-    panel (the first kernel starts after one small copy), panels of 1024 steps, and a last panel just long enough for
-    its kernels to cover the copy of C back to the host.  Every boundary but the end is a multiple of 8."""
-    if K < _FIRST_PANEL + _PANEL + _LAST_PANEL:
+    panel (the first kernel starts after one small copy), then panels that double up to 2048 steps (a panel's copy
+    takes a small fraction of the kernel before it, and every kernel ends with a partly filled wave, so few long ones
+    are better than many), and a last panel just long enough for its kernels to cover the copy of C back to the host.
+    Every boundary but the end is a multiple of 8."""
+    if K < _FIRST_PANEL + 1024 + _LAST_PANEL:
         return None
     last0 = (K - _LAST_PANEL) // 8 * 8
-    cuts = [0, _FIRST_PANEL]
-    while last0 - cuts[-1] > _PANEL + _PANEL // 2:
-        cuts.append(cuts[-1] + _PANEL)
+    cuts, width = [0, _FIRST_PANEL], 2 * _FIRST_PANEL
+    while last0 - cuts[-1] > width + width // 2:
+        cuts.append(cuts[-1] + width)
+        width = min(2 * width, _PANEL)
     if last0 > cuts[-1]:
         cuts.append(last0)
     cuts.append(K)
