@@ -73,6 +73,12 @@ MPT_API int mpt_stream_priority_range(int *lowest, int *highest);
 MPT_API int mpt_copy_columns_async(void *dst, size_t dst_pitch, const void *src, size_t src_pitch, size_t width_bytes,
                                    size_t rows, void *stream);
 
+/* No counterpart in the reference (the layers there call .contiguous() on transposed views: functional.py:128,154).
+ * out[b][c][r] = in[b][r][c] for `batch` dense row-major matrices of `rows` x `cols` floats: the dense copy of a
+ * transposed operand (W^T, dY^T, X^T, K^T) the GEMM entry points need, at close to the copy bandwidth.
+ * batch and rows / 64 are limited to 65535. */
+MPT_API int mpt_transpose_last2(const float *in, float *out, int64_t batch, int64_t rows, int64_t cols, void *stream);
+
 /* ---- elementwise quantizers ------------------------------------------------------------- */
 
 /* replaces float_quantize_nearest (pybind_cuda.cpp:44 -> quant.cu:143 -> fp_kernel.cu:164) */

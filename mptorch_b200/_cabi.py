@@ -70,6 +70,7 @@ def lib() -> C.CDLL:
             "mpt_float_mm_nearest_static": [p, p, p, i64, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, p],
             "mpt_float_mm_nearest_piece": [p, p, p, i64] + [i32] * 12 + [p, sz, p],
             "mpt_copy_columns_async": [p, sz, p, sz, sz, sz, p],
+            "mpt_transpose_last2": [p, p, i64, i64, i64, p],
             "mpt_float_mm_nearest_fma": [p, p, p, i64, i32, i32, i32, i32, i32, i32, i32, i32, i32, p, sz, p],
             "mpt_float_mm_stochastic": [p, p, p, i64, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, u64, p, sz, p],
             "mpt_float_softmax_forward": [p, p, i64, i32, i64] + [i32] * 9 + [p],

@@ -268,6 +268,20 @@ def float_mm_nearest_piece(a, b, c, man_add, exp_add, man_mul, exp_mul, subnorma
              stream_ptr(a.device))
 
 
+def transpose_last2(x):
+    """A dense copy of ``x.transpose(-2, -1)`` for a contiguous float32 CUDA tensor with at least two dimensions, or None
+    when the kernel's grid limits do not admit the shape (the caller then lets torch copy)."""
+    rows, cols = x.shape[-2], x.shape[-1]
+    batch = x.numel() // (rows * cols) if rows * cols else 0
+    if batch > 65535 or (rows + 63) // 64 > 65535:
+        return None
+    out = torch.empty(*x.shape[:-2], cols, rows, device=x.device, dtype=torch.float32)
+    if x.numel():
+        with torch.cuda.device(x.device):
+            call("mpt_transpose_last2", ptr(x), ptr(out), batch, rows, cols, stream_ptr(x.device))
+    return out
+
+
 def copy_columns_async(dst, src, col0: int, col1: int):
     """dst[:, :] = src[:, col0:col1] for row-major float32 matrices on either side of the bus, as one pitched copy on
     the current stream of dst's (or src's) device; dst is dense with col1 - col0 columns."""

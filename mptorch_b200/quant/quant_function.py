@@ -43,6 +43,14 @@ def _require_cuda(x: torch.Tensor, who: str) -> None:
 
 
 def _f32c(x: torch.Tensor) -> torch.Tensor:
+    """``x`` as a dense float32 tensor.  A transposed view of a dense CUDA tensor (W^T, dY^T, X^T, K^T: what the layers
+    hand the GEMM) is copied by the tiled transpose kernel instead of torch's strided elementwise copy."""
+    if x.dtype == torch.float32 and x.is_cuda and x.dim() >= 2 and not x.is_contiguous() and x.shape[-1] > 1 and x.shape[-2] > 1:
+        t = x.transpose(-2, -1)
+        if t.is_contiguous():
+            y = _be.transpose_last2(t)
+            if y is not None:
+                return y
     return x.contiguous() if x.dtype == torch.float32 else x.float().contiguous()
 
 

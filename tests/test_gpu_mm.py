@@ -433,3 +433,25 @@ def test_streamed_k_panel_pipeline_equals_one_call():
                                           fma=fma, subnormals=True, saturate=False)
                 assert torch.equal(got.view(torch.int32), want.view(torch.int32)), (M, K, N, fma, order, block)
     assert _k_panels(1000) is None
+
+
+def test_transposed_operands_are_copied_by_the_transpose_kernel():
+    """backend.transpose_last2 against torch for ragged, batched and vector-friendly shapes, and the GEMM on a
+    transposed view against the GEMM on torch's dense copy of it."""
+    import mptorch_b200.backend as be
+    import mptorch_b200.quant as q
+
+    g = torch.Generator(device="cuda").manual_seed(2)
+    for shape in ((1, 1), (3, 5), (64, 64), (65, 127), (7, 300, 200), (2, 3, 128, 64), (1000, 3), (2, 1024, 768), (5, 0, 4)):
+        x = torch.randn(*shape, device="cuda", generator=g)
+        y = be.transpose_last2(x)
+        assert y.is_contiguous() and torch.equal(y, x.transpose(-2, -1).contiguous()), shape
+    x = torch.randn(4000, device="cuda", generator=g)[1:3601].view(60, 60)      # 4-byte aligned only
+    assert torch.equal(be.transpose_last2(x.contiguous()), x.t().contiguous())
+    a = torch.randn(96, 200, device="cuda", generator=g)
+    w = torch.randn(72, 200, device="cuda", generator=g)
+    kw = dict(man_add=10, exp_add=5, man_mul=3, exp_mul=4, rounding="nearest", fma=False, subnormals=True, saturate=False)
+    assert torch.equal(q.float_mm(a, w.t(), **kw), q.float_mm(a, w.t().contiguous(), **kw))
+    a3 = torch.randn(3, 200, 96, device="cuda", generator=g)
+    b3 = torch.randn(3, 200, 40, device="cuda", generator=g)
+    assert torch.equal(q.float_bmm(a3.transpose(-2, -1), b3, **kw), q.float_bmm(a3.transpose(-2, -1).contiguous(), b3, **kw))
