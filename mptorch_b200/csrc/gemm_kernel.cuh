@@ -153,11 +153,22 @@ static __global__ void __launch_bounds__(256) stats_kernel(const float* __restri
     uint32_t* mn = which ? &stats[blockIdx.y].minnz_b : &stats[blockIdx.y].minnz_a;
     uint32_t lmax = 0u, lmin = 0xFFFFFFFFu;
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
-        const uint32_t a = __float_as_uint(x[i]) & 0x7FFFFFFFu;
+    const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    auto take = [&](float v) {
+        const uint32_t a = __float_as_uint(v) & 0x7FFFFFFFu;
         lmax = max(lmax, a);
-        if (a != 0u) lmin = min(lmin, a);
+        lmin = min(lmin, a - 1u);                      // zero wraps to the largest value and so never wins
+    };
+    // 16-byte loads, four in flight per thread, where this entry starts on a 16-byte boundary
+    const int64_t n4 = (reinterpret_cast<uintptr_t>(x) & 15u) == 0 ? n / 4 : 0;
+    const float4* x4 = reinterpret_cast<const float4*>(x);
+#pragma unroll 4
+    for (int64_t i = tid; i < n4; i += stride) {
+        const float4 v = x4[i];
+        take(v.x); take(v.y); take(v.z); take(v.w);
     }
+    for (int64_t i = 4 * n4 + tid; i < n; i += stride) take(x[i]);
+    lmin = lmin == 0xFFFFFFFFu ? lmin : lmin + 1u;     // back from (pattern - 1); all zero stays 0xFFFFFFFF
     lmax = __reduce_max_sync(0xFFFFFFFFu, lmax);
     lmin = __reduce_min_sync(0xFFFFFFFFu, lmin);
     if ((threadIdx.x & 31) == 0) {
