@@ -325,6 +325,38 @@ __device__ __forceinline__ float rr(const Caster& c, float x, bool& odd) {
     return c.fast.fast(x);
 }
 
+// Two roundings at once for the checked modes: the exponent extraction and clamp stay per value, the two FMAs of the
+// FP-pipe rounding become one packed fp32x2 instruction each.  Same operations per value as rr<MODE>.
+template <int MODE>
+__device__ __forceinline__ float2 rr2(const Caster& c, float2 x, bool& odd) {
+    if (MODE == 0) return make_float2(c.fast(x.x), c.fast(x.y));
+    const FastRn& r = c.fast.fast;
+    const uint32_t t0 = __float_as_uint(x.x), t1 = __float_as_uint(x.y);
+    const int e0 = (int)(t0 & 0x7F800000u), e1 = (int)(t1 & 0x7F800000u);
+    const float2 m = make_float2(__int_as_float(e0 > r.min_e_bits ? e0 : r.min_e_bits), __int_as_float(e1 > r.min_e_bits ? e1 : r.min_e_bits));
+    const float2 y = __ffma2_rn(m, make_float2(r.k, r.k), x);
+    float2 z = __ffma2_rn(m, make_float2(-r.k, -r.k), y);
+    if (MODE == 2) {
+        odd |= (t0 + t0 - 1u < 0x00FFFFFFu) | (t1 + t1 - 1u < 0x00FFFFFFu);
+        z.x = __uint_as_float(__float_as_uint(z.x) | (t0 & c.neg_zero));
+        z.y = __uint_as_float(__float_as_uint(z.y) | (t1 & c.neg_zero));
+    }
+    return z;
+}
+
+// a / b for two dividends, given r = RN(1 / b) (see row_div).
+template <int MODE>
+__device__ __forceinline__ float2 row_div2(float2 a, float b, float r, bool& odd) {
+    if (MODE == 2) {
+        const uint32_t t0 = __float_as_uint(a.x), t1 = __float_as_uint(a.y);
+        odd |= (t0 + t0 - 1u < 0x2BFFFFFEu) | (t1 + t1 - 1u < 0x2BFFFFFEu);
+    }
+    const float2 r2 = make_float2(r, r);
+    const float2 q = __fmul2_rn(a, r2);
+    const float2 rem = __ffma2_rn(make_float2(-b, -b), q, a);
+    return __ffma2_rn(rem, r2, q);
+}
+
 template <int MODE>
 struct RAdd {
     const Caster& c;

@@ -55,7 +55,7 @@ class QBlock(nn.Module):
         q = q.view(B, T, h, d // h).transpose(1, 2).contiguous()
         k = k.view(B, T, h, d // h).transpose(1, 2).contiguous()
         v = v.view(B, T, h, d // h).transpose(1, 2).contiguous()
-        att = qmatmul(q, k.transpose(-2, -1).contiguous(), self.affine) * (1.0 / math.sqrt(d // h))
+        att = qmatmul(q, k.transpose(-2, -1), self.affine) * (1.0 / math.sqrt(d // h))
         mask = torch.ones(T, T, device=x.device, dtype=torch.bool).tril()
         att = self.softmax(att.masked_fill(~mask, float("-inf")))
         y = qmatmul(att, v, self.affine).transpose(1, 2).contiguous().view(B, T, d)
