@@ -723,6 +723,11 @@ def main() -> int:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_ms = t.item() / e2e_steps
     b_h2d_rows = S if (args.no_overlap or world == 1) else S // world
+    # the rows that came back through host memory against the same rows of the device-resident product of the timed steps
+    same = torch.tensor([int(torch.equal(ch.view(torch.int32), c_full[rank * rows:(rank + 1) * rows].cpu().view(torch.int32)))], device=dev)
+    if world > 1:
+        dist.all_reduce(same, op=dist.ReduceOp.MIN)
+    e2e_same_bits = bool(same.item())
     del ah, bh, ch, a, b, c_full
     torch.cuda.empty_cache()
 
@@ -839,7 +844,7 @@ def main() -> int:
             "notes": "M rows sharded over %d GPU(s)%s" % (world, (", C all-gathered in %d row panel(s) per rank" % panels) if world > 1 else ""),
             "clocks": clocks,
             "e2e": {"value": macs / e2e_ms / 1e6, "unit": "GMAC/s", "h2d_bytes_per_step": 4 * (rows * S + b_h2d_rows * S),
-                    "d2h_bytes_per_step": 4 * rows * S, "ms_per_step": e2e_ms,
+                    "d2h_bytes_per_step": 4 * rows * S, "ms_per_step": e2e_ms, "same_bits_as_device_result": e2e_same_bits,
                     "b_operand": "each rank copies 1/%d of every K panel of B from host memory; one NCCL all-gather per panel assembles it under the kernels of the panels before" % world if b_h2d_rows != S
                     else "A and B copied from host memory in K panels under the kernels of the panels before; C returns in row blocks under the last panel"},
             "gpu_launches": launches_timed,
