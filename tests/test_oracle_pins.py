@@ -117,7 +117,7 @@ def test_kat_float_quantize(oracle):
     assert q([3.1516], 1, 8, "nearest", True, False)[0] == 3.0
     out = q([20.0625, 20.06251, float("inf"), -float("inf")], 7, 8, "nearest", True, False)
     assert list(out) == [20.0, 20.125, float("inf"), -float("inf")]
-    # stated in the survey of the reference: IEEE-like e4m3 tops out at 240 when saturating
+    # IEEE-like e4m3 (the top exponent code reserved for infinity and NaN) tops out at 240 when saturating
     assert list(q([1.3, 1e-6, 70000.0, -0.3], 3, 4, "nearest", True, True)) == [1.25, 0.0, 240.0, -0.3125]
 
 
