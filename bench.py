@@ -356,7 +356,28 @@ def kernels_legs(dev, steps: int, warmup: int, scale: float = 1.0, with_referenc
             qmod.implicit_conv_eligible = eligible
     for k in ("qconv2d_fwd_implicit_gemm", "qconv2d_fwd_unfold_gemm"):
         out[k] = {"ms": out[k]["ms"], "gmacs": round(conv_macs / out[k]["ms"] / 1e6, 1)}
-    del xc, conv
+    # the same layer forward + backward: input gradient through the GEMM and F.fold, weight gradient as an implicit GEMM
+    # (no unfolded input) against the unfold + GEMM composition
+    import mptorch_b200.quant.functional as qfun
+
+    xg = xc.clone().requires_grad_(True)
+    gy = torch.randn(nb, 64, 56, 56, device=dev, generator=g)
+
+    def conv_step():
+        xg.grad = None
+        conv.weight.grad = None
+        conv(xg).backward(gy)
+
+    timed("qconv2d_fwd_bwd_implicit_wgrad", conv_step, 0)
+    wgrad_ok = qfun.implicit_wgrad_eligible
+    qfun.implicit_wgrad_eligible = lambda f: False
+    try:
+        timed("qconv2d_fwd_bwd_unfold_wgrad", conv_step, 0)
+    finally:
+        qfun.implicit_wgrad_eligible = wgrad_ok
+    for k in ("qconv2d_fwd_bwd_implicit_wgrad", "qconv2d_fwd_bwd_unfold_wgrad"):
+        out[k] = {"ms": out[k]["ms"], "gmacs": round(3 * conv_macs / out[k]["ms"] / 1e6, 1)}
+    del xc, conv, xg, gy
     # fused optimizer steps over the parameter tensors of a GPT-2-small (embeddings + one block, 46.5 M parameters):
     # QSGD with momentum and QAdamW, momentum / moments and weights in e8m7 with the Kahan compensation buffer
     from mptorch_b200.optim import QAdamW, QSGD, fma_quantizer

@@ -209,7 +209,10 @@ int run_conv_wgrad(const float* gout, const float* x, float* gw, int n_img, int 
         p.a = gout + (int64_t)g * og * L;
         p.b = x + (int64_t)g * cg * H * W;
         p.c = gw + (int64_t)g * og * Kw;
-        const int rc = launch_conv_wgrad_any(algo, fma, p, st);
+        // fewer 128-row tiles than SMs: the 16-row instantiation spreads the same outputs over eight times the CTAs
+        const int64_t big_tiles = (((int64_t)p.M + BM - 1) / BM) * (((int64_t)p.N + BN - 1) / BN);
+        const bool small = big_tiles < sm_count() && ((int64_t)p.M + kSmallTileRows - 1) / kSmallTileRows <= 65535;
+        const int rc = small ? launch_conv_wgrad_small_any(algo, fma, p, st) : launch_conv_wgrad_any(algo, fma, p, st);
         if (rc) return rc;
     }
     return MPT_OK;

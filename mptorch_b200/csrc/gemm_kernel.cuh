@@ -857,8 +857,11 @@ int launch_conv(const MmParams& p, cudaStream_t st) {
 }
 
 // Weight-gradient launch: both operands are gathered with scalar copies; the result is an ordinary row-major matrix.
-template <int ALGO, bool FMA>
+// TILE_ROWS names the tile height of the including translation unit, so that units built with different heights
+// instantiate different functions.
+template <int ALGO, bool FMA, int TILE_ROWS = BM>
 int launch_conv_wgrad(const MmParams& p, cudaStream_t st) {
+    static_assert(TILE_ROWS == BM, "one tile height per translation unit");
     dim3 grid((unsigned)(((int64_t)p.N + BN - 1) / BN), (unsigned)(((int64_t)p.M + BM - 1) / BM), 1);
     const bool add_guard = FMA || (p.fmul.min_exp - p.fmul.man) < (p.fadd.min_exp - p.fadd.man);
     auto kern = add_guard ? mm_kernel<ALGO, FMA, false, true, true, CONV_WGRAD> : mm_kernel<ALGO, FMA, false, true, FMA, CONV_WGRAD>;
@@ -875,5 +878,7 @@ int launch_mm_kahan(bool fma, const MmParams& p, int64_t batch, bool vec, cudaSt
 int launch_mm_sr(bool fma, const MmParams& p, int64_t batch, bool vec, cudaStream_t st);
 int launch_conv_any(int algo, bool fma, const MmParams& p, cudaStream_t st);
 int launch_conv_wgrad_any(int algo, bool fma, const MmParams& p, cudaStream_t st);
+int launch_conv_wgrad_small_any(int algo, bool fma, const MmParams& p, cudaStream_t st);
+constexpr int kSmallTileRows = 16;      // tile height of the instantiation behind launch_conv_wgrad_small_any
 
 }  // namespace mpt

@@ -111,7 +111,10 @@ def test_implicit_weight_gradient_entry_point(q):
 
     torch.manual_seed(7)
     for (n, c, h, w, cout, k, s, p, d, groups) in [(3, 4, 9, 7, 6, (3, 2), (2, 1), (1, 0), (1, 2), 2), (2, 3, 11, 11, 70, (3, 3), (1, 1), (1, 1), (1, 1), 1),
-                                                    (1, 2, 5, 5, 2, (5, 5), (1, 1), (2, 2), (1, 1), 1)]:
+                                                    (1, 2, 5, 5, 2, (5, 5), (1, 1), (2, 2), (1, 1), 1),
+                                                    # 10 x 18 tiles of 128 x 64: more than the SM count, the 128-row instantiation
+                                                    # (the cases above have few tiles and take the 16-row one)
+                                                    (1, 128, 4, 4, 1280, (3, 3), (1, 1), (1, 1), (1, 1), 1)]:
         x = torch.randn(n, c, h, w, device="cuda")
         oh = (h + 2 * p[0] - d[0] * (k[0] - 1) - 1) // s[0] + 1
         ow = (w + 2 * p[1] - d[1] * (k[1] - 1) - 1) // s[1] + 1
