@@ -100,6 +100,12 @@ int run_mm(const float* a, const float* b, float* c, int64_t batch, int M, int N
         p.stats = s;
     }
     const bool vec = (K % 4 == 0) && (N % 4 == 0) && (((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) & 15u) == 0);
+    if (algo == ALGO_SEQ || algo == ALGO_TILE8) {
+        // fewer 128-row tiles than SMs: the 16-row instantiation spreads the same outputs over eight times the CTAs
+        const int64_t big_tiles = (((int64_t)M + BM - 1) / BM) * (((int64_t)N + BN - 1) / BN) * batch;
+        if (big_tiles < sm_count() && ((int64_t)M + kSmallTileRows - 1) / kSmallTileRows <= 65535)
+            return launch_mm_small(algo, fma, p, batch, vec, st);
+    }
     switch (algo) {
         case ALGO_SEQ: return launch_mm_seq(fma, p, batch, vec, st);
         case ALGO_TILE8: return launch_mm_tile8(fma, p, batch, vec, st);

@@ -259,8 +259,10 @@ __device__ __forceinline__ void load_tiles(const MmParams& p, const float* A, co
     }
     if (VEC) {
 #pragma unroll
-        for (int u = 0; u < (BM * BK / 4) / THREADS; ++u) {
+        constexpr int kAChunks = BM * BK / 4;               // 16-byte pieces of the A tile; fewer than threads for 16-row tiles
+        for (int u = 0; u < (kAChunks + THREADS - 1) / THREADS; ++u) {
             const int c = tid + u * THREADS;
+            if (kAChunks % THREADS != 0 && c >= kAChunks) break;
             const int row = c >> 3, kc = (c & 7) << 2;
             const int gm = m0 + row, gk = k0 + kc;
             int bytes = (gm < p.M) ? (p.K - gk) * 4 : 0;
@@ -821,8 +823,11 @@ inline bool use_packed() {
     return packed;
 }
 
-template <int ALGO, bool FMA>
+// TILE_ROWS names the tile height of the including translation unit, so that units built with different heights
+// instantiate different functions.
+template <int ALGO, bool FMA, int TILE_ROWS = BM>
 int launch_mm(const MmParams& p, int64_t batch, bool vec, cudaStream_t st) {
+    static_assert(TILE_ROWS == BM, "one tile height per translation unit");
     dim3 grid((unsigned)(((int64_t)p.N + BN - 1) / BN), (unsigned)(((int64_t)p.M + BM - 1) / BM), (unsigned)batch);
     if (grid.y > 65535u) { set_error("float_mm: M=%d has more than 65535 row tiles of %d", p.M, BM); return MPT_ERR_INVALID_ARGUMENT; }
     // The stochastic kernel has one form (scalar, both clamps); its translation unit picks tile height and residency.
@@ -879,6 +884,7 @@ int launch_mm_sr(bool fma, const MmParams& p, int64_t batch, bool vec, cudaStrea
 int launch_conv_any(int algo, bool fma, const MmParams& p, cudaStream_t st);
 int launch_conv_wgrad_any(int algo, bool fma, const MmParams& p, cudaStream_t st);
 int launch_conv_wgrad_small_any(int algo, bool fma, const MmParams& p, cudaStream_t st);
+int launch_mm_small(int algo, bool fma, const MmParams& p, int64_t batch, bool vec, cudaStream_t st);   // ALGO_SEQ / ALGO_TILE8
 constexpr int kSmallTileRows = 16;      // tile height of the instantiation behind launch_conv_wgrad_small_any
 
 }  // namespace mpt
