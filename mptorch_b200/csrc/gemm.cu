@@ -45,9 +45,16 @@ KahanBounds kahan_bounds(int man) {
     return KahanBounds{(top.v[0] + top.v[1]) * 1.001, top.v[2] * 1.001, top.v[3] * 1.001};
 }
 
-int run_mm(const float* a, const float* b, float* c, int64_t batch, int M, int N, int K, const AnyFmt& gadd, const AnyFmt& gmul,
-           int rbits_add, int rbits_mul, bool fma, int algo, uint64_t seed, void* workspace, size_t workspace_bytes,
+int run_mm(const float* a, const float* b, float* c, int64_t batch, int M, int N, int K, const AnyFmt& gadd, const AnyFmt& gmul_in,
+           int rbits_add, int rbits_mul, bool fma_in, int algo, uint64_t seed, void* workspace, size_t workspace_bytes,
            cudaStream_t st, int resume = 0) {
+    // A multiply format that rounds nothing leaves `sum + a * b` in the reference's CUDA kernel (mm_kernel.h:53), and
+    // its build contracts that into one fused multiply-add (measured: its results equal the fused variant with the
+    // add format, not the separately rounded product).  The CUDA order follows the CUDA build; the sequential order
+    // follows the CPU build, which multiplies and adds separately.
+    const bool contracted = !fma_in && algo == ALGO_TILE8 && gadd.kind == FMT_FLOAT && gmul_in.kind == FMT_FLOAT && fmt_identity(gmul_in.fp);
+    const bool fma = fma_in || contracted;
+    const AnyFmt gmul = contracted ? gadd : gmul_in;
     const FpFmt fadd = gadd.fp, fmul = gmul.fp;
     const bool all_float = gadd.kind == FMT_FLOAT && (fma || gmul.kind == FMT_FLOAT);
     if (batch == 0 || M == 0 || N == 0) return MPT_OK;
@@ -64,7 +71,7 @@ int run_mm(const float* a, const float* b, float* c, int64_t batch, int M, int N
     p.stride_a = (int64_t)M * K; p.stride_b = (int64_t)K * N; p.stride_c = (int64_t)M * N;
     p.fadd = fadd; p.fmul = fmul;
     p.gadd = gadd; p.gmul = fma ? gadd : gmul;
-    p.radd = FastRn::make(fadd); p.rmul = FastRn::make(fmul);
+    p.radd = mm_fast_rn(fadd); p.rmul = mm_fast_rn(fmul);
     p.rbits_add = rbits_add; p.rbits_mul = rbits_mul;
     p.seed_lo = (uint32_t)seed; p.seed_hi = (uint32_t)(seed >> 32);
     p.growth8 = (float)growth8_bound(fadd.man);
@@ -79,7 +86,7 @@ int run_mm(const float* a, const float* b, float* c, int64_t batch, int M, int N
     p.sr_ok = all_float && FullSr::supported(fadd) && (fma || FullSr::supported(fmul));
     p.sadd = FullSr::make(fadd, rbits_add); p.smul = FullSr::make(fma ? fadd : fmul, fma ? rbits_add : rbits_mul);
 
-    const bool fmt_fast = algo == ALGO_SR ? p.sr_ok != 0 : (fast_rn_supported(fadd) && (fma || fast_rn_supported(fmul)));
+    const bool fmt_fast = algo == ALGO_SR ? p.sr_ok != 0 : (mm_fast_format(fadd) && (fma || mm_fast_format(fmul)));
     const bool fast_candidate = all_float && fmt_fast && workspace != nullptr &&
                                 workspace_bytes >= sizeof(MmStats) * (size_t)batch &&
                                 (reinterpret_cast<uintptr_t>(workspace) & 15u) == 0 && K > 0;

@@ -111,6 +111,18 @@ struct MmParams {
 };
 enum { MM_FROM_C = 1, MM_MORE = 2 };
 
+// The format that rounds nothing (man >= 23 and exp >= 8: the reference's `noquantize`, fp_kernel.cu:23): fp32
+// accumulation of low-precision products is the usual use.  The range-checked fast path covers it with the magic
+// constant set to zero: FFMA(m, 0, x) = x + 0 leaves every finite x as it is, except that -0 becomes +0, which no sum
+// can tell apart here (the running sums start at +0 and an IEEE sum is -0 only when both terms are).
+__host__ __device__ inline bool fmt_identity(const FpFmt& f) { return f.man >= 23 && f.exp >= 8; }
+__host__ __device__ inline bool mm_fast_format(const FpFmt& f) { return fast_rn_supported(f) || fmt_identity(f); }
+__host__ __device__ inline FastRn mm_fast_rn(const FpFmt& f) {
+    FastRn r = FastRn::make(f);
+    if (fmt_identity(f)) r.k = 0.0f;
+    return r;
+}
+
 // Nearest rounding to the add / multiply format on the whole input domain.  The exact caster is an out-of-line call
 // (taken for formats without the fast rounding, and for the tiny or huge inputs 8-bit-exponent formats treat
 // specially), so that the many rounding sites of the Kahan kernels stay small.
@@ -578,7 +590,9 @@ __device__ __forceinline__ FastPlan make_plan(const MmParams& p, int64_t batch) 
         plan.acc_limit = lim;
         return plan;
     }
-    if (!fast_rn_supported(p.fadd) || (!FMA && !fast_rn_supported(p.fmul))) return plan;
+    if (!mm_fast_format(p.fadd) || (!FMA && !mm_fast_format(p.fmul))) return plan;
+    // the compensated sum's bounds are worked out for formats that round; it keeps the exact path for the identity
+    if (ALGO == ALGO_KAHAN && (fmt_identity(p.fadd) || (!FMA && fmt_identity(p.fmul)))) return plan;
     const int lim_add = fast_rn_exp_limit(p.fadd);
     if (!FMA && pe - 1 > fast_rn_exp_limit(p.fmul)) return plan;
     if (p.fadd.exp == 8 || (!FMA && p.fmul.exp == 8)) {

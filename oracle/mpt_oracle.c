@@ -428,13 +428,19 @@ static void mm_impl(const float *a, const float *b, float *c, int64_t B, int M, 
                 }
                 memcpy(C, s1, (size_t)N * sizeof(float));
             } else {
+                /* A multiply format that rounds nothing (man >= 23, exp >= 8) leaves `inner + a * b` in the
+                   CUDA kernel, and the reference's CUDA build evaluates that as one fused multiply-add
+                   (measured on its unmodified build: equal to the fused variant with the add format, bit for
+                   bit, and different from the separately rounded product).  Order 1 restates the CUDA
+                   kernel, so it does the same; order 0, the CPU kernel, multiplies and adds separately. */
+                const int fused = fma || (fa.kind == 0 && fm.kind == 0 && fm.man >= 23 && fm.exp >= 8);
                 for (int k0 = 0; k0 < Kpad; k0 += 8) {
                     for (int kk = 0; kk < 8; ++kk) {
                         int k = k0 + kk;
                         float av = k < K ? A[k] : 0.f;
                         for (int j = 0; j < N; ++j) {
                             float bv = k < K ? Bm[(int64_t)k * N + j] : 0.f;
-                            s1[j] = fma ? Q(fmaf(av, bv, s1[j]), fa) : Q(s1[j] + Q(av * bv, fm), fa);
+                            s1[j] = fused ? Q(fmaf(av, bv, s1[j]), fa) : Q(s1[j] + Q(av * bv, fm), fa);
                         }
                     }
                     for (int j = 0; j < N; ++j) { s2[j] = Q(s2[j] + s1[j], fa); s1[j] = 0.f; }

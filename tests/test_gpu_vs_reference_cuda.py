@@ -227,3 +227,35 @@ def test_softmax_and_layernorm_cuda_order(ref_cuda):
         ref_cuda.float_quantize_layernorm_backward(xl, gl, w, b, mean, rstd, gi, gg, gb, [-1], m, e, m, e, m, e, True, False)
         ogi, ogg, ogb = q.float_layernorm_backward(xl, gl, w, b, mean, rstd, [-1], m, e, m, e, m, e)
         assert bits_equal(ogi, gi) and bits_equal(ogg, gg) and bits_equal(ogb, gb), ("layernorm bwd", e, m)
+
+
+@pytest.mark.parametrize("shape", [(256, 256, 256), (78, 101, 145), (300, 2048, 136)])
+def test_mm_with_formats_that_round_nothing(ref_cuda, be, shape):
+    """fp32 as the add format (low-precision products accumulated in fp32), as the multiply format, or as both, against
+    the reference's CUDA kernel.  With a multiply format that rounds nothing that kernel's `sum + a * b` is evaluated as
+    one fused multiply-add by the reference's build; the CUDA order reproduces it.  The operands include magnitudes whose
+    sums leave the range-checked path (1e30) and zeros of both signs."""
+    M, K, N = shape
+    a = torch.randn(M, K, device="cuda")
+    b = torch.randn(K, N, device="cuda")
+    a[1, :] = 0.0
+    a[2, ::3] = -0.0
+    a[3, :8] = 1e30
+    b[:8, 5] = 1e30
+    for (ma, ea, mm_, em) in [(23, 8, 23, 8), (23, 8, 3, 4), (23, 8, 2, 5), (23, 8, 7, 8), (10, 5, 23, 8), (7, 8, 23, 8), (2, 5, 23, 8)]:
+        for batched in (False, True):
+            aa, bb = (a.view(1, M, K).repeat(2, 1, 1).contiguous(), b.view(1, K, N).repeat(2, 1, 1).contiguous()) if batched else (a, b)
+            want = torch.zeros(*aa.shape[:-1], N, device="cuda")
+            got = torch.empty_like(want)
+            if batched:
+                ref_cuda.float_quantize_nearest_bmm(aa, bb, want, M, N, K, ma, ea, mm_, em, True, False, False)
+                be.float_quantize_nearest_bmm(aa, bb, got, M, N, K, ma, ea, mm_, em, True, False, False, order="cuda")
+            else:
+                ref_cuda.float_quantize_nearest_mm(aa, bb, want, M, N, K, ma, ea, mm_, em, True, False, False)
+                be.float_quantize_nearest_mm(aa, bb, got, M, N, K, ma, ea, mm_, em, True, False, False, order="cuda")
+            assert bits_equal(got, want), (shape, ma, ea, mm_, em, batched)
+    want = torch.zeros(M, N, device="cuda")
+    got = torch.empty_like(want)
+    ref_cuda.float_quantize_nearest_mm_fma(a, b, want, M, N, K, 23, 8, True, False, False)
+    be.float_quantize_nearest_mm_fma(a, b, got, M, N, K, 23, 8, True, False, False, order="cuda")
+    assert bits_equal(got, want), ("fma", shape)
