@@ -457,6 +457,38 @@ def c4_sweep(dev, sizes=(2048, 4096, 8192), variants=True) -> dict:
                 rec(name, "cuda", "stochastic", timed(lambda: be.float_quantize_stochastic_mm(a, b, c, S, S, S, ma, ea, 23 - ma, mm, em, 23 - mm, True, False, seed=5), 3))
             rec("fma e5m10", "cuda", "kahan fma", timed(lambda: be.float_quantize_nearest_mm_fma(a, b, c, S, S, S, 10, 5, True, False, True, order="cuda"), 3))
             rec("fma e5m10", "cuda", "stochastic fma", timed(lambda: be.float_quantize_stochastic_mm_fma(a, b, c, S, S, S, 10, 5, 13, True, False, seed=5), 3))
+        if variants and S == min(sizes):
+            # formats outside the three pairs, each with the reference's own CUDA kernel on the same operands: fp32
+            # accumulation (a format that rounds nothing), and formats only the exact casters cover
+            ref = _ref_cuda()
+            r = torch.empty(S, S, device=dev)
+
+            def both(name, form, ours, theirs):
+                ms = timed(ours, 5)
+                row = {"size": S, "formats": name, "order": "cuda", "form": form, "ms": round(ms, 3), "tmacs": round(float(S) ** 3 / ms / 1e9, 3)}
+                if ref is not None:
+                    try:
+                        rms = timed(theirs, 3)
+                        row["reference_cuda_ms"] = round(rms, 3)
+                        row["same_bits_as_reference_cuda"] = bool(((c.view(torch.int32) == r.view(torch.int32)) | (c.isnan() & r.isnan())).all())
+                    except Exception as ex:
+                        row["reference_cuda_error"] = repr(ex)[:120]
+                rows.append(row)
+
+            both("mul e4m3 / add fp32", "mul+add", lambda: be.float_quantize_nearest_mm(a, b, c, S, S, S, 23, 8, 3, 4, True, False, False, order="cuda"),
+                 lambda: ref.float_quantize_nearest_mm(a, b, r, S, S, S, 23, 8, 3, 4, True, False, False))
+            both("mul fp32 / add fp32", "mul+add", lambda: be.float_quantize_nearest_mm(a, b, c, S, S, S, 23, 8, 23, 8, True, False, False, order="cuda"),
+                 lambda: ref.float_quantize_nearest_mm(a, b, r, S, S, S, 23, 8, 23, 8, True, False, False))
+            both("mul e5m2 / add e5m2, no subnormals", "mul+add (exact casters)",
+                 lambda: be.float_quantize_nearest_mm(a, b, c, S, S, S, 2, 5, 2, 5, False, False, False, order="cuda"),
+                 lambda: ref.float_quantize_nearest_mm(a, b, r, S, S, S, 2, 5, 2, 5, False, False, False))
+            both("supernormal e8m7, 1 binade each side", "mul+add (exact casters)",
+                 lambda: be.superfp_quantize_nearest_mm(a, b, c, S, S, S, 7, 8, 7, 8, 1, 1, 1, 1, True, order="cuda"),
+                 lambda: ref.superfp_quantize_nearest_mm(a, b, r, S, S, S, 7, 8, 7, 8, 1, 1, 1, 1, True))
+            both("supernormal e8m7, 1 binade each side", "fma (exact casters)",
+                 lambda: be.superfp_quantize_nearest_mm_fma(a, b, c, S, S, S, 7, 8, 1, 1, True, order="cuda"),
+                 lambda: ref.superfp_quantize_nearest_mm_fma(a, b, r, S, S, S, 7, 8, 1, 1, True))
+            del r
         del a, b, c
     return {"rows": rows}
 
@@ -469,7 +501,9 @@ def run_c4(args) -> int:
     sizes = (2048, 4096, 8192) if args.size == SIZE else (args.size,)
     out = c4_sweep(dev, sizes)
     for r in out["rows"]:
-        sys.stderr.write("%5d  %-22s %-4s %-16s %9.3f ms %7.3f TMAC/s\n" % (r["size"], r["formats"], r["order"], r["form"], r["ms"], r["tmacs"]))
+        sys.stderr.write("%5d  %-38s %-4s %-24s %9.3f ms %7.3f TMAC/s%s\n" % (r["size"], r["formats"], r["order"], r["form"], r["ms"], r["tmacs"],
+                                                                              ("   reference CUDA %.3f ms, same bits %s" % (r["reference_cuda_ms"], r["same_bits_as_reference_cuda"]))
+                                                                              if "reference_cuda_ms" in r else ""))
     print(json.dumps({"metric": "float_mm sweep (benchmark config 4), simulated TMAC/s", "unit": "TMAC/s", "n_gpus": 1, **out}))
     return 0
 

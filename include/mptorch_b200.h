@@ -138,7 +138,11 @@ MPT_API size_t mpt_mm_workspace_bytes(int64_t batch);
  *   C[b] = A[b] x B[b],  A: [batch, M, K], B: [batch, K, N], C: [batch, M, N]
  * every product is rounded to (man_mul, exp_mul) and every sum to (man_add, exp_add); both use the
  * `subnormals` and `saturate` flags.  order: MPT_ORDER_SEQ or MPT_ORDER_CUDA.
- * compensated != 0 selects Kahan summation (mm_kernel.h:457-676). */
+ * compensated != 0 selects Kahan summation (mm_kernel.h:457-676).
+ * A format with man >= 23 and exp >= 8 rounds nothing (fp32 accumulation).  With such a multiply format the
+ * reference's CUDA build evaluates `sum + a * b` as one fused multiply-add; MPT_ORDER_CUDA does the same (its
+ * results are those of mpt_float_mm_nearest_fma with the add format), MPT_ORDER_SEQ multiplies and adds
+ * separately as the reference's CPU build does. */
 MPT_API int mpt_float_mm_nearest(const float *a, const float *b, float *c, int64_t batch, int M, int N, int K,
                                  int man_add, int exp_add, int man_mul, int exp_mul,
                                  int subnormals, int saturate, int compensated, int order,

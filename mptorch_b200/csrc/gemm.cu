@@ -107,6 +107,8 @@ int run_mm(const float* a, const float* b, float* c, int64_t batch, int M, int N
         p.stats = s;
     }
     const bool vec = (K % 4 == 0) && (N % 4 == 0) && (((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) & 15u) == 0);
+    // formats without the FP-pipe rounding: the kernel built around the exact casters
+    if ((algo == ALGO_SEQ || algo == ALGO_TILE8) && !(all_float && fmt_fast)) return launch_mm_exact(algo, fma, p, batch, st);
     if (algo == ALGO_SEQ || algo == ALGO_TILE8) {
         // fewer 128-row tiles than SMs: the 16-row instantiation spreads the same outputs over eight times the CTAs
         const int64_t big_tiles = (((int64_t)M + BM - 1) / BM) * (((int64_t)N + BN - 1) / BN) * batch;

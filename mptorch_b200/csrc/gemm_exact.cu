@@ -1,0 +1,104 @@
+// GEMM for rounding formats the FP-pipe rounding does not cover (supernormal float, binary8, float formats without
+// subnormals or with 22-23 mantissa bits below 8 exponent bits): every rounding is the exact caster, 60-200
+// instructions with data-dependent branches, so the kernel is bound by those and shaped for them rather than for
+// operand reuse: one warp-wide row of 32 outputs per warp step, four outputs per thread as independent chains, many
+// resident warps (about 40 registers per thread), the casters inlined once per format kind.  The accumulation
+// orders, the zero padding of the CUDA order and the continuation from the sums held in C are those of mm_kernel.
+#include "gemm_kernel.cuh"
+
+namespace mpt {
+namespace {
+
+constexpr int XT = 32;        // tile edge: 32 x 32 outputs, K slabs of 32
+constexpr int XPER = 4;       // outputs per thread: rows ty, ty + 8, ty + 16, ty + 24 of column tx
+
+// KIND 0: both formats are float formats, 2: both supernormal, 3: both binary8 (that caster alone is inlined);
+// KIND 1: any mixture (cast_any).
+template <int KIND>
+__device__ __forceinline__ float round_to(float x, const AnyFmt& f) {
+    if (KIND == 0) return cast_fp_nearest(x, f.fp);
+    if (KIND == 2) return cast_superfp(x, f.fp.man, f.fp.exp, f.bl, f.bu, f.fp.sat != 0);
+    if (KIND == 3) return cast_binary8(x, f.P, f.is_signed != 0, f.policy, f.fp.sub != 0, RND_NEAREST, 0u, 0);
+    return cast_any(x, f);
+}
+
+template <int ALGO, bool FMA, int KIND>
+__global__ void __launch_bounds__(256) exact_mm_kernel(const __grid_constant__ MmParams p) {
+    __shared__ float As[XT][XT + 1];
+    __shared__ float Bs[XT][XT];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int m0 = blockIdx.y * XT, n0 = blockIdx.x * XT;
+    const int64_t batch = blockIdx.z;
+    const float* A = p.a + batch * p.stride_a;
+    const float* B = p.b + batch * p.stride_b;
+    float* C = p.c + batch * p.stride_c;
+    const int ksteps = (ALGO == ALGO_SEQ || (p.resume & MM_MORE)) ? p.K : p.K + 8 - p.K % 8;
+    const int gn = n0 + tx;
+
+    float run[XPER], outer[XPER];       // the running (inner) sum; the outer sum of the CUDA order
+#pragma unroll
+    for (int i = 0; i < XPER; ++i) {
+        run[i] = 0.0f; outer[i] = 0.0f;
+        if (p.resume & MM_FROM_C) {
+            const int gm = m0 + ty + 8 * i;
+            const float v = (gm < p.M && gn < p.N) ? C[(int64_t)gm * p.N + gn] : 0.0f;
+            if (ALGO == ALGO_TILE8) outer[i] = v; else run[i] = v;
+        }
+    }
+    for (int k0 = 0; k0 < ksteps; k0 += XT) {
+#pragma unroll
+        for (int i = 0; i < XPER; ++i) {
+            const int r = ty + 8 * i;
+            const int gm = m0 + r, gk = k0 + tx;
+            As[r][tx] = (gm < p.M && gk < p.K) ? A[(int64_t)gm * p.K + gk] : 0.0f;
+            const int bk = k0 + r;
+            Bs[r][tx] = (bk < p.K && gn < p.N) ? B[(int64_t)bk * p.N + gn] : 0.0f;
+        }
+        __syncthreads();
+        const int nk = min(XT, ksteps - k0);
+#pragma unroll 1
+        for (int k = 0; k < nk; ++k) {
+            const float b = Bs[k][tx];
+#pragma unroll
+            for (int i = 0; i < XPER; ++i) {
+                const float a = As[ty + 8 * i][k];
+                run[i] = FMA ? round_to<KIND>(fma_rn(a, b, run[i]), p.gadd)
+                             : round_to<KIND>(add_rn(run[i], round_to<KIND>(mul_rn(a, b), p.gmul)), p.gadd);
+            }
+            if (ALGO == ALGO_TILE8 && ((k0 + k) & 7) == 7) {
+#pragma unroll
+                for (int i = 0; i < XPER; ++i) { outer[i] = round_to<KIND>(add_rn(outer[i], run[i]), p.gadd); run[i] = 0.0f; }
+            }
+        }
+        __syncthreads();
+    }
+    if (gn < p.N) {
+#pragma unroll
+        for (int i = 0; i < XPER; ++i) {
+            const int gm = m0 + ty + 8 * i;
+            if (gm < p.M) C[(int64_t)gm * p.N + gn] = ALGO == ALGO_TILE8 ? outer[i] : run[i];
+        }
+    }
+}
+
+template <int ALGO, bool FMA>
+int launch_exact(const MmParams& p, int64_t batch, cudaStream_t st) {
+    const int64_t gy = ((int64_t)p.M + XT - 1) / XT, gx = ((int64_t)p.N + XT - 1) / XT;
+    if (gy > 65535) { set_error("float_mm: M=%d has more than 65535 row tiles of %d", p.M, XT); return MPT_ERR_INVALID_ARGUMENT; }
+    const dim3 grid((unsigned)gx, (unsigned)gy, (unsigned)batch);
+    const int ka = p.gadd.kind, km = p.gmul.kind;          // run_mm sets gmul = gadd for the fused form
+    if (ka == FMT_FLOAT && km == FMT_FLOAT) exact_mm_kernel<ALGO, FMA, 0><<<grid, 256, 0, st>>>(p);
+    else if (ka == FMT_SUPERFP && km == FMT_SUPERFP) exact_mm_kernel<ALGO, FMA, 2><<<grid, 256, 0, st>>>(p);
+    else if (ka == FMT_BINARY8 && km == FMT_BINARY8) exact_mm_kernel<ALGO, FMA, 3><<<grid, 256, 0, st>>>(p);
+    else exact_mm_kernel<ALGO, FMA, 1><<<grid, 256, 0, st>>>(p);
+    return check_launch("float_mm");
+}
+
+}  // namespace
+
+int launch_mm_exact(int algo, bool fma, const MmParams& p, int64_t batch, cudaStream_t st) {
+    if (algo == ALGO_SEQ) return fma ? launch_exact<ALGO_SEQ, true>(p, batch, st) : launch_exact<ALGO_SEQ, false>(p, batch, st);
+    return fma ? launch_exact<ALGO_TILE8, true>(p, batch, st) : launch_exact<ALGO_TILE8, false>(p, batch, st);
+}
+
+}  // namespace mpt

@@ -349,6 +349,31 @@ __device__ __forceinline__ float2 mac_fast2(float2 acc, float2 a2, float2 b2, co
     return fast_rn2<ADDG>(radd, __fadd2_rn(acc, fast_rn2<true>(rmul, __fmul2_rn(a2, b2))));
 }
 
+// One accumulation step of the exact path for four outputs that share the A element, as a function call: the exact
+// casters are long (three format kinds, subnormal and overflow branches), and a copy inlined at each of the 64
+// roundings of a thread's step would not fit the instruction cache.  The kind is tested once per call.
+template <bool FMA>
+static __device__ __noinline__ float4 mac_exact4(float4 acc, float a, float4 b, const MmParams* pp) {
+    const AnyFmt& fa = pp->gadd;
+    const AnyFmt& fm = pp->gmul;
+    if (fa.kind == FMT_FLOAT && (FMA || fm.kind == FMT_FLOAT)) {
+        const FpFmt ga = fa.fp, gm = fm.fp;
+        if (FMA) {
+            acc.x = cast_fp_nearest(fma_rn(a, b.x, acc.x), ga); acc.y = cast_fp_nearest(fma_rn(a, b.y, acc.y), ga);
+            acc.z = cast_fp_nearest(fma_rn(a, b.z, acc.z), ga); acc.w = cast_fp_nearest(fma_rn(a, b.w, acc.w), ga);
+        } else {
+            acc.x = cast_fp_nearest(add_rn(acc.x, cast_fp_nearest(mul_rn(a, b.x), gm)), ga);
+            acc.y = cast_fp_nearest(add_rn(acc.y, cast_fp_nearest(mul_rn(a, b.y), gm)), ga);
+            acc.z = cast_fp_nearest(add_rn(acc.z, cast_fp_nearest(mul_rn(a, b.z), gm)), ga);
+            acc.w = cast_fp_nearest(add_rn(acc.w, cast_fp_nearest(mul_rn(a, b.w), gm)), ga);
+        }
+        return acc;
+    }
+    acc.x = mac_exact<FMA>(acc.x, a, b.x, fa, fm); acc.y = mac_exact<FMA>(acc.y, a, b.y, fa, fm);
+    acc.z = mac_exact<FMA>(acc.z, a, b.z, fa, fm); acc.w = mac_exact<FMA>(acc.w, a, b.w, fa, fm);
+    return acc;
+}
+
 // `nk` (1..8) accumulation steps starting at slab row kbase, for the thread's 8x4 outputs.
 template <bool FMA, bool FAST, bool PACKED, bool ADDG>
 __device__ __forceinline__ void group_steps(float (&acc)[TM][TN], const float* As, const float* Bs, int kbase, int nk,
@@ -394,10 +419,8 @@ __device__ __forceinline__ void group_steps(float (&acc)[TM][TN], const float* A
                 acc[i][2] = mac_fast<FMA>(acc[i][2], a, bv.z, p.radd, p.rmul);
                 acc[i][3] = mac_fast<FMA>(acc[i][3], a, bv.w, p.radd, p.rmul);
             } else {
-                acc[i][0] = mac_exact<FMA>(acc[i][0], a, bv.x, p.gadd, p.gmul);
-                acc[i][1] = mac_exact<FMA>(acc[i][1], a, bv.y, p.gadd, p.gmul);
-                acc[i][2] = mac_exact<FMA>(acc[i][2], a, bv.z, p.gadd, p.gmul);
-                acc[i][3] = mac_exact<FMA>(acc[i][3], a, bv.w, p.gadd, p.gmul);
+                const float4 r = mac_exact4<FMA>(make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]), a, bv, &p);
+                acc[i][0] = r.x; acc[i][1] = r.y; acc[i][2] = r.z; acc[i][3] = r.w;
             }
         }
     }
@@ -899,6 +922,7 @@ int launch_conv_any(int algo, bool fma, const MmParams& p, cudaStream_t st);
 int launch_conv_wgrad_any(int algo, bool fma, const MmParams& p, cudaStream_t st);
 int launch_conv_wgrad_small_any(int algo, bool fma, const MmParams& p, cudaStream_t st);
 int launch_mm_small(int algo, bool fma, const MmParams& p, int64_t batch, bool vec, cudaStream_t st);   // ALGO_SEQ / ALGO_TILE8
+int launch_mm_exact(int algo, bool fma, const MmParams& p, int64_t batch, cudaStream_t st);             // ALGO_SEQ / ALGO_TILE8
 constexpr int kSmallTileRows = 16;      // tile height of the instantiation behind launch_conv_wgrad_small_any
 
 }  // namespace mpt
