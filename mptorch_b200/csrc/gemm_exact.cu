@@ -23,19 +23,30 @@ __device__ __forceinline__ float round_to(float x, const AnyFmt& f) {
 }
 
 template <int ALGO, bool FMA, int KIND>
-__global__ void __launch_bounds__(256) exact_mm_kernel(const __grid_constant__ MmParams p) {
+__global__ void __launch_bounds__(256) exact_mm_kernel(const __grid_constant__ MmParams p, int64_t nbatch) {
     __shared__ float As[XT][XT + 1];
     __shared__ float Bs[XT][XT];
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-    const int m0 = blockIdx.y * XT, n0 = blockIdx.x * XT;
-    const int64_t batch = blockIdx.z;
+    const int tiles_n = (p.N + XT - 1) / XT, tiles_m = (p.M + XT - 1) / XT;
+    const int64_t per_entry = (int64_t)tiles_n * tiles_m, total = per_entry * nbatch;
+    const int ksteps = (ALGO == ALGO_SEQ || (p.resume & MM_MORE)) ? p.K : p.K + 8 - p.K % 8;
+    // a CTA walks tiles (a grid of a few CTAs per SM): launched behind mm_kernel for the same product it usually has
+    // nothing to do, and finding that out must cost microseconds whatever the size of the product
+    int64_t planned = -1;       // batch entry the verdict below belongs to (reading the statistics costs a trip to L2)
+    bool taken = false;         // mm_kernel computed that entry
+    for (int64_t tile = blockIdx.x; tile < total; tile += gridDim.x) {
+    const int64_t batch = tile / per_entry;
+    const int in_entry = (int)(tile - batch * per_entry);
+    // only the batch entries mm_kernel left alone
+    if (p.defer_exact && batch != planned) { planned = batch; taken = make_plan<ALGO, FMA>(p, batch).ok; }
+    if (p.defer_exact && taken) continue;
+    const int m0 = (in_entry / tiles_n) * XT, n0 = (in_entry % tiles_n) * XT;
     const float* A = p.a + batch * p.stride_a;
     const float* B = p.b + batch * p.stride_b;
     float* C = p.c + batch * p.stride_c;
-    const int ksteps = (ALGO == ALGO_SEQ || (p.resume & MM_MORE)) ? p.K : p.K + 8 - p.K % 8;
     const int gn = n0 + tx;
 
-    float run[XPER], outer[XPER];       // the running (inner) sum; the outer sum of the CUDA order
+    float run[XPER], outer[XPER];       // the running (inner) sum; the outer sum of the CUDA order / the compensation term
 #pragma unroll
     for (int i = 0; i < XPER; ++i) {
         run[i] = 0.0f; outer[i] = 0.0f;
@@ -62,8 +73,17 @@ __global__ void __launch_bounds__(256) exact_mm_kernel(const __grid_constant__ M
 #pragma unroll
             for (int i = 0; i < XPER; ++i) {
                 const float a = As[ty + 8 * i][k];
-                run[i] = FMA ? round_to<KIND>(fma_rn(a, b, run[i]), p.gadd)
-                             : round_to<KIND>(add_rn(run[i], round_to<KIND>(mul_rn(a, b), p.gmul)), p.gadd);
+                if (ALGO == ALGO_KAHAN) {
+                    // y = Q(product - comp); t = Q(sum + y); comp = Q(Q(t - sum) - y); sum = t   (mm_kernel.h:457-520)
+                    const float y = FMA ? round_to<KIND>(fma_rn(a, b, -outer[i]), p.gadd)
+                                        : round_to<KIND>(add_rn(round_to<KIND>(mul_rn(a, b), p.gmul), -outer[i]), p.gadd);
+                    const float t = round_to<KIND>(add_rn(run[i], y), p.gadd);
+                    outer[i] = round_to<KIND>(add_rn(round_to<KIND>(add_rn(t, -run[i]), p.gadd), -y), p.gadd);
+                    run[i] = t;
+                } else {
+                    run[i] = FMA ? round_to<KIND>(fma_rn(a, b, run[i]), p.gadd)
+                                 : round_to<KIND>(add_rn(run[i], round_to<KIND>(mul_rn(a, b), p.gmul)), p.gadd);
+                }
             }
             if (ALGO == ALGO_TILE8 && ((k0 + k) & 7) == 7) {
 #pragma unroll
@@ -79,18 +99,19 @@ __global__ void __launch_bounds__(256) exact_mm_kernel(const __grid_constant__ M
             if (gm < p.M) C[(int64_t)gm * p.N + gn] = ALGO == ALGO_TILE8 ? outer[i] : run[i];
         }
     }
+    }   // tiles
 }
 
 template <int ALGO, bool FMA>
 int launch_exact(const MmParams& p, int64_t batch, cudaStream_t st) {
-    const int64_t gy = ((int64_t)p.M + XT - 1) / XT, gx = ((int64_t)p.N + XT - 1) / XT;
-    if (gy > 65535) { set_error("float_mm: M=%d has more than 65535 row tiles of %d", p.M, XT); return MPT_ERR_INVALID_ARGUMENT; }
-    const dim3 grid((unsigned)gx, (unsigned)gy, (unsigned)batch);
+    const int64_t tiles = (((int64_t)p.M + XT - 1) / XT) * (((int64_t)p.N + XT - 1) / XT) * batch;
+    const int64_t cap = (int64_t)sm_count() * 8;
+    const dim3 grid((unsigned)(tiles < cap ? tiles : cap));
     const int ka = p.gadd.kind, km = p.gmul.kind;          // run_mm sets gmul = gadd for the fused form
-    if (ka == FMT_FLOAT && km == FMT_FLOAT) exact_mm_kernel<ALGO, FMA, 0><<<grid, 256, 0, st>>>(p);
-    else if (ka == FMT_SUPERFP && km == FMT_SUPERFP) exact_mm_kernel<ALGO, FMA, 2><<<grid, 256, 0, st>>>(p);
-    else if (ka == FMT_BINARY8 && km == FMT_BINARY8) exact_mm_kernel<ALGO, FMA, 3><<<grid, 256, 0, st>>>(p);
-    else exact_mm_kernel<ALGO, FMA, 1><<<grid, 256, 0, st>>>(p);
+    if (ka == FMT_FLOAT && km == FMT_FLOAT) exact_mm_kernel<ALGO, FMA, 0><<<grid, 256, 0, st>>>(p, batch);
+    else if (ka == FMT_SUPERFP && km == FMT_SUPERFP) exact_mm_kernel<ALGO, FMA, 2><<<grid, 256, 0, st>>>(p, batch);
+    else if (ka == FMT_BINARY8 && km == FMT_BINARY8) exact_mm_kernel<ALGO, FMA, 3><<<grid, 256, 0, st>>>(p, batch);
+    else exact_mm_kernel<ALGO, FMA, 1><<<grid, 256, 0, st>>>(p, batch);
     return check_launch("float_mm");
 }
 
@@ -98,6 +119,7 @@ int launch_exact(const MmParams& p, int64_t batch, cudaStream_t st) {
 
 int launch_mm_exact(int algo, bool fma, const MmParams& p, int64_t batch, cudaStream_t st) {
     if (algo == ALGO_SEQ) return fma ? launch_exact<ALGO_SEQ, true>(p, batch, st) : launch_exact<ALGO_SEQ, false>(p, batch, st);
+    if (algo == ALGO_KAHAN) return fma ? launch_exact<ALGO_KAHAN, true>(p, batch, st) : launch_exact<ALGO_KAHAN, false>(p, batch, st);
     return fma ? launch_exact<ALGO_TILE8, true>(p, batch, st) : launch_exact<ALGO_TILE8, false>(p, batch, st);
 }
 

@@ -108,6 +108,11 @@ struct MmParams {
     // MM_FROM_C starts the running sums from what C holds (the sums after the pieces before) instead of zero,
     // MM_MORE says another piece follows, so the zero padding the CUDA order walks after the last step is left to it.
     int resume = 0;
+    // Set when a launch of exact_mm_kernel for the same product follows on the stream: a batch entry whose operand
+    // statistics rule the range-checked path out altogether (a NaN or infinity among the operands, products or
+    // sums beyond the formats' ranges, denormal intermediates of 8-bit-exponent formats) is left to that kernel,
+    // which is shaped for the exact casters; mm_kernel returns at once for it, exact_mm_kernel for every other entry.
+    int defer_exact = 0;
 };
 enum { MM_FROM_C = 1, MM_MORE = 2 };
 
@@ -688,6 +693,7 @@ __global__ void __launch_bounds__(THREADS, MINB) mm_kernel(const __grid_constant
     const int ntiles = (ksteps + BK - 1) / BK;
 
     const FastPlan plan = make_plan<ALGO, FMA>(p, batch);
+    if (CONV == CONV_NONE && p.defer_exact && !plan.ok) return;
 
     if (CONV == CONV_FWD) {
         if (tid < BM) {
@@ -922,7 +928,7 @@ int launch_conv_any(int algo, bool fma, const MmParams& p, cudaStream_t st);
 int launch_conv_wgrad_any(int algo, bool fma, const MmParams& p, cudaStream_t st);
 int launch_conv_wgrad_small_any(int algo, bool fma, const MmParams& p, cudaStream_t st);
 int launch_mm_small(int algo, bool fma, const MmParams& p, int64_t batch, bool vec, cudaStream_t st);   // ALGO_SEQ / ALGO_TILE8
-int launch_mm_exact(int algo, bool fma, const MmParams& p, int64_t batch, cudaStream_t st);             // ALGO_SEQ / ALGO_TILE8
+int launch_mm_exact(int algo, bool fma, const MmParams& p, int64_t batch, cudaStream_t st);             // all but ALGO_SR
 constexpr int kSmallTileRows = 16;      // tile height of the instantiation behind launch_conv_wgrad_small_any
 
 }  // namespace mpt
