@@ -109,18 +109,20 @@ int run_mm(const float* a, const float* b, float* c, int64_t batch, int M, int N
     const bool vec = (K % 4 == 0) && (N % 4 == 0) && (((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) & 15u) == 0);
     // formats without the FP-pipe rounding: the kernel built around the exact casters
     if (algo != ALGO_SR && !(all_float && fmt_fast)) return launch_mm_exact(algo, fma, p, batch, st);
-    if (algo != ALGO_SR && p.stats != nullptr) {
-        // range-checked launch first, then the exact kernel for the batch entries whose statistics rule that path out
-        p.defer_exact = 1;
-        int rc;
-        const int64_t big_tiles = (((int64_t)M + BM - 1) / BM) * (((int64_t)N + BN - 1) / BN) * batch;
-        // fewer 128-row tiles than SMs: the 16-row instantiation spreads the same outputs over eight times the CTAs
-        if (algo != ALGO_KAHAN && big_tiles < sm_count() && ((int64_t)M + kSmallTileRows - 1) / kSmallTileRows <= 65535)
-            rc = launch_mm_small(algo, fma, p, batch, vec, st);
-        else
-            rc = algo == ALGO_SEQ ? launch_mm_seq(fma, p, batch, vec, st)
-               : algo == ALGO_TILE8 ? launch_mm_tile8(fma, p, batch, vec, st) : launch_mm_kahan(fma, p, batch, vec, st);
-        return rc ? rc : launch_mm_exact(algo, fma, p, batch, st);
+    // fewer 128-row tiles than SMs: the 16-row instantiation spreads the same outputs over eight times the CTAs
+    const int64_t big_tiles = (((int64_t)M + BM - 1) / BM) * (((int64_t)N + BN - 1) / BN) * batch;
+    const bool small = (algo == ALGO_SEQ || algo == ALGO_TILE8) && big_tiles < sm_count() &&
+                       ((int64_t)M + kSmallTileRows - 1) / kSmallTileRows <= 65535;
+    // Range-checked launch, then the exact kernel for the batch entries whose statistics rule that path out.  The
+    // second launch costs a few microseconds when it has nothing to do, so only products long enough not to notice
+    // (2^33 MACs, about 2 ms) get it; shorter ones keep the exact path inside mm_kernel for such entries.
+    const bool defer = algo != ALGO_SR && p.stats != nullptr && (double)batch * M * N * K >= 8589934592.0;
+    p.defer_exact = defer ? 1 : 0;
+    if (small || defer) {
+        const int rc = small ? launch_mm_small(algo, fma, p, batch, vec, st)
+                     : algo == ALGO_SEQ ? launch_mm_seq(fma, p, batch, vec, st)
+                     : algo == ALGO_TILE8 ? launch_mm_tile8(fma, p, batch, vec, st) : launch_mm_kahan(fma, p, batch, vec, st);
+        return (rc || !defer) ? rc : launch_mm_exact(algo, fma, p, batch, st);
     }
     switch (algo) {
         case ALGO_SEQ: return launch_mm_seq(fma, p, batch, vec, st);
