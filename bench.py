@@ -479,7 +479,7 @@ def c4_sweep(dev, sizes=(2048, 4096, 8192), variants=True) -> dict:
                  lambda: ref.float_quantize_nearest_mm(a, b, r, S, S, S, 23, 8, 3, 4, True, False, False))
             both("mul fp32 / add fp32", "mul+add", lambda: be.float_quantize_nearest_mm(a, b, c, S, S, S, 23, 8, 23, 8, True, False, False, order="cuda"),
                  lambda: ref.float_quantize_nearest_mm(a, b, r, S, S, S, 23, 8, 23, 8, True, False, False))
-            both("mul e5m2 / add e5m2, no subnormals", "mul+add (exact casters)",
+            both("mul e5m2 / add e5m2, no subnormals", "mul+add (settling rounding)",
                  lambda: be.float_quantize_nearest_mm(a, b, c, S, S, S, 2, 5, 2, 5, False, False, False, order="cuda"),
                  lambda: ref.float_quantize_nearest_mm(a, b, r, S, S, S, 2, 5, 2, 5, False, False, False))
             both("supernormal e8m7, 1 binade each side", "mul+add (exact casters)",

@@ -343,6 +343,24 @@ struct FastRn {
     }
 };
 
+// The same rounding for a format WITHOUT subnormals (the reference's default for FloatingPoint), for a finite x that is
+// zero or a normal fp32 number and whose rounded value stays below the format's overflow threshold.  The reference
+// rounds every value at its own exponent (no fixed quantum below the smallest normal) and then settles what landed
+// below 2^min_exp (bit_helper.cu:193-198): the smallest normal value if the ROUNDED value is in the binade just below
+// it and the ORIGINAL mantissa field exceeds one half, zero otherwise, with the sign of the input either way.  Here: the
+// FP-pipe rounding without the exponent clamp, then that rule on the bits with two compares and two selects.
+MPT_HD float fast_rn_nosub(const FastRn& r, float x) {
+    const uint32_t t = f2u(x);
+    const float m = u2f(t & 0x7F800000u);
+    const float y = fma_rn(m, r.k, x);
+    const float q = fma_rn(m, -r.k, y);
+    const uint32_t a = f2u(q) & 0x7FFFFFFFu;
+    const uint32_t min_norm = (uint32_t)r.min_e_bits;                  // bit pattern of 2^min_exp
+    const bool up = a >= min_norm - 0x00800000u && (t & 0x007FFFFFu) > 0x00400000u;
+    const uint32_t settled = (t & 0x80000000u) | (up ? min_norm : 0u);
+    return a < min_norm ? u2f(settled) : q;
+}
+
 // a / b rounded to nearest even, given r = RN(1 / b) (the correctly rounded reciprocal): the quotient estimate
 // a * r is within one ulp, the remainder a - b * q is exact in one FMA, and the correction FMA lands on the correctly
 // rounded quotient (Markstein's correction step).  Exact while 1 / b, the quotient and the remainder are normal

@@ -86,7 +86,10 @@ int run_mm(const float* a, const float* b, float* c, int64_t batch, int M, int N
     p.sr_ok = all_float && FullSr::supported(fadd) && (fma || FullSr::supported(fmul));
     p.sadd = FullSr::make(fadd, rbits_add); p.smul = FullSr::make(fma ? fadd : fmul, fma ? rbits_add : rbits_mul);
 
-    const bool fmt_fast = algo == ALGO_SR ? p.sr_ok != 0 : (mm_fast_format(fadd) && (fma || mm_fast_format(fmul)));
+    // formats without subnormals: their own instantiation of the range-checked kernel (plain and sequential sums)
+    const bool nosub = (algo == ALGO_SEQ || algo == ALGO_TILE8) && mm_fast_format_nosub(fadd) && (fma || mm_fast_format_nosub(fmul));
+    p.nosub = nosub ? 1 : 0;
+    const bool fmt_fast = algo == ALGO_SR ? p.sr_ok != 0 : (nosub || (mm_fast_format(fadd) && (fma || mm_fast_format(fmul))));
     const bool fast_candidate = all_float && fmt_fast && workspace != nullptr &&
                                 workspace_bytes >= sizeof(MmStats) * (size_t)batch &&
                                 (reinterpret_cast<uintptr_t>(workspace) & 15u) == 0 && K > 0;
@@ -118,6 +121,10 @@ int run_mm(const float* a, const float* b, float* c, int64_t batch, int M, int N
     // (2^33 MACs, about 2 ms) get it; shorter ones keep the exact path inside mm_kernel for such entries.
     const bool defer = algo != ALGO_SR && p.stats != nullptr && (double)batch * M * N * K >= 8589934592.0;
     p.defer_exact = defer ? 1 : 0;
+    if (nosub && p.stats != nullptr) {
+        const int rc = launch_mm_nosub(algo, fma, p, batch, vec, st);
+        return (rc || !defer) ? rc : launch_mm_exact(algo, fma, p, batch, st);
+    }
     if (small || defer) {
         const int rc = small ? launch_mm_small(algo, fma, p, batch, vec, st)
                      : algo == ALGO_SEQ ? launch_mm_seq(fma, p, batch, vec, st)

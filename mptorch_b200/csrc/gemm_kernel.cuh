@@ -113,6 +113,7 @@ struct MmParams {
     // sums beyond the formats' ranges, denormal intermediates of 8-bit-exponent formats) is left to that kernel,
     // which is shaped for the exact casters; mm_kernel returns at once for it, exact_mm_kernel for every other entry.
     int defer_exact = 0;
+    int nosub = 0;               // the formats have no subnormals and the launch is of the NOSUB instantiation
 };
 enum { MM_FROM_C = 1, MM_MORE = 2 };
 
@@ -323,8 +324,12 @@ __device__ __forceinline__ float mac_exact(float acc, float a, float b, const An
     if (FMA) return cast_any(fma_rn(a, b, acc), fadd);
     return cast_any(add_rn(acc, cast_any(mul_rn(a, b), fmul)), fadd);
 }
-template <bool FMA>
+template <bool FMA, bool NOSUB = false>
 __device__ __forceinline__ float mac_fast(float acc, float a, float b, const FastRn& radd, const FastRn& rmul) {
+    if (NOSUB) {
+        if (FMA) return fast_rn_nosub(radd, fma_rn(a, b, acc));
+        return fast_rn_nosub(radd, add_rn(acc, fast_rn_nosub(rmul, mul_rn(a, b))));
+    }
     if (FMA) return radd(fma_rn(a, b, acc));
     return radd(add_rn(acc, rmul(mul_rn(a, b))));
 }
@@ -380,7 +385,7 @@ static __device__ __noinline__ float4 mac_exact4(float4 acc, float a, float4 b, 
 }
 
 // `nk` (1..8) accumulation steps starting at slab row kbase, for the thread's 8x4 outputs.
-template <bool FMA, bool FAST, bool PACKED, bool ADDG>
+template <bool FMA, bool FAST, bool PACKED, bool ADDG, bool NOSUB = false>
 __device__ __forceinline__ void group_steps(float (&acc)[TM][TN], const float* As, const float* Bs, int kbase, int nk,
                                             int ty, int tx, const MmParams& p) {
     if (FAST && nk == 8) {
@@ -402,10 +407,10 @@ __device__ __forceinline__ void group_steps(float (&acc)[TM][TN], const float* A
                         const float2 hi = mac_fast2<FMA, ADDG>(make_float2(acc[i][2], acc[i][3]), a2, make_float2(bv.z, bv.w), p.radd, p.rmul);
                         acc[i][0] = lo.x; acc[i][1] = lo.y; acc[i][2] = hi.x; acc[i][3] = hi.y;
                     } else {
-                        acc[i][0] = mac_fast<FMA>(acc[i][0], a, bv.x, p.radd, p.rmul);
-                        acc[i][1] = mac_fast<FMA>(acc[i][1], a, bv.y, p.radd, p.rmul);
-                        acc[i][2] = mac_fast<FMA>(acc[i][2], a, bv.z, p.radd, p.rmul);
-                        acc[i][3] = mac_fast<FMA>(acc[i][3], a, bv.w, p.radd, p.rmul);
+                        acc[i][0] = mac_fast<FMA, NOSUB>(acc[i][0], a, bv.x, p.radd, p.rmul);
+                        acc[i][1] = mac_fast<FMA, NOSUB>(acc[i][1], a, bv.y, p.radd, p.rmul);
+                        acc[i][2] = mac_fast<FMA, NOSUB>(acc[i][2], a, bv.z, p.radd, p.rmul);
+                        acc[i][3] = mac_fast<FMA, NOSUB>(acc[i][3], a, bv.w, p.radd, p.rmul);
                     }
                 }
             }
@@ -419,10 +424,10 @@ __device__ __forceinline__ void group_steps(float (&acc)[TM][TN], const float* A
         for (int i = 0; i < TM; ++i) {
             const float a = As[(ty + 16 * i) * AS_LD + kbase + k];
             if (FAST) {
-                acc[i][0] = mac_fast<FMA>(acc[i][0], a, bv.x, p.radd, p.rmul);
-                acc[i][1] = mac_fast<FMA>(acc[i][1], a, bv.y, p.radd, p.rmul);
-                acc[i][2] = mac_fast<FMA>(acc[i][2], a, bv.z, p.radd, p.rmul);
-                acc[i][3] = mac_fast<FMA>(acc[i][3], a, bv.w, p.radd, p.rmul);
+                acc[i][0] = mac_fast<FMA, NOSUB>(acc[i][0], a, bv.x, p.radd, p.rmul);
+                acc[i][1] = mac_fast<FMA, NOSUB>(acc[i][1], a, bv.y, p.radd, p.rmul);
+                acc[i][2] = mac_fast<FMA, NOSUB>(acc[i][2], a, bv.z, p.radd, p.rmul);
+                acc[i][3] = mac_fast<FMA, NOSUB>(acc[i][3], a, bv.w, p.radd, p.rmul);
             } else {
                 const float4 r = mac_exact4<FMA>(make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]), a, bv, &p);
                 acc[i][0] = r.x; acc[i][1] = r.y; acc[i][2] = r.z; acc[i][3] = r.w;
@@ -598,6 +603,10 @@ __device__ __forceinline__ float absmax_of(const float (&v)[TM][TN]) {
 //               (ALGO_SEQ), or an outer sum below this takes the fast fold (ALGO_TILE8)
 struct FastPlan { bool ok; float acc_limit; };
 
+// Formats without subnormals qualify when the launch is of the NOSUB instantiation (the host decides; the kernel's
+// roundings then settle what lands below the smallest normal value the way the reference does).
+__host__ __device__ inline bool mm_fast_format_nosub(const FpFmt& f) { return !f.sub && f.man <= 21 && f.exp >= 2; }
+
 template <int ALGO, bool FMA>
 __device__ __forceinline__ FastPlan make_plan(const MmParams& p, int64_t batch) {
     FastPlan plan{false, 0.0f};
@@ -618,12 +627,17 @@ __device__ __forceinline__ FastPlan make_plan(const MmParams& p, int64_t batch) 
         plan.acc_limit = lim;
         return plan;
     }
-    if (!mm_fast_format(p.fadd) || (!FMA && !mm_fast_format(p.fmul))) return plan;
+    const bool nosub = p.nosub != 0;
+    if (nosub ? (!mm_fast_format_nosub(p.fadd) || (!FMA && !mm_fast_format_nosub(p.fmul)))
+              : (!mm_fast_format(p.fadd) || (!FMA && !mm_fast_format(p.fmul)))) return plan;
+    if (nosub && ALGO == ALGO_KAHAN) return plan;
     // the compensated sum's bounds are worked out for formats that round; it keeps the exact path for the identity
     if (ALGO == ALGO_KAHAN && (fmt_identity(p.fadd) || (!FMA && fmt_identity(p.fmul)))) return plan;
     const int lim_add = fast_rn_exp_limit(p.fadd);
     if (!FMA && pe - 1 > fast_rn_exp_limit(p.fmul)) return plan;
-    if (p.fadd.exp == 8 || (!FMA && p.fmul.exp == 8)) {
+    // (without subnormals every value is rounded at its own exponent, which the FP-pipe rounding does for normal
+    // fp32 numbers only: the same proof that no nonzero intermediate is an fp32 denormal is needed)
+    if (nosub || p.fadd.exp == 8 || (!FMA && p.fmul.exp == 8)) {
         // the reference rounds fp32-denormal inputs of 8-bit-exponent formats one bit coarser;
         // stay exact unless every nonzero intermediate is provably far above 2^-126
         if (s.minnz_a < 0x00800000u || s.minnz_b < 0x00800000u) return plan;
@@ -656,7 +670,7 @@ __device__ __forceinline__ FastPlan make_plan(const MmParams& p, int64_t batch) 
     return plan;
 }
 
-template <int ALGO, bool FMA, bool VEC, bool PACKED, bool ADDG, int CONV = CONV_NONE, int MINB = MPT_MM_MIN_CTAS>
+template <int ALGO, bool FMA, bool VEC, bool PACKED, bool ADDG, int CONV = CONV_NONE, int MINB = MPT_MM_MIN_CTAS, bool NOSUB = false>
 __global__ void __launch_bounds__(THREADS, MINB) mm_kernel(const __grid_constant__ MmParams p) {
     extern __shared__ __align__(16) float smem[];
     float* As = smem;
@@ -756,7 +770,7 @@ __global__ void __launch_bounds__(THREADS, MINB) mm_kernel(const __grid_constant
             for (int g = 0; g * 8 < nk_tile; ++g) {
                 const int nk = (nk_tile - g * 8) < 8 ? (nk_tile - g * 8) : 8;
                 if (ALGO == ALGO_TILE8) {
-                    if (plan.ok) group_steps<FMA, true, PACKED, ADDG>(acc, as, bs, g * 8, nk, ty, tx, p);
+                    if (plan.ok) group_steps<FMA, true, PACKED, ADDG, NOSUB>(acc, as, bs, g * 8, nk, ty, tx, p);
                     else group_steps<FMA, false, false, true>(acc, as, bs, g * 8, nk, ty, tx, p);
                     // fold the group into the outer sum
                     if (plan.ok && absmax_of(aux) < plan.acc_limit) {
@@ -768,7 +782,8 @@ __global__ void __launch_bounds__(THREADS, MINB) mm_kernel(const __grid_constant
                                 aux[i][0] = lo.x; aux[i][1] = lo.y; aux[i][2] = hi.x; aux[i][3] = hi.y;
                             } else {
 #pragma unroll
-                                for (int j = 0; j < TN; ++j) aux[i][j] = p.radd(add_rn(aux[i][j], acc[i][j]));
+                                for (int j = 0; j < TN; ++j)
+                                    aux[i][j] = NOSUB ? fast_rn_nosub(p.radd, add_rn(aux[i][j], acc[i][j])) : p.radd(add_rn(aux[i][j], acc[i][j]));
                             }
 #pragma unroll
                             for (int j = 0; j < TN; ++j) acc[i][j] = 0.0f;
@@ -780,7 +795,7 @@ __global__ void __launch_bounds__(THREADS, MINB) mm_kernel(const __grid_constant
                             for (int j = 0; j < TN; ++j) { aux[i][j] = cast_any(add_rn(aux[i][j], acc[i][j]), p.gadd); acc[i][j] = 0.0f; }
                     }
                 } else {
-                    if (plan.ok && absmax_of(acc) < plan.acc_limit) group_steps<FMA, true, PACKED, ADDG>(acc, as, bs, g * 8, nk, ty, tx, p);
+                    if (plan.ok && absmax_of(acc) < plan.acc_limit) group_steps<FMA, true, PACKED, ADDG, NOSUB>(acc, as, bs, g * 8, nk, ty, tx, p);
                     else group_steps<FMA, false, false, true>(acc, as, bs, g * 8, nk, ty, tx, p);
                 }
             }
@@ -891,6 +906,20 @@ int launch_mm(const MmParams& p, int64_t batch, bool vec, cudaStream_t st) {
     return check_launch("float_mm");
 }
 
+// Formats without subnormals: the scalar range-checked path with the settling rounding (fast_rn_nosub).
+template <int ALGO, bool FMA, int TILE_ROWS = BM>
+int launch_mm_nosub_t(const MmParams& p, int64_t batch, bool vec, cudaStream_t st) {
+    static_assert(TILE_ROWS == BM, "one tile height per translation unit");
+    dim3 grid((unsigned)(((int64_t)p.N + BN - 1) / BN), (unsigned)(((int64_t)p.M + BM - 1) / BM), (unsigned)batch);
+    if (grid.y > 65535u) { set_error("float_mm: M=%d has more than 65535 row tiles of %d", p.M, BM); return MPT_ERR_INVALID_ARGUMENT; }
+    auto kern = vec ? mm_kernel<ALGO, FMA, true, false, true, CONV_NONE, MPT_MM_MIN_CTAS, true>
+                    : mm_kernel<ALGO, FMA, false, false, true, CONV_NONE, MPT_MM_MIN_CTAS, true>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+    if (e != cudaSuccess) { set_error("float_mm: cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return MPT_ERR_CUDA; }
+    kern<<<grid, THREADS, SMEM_BYTES, st>>>(p);
+    return check_launch("float_mm");
+}
+
 // Convolution launch: scalar operand copies (the gather has no 16-byte runs), packed fast path.
 template <int ALGO, bool FMA>
 int launch_conv(const MmParams& p, cudaStream_t st) {
@@ -929,6 +958,7 @@ int launch_conv_wgrad_any(int algo, bool fma, const MmParams& p, cudaStream_t st
 int launch_conv_wgrad_small_any(int algo, bool fma, const MmParams& p, cudaStream_t st);
 int launch_mm_small(int algo, bool fma, const MmParams& p, int64_t batch, bool vec, cudaStream_t st);   // ALGO_SEQ / ALGO_TILE8
 int launch_mm_exact(int algo, bool fma, const MmParams& p, int64_t batch, cudaStream_t st);             // all but ALGO_SR
+int launch_mm_nosub(int algo, bool fma, const MmParams& p, int64_t batch, bool vec, cudaStream_t st);  // ALGO_SEQ / ALGO_TILE8
 constexpr int kSmallTileRows = 16;      // tile height of the instantiation behind launch_conv_wgrad_small_any
 
 }  // namespace mpt

@@ -107,6 +107,27 @@ static int64_t sweep_all(uint64_t first, uint64_t count, uint64_t stride, uint32
     return bad;
 }
 
+// fast_rn_nosub vs the exact caster of the same format without subnormals, over the domain the range-checked GEMM
+// path guarantees: zero or a normal fp32 number, exponent at most fast_rn_exp_limit
+HC_API int64_t hc_sweep_fast_rn_nosub(int man, int exp, uint64_t first, uint64_t count, uint64_t stride, uint32_t* first_bad) {
+    const FpFmt f = make_fmt(man, exp, 0, 0);
+    const FastRn fast = FastRn::make(f);
+    const int lim = fast_rn_exp_limit(f);
+    int64_t bad = 0;
+    uint32_t worst = 0xFFFFFFFFu;
+#pragma omp parallel for reduction(+ : bad) reduction(min : worst)
+    for (int64_t i = 0; i < (int64_t)count; ++i) {
+        const uint32_t bits = (uint32_t)(first + (uint64_t)i * stride);
+        const uint32_t a = bits & 0x7FFFFFFFu;
+        const int e = (int)(a >> 23) - 127;
+        if (a != 0u && (a < 0x00800000u || e > lim)) continue;
+        const float x = u2f(bits);
+        if (f2u(fast_rn_nosub(fast, x)) != f2u(cast_fp_nearest(x, f))) { ++bad; if (bits < worst) worst = bits; }
+    }
+    if (first_bad) *first_bad = worst;
+    return bad;
+}
+
 // whole-domain truncation (FullRz) vs the exact truncating caster
 HC_API int64_t hc_sweep_full_rz(int man, int exp, int sat, uint64_t first, uint64_t count, uint64_t stride, uint32_t* first_bad) {
     const FpFmt f = make_fmt(man, exp, 1, sat);

@@ -31,6 +31,8 @@ def hc():
     L.hc_superfp.argtypes = [p, p, i64, i32, i32, i32, i32, i32]
     L.hc_sweep_fast_rn.restype = i64
     L.hc_sweep_fast_rn.argtypes = [i32, i32, u64, u64, u64, p]
+    L.hc_sweep_fast_rn_nosub.restype = i64
+    L.hc_sweep_fast_rn_nosub.argtypes = [i32, i32, u64, u64, u64, p]
     L.hc_sweep_full_rz.restype = i64
     L.hc_sweep_full_rz.argtypes = [i32, i32, i32, u64, u64, u64, p]
     L.hc_sweep_full_b8.restype = i64
@@ -180,3 +182,17 @@ def test_division_by_row_reciprocal_is_correctly_rounded(hc, lo, hi, man):
     first_bad = np.zeros(1, dtype=np.uint32)
     bad = hc.hc_sweep_div_with_rcp(12345 + man, 60_000_000, lo, hi, man, _ptr(first_bad))
     assert bad == 0, f"{bad} quotients differ from IEEE division, first dividend 0x{int(first_bad[0]):08x}"
+
+
+@pytest.mark.parametrize("fmt", [(5, 2), (4, 3), (5, 10), (8, 7), (3, 4), (2, 1), (6, 9), (8, 21), (5, 0)])
+def test_fast_rounding_without_subnormals_equals_exact_caster(hc, fmt):
+    """fast_rn_nosub (the range-checked GEMM path of formats without subnormals) against the exact caster on every
+    eighth fp32 pattern plus a dense window around the format's smallest normal value, inside the path's domain."""
+    e, m = fmt
+    bad_at = np.zeros(1, dtype=np.uint32)
+    assert hc.hc_sweep_fast_rn_nosub(m, e, 0, 1 << 29, 8, _ptr(bad_at)) == 0, hex(int(bad_at[0]))
+    assert hc.hc_sweep_fast_rn_nosub(m, e, 3, 1 << 29, 8, _ptr(bad_at)) == 0, hex(int(bad_at[0]))
+    min_norm = (2 - 2 ** (e - 1) + 127) << 23
+    for sign in (0, 1 << 31):
+        lo = max(min_norm - (3 << 23), 1 << 23)
+        assert hc.hc_sweep_fast_rn_nosub(m, e, sign + lo, 4 << 23, 1, _ptr(bad_at)) == 0, hex(int(bad_at[0]))

@@ -259,3 +259,40 @@ def test_mm_with_formats_that_round_nothing(ref_cuda, be, shape):
     ref_cuda.float_quantize_nearest_mm_fma(a, b, want, M, N, K, 23, 8, True, False, False)
     be.float_quantize_nearest_mm_fma(a, b, got, M, N, K, 23, 8, True, False, False, order="cuda")
     assert bits_equal(got, want), ("fma", shape)
+
+
+@pytest.mark.parametrize("shape", [(256, 256, 256), (78, 101, 145), (300, 2048, 136)])
+def test_mm_formats_without_subnormals(ref_cuda, be, shape):
+    """Float formats without subnormals (the default of the reference's FloatingPoint) on the range-checked path:
+    products and sums that land below the smallest normal value are settled as the reference's
+    clip_exponent_without_subnormals does (bit_helper.cu:166-199).  Operands scaled so that a large share of the
+    products and many partial sums fall below 2^min_exp, rows that cancel to zero, zeros of both signs, and operands
+    large enough to leave the range-checked path; plain and fused, batched and not."""
+    M, K, N = shape
+    g = torch.Generator(device="cuda").manual_seed(9)
+    a = torch.randn(M, K, device="cuda", generator=g)
+    b = torch.randn(K, N, device="cuda", generator=g)
+    a[0] *= 2.0 ** -7
+    a[1] *= 2.0 ** -12
+    a[2, 1::2] = -a[2, 0::2][: a[2, 1::2].numel()]
+    b[1::2, 3] = b[0::2, 3][: b[1::2, 3].numel()]
+    a[3] = 0.0
+    a[4, ::3] = -0.0
+    for (ma, ea, mm_, em) in [(2, 5, 2, 5), (10, 5, 3, 4), (7, 8, 2, 5), (3, 4, 3, 4), (1, 3, 1, 3), (21, 8, 10, 5)]:
+        for scale in (1.0, 2.0 ** -5, 300.0):
+            aa = (a * scale).contiguous()
+            want = torch.zeros(M, N, device="cuda")
+            got = torch.empty_like(want)
+            ref_cuda.float_quantize_nearest_mm(aa, b, want, M, N, K, ma, ea, mm_, em, False, False, False)
+            be.float_quantize_nearest_mm(aa, b, got, M, N, K, ma, ea, mm_, em, False, False, False, order="cuda")
+            assert bits_equal(got, want), (shape, ma, ea, mm_, em, scale, int((got.view(torch.int32) != want.view(torch.int32)).sum()))
+            ref_cuda.float_quantize_nearest_mm_fma(aa, b, want, M, N, K, ma, ea, False, False, False)
+            be.float_quantize_nearest_mm_fma(aa, b, got, M, N, K, ma, ea, False, False, False, order="cuda")
+            assert bits_equal(got, want), ("fma", shape, ma, ea, scale)
+        a3, b3 = a.view(1, M, K).repeat(3, 1, 1).contiguous(), b.view(1, K, N).repeat(3, 1, 1).contiguous()
+        a3[1] *= 2.0 ** -6
+        want = torch.zeros(3, M, N, device="cuda")
+        got = torch.empty_like(want)
+        ref_cuda.float_quantize_nearest_bmm(a3, b3, want, M, N, K, ma, ea, mm_, em, False, True, False)
+        be.float_quantize_nearest_bmm(a3, b3, got, M, N, K, ma, ea, mm_, em, False, True, False, order="cuda")
+        assert bits_equal(got, want), ("bmm saturate", shape, ma, ea, mm_, em)
