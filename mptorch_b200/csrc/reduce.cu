@@ -308,10 +308,11 @@ int mpt_softmax_forward_fmt(const float* in, float* out, int64_t outer, int chan
     MPT_REQUIRE(in && out, "softmax_forward: null pointer");
     const Caster fe = Caster::make(e), fo = Caster::make(o), fa = Caster::make(a);
     const bool tree = order != MPT_ORDER_SEQ;
-    if (tree && rows_shape_ok(g, 2048) && fe.use_fast && fo.use_fast && fa.use_fast) {
-        // trusted: exp(.) <= 1 must be inside the exp format's fast range
-        // and x - max in (-128, 0] inside the offset format's
-        const int trusted = rows_mode({&fe, &fo, &fa}, fast_rn_exp_limit(fe.any.fp) >= 0 && fast_rn_exp_limit(fo.any.fp) >= 6);
+    // trusted: exp(.) <= 1 must be inside the exp format's fast range
+    // and x - max in (-128, 0] inside the offset format's
+    const int trusted = (tree && rows_shape_ok(g, 2048))
+                            ? rows_path({&fe, &fo, &fa}, fast_rn_exp_limit(fe.any.fp) >= 0 && fast_rn_exp_limit(fo.any.fp) >= 6) : -1;
+    if (trusted >= 0) {
         RowLimits lim{};
         lim.top[1] = top_of(fo); lim.top[2] = top_of(fa);
         launch_softmax_fwd_rows(in, out, g, fe, fo, fa, trusted, lim, stream);
@@ -356,8 +357,8 @@ int mpt_softmax_backward_fmt(const float* y, const float* grad, float* out, int6
     MPT_REQUIRE(y && grad && out, "softmax_backward: null pointer");
     const Caster fa = Caster::make(a), fm = Caster::make(m);
     const bool tree = order != MPT_ORDER_SEQ;
-    if (tree && rows_shape_ok(g, 1024) && fa.use_fast && fm.use_fast) {
-        const int trusted = rows_mode({&fa, &fm}, true);
+    const int trusted = (tree && rows_shape_ok(g, 1024)) ? rows_path({&fa, &fm}, true) : -1;
+    if (trusted >= 0) {
         RowLimits lim{};
         lim.top[0] = top_of(fa); lim.top[1] = top_of(fm);
         lim.growth = (float)(pow(step_growth(fa), channel / 64 + 6) * 1.001);
@@ -385,8 +386,8 @@ int mpt_layernorm_forward_fmt(const float* in, const float* weight, const float*
     MPT_REQUIRE(in && weight && bias && out && mean && rstd, "layernorm_forward: null pointer");
     const LnFmt f{Caster::make(a), Caster::make(m), Caster::make(d), Caster::make(q), SeqAdder::make(a)};
     const bool tree = order != MPT_ORDER_SEQ;
-    if (tree && rows_shape_ok(g, 2048) && f.acc.use_fast && f.mul.use_fast && f.div.use_fast) {
-        const int trusted = rows_mode({&f.acc, &f.mul, &f.div}, true);
+    const int trusted = (tree && rows_shape_ok(g, 2048)) ? rows_path({&f.acc, &f.mul, &f.div}, true) : -1;
+    if (trusted >= 0) {
         const RowLimits lim = ln_limits(f, channel);
         launch_layernorm_fwd_rows(in, weight, bias, out, mean, rstd, eps, g, f, trusted, lim, stream);
         return check_launch("layernorm_forward");
@@ -412,8 +413,8 @@ int mpt_layernorm_backward_fmt(const float* in, const float* grad_out, const flo
     if (g.rows > 0) {
         MPT_REQUIRE(in && grad_out && weight && mean && rstd && grad_in, "layernorm_backward: null pointer");
         const bool tree = order != MPT_ORDER_SEQ;
-        if (tree && rows_shape_ok(g, 1024) && f.acc.use_fast && f.mul.use_fast) {
-            const int trusted = rows_mode({&f.acc, &f.mul}, true);
+        const int trusted = (tree && rows_shape_ok(g, 1024)) ? rows_path({&f.acc, &f.mul}, true) : -1;
+        if (trusted >= 0) {
             const RowLimits lim = ln_limits(f, channel);
             launch_layernorm_bwd_rows(in, grad_out, weight, mean, rstd, grad_in, g, f, trusted, lim, stream);
         } else

@@ -45,6 +45,7 @@ struct Caster {
     FullRn fast;
     AnyFmt any;
     int use_fast;
+    int nosub_fast;        // a float format without subnormals that the settling FP-pipe rounding (fast_rn_nosub) covers
     uint32_t neg_zero;     // what -0 rounds to: -0 in 8-bit-exponent formats, +0 in the others (as the reference does)
     __host__ static Caster make(const AnyFmt& a) {
         Caster c;
@@ -52,6 +53,7 @@ struct Caster {
         c.neg_zero = (a.kind == FMT_FLOAT && a.fp.exp == 8) ? 0x80000000u : 0u;
         c.fast = FullRn::make(a.fp);
         c.use_fast = (a.kind == FMT_FLOAT && fast_rn_supported(a.fp)) ? 1 : 0;
+        c.nosub_fast = (a.kind == FMT_FLOAT && !a.fp.sub && a.fp.man <= 21 && a.fp.exp >= 2) ? 1 : 0;
         return c;
     }
     __host__ static Caster make(const FpFmt& f) { return make(any_float(f)); }
@@ -310,9 +312,17 @@ __device__ __forceinline__ void layernorm_bwd_row(const float* x, const float* g
 // with a select) and round fp32-denormal inputs in their own way, so every rounding also records, branch-free,
 // whether it saw a nonzero denormal, and a row that did is handed to the whole-domain fallback like a row that
 // fails its range check.
+// MODE 3: formats without subnormals.  The FP-pipe rounding runs without its exponent clamp and what lands below the
+// smallest normal value is settled as the reference does (fast_rn_nosub); like MODE 2 it is exact for zero and normal
+// fp32 inputs only, so every rounding records a nonzero denormal input and the row falls back.
 template <int MODE>
 __device__ __forceinline__ float rr(const Caster& c, float x, bool& odd) {
     if (MODE == 0) return c.fast(x);
+    if (MODE == 3) {
+        const uint32_t t = __float_as_uint(x);
+        odd |= (t + t - 1u < 0x00FFFFFFu);
+        return fast_rn_nosub(c.fast.fast, x);
+    }
     if (MODE == 2) {
         // t + t drops the sign bit, so one three-input add and one compare find a nonzero fp32 denormal.  A zero result
         // can only come from a zero input here (8-bit-exponent formats have subnormals below every fp32 normal, and
@@ -330,6 +340,7 @@ __device__ __forceinline__ float rr(const Caster& c, float x, bool& odd) {
 template <int MODE>
 __device__ __forceinline__ float2 rr2(const Caster& c, float2 x, bool& odd) {
     if (MODE == 0) return make_float2(c.fast(x.x), c.fast(x.y));
+    if (MODE == 3) return make_float2(rr<3>(c, x.x, odd), rr<3>(c, x.y, odd));
     const FastRn& r = c.fast.fast;
     const uint32_t t0 = __float_as_uint(x.x), t1 = __float_as_uint(x.y);
     const int e0 = (int)(t0 & 0x7F800000u), e1 = (int)(t1 & 0x7F800000u);
@@ -347,7 +358,7 @@ __device__ __forceinline__ float2 rr2(const Caster& c, float2 x, bool& odd) {
 // a / b for two dividends, given r = RN(1 / b) (see row_div).
 template <int MODE>
 __device__ __forceinline__ float2 row_div2(float2 a, float b, float r, bool& odd) {
-    if (MODE == 2) {
+    if (MODE >= 2) {
         const uint32_t t0 = __float_as_uint(a.x), t1 = __float_as_uint(a.y);
         odd |= (t0 + t0 - 1u < 0x2BFFFFFEu) | (t1 + t1 - 1u < 0x2BFFFFFEu);
     }
@@ -369,7 +380,7 @@ struct RAdd {
 // subnormal is larger).
 template <int MODE>
 __device__ __forceinline__ float row_div(float a, float b, float r, bool& odd) {
-    if (MODE == 2) { const uint32_t t = __float_as_uint(a); odd |= (t + t - 1u < 0x2BFFFFFEu); }
+    if (MODE >= 2) { const uint32_t t = __float_as_uint(a); odd |= (t + t - 1u < 0x2BFFFFFEu); }
     return div_with_rcp(a, b, r);
 }
 
@@ -434,6 +445,15 @@ inline int rows_mode(std::initializer_list<const Caster*> cs, bool ranges_ok) {
         if (!small_exp(*c)) return 2;
     return 1;
 }
+// The same for any set of formats: -1 when the register-resident kernels do not apply (a format without either
+// FP-pipe rounding, a mixture of formats with and without subnormals, or formats without subnormals whose static
+// range conditions fail: they have no whole-domain form of the fast rounding to fall back on inside those kernels).
+inline int rows_path(std::initializer_list<const Caster*> cs, bool ranges_ok) {
+    bool all_sub = true, all_nosub = true;
+    for (const Caster* c : cs) { all_sub = all_sub && c->use_fast; all_nosub = all_nosub && c->nosub_fast; }
+    if (all_sub) return rows_mode(cs, ranges_ok);
+    return (all_nosub && ranges_ok) ? 3 : -1;
+}
 
 inline RowLimits ln_limits(const LnFmt& f, int channel) {
     RowLimits lim{};
@@ -450,6 +470,7 @@ inline RowLimits ln_limits(const LnFmt& f, int channel) {
     case J:                                                                                                                 \
         if (mode_ == 1) KERNEL<J, 1><<<grid_, thr_, 0, st_>>>(__VA_ARGS__);                                                 \
         else if (mode_ == 2) KERNEL<J, 2><<<grid_, thr_, 0, st_>>>(__VA_ARGS__);                                            \
+        else if (mode_ == 3) KERNEL<J, 3><<<grid_, thr_, 0, st_>>>(__VA_ARGS__);                                            \
         else KERNEL<J, 0><<<grid_, thr_, 0, st_>>>(__VA_ARGS__);                                                            \
         break;
 #define MPT_ROWS_DISPATCH(KERNEL, TRUSTED, ...)                                                                             \

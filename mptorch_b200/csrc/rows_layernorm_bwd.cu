@@ -78,7 +78,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) layernorm_bwd_rows_kernel
                 gi = rr<MODE>(f.acc, __fsub_rn(gi, wg), odd);
                 xh[j] = rr<MODE>(f.mul, __fmul_rn(gi, r), odd);
             }
-            if (MODE == 2) ok = !__any_sync(0xFFFFFFFFu, odd);
+            if (MODE >= 2) ok = !__any_sync(0xFFFFFFFFu, odd);
             if (ok) {
 #pragma unroll
                 for (int j = 0; j < JMAX; ++j) o[lane + 32 * j] = xh[j];

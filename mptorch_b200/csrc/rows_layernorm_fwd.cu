@@ -115,7 +115,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) layernorm_fwd_rows_kernel
                 pm = warp_max_nonneg(pm);
                 // fmaxf skips a NaN product (a NaN weight); the trusted rounding turns it into NaN as the exact one does
                 ok = pm < lim.top[1];
-                if (MODE == 2) ok = ok && !__any_sync(0xFFFFFFFFu, odd);
+                if (MODE >= 2) ok = ok && !__any_sync(0xFFFFFFFFu, odd);
             }
             if (ok) {
 #pragma unroll

@@ -49,7 +49,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) softmax_bwd_rows_kernel(c
     if (ok) {
 #pragma unroll
         for (int j = 0; j < JMAX; ++j) b[j] = __fmul_rn(rr<MODE>(fadd, __fsub_rn(b[j], s), odd), a[j]);
-        if (MODE == 2) ok = !__any_sync(0xFFFFFFFFu, odd);
+        if (MODE >= 2) ok = !__any_sync(0xFFFFFFFFu, odd);
         if (ok) {
 #pragma unroll
             for (int j = 0; j < JMAX; ++j) o[lane + 32 * j] = b[j];

@@ -53,7 +53,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) softmax_fwd_rows_kernel(c
                 const float r = __frcp_rn(sum);
 #pragma unroll
                 for (int j = 0; j < JMAX; ++j) v[j] = row_div<MODE>(v[j], sum, r, odd);
-                if (MODE == 2) ok = !__any_sync(0xFFFFFFFFu, odd);
+                if (MODE >= 2) ok = !__any_sync(0xFFFFFFFFu, odd);
                 if (ok) {
 #pragma unroll
                     for (int j = 0; j < JMAX; ++j) y[lane + 32 * j] = v[j];

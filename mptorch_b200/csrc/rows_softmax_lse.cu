@@ -58,7 +58,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) softmax_lse_rows_kernel(c
     if (ok) {
 #pragma unroll
         for (int j = 0; j < JMAX; ++j) v[j] = expf(rr<MODE>(foff, __fsub_rn(v[j], lgs), odd));
-        if (MODE == 2) ok = !__any_sync(0xFFFFFFFFu, odd);
+        if (MODE >= 2) ok = !__any_sync(0xFFFFFFFFu, odd);
         if (ok) {
 #pragma unroll
             for (int j = 0; j < JMAX; ++j) y[lane + 32 * j] = v[j];

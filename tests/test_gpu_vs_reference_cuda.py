@@ -296,3 +296,54 @@ def test_mm_formats_without_subnormals(ref_cuda, be, shape):
         ref_cuda.float_quantize_nearest_bmm(a3, b3, want, M, N, K, ma, ea, mm_, em, False, True, False)
         be.float_quantize_nearest_bmm(a3, b3, got, M, N, K, ma, ea, mm_, em, False, True, False, order="cuda")
         assert bits_equal(got, want), ("bmm saturate", shape, ma, ea, mm_, em)
+
+
+def test_softmax_and_layernorm_in_formats_without_subnormals(ref_cuda, be):
+    """The register-resident row kernels in their mode for formats without subnormals (settling rounding), against the
+    reference's CUDA kernels: inputs scaled so that exponentials, squares and products land below the smallest normal
+    value of the format, rows with fp32 denormals and infinities (which leave the trusted path), reduced dimension
+    last (register-resident kernels) and in the middle (general kernels)."""
+    import mptorch_b200.quant as q
+
+    g = torch.Generator(device="cuda").manual_seed(4)
+    x = torch.randn(6, 40, 1024, device="cuda", generator=g) * 3
+    x[0, 0] *= 8.0
+    x[0, 1, :5] = 1e-41
+    x[0, 2, 7] = float("-inf")
+    gr = torch.randn(6, 40, 1024, device="cuda", generator=g)
+    gr[1] *= 2.0 ** -10
+    for (e, m) in [(5, 10), (4, 3), (8, 7), (5, 2)]:
+        for dim in (-1, 1):
+            want = torch.zeros_like(x)
+            ref_cuda.float_quantize_nearest_softmax_forward(x, want, dim, m, e, m, e, m, e, False, False)
+            got = torch.empty_like(x)
+            be.float_quantize_nearest_softmax_forward(x, got, dim, m, e, m, e, m, e, False, False)
+            assert bits_equal(got, want), ("softmax", e, m, dim)
+            want2 = torch.zeros_like(x)
+            ref_cuda.float_quantize_nearest_softmax_lse_forward(x, want2, dim, m, e, m, e, False, False)
+            got2 = torch.empty_like(x)
+            be.float_quantize_nearest_softmax_lse_forward(x, got2, dim, m, e, m, e, False, False)
+            assert bits_equal(got2, want2), ("softmax lse", e, m, dim)
+            want3 = torch.zeros_like(x)
+            ref_cuda.float_quantize_nearest_softmax_backward(want, gr, want3, dim, m, e, m, e, False, False)
+            got3 = torch.empty_like(x)
+            be.float_quantize_nearest_softmax_backward(want, gr, got3, dim, m, e, m, e, False, False)
+            assert bits_equal(got3, want3), ("softmax bwd", e, m, dim)
+    xl = torch.randn(4, 256, 768, device="cuda", generator=g) * 2 + 0.3
+    xl[0, :8] *= 2.0 ** -9
+    xl[1, 3, :4] = 1e-40
+    gl = torch.randn(4, 256, 768, device="cuda", generator=g)
+    gl[2] *= 2.0 ** -8
+    w = torch.randn(768, device="cuda", generator=g)
+    b = torch.randn(768, device="cuda", generator=g)
+    for (e, m) in [(5, 10), (8, 7), (6, 9)]:
+        y, mean, rstd = torch.zeros_like(xl), torch.zeros(4, 256, device="cuda"), torch.zeros(4, 256, device="cuda")
+        ref_cuda.float_quantize_layernorm_forward(xl, w, b, y, mean, rstd, 1e-5, [-1], m, e, m, e, m, e, m, e, False, False)
+        gy, gm, grs = torch.empty_like(xl), torch.empty(4, 256, device="cuda"), torch.empty(4, 256, device="cuda")
+        be.float_quantize_layernorm_forward(xl, w, b, gy, gm, grs, 1e-5, [-1], m, e, m, e, m, e, m, e, False, False)
+        assert bits_equal(gy, y) and bits_equal(gm, mean) and bits_equal(grs, rstd), ("layernorm fwd", e, m)
+        gi, gg, gb = torch.zeros_like(xl), torch.zeros(768, device="cuda"), torch.zeros(768, device="cuda")
+        ref_cuda.float_quantize_layernorm_backward(xl, gl, w, b, mean, rstd, gi, gg, gb, [-1], m, e, m, e, m, e, False, False)
+        ogi, ogg, ogb = torch.empty_like(xl), torch.empty(768, device="cuda"), torch.empty(768, device="cuda")
+        be.float_quantize_layernorm_backward(xl, gl, w, b, mean, rstd, ogi, ogg, ogb, [-1], m, e, m, e, m, e, False, False)
+        assert bits_equal(ogi, gi) and bits_equal(ogg, gg) and bits_equal(ogb, gb), ("layernorm bwd", e, m)
