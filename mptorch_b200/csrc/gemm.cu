@@ -85,11 +85,12 @@ int run_mm(const float* a, const float* b, float* c, int64_t batch, int M, int N
     p.wadd = FullRn::make(fadd); p.wmul = FullRn::make(fma ? fadd : fmul);
     p.sr_ok = all_float && FullSr::supported(fadd) && (fma || FullSr::supported(fmul));
     p.sadd = FullSr::make(fadd, rbits_add); p.smul = FullSr::make(fma ? fadd : fmul, fma ? rbits_add : rbits_mul);
+    p.sr_nosub = all_float && !fadd.sub && fadd.exp >= 2 && (fma || (!fmul.sub && fmul.exp >= 2));
 
     // formats without subnormals: their own instantiation of the range-checked kernel (plain and sequential sums)
     const bool nosub = (algo == ALGO_SEQ || algo == ALGO_TILE8) && mm_fast_format_nosub(fadd) && (fma || mm_fast_format_nosub(fmul));
     p.nosub = nosub ? 1 : 0;
-    const bool fmt_fast = algo == ALGO_SR ? p.sr_ok != 0 : (nosub || (mm_fast_format(fadd) && (fma || mm_fast_format(fmul))));
+    const bool fmt_fast = algo == ALGO_SR ? (p.sr_ok != 0 || p.sr_nosub != 0) : (nosub || (mm_fast_format(fadd) && (fma || mm_fast_format(fmul))));
     const bool fast_candidate = all_float && fmt_fast && workspace != nullptr &&
                                 workspace_bytes >= sizeof(MmStats) * (size_t)batch &&
                                 (reinterpret_cast<uintptr_t>(workspace) & 15u) == 0 && K > 0;

@@ -99,6 +99,7 @@ struct MmParams {
     int whole_ok;
     FullSr sadd, smul;
     int sr_ok;
+    int sr_nosub = 0;            // formats without subnormals: the in-range stochastic rounding below covers them too
     // Kahan fast path: with |sum|, |comp| <= L and |a*b| <= P at the start of an 8-step group, every intermediate of
     // the group stays below kah_sc * L + kah_p * P + kah_const (coefficients worked out on the host from the add
     // format's rounding error, see kahan_bounds in gemm.cu)
@@ -501,7 +502,18 @@ __device__ __forceinline__ void kahan_group_fast(float (&acc)[TM][TN], float (&a
 // step's), (k / 4, lin) for the fused MAC (word k % 4), so that every generated word is used.
 // Stochastic rounding of a finite value that cannot reach the format's overflow threshold (the caller has shown so):
 // FullSr without its NaN branch and overflow select.
+template <bool NOSUB>
 __device__ __forceinline__ float sr_inrange(const FullSr& f, float x, uint32_t rnd) {
+    if (NOSUB) {
+        // Without subnormals the reference rounds every value at its own exponent and then settles what landed below
+        // 2^min_exp (bit_helper.cu:110-123): the smallest normal value with the input's sign if the rounded magnitude
+        // exceeds 2^(min_exp - 1), +0 otherwise.  Integer arithmetic throughout, so every finite input is covered.
+        const uint32_t t = __float_as_uint(x);
+        const uint32_t q = (t + (rnd & f.rmask)) & f.keep;
+        const uint32_t a = q & 0x7FFFFFFFu;
+        const uint32_t settled = a > f.min_norm - 0x00800000u ? ((t & 0x80000000u) | f.min_norm) : 0u;
+        return __uint_as_float(a < f.min_norm ? settled : q);
+    }
     // values below the smallest normal are lifted into its binade, rounded there and brought back; for all others the
     // lift is zero and both additions leave the value as it is (a zero input counts as small, so -0 never meets + 0)
     const float lift = fabsf(x) < __uint_as_float(f.min_norm) ? copysignf(__uint_as_float(f.min_norm), x) : 0.0f;
@@ -510,18 +522,18 @@ __device__ __forceinline__ float sr_inrange(const FullSr& f, float x, uint32_t r
     return add_rn(__uint_as_float(q), -lift);
 }
 // One accumulation step; FAST: the caller has shown that nothing can leave the formats' ranges.
-template <bool FMA, bool FAST>
+template <bool FMA, bool FAST, bool NOSUB = false>
 __device__ __forceinline__ float sr_mac(float acc, float a, float b, uint32_t radd_word, uint32_t rmul_word, const MmParams& p) {
     if (FAST) {
-        if (FMA) return sr_inrange(p.sadd, fma_rn(a, b, acc), radd_word);
-        return sr_inrange(p.sadd, add_rn(acc, sr_inrange(p.smul, mul_rn(a, b), rmul_word)), radd_word);
+        if (FMA) return sr_inrange<NOSUB>(p.sadd, fma_rn(a, b, acc), radd_word);
+        return sr_inrange<NOSUB>(p.sadd, add_rn(acc, sr_inrange<NOSUB>(p.smul, mul_rn(a, b), rmul_word)), radd_word);
     }
     if (FMA) return sr_add(p, fma_rn(a, b, acc), radd_word);
     return sr_add(p, add_rn(acc, sr_mul(p, mul_rn(a, b), rmul_word)), radd_word);
 }
 // Eight steps (kglob .. kglob + 7, kglob a multiple of 8) for the thread's outputs on the fast path, one Philox call per
 // output and PER steps.  The loop over the Philox calls stays rolled (the body, unrolled over the 32 outputs, is large).
-template <bool FMA>
+template <bool FMA, bool NOSUB>
 __device__ __forceinline__ void sr_group_fast(float (&acc)[TM][TN], const float* As, const float* Bs, int kbase, uint32_t kglob,
                                               int ty, int tx, int m0, int n0, int64_t batch, const MmParams& p) {
     constexpr int PER = FMA ? 4 : 2;          // accumulation steps served by one Philox call
@@ -553,8 +565,8 @@ __device__ __forceinline__ void sr_group_fast(float (&acc)[TM][TN], const float*
                 float v = acc[i][j];
 #pragma unroll
                 for (int u = 0; u < PER; ++u)
-                    v = FMA ? sr_mac<true, true>(v, av[u], bv[u][j], ph.c[u], 0u, p)
-                            : sr_mac<false, true>(v, av[u], bv[u][j], ph.c[2 * u], ph.c[2 * u + 1], p);
+                    v = FMA ? sr_mac<true, true, NOSUB>(v, av[u], bv[u][j], ph.c[u], 0u, p)
+                            : sr_mac<false, true, NOSUB>(v, av[u], bv[u][j], ph.c[2 * u], ph.c[2 * u + 1], p);
                 acc[i][j] = v;
             }
         }
@@ -618,7 +630,7 @@ __device__ __forceinline__ FastPlan make_plan(const MmParams& p, int64_t batch) 
     if (ALGO == ALGO_SR) {
         // stochastic rounding moves a value by less than one quantum: a product below 2^pe stays at or below 2^pe, a sum
         // grows by at most (1 + 2^-man) per step; nothing may reach the upper edge of the top binade (the exponent clip)
-        if (!p.sr_ok) return plan;
+        if (!p.sr_ok && !p.sr_nosub) return plan;
         const int top_add = p.fadd.max_store - 127, top_mul = p.fmul.max_store - 127;
         if (!FMA && pe > top_mul) return plan;
         const float lim = ldexpf(1.0f, top_add) / p.growth8_sr - ldexpf(8.0f, pe);
@@ -821,7 +833,7 @@ __global__ void __launch_bounds__(THREADS, MINB) mm_kernel(const __grid_constant
         } else {   // ALGO_SR
             for (int g = 0; g * 8 < nk_tile; ++g) {
                 const uint32_t kglob = (uint32_t)(t * BK + g * 8);
-                if (plan.ok && absmax_of(acc) < plan.acc_limit) sr_group_fast<FMA>(acc, as, bs, g * 8, kglob, ty, tx, m0, n0, batch, p);
+                if (plan.ok && absmax_of(acc) < plan.acc_limit) sr_group_fast<FMA, NOSUB>(acc, as, bs, g * 8, kglob, ty, tx, m0, n0, batch, p);
                 else {
                     float tmp[TM * TN];
 #pragma unroll
@@ -900,6 +912,8 @@ int launch_mm(const MmParams& p, int64_t batch, bool vec, cudaStream_t st) {
                               : mm_kernel<ALGO, FMA, true, false, true, CONV_NONE, kMinB>)
                     : (packed ? (add_guard ? mm_kernel<ALGO, FMA, false, kHasFast, true, CONV_NONE, kMinB> : mm_kernel<ALGO, FMA, false, kHasFast, !kCanDrop, CONV_NONE, kMinB>)
                               : mm_kernel<ALGO, FMA, false, false, true, CONV_NONE, kMinB>);
+    if (ALGO == ALGO_SR && p.sr_nosub)      // formats without subnormals: the instantiation with their in-range rounding
+        kern = vec ? mm_kernel<ALGO, FMA, true, false, true, CONV_NONE, kMinB, true> : mm_kernel<ALGO, FMA, false, false, true, CONV_NONE, kMinB, true>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
     if (e != cudaSuccess) { set_error("float_mm: cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return MPT_ERR_CUDA; }
     kern<<<grid, THREADS, SMEM_BYTES, st>>>(p);

@@ -237,16 +237,16 @@ def test_stochastic_range_checked_path(be, oracle, fma):
             a = (rng.standard_normal((M, K)) * scale).astype(np.float32)
             b = rng.standard_normal((K, N)).astype(np.float32)
             a[rng.random((M, K)) < 0.1] = 0.0
-            for sat in (False, True):
+            for sat, sub in ((False, True), (True, True), (False, False), (True, False)):      # without subnormals too
                 c = torch.full((M, N), float("nan"), device="cuda")
                 if fma:
-                    be.float_quantize_stochastic_mm_fma(dev(a), dev(b), c, M, N, K, fadd[1], fadd[0], rb_a, True, sat, seed=seed)
-                    want = oracle.mm_sr(a, b, fadd[1], fadd[0], rb_a, fadd[1], fadd[0], rb_a, True, sat, True, seed)
+                    be.float_quantize_stochastic_mm_fma(dev(a), dev(b), c, M, N, K, fadd[1], fadd[0], rb_a, sub, sat, seed=seed)
+                    want = oracle.mm_sr(a, b, fadd[1], fadd[0], rb_a, fadd[1], fadd[0], rb_a, sub, sat, True, seed)
                 else:
-                    be.float_quantize_stochastic_mm(dev(a), dev(b), c, M, N, K, fadd[1], fadd[0], rb_a, fmul[1], fmul[0], rb_m, True, sat, seed=seed)
-                    want = oracle.mm_sr(a, b, fadd[1], fadd[0], rb_a, fmul[1], fmul[0], rb_m, True, sat, False, seed)
+                    be.float_quantize_stochastic_mm(dev(a), dev(b), c, M, N, K, fadd[1], fadd[0], rb_a, fmul[1], fmul[0], rb_m, sub, sat, seed=seed)
+                    want = oracle.mm_sr(a, b, fadd[1], fadd[0], rb_a, fmul[1], fmul[0], rb_m, sub, sat, False, seed)
                 got = c.cpu().numpy()
-                assert same_bits(got, want), f"{fadd} {fmul} fma={fma} {(M, K, N)} x{scale} sat={sat}: " + mismatch_report(got, want)
+                assert same_bits(got, want), f"{fadd} {fmul} fma={fma} {(M, K, N)} x{scale} sat={sat} sub={sub}: " + mismatch_report(got, want)
 
 
 def test_stochastic_matches_oracle_philox(be, oracle):
