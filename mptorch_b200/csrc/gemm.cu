@@ -163,8 +163,10 @@ int run_conv(const float* x, const float* wt, float* y, int n_img, int c_in, int
     p.kah_sc = p.kah_p = p.kah_const = 0.0f; p.growth8_sr = 1.0f;
     p.wadd = p.wmul = FullRn::make(fadd);
     p.sadd = p.smul = FullSr::make(fadd, 0);
-    const bool fast_candidate = fast_rn_supported(fadd) && (fma || fast_rn_supported(fmul)) && workspace != nullptr &&
+    const bool nosub = mm_fast_format_nosub(fadd) && (fma || mm_fast_format_nosub(fmul));
+    const bool fast_candidate = (nosub || (fast_rn_supported(fadd) && (fma || fast_rn_supported(fmul)))) && workspace != nullptr &&
                                 workspace_bytes >= sizeof(MmStats) && (reinterpret_cast<uintptr_t>(workspace) & 15u) == 0 && K64 > 0;
+    p.nosub = (nosub && fast_candidate) ? 1 : 0;
     if (K64 == 0) {
         cudaError_t e = cudaMemsetAsync(y, 0, sizeof(float) * (size_t)n_img * c_out * OH * OW, st);
         if (e != cudaSuccess) { set_error("float_conv2d: cudaMemsetAsync: %s", cudaGetErrorString(e)); return MPT_ERR_CUDA; }
@@ -223,8 +225,10 @@ int run_conv_wgrad(const float* gout, const float* x, float* gw, int n_img, int 
     p.kah_sc = p.kah_p = p.kah_const = 0.0f; p.growth8_sr = 1.0f;
     p.wadd = p.wmul = FullRn::make(fadd);
     p.sadd = p.smul = FullSr::make(fadd, 0);
-    const bool fast_candidate = fast_rn_supported(fadd) && (fma || fast_rn_supported(fmul)) && workspace != nullptr &&
+    const bool nosub = mm_fast_format_nosub(fadd) && (fma || mm_fast_format_nosub(fmul));
+    const bool fast_candidate = (nosub || (fast_rn_supported(fadd) && (fma || fast_rn_supported(fmul)))) && workspace != nullptr &&
                                 workspace_bytes >= sizeof(MmStats) && (reinterpret_cast<uintptr_t>(workspace) & 15u) == 0;
+    p.nosub = (nosub && fast_candidate) ? 1 : 0;
     if (fast_candidate) {
         MmStats* s = static_cast<MmStats*>(workspace);
         stats_init_kernel<<<1, 256, 0, st>>>(s, 1);

@@ -940,6 +940,7 @@ int launch_conv(const MmParams& p, cudaStream_t st) {
     dim3 grid((unsigned)(((int64_t)p.N + BN - 1) / BN), (unsigned)(((int64_t)p.M + BM - 1) / BM), 1);
     const bool add_guard = FMA || (p.fmul.min_exp - p.fmul.man) < (p.fadd.min_exp - p.fadd.man);
     auto kern = add_guard ? mm_kernel<ALGO, FMA, false, true, true, CONV_FWD> : mm_kernel<ALGO, FMA, false, true, FMA, CONV_FWD>;
+    if (p.nosub) kern = mm_kernel<ALGO, FMA, false, false, true, CONV_FWD, MPT_MM_MIN_CTAS, true>;      // formats without subnormals
     const size_t smem = SMEM_BYTES + BM * sizeof(ConvRow);
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) { set_error("float_conv2d: cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return MPT_ERR_CUDA; }
@@ -956,6 +957,7 @@ int launch_conv_wgrad(const MmParams& p, cudaStream_t st) {
     dim3 grid((unsigned)(((int64_t)p.N + BN - 1) / BN), (unsigned)(((int64_t)p.M + BM - 1) / BM), 1);
     const bool add_guard = FMA || (p.fmul.min_exp - p.fmul.man) < (p.fadd.min_exp - p.fadd.man);
     auto kern = add_guard ? mm_kernel<ALGO, FMA, false, true, true, CONV_WGRAD> : mm_kernel<ALGO, FMA, false, true, FMA, CONV_WGRAD>;
+    if (p.nosub) kern = mm_kernel<ALGO, FMA, false, false, true, CONV_WGRAD, MPT_MM_MIN_CTAS, true>;    // formats without subnormals
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
     if (e != cudaSuccess) { set_error("float_conv2d_wgrad: cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return MPT_ERR_CUDA; }
     kern<<<grid, THREADS, SMEM_BYTES, st>>>(p);

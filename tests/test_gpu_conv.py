@@ -64,9 +64,12 @@ CASES = [
 @pytest.mark.parametrize("case", CASES)
 @pytest.mark.parametrize("order", ["cuda", "seq"])
 @pytest.mark.parametrize("fma", [False, True])
-def test_implicit_conv_equals_unfold_composition(q, monkeypatch, case, order, fma):
+@pytest.mark.parametrize("sub", [True, False])
+def test_implicit_conv_equals_unfold_composition(q, monkeypatch, case, order, fma, sub):
+    """`sub` False: MAC formats without subnormals (the settling rounding of the implicit kernels against that of the
+    plain GEMM, which is pinned against the reference's CUDA kernel)."""
     n, c, h, w, cout, k, s, p, d, groups, bias, mode = case
-    add, mul = fp(5, 10), fp(4, 3)
+    add, mul = fp(5, 10, sub), fp(4, 3, sub)
     mac = (add,) if fma else (add, mul)
     wq = q.quantizer(forward_number=fp(5, 2, True, True), forward_rounding="nearest")
     fmt = q.QAffineFormats(fwd_mac=mac, bwd_mac=mac, fwd_rnd="nearest", bwd_rnd="nearest", weight_quant=wq, input_quant=wq,
