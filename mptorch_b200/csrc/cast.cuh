@@ -349,16 +349,41 @@ struct FastRn {
 // below 2^min_exp (bit_helper.cu:193-198): the smallest normal value if the ROUNDED value is in the binade just below
 // it and the ORIGINAL mantissa field exceeds one half, zero otherwise, with the sign of the input either way.  Here: the
 // FP-pipe rounding without the exponent clamp, then that rule on the bits with two compares and two selects.
+MPT_HD float nosub_settle(uint32_t min_norm, uint32_t t, float q) {
+    const uint32_t a = f2u(q) & 0x7FFFFFFFu;
+    const bool up = a >= min_norm - 0x00800000u && (t & 0x007FFFFFu) > 0x00400000u;
+    const uint32_t settled = (t & 0x80000000u) | (up ? min_norm : 0u);
+    return a < min_norm ? u2f(settled) : q;
+}
 MPT_HD float fast_rn_nosub(const FastRn& r, float x) {
     const uint32_t t = f2u(x);
     const float m = u2f(t & 0x7F800000u);
     const float y = fma_rn(m, r.k, x);
     const float q = fma_rn(m, -r.k, y);
-    const uint32_t a = f2u(q) & 0x7FFFFFFFu;
-    const uint32_t min_norm = (uint32_t)r.min_e_bits;                  // bit pattern of 2^min_exp
-    const bool up = a >= min_norm - 0x00800000u && (t & 0x007FFFFFu) > 0x00400000u;
-    const uint32_t settled = (t & 0x80000000u) | (up ? min_norm : 0u);
-    return a < min_norm ? u2f(settled) : q;
+    return nosub_settle((uint32_t)r.min_e_bits, t, q);                 // min_e_bits: the bit pattern of 2^min_exp
+}
+// The same function for roundings whose result is rarely a nonzero value below the smallest normal one (a sum of
+// rounded products: it is zero, or at least one quantum of the product format): the settling rule sits behind a
+// branch (a call, so that the compiler does not turn it back into selects), which leaves three integer instructions
+// on the common path instead of nine.  A zero result (from a zero input only: a normal value rounded at its own exponent
+// is never zero) needs no settling beyond the input's sign, which the magic addition drops and one OR puts back.
+#ifdef __CUDA_ARCH__
+static __device__ __noinline__ float nosub_settle_cold(uint32_t min_norm, uint32_t t, float q) { return nosub_settle(min_norm, t, q); }
+#endif
+MPT_HD float fast_rn_nosub_rare(const FastRn& r, float x) {
+    const uint32_t t = f2u(x);
+    const float m = u2f(t & 0x7F800000u);
+    const float y = fma_rn(m, r.k, x);
+    const float q = fma_rn(m, -r.k, y);
+    const uint32_t qb = f2u(q) | (t & 0x80000000u);
+    if (qb + qb - 1u < 2u * (uint32_t)r.min_e_bits - 1u) {             // 0 < |q| < 2^min_exp
+#ifdef __CUDA_ARCH__
+        return nosub_settle_cold((uint32_t)r.min_e_bits, t, q);
+#else
+        return nosub_settle((uint32_t)r.min_e_bits, t, q);
+#endif
+    }
+    return u2f(qb);
 }
 
 // a / b rounded to nearest even, given r = RN(1 / b) (the correctly rounded reciprocal): the quotient estimate

@@ -328,8 +328,10 @@ __device__ __forceinline__ float mac_exact(float acc, float a, float b, const An
 template <bool FMA, bool NOSUB = false>
 __device__ __forceinline__ float mac_fast(float acc, float a, float b, const FastRn& radd, const FastRn& rmul) {
     if (NOSUB) {
+        // products land below the smallest normal value all the time (branch-free settling); sums of rounded products
+        // almost never do (settling behind a branch)
         if (FMA) return fast_rn_nosub(radd, fma_rn(a, b, acc));
-        return fast_rn_nosub(radd, add_rn(acc, fast_rn_nosub(rmul, mul_rn(a, b))));
+        return fast_rn_nosub_rare(radd, add_rn(acc, fast_rn_nosub(rmul, mul_rn(a, b))));
     }
     if (FMA) return radd(fma_rn(a, b, acc));
     return radd(add_rn(acc, rmul(mul_rn(a, b))));
@@ -795,7 +797,7 @@ __global__ void __launch_bounds__(THREADS, MINB) mm_kernel(const __grid_constant
                             } else {
 #pragma unroll
                                 for (int j = 0; j < TN; ++j)
-                                    aux[i][j] = NOSUB ? fast_rn_nosub(p.radd, add_rn(aux[i][j], acc[i][j])) : p.radd(add_rn(aux[i][j], acc[i][j]));
+                                    aux[i][j] = NOSUB ? fast_rn_nosub_rare(p.radd, add_rn(aux[i][j], acc[i][j])) : p.radd(add_rn(aux[i][j], acc[i][j]));
                             }
 #pragma unroll
                             for (int j = 0; j < TN; ++j) acc[i][j] = 0.0f;

@@ -122,7 +122,8 @@ HC_API int64_t hc_sweep_fast_rn_nosub(int man, int exp, uint64_t first, uint64_t
         const int e = (int)(a >> 23) - 127;
         if (a != 0u && (a < 0x00800000u || e > lim)) continue;
         const float x = u2f(bits);
-        if (f2u(fast_rn_nosub(fast, x)) != f2u(cast_fp_nearest(x, f))) { ++bad; if (bits < worst) worst = bits; }
+        const uint32_t want = f2u(cast_fp_nearest(x, f));
+        if (f2u(fast_rn_nosub(fast, x)) != want || f2u(fast_rn_nosub_rare(fast, x)) != want) { ++bad; if (bits < worst) worst = bits; }
     }
     if (first_bad) *first_bad = worst;
     return bad;
