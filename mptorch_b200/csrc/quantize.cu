@@ -80,6 +80,27 @@ struct FpNearestFast {
     __device__ __forceinline__ float one(float x, int64_t) const { return r(x); }
     MPT_VEC_FROM_ONE
 };
+// Formats without subnormals (the reference's FloatingPoint default): the settling FP-pipe rounding for zero and for
+// normal fp32 inputs below the overflow threshold, which is nearly every input; fp32 denormals, overflow, infinities
+// and NaN take the exact caster behind one compare.
+struct FpNearestFastNoSub {
+    FpFmt f;
+    FastRn r;
+    uint32_t span;        // as bit patterns: |x| in [2^-126, min(overflow threshold, largest magnitude the magic constant of an
+                          // 8-bit-exponent format can serve)) is the fast domain
+    __host__ static FpNearestFastNoSub make(const FpFmt& f) {
+        const FullRn full = FullRn::make(f);
+        const uint32_t top = full.ovf_from < full.exact_from ? full.ovf_from : full.exact_from;
+        return FpNearestFastNoSub{f, full.fast, top - 0x00800000u};
+    }
+    __device__ __forceinline__ float one(float x, int64_t) const {
+        const uint32_t a = __float_as_uint(x) & 0x7FFFFFFFu;
+        if (a == 0u) return x;
+        if (a - 0x00800000u >= span) return cast_fp_nearest(x, f);
+        return fast_rn_nosub(r, x);
+    }
+    MPT_VEC_FROM_ONE
+};
 struct FpTruncateFast {
     FullRz r;
     __device__ __forceinline__ float one(float x, int64_t) const { return r(x); }
@@ -250,6 +271,7 @@ int mpt_float_quantize_nearest(const float* in, float* out, int64_t n, int man, 
     MPT_REQUIRE(valid_format(man, exp), "float_quantize_nearest: unsupported format man=%d exp=%d", man, exp);
     const FpFmt f = make_fmt(man, exp, subnormals, saturate);
     if (fast_rn_supported(f)) return launch_map(in, out, n, FpNearestFast{FullRn::make(f)}, as_stream(stream), "float_quantize_nearest");
+    if (!f.sub && f.man <= 21 && f.exp >= 2) return launch_map(in, out, n, FpNearestFastNoSub::make(f), as_stream(stream), "float_quantize_nearest");
     return launch_map(in, out, n, FpNearest{f}, as_stream(stream), "float_quantize_nearest");
 }
 
@@ -299,6 +321,7 @@ int mpt_float_quantize_multi(const float* const* in, float* const* out, const in
     const char* who = "float_quantize_multi";
     if (rounding == MPT_RND_NEAREST) {
         if (fast_rn_supported(f)) return launch_multi(in, out, n, count, SameForAll<FpNearestFast>{{FullRn::make(f)}}, st, who);
+        if (!f.sub && f.man <= 21 && f.exp >= 2) return launch_multi(in, out, n, count, SameForAll<FpNearestFastNoSub>{FpNearestFastNoSub::make(f)}, st, who);
         return launch_multi(in, out, n, count, SameForAll<FpNearest>{{f}}, st, who);
     }
     if (rounding == MPT_RND_TRUNCATE) {
