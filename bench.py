@@ -695,7 +695,9 @@ def main() -> int:
         out = torch.empty(x.shape[0], S, device=dev)
         be.float_quantize_nearest_mm(x, y, out, x.shape[0], S, S, FMT["man_add"], FMT["exp_add"], FMT["man_mul"],
                                      FMT["exp_mul"], True, False, False, order=args.order)
-        launches[0] += 4                                     # stats_init_kernel, two stats_kernel, mm_kernel
+        # stats_init_kernel, two stats_kernel, mm_kernel, and for products of at least 2^33 MACs the exact_mm_kernel
+        # launch that follows it (which finds nothing to do on these operands)
+        launches[0] += 4 + (1 if x.shape[0] * S * S >= 2 ** 33 else 0)
         return out
 
     def step():
@@ -704,7 +706,7 @@ def main() -> int:
         if world == 1:
             be.float_quantize_nearest_mm(a, b, c_full, S, S, S, FMT["man_add"], FMT["exp_add"], FMT["man_mul"],
                                          FMT["exp_mul"], True, False, False, order=args.order)
-            launches[0] += 4
+            launches[0] += 4 + (1 if S ** 3 >= 2 ** 33 else 0)
         else:
             sharded_float_mm(a, b, S, mm_rows, panels=panels, out=c_full)
 
