@@ -493,6 +493,132 @@ def c4_sweep(dev, sizes=(2048, 4096, 8192), variants=True) -> dict:
     return {"rows": rows}
 
 
+def formats_sweep(dev) -> dict:
+    """The paths outside the three benchmark format pairs, each beside the reference's own CUDA kernel (unmodified
+    sources built for sm_100a) on the same tensors, with a bit comparison: float formats WITHOUT subnormals (the
+    reference's FloatingPoint default) through the quantizer, the GEMM (plain, compensated, stochastic), softmax,
+    layernorm and the convolution layer; products whose operands rule the range-checked path out; and the block
+    training step in formats without subnormals."""
+    import torch
+
+    import mptorch_b200.quant as q
+    import mptorch_b200.quant.modules as qmod
+    from mptorch_b200 import FloatingPoint
+    from mptorch_b200 import backend as be
+    from mptorch_b200.gpt2_block import BlockConfig, QTinyGPT, default_formats
+
+    ref = _ref_cuda()
+    g = torch.Generator(device=dev).manual_seed(1)
+
+    def clock(fn, n=3):
+        fn()
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        return e0.elapsed_time(e1) / n
+
+    def same(x, y):
+        return bool(((x.view(torch.int32) == y.view(torch.int32)) | (x.isnan() & y.isnan())).all())
+
+    rows = []
+
+    def row(name, ours, theirs=None, o=None, r=None):
+        rec = {"path": name, "ms": round(clock(ours), 4)}
+        if ref is not None and theirs is not None:
+            rec["reference_cuda_ms"] = round(clock(theirs), 4)
+            if o is not None:
+                rec["same_bits_as_reference_cuda"] = same(o, r)
+        rows.append(rec)
+
+    x = torch.randn(1 << 26, device=dev, generator=g) * 3
+    row("float_quantize nearest e4m3 without subnormals, 2^26 elements", lambda: be.float_quantize_nearest(x, 3, 4, False, True),
+        lambda: ref.float_quantize_nearest(x, 3, 4, False, True), be.float_quantize_nearest(x, 3, 4, False, True),
+        ref.float_quantize_nearest(x, 3, 4, False, True) if ref is not None else None)
+    del x
+    S = 2048
+    a = torch.randn(S, S, device=dev, generator=g)
+    b = torch.randn(S, S, device=dev, generator=g)
+    c, r = torch.empty(S, S, device=dev), torch.empty(S, S, device=dev)
+
+    def mm(name, aa, ma, ea, mm_, em, sub, sat, comp):
+        row("float_mm 2048^3 " + name,
+            lambda: be.float_quantize_nearest_mm(aa, b, c, S, S, S, ma, ea, mm_, em, sub, sat, comp, order="cuda"),
+            lambda: ref.float_quantize_nearest_mm(aa, b, r, S, S, S, ma, ea, mm_, em, sub, sat, comp), c, r)
+
+    mm("e5m2 / e5m2 without subnormals", a, 2, 5, 2, 5, False, False, False)
+    mm("e5m10 / e4m3 without subnormals", a, 10, 5, 3, 4, False, False, False)
+    mm("e5m10 / e4m3 without subnormals, compensated", a, 10, 5, 3, 4, False, False, True)
+    mm("fp32 add / e4m3 mul, compensated", a, 23, 8, 3, 4, True, False, True)
+    mm("e3m4 / e3m4 (range checks fail: exact kernel)", a, 4, 3, 4, 3, True, True, False)
+    mm("e5m2 / e5m2, operands x 200 (sums overflow: exact kernel)", a * 200, 2, 5, 2, 5, True, False, False)
+    a_inf = a.clone()
+    a_inf[0, 0] = float("inf")
+    mm("e5m10 / e4m3, one infinity in A (exact kernel)", a_inf, 10, 5, 3, 4, True, False, False)
+    for sub in (True, False):
+        row("float_mm stochastic 2048^3 e5m10 / e4m3 subnormals=%s" % sub,
+            lambda: be.float_quantize_stochastic_mm(a, b, c, S, S, S, 10, 5, 13, 3, 4, 20, sub, False, seed=5),
+            lambda: ref.float_quantize_stochastic_mm(a, b, r, S, S, S, 10, 5, 13, 3, 4, 20, sub, False))
+    del a, b, c, r, a_inf
+    att = torch.randn(12288, 1024, device=dev, generator=g)
+    so, sr = torch.empty_like(att), torch.empty_like(att)
+    row("softmax forward 12288 x 1024 e5m10 without subnormals",
+        lambda: be.float_quantize_nearest_softmax_forward(att, so, -1, 10, 5, 10, 5, 10, 5, False, False),
+        lambda: ref.float_quantize_nearest_softmax_forward(att, sr, -1, 10, 5, 10, 5, 10, 5, False, False), so, sr)
+    del att, so, sr
+    xl = torch.randn(16384, 768, device=dev, generator=g)
+    w, bb = torch.randn(768, device=dev, generator=g), torch.randn(768, device=dev, generator=g)
+    y1, m1, r1 = torch.empty_like(xl), torch.empty(16384, device=dev), torch.empty(16384, device=dev)
+    y2, m2, r2 = torch.empty_like(xl), torch.empty(16384, device=dev), torch.empty(16384, device=dev)
+    row("layernorm forward 16384 x 768 e5m10 without subnormals",
+        lambda: be.float_quantize_layernorm_forward(xl, w, bb, y1, m1, r1, 1e-5, [-1], 10, 5, 10, 5, 10, 5, 10, 5, False, False),
+        lambda: ref.float_quantize_layernorm_forward(xl, w, bb, y2, m2, r2, 1e-5, [-1], 10, 5, 10, 5, 10, 5, 10, 5, False, False), y1, y2)
+    del xl, y1, y2
+    for sub in (True, False):
+        fmt = q.QAffineFormats(fwd_mac=(FloatingPoint(5, 10, sub, False), FloatingPoint(4, 3, sub, False)),
+                               bwd_mac=(FloatingPoint(5, 10, sub, False), FloatingPoint(4, 3, sub, False)))
+        conv = q.QConv2d(64, 64, 3, fmt, padding=1).to(dev)
+        xc = torch.randn(64, 64, 56, 56, device=dev, generator=g)
+        with torch.no_grad():
+            row("QConv2d forward 64 x 64 x 56 x 56, 3 x 3, implicit GEMM, subnormals=%s" % sub, lambda: conv(xc))
+            eligible = qmod.implicit_conv_eligible
+            qmod.implicit_conv_eligible = lambda f, t: False
+            try:
+                row("QConv2d forward, unfold + GEMM, subnormals=%s" % sub, lambda: conv(xc))
+            finally:
+                qmod.implicit_conv_eligible = eligible
+        del conv, xc
+    for sub in (True, False):
+        torch.manual_seed(0)
+        model = QTinyGPT(BlockConfig(), default_formats(FloatingPoint(5, 10, sub, False), FloatingPoint(4, 3, sub, False))).to(dev)
+        idx = torch.randint(0, 50257, (8, 1024), device=dev)
+
+        def step():
+            model.zero_grad(set_to_none=True)
+            model(idx).float().pow(2).mean().backward()
+
+        row("GPT-2-small block forward + backward (no update), subnormals=%s" % sub, step)
+        del model
+    return {"rows": rows}
+
+
+def run_formats(args) -> int:
+    import torch
+
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    out = formats_sweep(dev)
+    for r in out["rows"]:
+        sys.stderr.write("%-76s %9.3f ms%s\n" % (r["path"], r["ms"], ("   reference CUDA %9.3f ms%s" % (
+            r["reference_cuda_ms"], ("  same bits %s" % r["same_bits_as_reference_cuda"]) if "same_bits_as_reference_cuda" in r else ""))
+            if "reference_cuda_ms" in r else ""))
+    print(json.dumps({"metric": "paths outside the benchmark format pairs, ms beside the reference's CUDA kernels", "unit": "ms", "n_gpus": 1, **out}))
+    return 0
+
+
 def run_c4(args) -> int:
     import torch
 
@@ -639,7 +765,7 @@ def main() -> int:
                     help="row panels per rank whose all-gather runs under the next panel's kernel (1: one launch and one "
                          "all-gather, the fastest form measured at 2, 4 and 8 GPUs)")
     ap.add_argument("--quant-log2n", type=int, default=28, help="log2 of the quantizer leg's element count")
-    ap.add_argument("--workload", default="mm", choices=["mm", "block", "kernels", "c4"],
+    ap.add_argument("--workload", default="mm", choices=["mm", "block", "kernels", "c4", "formats"],
                     help="mm: the headline float_mm (default); block: benchmark config 5, one GPT-2-small-shaped block, "
                          "fwd+bwd with (add e5m10, mul e4m3) MACs, data parallel with a gradient all-reduce")
     ap.add_argument("--record-counters", nargs="+", metavar="CSV",
@@ -660,6 +786,8 @@ def main() -> int:
         return run_kernels(args)
     if args.workload == "c4":
         return run_c4(args)
+    if args.workload == "formats":
+        return run_formats(args)
 
     import torch
     import torch.distributed as dist
