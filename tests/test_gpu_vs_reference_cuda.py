@@ -347,3 +347,27 @@ def test_softmax_and_layernorm_in_formats_without_subnormals(ref_cuda, be):
         ogi, ogg, ogb = torch.empty_like(xl), torch.empty(768, device="cuda"), torch.empty(768, device="cuda")
         be.float_quantize_layernorm_backward(xl, gl, w, b, mean, rstd, ogi, ogg, ogb, [-1], m, e, m, e, m, e, False, False)
         assert bits_equal(ogi, gi) and bits_equal(ogg, gg) and bits_equal(ogb, gb), ("layernorm bwd", e, m)
+
+
+def test_large_products_leave_failed_range_checks_to_the_exact_kernel(ref_cuda, be):
+    """Products of at least 2^33 MACs launch the exact kernel behind the range-checked one; it computes the batch
+    entries whose operand statistics rule the range-checked path out and skips the others.  Batch of two 2048^3
+    products: entry 0 is ordinary, entry 1 holds one infinity; then a single product with operands scaled by 200
+    (sums overflow e5m2).  Against the reference's CUDA kernels."""
+    S = 2048
+    g = torch.Generator(device="cuda").manual_seed(6)
+    a = torch.randn(2, S, S, device="cuda", generator=g)
+    b = torch.randn(2, S, S, device="cuda", generator=g)
+    a[1, 5, 7] = float("inf")
+    want = torch.zeros(2, S, S, device="cuda")
+    got = torch.full((2, S, S), float("nan"), device="cuda")
+    ref_cuda.float_quantize_nearest_bmm(a, b, want, S, S, S, 10, 5, 3, 4, True, False, False)
+    be.float_quantize_nearest_bmm(a, b, got, S, S, S, 10, 5, 3, 4, True, False, False, order="cuda")
+    assert bits_equal(got[0], want[0]), "entry on the range-checked path"
+    assert bits_equal(got[1], want[1]), "entry left to the exact kernel"
+    a2 = (a[0] * 200).contiguous()
+    w2 = torch.zeros(S, S, device="cuda")
+    g2 = torch.full((S, S), float("nan"), device="cuda")
+    ref_cuda.float_quantize_nearest_mm(a2, b[0], w2, S, S, S, 2, 5, 2, 5, True, False, False)
+    be.float_quantize_nearest_mm(a2, b[0], g2, S, S, S, 2, 5, 2, 5, True, False, False, order="cuda")
+    assert bits_equal(g2, w2)
