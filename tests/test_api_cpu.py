@@ -146,3 +146,33 @@ def test_implicit_conv_needs_cuda_and_plain_nearest_formats():
 
     f = q.QAffineFormats(fwd_mac=(FloatingPoint(5, 10, True, False), FloatingPoint(4, 3, True, False)), fwd_rnd="nearest")
     assert not implicit_conv_eligible(f, torch.zeros(1))          # CPU tensor
+
+
+def test_k_panels_of_the_streamed_product():
+    """Host logic of float_mm_streamed's K-panel pipeline: the panels tile [0, K) in order, every boundary but the end
+    is a multiple of 8 (the group size of the CUDA accumulation order), the first panel is short, the last one is at
+    least 512 steps, and short K disables the pipeline."""
+    from mptorch_b200.quant.quant_function import _k_panels
+
+    assert _k_panels(0) is None and _k_panels(1000) is None and _k_panels(1791) is None
+    for K in (1792, 1800, 2048, 2053, 3000, 4096, 8191, 8192, 10000, 65536, 100003):
+        panels = _k_panels(K)
+        assert panels[0][0] == 0 and panels[-1][1] == K
+        assert all(a[1] == b[0] for a, b in zip(panels, panels[1:]))
+        assert all(k1 > k0 for k0, k1 in panels)
+        assert all(k1 % 8 == 0 for _, k1 in panels[:-1])
+        assert panels[0][1] == 256 and panels[-1][1] - panels[-1][0] >= 512
+        assert max(k1 - k0 for k0, k1 in panels) <= 3072
+
+
+def test_second_gradient_context_is_inert_on_cpu():
+    """The two-stream backward helper does nothing for CPU tensors (and when switched off)."""
+    import torch
+
+    from mptorch_b200.quant import functional as F
+
+    s = F._second_gradient(torch.zeros(3))
+    with s:
+        y = torch.ones(3) * 2
+    s.join(y, None)
+    assert s.side is None and float(y.sum()) == 6.0
