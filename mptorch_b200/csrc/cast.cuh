@@ -386,6 +386,20 @@ MPT_HD float fast_rn_nosub_rare(const FastRn& r, float x) {
     return u2f(qb);
 }
 
+// Third form, with no branch at all: the rounding without the settling rule, and a flag that the result was a nonzero
+// value below the smallest normal one, in which case the caller discards what it computed and redoes it on the exact
+// casters.  For the sum roundings of the GEMM's inner sums, which start from zero every eight steps: nothing has to be
+// saved to redo a group, and straight-line code lets the compiler interleave the thread's 32 independent chains.
+MPT_HD float fast_rn_nosub_flag(const FastRn& r, float x, uint32_t& rare) {
+    const uint32_t t = f2u(x);
+    const float m = u2f(t & 0x7F800000u);
+    const float y = fma_rn(m, r.k, x);
+    const float q = fma_rn(m, -r.k, y);
+    const uint32_t qb = f2u(q) | (t & 0x80000000u);                    // a zero keeps the input's sign
+    rare |= (qb + qb - 1u < 2u * (uint32_t)r.min_e_bits - 1u) ? 1u : 0u;
+    return u2f(qb);
+}
+
 // a / b rounded to nearest even, given r = RN(1 / b) (the correctly rounded reciprocal): the quotient estimate
 // a * r is within one ulp, the remainder a - b * q is exact in one FMA, and the correction FMA lands on the correctly
 // rounded quotient (Markstein's correction step).  Exact while 1 / b, the quotient and the remainder are normal

@@ -325,6 +325,13 @@ __device__ __forceinline__ float mac_exact(float acc, float a, float b, const An
     if (FMA) return cast_any(fma_rn(a, b, acc), fadd);
     return cast_any(add_rn(acc, cast_any(mul_rn(a, b), fmul)), fadd);
 }
+// Formats without subnormals, inner sums of the CUDA order: the sum rounding only flags a result that needs the
+// settling rule; the caller redoes the group of eight steps (which started from zero) on the exact casters.
+template <bool FMA>
+__device__ __forceinline__ float mac_fast_flag(float acc, float a, float b, const FastRn& radd, const FastRn& rmul, uint32_t& rare) {
+    if (FMA) return fast_rn_nosub_flag(radd, fma_rn(a, b, acc), rare);
+    return fast_rn_nosub_flag(radd, add_rn(acc, fast_rn_nosub(rmul, mul_rn(a, b))), rare);
+}
 template <bool FMA, bool NOSUB = false>
 __device__ __forceinline__ float mac_fast(float acc, float a, float b, const FastRn& radd, const FastRn& rmul) {
     if (NOSUB) {
@@ -388,9 +395,12 @@ static __device__ __noinline__ float4 mac_exact4(float4 acc, float a, float4 b, 
 }
 
 // `nk` (1..8) accumulation steps starting at slab row kbase, for the thread's 8x4 outputs.
-template <bool FMA, bool FAST, bool PACKED, bool ADDG, bool NOSUB = false>
-__device__ __forceinline__ void group_steps(float (&acc)[TM][TN], const float* As, const float* Bs, int kbase, int nk,
+// REDO (formats without subnormals, sums that start from zero): returns true when a sum rounding met a value that needs
+// the settling rule; the caller then zeroes the accumulators and runs the group on the exact path.
+template <bool FMA, bool FAST, bool PACKED, bool ADDG, bool NOSUB = false, bool REDO = false>
+__device__ __forceinline__ bool group_steps(float (&acc)[TM][TN], const float* As, const float* Bs, int kbase, int nk,
                                             int ty, int tx, const MmParams& p) {
+    uint32_t rare = 0u;
     if (FAST && nk == 8) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -409,6 +419,11 @@ __device__ __forceinline__ void group_steps(float (&acc)[TM][TN], const float* A
                         const float2 lo = mac_fast2<FMA, ADDG>(make_float2(acc[i][0], acc[i][1]), a2, make_float2(bv.x, bv.y), p.radd, p.rmul);
                         const float2 hi = mac_fast2<FMA, ADDG>(make_float2(acc[i][2], acc[i][3]), a2, make_float2(bv.z, bv.w), p.radd, p.rmul);
                         acc[i][0] = lo.x; acc[i][1] = lo.y; acc[i][2] = hi.x; acc[i][3] = hi.y;
+                    } else if (NOSUB && REDO) {
+                        acc[i][0] = mac_fast_flag<FMA>(acc[i][0], a, bv.x, p.radd, p.rmul, rare);
+                        acc[i][1] = mac_fast_flag<FMA>(acc[i][1], a, bv.y, p.radd, p.rmul, rare);
+                        acc[i][2] = mac_fast_flag<FMA>(acc[i][2], a, bv.z, p.radd, p.rmul, rare);
+                        acc[i][3] = mac_fast_flag<FMA>(acc[i][3], a, bv.w, p.radd, p.rmul, rare);
                     } else {
                         acc[i][0] = mac_fast<FMA, NOSUB>(acc[i][0], a, bv.x, p.radd, p.rmul);
                         acc[i][1] = mac_fast<FMA, NOSUB>(acc[i][1], a, bv.y, p.radd, p.rmul);
@@ -418,7 +433,7 @@ __device__ __forceinline__ void group_steps(float (&acc)[TM][TN], const float* A
                 }
             }
         }
-        return;
+        return rare != 0u;
     }
 #pragma unroll 1
     for (int k = 0; k < nk; ++k) {
@@ -437,6 +452,7 @@ __device__ __forceinline__ void group_steps(float (&acc)[TM][TN], const float* A
             }
         }
     }
+    return false;
 }
 
 // ---- Kahan-compensated accumulation (reference quant_cuda/mm_kernel.h:487-497, fma variant :600-608) --------------
@@ -784,8 +800,16 @@ __global__ void __launch_bounds__(THREADS, MINB) mm_kernel(const __grid_constant
             for (int g = 0; g * 8 < nk_tile; ++g) {
                 const int nk = (nk_tile - g * 8) < 8 ? (nk_tile - g * 8) : 8;
                 if (ALGO == ALGO_TILE8) {
-                    if (plan.ok) group_steps<FMA, true, PACKED, ADDG, NOSUB>(acc, as, bs, g * 8, nk, ty, tx, p);
-                    else group_steps<FMA, false, false, true>(acc, as, bs, g * 8, nk, ty, tx, p);
+                    if (plan.ok) {
+                        // without subnormals: a flagged group starts over from its zeros on the exact casters
+                        if (group_steps<FMA, true, PACKED, ADDG, NOSUB, NOSUB>(acc, as, bs, g * 8, nk, ty, tx, p)) {
+#pragma unroll
+                            for (int i = 0; i < TM; ++i)
+#pragma unroll
+                                for (int j = 0; j < TN; ++j) acc[i][j] = 0.0f;
+                            group_steps<FMA, false, false, true>(acc, as, bs, g * 8, nk, ty, tx, p);
+                        }
+                    } else group_steps<FMA, false, false, true>(acc, as, bs, g * 8, nk, ty, tx, p);
                     // fold the group into the outer sum
                     if (plan.ok && absmax_of(aux) < plan.acc_limit) {
 #pragma unroll

@@ -123,7 +123,12 @@ HC_API int64_t hc_sweep_fast_rn_nosub(int man, int exp, uint64_t first, uint64_t
         if (a != 0u && (a < 0x00800000u || e > lim)) continue;
         const float x = u2f(bits);
         const uint32_t want = f2u(cast_fp_nearest(x, f));
-        if (f2u(fast_rn_nosub(fast, x)) != want || f2u(fast_rn_nosub_rare(fast, x)) != want) { ++bad; if (bits < worst) worst = bits; }
+        uint32_t rare = 0u;
+        const uint32_t flagged = f2u(fast_rn_nosub_flag(fast, x, rare));
+        // the flagged form promises the exact result whenever it does not raise its flag, and must raise it exactly
+        // when the plain rounding lands on a nonzero value below the smallest normal one
+        const bool flag_ok = rare ? true : flagged == want;
+        if (f2u(fast_rn_nosub(fast, x)) != want || f2u(fast_rn_nosub_rare(fast, x)) != want || !flag_ok) { ++bad; if (bits < worst) worst = bits; }
     }
     if (first_bad) *first_bad = worst;
     return bad;
