@@ -12,13 +12,37 @@ namespace {
 constexpr int XT = 32;        // tile edge: 32 x 32 outputs, K slabs of 32
 constexpr int XPER = 4;       // outputs per thread: rows ty, ty + 8, ty + 16, ty + 24 of column tx
 
-// KIND 0: both formats are float formats, 2: both supernormal, 3: both binary8 (that caster alone is inlined);
-// KIND 1: any mixture (cast_any).
+// One format as this kernel rounds to it.  KIND 0: a float format, exact caster; 2: supernormal; 3: binary8 (that caster
+// alone is inlined); 1: any mixture (cast_any); 4: float formats the FP-pipe rounding covers, through its whole-domain
+// form (FullRn: what reaches this kernel with such formats are products whose operands ruled the range-checked path
+// out, and compensated sums of fp32-accumulating formats); 5: float formats without subnormals, the settling rounding
+// with the exact caster behind one compare for fp32 denormals, overflow, infinities and NaN.
+struct Rounding {
+    AnyFmt any;
+    FullRn full;
+    uint32_t span;
+    __device__ __forceinline__ static Rounding make(const AnyFmt& f) {
+        Rounding r;
+        r.any = f;
+        r.full = FullRn::make(f.fp);
+        const uint32_t top = r.full.ovf_from < r.full.exact_from ? r.full.ovf_from : r.full.exact_from;
+        r.span = top - 0x00800000u;
+        return r;
+    }
+};
 template <int KIND>
-__device__ __forceinline__ float round_to(float x, const AnyFmt& f) {
+__device__ __forceinline__ float round_to(float x, const Rounding& r) {
+    const AnyFmt& f = r.any;
     if (KIND == 0) return cast_fp_nearest(x, f.fp);
     if (KIND == 2) return cast_superfp(x, f.fp.man, f.fp.exp, f.bl, f.bu, f.fp.sat != 0);
     if (KIND == 3) return cast_binary8(x, f.P, f.is_signed != 0, f.policy, f.fp.sub != 0, RND_NEAREST, 0u, 0);
+    if (KIND == 4) return fmt_identity(f.fp) ? x : r.full(x);
+    if (KIND == 5) {
+        const uint32_t a = __float_as_uint(x) & 0x7FFFFFFFu;
+        if (a == 0u) return x;
+        if (a - 0x00800000u >= r.span) return cast_fp_nearest(x, f.fp);
+        return fast_rn_nosub(r.full.fast, x);
+    }
     return cast_any(x, f);
 }
 
@@ -46,6 +70,7 @@ __global__ void __launch_bounds__(256) exact_mm_kernel(const __grid_constant__ M
     float* C = p.c + batch * p.stride_c;
     const int gn = n0 + tx;
 
+    const Rounding qa = Rounding::make(p.gadd), qm = Rounding::make(p.gmul);
     float run[XPER], outer[XPER];       // the running (inner) sum; the outer sum of the CUDA order / the compensation term
 #pragma unroll
     for (int i = 0; i < XPER; ++i) {
@@ -75,19 +100,19 @@ __global__ void __launch_bounds__(256) exact_mm_kernel(const __grid_constant__ M
                 const float a = As[ty + 8 * i][k];
                 if (ALGO == ALGO_KAHAN) {
                     // y = Q(product - comp); t = Q(sum + y); comp = Q(Q(t - sum) - y); sum = t   (mm_kernel.h:457-520)
-                    const float y = FMA ? round_to<KIND>(fma_rn(a, b, -outer[i]), p.gadd)
-                                        : round_to<KIND>(add_rn(round_to<KIND>(mul_rn(a, b), p.gmul), -outer[i]), p.gadd);
-                    const float t = round_to<KIND>(add_rn(run[i], y), p.gadd);
-                    outer[i] = round_to<KIND>(add_rn(round_to<KIND>(add_rn(t, -run[i]), p.gadd), -y), p.gadd);
+                    const float y = FMA ? round_to<KIND>(fma_rn(a, b, -outer[i]), qa)
+                                        : round_to<KIND>(add_rn(round_to<KIND>(mul_rn(a, b), qm), -outer[i]), qa);
+                    const float t = round_to<KIND>(add_rn(run[i], y), qa);
+                    outer[i] = round_to<KIND>(add_rn(round_to<KIND>(add_rn(t, -run[i]), qa), -y), qa);
                     run[i] = t;
                 } else {
-                    run[i] = FMA ? round_to<KIND>(fma_rn(a, b, run[i]), p.gadd)
-                                 : round_to<KIND>(add_rn(run[i], round_to<KIND>(mul_rn(a, b), p.gmul)), p.gadd);
+                    run[i] = FMA ? round_to<KIND>(fma_rn(a, b, run[i]), qa)
+                                 : round_to<KIND>(add_rn(run[i], round_to<KIND>(mul_rn(a, b), qm)), qa);
                 }
             }
             if (ALGO == ALGO_TILE8 && ((k0 + k) & 7) == 7) {
 #pragma unroll
-                for (int i = 0; i < XPER; ++i) { outer[i] = round_to<KIND>(add_rn(outer[i], run[i]), p.gadd); run[i] = 0.0f; }
+                for (int i = 0; i < XPER; ++i) { outer[i] = round_to<KIND>(add_rn(outer[i], run[i]), qa); run[i] = 0.0f; }
             }
         }
         __syncthreads();
@@ -108,7 +133,11 @@ int launch_exact(const MmParams& p, int64_t batch, cudaStream_t st) {
     const int64_t cap = (int64_t)sm_count() * 8;
     const dim3 grid((unsigned)(tiles < cap ? tiles : cap));
     const int ka = p.gadd.kind, km = p.gmul.kind;          // run_mm sets gmul = gadd for the fused form
-    if (ka == FMT_FLOAT && km == FMT_FLOAT) exact_mm_kernel<ALGO, FMA, 0><<<grid, 256, 0, st>>>(p, batch);
+    const auto covered = [](const FpFmt& f) { return fast_rn_supported(f) || fmt_identity(f); };
+    if (ka == FMT_FLOAT && km == FMT_FLOAT && covered(p.gadd.fp) && covered(p.gmul.fp)) exact_mm_kernel<ALGO, FMA, 4><<<grid, 256, 0, st>>>(p, batch);
+    else if (ka == FMT_FLOAT && km == FMT_FLOAT && mm_fast_format_nosub(p.gadd.fp) && mm_fast_format_nosub(p.gmul.fp))
+        exact_mm_kernel<ALGO, FMA, 5><<<grid, 256, 0, st>>>(p, batch);
+    else if (ka == FMT_FLOAT && km == FMT_FLOAT) exact_mm_kernel<ALGO, FMA, 0><<<grid, 256, 0, st>>>(p, batch);
     else if (ka == FMT_SUPERFP && km == FMT_SUPERFP) exact_mm_kernel<ALGO, FMA, 2><<<grid, 256, 0, st>>>(p, batch);
     else if (ka == FMT_BINARY8 && km == FMT_BINARY8) exact_mm_kernel<ALGO, FMA, 3><<<grid, 256, 0, st>>>(p, batch);
     else exact_mm_kernel<ALGO, FMA, 1><<<grid, 256, 0, st>>>(p, batch);
