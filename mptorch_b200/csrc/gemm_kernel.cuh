@@ -376,6 +376,18 @@ template <bool FMA>
 static __device__ __noinline__ float4 mac_exact4(float4 acc, float a, float4 b, const MmParams* pp) {
     const AnyFmt& fa = pp->gadd;
     const AnyFmt& fm = pp->gmul;
+    if (pp->whole_ok) {
+        // formats the FP-pipe rounding covers: its whole-domain form (same bits as the exact caster on every input)
+        const MmParams& p = *pp;
+        if (FMA) {
+            acc.x = round_add(p, fma_rn(a, b.x, acc.x)); acc.y = round_add(p, fma_rn(a, b.y, acc.y));
+            acc.z = round_add(p, fma_rn(a, b.z, acc.z)); acc.w = round_add(p, fma_rn(a, b.w, acc.w));
+        } else {
+            acc.x = round_add(p, add_rn(acc.x, round_mul(p, mul_rn(a, b.x)))); acc.y = round_add(p, add_rn(acc.y, round_mul(p, mul_rn(a, b.y))));
+            acc.z = round_add(p, add_rn(acc.z, round_mul(p, mul_rn(a, b.z)))); acc.w = round_add(p, add_rn(acc.w, round_mul(p, mul_rn(a, b.w))));
+        }
+        return acc;
+    }
     if (fa.kind == FMT_FLOAT && (FMA || fm.kind == FMT_FLOAT)) {
         const FpFmt ga = fa.fp, gm = fm.fp;
         if (FMA) {
