@@ -985,7 +985,7 @@ def main() -> int:
 
     # ---- the other benchmark configurations, so that one driver-run line carries them: config 3 and the reductions
     # (HBM-bound kernels), config 4 (the GEMM sweep with its variants), config 5 (the training step, every N)
-    kernels = sweep = None
+    kernels = sweep = formats = None
     if extras and rank == 0 and world == 1:
         try:
             kernels = kernels_legs(dev, 10, 3, 1.0, with_reference=ref is not None)
@@ -996,6 +996,11 @@ def main() -> int:
             sweep = c4_sweep(dev)
         except Exception as ex:
             sweep = {"error": repr(ex)[:300]}
+        torch.cuda.empty_cache()
+        try:
+            formats = formats_sweep(dev)          # formats without subnormals and failed range checks, reference beside
+        except Exception as ex:
+            formats = {"error": repr(ex)[:300]}
         torch.cuda.empty_cache()
     block = None
     if extras:
@@ -1059,6 +1064,8 @@ def main() -> int:
             line["roofline_kernels"] = kernels
         if sweep is not None:
             line["c4_sweep"] = sweep
+        if formats is not None:
+            line["formats_sweep"] = formats
         if block is not None:
             line["block_step"] = block
         if world == 1 and not args.no_cpu_baseline:
