@@ -41,10 +41,10 @@ __device__ __noinline__ float exact_nearest(float x, FpFmt fmt) { return cast_fp
 struct Rounder {
     FullRn fast;
     FpFmt fmt;
-    int mode;                // 0 identity, 1 fast, 2 exact
+    int mode;                // 0 identity, 1 fast, 2 exact, 3 a float format without subnormals (fast in line<true> only)
     __device__ __forceinline__ float operator()(float x) const {
         if (mode == 0) return x;
-        if (mode == 2) return exact_nearest(x, fmt);
+        if (mode >= 2) return exact_nearest(x, fmt);
         if (fmt.exp == 8) {
             // formats with an 8-bit exponent: fp32 denormals and the largest magnitudes go to the exact caster; a
             // positive zero (the usual gradient of an unused embedding row) is its own rounding
@@ -62,23 +62,29 @@ struct Rounder {
     // sets `rare`; the caller then recomputes that element through operator().  Straight-line code lets the compiler
     // interleave the roundings of independent elements.
     uint32_t span;           // rare when (|x| bits - 0x00800000) >= span, zero excepted
-    uint32_t check;          // 1 where that test applies (mode 1, 8-bit exponent)
+    uint32_t check;          // 1 where that test applies (mode 1 with an 8-bit exponent; mode 3)
+    // NS: the kernel instantiation for formats without subnormals (modes 0 and 3): the settling rounding, with fp32
+    // denormals, -0, overflow, infinities and NaN left to the redo.
+    template <bool NS>
     __device__ __forceinline__ float line(float x, uint32_t& rare) const {
         const uint32_t t = f2u(x), a = t & 0x7FFFFFFFu;
         rare |= ((a - 0x00800000u >= span) && t != 0u) ? check : 0u;
-        const float y = (t == 0u) ? x : fast.line(x);
+        const float y = (t == 0u) ? x : (NS ? fast_rn_nosub(fast.fast, x) : fast.line(x));
         return mode == 0 ? x : y;
     }
-    __device__ __forceinline__ float line3(float x, float y, float z, uint32_t& rare) const { return line(add_rn(x, mul_rn(y, z)), rare); }
+    template <bool NS>
+    __device__ __forceinline__ float line3(float x, float y, float z, uint32_t& rare) const { return line<NS>(add_rn(x, mul_rn(y, z)), rare); }
 };
 
 Rounder make_rounder(int enabled, int man, int exp, int sub, int sat) {
     Rounder r;
     r.fmt = make_fmt(enabled ? man : 23, enabled ? exp : 8, sub, sat);
     r.fast = FullRn::make(r.fmt);
-    r.mode = !enabled ? 0 : (fast_rn_supported(r.fmt) ? 1 : 2);
-    r.check = (r.mode == 1 && r.fmt.exp == 8) ? 1u : 0u;
-    r.span = r.check ? r.fast.exact_from - 0x00800000u : 0xFFFFFFFFu;
+    const bool nosub = !r.fmt.sub && r.fmt.man <= 21 && r.fmt.exp >= 2;
+    r.mode = !enabled ? 0 : (fast_rn_supported(r.fmt) ? 1 : (nosub ? 3 : 2));
+    r.check = ((r.mode == 1 && r.fmt.exp == 8) || r.mode == 3) ? 1u : 0u;
+    const uint32_t top = r.fast.ovf_from < r.fast.exact_from ? r.fast.ovf_from : r.fast.exact_from;
+    r.span = r.mode == 3 ? top - 0x00800000u : (r.check ? r.fast.exact_from - 0x00800000u : 0xFFFFFFFFu);
     return r;
 }
 
@@ -158,15 +164,17 @@ __device__ __forceinline__ void zero4(float* dst) { dst[0] = dst[1] = dst[2] = d
 
 #define MPT_EACH for (int e = 0; e < kOptPer; ++e)
 
+template <bool NS>
 __device__ __forceinline__ void compensated_line(float& p, float& comp, float d, float scale, const Rounder& qa, uint32_t& rare) {
-    const float y = -qa.line3(comp, d, scale, rare);
-    const float s = qa.line3(p, y, 1.0f, rare);
-    comp = qa.line3(qa.line3(s, p, -1.0f, rare), y, -1.0f, rare);
+    const float y = -qa.line3<NS>(comp, d, scale, rare);
+    const float s = qa.line3<NS>(p, y, 1.0f, rare);
+    comp = qa.line3<NS>(qa.line3<NS>(s, p, -1.0f, rare), y, -1.0f, rare);
     p = s;
 }
 
 // The QSGD step over the kOptPer elements a thread holds, one phase at a time: the configuration's branches sit
 // between the phases, each phase is straight-line code over independent elements.  Same operations as sgd_elem.
+template <bool NS>
 __device__ __forceinline__ uint32_t sgd_block(float (&p)[kOptPer], float (&g)[kOptPer], float (&m)[kOptPer], float (&c)[kOptPer], bool first,
                                               const SgdArgs& a) {
     uint32_t rare = 0u;
@@ -179,14 +187,14 @@ __device__ __forceinline__ uint32_t sgd_block(float (&p)[kOptPer], float (&g)[kO
         if (first) {
             if (a.has_momentum_quant) {
 #pragma unroll
-                MPT_EACH m[e] = a.qm.line3(g[e], 0.0f, 0.0f, rare);
+                MPT_EACH m[e] = a.qm.line3<NS>(g[e], 0.0f, 0.0f, rare);
             } else {
 #pragma unroll
                 MPT_EACH m[e] = g[e];
             }
         } else if (a.has_momentum_quant) {
 #pragma unroll
-            MPT_EACH m[e] = a.qm.line3(mul_rn(m[e], a.momentum), g[e], a.one_minus_dampening, rare);
+            MPT_EACH m[e] = a.qm.line3<NS>(mul_rn(m[e], a.momentum), g[e], a.one_minus_dampening, rare);
         } else {
 #pragma unroll
             MPT_EACH m[e] = fma_rn(g[e], a.one_minus_dampening, mul_rn(m[e], a.momentum));
@@ -205,10 +213,10 @@ __device__ __forceinline__ uint32_t sgd_block(float (&p)[kOptPer], float (&g)[kO
     if (a.has_acc_quant) {
         if (!a.compensated) {
 #pragma unroll
-            MPT_EACH p[e] = a.qa.line3(p[e], d[e], a.neg_lr, rare);
+            MPT_EACH p[e] = a.qa.line3<NS>(p[e], d[e], a.neg_lr, rare);
         } else {
 #pragma unroll
-            MPT_EACH compensated_line(p[e], c[e], d[e], a.lr, a.qa, rare);
+            MPT_EACH compensated_line<NS>(p[e], c[e], d[e], a.lr, a.qa, rare);
         }
     } else if (!a.compensated) {
 #pragma unroll
@@ -242,7 +250,7 @@ __device__ __noinline__ void sgd_redo(float* P, float* G, float* M, float* C, in
 
 // LINE: neither quantizer needs the exact caster throughout (the host decides), so aligned full chunks take the
 // vector path with straight-line roundings.
-template <bool LINE>
+template <bool LINE, bool NS = false>
 __global__ void __launch_bounds__(kThreads) qsgd_kernel(const __grid_constant__ OptTable t, const __grid_constant__ SgdArgs a) {
     const int k = find_tensor(t, blockIdx.x);
     float* __restrict__ P = t.param[k];
@@ -265,7 +273,7 @@ __global__ void __launch_bounds__(kThreads) qsgd_kernel(const __grid_constant__ 
             if (rd_m) ld4(M + i, m + 4 * h); else zero4(m + 4 * h);
             if (use_c) ld4(C + i, c + 4 * h); else zero4(c + 4 * h);
         }
-        if (sgd_block(p, g, m, c, first, a)) { sgd_redo(P, G, M, C, base, first, a); return; }
+        if (sgd_block<NS>(p, g, m, c, first, a)) { sgd_redo(P, G, M, C, base, first, a); return; }
 #pragma unroll
         for (int h = 0; h < kOptVecs; ++h) {
             const int64_t i = base + (int64_t)h * (kThreads * 4);
@@ -325,6 +333,7 @@ __device__ __forceinline__ void adam_elem(float& p, float g, float& m, float& v,
 }
 
 // The QAdamW step over a thread's elements, phase by phase (see sgd_block).  Same operations as adam_elem.
+template <bool NS>
 __device__ __forceinline__ uint32_t adam_block(float (&p)[kOptPer], const float (&g)[kOptPer], float (&m)[kOptPer], float (&v)[kOptPer],
                                                float (&c)[kOptPer], float (&vm)[kOptPer], const AdamArgs& a) {
     uint32_t rare = 0u;
@@ -332,8 +341,8 @@ __device__ __forceinline__ uint32_t adam_block(float (&p)[kOptPer], const float 
     if (a.has_momentum_quant) {
 #pragma unroll
         MPT_EACH {
-            m[e] = a.qm.line3(mul_rn(m[e], a.beta1), g[e], a.one_minus_beta1, rare);
-            v[e] = a.qm.line3(mul_rn(v[e], a.beta2), mul_rn(g[e], g[e]), a.one_minus_beta2, rare);
+            m[e] = a.qm.line3<NS>(mul_rn(m[e], a.beta1), g[e], a.one_minus_beta1, rare);
+            v[e] = a.qm.line3<NS>(mul_rn(v[e], a.beta2), mul_rn(g[e], g[e]), a.one_minus_beta2, rare);
         }
     } else {
 #pragma unroll
@@ -363,10 +372,10 @@ __device__ __forceinline__ uint32_t adam_block(float (&p)[kOptPer], const float 
     if (a.has_acc_quant) {
         if (!a.compensated) {
 #pragma unroll
-            MPT_EACH p[e] = a.qa.line3(fma_rn(a.neg_step_size, q[e], p[e]), 0.0f, 0.0f, rare);
+            MPT_EACH p[e] = a.qa.line3<NS>(fma_rn(a.neg_step_size, q[e], p[e]), 0.0f, 0.0f, rare);
         } else {
 #pragma unroll
-            MPT_EACH compensated_line(p[e], c[e], a.qa.line3(q[e], 0.0f, 0.0f, rare), a.step_size, a.qa, rare);
+            MPT_EACH compensated_line<NS>(p[e], c[e], a.qa.line3<NS>(q[e], 0.0f, 0.0f, rare), a.step_size, a.qa, rare);
         }
     } else if (!a.compensated) {
 #pragma unroll
@@ -397,7 +406,7 @@ __device__ __noinline__ void adam_redo(float* P, const float* G, float* M, float
     }
 }
 
-template <bool LINE>
+template <bool LINE, bool NS = false>
 __global__ void __launch_bounds__(kThreads) qadamw_kernel(const __grid_constant__ OptTable t, const __grid_constant__ AdamArgs a) {
     const int k = find_tensor(t, blockIdx.x);
     float* __restrict__ P = t.param[k];
@@ -422,7 +431,7 @@ __global__ void __launch_bounds__(kThreads) qadamw_kernel(const __grid_constant_
             if (use_c) ld4(C + i, c + 4 * h); else zero4(c + 4 * h);
             if (use_vm) ld4(VM + i, vm + 4 * h); else zero4(vm + 4 * h);
         }
-        if (adam_block(p, g, m, v, c, vm, a)) { adam_redo(P, G, M, V, C, VM, base, a); return; }
+        if (adam_block<NS>(p, g, m, v, c, vm, a)) { adam_redo(P, G, M, V, C, VM, base, a); return; }
 #pragma unroll
         for (int h = 0; h < kOptVecs; ++h) {
             const int64_t i = base + (int64_t)h * (kThreads * 4);
@@ -553,8 +562,9 @@ int mpt_qsgd_step(const mpt_optim_tensor* tensors, int count, float lr, float mo
     a.has_momentum_quant = momentum_quant != 0; a.has_acc_quant = acc_quant != 0;
     a.qm = make_rounder(momentum_quant, man_mom, exp_mom, subnormals, saturate);
     a.qa = make_rounder(acc_quant, man_acc, exp_acc, subnormals, saturate);
-    const bool line = a.qm.mode != 2 && a.qa.mode != 2;
-    return launch_optim(tensors, count, a, line ? qsgd_kernel<true> : qsgd_kernel<false>, need_m, need_c, false, false, as_stream(stream), who);
+    const bool line = a.qm.mode <= 1 && a.qa.mode <= 1;
+    const bool ns = (a.qm.mode == 0 || a.qm.mode == 3) && (a.qa.mode == 0 || a.qa.mode == 3) && !line;
+    return launch_optim(tensors, count, a, line ? qsgd_kernel<true> : (ns ? qsgd_kernel<true, true> : qsgd_kernel<false>), need_m, need_c, false, false, as_stream(stream), who);
 }
 
 int mpt_qadamw_step(const mpt_optim_tensor* tensors, int count, float beta1, float beta2, float one_minus_beta1,
@@ -573,8 +583,9 @@ int mpt_qadamw_step(const mpt_optim_tensor* tensors, int count, float beta1, flo
     a.has_momentum_quant = momentum_quant != 0; a.has_acc_quant = acc_quant != 0;
     a.qm = make_rounder(momentum_quant, man_mom, exp_mom, subnormals, saturate);
     a.qa = make_rounder(acc_quant, man_acc, exp_acc, subnormals, saturate);
-    const bool line = a.qm.mode != 2 && a.qa.mode != 2;
-    return launch_optim(tensors, count, a, line ? qadamw_kernel<true> : qadamw_kernel<false>, true, true, compensated != 0, amsgrad != 0, as_stream(stream), who);
+    const bool line = a.qm.mode <= 1 && a.qa.mode <= 1;
+    const bool ns = (a.qm.mode == 0 || a.qm.mode == 3) && (a.qa.mode == 0 || a.qa.mode == 3) && !line;
+    return launch_optim(tensors, count, a, line ? qadamw_kernel<true> : (ns ? qadamw_kernel<true, true> : qadamw_kernel<false>), true, true, compensated != 0, amsgrad != 0, as_stream(stream), who);
 }
 
 size_t mpt_scale_quantize_workspace_bytes(int64_t matrices) { return sizeof(uint32_t) * (size_t)(matrices < 1 ? 1 : matrices); }

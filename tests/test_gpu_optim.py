@@ -279,7 +279,7 @@ def _awkward(n, g, scale):
 
 
 @pytest.mark.parametrize("opt", ["sgd", "sgd_comp", "adamw", "adamw_comp"])
-@pytest.mark.parametrize("fmt", [(8, 7), (8, 3), (5, 10)])
+@pytest.mark.parametrize("fmt", [(8, 7), (8, 3), (5, 10), (8, 7, False), (5, 10, False), (4, 3, False)])
 def test_fused_steps_with_denormals_extremes_and_nonfinite_values(opt, fmt):
     """Whole 2048-element chunks (the vector path of the fused kernels) holding inputs that the straight-line rounding
     hands to the exact caster; the per-tensor sequence of torch kernels and quantizer calls is the reference."""
@@ -287,7 +287,7 @@ def test_fused_steps_with_denormals_extremes_and_nonfinite_values(opt, fmt):
     from mptorch_b200.optim import QAdamW, QSGD, fma_quantizer
 
     g = torch.Generator().manual_seed(21)
-    q = fma_quantizer(FloatingPoint(fmt[0], fmt[1], True, True))
+    q = fma_quantizer(FloatingPoint(fmt[0], fmt[1], fmt[2] if len(fmt) > 2 else True, True))      # third entry: subnormals
     n = 3 * 2048 + 17
     base = _awkward(n, g, 1.0)
     pa, pb = [torch.nn.Parameter(base.clone().cuda())], [torch.nn.Parameter(base.clone().cuda())]
